@@ -1,0 +1,187 @@
+/* ojas-cuda for B200: the C-ABI a Rust `impl Backend for CudaBackend` binds.
+ *
+ * One entry point per `ojas_core::Backend` method that one nanolab GPT training
+ * step exercises (trait declarations: ojas-core/src/backend.rs:889-2634; the
+ * reference's own CUDA backend refuses every one of them with `Unsupported`,
+ * ojas-cuda/src/backend.rs:194-515). Plain pointers and sizes only.
+ *
+ * Conventions
+ *  - Every call returns an ojc_status; the values are 1:1 with OjasError's
+ *    variants (ojas-core/src/error.rs:18-118). ojc_last_error() gives the detail.
+ *  - There is no host fallback: a device that cannot be opened is an explicit
+ *    error from ojc_open (AGENTS.md:42-44 of the reference).
+ *  - Tensors are descriptors over device memory obtained from ojc_alloc (which
+ *    charges the backend's byte budget, as Tensor::from_device_reserved does,
+ *    ojas-core/src/tensor.rs:1026). Outputs are caller-allocated descriptors.
+ *  - dtype F32 is the storage of record; BF16 operands are accepted where
+ *    Backend::bf16_operands() would say so (ojas-core/src/backend.rs:1029): a
+ *    matmul-class op given BF16 operands runs on the tcgen05 tensor path with
+ *    f32 accumulation, given F32 operands it runs the f32 tier.
+ *  - Non-finite values found on the device are deferred: kernels raise a fault
+ *    word that ojc_sync / ojc_download / ojc_clip_grad_norm report as
+ *    OJC_ERR_NON_FINITE naming the first op (ojas-core/src/backend.rs:963-973).
+ *  - A backend handle is single-owner-thread; all work is ordered on one stream
+ *    (the reference runtime is `!Send`, ojas-cuda/src/backend.rs:27-31).
+ */
+#ifndef OJAS_CUDA_H
+#define OJAS_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ojc_status {
+  OJC_OK = 0,
+  OJC_ERR_SHAPE = 1,
+  OJC_ERR_DTYPE = 2,
+  OJC_ERR_OUT_OF_RANGE = 3,
+  OJC_ERR_NON_FINITE = 4,
+  OJC_ERR_UNSUPPORTED_HEAD_DIM = 5,
+  OJC_ERR_CAPACITY_EXCEEDED = 6,
+  OJC_ERR_POISONED = 7,
+  OJC_ERR_DEVICE_LOST = 8,
+  OJC_ERR_WAIT_TIMEOUT = 9,
+  OJC_ERR_BACKEND = 10,
+  OJC_ERR_UNSUPPORTED = 11,
+  OJC_ERR_PLACEMENT = 12,
+  OJC_ERR_NO_DEVICE = 13
+} ojc_status;
+
+typedef enum ojc_dtype { OJC_F32 = 0, OJC_BF16 = 1, OJC_F16 = 2, OJC_U32 = 3 } ojc_dtype; /* ojas-core/src/dtype.rs:5-10 */
+
+#define OJC_MAX_RANK 6
+/* Shape + dtype + device pointer (ojas-core/src/tensor.rs:20-55). Strides are in
+ * elements; every op wants contiguous row-major tensors except the SDPA family,
+ * which reads q/k/v/out through the strides (so a permuted view costs no copy). */
+typedef struct ojc_tensor {
+  void* data;
+  int32_t dtype;
+  int32_t rank;
+  int64_t shape[OJC_MAX_RANK];
+  int64_t stride[OJC_MAX_RANK];
+} ojc_tensor;
+
+typedef struct ojc_backend ojc_backend;
+
+/* ---- lifetime, memory, transfers: BackendCore::{upload,download,sync} (backend.rs:917,939,971);
+ *      open errors keep their kind (ojas-cuda/README.md:16-19). */
+ojc_status ojc_open(int32_t device_ordinal, uint64_t budget_bytes, ojc_backend** out);
+ojc_status ojc_close(ojc_backend* be);
+const char* ojc_last_error(void);
+const char* ojc_status_name(int32_t status);
+ojc_status ojc_alloc(ojc_backend* be, uint64_t bytes, void** out);              /* charges the budget (budget.rs:65) */
+ojc_status ojc_free(ojc_backend* be, void* ptr);                                /* refunds it */
+ojc_status ojc_budget(ojc_backend* be, uint64_t* cap, uint64_t* live, uint64_t* peak); /* Budget::{cap,live,peak_bytes} budget.rs:19-240 */
+ojc_status ojc_reset_peak(ojc_backend* be);
+ojc_status ojc_upload(ojc_backend* be, void* dst_device, const void* src_host, uint64_t bytes);
+ojc_status ojc_download(ojc_backend* be, void* dst_host, const void* src_device, uint64_t bytes); /* counts a readback (budget.rs:201) */
+ojc_status ojc_sync(ojc_backend* be);                                           /* bounded wait; reports a deferred fault */
+ojc_status ojc_set_sync_timeout_ms(ojc_backend* be, uint64_t ms);               /* RuntimeConfig::sync_timeout, ojas-cuda/src/runtime.rs:76 */
+ojc_status ojc_readbacks(ojc_backend* be, uint64_t* count);
+void* ojc_stream(ojc_backend* be);                                              /* the cudaStream_t all work is ordered on */
+ojc_status ojc_fill_zero(ojc_backend* be, void* ptr, uint64_t bytes);
+uint64_t ojc_kernel_launches(ojc_backend* be);                                  /* kernels launched by this backend so far */
+
+/* ---- casts: BackendCore::{cast_bf16,to_bf16,to_f32} (backend.rs:982,1042,1070); RNE on the integer bits,
+ *      NaN keeps sign + payload and sets the quiet bit (autocast.rs:89-96). */
+ojc_status ojc_cast_bf16(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);  /* F32 -> F32 storage holding bf16-exact values */
+ojc_status ojc_to_bf16(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);    /* F32 -> BF16 */
+ojc_status ojc_to_f32(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);     /* BF16 -> F32 */
+
+/* ---- BackendModule ops of the block (backend.rs:1609-2634) */
+ojc_status ojc_embedding_forward(ojc_backend* be, const ojc_tensor* table, const ojc_tensor* ids, ojc_tensor* out);          /* :1615 */
+ojc_status ojc_embedding_backward(ojc_backend* be, const ojc_tensor* table_shape, const ojc_tensor* ids, const ojc_tensor* grad_out, ojc_tensor* grad_table); /* :1621 */
+ojc_status ojc_linear_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, ojc_tensor* y);               /* :1628 y = x W^T */
+ojc_status ojc_linear_backward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, const ojc_tensor* grad_y, ojc_tensor* grad_x, ojc_tensor* grad_w); /* :1631 */
+ojc_status ojc_linear_backward_input(ojc_backend* be, const ojc_tensor* weight, const ojc_tensor* grad_y, ojc_tensor* grad_x); /* :1648 */
+ojc_status ojc_rms_norm_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, float eps, ojc_tensor* y);   /* :1658 */
+ojc_status ojc_rms_norm_backward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, const ojc_tensor* grad_y, float eps, ojc_tensor* grad_x, ojc_tensor* grad_w); /* :1666 */
+ojc_status ojc_rope_half_split_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* cos_t, const ojc_tensor* sin_t, ojc_tensor* y);  /* :1674 x [B,T,H,dh], tables [T,dh] */
+ojc_status ojc_rope_half_split_backward(ojc_backend* be, const ojc_tensor* grad_y, const ojc_tensor* cos_t, const ojc_tensor* sin_t, ojc_tensor* grad_x); /* :1681 */
+ojc_status ojc_rms_qk_norm_forward(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* q_weight, const ojc_tensor* k_weight, float eps, ojc_tensor* q_out, ojc_tensor* k_out); /* :1688 per-head norm over the last axis */
+ojc_status ojc_rms_qk_norm_backward(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* q_weight, const ojc_tensor* k_weight, const ojc_tensor* grad_q, const ojc_tensor* grad_k, float eps, ojc_tensor* grad_q_in, ojc_tensor* grad_k_in, ojc_tensor* grad_q_weight, ojc_tensor* grad_k_weight); /* :1700 */
+ojc_status ojc_value_residual_blend_forward(ojc_backend* be, const ojc_tensor* v, const ojc_tensor* v0, const ojc_tensor* lambda, ojc_tensor* y); /* :1907 */
+ojc_status ojc_value_residual_blend_backward(ojc_backend* be, const ojc_tensor* v, const ojc_tensor* v0, const ojc_tensor* lambda, const ojc_tensor* grad_y, ojc_tensor* grad_v, ojc_tensor* grad_v0, ojc_tensor* grad_lambda); /* :1914 */
+ojc_status ojc_permute(ojc_backend* be, const ojc_tensor* x, const int32_t* dims, int32_t ndims, ojc_tensor* y);            /* :1131 only [0,2,1,3] on the path */
+/* window < 0: full causal. q [B,H,T,dh]; k,v [B,Hkv,T,dh]; lse [B,H,T] F32. (:1753,1767,1781) */
+ojc_status ojc_causal_sdpa_forward(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, int64_t window, ojc_tensor* out, ojc_tensor* lse);
+ojc_status ojc_causal_sdpa_backward(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const ojc_tensor* lse, const ojc_tensor* grad_out, int64_t window, ojc_tensor* grad_q, ojc_tensor* grad_k, ojc_tensor* grad_v);
+ojc_status ojc_causal_sdpa_backward_recompute(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* grad_out, int64_t window, ojc_tensor* grad_q, ojc_tensor* grad_k, ojc_tensor* grad_v);
+/* scales (optional, [rows,H] F32) is the saved sigmoid of `_forward_saving` (:1860,1879) */
+ojc_status ojc_per_head_sigmoid_gate_forward(ojc_backend* be, const ojc_tensor* input, const ojc_tensor* weight, const ojc_tensor* bias, const ojc_tensor* attn, ojc_tensor* out, ojc_tensor* scales);
+/* saved_scales optional (`_backward_saved`, :1868,1894) */
+ojc_status ojc_per_head_sigmoid_gate_backward(ojc_backend* be, const ojc_tensor* input, const ojc_tensor* weight, const ojc_tensor* bias, const ojc_tensor* attn, const ojc_tensor* grad_out, const ojc_tensor* saved_scales, ojc_tensor* grad_input, ojc_tensor* grad_weight, ojc_tensor* grad_bias, ojc_tensor* grad_attn);
+ojc_status ojc_silu_forward(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);                                           /* :1151 */
+ojc_status ojc_silu_backward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* grad_y, ojc_tensor* grad_x);            /* :1153 */
+ojc_status ojc_mul_forward(ojc_backend* be, const ojc_tensor* a, const ojc_tensor* b, ojc_tensor* y);                        /* :1155 */
+ojc_status ojc_mul_backward(ojc_backend* be, const ojc_tensor* a, const ojc_tensor* b, const ojc_tensor* grad_y, ojc_tensor* grad_a, ojc_tensor* grad_b); /* :1158 */
+ojc_status ojc_residual_add_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* y, ojc_tensor* out);             /* :1165 */
+ojc_status ojc_residual_add_backward(ojc_backend* be, const ojc_tensor* grad_out, ojc_tensor* grad_x, ojc_tensor* grad_y);   /* :1168 two copies */
+/* CeChunk only bounds the reference's scratch; here it bounds the logits tile rows (cols are never chunked). has_ignore/ignore = Option<u32>.
+ * grad_input / grad_weight may be NULL (CeGrads, backend.rs:3081-3136). loss: F32 [1]. (:2513) */
+ojc_status ojc_linear_cross_entropy_mean(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, int64_t chunk_rows, int64_t chunk_cols, ojc_tensor* loss, ojc_tensor* grad_input, ojc_tensor* grad_weight);
+ojc_status ojc_cross_entropy_mean_forward(ojc_backend* be, const ojc_tensor* logits, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, ojc_tensor* loss);      /* :2452 */
+ojc_status ojc_cross_entropy_mean_backward(ojc_backend* be, const ojc_tensor* logits, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, ojc_tensor* grad_logits); /* :2461 */
+ojc_status ojc_argmax_rows(ojc_backend* be, const ojc_tensor* x, ojc_tensor* out_u32);                                       /* :1525 ties -> lowest column */
+
+/* ---- gradient plumbing and optimizers */
+ojc_status ojc_accumulate_grad(ojc_backend* be, ojc_tensor* acc, const ojc_tensor* grad);                                    /* :1483 acc += grad */
+ojc_status ojc_scale_grad(ojc_backend* be, ojc_tensor* grad, float scale);                                                   /* :1502 */
+/* Global L2 norm over `count` F32 tensors, then scale by min(1, max/(norm+1e-6)) only if < 1 (:1471; clip_scale :277-303).
+ * One sync point: returns the norm on the host and reports any deferred fault. */
+ojc_status ojc_clip_grad_norm(ojc_backend* be, ojc_tensor* const* grads, int64_t count, float max_norm, float* norm_out);
+typedef struct ojc_adamw_config { double lr, beta1, beta2, eps, weight_decay; } ojc_adamw_config;                            /* AdamWConfig backend.rs:494 */
+/* In place on param, m, v. The 7 f32 words are formed inside from step_before + config (AdamWScalars, backend.rs:371-476).
+ * bf16_mirror (optional, BF16, same shape) is refreshed with the new parameter. */
+ojc_status ojc_adamw_step(ojc_backend* be, ojc_tensor* param, const ojc_tensor* grad, ojc_tensor* m, ojc_tensor* v, uint64_t step_before, const ojc_adamw_config* cfg, ojc_tensor* bf16_mirror); /* :2470 */
+typedef struct ojc_muon_config { double lr, momentum, weight_decay; int32_t nesterov; int32_t ns5_bf16; } ojc_muon_config;   /* MuonNs5Config backend.rs:548 */
+ojc_status ojc_muon_ns5_step(ojc_backend* be, ojc_tensor* param, const ojc_tensor* grad, ojc_tensor* momentum, const ojc_muon_config* cfg, ojc_tensor* bf16_mirror); /* :2485 */
+ojc_status ojc_optimizer_scratch_bytes(ojc_backend* be, int32_t kind /*0 AdamW, 1 Muon*/, int64_t rows, int64_t cols, uint64_t* bytes); /* :953 */
+
+/* ---- whole-step driver: the op sequence of Trainer::step (ojas-model/src/trainer.rs:672-1046) replayed in C++ over
+ *      the entry points above, so the path can be driven end to end without the Rust host. */
+typedef struct ojc_model_spec {            /* ModelSpec, ojas-model/src/spec.rs:45 */
+  int64_t vocab, n_embd, n_layer, n_head, n_kv_head, head_dim, hidden, max_seq;
+  int64_t window;                          /* -1: full causal */
+  double rope_base;
+  float rms_eps;
+} ojc_model_spec;
+typedef struct ojc_train_config {          /* TrainConfig, ojas-model/src/trainer.rs:100-172 */
+  int32_t autocast_bf16;                   /* 0: f32 tier, 1: bf16 autocast (Autocast<B>, autocast.rs:464) */
+  int32_t optimizer;                       /* 0: AdamW on every tensor (lr = adam_lr, wd = adam_weight_decay); 1: Muon NS5 on rank-2 hidden weights + AdamW(wd 0) elsewhere (ojas-cpu/src/train.rs:54-62) */
+  double adam_lr, adam_beta1, adam_beta2, adam_eps, adam_weight_decay;
+  double matrix_lr, muon_momentum, muon_weight_decay;
+  int32_t ns5_bf16;
+  float grad_clip;                         /* <= 0: no clipping */
+  int32_t has_ignore; uint32_t ignore_index;
+  int64_t ce_chunk_rows;                   /* rows of one fused-CE logits tile (0: default) */
+  float loss_seed;                         /* backward seed w_i (MicroWeights, trainer.rs:1083-1119); 1/world under data parallelism */
+} ojc_train_config;
+typedef struct ojc_step_report { float loss; float grad_norm; uint64_t step; uint64_t tokens; } ojc_step_report; /* StepReport trainer.rs:281-297 */
+typedef struct ojc_trainer ojc_trainer;
+ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const ojc_train_config* cfg, int64_t batch, int64_t seq, ojc_trainer** out);
+ojc_status ojc_trainer_close(ojc_trainer* tr);
+int64_t ojc_trainer_param_count(ojc_trainer* tr);
+ojc_status ojc_trainer_param_info(ojc_trainer* tr, int64_t index, char* name, int64_t name_cap, int32_t* rank, int64_t* shape2, int32_t* group, int32_t* trains);
+ojc_status ojc_trainer_set_param(ojc_trainer* tr, int64_t index, const float* host, uint64_t count);   /* also refreshes the bf16 mirror */
+ojc_status ojc_trainer_get_param(ojc_trainer* tr, int64_t index, float* host, uint64_t count);
+ojc_status ojc_trainer_get_grad(ojc_trainer* tr, int64_t index, float* host, uint64_t count);          /* after ojc_trainer_gradients */
+/* forward + fused CE + backward on host ids/targets [batch*seq] (copied in from the caller's pinned or pageable memory);
+ * gradients stay on the device. loss_out may be NULL (no readback). */
+ojc_status ojc_trainer_gradients(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, float* loss_out);
+ojc_status ojc_trainer_gradients_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev); /* inputs already resident */
+ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out);                                   /* clip + optimizer, step += 1 */
+ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, ojc_step_report* report); /* gradients + apply + the one loss readback */
+ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev, ojc_step_report* report);
+ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* logits_host);          /* forward_logits, block.rs:407-416; [batch*seq, vocab] */
+/* Data-parallel extension (new; the reference has no distributed code): gradients live in contiguous buckets; the
+ * caller all-reduces each bucket (NCCL) between ojc_trainer_gradients and ojc_trainer_apply. */
+int64_t ojc_trainer_bucket_count(ojc_trainer* tr);
+ojc_status ojc_trainer_bucket(ojc_trainer* tr, int64_t index, void** device_ptr, uint64_t* floats);
+ojc_status ojc_trainer_bucket_ready_event(ojc_trainer* tr, int64_t index, void** cuda_event);          /* recorded when the bucket's last gradient is written */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

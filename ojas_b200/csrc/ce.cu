@@ -1,0 +1,231 @@
+// Mean cross-entropy over logits, and the fused tied-head form
+// linear_cross_entropy_mean that never holds [N, V] logits: rows are processed
+// in tiles (logits tile -> row statistics -> d(logits) -> dX, dW GEMMs).
+//
+// Per row (ojas-cpu/src/pointwise.rs:2329-2390, fused_ce.rs:290-452):
+//   loss_n = max + ln(sum exp(z - max)) - z[target];  G = (softmax - onehot) / n_valid
+// A row whose target holds the maximum and whose sum rounds to 1 uses the
+// target-excluded form: loss = log1p(s), G_target = -(s / (1 + s)) / n_valid with
+// s = sum over the other classes (the softmax-collapse rule, pointwise.rs:2300-2307).
+// Rows whose target equals ignore_index contribute nothing and get a zero gradient.
+#include "ce.cuh"
+#include "common.cuh"
+#include "dispatch.cuh"
+#include "gemm.cuh"
+#include "linear.cuh"
+
+namespace {
+
+// valid[0] = number of non-ignored targets; a target outside the vocabulary raises the range fault.
+__global__ void ce_count_kernel(const uint32_t* __restrict__ targets, int64_t rows, int has_ignore, uint32_t ignore, int64_t vocab, uint32_t* __restrict__ valid,
+                                uint32_t* fault) {
+  __shared__ uint32_t red[32];
+  uint32_t cnt = 0;
+  for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) {
+    uint32_t t = targets[i];
+    if (has_ignore && t == ignore) continue;
+    if (t >= vocab) { raise_fault(fault, OP_ID_RANGE); continue; }
+    ++cnt;
+  }
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t total = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += red[w];
+    valid[0] = total;
+    if (total == 0) raise_fault(fault, OP_CE);  // an all-ignored batch has no mean (fused_ce.rs:148-150)
+  }
+}
+
+// One block per row. terms[row] = the row's loss term (0 for ignored rows). grad (optional) = G row.
+template <class TL, class TG>
+__global__ void ce_rows_kernel(const TL* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
+                               const uint32_t* __restrict__ valid, float* __restrict__ terms, TG* __restrict__ grad, int64_t ldg, float seed, uint32_t* fault) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const TL* z = logits + row * ld;
+  const uint32_t target = targets[row];
+  const bool ignored = has_ignore && target == ignore;
+  if (ignored || target >= vocab) {
+    if (threadIdx.x == 0) terms[row] = 0.0f;
+    if (grad) for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) stf(grad, row * ldg + c, 0.0f);
+    return;
+  }
+  float mx = -INFINITY;
+  for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) mx = fmaxf(mx, ldf(z, c));
+  mx = block_max(mx, red);
+  float sum = 0.0f;
+  for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) sum += expf(ldf(z, c) - mx);
+  sum = block_sum(sum, red);
+  const float picked = ldf(z, target);
+  if (!(isfinite(mx) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
+  float other = 0.0f;
+  bool collapsed = false;
+  if (picked == mx && sum == 1.0f) {
+    float o = 0.0f;
+    for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += expf(ldf(z, c) - mx);
+    other = block_sum(o, red);
+    collapsed = other > 0.0f;
+  }
+  if (threadIdx.x == 0) terms[row] = collapsed ? log1pf(other) : (mx + logf(sum) - picked);
+  if (grad) {
+    const float denom = (float)valid[0];
+    const float inv = collapsed ? 1.0f / (1.0f + other) : 1.0f / sum;
+    for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) {
+      float g = (expf(ldf(z, c) - mx) * inv) / denom;
+      if (c == target) g = collapsed ? -(other * inv) / denom : g - 1.0f / denom;
+      stf(grad, row * ldg + c, g * seed);
+    }
+  }
+}
+
+// loss = (sum of the row terms, added in a fixed tree order) / n_valid
+__global__ void ce_loss_finish_kernel(const float* __restrict__ terms, int64_t rows, const uint32_t* __restrict__ valid, float* __restrict__ loss, uint32_t* fault) {
+  __shared__ double red[256];
+  double acc = 0.0;
+  for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) acc += (double)terms[i];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = blockDim.x / 2; s > 0; s >>= 1) { if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  if (threadIdx.x == 0) {
+    float l = (float)(red[0] / (double)valid[0]);
+    if (!isfinite(l)) raise_fault(fault, OP_CE);
+    loss[0] = l;
+  }
+}
+
+}  // namespace
+
+ojc_status ce_count(ojc_backend* be, const uint32_t* targets, int64_t rows, int has_ignore, uint32_t ignore, int64_t vocab, uint32_t* valid_dev) {
+  ce_count_kernel<<<1, 1024, 0, be->stream>>>(targets, rows, has_ignore, ignore, vocab, valid_dev, be->fault_dev);
+  OJC_LAUNCHED(be, "cross_entropy_mean");
+  return OJC_OK;
+}
+
+ojc_status ce_rows(ojc_backend* be, const void* logits, int32_t l_dt, int64_t ld, const uint32_t* targets, int64_t rows, int64_t vocab, int has_ignore,
+                   uint32_t ignore, const uint32_t* valid_dev, float* terms, void* grad, int32_t g_dt, int64_t ldg, float seed) {
+  const char* op = "cross_entropy_mean";
+  if (rows == 0) return OJC_OK;
+  return dispatch_float(op, l_dt, [&](auto tl) { return dispatch_float(op, grad ? g_dt : OJC_F32, [&](auto tg) {
+    using TL = decltype(tl); using TG = decltype(tg);
+    ce_rows_kernel<TL, TG><<<(unsigned)rows, 256, 0, be->stream>>>((const TL*)logits, ld, targets, vocab, has_ignore, ignore, valid_dev, terms, (TG*)grad, ldg, seed, be->fault_dev);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  }); });
+}
+
+ojc_status ce_loss_finish(ojc_backend* be, const float* terms, int64_t rows, const uint32_t* valid_dev, float* loss_dev) {
+  ce_loss_finish_kernel<<<1, 256, 0, be->stream>>>(terms, rows, valid_dev, loss_dev, be->fault_dev);
+  OJC_LAUNCHED(be, "cross_entropy_mean");
+  return OJC_OK;
+}
+
+// The fused tied-head loss. x [rows, dim] and w [vocab, dim] share a dtype class (both F32: f32 tier with F32 logits
+// and F32 G; both BF16: tensor-core GEMMs, F32 logits, BF16 G). gx (same dtype as x, or F32) and gw (F32) are optional;
+// gw_accumulate adds into gw (the tied embedding's gradient buffer). `seed` scales G, i.e. both gradients.
+ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const void* w, int32_t w_dt, const uint32_t* targets, int64_t rows, int64_t dim,
+                          int64_t vocab, int has_ignore, uint32_t ignore, int64_t chunk_rows, float* loss_dev, void* gx, int32_t gx_dt, float* gw,
+                          bool gw_accumulate, float seed) {
+  const char* op = "linear_cross_entropy_mean";
+  const bool bf = x_dt == OJC_BF16 && w_dt == OJC_BF16;
+  const int32_t g_dt = bf ? OJC_BF16 : OJC_F32;
+  if (chunk_rows <= 0) chunk_rows = bf ? 4096 : 1024;
+  if (chunk_rows > rows) chunk_rows = rows;
+  const bool want = gx || gw;
+  const int64_t ldl = (vocab + 7) & ~int64_t(7);  // keep tile rows 16-byte aligned for the tensor-core kernels
+  void *logits = nullptr, *gbuf = nullptr, *small = nullptr;
+  OJC_TRY(ojc_alloc(be, (uint64_t)chunk_rows * ldl * 4, &logits));
+  ojc_status st = OJC_OK;
+  if (want) st = ojc_alloc(be, (uint64_t)chunk_rows * ldl * dtype_size(g_dt), &gbuf);
+  if (st == OJC_OK) st = ojc_alloc(be, (uint64_t)rows * 4 + 256, &small);
+  auto run = [&]() -> ojc_status {
+    uint32_t* valid = (uint32_t*)small;
+    float* terms = (float*)((char*)small + 256);
+    OJC_TRY(ce_count(be, targets, rows, has_ignore, ignore, vocab, valid));
+    for (int64_t r0 = 0; r0 < rows; r0 += chunk_rows) {
+      const int64_t r = std::min(chunk_rows, rows - r0);
+      const char* xc = (const char*)x + r0 * dim * dtype_size(x_dt);
+      GemmOperand a{xc, x_dt, dim, 1}, b{w, w_dt, 1, dim};
+      OJC_TRY(gemm_auto(be, op, a, b, logits, OJC_F32, ldl, r, vocab, dim, 1.0f, false, nullptr));
+      OJC_TRY(ce_rows(be, logits, OJC_F32, ldl, targets + r0, r, vocab, has_ignore, ignore, valid, terms + r0, want ? gbuf : nullptr, g_dt, ldl, seed));
+      if (gx) {  // dX_c = G . W
+        GemmOperand ga{gbuf, g_dt, ldl, 1}, wb{w, w_dt, dim, 1};
+        OJC_TRY(gemm_auto(be, op, ga, wb, (char*)gx + r0 * dim * dtype_size(gx_dt), gx_dt, dim, r, dim, vocab, 1.0f, false, nullptr));
+      }
+      if (gw) {  // dW += G^T . x_c (rows ascending across tiles)
+        GemmOperand gt{gbuf, g_dt, 1, ldl}, xb{xc, x_dt, dim, 1};
+        OJC_TRY(gemm_auto(be, op, gt, xb, gw, OJC_F32, dim, vocab, dim, r, 1.0f, gw_accumulate || r0 > 0, nullptr));
+      }
+    }
+    return ce_loss_finish(be, terms, rows, valid, loss_dev);
+  };
+  if (st == OJC_OK) st = run();
+  if (logits) ojc_free(be, logits);
+  if (gbuf) ojc_free(be, gbuf);
+  if (small) ojc_free(be, small);
+  return st;
+}
+
+extern "C" {
+
+static ojc_status ce_args(const char* op, const ojc_tensor* logits, const ojc_tensor* targets, int64_t* rows, int64_t* vocab) {
+  OJC_TRY(check_tensor(op, "logits", logits)); OJC_TRY(check_tensor(op, "targets", targets));
+  if (logits->rank != 2 || numel(targets) != logits->shape[0]) return ojc_fail(OJC_ERR_SHAPE, op, "logits [rows, vocab], targets [rows]");
+  if (targets->dtype != OJC_U32 || !is_float(logits)) return ojc_fail(OJC_ERR_DTYPE, op, "logits float, targets U32");
+  *rows = logits->shape[0]; *vocab = logits->shape[1];
+  if (*rows == 0 || *vocab == 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
+  return OJC_OK;
+}
+
+ojc_status ojc_cross_entropy_mean_forward(ojc_backend* be, const ojc_tensor* logits, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, ojc_tensor* loss) {
+  const char* op = "cross_entropy_mean_forward";
+  OJC_ALIVE(be, op);
+  int64_t rows, vocab;
+  OJC_TRY(ce_args(op, logits, targets, &rows, &vocab));
+  OJC_TRY(check_tensor(op, "loss", loss));
+  if (numel(loss) != 1 || loss->dtype != OJC_F32) return ojc_fail(OJC_ERR_SHAPE, op, "loss must be one F32 value");
+  void* small = nullptr;
+  OJC_TRY(ojc_alloc(be, (uint64_t)rows * 4 + 256, &small));
+  uint32_t* valid = (uint32_t*)small; float* terms = (float*)((char*)small + 256);
+  ojc_status st = ce_count(be, (const uint32_t*)targets->data, rows, has_ignore, ignore, vocab, valid);
+  if (st == OJC_OK) st = ce_rows(be, logits->data, logits->dtype, vocab, (const uint32_t*)targets->data, rows, vocab, has_ignore, ignore, valid, terms, nullptr, OJC_F32, 0, 1.0f);
+  if (st == OJC_OK) st = ce_loss_finish(be, terms, rows, valid, (float*)loss->data);
+  ojc_free(be, small);
+  return st;
+}
+
+ojc_status ojc_cross_entropy_mean_backward(ojc_backend* be, const ojc_tensor* logits, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, ojc_tensor* grad) {
+  const char* op = "cross_entropy_mean_backward";
+  OJC_ALIVE(be, op);
+  int64_t rows, vocab;
+  OJC_TRY(ce_args(op, logits, targets, &rows, &vocab));
+  OJC_TRY(check_tensor(op, "grad_logits", grad));
+  if (!same_shape(grad, logits) || !is_float(grad)) return ojc_fail(OJC_ERR_SHAPE, op, "grad_logits must match logits");
+  void* small = nullptr;
+  OJC_TRY(ojc_alloc(be, (uint64_t)rows * 4 + 256, &small));
+  uint32_t* valid = (uint32_t*)small; float* terms = (float*)((char*)small + 256);
+  ojc_status st = ce_count(be, (const uint32_t*)targets->data, rows, has_ignore, ignore, vocab, valid);
+  if (st == OJC_OK) st = ce_rows(be, logits->data, logits->dtype, vocab, (const uint32_t*)targets->data, rows, vocab, has_ignore, ignore, valid, terms, grad->data, grad->dtype, vocab, 1.0f);
+  ojc_free(be, small);
+  return st;
+}
+
+ojc_status ojc_linear_cross_entropy_mean(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore,
+                                         int64_t chunk_rows, int64_t chunk_cols, ojc_tensor* loss, ojc_tensor* gx, ojc_tensor* gw) {
+  const char* op = "linear_cross_entropy_mean";
+  OJC_ALIVE(be, op);
+  (void)chunk_cols;  // the vocabulary axis is never tiled here
+  OJC_TRY(check_tensor(op, "x", x)); OJC_TRY(check_tensor(op, "weight", w)); OJC_TRY(check_tensor(op, "targets", targets)); OJC_TRY(check_tensor(op, "loss", loss));
+  if (x->rank != 2 || w->rank != 2 || x->shape[1] != w->shape[1] || numel(targets) != x->shape[0]) return ojc_fail(OJC_ERR_SHAPE, op, "x [rows, d], weight [vocab, d], targets [rows]");
+  if (targets->dtype != OJC_U32 || !is_float(x) || !is_float(w)) return ojc_fail(OJC_ERR_DTYPE, op, "x and weight float, targets U32");
+  if (numel(loss) != 1 || loss->dtype != OJC_F32) return ojc_fail(OJC_ERR_SHAPE, op, "loss must be one F32 value");
+  if (numel(x) == 0 || numel(w) == 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
+  if (chunk_rows < 0) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "chunk rows is negative");
+  if (gx) { OJC_TRY(check_tensor(op, "grad_input", gx)); if (!same_shape(gx, x) || !is_float(gx)) return ojc_fail(OJC_ERR_SHAPE, op, "grad_input must match x"); }
+  if (gw) { OJC_TRY(check_tensor(op, "grad_weight", gw)); if (!same_shape(gw, w) || gw->dtype != OJC_F32) return ojc_fail(OJC_ERR_SHAPE, op, "grad_weight must be F32 like weight"); }
+  return linear_ce_impl(be, x->data, x->dtype, w->data, w->dtype, (const uint32_t*)targets->data, x->shape[0], x->shape[1], w->shape[0], has_ignore, ignore,
+                        chunk_rows, (float*)loss->data, gx ? gx->data : nullptr, gx ? gx->dtype : OJC_F32, gw ? (float*)gw->data : nullptr, false, 1.0f);
+}
+
+}  // extern "C"

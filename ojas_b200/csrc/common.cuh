@@ -1,0 +1,138 @@
+// Shared declarations of the sm_100a library: the backend object, status and
+// fault plumbing, tensor-descriptor checks and small device helpers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/ojas_cuda.h"
+
+typedef __nv_bfloat16 bf16;
+
+// Op ids written into the deferred fault word (first faulting op wins), in the
+// spirit of the reference's fault.wgsl / deferred-fault contract
+// (ojas-core/src/backend.rs:963-973).
+enum OjcOp : uint32_t {
+  OP_NONE = 0, OP_EMBEDDING, OP_LINEAR, OP_RMS_NORM, OP_ROPE, OP_VRES, OP_SDPA, OP_GATE, OP_SILU, OP_MUL,
+  OP_ADD, OP_LINEAR_CE, OP_CE, OP_ACCUMULATE, OP_SCALE, OP_CLIP, OP_ADAMW, OP_MUON, OP_ARGMAX, OP_CAST, OP_GEMM_WAIT,
+  OP_ID_RANGE,  // a token id or target outside the vocabulary: reported as OutOfRange
+  OP_COUNT
+};
+const char* ojc_op_name(uint32_t op);
+
+struct ojc_backend {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t sync_event = nullptr;
+  uint64_t cap = 0, live = 0, peak = 0, readbacks = 0, launches = 0;
+  uint64_t sync_timeout_ms = 60000;
+  bool lost = false;                       // a sticky CUDA error was seen: every later call is DeviceLost
+  uint32_t* fault_dev = nullptr;           // [0] first op id, [1] op mask
+  uint32_t* fault_host = nullptr;          // pinned
+  std::unordered_map<void*, uint64_t> live_blocks;            // ptr -> charged bytes
+  std::unordered_map<void*, uint64_t> block_size;             // ptr -> real (rounded) bytes
+  std::multimap<uint64_t, void*> free_blocks;                 // rounded bytes -> ptr
+  void* scratch = nullptr;                 // grows on demand; library-internal workspace (not charged to the caller's tensors)
+  uint64_t scratch_bytes = 0;
+  int sm_count = 148;
+  void* tmap_encode = nullptr;             // cuTensorMapEncodeTiled, resolved once
+};
+
+ojc_status ojc_fail(ojc_status st, const char* op, const std::string& detail);
+ojc_status ojc_cuda_check(ojc_backend* be, cudaError_t err, const char* op);
+// Library workspace of at least `bytes` (256-byte aligned); contents are undefined.
+ojc_status ojc_scratch(ojc_backend* be, uint64_t bytes, void** out);
+
+#define OJC_TRY(expr) do { ojc_status st__ = (expr); if (st__ != OJC_OK) return st__; } while (0)
+#define OJC_CUDA(be, expr, op) OJC_TRY(ojc_cuda_check((be), (expr), (op)))
+#define OJC_LAUNCHED(be, op) do { (be)->launches++; OJC_TRY(ojc_cuda_check((be), cudaGetLastError(), (op))); } while (0)
+#define OJC_ALIVE(be, op) do { if (!(be)) return ojc_fail(OJC_ERR_BACKEND, (op), "null backend"); \
+    if ((be)->lost) return ojc_fail(OJC_ERR_DEVICE_LOST, (op), "the device was lost earlier"); } while (0)
+
+// ---- tensor descriptor helpers
+inline int64_t numel(const ojc_tensor* t) { int64_t n = 1; for (int i = 0; i < t->rank; ++i) n *= t->shape[i]; return n; }
+inline bool contiguous(const ojc_tensor* t) {
+  int64_t expect = 1;
+  for (int i = t->rank - 1; i >= 0; --i) { if (t->shape[i] != 1 && t->stride[i] != expect) return false; expect *= t->shape[i]; }
+  return true;
+}
+inline bool same_shape(const ojc_tensor* a, const ojc_tensor* b) {
+  if (a->rank != b->rank) return false;
+  for (int i = 0; i < a->rank; ++i) if (a->shape[i] != b->shape[i]) return false;
+  return true;
+}
+inline size_t dtype_size(int32_t dt) { return dt == OJC_BF16 || dt == OJC_F16 ? 2 : 4; }
+inline bool is_float(const ojc_tensor* t) { return t->dtype == OJC_F32 || t->dtype == OJC_BF16; }
+ojc_status check_tensor(const char* op, const char* what, const ojc_tensor* t, bool need_contig = true);
+
+// ---- device helpers
+#ifdef __CUDACC__
+__device__ __forceinline__ float ldf(const float* p, int64_t i) { return p[i]; }
+__device__ __forceinline__ float ldf(const bf16* p, int64_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void stf(float* p, int64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(bf16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// bf16 round-to-nearest-even on the integer bits; NaN keeps sign + payload and
+// sets the quiet bit (ojas-core/src/autocast.rs:89-96).
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
+  uint32_t bits = __float_as_uint(v);
+  if ((bits & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((bits >> 16) | 0x0040u);
+  uint32_t round = 0x7FFFu + ((bits >> 16) & 1u);
+  return (uint16_t)((bits + round) >> 16);
+}
+__device__ __forceinline__ float round_bf16(float v) { return __uint_as_float((uint32_t)f32_to_bf16_bits(v) << 16); }
+
+__device__ __forceinline__ void raise_fault(uint32_t* fault, uint32_t op) {
+  atomicCAS(&fault[0], 0u, op);
+  atomicOr(&fault[1], 1u << (op & 31u));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum in a fixed order (warp butterflies, then warp 0 over the warp
+// partials): every thread returns the total. `red` holds >= 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? red[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+#endif
+
+// Grid for a grid-stride elementwise kernel: enough CTAs to fill the GPU, a
+// multiple of the SM count.
+inline int elementwise_grid(const ojc_backend* be, int64_t work_items, int threads) {
+  int64_t blocks = (work_items + threads - 1) / threads;
+  int64_t cap = (int64_t)be->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}

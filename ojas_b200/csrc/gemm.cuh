@@ -1,0 +1,23 @@
+// GEMM entry points shared by the linear, fused cross-entropy, gate and Muon code.
+#pragma once
+#include "common.cuh"
+
+// A strided matrix view: element (i, j) lives at ptr[i * rs + j * cs].
+struct GemmOperand {
+  const void* ptr;
+  int32_t dtype;
+  int64_t rs, cs;
+};
+
+enum GemmOutMode { GEMM_STORE = 0, GEMM_ACCUMULATE = 1 };
+
+// C[m,n] = alpha * A[m,k] . B[k,n] (+ residual[m,n]) (+ C when accumulate); C row-major with leading dimension ldc.
+ojc_status gemm_f32(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
+                    int64_t n, int64_t k, float alpha, bool accumulate, const float* residual);
+// bf16 x bf16 -> f32-accumulated tcgen05 kernel. OJC_ERR_UNSUPPORTED when the operands break the TMA alignment rules.
+bool gemm_tc_eligible(const GemmOperand& a, const GemmOperand& b, const void* c, int32_t c_dtype, int64_t ldc, int64_t m, int64_t n, int64_t k);
+ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
+                   int64_t n, int64_t k, float alpha, bool accumulate, const float* residual);
+// Tensor-core kernel when both operands are bf16 and eligible, the f32 tier otherwise.
+ojc_status gemm_auto(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
+                     int64_t n, int64_t k, float alpha, bool accumulate, const float* residual);

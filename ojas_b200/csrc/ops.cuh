@@ -1,0 +1,17 @@
+// Internal entry points of the memory-bound kernels, shared with the step driver.
+#pragma once
+#include "common.cuh"
+
+ojc_status embedding_backward_impl(ojc_backend* be, const uint32_t* ids, const void* grad, int32_t grad_dtype, float* out, int64_t tokens, int64_t vocab,
+                                   int64_t dim, bool accumulate);
+ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, float eps, ojc_tensor* y);
+ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, const ojc_tensor* gy, float eps, ojc_tensor* gx, ojc_tensor* gw,
+                             bool accumulate_gw, bool accumulate_gx);
+ojc_status rope_impl(ojc_backend* be, const char* op, const ojc_tensor* x, const ojc_tensor* cos_t, const ojc_tensor* sin_t, ojc_tensor* y, int backward);
+ojc_status vres_backward_impl(ojc_backend* be, const ojc_tensor* v, const ojc_tensor* v0, const ojc_tensor* lambda, const ojc_tensor* gy, ojc_tensor* gv,
+                              ojc_tensor* gv0, float* glambda, bool accumulate_lambda);
+ojc_status gate_backward_impl(ojc_backend* be, const ojc_tensor* input, const ojc_tensor* weight, const ojc_tensor* bias, const ojc_tensor* attn,
+                              const ojc_tensor* gout, const ojc_tensor* saved, ojc_tensor* ginput, float* gweight, float* gbias, ojc_tensor* gattn,
+                              bool accumulate_w);
+ojc_status swiglu_forward_impl(ojc_backend* be, const void* a, const void* u, void* m, int32_t dt, int64_t n);
+ojc_status swiglu_backward_impl(ojc_backend* be, const void* a, const void* u, const void* gm, void* ga, void* gu, int32_t dt, int64_t n);

@@ -1,0 +1,360 @@
+// Optimizer-side ops: global gradient norm + clip, fused AdamW, Muon with five
+// Newton-Schulz iterations. Reductions are two-stage with f64 finishes in a
+// fixed order; the norm pass doubles as the non-finite scan, as the reference's
+// does (ojas-cpu/src/optim.rs:86-95).
+#include "common.cuh"
+#include "dispatch.cuh"
+#include "gemm.cuh"
+#include "optim.cuh"
+
+namespace {
+
+constexpr int NORM_CHUNK = 8192;  // elements per block of the sum-of-squares pass
+
+__global__ void sumsq_partial_kernel(const float* __restrict__ x, int64_t n, double* __restrict__ part, uint32_t* fault, uint32_t op_id) {
+  __shared__ float red[32];
+  const int64_t base = (int64_t)blockIdx.x * NORM_CHUNK;
+  float acc = 0.0f;
+  for (int i = threadIdx.x; i < NORM_CHUNK; i += blockDim.x) {
+    int64_t idx = base + i;
+    if (idx < n) { float v = x[idx]; acc = fmaf(v, v, acc); }
+  }
+  float t = block_sum(acc, red);
+  if (threadIdx.x == 0) {
+    if (!isfinite(t)) raise_fault(fault, op_id);
+    part[blockIdx.x] = (double)t;
+  }
+}
+
+// out[0] = norm (f32 of the f64 square root), out[1] = clip scale = min(1, max / (norm + 1e-6)) (ojas-core/src/backend.rs:277-303).
+__global__ void norm_finish_kernel(const double* __restrict__ part, int64_t nparts, float max_norm, float* __restrict__ out) {
+  __shared__ double red[256];
+  double acc = 0.0;
+  for (int64_t p = threadIdx.x; p < nparts; p += blockDim.x) acc += part[p];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = blockDim.x / 2; s > 0; s >>= 1) { if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  if (threadIdx.x == 0) {
+    float norm = (float)sqrt(red[0]);
+    out[0] = norm;
+    float coef = max_norm / (norm + 1e-6f);
+    out[1] = max_norm >= 0.0f ? fminf(coef, 1.0f) : 1.0f;  // a negative max_norm asks for the norm only
+  }
+}
+
+__global__ void scale_by_device_kernel(float* __restrict__ x, int64_t n, const float* __restrict__ scale) {
+  const float s = scale[0];
+  if (!(s < 1.0f)) return;  // multiply only when clipping (ojas-cpu/src/backend.rs:788-791)
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) x[i] *= s;
+}
+
+// The 7 f32 words of AdamWScalars::f32_words (ojas-core/src/backend.rs:462-476).
+struct AdamWords { float decay, one_minus_b1, beta2, one_minus_b2, step_size, bc2_sqrt, eps; int decays, lerp_low; float lerp_high; };
+
+// One element of torch's single-tensor AdamW in f32 (ojas-cpu/src/optim.rs:341-366): decay first, lerp form switch
+// at weight 0.5, eps outside the square root. grad_scale (optional, device) folds the clip coefficient in.
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, bf16* __restrict__ mirror,
+                             int64_t n, AdamWords w, const float* __restrict__ grad_scale, uint32_t* fault) {
+  float gs = 1.0f;
+  if (grad_scale) { gs = grad_scale[0]; if (!(gs < 1.0f)) gs = 1.0f; }
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
+    const float pi = p[i];
+    float gi = g[i];
+    if (gs != 1.0f) gi *= gs;
+    const float mi = m[i], vi = v[i];
+    const float m1 = w.lerp_low ? mi + w.one_minus_b1 * (gi - mi) : gi - (gi - mi) * w.lerp_high;
+    const float v1 = w.beta2 * vi + w.one_minus_b2 * gi * gi;
+    const float denom = sqrtf(v1) / w.bc2_sqrt + w.eps;
+    const float delta = (-w.step_size) * m1 / denom;
+    float q = pi;
+    if (w.decays) q *= w.decay;
+    q += delta;
+    const float np = (!w.decays && delta == 0.0f) ? pi : q;
+    if (!(isfinite(m1) && isfinite(v1) && isfinite(denom) && isfinite(delta) && isfinite(np))) { raise_fault(fault, OP_ADAMW); continue; }
+    p[i] = np; m[i] = m1; v[i] = v1;
+    if (mirror) mirror[i] = __float2bfloat16_rn(np);
+  }
+}
+
+// buf = mu * mom + g; u = nesterov ? fma(mu, buf, g) : buf; mom = buf (ojas-cpu/src/optim.rs:684-712).
+// Also the block partial of sum u^2 (of the bf16-rounded u when ns5 runs in bf16).
+__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ mom, float* __restrict__ u, int64_t n, float mu, int nesterov,
+                                     int round_u, const float* __restrict__ grad_scale, double* __restrict__ part, uint32_t* fault) {
+  __shared__ float red[32];
+  float gs = 1.0f;
+  if (grad_scale) { gs = grad_scale[0]; if (!(gs < 1.0f)) gs = 1.0f; }
+  const int64_t base = (int64_t)blockIdx.x * NORM_CHUNK;
+  float acc = 0.0f;
+  for (int i = threadIdx.x; i < NORM_CHUNK; i += blockDim.x) {
+    int64_t idx = base + i;
+    if (idx >= n) break;
+    float gi = g[idx];
+    if (gs != 1.0f) gi *= gs;
+    const float buf = mu * mom[idx] + gi;
+    float ui = nesterov ? fmaf(mu, buf, gi) : buf;
+    if (round_u) ui = round_bf16(ui);
+    mom[idx] = buf;
+    u[idx] = ui;
+    acc = fmaf(ui, ui, acc);
+  }
+  float t = block_sum(acc, red);
+  if (threadIdx.x == 0) { if (!isfinite(t)) raise_fault(fault, OP_MUON); part[blockIdx.x] = (double)t; }
+}
+
+// X = u / (norm + 1e-7), written in the wide orientation (transposed when rows > cols), as TX (f32 or bf16).
+// In bf16 mode the norm, norm + eps and the quotient are each rounded (ojas-cpu/src/optim.rs:893-910).
+template <class TX>
+__global__ void muon_normalize_kernel(const float* __restrict__ u, const float* __restrict__ norm, TX* __restrict__ x, int rows, int cols, int tall, int bf16_mode) {
+  const float nrm = norm[0];
+  const float denom = bf16_mode ? round_bf16(round_bf16(nrm) + 1e-7f) : nrm + 1e-7f;
+  const int64_t n = (int64_t)rows * cols;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
+    int64_t r = i / cols, c = i % cols;
+    float v = u[i] / denom;
+    int64_t o = tall ? c * rows + r : i;
+    stf(x, o, v);  // the bf16 store rounds to nearest even
+  }
+}
+
+// out = b * A + c * A2 (A2 overwritten), every scalar multiple and the sum rounded in bf16 mode (optim.rs:947-957).
+template <class T>
+__global__ void ns_combine_a_kernel(const T* __restrict__ a, T* __restrict__ a2, int64_t n, float bcoef, float ccoef, int bf16_mode) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
+    float av = ldf(a, i), a2v = ldf(a2, i);
+    float r = bf16_mode ? round_bf16(round_bf16(bcoef * av) + round_bf16(ccoef * a2v)) : bcoef * av + ccoef * a2v;
+    stf(a2, i, r);
+  }
+}
+
+// bx = a * x + bx (optim.rs:966-974)
+template <class T>
+__global__ void ns_combine_x_kernel(const T* __restrict__ x, T* __restrict__ bx, int64_t n, float acoef, int bf16_mode, uint32_t* fault) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
+    float xv = ldf(x, i), bv = ldf(bx, i);
+    float r = bf16_mode ? round_bf16(round_bf16(acoef * xv) + bv) : acoef * xv + bv;
+    if (!isfinite(r)) raise_fault(fault, OP_MUON);
+    stf(bx, i, r);
+  }
+}
+
+// p = fma(alpha, X, p * decay) with X read back through the transpose when the matrix was tall (optim.rs:718-736).
+template <class TX>
+__global__ void muon_apply_kernel(float* __restrict__ p, const TX* __restrict__ x, bf16* __restrict__ mirror, int rows, int cols, int tall, float alpha,
+                                  float decay, int decays, uint32_t* fault) {
+  const int64_t n = (int64_t)rows * cols;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
+    int64_t r = i / cols, c = i % cols;
+    float o = ldf(x, tall ? c * rows + r : i);
+    float base = decays ? p[i] * decay : p[i];
+    float np = fmaf(alpha, o, base);
+    if (!isfinite(np)) { raise_fault(fault, OP_MUON); continue; }
+    p[i] = np;
+    if (mirror) mirror[i] = __float2bfloat16_rn(np);
+  }
+}
+
+double pow_u64(double base, uint64_t e) {  // ojas-core/src/backend.rs:244-257
+  double result = 1.0, b = base;
+  while (e > 0) { if (e & 1) result *= b; e >>= 1; if (e > 0) b *= b; }
+  return result;
+}
+
+}  // namespace
+
+int64_t norm_partials(int64_t n) { return (n + NORM_CHUNK - 1) / NORM_CHUNK; }
+
+ojc_status grad_norm_device(ojc_backend* be, const float* const* ptrs, const int64_t* lens, int64_t count, float max_norm, float* norm_and_scale_dev) {
+  const char* op = "clip_grad_norm";
+  int64_t total_parts = 0;
+  for (int64_t i = 0; i < count; ++i) total_parts += norm_partials(lens[i]);
+  void* ws = nullptr;
+  OJC_TRY(ojc_scratch(be, (uint64_t)total_parts * 8 + 8, &ws));
+  double* part = (double*)ws;
+  int64_t off = 0;
+  for (int64_t i = 0; i < count; ++i) {
+    int64_t parts = norm_partials(lens[i]);
+    if (parts == 0) continue;
+    sumsq_partial_kernel<<<(unsigned)parts, 256, 0, be->stream>>>(ptrs[i], lens[i], part + off, be->fault_dev, OP_CLIP);
+    OJC_LAUNCHED(be, op);
+    off += parts;
+  }
+  norm_finish_kernel<<<1, 256, 0, be->stream>>>(part, total_parts, max_norm, norm_and_scale_dev);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+ojc_status scale_by_device(ojc_backend* be, float* x, int64_t n, const float* scale_dev) {
+  if (n == 0) return OJC_OK;
+  scale_by_device_kernel<<<elementwise_grid(be, n, 256), 256, 0, be->stream>>>(x, n, scale_dev);
+  OJC_LAUNCHED(be, "clip_grad_norm");
+  return OJC_OK;
+}
+
+ojc_status adamw_device(ojc_backend* be, float* p, const float* g, float* m, float* v, bf16* mirror, int64_t n, uint64_t step_before,
+                        const ojc_adamw_config& cfg, const float* grad_scale_dev) {
+  const char* op = "adamw_step";
+  // check_adamw, ojas-core/src/backend.rs:312-356
+  const double sc[5] = {cfg.lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay};
+  for (double s : sc) if (!std::isfinite(s)) return ojc_fail(OJC_ERR_NON_FINITE, op, "a configuration scalar is not finite");
+  if (!(cfg.beta1 >= 0.0 && cfg.beta1 < 1.0 && cfg.beta2 >= 0.0 && cfg.beta2 < 1.0)) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "adamw beta must be in [0, 1)");
+  if (cfg.eps <= 0.0) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "adamw eps must be > 0");
+  if (cfg.lr < 0.0 || cfg.weight_decay < 0.0) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "lr or weight_decay is negative");
+  if (step_before == UINT64_MAX) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "step counter overflows");
+  const uint64_t step = step_before + 1;
+  const double bc1 = 1.0 - pow_u64(cfg.beta1, step), bc2 = 1.0 - pow_u64(cfg.beta2, step);
+  if (!(std::isfinite(bc1) && std::isfinite(bc2) && bc1 > 0.0 && bc2 > 0.0)) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "adamw bias correction is not a positive finite value");
+  AdamWords w;
+  const double one_minus_b1 = 1.0 - cfg.beta1;
+  w.decay = (float)(1.0 - cfg.lr * cfg.weight_decay);
+  w.one_minus_b1 = (float)one_minus_b1;
+  w.beta2 = (float)cfg.beta2;
+  w.one_minus_b2 = (float)(1.0 - cfg.beta2);
+  w.step_size = (float)(cfg.lr / bc1);
+  w.bc2_sqrt = (float)std::sqrt(bc2);
+  w.eps = (float)cfg.eps;
+  w.decays = cfg.weight_decay != 0.0;
+  w.lerp_low = w.one_minus_b1 < 0.5f;
+  w.lerp_high = 1.0f - w.one_minus_b1;
+  const float words[7] = {w.decay, w.one_minus_b1, w.beta2, w.one_minus_b2, w.step_size, w.bc2_sqrt, w.eps};
+  for (float x : words) if (!std::isfinite(x)) return ojc_fail(OJC_ERR_NON_FINITE, op, "a scalar word is not finite in f32");
+  if (n == 0) return OJC_OK;
+  adamw_kernel<<<elementwise_grid(be, n, 256), 256, 0, be->stream>>>(p, g, m, v, mirror, n, w, grad_scale_dev, be->fault_dev);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+uint64_t muon_scratch_bytes(int64_t rows, int64_t cols, bool bf16_mode) {
+  const int64_t r = rows < cols ? rows : cols, n = rows * cols;
+  const uint64_t es = bf16_mode ? 2 : 4;
+  auto al = [](uint64_t b) { return (b + 255) & ~uint64_t(255); };
+  return al(n * 4) /*u*/ + 2 * al(n * es) /*x, bx*/ + 2 * al((uint64_t)r * r * es) /*A, A2*/ + al(norm_partials(n) * 8) + 256;
+}
+
+ojc_status muon_device(ojc_backend* be, float* p, const float* g, float* mom, bf16* mirror, int64_t rows, int64_t cols, const ojc_muon_config& cfg,
+                       const float* grad_scale_dev) {
+  const char* op = "muon_ns5_step";
+  if (!std::isfinite(cfg.lr) || !std::isfinite(cfg.momentum) || !std::isfinite(cfg.weight_decay)) return ojc_fail(OJC_ERR_NON_FINITE, op, "a configuration scalar is not finite");
+  if (cfg.lr < 0.0 || cfg.momentum < 0.0 || cfg.weight_decay < 0.0) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "lr, momentum or weight_decay is negative");
+  if (rows <= 0 || cols <= 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
+  const bool bf = cfg.ns5_bf16 != 0, tall = rows > cols;
+  const int64_t r = tall ? cols : rows, c = tall ? rows : cols, n = rows * cols;
+  const int32_t dt = bf ? OJC_BF16 : OJC_F32;
+  const uint64_t es = bf ? 2 : 4;
+  auto al = [](uint64_t b) { return (b + 255) & ~uint64_t(255); };
+  void* ws = nullptr;
+  OJC_TRY(ojc_alloc(be, muon_scratch_bytes(rows, cols, bf), &ws));
+  char* cur = (char*)ws;
+  float* u = (float*)cur; cur += al(n * 4);
+  void* x = cur; cur += al(n * es);
+  void* bx = cur; cur += al(n * es);
+  void* am = cur; cur += al((uint64_t)r * r * es);
+  void* a2 = cur; cur += al((uint64_t)r * r * es);
+  double* part = (double*)cur; cur += al(norm_partials(n) * 8);
+  float* norm = (float*)cur;
+  ojc_status st = OJC_OK;
+  auto run = [&]() -> ojc_status {
+    const int64_t parts = norm_partials(n);
+    muon_momentum_kernel<<<(unsigned)parts, 256, 0, be->stream>>>(g, mom, u, n, (float)cfg.momentum, cfg.nesterov, bf ? 1 : 0, grad_scale_dev, part, be->fault_dev);
+    OJC_LAUNCHED(be, op);
+    norm_finish_kernel<<<1, 256, 0, be->stream>>>(part, parts, -1.0f, norm);
+    OJC_LAUNCHED(be, op);
+    const int grid = elementwise_grid(be, n, 256), grid_a = elementwise_grid(be, r * r, 256);
+    if (bf) muon_normalize_kernel<bf16><<<grid, 256, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, tall, 1);
+    else muon_normalize_kernel<float><<<grid, 256, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, tall, 0);
+    OJC_LAUNCHED(be, op);
+    const float a = (float)3.4445, b = (float)-4.7750, cc = (float)2.0315;  // MUON_NS5_{A,B,C}, ojas-core/src/backend.rs:144-146
+    for (int it = 0; it < 5; ++it) {
+      GemmOperand xk{x, dt, c, 1}, xt{x, dt, 1, c}, xn{x, dt, c, 1};
+      OJC_TRY(gemm_auto(be, op, xk, xt, am, dt, r, r, r, c, 1.0f, false, nullptr));                       // A = X X^T
+      GemmOperand ak{am, dt, r, 1}, an{am, dt, r, 1};
+      OJC_TRY(gemm_auto(be, op, ak, an, a2, dt, r, r, r, r, 1.0f, false, nullptr));                      // A2 = A A
+      if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r, b, cc, 1);
+      else ns_combine_a_kernel<float><<<grid_a, 256, 0, be->stream>>>((const float*)am, (float*)a2, r * r, b, cc, 0);
+      OJC_LAUNCHED(be, op);
+      GemmOperand bk{a2, dt, r, 1};
+      OJC_TRY(gemm_auto(be, op, bk, xn, bx, dt, c, r, c, r, 1.0f, false, nullptr));                      // BX = B X
+      if (bf) ns_combine_x_kernel<bf16><<<grid, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n, a, 1, be->fault_dev);
+      else ns_combine_x_kernel<float><<<grid, 256, 0, be->stream>>>((const float*)x, (float*)bx, n, a, 0, be->fault_dev);
+      OJC_LAUNCHED(be, op);
+      std::swap(x, bx);
+    }
+    const double scale = std::sqrt(std::max(1.0, (double)rows / (double)cols));
+    const float alpha = (float)(-cfg.lr * scale), decay = (float)(1.0 - cfg.lr * cfg.weight_decay);
+    if (bf) muon_apply_kernel<bf16><<<grid, 256, 0, be->stream>>>(p, (const bf16*)x, mirror, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    else muon_apply_kernel<float><<<grid, 256, 0, be->stream>>>(p, (const float*)x, mirror, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  };
+  st = run();
+  ojc_free(be, ws);
+  return st;
+}
+
+extern "C" {
+
+ojc_status ojc_clip_grad_norm(ojc_backend* be, ojc_tensor* const* grads, int64_t count, float max_norm, float* norm_out) {
+  const char* op = "clip_grad_norm";
+  OJC_ALIVE(be, op);
+  if (count < 0 || (count > 0 && !grads)) return ojc_fail(OJC_ERR_SHAPE, op, "bad gradient list");
+  if (std::isnan(max_norm) || max_norm == -INFINITY) return ojc_fail(OJC_ERR_NON_FINITE, op, "max_norm is not a number");
+  if (max_norm < 0.0f) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "max_norm is negative");
+  std::vector<const float*> ptrs(count);
+  std::vector<int64_t> lens(count);
+  for (int64_t i = 0; i < count; ++i) {
+    OJC_TRY(check_tensor(op, "grad", grads[i]));
+    if (grads[i]->dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "gradients must be F32");
+    ptrs[i] = (const float*)grads[i]->data; lens[i] = numel(grads[i]);
+  }
+  void* ns = nullptr;
+  OJC_TRY(ojc_alloc(be, 8, &ns));
+  ojc_status st = grad_norm_device(be, ptrs.data(), lens.data(), count, std::isinf(max_norm) ? 3.0e38f : max_norm, (float*)ns);
+  float host[2] = {0, 1};
+  if (st == OJC_OK) st = ojc_download(be, host, ns, 8);  // the sync point: also reports a deferred fault (the norm pass is the NaN scan)
+  if (st == OJC_OK && !std::isfinite(host[0])) st = ojc_fail(OJC_ERR_NON_FINITE, op, "the gradient norm is not finite");
+  if (st == OJC_OK && host[1] < 1.0f)
+    for (int64_t i = 0; i < count && st == OJC_OK; ++i) st = scale_by_device(be, (float*)grads[i]->data, lens[i], (float*)ns + 1);
+  ojc_free(be, ns);
+  if (norm_out) *norm_out = host[0];
+  return st;
+}
+
+ojc_status ojc_adamw_step(ojc_backend* be, ojc_tensor* param, const ojc_tensor* grad, ojc_tensor* m, ojc_tensor* v, uint64_t step_before,
+                          const ojc_adamw_config* cfg, ojc_tensor* mirror) {
+  const char* op = "adamw_step";
+  OJC_ALIVE(be, op);
+  if (!cfg) return ojc_fail(OJC_ERR_BACKEND, op, "null config");
+  OJC_TRY(check_tensor(op, "param", param)); OJC_TRY(check_tensor(op, "grad", grad)); OJC_TRY(check_tensor(op, "m", m)); OJC_TRY(check_tensor(op, "v", v));
+  if (!same_shape(param, grad) || !same_shape(param, m) || !same_shape(param, v)) return ojc_fail(OJC_ERR_SHAPE, op, "param, grad, m, v must share a shape");
+  if (param->dtype != OJC_F32 || grad->dtype != OJC_F32 || m->dtype != OJC_F32 || v->dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "param, grad, m, v must be F32");
+  if (mirror) { OJC_TRY(check_tensor(op, "bf16_mirror", mirror)); if (mirror->dtype != OJC_BF16 || numel(mirror) != numel(param)) return ojc_fail(OJC_ERR_SHAPE, op, "mirror must be BF16 of the parameter's size"); }
+  if (numel(param) == 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
+  return adamw_device(be, (float*)param->data, (const float*)grad->data, (float*)m->data, (float*)v->data, mirror ? (bf16*)mirror->data : nullptr,
+                      numel(param), step_before, *cfg, nullptr);
+}
+
+ojc_status ojc_muon_ns5_step(ojc_backend* be, ojc_tensor* param, const ojc_tensor* grad, ojc_tensor* momentum, const ojc_muon_config* cfg, ojc_tensor* mirror) {
+  const char* op = "muon_ns5_step";
+  OJC_ALIVE(be, op);
+  if (!cfg) return ojc_fail(OJC_ERR_BACKEND, op, "null config");
+  OJC_TRY(check_tensor(op, "param", param)); OJC_TRY(check_tensor(op, "grad", grad)); OJC_TRY(check_tensor(op, "momentum", momentum));
+  if (param->rank != 2 || !same_shape(param, grad) || !same_shape(param, momentum)) return ojc_fail(OJC_ERR_SHAPE, op, "param, grad, momentum must be one [rows, cols] shape");
+  if (param->dtype != OJC_F32 || grad->dtype != OJC_F32 || momentum->dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "param, grad, momentum must be F32");
+  if (mirror) { OJC_TRY(check_tensor(op, "bf16_mirror", mirror)); if (mirror->dtype != OJC_BF16 || numel(mirror) != numel(param)) return ojc_fail(OJC_ERR_SHAPE, op, "mirror must be BF16 of the parameter's size"); }
+  return muon_device(be, (float*)param->data, (const float*)grad->data, (float*)momentum->data, mirror ? (bf16*)mirror->data : nullptr, param->shape[0],
+                     param->shape[1], *cfg, nullptr);
+}
+
+ojc_status ojc_optimizer_scratch_bytes(ojc_backend* be, int32_t kind, int64_t rows, int64_t cols, uint64_t* bytes) {
+  if (!bytes) return ojc_fail(OJC_ERR_BACKEND, "optimizer_scratch_bytes", "null out pointer");
+  if (kind == 0) { *bytes = 0; return OJC_OK; }
+  if (kind == 1) { *bytes = std::max(muon_scratch_bytes(rows, cols, false), muon_scratch_bytes(rows, cols, true)); return OJC_OK; }
+  return ojc_fail(OJC_ERR_UNSUPPORTED, "optimizer_scratch_bytes", "unknown optimizer kind");
+}
+
+}  // extern "C"

@@ -1,0 +1,24 @@
+// Shared declarations of the attention kernels.
+#pragma once
+#include "common.cuh"
+
+template <class P>
+struct SdpaView {  // [B, H, T, dh] through strides; the dh axis is contiguous
+  P* ptr;
+  int64_t sb, sh, st;
+  __host__ __device__ __forceinline__ P* row(int b, int h, int t) const { return ptr + b * sb + h * sh + t * st; }
+};
+
+struct SdpaDims { int batch, heads, kv_heads, time, dim; float scale; };
+
+ojc_status sdpa_check(const char* op, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, SdpaDims* d);
+ojc_status sdpa_forward_f32tier(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, int64_t window, ojc_tensor* out,
+                                float* lse, const SdpaDims& d);
+ojc_status sdpa_backward_f32tier(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
+                                 const ojc_tensor* gout, int64_t window, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* dr);
+// bf16 tensor-core tier (head_dim 64 or 128, full causal attention)
+bool sdpa_tc_eligible(const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const SdpaDims& d);
+ojc_status sdpa_forward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, int64_t window, ojc_tensor* out, float* lse,
+                           const SdpaDims& d);
+ojc_status sdpa_backward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
+                            const ojc_tensor* gout, int64_t window, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* dr);

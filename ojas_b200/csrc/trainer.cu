@@ -1,0 +1,560 @@
+// The nanolab GPT training step as a C++ driver over this library's ops.
+//
+// It replays what the reference's host layers do with a Backend:
+//   parameters  ojas-model/src/names.rs:188-300 (param_table order and groups)
+//   forward     ojas-model/src/block.rs:218-264 (block_with), 351-404 (hidden), 423-447 (forward_loss)
+//   backward    the reverse walk of ojas-autograd/src/tape.rs:2004-2466, fan-in by accumulation (2565-2591)
+//   optimizer   ojas-model/src/trainer.rs:754-1046 (clip, per-slot Muon / AdamW in table order, one readback)
+// Under bf16 autocast the rounding points follow ojas-core/src/autocast.rs: the residual stream, norm statistics,
+// loss, weight gradients and optimizer state stay f32; matmul-class operands and activation outputs are bf16.
+// Permutes are views: attention reads and writes [B,T,H,dh] storage through [B,H,T,dh] strides.
+#include <cstring>
+
+#include "ce.cuh"
+#include "common.cuh"
+#include "linear.cuh"
+#include "ops.cuh"
+#include "optim.cuh"
+
+namespace {
+
+enum { P_NORM1 = 0, P_Q, P_K, P_V, P_O, P_QN, P_KN, P_GW, P_GB, P_LAMBDA, P_NORM2, P_FG, P_FU, P_FD, P_PER_BLOCK };
+enum { GROUP_ADAMW = 0, GROUP_MUON = 1 };
+
+struct Param {
+  std::string name;
+  int rank; int64_t shape[2]; int64_t n; int group; bool trains;
+  int64_t offset;  // floats into the flat buffers
+};
+
+struct LayerActs {
+  void *h, *q, *k, *rawv, *qr, *kr, *v, *y, *yg, *h2, *a, *u, *m;  // activation dtype
+  float *x, *x1, *lse, *scales;                                     // f32
+};
+
+ojc_tensor T1(void* p, int32_t dt, int64_t n) { ojc_tensor t{}; t.data = p; t.dtype = dt; t.rank = 1; t.shape[0] = n; t.stride[0] = 1; return t; }
+ojc_tensor T2(void* p, int32_t dt, int64_t r, int64_t c) {
+  ojc_tensor t{}; t.data = p; t.dtype = dt; t.rank = 2; t.shape[0] = r; t.shape[1] = c; t.stride[0] = c; t.stride[1] = 1; return t;
+}
+ojc_tensor T4(void* p, int32_t dt, int64_t a, int64_t b, int64_t c, int64_t d) {
+  ojc_tensor t{}; t.data = p; t.dtype = dt; t.rank = 4; t.shape[0] = a; t.shape[1] = b; t.shape[2] = c; t.shape[3] = d;
+  t.stride[3] = 1; t.stride[2] = d; t.stride[1] = c * d; t.stride[0] = b * c * d; return t;
+}
+// [B,T,H,dh] storage seen as [B,H,T,dh]
+ojc_tensor TBHTD(void* p, int32_t dt, int64_t b, int64_t t, int64_t h, int64_t d) {
+  ojc_tensor x{}; x.data = p; x.dtype = dt; x.rank = 4; x.shape[0] = b; x.shape[1] = h; x.shape[2] = t; x.shape[3] = d;
+  x.stride[0] = t * h * d; x.stride[1] = d; x.stride[2] = h * d; x.stride[3] = 1; return x;
+}
+
+}  // namespace
+
+struct ojc_trainer {
+  ojc_backend* be = nullptr;
+  ojc_model_spec spec{};
+  ojc_train_config cfg{};
+  int64_t B = 0, T = 0, N = 0;
+  std::vector<Param> params;
+  int64_t flat_n = 0;
+  float *w = nullptr, *g = nullptr, *m1 = nullptr, *m2 = nullptr;  // flat parameter-shaped buffers (m1 doubles as the Muon momentum)
+  bf16* mirror = nullptr;
+  int32_t act_dt = OJC_F32;
+  std::vector<LayerActs> acts;
+  std::vector<void*> owned;
+  float *cos_t = nullptr, *sin_t = nullptr, *x_final = nullptr, *gx = nullptr, *g_h = nullptr, *g_h2 = nullptr, *gv0_acc = nullptr, *stats = nullptr;
+  void *hf = nullptr, *gx_b = nullptr, *g_m = nullptr, *g_a = nullptr, *g_u = nullptr, *g_yg = nullptr, *g_y = nullptr, *g_qr = nullptr, *g_kr = nullptr,
+       *g_v = nullptr, *g_qn = nullptr, *g_kn = nullptr, *g_q = nullptr, *g_k = nullptr, *g_rawv = nullptr, *g_v0l = nullptr, *qn = nullptr, *kn = nullptr;
+  uint32_t *ids = nullptr, *targets = nullptr;
+  uint64_t step = 0;
+  bool poisoned = false, grads_ready = false;
+  struct Bucket { int64_t offset, floats; int first_param; cudaEvent_t ready; bool recorded; };
+  std::vector<Bucket> buckets;
+
+  const Param& P(int64_t layer, int which) const { return params[1 + layer * P_PER_BLOCK + which]; }
+  float* W(const Param& p) const { return w + p.offset; }
+  float* G(const Param& p) const { return g + p.offset; }
+  // the operand a matmul-class op reads: the bf16 mirror under autocast, the f32 master otherwise
+  const void* WM(const Param& p) const { return act_dt == OJC_BF16 ? (const void*)(mirror + p.offset) : (const void*)(w + p.offset); }
+};
+
+namespace {
+
+void build_table(ojc_trainer* tr) {
+  const ojc_model_spec& s = tr->spec;
+  const int64_t d = s.n_embd, q = s.n_head * s.head_dim, kv = s.n_kv_head * s.head_dim;
+  int64_t off = 0;
+  auto push = [&](std::string name, int rank, int64_t a, int64_t b, bool embedding, bool trains) {
+    Param p; p.name = std::move(name); p.rank = rank; p.shape[0] = a; p.shape[1] = b; p.n = a * b;
+    p.group = embedding ? GROUP_ADAMW : (rank >= 2 ? GROUP_MUON : GROUP_ADAMW);  // ojas-cpu/src/train.rs:54-62
+    p.trains = trains; p.offset = off;
+    off += (p.n + 63) & ~int64_t(63);  // 256-byte aligned slots; the padding stays zero
+    tr->params.push_back(std::move(p));
+  };
+  push("tok_emb.weight", 2, s.vocab, d, true, true);
+  for (int64_t i = 0; i < s.n_layer; ++i) {
+    std::string p = "blocks." + std::to_string(i), m = p + ".mixer";
+    push(p + ".norm1.weight", 1, d, 1, false, true);
+    push(m + ".q_proj.weight", 2, q, d, false, true);
+    push(m + ".k_proj.weight", 2, kv, d, false, true);
+    push(m + ".v_proj.weight", 2, kv, d, false, true);
+    push(m + ".o_proj.weight", 2, d, q, false, true);
+    push(m + ".q_norm.weight", 1, s.head_dim, 1, false, true);
+    push(m + ".k_norm.weight", 1, s.head_dim, 1, false, true);
+    push(m + ".gate.weight", 2, s.n_head, d, false, true);
+    push(m + ".gate.bias", 1, s.n_head, 1, false, true);
+    push(m + ".vr_lambda", 1, 1, 1, false, i != 0);
+    push(p + ".norm2.weight", 1, d, 1, false, true);
+    push(p + ".ffn.gate.weight", 2, s.hidden, d, false, true);
+    push(p + ".ffn.up.weight", 2, s.hidden, d, false, true);
+    push(p + ".ffn.down.weight", 2, d, s.hidden, false, true);
+  }
+  push("norm_f.weight", 1, d, 1, false, true);
+  tr->flat_n = off;
+}
+
+ojc_status take(ojc_trainer* tr, uint64_t bytes, void** out) {
+  OJC_TRY(ojc_alloc(tr->be, bytes, out));
+  tr->owned.push_back(*out);
+  return OJC_OK;
+}
+template <class P> ojc_status take_as(ojc_trainer* tr, uint64_t bytes, P** out) { void* p = nullptr; OJC_TRY(take(tr, bytes, &p)); *out = (P*)p; return OJC_OK; }
+
+void rope_tables_host(double base, int64_t len, int64_t dim, std::vector<float>& cos_t, std::vector<float>& sin_t) {
+  // ojas-model/src/block.rs:62-85: f64 powf / sin_cos, then f32
+  const int64_t half = dim / 2;
+  cos_t.assign(len * dim, 0.0f); sin_t.assign(len * dim, 0.0f);
+  for (int64_t row = 0; row < len; ++row)
+    for (int64_t i = 0; i < half; ++i) {
+      double inv = std::pow(base, -((double)(2 * i)) / (double)dim);
+      double s = std::sin((double)row * inv), c = std::cos((double)row * inv);
+      cos_t[row * dim + i] = (float)c; cos_t[row * dim + half + i] = (float)c;
+      sin_t[row * dim + i] = (float)s; sin_t[row * dim + half + i] = (float)s;
+    }
+}
+
+ojc_status refresh_mirror(ojc_trainer* tr, const Param& p) {
+  if (tr->act_dt != OJC_BF16) return OJC_OK;
+  ojc_tensor src = T1(tr->W(p), OJC_F32, p.n), dst = T1(tr->mirror + p.offset, OJC_BF16, p.n);
+  return ojc_to_bf16(tr->be, &src, &dst);
+}
+
+// ---------------------------------------------------------------------------------------------- forward
+ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
+  ojc_backend* be = tr->be;
+  const ojc_model_spec& s = tr->spec;
+  const int64_t d = s.n_embd, H = s.n_head, Hkv = s.n_kv_head, dh = s.head_dim, F = s.hidden, N = tr->N, B = tr->B, T = tr->T;
+  const int64_t qw = H * dh, kvw = Hkv * dh, L = s.n_layer;
+  const int32_t A = tr->act_dt;
+  const float eps = s.rms_eps;
+  ojc_tensor cos_t = T2(tr->cos_t, OJC_F32, T, dh), sin_t = T2(tr->sin_t, OJC_F32, T, dh);
+  {
+    ojc_tensor table = T2(tr->w + tr->params[0].offset, OJC_F32, s.vocab, d), ids = T1((void*)ids_dev, OJC_U32, N), out = T2(tr->acts[0].x, OJC_F32, N, d);
+    OJC_TRY(ojc_embedding_forward(be, &table, &ids, &out));
+  }
+  for (int64_t l = 0; l < L; ++l) {
+    LayerActs& a = tr->acts[l];
+    float* x_next = (l + 1 < L) ? tr->acts[l + 1].x : tr->x_final;
+    ojc_tensor x = T2(a.x, OJC_F32, N, d), h = T2(a.h, A, N, d);
+    ojc_tensor n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d);
+    OJC_TRY(rms_forward_impl(be, &x, &n1, eps, &h));
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, qw, nullptr));
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_K)), A, a.k, A, N, d, kvw, nullptr));
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_V)), A, a.rawv, A, N, d, kvw, nullptr));
+    {
+      ojc_tensor q = T2(a.q, A, N * H, dh), qn = T2(tr->qn, A, N * H, dh), qnw = T1(tr->W(tr->P(l, P_QN)), OJC_F32, dh);
+      ojc_tensor k = T2(a.k, A, N * Hkv, dh), kn = T2(tr->kn, A, N * Hkv, dh), knw = T1(tr->W(tr->P(l, P_KN)), OJC_F32, dh);
+      OJC_TRY(rms_forward_impl(be, &q, &qnw, eps, &qn));
+      OJC_TRY(rms_forward_impl(be, &k, &knw, eps, &kn));
+      ojc_tensor qn4 = T4(tr->qn, A, B, T, H, dh), qr4 = T4(a.qr, A, B, T, H, dh), kn4 = T4(tr->kn, A, B, T, Hkv, dh), kr4 = T4(a.kr, A, B, T, Hkv, dh);
+      OJC_TRY(rope_impl(be, "rope_half_split_forward", &qn4, &cos_t, &sin_t, &qr4, 0));
+      OJC_TRY(rope_impl(be, "rope_half_split_forward", &kn4, &cos_t, &sin_t, &kr4, 0));
+    }
+    if (l > 0) {
+      ojc_tensor rv = T1(a.rawv, A, N * kvw), v0 = T1(tr->acts[0].rawv, A, N * kvw), lam = T1(tr->W(tr->P(l, P_LAMBDA)), OJC_F32, 1), v = T1(a.v, A, N * kvw);
+      OJC_TRY(ojc_value_residual_blend_forward(be, &rv, &v0, &lam, &v));
+    }
+    {
+      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), v = TBHTD(l > 0 ? a.v : a.rawv, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+      ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
+      lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
+      OJC_TRY(ojc_causal_sdpa_forward(be, &q, &k, &v, s.window, &y, &lse));
+    }
+    {
+      ojc_tensor h2d = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
+      ojc_tensor y = T2(a.y, A, N * H, dh), yg = T2(a.yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H);
+      OJC_TRY(ojc_per_head_sigmoid_gate_forward(be, &h2d, &gw, &gb, &y, &yg, &sc));
+    }
+    OJC_TRY(linear_forward_impl(be, a.yg, A, tr->WM(tr->P(l, P_O)), A, a.x1, OJC_F32, N, qw, d, a.x));  // x1 = x + o_proj(yg)
+    {
+      ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), h2 = T2(a.h2, A, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d);
+      OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2));
+    }
+    OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, F, nullptr));
+    OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FU)), A, a.u, A, N, d, F, nullptr));
+    if ((N * F) % 4 == 0) OJC_TRY(swiglu_forward_impl(be, a.a, a.u, a.m, A, N * F));
+    else {
+      ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), tm = T1(a.m, A, N * F);
+      OJC_TRY(ojc_silu_forward(be, &ta, &tm));
+      OJC_TRY(ojc_mul_forward(be, &tm, &tu, &tm));
+    }
+    OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, a.x1));  // x2 = x1 + down(m)
+  }
+  ojc_tensor xf = T2(tr->x_final, OJC_F32, N, d), hf = T2(tr->hf, A, N, d), nf = T1(tr->W(tr->params.back()), OJC_F32, d);
+  return rms_forward_impl(be, &xf, &nf, eps, &hf);
+}
+
+ojc_status record_ready(ojc_trainer* tr, int first_param_done) {
+  // a bucket is complete once every parameter from its first one to the end of the table has its gradient
+  for (auto& b : tr->buckets)
+    if (!b.recorded && b.first_param >= first_param_done && b.first_param != 0) {
+      OJC_CUDA(tr->be, cudaEventRecord(b.ready, tr->be->stream), "bucket_ready");
+      b.recorded = true;
+    }
+  return OJC_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- backward
+ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev) {
+  ojc_backend* be = tr->be;
+  const ojc_model_spec& s = tr->spec;
+  const int64_t d = s.n_embd, H = s.n_head, Hkv = s.n_kv_head, dh = s.head_dim, F = s.hidden, N = tr->N, B = tr->B, T = tr->T, V = s.vocab;
+  const int64_t qw = H * dh, kvw = Hkv * dh, L = s.n_layer;
+  const int32_t A = tr->act_dt;
+  const bool bf = A == OJC_BF16;
+  const float eps = s.rms_eps;
+  ojc_tensor cos_t = T2(tr->cos_t, OJC_F32, T, dh), sin_t = T2(tr->sin_t, OJC_F32, T, dh);
+  const Param& tok = tr->params[0];
+  for (auto& b : tr->buckets) b.recorded = false;
+  // fused tied-head loss: both gradients come out of the forward call (ojas-autograd/src/tape.rs:1766-1779)
+  OJC_TRY(linear_ce_impl(be, tr->hf, A, tr->WM(tok), A, targets_dev, N, d, V, tr->cfg.has_ignore, tr->cfg.ignore_index, tr->cfg.ce_chunk_rows, tr->stats, tr->g_h,
+                         OJC_F32, tr->G(tok), false, tr->cfg.loss_seed));
+  {
+    ojc_tensor xf = T2(tr->x_final, OJC_F32, N, d), nf = T1(tr->W(tr->params.back()), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
+    ojc_tensor gnf = T1(tr->G(tr->params.back()), OJC_F32, d);
+    OJC_TRY(rms_backward_impl(be, &xf, &nf, &gy, eps, &gx, &gnf, false, false));
+  }
+  OJC_TRY(record_ready(tr, (int)tr->params.size() - 1));
+  // the residual gradient as a matmul operand: f32 in the f32 tier, a bf16 copy under autocast
+  auto residual_operand = [&]() -> ojc_status {
+    if (!bf) return OJC_OK;
+    ojc_tensor src = T1(tr->gx, OJC_F32, N * d), dst = T1(tr->gx_b, OJC_BF16, N * d);
+    return ojc_to_bf16(be, &src, &dst);
+  };
+  const void* gxo = bf ? tr->gx_b : (void*)tr->gx;
+  bool have_v0 = false;
+  for (int64_t l = L - 1; l >= 0; --l) {
+    LayerActs& a = tr->acts[l];
+    OJC_TRY(residual_operand());
+    // x2 = x1 + down(m)
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
+    OJC_TRY(linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false));
+    if ((N * F) % 4 == 0) OJC_TRY(swiglu_backward_impl(be, a.a, a.u, tr->g_m, tr->g_a, tr->g_u, A, N * F));
+    else {
+      ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), gm = T1(tr->g_m, A, N * F), ga = T1(tr->g_a, A, N * F), gu = T1(tr->g_u, A, N * F);
+      ojc_tensor sil = T1(a.m, A, N * F);  // silu(a) recomputed into the slot of m, which is no longer needed
+      OJC_TRY(ojc_silu_forward(be, &ta, &sil));
+      OJC_TRY(ojc_mul_backward(be, &sil, &tu, &gm, &ga, &gu));  // ga = g_silu for now
+      OJC_TRY(ojc_silu_backward(be, &ta, &ga, &ga));
+    }
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FU)), A, tr->g_u, A, tr->g_h2, OJC_F32, N, d, F, false));
+    OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_u, A, tr->G(tr->P(l, P_FU)), N, d, F, false));
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FG)), A, tr->g_a, A, tr->g_h2, OJC_F32, N, d, F, true));
+    OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, F, false));
+    {
+      ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d), gy = T2(tr->g_h2, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
+      ojc_tensor gn2 = T1(tr->G(tr->P(l, P_NORM2)), OJC_F32, d);
+      OJC_TRY(rms_backward_impl(be, &x1, &n2, &gy, eps, &gx, &gn2, false, true));  // gx now holds d/dx1
+    }
+    OJC_TRY(residual_operand());
+    // x1 = x + o_proj(yg)
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_O)), A, gxo, A, tr->g_yg, A, N, qw, d, false));
+    OJC_TRY(linear_backward_weight_impl(be, a.yg, A, gxo, A, tr->G(tr->P(l, P_O)), N, qw, d, false));
+    {
+      ojc_tensor h = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
+      ojc_tensor y = T2(a.y, A, N * H, dh), gyg = T2(tr->g_yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H), gh = T2(tr->g_h, OJC_F32, N, d), gy = T2(tr->g_y, A, N * H, dh);
+      OJC_TRY(gate_backward_impl(be, &h, &gw, &gb, &y, &gyg, &sc, &gh, tr->G(tr->P(l, P_GW)), tr->G(tr->P(l, P_GB)), &gy, false));
+    }
+    {
+      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), v = TBHTD(l > 0 ? a.v : a.rawv, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+      ojc_tensor gy = TBHTD(tr->g_y, A, B, T, H, dh), gq = TBHTD(tr->g_qr, A, B, T, H, dh), gk = TBHTD(tr->g_kr, A, B, T, Hkv, dh), gv = TBHTD(tr->g_v, A, B, T, Hkv, dh);
+      ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
+      lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
+      OJC_TRY(ojc_causal_sdpa_backward(be, &q, &k, &v, &y, &lse, &gy, s.window, &gq, &gk, &gv));
+    }
+    const void* g_rawv = tr->g_v;
+    if (l > 0) {
+      ojc_tensor rv = T1(a.rawv, A, N * kvw), v0 = T1(tr->acts[0].rawv, A, N * kvw), lam = T1(tr->W(tr->P(l, P_LAMBDA)), OJC_F32, 1), gv = T1(tr->g_v, A, N * kvw);
+      ojc_tensor grv = T1(tr->g_rawv, A, N * kvw), gv0 = T1(tr->g_v0l, A, N * kvw);
+      OJC_TRY(vres_backward_impl(be, &rv, &v0, &lam, &gv, &grv, &gv0, tr->G(tr->P(l, P_LAMBDA)), false));
+      ojc_tensor acc = T1(tr->gv0_acc, OJC_F32, N * kvw);
+      if (!have_v0) { OJC_TRY(ojc_fill_zero(be, tr->gv0_acc, (uint64_t)N * kvw * 4)); have_v0 = true; }
+      OJC_TRY(ojc_residual_add_forward(be, &acc, &gv0, &acc));
+      g_rawv = tr->g_rawv;
+    } else if (have_v0) {
+      // layer 0's raw v also fed every later layer's blend: add those contributions (gathered in reverse-walk order)
+      ojc_tensor acc = T1(tr->gv0_acc, OJC_F32, N * kvw), gv = T1(tr->g_v, A, N * kvw), grv = T1(tr->g_rawv, A, N * kvw);
+      OJC_TRY(ojc_residual_add_forward(be, &acc, &gv, &grv));
+      g_rawv = tr->g_rawv;
+    }
+    {
+      ojc_tensor gkr = T4(tr->g_kr, A, B, T, Hkv, dh), gkn = T4(tr->g_kn, A, B, T, Hkv, dh), gqr = T4(tr->g_qr, A, B, T, H, dh), gqn = T4(tr->g_qn, A, B, T, H, dh);
+      OJC_TRY(rope_impl(be, "rope_half_split_backward", &gkr, &cos_t, &sin_t, &gkn, 1));
+      OJC_TRY(rope_impl(be, "rope_half_split_backward", &gqr, &cos_t, &sin_t, &gqn, 1));
+      ojc_tensor k = T2(a.k, A, N * Hkv, dh), knw = T1(tr->W(tr->P(l, P_KN)), OJC_F32, dh), gkn2 = T2(tr->g_kn, A, N * Hkv, dh), gk = T2(tr->g_k, A, N * Hkv, dh);
+      ojc_tensor gknw = T1(tr->G(tr->P(l, P_KN)), OJC_F32, dh);
+      OJC_TRY(rms_backward_impl(be, &k, &knw, &gkn2, eps, &gk, &gknw, false, false));
+      ojc_tensor q = T2(a.q, A, N * H, dh), qnw = T1(tr->W(tr->P(l, P_QN)), OJC_F32, dh), gqn2 = T2(tr->g_qn, A, N * H, dh), gq = T2(tr->g_q, A, N * H, dh);
+      ojc_tensor gqnw = T1(tr->G(tr->P(l, P_QN)), OJC_F32, dh);
+      OJC_TRY(rms_backward_impl(be, &q, &qnw, &gqn2, eps, &gq, &gqnw, false, false));
+    }
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_V)), A, g_rawv, A, tr->g_h, OJC_F32, N, d, kvw, true));
+    OJC_TRY(linear_backward_weight_impl(be, a.h, A, g_rawv, A, tr->G(tr->P(l, P_V)), N, d, kvw, false));
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_K)), A, tr->g_k, A, tr->g_h, OJC_F32, N, d, kvw, true));
+    OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_k, A, tr->G(tr->P(l, P_K)), N, d, kvw, false));
+    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_Q)), A, tr->g_q, A, tr->g_h, OJC_F32, N, d, qw, true));
+    OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, qw, false));
+    {
+      ojc_tensor x = T2(a.x, OJC_F32, N, d), n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
+      ojc_tensor gn1 = T1(tr->G(tr->P(l, P_NORM1)), OJC_F32, d);
+      OJC_TRY(rms_backward_impl(be, &x, &n1, &gy, eps, &gx, &gn1, false, true));
+    }
+    if (l == 0 && s.n_layer > 0) OJC_TRY(ojc_fill_zero(be, tr->G(tr->P(0, P_LAMBDA)), 4));  // layer 0's lambda never trains (names.rs:262-268)
+    OJC_TRY(record_ready(tr, 1 + (int)l * P_PER_BLOCK));
+  }
+  OJC_TRY(embedding_backward_impl(be, ids_dev, tr->gx, OJC_F32, tr->G(tok), N, V, d, true));
+  for (auto& b : tr->buckets) if (b.first_param == 0) OJC_CUDA(be, cudaEventRecord(b.ready, be->stream), "bucket_ready");
+  return OJC_OK;
+}
+
+ojc_status check_live(ojc_trainer* tr, const char* op) {
+  if (!tr) return ojc_fail(OJC_ERR_BACKEND, op, "null trainer");
+  OJC_ALIVE(tr->be, op);
+  if (tr->poisoned) return ojc_fail(OJC_ERR_POISONED, op, "an earlier optimizer phase failed; the trainer state is not trustworthy (TrainState::Poisoned)");
+  return OJC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const ojc_train_config* cfg, int64_t batch, int64_t seq, ojc_trainer** out) {
+  const char* op = "trainer_open";
+  OJC_ALIVE(be, op);
+  if (!spec || !cfg || !out) return ojc_fail(OJC_ERR_BACKEND, op, "null argument");
+  *out = nullptr;
+  const ojc_model_spec& s = *spec;
+  if (s.vocab <= 0 || s.n_embd <= 0 || s.n_layer <= 0 || s.n_head <= 0 || s.n_kv_head <= 0 || s.head_dim <= 0 || s.hidden <= 0 || s.max_seq <= 0)
+    return ojc_fail(OJC_ERR_SHAPE, op, "every ModelSpec extent must be positive");
+  if (s.n_head % s.n_kv_head != 0 || s.head_dim % 2 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "n_head must be a multiple of n_kv_head and head_dim even");
+  if (batch <= 0 || seq <= 0 || seq > s.max_seq) return ojc_fail(OJC_ERR_SHAPE, op, "batch and seq must be positive and seq <= max_seq");
+  ojc_trainer* tr = new ojc_trainer();
+  tr->be = be; tr->spec = s; tr->cfg = *cfg; tr->B = batch; tr->T = seq; tr->N = batch * seq;
+  tr->act_dt = cfg->autocast_bf16 ? OJC_BF16 : OJC_F32;
+  if (tr->cfg.loss_seed == 0.0f) tr->cfg.loss_seed = 1.0f;
+  build_table(tr);
+  const int64_t d = s.n_embd, H = s.n_head, Hkv = s.n_kv_head, dh = s.head_dim, F = s.hidden, N = tr->N, L = s.n_layer;
+  const int64_t qw = H * dh, kvw = Hkv * dh;
+  const uint64_t es = dtype_size(tr->act_dt);
+  auto fail = [&](ojc_status st) { ojc_trainer_close(tr); return st; };
+  ojc_status st = OJC_OK;
+#define TAKE(ptr, bytes) if ((st = take_as(tr, (uint64_t)(bytes), &(ptr))) != OJC_OK) return fail(st)
+  TAKE(tr->w, tr->flat_n * 4); TAKE(tr->g, tr->flat_n * 4); TAKE(tr->m1, tr->flat_n * 4); TAKE(tr->m2, tr->flat_n * 4);
+  if (tr->act_dt == OJC_BF16) TAKE(tr->mirror, tr->flat_n * 2);
+  for (float* p : {tr->w, tr->g, tr->m1, tr->m2}) if ((st = ojc_fill_zero(be, p, (uint64_t)tr->flat_n * 4)) != OJC_OK) return fail(st);
+  if (tr->mirror && (st = ojc_fill_zero(be, tr->mirror, (uint64_t)tr->flat_n * 2)) != OJC_OK) return fail(st);
+  tr->acts.resize(L);
+  for (int64_t l = 0; l < L; ++l) {
+    LayerActs& a = tr->acts[l];
+    TAKE(a.x, N * d * 4); TAKE(a.x1, N * d * 4); TAKE(a.lse, tr->B * H * tr->T * 4); TAKE(a.scales, N * H * 4);
+    TAKE(a.h, N * d * es); TAKE(a.q, N * qw * es); TAKE(a.k, N * kvw * es); TAKE(a.rawv, N * kvw * es); TAKE(a.qr, N * qw * es); TAKE(a.kr, N * kvw * es);
+    if (l > 0) TAKE(a.v, N * kvw * es); else a.v = nullptr;
+    TAKE(a.y, N * qw * es); TAKE(a.yg, N * qw * es); TAKE(a.h2, N * d * es); TAKE(a.a, N * F * es); TAKE(a.u, N * F * es); TAKE(a.m, N * F * es);
+  }
+  TAKE(tr->x_final, N * d * 4); TAKE(tr->gx, N * d * 4); TAKE(tr->g_h, N * d * 4); TAKE(tr->g_h2, N * d * 4); TAKE(tr->gv0_acc, N * kvw * 4); TAKE(tr->stats, 256);
+  TAKE(tr->hf, N * d * es); TAKE(tr->gx_b, N * d * 2); TAKE(tr->g_m, N * F * es); TAKE(tr->g_a, N * F * es); TAKE(tr->g_u, N * F * es);
+  TAKE(tr->g_yg, N * qw * es); TAKE(tr->g_y, N * qw * es); TAKE(tr->g_qr, N * qw * es); TAKE(tr->g_kr, N * kvw * es); TAKE(tr->g_v, N * kvw * es);
+  TAKE(tr->g_qn, N * qw * es); TAKE(tr->g_kn, N * kvw * es); TAKE(tr->g_q, N * qw * es); TAKE(tr->g_k, N * kvw * es); TAKE(tr->g_rawv, N * kvw * es);
+  TAKE(tr->g_v0l, N * kvw * es); TAKE(tr->qn, N * qw * es); TAKE(tr->kn, N * kvw * es);
+  TAKE(tr->cos_t, tr->T * dh * 4); TAKE(tr->sin_t, tr->T * dh * 4); TAKE(tr->ids, N * 4); TAKE(tr->targets, N * 4);
+#undef TAKE
+  std::vector<float> cos_h, sin_h;
+  rope_tables_host(s.rope_base, tr->T, dh, cos_h, sin_h);
+  if ((st = ojc_upload(be, tr->cos_t, cos_h.data(), cos_h.size() * 4)) != OJC_OK) return fail(st);
+  if ((st = ojc_upload(be, tr->sin_t, sin_h.data(), sin_h.size() * 4)) != OJC_OK) return fail(st);
+  if ((st = ojc_fill_zero(be, tr->stats, 256)) != OJC_OK) return fail(st);
+  // gradient buckets of about 25 MB, filled from the end of the table (the order gradients become final)
+  const int64_t bucket_floats = (25ll << 20) / 4;
+  int64_t end = tr->flat_n;
+  int last = (int)tr->params.size() - 1;
+  while (last >= 0) {
+    int first = last;
+    while (first > 0 && end - tr->params[first].offset < bucket_floats) --first;
+    ojc_trainer::Bucket b{tr->params[first].offset, end - tr->params[first].offset, first, nullptr, false};
+    if (cudaEventCreateWithFlags(&b.ready, cudaEventDisableTiming) != cudaSuccess) return fail(ojc_fail(OJC_ERR_BACKEND, op, "cannot create an event"));
+    tr->buckets.push_back(b);
+    end = tr->params[first].offset;
+    last = first - 1;
+  }
+  *out = tr;
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_close(ojc_trainer* tr) {
+  if (!tr) return OJC_OK;
+  if (tr->be && tr->be->stream) cudaStreamSynchronize(tr->be->stream);
+  for (void* p : tr->owned) ojc_free(tr->be, p);
+  for (auto& b : tr->buckets) if (b.ready) cudaEventDestroy(b.ready);
+  delete tr;
+  return OJC_OK;
+}
+
+int64_t ojc_trainer_param_count(ojc_trainer* tr) { return tr ? (int64_t)tr->params.size() : 0; }
+
+ojc_status ojc_trainer_param_info(ojc_trainer* tr, int64_t index, char* name, int64_t name_cap, int32_t* rank, int64_t* shape2, int32_t* group, int32_t* trains) {
+  if (!tr || index < 0 || index >= (int64_t)tr->params.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "trainer_param_info", "parameter index out of range");
+  const Param& p = tr->params[index];
+  if (name && name_cap > 0) snprintf(name, (size_t)name_cap, "%s", p.name.c_str());
+  if (rank) *rank = p.rank;
+  if (shape2) { shape2[0] = p.shape[0]; shape2[1] = p.shape[1]; }
+  if (group) *group = p.group;
+  if (trains) *trains = p.trains ? 1 : 0;
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_set_param(ojc_trainer* tr, int64_t index, const float* host, uint64_t count) {
+  const char* op = "trainer_set_param";
+  OJC_TRY(check_live(tr, op));
+  if (index < 0 || index >= (int64_t)tr->params.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "parameter index out of range");
+  const Param& p = tr->params[index];
+  if ((int64_t)count != p.n) return ojc_fail(OJC_ERR_SHAPE, op, "element count does not match the parameter");
+  OJC_TRY(ojc_upload(tr->be, tr->W(p), host, count * 4));
+  return refresh_mirror(tr, p);
+}
+
+ojc_status ojc_trainer_get_param(ojc_trainer* tr, int64_t index, float* host, uint64_t count) {
+  const char* op = "trainer_get_param";
+  if (!tr || index < 0 || index >= (int64_t)tr->params.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "parameter index out of range");
+  const Param& p = tr->params[index];
+  if ((int64_t)count != p.n) return ojc_fail(OJC_ERR_SHAPE, op, "element count does not match the parameter");
+  return ojc_download(tr->be, host, tr->W(p), count * 4);
+}
+
+ojc_status ojc_trainer_get_grad(ojc_trainer* tr, int64_t index, float* host, uint64_t count) {
+  const char* op = "trainer_get_grad";
+  if (!tr || index < 0 || index >= (int64_t)tr->params.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "parameter index out of range");
+  const Param& p = tr->params[index];
+  if ((int64_t)count != p.n) return ojc_fail(OJC_ERR_SHAPE, op, "element count does not match the parameter");
+  if (!tr->grads_ready) return ojc_fail(OJC_ERR_BACKEND, op, "no gradients have been computed yet");
+  return ojc_download(tr->be, host, tr->G(p), count * 4);
+}
+
+ojc_status ojc_trainer_gradients_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev) {
+  const char* op = "trainer_gradients";
+  OJC_TRY(check_live(tr, op));
+  if (!ids_dev || !targets_dev) return ojc_fail(OJC_ERR_PLACEMENT, op, "ids and targets must be device pointers");
+  OJC_TRY(forward_hidden(tr, ids_dev));
+  OJC_TRY(backward(tr, ids_dev, targets_dev));
+  tr->grads_ready = true;
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_gradients(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, float* loss_out) {
+  const char* op = "trainer_gradients";
+  OJC_TRY(check_live(tr, op));
+  if (!ids_host || !targets_host) return ojc_fail(OJC_ERR_BACKEND, op, "null ids or targets");
+  // token ids are range-checked on the host before anything is launched (check_ids, ojas-cpu/src/pointwise.rs:285-295)
+  for (int64_t i = 0; i < tr->N; ++i) if (ids_host[i] >= (uint64_t)tr->spec.vocab) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "embedding_forward", "token id outside the vocabulary");
+  OJC_CUDA(tr->be, cudaMemcpyAsync(tr->ids, ids_host, (size_t)tr->N * 4, cudaMemcpyHostToDevice, tr->be->stream), op);
+  OJC_CUDA(tr->be, cudaMemcpyAsync(tr->targets, targets_host, (size_t)tr->N * 4, cudaMemcpyHostToDevice, tr->be->stream), op);
+  OJC_TRY(ojc_trainer_gradients_device(tr, tr->ids, tr->targets));
+  if (loss_out) OJC_TRY(ojc_download(tr->be, loss_out, tr->stats, 4));
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
+  const char* op = "trainer_apply";
+  OJC_TRY(check_live(tr, op));
+  if (!tr->grads_ready) return ojc_fail(OJC_ERR_BACKEND, op, "no gradients to apply");
+  ojc_backend* be = tr->be;
+  const float* gp = tr->g;
+  const int64_t glen = tr->flat_n;
+  const bool clip = tr->cfg.grad_clip > 0.0f;
+  // stats[0] loss, [1] grad norm, [2] clip scale. A failure from here on leaves parameters partly stepped: poison.
+  auto run = [&]() -> ojc_status {
+    OJC_TRY(grad_norm_device(be, &gp, &glen, 1, clip ? tr->cfg.grad_clip : -1.0f, tr->stats + 1));
+    const float* scale = clip ? tr->stats + 2 : nullptr;
+    for (const Param& p : tr->params) {
+      if (!p.trains) continue;
+      bf16* mir = tr->mirror ? tr->mirror + p.offset : nullptr;
+      if (tr->cfg.optimizer == 1 && p.group == GROUP_MUON) {
+        ojc_muon_config mc{tr->cfg.matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
+        OJC_TRY(muon_device(be, tr->W(p), tr->G(p), tr->m1 + p.offset, mir, p.shape[0], p.shape[1], mc, scale));
+      } else {
+        // the hybrid recipe runs AdamW without decay on embeddings and vectors (ADAM_HYBRID_WEIGHT_DECAY, ojas-cpu/src/train.rs:31-37)
+        ojc_adamw_config ac{tr->cfg.adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.optimizer == 1 ? 0.0 : tr->cfg.adam_weight_decay};
+        OJC_TRY(adamw_device(be, tr->W(p), tr->G(p), tr->m1 + p.offset, tr->m2 + p.offset, mir, p.n, tr->step, ac, scale));
+      }
+    }
+    return OJC_OK;
+  };
+  ojc_status st = run();
+  if (st != OJC_OK) { tr->poisoned = true; return st; }
+  tr->step += 1;
+  tr->grads_ready = false;
+  if (grad_norm_out) {
+    st = ojc_download(be, grad_norm_out, tr->stats + 1, 4);
+    if (st != OJC_OK) tr->poisoned = true;
+  }
+  return st;
+}
+
+static ojc_status finish_step(ojc_trainer* tr, ojc_step_report* report) {
+  // the one readback of the step: loss, norm and the deferred fault word (Trainer::finish, trainer.rs:1031-1046)
+  float host[3] = {0, 0, 1};
+  ojc_status st = ojc_download(tr->be, host, tr->stats, 12);
+  if (st != OJC_OK) { tr->poisoned = true; return st; }
+  if (report) { report->loss = host[0]; report->grad_norm = host[1]; report->step = tr->step; report->tokens = (uint64_t)tr->N; }
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev, ojc_step_report* report) {
+  OJC_TRY(ojc_trainer_gradients_device(tr, ids_dev, targets_dev));
+  OJC_TRY(ojc_trainer_apply(tr, nullptr));
+  return finish_step(tr, report);
+}
+
+ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, ojc_step_report* report) {
+  OJC_TRY(ojc_trainer_gradients(tr, ids_host, targets_host, nullptr));
+  OJC_TRY(ojc_trainer_apply(tr, nullptr));
+  return finish_step(tr, report);
+}
+
+ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* logits_host) {
+  const char* op = "trainer_logits";
+  OJC_TRY(check_live(tr, op));
+  if (!ids_host || !logits_host) return ojc_fail(OJC_ERR_BACKEND, op, "null argument");
+  for (int64_t i = 0; i < tr->N; ++i) if (ids_host[i] >= (uint64_t)tr->spec.vocab) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "embedding_forward", "token id outside the vocabulary");
+  OJC_TRY(ojc_upload(tr->be, tr->ids, ids_host, (uint64_t)tr->N * 4));
+  OJC_TRY(forward_hidden(tr, tr->ids));
+  const int64_t V = tr->spec.vocab, d = tr->spec.n_embd;
+  void* logits = nullptr;
+  OJC_TRY(ojc_alloc(tr->be, (uint64_t)tr->N * V * 4, &logits));
+  ojc_status st = linear_forward_impl(tr->be, tr->hf, tr->act_dt, tr->WM(tr->params[0]), tr->act_dt, logits, OJC_F32, tr->N, d, V, nullptr);
+  if (st == OJC_OK) st = ojc_download(tr->be, logits_host, logits, (uint64_t)tr->N * V * 4);
+  ojc_free(tr->be, logits);
+  return st;
+}
+
+int64_t ojc_trainer_bucket_count(ojc_trainer* tr) { return tr ? (int64_t)tr->buckets.size() : 0; }
+ojc_status ojc_trainer_bucket(ojc_trainer* tr, int64_t index, void** device_ptr, uint64_t* floats) {
+  if (!tr || index < 0 || index >= (int64_t)tr->buckets.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "trainer_bucket", "bucket index out of range");
+  if (device_ptr) *device_ptr = tr->g + tr->buckets[index].offset;
+  if (floats) *floats = (uint64_t)tr->buckets[index].floats;
+  return OJC_OK;
+}
+ojc_status ojc_trainer_bucket_ready_event(ojc_trainer* tr, int64_t index, void** cuda_event) {
+  if (!tr || index < 0 || index >= (int64_t)tr->buckets.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "trainer_bucket", "bucket index out of range");
+  if (cuda_event) *cuda_event = (void*)tr->buckets[index].ready;
+  return OJC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,204 @@
+"""Whole-step parity of the C++ step driver: against the reference's torch goldens (tests/golden) and against the CPU
+oracle on BASELINE config 1 (tiny GPT, one full AdamW step, f32), plus the bf16-autocast tolerance of the north star.
+
+Gates (ojas-oracle/src/parity.rs:29-45 and the north star): f32 mode loss 1e-5 relative, every gradient 1e-4 normwise
+(exactly zero where the golden is zero); bf16 autocast loss within 1e-2 relative after one step.
+"""
+import json
+
+import numpy as np
+import pytest
+from safetensors import safe_open
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+LOSS_TOL, LOGITS_TOL, GRAD_TOL = 1e-5, 1e-5, 1e-4
+
+
+@pytest.fixture(scope="module")
+def be():
+    from ojas_b200 import CudaBackend
+    backend = CudaBackend(0, 64 << 30)
+    yield backend
+    backend.close()
+
+
+def load(path, prefix=""):
+    f = safe_open(str(path), "np")
+    return {k[len(prefix):]: f.get_tensor(k) for k in f.keys() if k.startswith(prefix)}, f.metadata()
+
+
+def spec_pair(meta):
+    from ojas_b200 import ModelSpec
+    s = json.loads(meta["ojas.spec"])
+    kw = dict(vocab=s["vocab"], n_embd=s["n_embd"], n_layer=s["n_layer"], n_head=s["n_head"], n_kv_head=s["n_kv_head"], head_dim=s["head_dim"],
+              hidden=s["hidden"], max_seq=s["max_seq"], window=s.get("window"), rope_base=s["rope_base"], rms_eps=s["rms_eps"])
+    return ModelSpec(**kw), orc.Spec(**kw)
+
+
+def normwise(got, want):
+    got, want = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
+    return np.linalg.norm(got - want) / np.linalg.norm(want)
+
+
+def make_trainer(be, spec, params_by_name, batch, seq, **cfg):
+    from ojas_b200 import TrainConfig, Trainer
+    tr = Trainer(be, spec, TrainConfig(**cfg), batch, seq)
+    tr.set_params([params_by_name[p.name] for p in tr.params])
+    return tr
+
+
+def check_grads(tr, want, no_grad, tol=GRAD_TOL):
+    for i, p in enumerate(tr.params):
+        if p.name in no_grad:
+            assert not p.trains
+            continue
+        g, w = tr.get_grad(i), want[p.name]
+        if not np.any(w):
+            assert not np.any(g), p.name
+        else:
+            assert normwise(g, w) <= tol, (p.name, normwise(g, w))
+
+
+def test_tiny_forward_and_gradients_match_the_torch_goldens(be, golden_dir):
+    params, meta = load(golden_dir / "tiny/init.safetensors")
+    spec, _ = spec_pair(meta)
+    fwd, fmeta = load(golden_dir / "tiny/forward.safetensors")
+    want_loss = float(np.uint32(json.loads(fmeta["ojas.oracle"])["loss_f32_bits"]).view(np.float32))
+    for which in ("grads_init", "grads_step5"):
+        want, gmeta = load(golden_dir / f"tiny/{which}.safetensors")
+        gmeta = json.loads(gmeta["ojas.oracle"])
+        p = params if which == "grads_init" else load(golden_dir / "tiny/trace_ns5_f32.safetensors")[0]
+        tr = make_trainer(be, spec, p, 2, 32, loss_seed=gmeta["loss_seed"], grad_clip=0.0)
+        if which == "grads_init":
+            logits = tr.logits(fwd["x"])
+            assert normwise(logits.reshape(2, 32, 256), fwd["logits"]) <= LOGITS_TOL
+        loss = tr.gradients(fwd["x"], fwd["y"])
+        assert abs(loss - gmeta["loss"]) / gmeta["loss"] <= LOSS_TOL
+        if which == "grads_init":
+            assert abs(loss - want_loss) / want_loss <= LOSS_TOL
+        check_grads(tr, want, gmeta["no_grad"])
+        tr.close()
+
+
+@pytest.mark.parametrize("variant", ["gqa", "swa"])
+def test_gqa_and_sliding_window_variants(be, golden_dir, variant):
+    path = golden_dir / f"variants/{variant}.safetensors"
+    params, meta = load(path, "param/")
+    grads, _ = load(path, "grad/")
+    rest, _ = load(path)
+    spec, _ = spec_pair(meta)
+    info = json.loads(meta["ojas.oracle"])
+    tr = make_trainer(be, spec, params, 2, 32, loss_seed=info["loss_seed"], grad_clip=0.0)
+    assert normwise(tr.logits(rest["x"]).reshape(rest["logits"].shape), rest["logits"]) <= LOGITS_TOL
+    loss = tr.gradients(rest["x"], rest["y"])
+    assert abs(loss - info["loss"]) / info["loss"] <= LOSS_TOL
+    check_grads(tr, grads, info["no_grad"])
+    tr.close()
+
+
+def config1():
+    """BASELINE config 1: 4 layers, d 256, 4 x 64 heads, hidden 1024, V 4096, T 256, B 8; weights N(0, 0.02) from seed 0
+    (every matrix, o_proj and ffn.down included); ids uniform from SplitMix64(1), targets = inputs shifted by one."""
+    kw = dict(vocab=4096, n_embd=256, n_layer=4, n_head=4, n_kv_head=4, head_dim=64, hidden=1024, max_seq=256)
+    ospec = orc.Spec(**kw)
+    params = orc.init_params(ospec, 0, normal_everywhere=True)
+    rng = orc.SplitMix64(1)
+    b, t = 8, 256
+    draws = np.array([rng.below(4096) for _ in range(b * (t + 1))], np.uint32).reshape(b, t + 1)
+    return kw, ospec, params, draws[:, :-1].copy(), draws[:, 1:].copy()
+
+
+@pytest.fixture(scope="module")
+def c1():
+    kw, ospec, params, x, y = config1()
+    loss, grads, _ = orc.forward_loss(ospec, params, x, y)
+    table = orc.param_table(ospec)
+    stepped = []
+    for info, p, g in zip(table, params, grads):
+        q, m, v = p.copy().ravel(), np.zeros(p.size, np.float32), np.zeros(p.size, np.float32)
+        if info.trains:
+            orc.adamw_step(q, g.ravel(), m, v, 0, 3e-4, weight_decay=0.1)
+        stepped.append(q.reshape(p.shape))
+    return kw, params, x, y, loss, grads, stepped
+
+
+def test_config1_one_full_adamw_step_f32(be, c1):
+    from ojas_b200 import ModelSpec
+    kw, params, x, y, oloss, ograds, ostepped = c1
+    tr = make_trainer(be, ModelSpec(**kw), {p.name: v for p, v in zip(orc.param_table(orc.Spec(**kw)), params)}, 8, 256, optimizer="adamw", adam_lr=3e-4,
+                      adam_weight_decay=0.1, grad_clip=0.0)
+    loss = tr.gradients(x, y)
+    assert abs(loss - oloss) / oloss <= LOSS_TOL, (loss, oloss)
+    for i, p in enumerate(tr.params):
+        if p.trains:
+            assert normwise(tr.get_grad(i), ograds[i]) <= GRAD_TOL, (p.name, normwise(tr.get_grad(i), ograds[i]))
+    before = be.device_readbacks()
+    rep = tr.step(x, y)
+    assert be.device_readbacks() == before + 1  # one readback per step (Budget::device_readbacks, trainer gate G10)
+    assert abs(rep.loss - oloss) / oloss <= LOSS_TOL and rep.step == 1 and rep.tokens == 8 * 256
+    assert abs(rep.grad_norm - float(orc.grad_norm(ograds))) <= 1e-5 * float(orc.grad_norm(ograds))
+    for i, p in enumerate(tr.params):
+        assert normwise(tr.get_param(i), ostepped[i]) <= 1e-6, p.name
+    tr.close()
+
+
+def test_config1_bf16_autocast_loss_within_one_percent(be, c1):
+    from ojas_b200 import ModelSpec
+    kw, params, x, y, oloss, ograds, _ = c1
+    tr = make_trainer(be, ModelSpec(**kw), {p.name: v for p, v in zip(orc.param_table(orc.Spec(**kw)), params)}, 8, 256, autocast_bf16=True, optimizer="adamw",
+                      adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=0.0)
+    rep = tr.step(x, y)
+    assert abs(rep.loss - oloss) / oloss <= 1e-2, (rep.loss, oloss)
+    rep2 = tr.step(x, y)
+    assert rep2.loss < rep.loss  # the step went downhill on the same batch
+    tr.close()
+    tr = make_trainer(be, ModelSpec(**kw), {p.name: v for p, v in zip(orc.param_table(orc.Spec(**kw)), params)}, 8, 256, autocast_bf16=True, grad_clip=0.0)
+    tr.gradients(x, y)
+    worst = max(normwise(tr.get_grad(i), ograds[i]) for i, p in enumerate(tr.params) if p.trains and len(p.shape) == 2)
+    assert worst <= 5e-2, worst  # bf16 operands: a few 1e-3 per matrix is expected; a wrong kernel is off by O(1)
+    tr.close()
+
+
+def test_muon_hybrid_step_matches_the_oracle_grouping(be, golden_dir):
+    """Trainer semantics: Muon NS5 on rank-2 hidden weights, AdamW without decay on the embedding and vectors, clip 1.0."""
+    params, meta = load(golden_dir / "tiny/trace_ns5_f32.safetensors")
+    spec, ospec = spec_pair(meta)
+    fwd, _ = load(golden_dir / "tiny/forward.safetensors")
+    table = orc.param_table(ospec)
+    plist = [params[i.name] for i in table]
+    _, grads, _ = orc.forward_loss(ospec, plist, fwd["x"], fwd["y"])
+    clipped = [g.copy() for g in grads]
+    orc.clip_grad_norm(clipped, 1.0)
+    want = []
+    for info, p, g in zip(table, plist, clipped):
+        q = p.copy()
+        if not info.trains:
+            pass
+        elif info.group == 1:
+            mom = np.zeros_like(q)
+            orc.muon_ns5_step(q, g, mom, lr=0.025, momentum=0.95, weight_decay=0.1)
+        else:
+            flat, m, v = q.ravel(), np.zeros(q.size, np.float32), np.zeros(q.size, np.float32)
+            orc.adamw_step(flat, g.ravel(), m, v, 0, 6e-4, weight_decay=0.0)
+        want.append(q)
+    tr = make_trainer(be, spec, params, 2, 32, optimizer="muon", muon_momentum=0.95, grad_clip=1.0)
+    tr.step(fwd["x"], fwd["y"])
+    for i, p in enumerate(tr.params):
+        assert normwise(tr.get_param(i) - plist[i] + 1e-30, want[i] - plist[i] + 1e-30) <= 2e-3 or not p.trains, p.name
+    tr.close()
+
+
+def test_out_of_range_token_is_refused_before_any_launch(be):
+    from ojas_b200 import ModelSpec, OjasError, TrainConfig, Trainer
+    spec = ModelSpec(vocab=64, n_embd=32, n_layer=1, n_head=2, n_kv_head=2, head_dim=16, hidden=64, max_seq=8)
+    tr = Trainer(be, spec, TrainConfig(), 1, 8)
+    ids = np.arange(8, dtype=np.uint32)
+    ids[3] = 64
+    launches = be.kernel_launches()
+    with pytest.raises(OjasError) as e:
+        tr.gradients(ids, ids)
+    assert e.value.kind == "OutOfRange" and be.kernel_launches() == launches
+    tr.close()
