@@ -83,6 +83,13 @@ void* ojc_stream(ojc_backend* be);                                              
 ojc_status ojc_fill_zero(ojc_backend* be, void* ptr, uint64_t bytes);
 uint64_t ojc_kernel_launches(ojc_backend* be);                                  /* kernels launched by this backend so far */
 
+/* ---- instrumentation (no counterpart in the reference): when enabled, every tensor-core GEMM launch is bracketed by CUDA
+ *      events on the backend's stream; the read call waits for the stream, returns the summed device time, the summed
+ *      2*m*n*k and the launch count since the last read, and resets them. */
+ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable);
+ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches);
+ojc_status ojc_stream_wait_event(ojc_backend* be, void* cuda_stream, void* cuda_event);  /* cuda_stream waits for an event recorded by this backend (NULL stream: the backend's own) */
+
 /* ---- casts: BackendCore::{cast_bf16,to_bf16,to_f32} (backend.rs:982,1042,1070); RNE on the integer bits,
  *      NaN keeps sign + payload and sets the quiet bit (autocast.rs:89-96). */
 ojc_status ojc_cast_bf16(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);  /* F32 -> F32 storage holding bf16-exact values */
@@ -172,6 +179,7 @@ ojc_status ojc_trainer_get_grad(ojc_trainer* tr, int64_t index, float* host, uin
 ojc_status ojc_trainer_gradients(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, float* loss_out);
 ojc_status ojc_trainer_gradients_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev); /* inputs already resident */
 ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out);                                   /* clip + optimizer, step += 1 */
+ojc_status ojc_trainer_finish(ojc_trainer* tr, ojc_step_report* report);                               /* Trainer::finish (trainer.rs:1031): sync + the one readback (loss, norm, fault word) */
 ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, ojc_step_report* report); /* gradients + apply + the one loss readback */
 ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev, ojc_step_report* report);
 ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* logits_host);          /* forward_logits, block.rs:407-416; [batch*seq, vocab] */

@@ -93,6 +93,10 @@ class Tensor:
         return self.backend.download(self)
 
 
+def _dt(choice, default):
+    return default if choice is None else choice
+
+
 def _p(t: "Tensor | None"):
     return C.byref(t.c()) if t is not None else None
 
@@ -166,6 +170,18 @@ class CudaBackend:
     def stream(self) -> int:
         return int(lib.ojc_stream(self._handle) or 0)
 
+    def profile_gemm(self, enable: bool):
+        _check(lib.ojc_profile_gemm(self._handle, C.c_int32(int(enable))))
+
+    def profile_gemm_read(self):
+        """(device milliseconds, 2mnk flops, launches) of the tensor-core GEMMs since the last read."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_uint64()
+        _check(lib.ojc_profile_gemm_read(self._handle, C.byref(ms), C.byref(fl), C.byref(n)))
+        return ms.value, fl.value, n.value
+
+    def stream_wait_event(self, stream_ptr: int, event_ptr: int):
+        _check(lib.ojc_stream_wait_event(self._handle, C.c_void_p(stream_ptr), C.c_void_p(event_ptr)))
+
     def set_sync_timeout_ms(self, ms: int):
         lib.ojc_set_sync_timeout_ms(self._handle, C.c_uint64(ms))
 
@@ -223,7 +239,7 @@ class CudaBackend:
 
     # ---- BackendModule
     def embedding_forward(self, table: Tensor, ids: Tensor, out_dtype: DType | None = None) -> Tensor:
-        out = self.empty(ids.shape + (table.shape[1],), out_dtype or table.dtype)
+        out = self.empty(ids.shape + (table.shape[1],), _dt(out_dtype, table.dtype))
         _check(lib.ojc_embedding_forward(self._handle, _p(table), _p(ids), _p(out)))
         return out
 
@@ -233,22 +249,22 @@ class CudaBackend:
         return g
 
     def linear_forward(self, x: Tensor, weight: Tensor, out_dtype: DType | None = None) -> Tensor:
-        y = self.empty(x.shape[:-1] + (weight.shape[0],), out_dtype or x.dtype)
+        y = self.empty(x.shape[:-1] + (weight.shape[0],), _dt(out_dtype, x.dtype))
         _check(lib.ojc_linear_forward(self._handle, _p(x), _p(weight), _p(y)))
         return y
 
     def linear_backward(self, x: Tensor, weight: Tensor, grad_y: Tensor, out_dtype: DType | None = None):
-        gx, gw = self.empty(x.shape, out_dtype or x.dtype), self.empty(weight.shape, DType.F32)
+        gx, gw = self.empty(x.shape, _dt(out_dtype, x.dtype)), self.empty(weight.shape, DType.F32)
         _check(lib.ojc_linear_backward(self._handle, _p(x), _p(weight), _p(grad_y), _p(gx), _p(gw)))
         return gx, gw
 
     def linear_backward_input(self, weight: Tensor, grad_y: Tensor, out_dtype: DType | None = None) -> Tensor:
-        gx = self.empty(grad_y.shape[:-1] + (weight.shape[1],), out_dtype or grad_y.dtype)
+        gx = self.empty(grad_y.shape[:-1] + (weight.shape[1],), _dt(out_dtype, grad_y.dtype))
         _check(lib.ojc_linear_backward_input(self._handle, _p(weight), _p(grad_y), _p(gx)))
         return gx
 
     def rms_norm_forward(self, x: Tensor, weight: Tensor, eps: float, out_dtype: DType | None = None) -> Tensor:
-        y = self.empty(x.shape, out_dtype or x.dtype)
+        y = self.empty(x.shape, _dt(out_dtype, x.dtype))
         _check(lib.ojc_rms_norm_forward(self._handle, _p(x), _p(weight), C.c_float(eps), _p(y)))
         return y
 
@@ -328,14 +344,14 @@ class CudaBackend:
         return out, scales
 
     def per_head_sigmoid_gate_backward(self, inp, weight, bias, attn, grad_out, saved_scales=None, grad_input_dtype=None):
-        gi, gw, gb, ga = self.empty(inp.shape, grad_input_dtype or inp.dtype), self.empty(weight.shape), self.empty(bias.shape), self.empty(attn.shape, attn.dtype)
+        gi, gw, gb, ga = self.empty(inp.shape, _dt(grad_input_dtype, inp.dtype)), self.empty(weight.shape), self.empty(bias.shape), self.empty(attn.shape, attn.dtype)
         _check(lib.ojc_per_head_sigmoid_gate_backward(self._handle, _p(inp), _p(weight), _p(bias), _p(attn), _p(grad_out), _p(saved_scales), _p(gi), _p(gw), _p(gb), _p(ga)))
         return gi, gw, gb, ga
 
     per_head_sigmoid_gate_backward_saved = per_head_sigmoid_gate_backward
 
     def _unary(self, fn, x, out_dtype=None):
-        y = self.empty(x.shape, out_dtype or x.dtype)
+        y = self.empty(x.shape, _dt(out_dtype, x.dtype))
         _check(fn(self._handle, _p(x), _p(y)))
         return y
 
@@ -370,7 +386,7 @@ class CudaBackend:
     def linear_cross_entropy_mean(self, x, weight, targets, ignore_index=None, chunk=(0, 0), grads=(True, True), grad_input_dtype=None):
         """LinearCe {loss, grad_input, grad_weight} (ojas-core/src/backend.rs:2513, CeChunk/CeGrads 3081-3136)."""
         loss = self.empty((1,), DType.F32)
-        gx = self.empty(x.shape, grad_input_dtype or x.dtype) if grads[0] else None
+        gx = self.empty(x.shape, _dt(grad_input_dtype, x.dtype)) if grads[0] else None
         gw = self.empty(weight.shape, DType.F32) if grads[1] else None
         _check(lib.ojc_linear_cross_entropy_mean(self._handle, _p(x), _p(weight), _p(targets), C.c_int32(ignore_index is not None), C.c_uint32(ignore_index or 0),
                                                  C.c_int64(chunk[0]), C.c_int64(chunk[1]), _p(loss), _p(gx), _p(gw)))
@@ -513,7 +529,8 @@ class Trainer:
 
     def close(self):
         if self._h:
-            lib.ojc_trainer_close(self._h)
+            if self.backend._handle:  # a closed backend already released everything the trainer owned
+                lib.ojc_trainer_close(self._h)
             self._h = None
 
     def __del__(self):
@@ -548,10 +565,16 @@ class Trainer:
         _check(lib.ojc_trainer_gradients(self._h, C.c_void_p(ids.ctypes.data), C.c_void_p(targets.ctypes.data), C.byref(loss)))
         return loss.value
 
-    def apply(self) -> float:
+    def apply(self, read_norm: bool = True):
+        """Clip + optimizer. With read_norm the gradient norm is read back (a sync); without, nothing is."""
         norm = C.c_float()
-        _check(lib.ojc_trainer_apply(self._h, C.byref(norm)))
-        return norm.value
+        _check(lib.ojc_trainer_apply(self._h, C.byref(norm) if read_norm else None))
+        return norm.value if read_norm else None
+
+    def finish(self) -> StepReport:
+        rep = _lib.StepReport()
+        _check(lib.ojc_trainer_finish(self._h, C.byref(rep)))
+        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens)
 
     def step(self, ids, targets) -> StepReport:
         ids, targets = self._ids(ids), self._ids(targets)

@@ -41,6 +41,10 @@ struct ojc_backend {
   uint64_t scratch_bytes = 0;
   int sm_count = 148;
   void* tmap_encode = nullptr;             // cuTensorMapEncodeTiled, resolved once
+  bool profile_gemm = false;               // bracket tensor-core GEMM launches with events
+  struct GemmSample { cudaEvent_t start, stop; double flops; };
+  std::vector<GemmSample> gemm_samples;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> event_pool;
 };
 
 ojc_status ojc_fail(ojc_status st, const char* op, const std::string& detail);

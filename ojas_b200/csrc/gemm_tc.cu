@@ -366,8 +366,18 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     args.partial = (float*)ws;
   }
   int grid = tiles * splits < be->sm_count ? tiles * splits : be->sm_count;
+  ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k};
+  if (be->profile_gemm) {
+    if (!be->event_pool.empty()) { sample.start = be->event_pool.back().first; sample.stop = be->event_pool.back().second; be->event_pool.pop_back(); }
+    else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }
+    OJC_CUDA(be, cudaEventRecord(sample.start, be->stream), op);
+  }
   gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, args);
   OJC_LAUNCHED(be, op);
+  if (be->profile_gemm) {
+    OJC_CUDA(be, cudaEventRecord(sample.stop, be->stream), op);
+    be->gemm_samples.push_back(sample);
+  }
   if (splits > 1) {
     splitk_reduce_kernel<<<elementwise_grid(be, m * n, 256), 256, 0, be->stream>>>(args.partial, splits, c, args.c_bf16, ldc, (int)m, (int)n, alpha,
                                                                                    args.accumulate, residual);

@@ -120,6 +120,8 @@ ojc_status ojc_close(ojc_backend* be) {
   if (!be) return OJC_OK;
   cudaSetDevice(be->device);
   if (be->stream) cudaStreamSynchronize(be->stream);
+  for (auto& s : be->gemm_samples) { cudaEventDestroy(s.start); cudaEventDestroy(s.stop); }
+  for (auto& e : be->event_pool) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
   for (auto& kv : be->live_blocks) cudaFree(kv.first);
   release_cache(be);
   if (be->scratch) cudaFree(be->scratch);
@@ -236,6 +238,36 @@ ojc_status ojc_download(ojc_backend* be, void* dst, const void* src, uint64_t by
   OJC_TRY(bounded_wait(be, "download"));
   be->readbacks++;
   return report_fault(be, "download");
+}
+
+ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable) {
+  OJC_ALIVE(be, "profile_gemm");
+  be->profile_gemm = enable != 0;
+  return OJC_OK;
+}
+
+ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches) {
+  OJC_ALIVE(be, "profile_gemm_read");
+  OJC_CUDA(be, cudaStreamSynchronize(be->stream), "profile_gemm_read");
+  double ms = 0.0, flops = 0.0;
+  for (auto& s : be->gemm_samples) {
+    float t = 0.0f;
+    if (cudaEventElapsedTime(&t, s.start, s.stop) == cudaSuccess) ms += t; else cudaGetLastError();
+    flops += s.flops;
+    be->event_pool.emplace_back(s.start, s.stop);
+  }
+  if (total_ms) *total_ms = ms;
+  if (total_flops) *total_flops = flops;
+  if (launches) *launches = be->gemm_samples.size();
+  be->gemm_samples.clear();
+  return OJC_OK;
+}
+
+ojc_status ojc_stream_wait_event(ojc_backend* be, void* cuda_stream, void* cuda_event) {
+  OJC_ALIVE(be, "stream_wait_event");
+  if (!cuda_event) return ojc_fail(OJC_ERR_BACKEND, "stream_wait_event", "null event");
+  OJC_CUDA(be, cudaStreamWaitEvent(cuda_stream ? (cudaStream_t)cuda_stream : be->stream, (cudaEvent_t)cuda_event, 0), "stream_wait_event");
+  return OJC_OK;
 }
 
 ojc_status ojc_fill_zero(ojc_backend* be, void* ptr, uint64_t bytes) {

@@ -356,9 +356,9 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
   const uint64_t es = dtype_size(tr->act_dt);
   auto fail = [&](ojc_status st) { ojc_trainer_close(tr); return st; };
   ojc_status st = OJC_OK;
-#define TAKE(ptr, bytes) if ((st = take_as(tr, (uint64_t)(bytes), &(ptr))) != OJC_OK) return fail(st)
+#define TAKE(ptr, bytes) do { if ((st = take_as(tr, (uint64_t)(bytes), &(ptr))) != OJC_OK) return fail(st); } while (0)
   TAKE(tr->w, tr->flat_n * 4); TAKE(tr->g, tr->flat_n * 4); TAKE(tr->m1, tr->flat_n * 4); TAKE(tr->m2, tr->flat_n * 4);
-  if (tr->act_dt == OJC_BF16) TAKE(tr->mirror, tr->flat_n * 2);
+  if (tr->act_dt == OJC_BF16) { TAKE(tr->mirror, tr->flat_n * 2); }
   for (float* p : {tr->w, tr->g, tr->m1, tr->m2}) if ((st = ojc_fill_zero(be, p, (uint64_t)tr->flat_n * 4)) != OJC_OK) return fail(st);
   if (tr->mirror && (st = ojc_fill_zero(be, tr->mirror, (uint64_t)tr->flat_n * 2)) != OJC_OK) return fail(st);
   tr->acts.resize(L);
@@ -366,7 +366,8 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
     LayerActs& a = tr->acts[l];
     TAKE(a.x, N * d * 4); TAKE(a.x1, N * d * 4); TAKE(a.lse, tr->B * H * tr->T * 4); TAKE(a.scales, N * H * 4);
     TAKE(a.h, N * d * es); TAKE(a.q, N * qw * es); TAKE(a.k, N * kvw * es); TAKE(a.rawv, N * kvw * es); TAKE(a.qr, N * qw * es); TAKE(a.kr, N * kvw * es);
-    if (l > 0) TAKE(a.v, N * kvw * es); else a.v = nullptr;
+    a.v = nullptr;
+    if (l > 0) { TAKE(a.v, N * kvw * es); }
     TAKE(a.y, N * qw * es); TAKE(a.yg, N * qw * es); TAKE(a.h2, N * d * es); TAKE(a.a, N * F * es); TAKE(a.u, N * F * es); TAKE(a.m, N * F * es);
   }
   TAKE(tr->x_final, N * d * 4); TAKE(tr->gx, N * d * 4); TAKE(tr->g_h, N * d * 4); TAKE(tr->g_h2, N * d * 4); TAKE(tr->gv0_acc, N * kvw * 4); TAKE(tr->stats, 256);
@@ -514,6 +515,11 @@ static ojc_status finish_step(ojc_trainer* tr, ojc_step_report* report) {
   if (st != OJC_OK) { tr->poisoned = true; return st; }
   if (report) { report->loss = host[0]; report->grad_norm = host[1]; report->step = tr->step; report->tokens = (uint64_t)tr->N; }
   return OJC_OK;
+}
+
+ojc_status ojc_trainer_finish(ojc_trainer* tr, ojc_step_report* report) {
+  OJC_TRY(check_live(tr, "trainer_finish"));
+  return finish_step(tr, report);
 }
 
 ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev, ojc_step_report* report) {

@@ -88,7 +88,9 @@ def test_rms_norm(be, rows, dim):
     assert rel(be.rms_norm_forward(dx, dw, 1e-6).numpy(), orc.rms_norm_forward(x, w, 1e-6)) <= FWD_TOL
     gx, gw = be.rms_norm_backward(dx, dw, dgy, 1e-6)
     ogx, ogw = orc.rms_norm_backward(x, w, gy, 1e-6)
-    assert rel(gx.numpy(), ogx) <= GRAD_TOL and rel(gw.numpy(), ogw) <= GRAD_TOL
+    if dim > 1:  # with one column dX is pure cancellation noise on both sides
+        assert rel(gx.numpy(), ogx) <= GRAD_TOL
+    assert rel(gw.numpy(), ogw) <= GRAD_TOL
 
 
 def test_rms_qk_norm_is_two_row_norms(be):
@@ -127,6 +129,25 @@ def test_causal_sdpa_f32_tier(be, shape, hkv, window):
     assert max(rel(gq.numpy(), ogq), rel(gk.numpy(), ogk), rel(gv.numpy(), ogv)) <= GRAD_TOL
     rq, rk, rv = be.causal_sdpa_backward_recompute(dq, dk, dv, dgy, window)
     assert max(rel(rq.numpy(), ogq), rel(rk.numpy(), ogk), rel(rv.numpy(), ogv)) <= GRAD_TOL
+
+
+@pytest.mark.parametrize("shape,hkv,window", [((1, 2, 300, 64), 2, None), ((2, 4, 128, 64), 2, None), ((1, 2, 129, 128), 2, None), ((1, 2, 200, 64), 1, 40),
+                                              ((1, 1, 64, 64), 1, None), ((1, 2, 1, 64), 2, None), ((2, 3, 1024, 64), 3, None)])
+def test_causal_sdpa_bf16_tensor_core_tier(be, shape, hkv, window):
+    """bf16 q/k/v on the tensor-core kernels, against the f32 oracle on the same bf16-exact inputs: 2e-2 relative."""
+    from ojas_b200 import DType
+    b, h, t, d = shape
+    q, gy = orc.round_bf16(rnd(300, shape, 1.0)), orc.round_bf16(rnd(303, shape, 1.0))
+    k, v = orc.round_bf16(rnd(301, (b, hkv, t, d), 1.0)), orc.round_bf16(rnd(302, (b, hkv, t, d), 1.0))
+    oy, olse = orc.causal_sdpa_forward(q, k, v, window)
+    ogq, ogk, ogv = orc.causal_sdpa_backward(q, k, v, oy, olse, gy, window)
+    dq, dk, dv, dgy = (be.upload(a, DType.BF16) for a in (q, k, v, gy))
+    y, lse = be.causal_sdpa_forward(dq, dk, dv, window)
+    assert rel(y.numpy(), oy) <= 2e-2 and rel(lse.numpy(), olse) <= 1e-4
+    gq, gk, gv = be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy, window)
+    assert max(rel(gq.numpy(), ogq), rel(gk.numpy(), ogk), rel(gv.numpy(), ogv)) <= 2e-2
+    rq, rk, rv = be.causal_sdpa_backward_recompute(dq, dk, dv, dgy, window)
+    assert max(rel(rq.numpy(), ogq), rel(rk.numpy(), ogk), rel(rv.numpy(), ogv)) <= 2e-2
 
 
 def test_sdpa_reads_permuted_views_without_a_copy(be):

@@ -141,7 +141,7 @@ def test_config1_one_full_adamw_step_f32(be, c1):
     assert abs(rep.loss - oloss) / oloss <= LOSS_TOL and rep.step == 1 and rep.tokens == 8 * 256
     assert abs(rep.grad_norm - float(orc.grad_norm(ograds))) <= 1e-5 * float(orc.grad_norm(ograds))
     for i, p in enumerate(tr.params):
-        assert normwise(tr.get_param(i), ostepped[i]) <= 1e-6, p.name
+        assert normwise(tr.get_param(i), ostepped[i]) <= 1e-4, p.name  # TRACE_PARAM_NORMWISE_REL_TOL, ojas-oracle/src/parity.rs:41-43
     tr.close()
 
 
@@ -164,8 +164,8 @@ def test_config1_bf16_autocast_loss_within_one_percent(be, c1):
 
 def test_muon_hybrid_step_matches_the_oracle_grouping(be, golden_dir):
     """Trainer semantics: Muon NS5 on rank-2 hidden weights, AdamW without decay on the embedding and vectors, clip 1.0."""
-    params, meta = load(golden_dir / "tiny/trace_ns5_f32.safetensors")
-    spec, ospec = spec_pair(meta)
+    params, _ = load(golden_dir / "tiny/trace_ns5_f32.safetensors")
+    spec, ospec = spec_pair(load(golden_dir / "tiny/init.safetensors")[1])
     fwd, _ = load(golden_dir / "tiny/forward.safetensors")
     table = orc.param_table(ospec)
     plist = [params[i.name] for i in table]
