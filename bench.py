@@ -1,0 +1,312 @@
+#!/usr/bin/env python
+"""Benchmark of the one hot path: the nanolab GPT-124M bf16 training step on B200.
+
+    python bench.py --gpus N --steps K --warmup W            this library (one process per GPU; torchrun for N > 1)
+    python bench.py --impl reference --gpus N --steps K ...  the CPU restatement of the reference's path on the host cores
+
+A step is one optimizer step (forward, fused tied-head cross-entropy, backward, AdamW on every tensor) over one batch
+of synthetic token ids: ModelSpec::nanolab_124m (hidden 2048), B 32 x T 1024 per GPU, bf16 autocast. Rank 0 prints one
+JSON line. `value` is tokens/s with the batch already in HBM; `e2e` is the same step through Trainer.step with pinned
+host ids/targets copied in and the loss read back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+BATCH, SEQ = 32, 1024
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tc_kernel, averaged over the step's GEMM launches
+# (profiles/gemm_tc_kernel_124m_step.md); None until a capture exists.
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def spec_kwargs() -> dict:
+    return dict(vocab=50304, n_embd=768, n_layer=12, n_head=12, n_kv_head=12, head_dim=64, hidden=2048, max_seq=1024)
+
+
+def init_weights(param_infos, seed: int):
+    """Random-init weights of the architecture: N(0, 0.02) on every matrix, ones on norm weights, zeros on bias / lambda."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    for p in param_infos:
+        if len(p.shape) == 2:
+            out.append((rng.standard_normal(p.shape, dtype=np.float32) * np.float32(0.02)).astype(np.float32))
+        elif p.name.endswith("norm.weight") or ".norm1." in p.name or ".norm2." in p.name or p.name == "norm_f.weight":
+            out.append(np.ones(p.shape, np.float32))
+        else:
+            out.append(np.zeros(p.shape, np.float32))
+    return out
+
+
+def token_batches(count: int, batch: int, seq: int, vocab: int, seed: int):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    for _ in range(count):
+        draws = rng.integers(0, vocab, size=(batch, seq + 1), dtype=np.uint32)
+        out.append((np.ascontiguousarray(draws[:, :-1]), np.ascontiguousarray(draws[:, 1:])))
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.lines, self.proc = device, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.device)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()  # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_step_rate(budget_s: float, steps: int, warmup: int):
+    """Times the CPU restatement of the reference's step (oracle/, all host threads) on a bounded sample of the workload:
+    the 124M model, B = 1, T chosen so (steps + warmup) steps fit the budget. Returns (tokens/s, cores, sample text, ms/step)."""
+    from oracle import oracle as orc
+    spec = orc.Spec(**spec_kwargs())
+    table = orc.param_table(spec)
+    params = init_weights(table, 0)
+    m1 = [np.zeros(p.size, np.float32) for p in params]
+    m2 = [np.zeros(p.size, np.float32) for p in params]
+    cores = os.cpu_count() or 1
+
+    def one_step(ids, targets, step_before):
+        loss, grads, _ = orc.forward_loss(spec, params, ids, targets)
+        for info, p, g, a, b in zip(table, params, grads, m1, m2):
+            if info.trains:
+                orc.adamw_step(p.reshape(-1), g.reshape(-1), a, b, step_before, 3e-4, weight_decay=0.1)
+        return float(loss)
+
+    probe_t = 64
+    (px, py), = token_batches(1, 1, probe_t, spec.vocab, 7)
+    t0 = time.perf_counter()
+    one_step(px, py, 0)
+    probe = time.perf_counter() - t0
+    # the optimizer sweep and the embedding-sized passes do not shrink with T: split the probe into a fixed and a per-token part
+    t1 = time.perf_counter()
+    one_step(px, py, 1)
+    probe = min(probe, time.perf_counter() - t1)
+    seq = 64
+    for cand in (1024, 512, 256, 128):
+        if probe * (cand / probe_t) * (steps + warmup) <= budget_s:
+            seq = cand
+            break
+    batches = token_batches(steps + warmup, 1, seq, spec.vocab, 11)
+    for i in range(warmup):
+        one_step(*batches[i], 2 + i)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        one_step(*batches[warmup + i], 2 + warmup + i)
+    elapsed = time.perf_counter() - t0
+    sample = f"nanolab-124M f32 strict-order step (fwd + fused CE + bwd + AdamW), B=1 T={seq}, {steps} steps after {warmup} warm-up, {cores} OpenMP threads"
+    return steps * seq / elapsed, cores, sample, 1000.0 * elapsed / steps
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    rate, cores, sample, ms = cpu_step_rate(150.0, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "nanolab_gpt_124m_train_tokens_per_s", "value": rate, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "nanolab GPT-124M train step (ModelSpec::nanolab_124m, hidden 2048): 12 layers, d 768, 12x64 heads, vocab 50304, seq 1024, "
+                        "micro-batch 32 per GPU, bf16 autocast, AdamW(lr 3e-4, betas 0.9/0.95, eps 1e-8, wd 0.1) on every tensor",
+            "global_batch": BATCH * n_gpus, "seq_len": SEQ, "parallelism": f"dp{n_gpus}",
+            "l2": "inputs larger than L2: one step streams about 14 GB of activations, weights and optimizer state"}
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+    from ojas_b200 import CudaBackend, ModelSpec, TrainConfig, Trainer
+    from ojas_b200.dp import BucketAllReduce
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    be = CudaBackend(local_rank, 150 << 30)
+    spec = ModelSpec(**spec_kwargs())
+    cfg = TrainConfig(autocast_bf16=True, optimizer="adamw", adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=0.0, loss_seed=1.0 / world)
+    tr = Trainer(be, spec, cfg, BATCH, SEQ)
+    tr.set_params(init_weights(tr.params, 0))  # identical weights on every rank
+    reducer = BucketAllReduce(be, tr, torch.device("cuda", local_rank)) if world > 1 else None
+
+    n_batches = 4
+    batches = token_batches(n_batches, BATCH, SEQ, spec.vocab, 1 + rank)  # a distinct id stream per rank
+    dev = [(be.upload(x), be.upload(y)) for x, y in batches]
+    pinned = []
+    for x, y in batches:
+        px, py = torch.empty(x.size, dtype=torch.int32).pin_memory(), torch.empty(y.size, dtype=torch.int32).pin_memory()
+        px.numpy().view(np.uint32)[:] = x.ravel(); py.numpy().view(np.uint32)[:] = y.ravel()
+        pinned.append((px, py))
+    main = torch.cuda.ExternalStream(be.stream(), device=torch.device("cuda", local_rank))
+
+    def step_resident(i):
+        ids, tg = dev[i % n_batches]
+        if reducer is None:
+            return tr.step_device(ids, tg)
+        tr.gradients_device(ids, tg)
+        reducer.exchange()
+        tr.apply(read_norm=False)
+        return tr.finish()
+
+    def step_e2e(i):
+        px, py = pinned[i % n_batches]
+        if reducer is None:
+            return tr.step_host_ptrs(px.data_ptr(), py.data_ptr())
+        ids, tg = dev[i % n_batches]
+        be.upload_ptr(ids, px.data_ptr(), px.numel() * 4); be.upload_ptr(tg, py.data_ptr(), py.numel() * 4)
+        tr.gradients_device(ids, tg)
+        reducer.exchange()
+        tr.apply(read_norm=False)
+        return tr.finish()
+
+    def timed(step_fn, steps):
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(main)
+        rep = None
+        for i in range(steps):
+            rep = step_fn(i)
+        stop.record(main)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=f"cuda:{local_rank}")
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), rep
+
+    for i in range(max(args.warmup, 3)):
+        step_resident(i)
+    be.profile_gemm(True)
+    launches0 = be.kernel_launches()
+    with ClockSampler(local_rank) as clocks:
+        ms, rep = timed(step_resident, args.steps)
+    launches = be.kernel_launches() - launches0
+    gemm_ms, gemm_flops, gemm_launches = be.profile_gemm_read()
+    be.profile_gemm(False)
+    e2e_ms = None
+    if not args.no_e2e:
+        step_e2e(0)
+        e2e_ms, _ = timed(step_e2e, args.steps)
+
+    tokens = BATCH * SEQ * world
+    value = tokens * args.steps / (ms / 1000.0)
+    pk, pk_kind = peaks()
+    fpt = spec.flops_per_token(SEQ)
+    line = {
+        "metric": "nanolab_gpt_124m_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(world),
+        "mfu": value * fpt / (world * pk["bf16_tflops"] * 1e12), "mfu_vs_sustained": value * fpt / (world * pk["bf16_tflops_sustained"] * 1e12),
+        "flops_per_token": fpt, "final_loss": rep.loss if rep else None,
+        "e2e": {"value": tokens * args.steps / (e2e_ms / 1000.0) if e2e_ms else None, "unit": "tokens/s", "h2d_bytes_per_step": 2 * BATCH * SEQ * 4,
+                "d2h_bytes_per_step": 12 + 8},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+    }
+    if gemm_ms > 0:
+        achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
+        line["roofline"] = {"kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM, all launches of the timed steps)", "bound": "tensor", "achieved": achieved,
+                            "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops_sustained"],
+                            "peak_source": f"bf16_tflops_sustained, of {pk_kind}", "launches": int(gemm_launches), "share_of_step_time": gemm_ms / ms,
+                            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rate, cores, sample, _ = cpu_step_rate(20.0, 1, 0)
+        line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    tr.close()
+    be.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the bounded CPU sample (the default run reports it)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (used for profiler captures)")
+    args = ap.parse_args()
+    rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

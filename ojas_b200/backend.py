@@ -211,6 +211,10 @@ class CudaBackend:
             return self.to_bf16(t)
         return t
 
+    def upload_ptr(self, t: Tensor, host_ptr: int, nbytes: int):
+        """Copy from a caller-owned (for example pinned) host buffer given by address into an existing tensor."""
+        _check(lib.ojc_upload(self._handle, C.c_void_p(t.ptr), C.c_void_p(host_ptr), C.c_uint64(nbytes)))
+
     def download(self, t: Tensor) -> np.ndarray:
         assert t.strides == _contig_strides(t.shape), "download wants a contiguous tensor"
         if t.dtype == DType.BF16:

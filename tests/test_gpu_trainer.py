@@ -141,6 +141,9 @@ def test_config1_one_full_adamw_step_f32(be, c1):
     assert abs(rep.loss - oloss) / oloss <= LOSS_TOL and rep.step == 1 and rep.tokens == 8 * 256
     assert abs(rep.grad_norm - float(orc.grad_norm(ograds))) <= 1e-5 * float(orc.grad_norm(ograds))
     for i, p in enumerate(tr.params):
+        if not np.any(ostepped[i]):
+            assert not np.any(tr.get_param(i)), p.name
+            continue
         assert normwise(tr.get_param(i), ostepped[i]) <= 1e-4, p.name  # TRACE_PARAM_NORMWISE_REL_TOL, ojas-oracle/src/parity.rs:41-43
     tr.close()
 
