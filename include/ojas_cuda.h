@@ -104,6 +104,15 @@ ojc_status ojc_linear_backward(ojc_backend* be, const ojc_tensor* x, const ojc_t
 ojc_status ojc_linear_backward_input(ojc_backend* be, const ojc_tensor* weight, const ojc_tensor* grad_y, ojc_tensor* grad_x); /* :1648 */
 ojc_status ojc_rms_norm_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, float eps, ojc_tensor* y);   /* :1658 */
 ojc_status ojc_rms_norm_backward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, const ojc_tensor* grad_y, float eps, ojc_tensor* grad_x, ojc_tensor* grad_w); /* :1666 */
+/* No counterpart in the reference. rms_norm_backward for hosts that must not let this library allocate: ojas charges every
+ * device byte to one Budget before it is allocated (ojas-core/src/budget.rs), and a host that has handed all device memory
+ * to that budget (or runs inside a region where cudaMalloc is forbidden) cannot let the regular entry point grow its
+ * workspace. This variant takes raw F32 device pointers and a cudaStream_t, calls no allocator, and keeps the per-block
+ * partial sums of grad_w in a fixed 2 MiB device array inside the library (held by every GPU that loads it). Limits:
+ * dim <= 2048, F32 contiguous operands; larger row counts run on fewer, longer blocks. The first call on a device looks
+ * up the array's address (make that call before any stream capture). All calls on a device share the array: calls that
+ * overlap on the GPU (different streams) race; calls on one stream are safe. */
+ojc_status ojc_rms_norm_backward_noalloc(void* cuda_stream, const float* x, const float* weight, const float* grad_y, int64_t rows, int64_t dim, float eps, float* grad_x, float* grad_w);
 ojc_status ojc_rope_half_split_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* cos_t, const ojc_tensor* sin_t, ojc_tensor* y);  /* :1674 x [B,T,H,dh], tables [T,dh] */
 ojc_status ojc_rope_half_split_backward(ojc_backend* be, const ojc_tensor* grad_y, const ojc_tensor* cos_t, const ojc_tensor* sin_t, ojc_tensor* grad_x); /* :1681 */
 ojc_status ojc_rms_qk_norm_forward(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* q_weight, const ojc_tensor* k_weight, float eps, ojc_tensor* q_out, ojc_tensor* k_out); /* :1688 per-head norm over the last axis */

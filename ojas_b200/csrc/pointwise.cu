@@ -821,3 +821,49 @@ ojc_status ojc_argmax_rows(ojc_backend* be, const ojc_tensor* x, ojc_tensor* out
 }
 
 }  // extern "C"
+
+// ======================================================================== RMSNorm backward without any allocation
+// Workspace for ojc_rms_norm_backward_noalloc: the per-block partial column sums of dW live in this fixed array instead
+// of the backend's growable workspace. Every GPU that loads the library holds these 2 MiB until the process exits.
+constexpr int64_t NOALLOC_PART_FLOATS = 1 << 19;
+static __device__ __align__(256) float g_rms_noalloc_part[NOALLOC_PART_FLOATS];
+// In host code the array's name is only a stand-in for the symbol: the device address is looked up once per device.
+static float* g_rms_noalloc_ptr[64] = {nullptr};
+
+extern "C" ojc_status ojc_rms_norm_backward_noalloc(void* cuda_stream, const float* x, const float* weight, const float* grad_y, int64_t rows, int64_t dim,
+                                                    float eps, float* grad_x, float* grad_w) {
+  const char* op = "rms_norm_backward_noalloc";
+  if (!x || !weight || !grad_y || !grad_x || !grad_w) return ojc_fail(OJC_ERR_PLACEMENT, op, "every operand must be a device pointer");
+  if (rows <= 0 || dim <= 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
+  if (dim > 2048) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "row width above 2048 is not supported");
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) { cudaGetLastError(); return ojc_fail(OJC_ERR_NO_DEVICE, op, "no current CUDA device"); }
+  if (!g_rms_noalloc_ptr[device]) {
+    // first call on this device: resolve the symbol with this device current (do this before any stream capture)
+    float* p = nullptr;
+    cudaError_t err = cudaGetSymbolAddress((void**)&p, g_rms_noalloc_part);
+    if (err != cudaSuccess || !p) { cudaGetLastError(); return ojc_fail(OJC_ERR_BACKEND, op, std::string("cudaGetSymbolAddress failed: ") + cudaGetErrorString(err)); }
+    g_rms_noalloc_ptr[device] = p;
+  }
+  float* part = g_rms_noalloc_ptr[device];
+  const int warps = dim > 512 ? 4 : 8;
+  int64_t blocks = (rows + warps - 1) / warps;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) { cudaGetLastError(); sms = 148; }
+  if (blocks > (int64_t)sms * 4) blocks = (int64_t)sms * 4;
+  if (blocks * dim > NOALLOC_PART_FLOATS) blocks = NOALLOC_PART_FLOATS / dim;  // fewer, longer blocks rather than a larger workspace
+  if (blocks < 1 || rows > (int64_t)INT32_MAX * warps) return ojc_fail(OJC_ERR_CAPACITY_EXCEEDED, op, "the problem does not fit the fixed 2 MiB workspace");
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  ojc_status st = dispatch_iters(op, (int)dim, [&](auto it) {
+    constexpr int IT = decltype(it)::value;
+    // every launched block overwrites its own row of the workspace and the finish kernel reads exactly those rows,
+    // so nothing left by an earlier call is ever read and nothing needs clearing
+    rms_backward_kernel<IT, float, float, float><<<(unsigned)blocks, warps * 32, warps * (int)dim * 4, stream>>>(x, weight, grad_y, grad_x, part, rows, (int)dim, eps, 0);
+    return OJC_OK;
+  });
+  if (st != OJC_OK) return st;
+  column_sum_finish_kernel<<<(unsigned)((dim + 127) / 128), 128, 0, stream>>>(part, grad_w, (int)blocks, (int)dim, 0);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return ojc_fail(OJC_ERR_BACKEND, op, std::string(cudaGetErrorName(err)) + ": " + cudaGetErrorString(err));
+  return OJC_OK;
+}
