@@ -2,14 +2,15 @@
 //
 //   C[m,n] = alpha * A[m,k] . B[k,n]  (+ residual)  (+ C)
 //
-// A persistent kernel, one CTA per SM, six warps with fixed roles:
+// A persistent kernel, one CTA per SM, ten warps with fixed roles:
 //   warp 0   TMA producer: cp.async.bulk.tensor loads of A and B tiles (128-byte
 //            swizzle, no cluster multicast) into a 4-stage shared-memory ring
 //   warp 1   allocates tensor memory and issues tcgen05.mma (one thread);
 //            accumulators live in TMEM, double-buffered (2 x 256 columns) so
 //            the epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM
-//            lanes), scale / add residual / accumulate, store f32 or bf16
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM
+//            lanes and half of the columns), scale / add residual / accumulate,
+//            store f32 (through padded staging rows, coalesced) or bf16
 // Tile 128 x 256 x 64; either operand may be K-major or MN-major in memory, so
 // x.W^T, g.W and g^T.x all run on the same kernel without transposed copies.
 // When the output has too few tiles to fill the GPU the reduction axis is
@@ -29,8 +30,15 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2, B_TILE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr int NUM_THREADS = 192;
+constexpr int STAGE_LD = 20;                      // floats per staged epilogue row (16 + 4 of padding)
+constexpr int EPI_STAGE_BYTES = 8 * 32 * STAGE_LD * 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
+#ifndef OJC_DIRECT_BF16
+#define OJC_DIRECT_BF16 1
+#endif
+constexpr int EPI_WARPS = 8;                     // two warps per TMEM lane quarter, each draining half of the columns
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
+static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 struct TcArgs {
@@ -41,6 +49,7 @@ struct TcArgs {
   int splits, kblocks_per_split;
   float* partial;           // [splits][m][n] when splits > 1
   uint32_t* fault;
+  int epi_warps;            // 4: bf16 rows stored directly by one warp per lane quarter; 8: staged f32 path, two warps per quarter
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -120,6 +129,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bar_base - raw) + 8 * (2 * STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stage_all = reinterpret_cast<float*>(smem_raw + (bar_base - raw) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (args.m + BM - 1) / BM, tiles_n = (args.n + BN - 1) / BN;
@@ -128,7 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), args.epi_warps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -195,9 +205,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         umma_commit(tfull_bar(acc));      // accumulator complete
       }
     }
-  } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+  } else if (warp < 2 + args.epi_warps) {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;         // TMEM lanes [32 * quarter, +32) are this warp's
+    float* stage = stage_all + (warp - 2) * 32 * STAGE_LD;
+    const int col_begin = args.epi_warps == 4 ? 0 : ((warp - 2) >> 2) * (BN / 2), col_end = args.epi_warps == 4 ? BN : col_begin + BN / 2;
     uint32_t local = 0;
     for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x, ++local) {
       const int split = u % args.splits, tile = u / args.splits;
@@ -205,51 +217,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int acc = local & 1;
       if (!mbar_wait(tfull_bar(acc), (local >> 1) & 1, args.fault, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = tm * BM + quarter * 32 + lane;
-      const bool row_ok = row < args.m;
+      const int row_base = tm * BM + quarter * 32;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col0 = tn * BN + c0;
-        if (!row_ok || col0 >= args.n) continue;
-        if (args.splits > 1) {
-          float* dst = args.partial + ((int64_t)split * args.m + row) * args.n + col0;
+        if (OJC_DIRECT_BF16 && args.c_bf16 && args.splits == 1 && !args.residual) {
+          // bf16 output: each thread writes 64 contiguous bytes of its own row (two full 32-byte sectors)
+          const int row = row_base + lane;
+          if (row < args.m && col0 < args.n) {
+            bf16* dst = reinterpret_cast<bf16*>(args.c) + (int64_t)row * args.ldc + col0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            if (col0 + j < args.n) *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j >= args.n) break;
+              uint4 t;
+              t.x = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 1])) << 16);
+              t.y = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 2])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 3])) << 16);
+              t.z = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 4])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 5])) << 16);
+              t.w = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 6])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 7])) << 16);
+              *reinterpret_cast<uint4*>(dst + j) = t;
+            }
+          }
           continue;
         }
-        const int64_t o = (int64_t)row * args.ldc + col0;
-        float v[32];
+        // f32 output: each thread holds one accumulator row; pass the block, 16 columns at a time, through this warp's
+        // padded staging rows so the global accesses are row-contiguous across lanes (4 lanes x 16 bytes per row).
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = args.alpha * __uint_as_float(r[j]);
-        if (args.residual) {
+        for (int half = 0; half < 2; ++half) {
+          if (half) __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            if (col0 + j < args.n) { float4 t = *reinterpret_cast<const float4*>(args.residual + o + j); v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w; }
-        }
-        if (!args.c_bf16) {
-          float* dst = reinterpret_cast<float*>(args.c) + o;
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<float4*>(stage + lane * STAGE_LD + j) = make_float4(__uint_as_float(r[half * 16 + j]), __uint_as_float(r[half * 16 + j + 1]),
+                                                                                   __uint_as_float(r[half * 16 + j + 2]), __uint_as_float(r[half * 16 + j + 3]));
+          __syncwarp();
+          const int cc = (lane & 3) * 4, gcol = col0 + half * 16 + cc;
+          if (gcol >= args.n) continue;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            if (col0 + j >= args.n) break;
-            if (args.accumulate) { float4 t = *reinterpret_cast<const float4*>(dst + j); v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w; }
-            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          }
-        } else {
-          bf16* dst = reinterpret_cast<bf16*>(args.c) + o;
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + j >= args.n) break;
-            uint4 t;
-            t.x = (uint32_t)f32_to_bf16_bits(v[j]) | ((uint32_t)f32_to_bf16_bits(v[j + 1]) << 16);
-            t.y = (uint32_t)f32_to_bf16_bits(v[j + 2]) | ((uint32_t)f32_to_bf16_bits(v[j + 3]) << 16);
-            t.z = (uint32_t)f32_to_bf16_bits(v[j + 4]) | ((uint32_t)f32_to_bf16_bits(v[j + 5]) << 16);
-            t.w = (uint32_t)f32_to_bf16_bits(v[j + 6]) | ((uint32_t)f32_to_bf16_bits(v[j + 7]) << 16);
-            *reinterpret_cast<uint4*>(dst + j) = t;
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + (lane >> 2), grow = row_base + rr;
+            if (grow >= args.m) continue;
+            float4 v = *reinterpret_cast<const float4*>(stage + rr * STAGE_LD + cc);
+            if (args.splits > 1) {
+              *reinterpret_cast<float4*>(args.partial + ((int64_t)split * args.m + grow) * args.n + gcol) = v;
+              continue;
+            }
+            const int64_t o = (int64_t)grow * args.ldc + gcol;
+            v.x *= args.alpha; v.y *= args.alpha; v.z *= args.alpha; v.w *= args.alpha;
+            if (args.residual) { const float4 t = *reinterpret_cast<const float4*>(args.residual + o); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
+            if (!args.c_bf16) {
+              float* dst = reinterpret_cast<float*>(args.c) + o;
+              if (args.accumulate) { const float4 t = *reinterpret_cast<const float4*>(dst); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
+              *reinterpret_cast<float4*>(dst) = v;
+            } else {
+              uint2 t;
+              t.x = (uint32_t)f32_to_bf16_bits(v.x) | ((uint32_t)f32_to_bf16_bits(v.y) << 16);
+              t.y = (uint32_t)f32_to_bf16_bits(v.z) | ((uint32_t)f32_to_bf16_bits(v.w) << 16);
+              *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.c) + o) = t;
+            }
           }
         }
       }
@@ -360,6 +387,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   args.a_mn_major = amn; args.b_mn_major = bmn;
   args.alpha = alpha; args.accumulate = accumulate ? 1 : 0; args.residual = residual;
   args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev;
+  args.epi_warps = (OJC_DIRECT_BF16 && args.c_bf16 && splits == 1 && !residual) ? 4 : EPI_WARPS;
   if (splits > 1) {
     void* ws = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)splits * m * n * 4, &ws));
