@@ -52,12 +52,15 @@ __global__ void ce_rows_kernel(const TL* __restrict__ logits, int64_t ld, const 
     if (grad) for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) stf(grad, row * ldg + c, 0.0f);
     return;
   }
-  float mx = -INFINITY;
-  for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) mx = fmaxf(mx, ldf(z, c));
-  mx = block_max(mx, red);
-  float sum = 0.0f;
-  for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) sum += expf(ldf(z, c) - mx);
-  sum = block_sum(sum, red);
+  // one pass for both statistics: each thread keeps a running (max, sum) over its columns, then the block combines them
+  float tm = -INFINITY, ts = 0.0f;
+  for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) {
+    const float v = ldf(z, c);
+    if (v > tm) { ts = ts * expf(tm - v) + 1.0f; tm = v; }
+    else ts += expf(v - tm);
+  }
+  const float mx = block_max(tm, red);
+  float sum = block_sum(tm == -INFINITY ? 0.0f : ts * expf(tm - mx), red);
   const float picked = ldf(z, target);
   if (!(isfinite(mx) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
   float other = 0.0f;

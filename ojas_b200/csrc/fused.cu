@@ -1,0 +1,288 @@
+// Fused forms the step driver uses under bf16 autocast, each equal to a short chain of the per-op entry points:
+//   qk_norm_rope_forward / backward   rms_norm (per head, weight [dh]) followed by rope_half_split, one pass over q or k
+//   gate_apply_forward / backward     the pointwise half of per_head_sigmoid_gate once the [rows, H] logits come from a GEMM
+// 128-bit accesses throughout; per-column weight-gradient sums are two-stage with a fixed order (no float atomics).
+#include "common.cuh"
+#include "ops.cuh"
+
+namespace {
+
+__device__ __forceinline__ void load8(const bf16* p, float v[8]) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+__device__ __forceinline__ void store8(bf16* p, const float v[8]) {
+  uint4 t;
+  t.x = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
+  t.y = (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+  t.z = (uint32_t)f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
+  t.w = (uint32_t)f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
+  *reinterpret_cast<uint4*>(p) = t;
+}
+__device__ __forceinline__ void load8f(const float* p, float v[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <int TPR> __device__ __forceinline__ float row_sum(float v) {
+#pragma unroll
+  for (int o = TPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// y = rope(rms_norm(x) * w). x, y: [tokens, heads, dh] with a token stride (so a column slice of a wider buffer works);
+// TPR = dh / 16 threads per row, each owning columns [8 part, 8 part + 8) of both halves, i.e. whole rotation pairs.
+template <int TPR>
+__global__ void qk_norm_rope_forward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
+                                            const float* __restrict__ sin_t, bf16* __restrict__ y, int64_t ys, int64_t rows, int heads, int time, float eps) {
+  constexpr int DH = 16 * TPR, HALF = 8 * TPR;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int part = (int)(gid % TPR);
+  const int64_t row_raw = gid / TPR;
+  const bool live = row_raw < rows;
+  const int64_t row = live ? row_raw : rows - 1;
+  const int64_t token = row / heads;
+  const int head = (int)(row % heads), t = (int)(token % time), c0 = part * 8;
+  const bf16* src = x + token * xs + (int64_t)head * DH;
+  float a[8], b[8], wa[8], wb[8], c1[8], c2[8], s1[8], s2[8];
+  load8(src + c0, a); load8(src + HALF + c0, b);
+  load8f(w + c0, wa); load8f(w + HALF + c0, wb);
+  load8f(cos_t + (int64_t)t * DH + c0, c1); load8f(cos_t + (int64_t)t * DH + HALF + c0, c2);
+  load8f(sin_t + (int64_t)t * DH + c0, s1); load8f(sin_t + (int64_t)t * DH + HALF + c0, s2);
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+  ss = row_sum<TPR>(ss);
+  const float rstd = 1.0f / sqrtf(ss / (float)DH + eps);
+  float y1[8], y2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float an = a[i] * rstd * wa[i], bn = b[i] * rstd * wb[i];
+    y1[i] = an * c1[i] - bn * s1[i];
+    y2[i] = bn * c2[i] + an * s2[i];
+  }
+  if (live) {
+    bf16* dst = y + token * ys + (int64_t)head * DH;
+    store8(dst + c0, y1); store8(dst + HALF + c0, y2);
+  }
+}
+
+// Backward of the above from the saved pre-norm x: rope backward, then RMSNorm backward; dW partials per block.
+template <int TPR>
+__global__ void qk_norm_rope_backward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
+                                             const float* __restrict__ sin_t, const bf16* __restrict__ gy, int64_t gys, bf16* __restrict__ gx, int64_t gxs,
+                                             float* __restrict__ part_out, int64_t rows, int heads, int time, float eps) {
+  constexpr int DH = 16 * TPR, HALF = 8 * TPR;
+  extern __shared__ float red[];  // [threads][16]
+  const int part = threadIdx.x % TPR;
+  const int c0 = part * 8;
+  float wa[8], wb[8], dwa[8], dwb[8];
+  load8f(w + c0, wa); load8f(w + HALF + c0, wb);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { dwa[i] = 0.0f; dwb[i] = 0.0f; }
+  const int64_t rows_per_pass = (int64_t)gridDim.x * (blockDim.x / TPR);
+  const int64_t passes = (rows + rows_per_pass - 1) / rows_per_pass;
+  for (int64_t pass = 0; pass < passes; ++pass) {
+    const int64_t row_raw = pass * rows_per_pass + (int64_t)blockIdx.x * (blockDim.x / TPR) + threadIdx.x / TPR;
+    const bool live = row_raw < rows;
+    const int64_t row = live ? row_raw : rows - 1;
+    const int64_t token = row / heads;
+    const int head = (int)(row % heads), t = (int)(token % time);
+    float a[8], b[8], ga[8], gb[8], c1[8], c2[8], s1[8], s2[8];
+    load8(x + token * xs + (int64_t)head * DH + c0, a); load8(x + token * xs + (int64_t)head * DH + HALF + c0, b);
+    load8(gy + token * gys + (int64_t)head * DH + c0, ga); load8(gy + token * gys + (int64_t)head * DH + HALF + c0, gb);
+    load8f(cos_t + (int64_t)t * DH + c0, c1); load8f(cos_t + (int64_t)t * DH + HALF + c0, c2);
+    load8f(sin_t + (int64_t)t * DH + c0, s1); load8f(sin_t + (int64_t)t * DH + HALF + c0, s2);
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    ss = row_sum<TPR>(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)DH + eps);
+    float da[8], db[8], dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      da[i] = ga[i] * c1[i] + gb[i] * s2[i];    // d/d(an): rope backward (ojas-cpu/src/norm.rs:303-306)
+      db[i] = -ga[i] * s1[i] + gb[i] * c2[i];
+      a[i] *= rstd; b[i] *= rstd;               // x hat
+      dot += (da[i] * wa[i]) * a[i] + (db[i] * wb[i]) * b[i];
+    }
+    dot = row_sum<TPR>(dot);
+    const float mean = dot / (float)DH;
+    float oa[8], ob[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      oa[i] = (da[i] * wa[i] - a[i] * mean) * rstd;
+      ob[i] = (db[i] * wb[i] - b[i] * mean) * rstd;
+      if (live) { dwa[i] += da[i] * a[i]; dwb[i] += db[i] * b[i]; }
+    }
+    if (live) {
+      bf16* dst = gx + token * gxs + (int64_t)head * DH;
+      store8(dst + c0, oa); store8(dst + HALF + c0, ob);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { red[threadIdx.x * 16 + i] = dwa[i]; red[threadIdx.x * 16 + 8 + i] = dwb[i]; }
+  __syncthreads();
+  if (threadIdx.x < DH) {
+    const int c = threadIdx.x, p = (c % HALF) / 8, slot = (c / HALF) * 8 + (c % 8);
+    float acc = 0.0f;
+    for (int th = p; th < (int)blockDim.x; th += TPR) acc += red[th * 16 + slot];
+    part_out[(int64_t)blockIdx.x * DH + c] = acc;
+  }
+}
+
+__global__ void fused_column_sum_kernel(const float* __restrict__ part, float* __restrict__ out, int nparts, int cols) {
+  __shared__ float red[8][33];
+  const int cl = threadIdx.x & 31, g = threadIdx.x >> 5, c = blockIdx.x * 32 + cl;
+  float acc = 0.0f;
+  if (c < cols) for (int p = g; p < nparts; p += 8) acc += part[(int64_t)p * cols + c];
+  red[g][cl] = acc;
+  __syncthreads();
+  if (g == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cl];
+    out[c] = t;
+  }
+}
+
+// out = attn * sigmoid(z + b) per head; z: [rows, zld] logits (zld >= heads), scales (optional) keeps the sigmoid.
+// One thread per 8 contiguous values of one (row, head).
+__global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, const float* __restrict__ bias, const bf16* __restrict__ attn, bf16* __restrict__ out,
+                                          float* __restrict__ scales, int64_t rows, int heads, int dh) {
+  const int per = dh / 8;
+  const int64_t total = rows * heads * per;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < total; i += stride) {
+    const int64_t rh = i / per;
+    const int64_t row = rh / heads;
+    const int h = (int)(rh % heads);
+    const float g = sigmoidf_(__bfloat162float(z[row * zld + h]) + bias[h]);
+    if (scales && (i % per) == 0) scales[rh] = g;
+    float v[8];
+    load8(attn + i * 8, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= g;
+    store8(out + i * 8, v);
+  }
+}
+
+// dAttn = gOut * g; gz[row, h] = (sum_dh gOut * attn) * g (1 - g), written as bf16 [rows, zld] with zero padding columns
+// (the operand of the two gate GEMMs) and as f32 partial column sums for the bias gradient. One warp per row.
+__global__ void gate_apply_backward_kernel(const float* __restrict__ scales, const bf16* __restrict__ attn, const bf16* __restrict__ gout, bf16* __restrict__ gattn,
+                                           bf16* __restrict__ gz, int zld, float* __restrict__ part_out, int64_t rows, int heads, int dh) {
+  extern __shared__ float red[];  // [warps][heads]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int per = dh / 8;                 // 16-byte chunks per head
+  float* mine = red + warp * heads;
+  for (int h = lane; h < heads; h += 32) mine[h] = 0.0f;
+  __syncwarp();
+  for (int64_t row = (int64_t)blockIdx.x * nwarps + warp; row < rows; row += (int64_t)gridDim.x * nwarps) {
+    const int chunks = heads * per;
+    for (int c = lane; c < ((chunks + 31) / 32) * 32; c += 32) {
+      const bool ok = c < chunks;
+      const int h = ok ? c / per : 0;
+      float dot = 0.0f, g = 0.0f;
+      if (ok) {
+        g = scales[row * heads + h];
+        float a[8], go[8];
+        const int64_t off = (row * heads) * dh + (int64_t)c * 8;
+        load8(attn + off, a); load8(gout + off, go);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { dot += go[k] * a[k]; go[k] *= g; }
+        store8(gattn + off, go);
+      }
+      // the `per` lanes of one head are contiguous (per divides 32 for head_dim 64 / 128 / 256)
+      for (int o = per / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (ok && (c % per) == 0) {
+        const float zg = dot * g * (1.0f - g);
+        gz[row * zld + h] = __float2bfloat16_rn(zg);
+        mine[h] += zg;
+      }
+    }
+    for (int h = heads + lane; h < zld; h += 32) gz[row * zld + h] = __float2bfloat16_rn(0.0f);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    float acc = 0.0f;
+    for (int wi = 0; wi < nwarps; ++wi) acc += red[wi * heads + h];
+    part_out[(int64_t)blockIdx.x * heads + h] = acc;
+  }
+}
+
+template <class F> ojc_status dispatch_tpr(const char* op, int dh, F&& f) {
+  switch (dh) {
+    case 16: return f(std::integral_constant<int, 1>());
+    case 32: return f(std::integral_constant<int, 2>());
+    case 64: return f(std::integral_constant<int, 4>());
+    case 128: return f(std::integral_constant<int, 8>());
+    case 256: return f(std::integral_constant<int, 16>());
+    default: return ojc_fail(OJC_ERR_UNSUPPORTED_HEAD_DIM, op, "the fused norm + rope kernel wants head_dim in {16, 32, 64, 128, 256}");
+  }
+}
+
+}  // namespace
+
+bool qk_norm_rope_supported(int dh) { return dh == 16 || dh == 32 || dh == 64 || dh == 128 || dh == 256; }
+
+ojc_status qk_norm_rope_forward(ojc_backend* be, const bf16* x, int64_t xs, const float* w, const float* cos_t, const float* sin_t, bf16* y, int64_t ys,
+                                int64_t tokens, int heads, int dh, int time, float eps) {
+  const char* op = "qk_norm_rope_forward";
+  const int64_t rows = tokens * heads;
+  if (rows == 0) return OJC_OK;
+  return dispatch_tpr(op, dh, [&](auto tpr) {
+    constexpr int TPR = decltype(tpr)::value;
+    const int64_t threads = rows * TPR;
+    qk_norm_rope_forward_kernel<TPR><<<(unsigned)((threads + 255) / 256), 256, 0, be->stream>>>(x, xs, w, cos_t, sin_t, y, ys, rows, heads, time, eps);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  });
+}
+
+ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, const float* w, const float* cos_t, const float* sin_t, const bf16* gy, int64_t gys,
+                                 bf16* gx, int64_t gxs, float* gw, int64_t tokens, int heads, int dh, int time, float eps) {
+  const char* op = "qk_norm_rope_backward";
+  const int64_t rows = tokens * heads;
+  if (rows == 0) return OJC_OK;
+  return dispatch_tpr(op, dh, [&](auto tpr) {
+    constexpr int TPR = decltype(tpr)::value;
+    const int rows_per_block = 256 / TPR;
+    int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+    if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
+    void* part = nullptr;
+    OJC_TRY(ojc_scratch(be, (uint64_t)blocks * dh * 4, &part));
+    qk_norm_rope_backward_kernel<TPR><<<(unsigned)blocks, 256, 256 * 16 * 4, be->stream>>>(x, xs, w, cos_t, sin_t, gy, gys, gx, gxs, (float*)part, rows, heads, time, eps);
+    OJC_LAUNCHED(be, op);
+    fused_column_sum_kernel<<<(dh + 31) / 32, 256, 0, be->stream>>>((const float*)part, gw, (int)blocks, dh);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  });
+}
+
+ojc_status gate_apply_forward(ojc_backend* be, const bf16* z, int zld, const float* bias, const bf16* attn, bf16* out, float* scales, int64_t rows, int heads, int dh) {
+  const char* op = "per_head_sigmoid_gate_forward";
+  if (dh % 8 != 0) return ojc_fail(OJC_ERR_UNSUPPORTED_HEAD_DIM, op, "head_dim must be a multiple of 8");
+  const int64_t total = rows * heads * (dh / 8);
+  gate_apply_forward_kernel<<<elementwise_grid(be, total, 256), 256, 0, be->stream>>>(z, zld, bias, attn, out, scales, rows, heads, dh);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16* attn, const bf16* gout, bf16* gattn, bf16* gz, int zld, float* gbias, int64_t rows,
+                               int heads, int dh) {
+  const char* op = "per_head_sigmoid_gate_backward";
+  const int per = dh / 8;
+  if (dh % 8 != 0 || per > 32 || (per & (per - 1)) != 0) return ojc_fail(OJC_ERR_UNSUPPORTED_HEAD_DIM, op, "head_dim must be 8, 16, 32, 64, 128 or 256");
+  const int warps = 8;
+  int64_t blocks = (rows + warps - 1) / warps;
+  if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
+  void* part = nullptr;
+  OJC_TRY(ojc_scratch(be, (uint64_t)blocks * heads * 4, &part));
+  gate_apply_backward_kernel<<<(unsigned)blocks, warps * 32, warps * heads * 4, be->stream>>>(scales, attn, gout, gattn, gz, zld, (float*)part, rows, heads, dh);
+  OJC_LAUNCHED(be, op);
+  fused_column_sum_kernel<<<(heads + 31) / 32, 256, 0, be->stream>>>((const float*)part, gbias, (int)blocks, heads);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}

@@ -15,3 +15,13 @@ ojc_status gate_backward_impl(ojc_backend* be, const ojc_tensor* input, const oj
                               bool accumulate_w);
 ojc_status swiglu_forward_impl(ojc_backend* be, const void* a, const void* u, void* m, int32_t dt, int64_t n);
 ojc_status swiglu_backward_impl(ojc_backend* be, const void* a, const void* u, const void* gm, void* ga, void* gu, int32_t dt, int64_t n);
+
+// fused.cu (bf16 storage)
+bool qk_norm_rope_supported(int dh);
+ojc_status qk_norm_rope_forward(ojc_backend* be, const bf16* x, int64_t xs, const float* w, const float* cos_t, const float* sin_t, bf16* y, int64_t ys,
+                                int64_t tokens, int heads, int dh, int time, float eps);
+ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, const float* w, const float* cos_t, const float* sin_t, const bf16* gy, int64_t gys,
+                                 bf16* gx, int64_t gxs, float* gw, int64_t tokens, int heads, int dh, int time, float eps);
+ojc_status gate_apply_forward(ojc_backend* be, const bf16* z, int zld, const float* bias, const bf16* attn, bf16* out, float* scales, int64_t rows, int heads, int dh);
+ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16* attn, const bf16* gout, bf16* gattn, bf16* gz, int zld, float* gbias, int64_t rows,
+                               int heads, int dh);

@@ -209,12 +209,13 @@ __global__ void rms_backward_kernel(const TX* __restrict__ x, const float* __res
   for (int j = 0; j < ITERS; ++j) { int c = lane + 32 * j; wv[j] = c < dim ? w[c] : 0.0f; dw[j] = 0.0f; }
   const float inv_dim = 1.0f / (float)dim;
   for (; row < rows; row += rstride) {
-    float xv[ITERS], gv[ITERS], ss = 0.0f;
+    float xv[ITERS], gv[ITERS], old[ITERS], ss = 0.0f;
 #pragma unroll
     for (int j = 0; j < ITERS; ++j) {
       int c = lane + 32 * j;
       xv[j] = c < dim ? ldf(x, row * dim + c) : 0.0f;
       gv[j] = c < dim ? ldf(gy, row * dim + c) : 0.0f;
+      old[j] = (gx_accumulate && c < dim) ? ldf(gx, row * dim + c) : 0.0f;  // issued with the other loads, not behind the stores
       ss += xv[j] * xv[j];
     }
     ss = warp_sum(ss);
@@ -229,11 +230,7 @@ __global__ void rms_backward_kernel(const TX* __restrict__ x, const float* __res
       int c = lane + 32 * j;
       float xhat = xv[j] * rstd;
       dw[j] += gv[j] * xhat;
-      if (c < dim) {
-        float dx = (gv[j] * wv[j] - xhat * mean) * rstd;
-        if (gx_accumulate) dx += ldf(gx, row * dim + c);
-        stf(gx, row * dim + c, dx);
-      }
+      if (c < dim) stf(gx, row * dim + c, (gv[j] * wv[j] - xhat * mean) * rstd + old[j]);
     }
   }
 #pragma unroll
@@ -246,12 +243,22 @@ __global__ void rms_backward_kernel(const TX* __restrict__ x, const float* __res
   }
 }
 
+// out[c] (+)= sum over parts of part[p, c]. Block = 32 columns x 8 part groups; group g adds parts g, g+8, ... in order,
+// then the eight group sums are added in group order: a fixed order whatever the grid.
 __global__ void column_sum_finish_kernel(const float* __restrict__ part, float* __restrict__ out, int nparts, int cols, int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float red[8][33];
+  const int cl = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
   float acc = 0.0f;
-  for (int p = 0; p < nparts; ++p) acc += part[(int64_t)p * cols + c];
-  out[c] = accumulate ? out[c] + acc : acc;
+  if (c < cols) for (int p = g; p < nparts; p += 8) acc += part[(int64_t)p * cols + c];
+  red[g][cl] = acc;
+  __syncthreads();
+  if (g == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cl];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 template <class F> static ojc_status dispatch_iters(const char* op, int dim, F&& f) {
@@ -314,7 +321,7 @@ ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_ten
       OJC_LAUNCHED(be, op);
       return OJC_OK;
     }); }));
-  column_sum_finish_kernel<<<(dim + 127) / 128, 128, 0, be->stream>>>((const float*)part, (float*)gw->data, (int)blocks, dim, accumulate_gw ? 1 : 0);
+  column_sum_finish_kernel<<<(dim + 31) / 32, 256, 0, be->stream>>>((const float*)part, (float*)gw->data, (int)blocks, dim, accumulate_gw ? 1 : 0);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }
@@ -862,7 +869,7 @@ extern "C" ojc_status ojc_rms_norm_backward_noalloc(void* cuda_stream, const flo
     return OJC_OK;
   });
   if (st != OJC_OK) return st;
-  column_sum_finish_kernel<<<(unsigned)((dim + 127) / 128), 128, 0, stream>>>(part, grad_w, (int)blocks, (int)dim, 0);
+  column_sum_finish_kernel<<<(unsigned)((dim + 31) / 32), 256, 0, stream>>>(part, grad_w, (int)blocks, (int)dim, 0);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return ojc_fail(OJC_ERR_BACKEND, op, std::string(cudaGetErrorName(err)) + ": " + cudaGetErrorString(err));
   return OJC_OK;

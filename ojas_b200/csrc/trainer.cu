@@ -64,6 +64,10 @@ struct ojc_trainer {
   void *hf = nullptr, *gx_b = nullptr, *g_m = nullptr, *g_a = nullptr, *g_u = nullptr, *g_yg = nullptr, *g_y = nullptr, *g_qr = nullptr, *g_kr = nullptr,
        *g_v = nullptr, *g_qn = nullptr, *g_kn = nullptr, *g_q = nullptr, *g_k = nullptr, *g_rawv = nullptr, *g_v0l = nullptr, *qn = nullptr, *kn = nullptr;
   uint32_t *ids = nullptr, *targets = nullptr;
+  bf16 *gate_z = nullptr, *gate_gz = nullptr;   // [N, gate_ld] logits / logit gradients of the gate GEMMs (bf16 tier)
+  float* gate_gw = nullptr;                     // [gate_ld, d] padded weight gradient
+  int gate_ld = 0;                              // 0: the gate runs on the per-row kernels
+  bool fused_qk = false;
   uint64_t step = 0;
   bool poisoned = false, grads_ready = false;
   struct Bucket { int64_t offset, floats; int first_param; cudaEvent_t ready; bool recorded; };
@@ -159,7 +163,10 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
     OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, qw, nullptr));
     OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_K)), A, a.k, A, N, d, kvw, nullptr));
     OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_V)), A, a.rawv, A, N, d, kvw, nullptr));
-    {
+    if (tr->fused_qk) {
+      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.q, qw, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (bf16*)a.qr, qw, N, (int)H, (int)dh, (int)T, eps));
+      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.k, kvw, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (bf16*)a.kr, kvw, N, (int)Hkv, (int)dh, (int)T, eps));
+    } else {
       ojc_tensor q = T2(a.q, A, N * H, dh), qn = T2(tr->qn, A, N * H, dh), qnw = T1(tr->W(tr->P(l, P_QN)), OJC_F32, dh);
       ojc_tensor k = T2(a.k, A, N * Hkv, dh), kn = T2(tr->kn, A, N * Hkv, dh), knw = T1(tr->W(tr->P(l, P_KN)), OJC_F32, dh);
       OJC_TRY(rms_forward_impl(be, &q, &qnw, eps, &qn));
@@ -178,7 +185,12 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
       lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
       OJC_TRY(ojc_causal_sdpa_forward(be, &q, &k, &v, s.window, &y, &lse));
     }
-    {
+    if (tr->gate_ld) {
+      // gate logits as a skinny GEMM over the weight rows [0, gate_ld) (rows past H are the next parameters' mirror
+      // values: their columns are never read), then the pointwise half
+      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_GW)), A, tr->gate_z, A, N, d, tr->gate_ld, nullptr));
+      OJC_TRY(gate_apply_forward(be, tr->gate_z, tr->gate_ld, tr->W(tr->P(l, P_GB)), (const bf16*)a.y, (bf16*)a.yg, a.scales, N, (int)H, (int)dh));
+    } else {
       ojc_tensor h2d = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
       ojc_tensor y = T2(a.y, A, N * H, dh), yg = T2(a.yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H);
       OJC_TRY(ojc_per_head_sigmoid_gate_forward(be, &h2d, &gw, &gb, &y, &yg, &sc));
@@ -268,7 +280,13 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     // x1 = x + o_proj(yg)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_O)), A, gxo, A, tr->g_yg, A, N, qw, d, false));
     OJC_TRY(linear_backward_weight_impl(be, a.yg, A, gxo, A, tr->G(tr->P(l, P_O)), N, qw, d, false));
-    {
+    if (tr->gate_ld) {
+      const int ld = tr->gate_ld;
+      OJC_TRY(gate_apply_backward(be, a.scales, (const bf16*)a.y, (const bf16*)tr->g_yg, (bf16*)tr->g_y, tr->gate_gz, ld, tr->G(tr->P(l, P_GB)), N, (int)H, (int)dh));
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_GW)), A, tr->gate_gz, A, tr->g_h, OJC_F32, N, d, ld, false));   // d/dh = gz . Wg (padding columns of gz are zero)
+      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->gate_gz, A, tr->gate_gw, N, d, ld, false));                          // [ld, d]; rows past H are zero
+      OJC_CUDA(be, cudaMemcpyAsync(tr->G(tr->P(l, P_GW)), tr->gate_gw, (size_t)H * d * 4, cudaMemcpyDeviceToDevice, be->stream), "per_head_sigmoid_gate_backward");
+    } else {
       ojc_tensor h = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
       ojc_tensor y = T2(a.y, A, N * H, dh), gyg = T2(tr->g_yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H), gh = T2(tr->g_h, OJC_F32, N, d), gy = T2(tr->g_y, A, N * H, dh);
       OJC_TRY(gate_backward_impl(be, &h, &gw, &gb, &y, &gyg, &sc, &gh, tr->G(tr->P(l, P_GW)), tr->G(tr->P(l, P_GB)), &gy, false));
@@ -295,7 +313,12 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       OJC_TRY(ojc_residual_add_forward(be, &acc, &gv, &grv));
       g_rawv = tr->g_rawv;
     }
-    {
+    if (tr->fused_qk) {
+      OJC_TRY(qk_norm_rope_backward(be, (const bf16*)a.k, kvw, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (const bf16*)tr->g_kr, kvw, (bf16*)tr->g_k, kvw,
+                                    tr->G(tr->P(l, P_KN)), N, (int)Hkv, (int)dh, (int)T, eps));
+      OJC_TRY(qk_norm_rope_backward(be, (const bf16*)a.q, qw, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (const bf16*)tr->g_qr, qw, (bf16*)tr->g_q, qw,
+                                    tr->G(tr->P(l, P_QN)), N, (int)H, (int)dh, (int)T, eps));
+    } else {
       ojc_tensor gkr = T4(tr->g_kr, A, B, T, Hkv, dh), gkn = T4(tr->g_kn, A, B, T, Hkv, dh), gqr = T4(tr->g_qr, A, B, T, H, dh), gqn = T4(tr->g_qn, A, B, T, H, dh);
       OJC_TRY(rope_impl(be, "rope_half_split_backward", &gkr, &cos_t, &sin_t, &gkn, 1));
       OJC_TRY(rope_impl(be, "rope_half_split_backward", &gqr, &cos_t, &sin_t, &gqn, 1));
@@ -375,6 +398,16 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
   TAKE(tr->g_yg, N * qw * es); TAKE(tr->g_y, N * qw * es); TAKE(tr->g_qr, N * qw * es); TAKE(tr->g_kr, N * kvw * es); TAKE(tr->g_v, N * kvw * es);
   TAKE(tr->g_qn, N * qw * es); TAKE(tr->g_kn, N * kvw * es); TAKE(tr->g_q, N * qw * es); TAKE(tr->g_k, N * kvw * es); TAKE(tr->g_rawv, N * kvw * es);
   TAKE(tr->g_v0l, N * kvw * es); TAKE(tr->qn, N * qw * es); TAKE(tr->kn, N * kvw * es);
+  if (tr->act_dt == OJC_BF16) {
+    tr->fused_qk = qk_norm_rope_supported((int)dh) && qw % 8 == 0 && kvw % 8 == 0;
+    const int64_t ld = (H + 7) & ~int64_t(7);
+    const Param& gwp = tr->P(0, P_GW);
+    const bool per_ok = dh % 8 == 0 && (dh / 8) <= 32 && (((dh / 8) & ((dh / 8) - 1)) == 0);
+    if (per_ok && d % 8 == 0 && tr->P(L - 1, P_GW).offset + ld * d <= tr->flat_n && gwp.n == H * d) {
+      tr->gate_ld = (int)ld;
+      TAKE(tr->gate_z, N * ld * 2); TAKE(tr->gate_gz, N * ld * 2); TAKE(tr->gate_gw, ld * d * 4);
+    }
+  }
   TAKE(tr->cos_t, tr->T * dh * 4); TAKE(tr->sin_t, tr->T * dh * 4); TAKE(tr->ids, N * 4); TAKE(tr->targets, N * 4);
 #undef TAKE
   std::vector<float> cos_h, sin_h;
