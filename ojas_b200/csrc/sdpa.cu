@@ -243,6 +243,7 @@ ojc_status ojc_causal_sdpa_forward(ojc_backend* be, const ojc_tensor* q, const o
   OJC_TRY(like(op, "out", out, q));
   OJC_TRY(check_tensor(op, "lse", lse));
   if (lse->dtype != OJC_F32 || numel(lse) != (int64_t)d.batch * d.heads * d.time) return ojc_fail(OJC_ERR_SHAPE, op, "lse must be F32 [B,H,T]");
+  if (sdpa_tcgen05_eligible(be, q, k, v, out, window, d)) return sdpa_forward_tcgen05(be, q, k, v, out, (float*)lse->data, d);
   if (sdpa_tc_eligible(q, k, v, out, d)) return sdpa_forward_tc(be, q, k, v, window, out, (float*)lse->data, d);
   return sdpa_forward_f32tier(be, q, k, v, window, out, (float*)lse->data, d);
 }

@@ -22,3 +22,6 @@ ojc_status sdpa_forward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tenso
                            const SdpaDims& d);
 ojc_status sdpa_backward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
                             const ojc_tensor* gout, int64_t window, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* dr);
+// tcgen05 / TMEM forward (head_dim 64, bf16, full causal)
+bool sdpa_tcgen05_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, int64_t window, const SdpaDims& d);
+ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, ojc_tensor* out, float* lse, const SdpaDims& d);
