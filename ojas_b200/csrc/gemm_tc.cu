@@ -39,7 +39,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*b
 constexpr int EPI_WARPS = 8;                     // two warps per TMEM lane quarter, each draining half of the columns
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 
 struct TcArgs {
   void* c; int c_bf16; int64_t ldc;
@@ -62,18 +62,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
 // Bounded wait: false (and the fault word raised) when the limit runs out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* fault, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = global_ns();
+  // the SM cycle counter bounds the wait (cheap to read; at most ~2 GHz, so the limit is at least two seconds)
+  const long long start = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int spin = 0; spin < 32; ++spin) if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (global_ns() - start > WAIT_LIMIT_NS) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
+    if (clock64() - start > WAIT_LIMIT_CYCLES) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
   }
 }
 

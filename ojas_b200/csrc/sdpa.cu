@@ -261,6 +261,10 @@ ojc_status ojc_causal_sdpa_backward(ojc_backend* be, const ojc_tensor* q, const 
   if (lse->dtype != OJC_F32 || numel(lse) != (int64_t)d.batch * d.heads * d.time) return ojc_fail(OJC_ERR_SHAPE, op, "lse must be F32 [B,H,T]");
   void* dr = nullptr;
   OJC_TRY(ojc_scratch(be, (uint64_t)d.batch * d.heads * d.time * 4, &dr));
+  if (sdpa_tcgen05_bwd_eligible(be, q, k, v, gout, gq, gk, gv, window, d) && out->dtype == OJC_BF16 && out->stride[3] == 1) {
+    OJC_TRY(sdpa_dr(be, out, gout, (float*)dr, d));
+    return sdpa_backward_tcgen05(be, q, k, v, (const float*)lse->data, gout, gq, gk, gv, d, (const float*)dr);
+  }
   if (sdpa_tc_eligible(q, k, v, out, d)) return sdpa_backward_tc(be, q, k, v, out, (const float*)lse->data, gout, window, gq, gk, gv, d, (float*)dr);
   return sdpa_backward_f32tier(be, q, k, v, out, (const float*)lse->data, gout, window, gq, gk, gv, d, (float*)dr);
 }

@@ -361,6 +361,13 @@ ojc_status sdpa_forward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tenso
   return OJC_OK;
 }
 
+ojc_status sdpa_dr(ojc_backend* be, const ojc_tensor* out, const ojc_tensor* gout, float* dr, const SdpaDims& d) {
+  dim3 grid((d.time * 32 + 255) / 256, d.batch * d.heads);
+  sdpa_dr_kernel<<<grid, 256, 0, be->stream>>>(view_of<const bf16>(out), view_of<const bf16>(gout), dr, d.heads, d.time, d.dim);
+  OJC_LAUNCHED(be, "causal_sdpa_backward");
+  return OJC_OK;
+}
+
 ojc_status sdpa_backward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
                             const ojc_tensor* gout, int64_t window, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* dr) {
   const char* op = "causal_sdpa_backward";

@@ -7,7 +7,7 @@
 
 namespace tc {
 
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t global_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
@@ -27,11 +27,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // false comes back; every role then leaves its loop and the CTA tears down normally.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* fault, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = global_ns();
+  // the SM cycle counter bounds the wait (cheap to read; at most ~2 GHz, so the limit is at least two seconds)
+  const long long start = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;   // try_wait parks the thread in hardware for a short while: no issue slots burnt
     if (*abort_flag) return false;
-    if (global_ns() - start > WAIT_LIMIT_NS) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
+    if (clock64() - start > WAIT_LIMIT_CYCLES) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
   }
 }
 
@@ -80,5 +81,9 @@ __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::be
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // generic-proxy shared-memory writes -> visible to the async proxy (TMA, tcgen05.mma operand reads)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+// two f32 -> packed bf16x2, round to nearest even (hardware convert; used where no NaN can occur)
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) { uint32_t r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
 
 }  // namespace tc
