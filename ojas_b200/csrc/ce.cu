@@ -83,6 +83,76 @@ __global__ void ce_rows_kernel(const TL* __restrict__ logits, int64_t ld, const 
   }
 }
 
+// The bf16-tier form of ce_rows_kernel for F32 logits and a BF16 gradient: 512 threads per row and two rows per SM (so the
+// rows in flight stay inside L2 between the statistics pass and the gradient pass), 128-bit loads, ex2.approx on
+// log2-scaled differences, one multiply per gradient element. Same row rules as above.
+__device__ __forceinline__ float ex2_fast(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { uint32_t r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+
+__global__ void __launch_bounds__(512, 2)
+ce_rows_fast_kernel(const float* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
+                    const uint32_t* __restrict__ valid, float* __restrict__ terms, bf16* __restrict__ grad, int64_t ldg, float seed, uint32_t* fault) {
+  __shared__ float red[32];
+  constexpr float L2E = 1.4426950408889634f;
+  const int64_t row = blockIdx.x;
+  const float* z = logits + row * ld;
+  bf16* g = grad ? grad + row * ldg : nullptr;
+  const uint32_t target = targets[row];
+  const int64_t v4 = vocab >> 2;            // whole float4 groups; the tail (vocab % 4) is handled by scalar code
+  if ((has_ignore && target == ignore) || target >= vocab) {
+    if (threadIdx.x == 0) terms[row] = 0.0f;
+    if (g) {
+      for (int64_t i = threadIdx.x; i < v4; i += blockDim.x) *reinterpret_cast<uint2*>(g + 4 * i) = make_uint2(0u, 0u);
+      for (int64_t c = 4 * v4 + threadIdx.x; c < vocab; c += blockDim.x) g[c] = __float2bfloat16_rn(0.0f);
+    }
+    return;
+  }
+  float tm = -INFINITY, ts = 0.0f;          // running maximum (log2 domain) and sum of 2^(v - tm)
+#pragma unroll 4
+  for (int64_t i = threadIdx.x; i < v4; i += blockDim.x) {
+    const float4 t = *reinterpret_cast<const float4*>(z + 4 * i);
+    const float a = t.x * L2E, b = t.y * L2E, c = t.z * L2E, d = t.w * L2E;
+    const float m4 = fmaxf(fmaxf(a, b), fmaxf(c, d));
+    if (m4 > tm) { ts *= ex2_fast(tm - m4); tm = m4; }
+    ts += ex2_fast(a - tm) + ex2_fast(b - tm) + ex2_fast(c - tm) + ex2_fast(d - tm);
+  }
+  for (int64_t c = 4 * v4 + threadIdx.x; c < vocab; c += blockDim.x) {
+    const float a = z[c] * L2E;
+    if (a > tm) { ts *= ex2_fast(tm - a); tm = a; }
+    ts += ex2_fast(a - tm);
+  }
+  const float mx2 = block_max(tm, red);
+  const float sum = block_sum(tm == -INFINITY ? 0.0f : ts * ex2_fast(tm - mx2), red);
+  const float picked = z[target];
+  const float mx = mx2 * (1.0f / L2E);
+  if (!(isfinite(mx2) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
+  float other = 0.0f;
+  bool collapsed = false;
+  if (picked * L2E == mx2 && sum == 1.0f) {
+    float o = 0.0f;
+    for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += ex2_fast(z[c] * L2E - mx2);
+    other = block_sum(o, red);
+    collapsed = other > 0.0f;
+  }
+  if (threadIdx.x == 0) terms[row] = collapsed ? log1pf(other) : (mx + logf(sum) - picked);
+  if (!g) return;
+  const float denom = (float)valid[0];
+  const float inv = collapsed ? 1.0f / (1.0f + other) : 1.0f / sum;
+  const float k = inv / denom * seed;
+#pragma unroll 4
+  for (int64_t i = threadIdx.x; i < v4; i += blockDim.x) {
+    const float4 t = *reinterpret_cast<const float4*>(z + 4 * i);
+    *reinterpret_cast<uint2*>(g + 4 * i) = make_uint2(pack_bf16x2(ex2_fast(fmaf(t.x, L2E, -mx2)) * k, ex2_fast(fmaf(t.y, L2E, -mx2)) * k),
+                                                      pack_bf16x2(ex2_fast(fmaf(t.z, L2E, -mx2)) * k, ex2_fast(fmaf(t.w, L2E, -mx2)) * k));
+  }
+  for (int64_t c = 4 * v4 + threadIdx.x; c < vocab; c += blockDim.x) g[c] = __float2bfloat16_rn(ex2_fast(fmaf(z[c], L2E, -mx2)) * k);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const float gt = collapsed ? -(other * inv) / denom : (ex2_fast(fmaf(picked, L2E, -mx2)) * inv) / denom - 1.0f / denom;
+    g[target] = __float2bfloat16_rn(gt * seed);
+  }
+}
+
 // loss = (sum of the row terms, added in a fixed tree order) / n_valid
 __global__ void ce_loss_finish_kernel(const float* __restrict__ terms, int64_t rows, const uint32_t* __restrict__ valid, float* __restrict__ loss, uint32_t* fault) {
   __shared__ double red[256];
@@ -110,6 +180,13 @@ ojc_status ce_rows(ojc_backend* be, const void* logits, int32_t l_dt, int64_t ld
                    uint32_t ignore, const uint32_t* valid_dev, float* terms, void* grad, int32_t g_dt, int64_t ldg, float seed) {
   const char* op = "cross_entropy_mean";
   if (rows == 0) return OJC_OK;
+  if (l_dt == OJC_F32 && grad && g_dt == OJC_BF16 && ld % 4 == 0 && ldg % 4 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(grad) & 7) == 0) {
+    ce_rows_fast_kernel<<<(unsigned)rows, 512, 0, be->stream>>>((const float*)logits, ld, targets, vocab, has_ignore, ignore, valid_dev, terms, (bf16*)grad, ldg, seed,
+                                                                be->fault_dev);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  }
   return dispatch_float(op, l_dt, [&](auto tl) { return dispatch_float(op, grad ? g_dt : OJC_F32, [&](auto tg) {
     using TL = decltype(tl); using TG = decltype(tg);
     ce_rows_kernel<TL, TG><<<(unsigned)rows, 256, 0, be->stream>>>((const TL*)logits, ld, targets, vocab, has_ignore, ignore, valid_dev, terms, (TG*)grad, ldg, seed, be->fault_dev);

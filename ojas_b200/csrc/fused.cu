@@ -7,6 +7,11 @@
 
 namespace {
 
+// hardware round-to-nearest-even conversions and approximate sigmoid: these kernels only run in the bf16 tier
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) { uint32_t r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+__device__ __forceinline__ float rbf(float v) { return __uint_as_float(pack2(0.0f, v) & 0xffff0000u); }
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
 __device__ __forceinline__ void load8(const bf16* p, float v[8]) {
   const uint4 t = *reinterpret_cast<const uint4*>(p);
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
@@ -14,12 +19,7 @@ __device__ __forceinline__ void load8(const bf16* p, float v[8]) {
   for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
 }
 __device__ __forceinline__ void store8(bf16* p, const float v[8]) {
-  uint4 t;
-  t.x = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
-  t.y = (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
-  t.z = (uint32_t)f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
-  t.w = (uint32_t)f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
-  *reinterpret_cast<uint4*>(p) = t;
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
 }
 __device__ __forceinline__ void load8f(const float* p, float v[8]) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -158,7 +158,7 @@ __global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, c
     const int64_t rh = i / per;
     const int64_t row = rh / heads;
     const int h = (int)(rh % heads);
-    const float g = sigmoidf_(__bfloat162float(z[row * zld + h]) + bias[h]);
+    const float g = sigmoid_fast(__bfloat162float(z[row * zld + h]) + bias[h]);
     if (scales && (i % per) == 0) scales[rh] = g;
     float v[8];
     load8(attn + i * 8, v);
@@ -209,6 +209,99 @@ __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, con
     float acc = 0.0f;
     for (int wi = 0; wi < nwarps; ++wi) acc += red[wi * heads + h];
     part_out[(int64_t)blockIdx.x * heads + h] = acc;
+  }
+}
+
+// ---- row-strided forms for column slices of a wider [rows, ld] buffer (the outputs of one GEMM over concatenated weights)
+// SwiGLU: a = au[:, 0:F], u = au[:, F:2F]; same arithmetic (and bf16 rounding of silu(a)) as swiglu_forward / backward.
+__global__ void swiglu_rows_forward_kernel(const bf16* __restrict__ au, int64_t ld, bf16* __restrict__ m, int64_t rows, int f8) {
+  const int64_t total = rows * f8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / f8; const int c = (int)(i % f8) * 8;
+    float a[8], u[8], r[8];
+    load8(au + row * ld + c, a); load8(au + row * ld + (int64_t)f8 * 8 + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = rbf(a[k] * sigmoid_fast(a[k])) * u[k];
+    store8(m + row * (int64_t)f8 * 8 + c, r);
+  }
+}
+__global__ void swiglu_rows_backward_kernel(const bf16* __restrict__ au, const bf16* __restrict__ gm, bf16* __restrict__ gau, int64_t ld, int64_t rows, int f8) {
+  const int64_t total = rows * f8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / f8; const int c = (int)(i % f8) * 8;
+    float a[8], u[8], g[8], ra[8], ru[8];
+    load8(au + row * ld + c, a); load8(au + row * ld + (int64_t)f8 * 8 + c, u); load8(gm + row * (int64_t)f8 * 8 + c, g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sg = sigmoid_fast(a[k]);
+      ru[k] = g[k] * rbf(a[k] * sg);
+      ra[k] = rbf(g[k] * u[k]) * sg * (1.0f + a[k] * (1.0f - sg));
+    }
+    store8(gau + row * ld + c, ra); store8(gau + row * ld + (int64_t)f8 * 8 + c, ru);
+  }
+}
+
+// Value-residual blend over strided rows: y = (1-s) v + s v0, s = sigmoid(lambda).
+__global__ void vres_rows_forward_kernel(const bf16* __restrict__ v, int64_t ldv, const bf16* __restrict__ v0, int64_t ld0, const float* __restrict__ lambda,
+                                         bf16* __restrict__ y, int64_t rows, int c8) {
+  const float s = sigmoidf_(lambda[0]);
+  const int64_t total = rows * c8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / c8; const int c = (int)(i % c8) * 8;
+    float a[8], b[8], r[8];
+    load8(v + row * ldv + c, a); load8(v0 + row * ld0 + c, b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = (1.0f - s) * a[k] + s * b[k];
+    store8(y + row * (int64_t)c8 * 8 + c, r);
+  }
+}
+// Backward of the blend, with the layer-0 accumulation folded in: gv = (1-s) g (strided), acc (+)= bf16(s g) in f32,
+// part[block] = sum (v0 - v) g  (finished by vres_rows_lambda_kernel in block order).
+__global__ void vres_rows_backward_kernel(const bf16* __restrict__ v, int64_t ldv, const bf16* __restrict__ v0, int64_t ld0, const float* __restrict__ lambda,
+                                          const bf16* __restrict__ gy, bf16* __restrict__ gv, int64_t ldg, float* __restrict__ acc, int first,
+                                          double* __restrict__ part, int64_t rows, int c8) {
+  __shared__ float red[32];
+  const float s = sigmoidf_(lambda[0]);
+  const int64_t total = rows * c8;
+  float sum = 0.0f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / c8; const int c = (int)(i % c8) * 8;
+    float a[8], b[8], g[8], r[8], o[8];
+    load8(v + row * ldv + c, a); load8(v0 + row * ld0 + c, b); load8(gy + row * (int64_t)c8 * 8 + c, g);
+    float* ap = acc + row * (int64_t)c8 * 8 + c;
+    if (first) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = 0.0f;
+    } else load8f(ap, o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { r[k] = (1.0f - s) * g[k]; o[k] += rbf(s * g[k]); sum += (b[k] - a[k]) * g[k]; }
+    store8(gv + row * ldg + c, r);
+    *reinterpret_cast<float4*>(ap) = make_float4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<float4*>(ap + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  }
+  const float t = block_sum(sum, red);
+  if (threadIdx.x == 0) part[blockIdx.x] = (double)t;
+}
+__global__ void vres_rows_lambda_kernel(const double* __restrict__ part, int nparts, const float* __restrict__ lambda, float* __restrict__ out) {
+  double a = 0.0;
+  for (int p = threadIdx.x; p < nparts; p += 32) a += part[p];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+  if (threadIdx.x == 0) { const float s = sigmoidf_(lambda[0]); out[0] = (float)(a * (double)s * (double)(1.0f - s)); }
+}
+// Layer 0's raw value gradient: out (strided) = bf16(acc + g), acc = the later layers' contributions (null: a plain strided copy).
+__global__ void vres_root_backward_kernel(const float* __restrict__ acc, const bf16* __restrict__ g, bf16* __restrict__ out, int64_t ldo, int64_t rows, int c8) {
+  const int64_t total = rows * c8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / c8; const int c = (int)(i % c8) * 8;
+    float a[8], r[8];
+    load8(g + row * (int64_t)c8 * 8 + c, r);
+    if (acc) {
+      load8f(acc + row * (int64_t)c8 * 8 + c, a);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) r[k] += a[k];
+    }
+    store8(out + row * ldo + c, r);
   }
 }
 
@@ -283,6 +376,48 @@ ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16*
   gate_apply_backward_kernel<<<(unsigned)blocks, warps * 32, warps * heads * 4, be->stream>>>(scales, attn, gout, gattn, gz, zld, (float*)part, rows, heads, dh);
   OJC_LAUNCHED(be, op);
   fused_column_sum_kernel<<<(heads + 31) / 32, 256, 0, be->stream>>>((const float*)part, gbias, (int)blocks, heads);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+ojc_status swiglu_rows_forward(ojc_backend* be, const bf16* au, int64_t ld, bf16* m, int64_t rows, int64_t f) {
+  const char* op = "swiglu_forward";
+  if (f % 8 != 0 || ld % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
+  swiglu_rows_forward_kernel<<<elementwise_grid(be, rows * (f / 8), 256), 256, 0, be->stream>>>(au, ld, m, rows, (int)(f / 8));
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+ojc_status swiglu_rows_backward(ojc_backend* be, const bf16* au, const bf16* gm, bf16* gau, int64_t ld, int64_t rows, int64_t f) {
+  const char* op = "swiglu_backward";
+  if (f % 8 != 0 || ld % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
+  swiglu_rows_backward_kernel<<<elementwise_grid(be, rows * (f / 8), 256), 256, 0, be->stream>>>(au, gm, gau, ld, rows, (int)(f / 8));
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+ojc_status vres_rows_forward(ojc_backend* be, const bf16* v, int64_t ldv, const bf16* v0, int64_t ld0, const float* lambda, bf16* y, int64_t rows, int64_t cols) {
+  const char* op = "value_residual_blend_forward";
+  if (cols % 8 != 0 || ldv % 8 != 0 || ld0 % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
+  vres_rows_forward_kernel<<<elementwise_grid(be, rows * (cols / 8), 256), 256, 0, be->stream>>>(v, ldv, v0, ld0, lambda, y, rows, (int)(cols / 8));
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+ojc_status vres_rows_backward(ojc_backend* be, const bf16* v, int64_t ldv, const bf16* v0, int64_t ld0, const float* lambda, const bf16* gy, bf16* gv, int64_t ldg,
+                              float* acc, bool first, float* glambda, int64_t rows, int64_t cols) {
+  const char* op = "value_residual_blend_backward";
+  if (cols % 8 != 0 || ldv % 8 != 0 || ld0 % 8 != 0 || ldg % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
+  const int blocks = be->sm_count * 4;
+  void* part = nullptr;
+  OJC_TRY(ojc_scratch(be, (uint64_t)blocks * 8, &part));
+  vres_rows_backward_kernel<<<blocks, 256, 0, be->stream>>>(v, ldv, v0, ld0, lambda, gy, gv, ldg, acc, first ? 1 : 0, (double*)part, rows, (int)(cols / 8));
+  OJC_LAUNCHED(be, op);
+  vres_rows_lambda_kernel<<<1, 32, 0, be->stream>>>((const double*)part, blocks, lambda, glambda);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+ojc_status vres_root_backward(ojc_backend* be, const float* acc, const bf16* g, bf16* out, int64_t ldo, int64_t rows, int64_t cols) {
+  const char* op = "value_residual_blend_backward";
+  if (cols % 8 != 0 || ldo % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
+  vres_root_backward_kernel<<<elementwise_grid(be, rows * (cols / 8), 256), 256, 0, be->stream>>>(acc, g, out, ldo, rows, (int)(cols / 8));
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }

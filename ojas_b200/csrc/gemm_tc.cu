@@ -4,13 +4,15 @@
 //
 // A persistent kernel, one CTA per SM, ten warps with fixed roles:
 //   warp 0   TMA producer: cp.async.bulk.tensor loads of A and B tiles (128-byte
-//            swizzle, no cluster multicast) into a 4-stage shared-memory ring
+//            swizzle, each CTA fetching its own tiles) into a 4-stage shared-memory ring
 //   warp 1   allocates tensor memory and issues tcgen05.mma (one thread);
 //            accumulators live in TMEM, double-buffered (2 x 256 columns) so
 //            the epilogue of tile i overlaps the main loop of tile i+1
 //   warps 2-9  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM
-//            lanes and half of the columns), scale / add residual / accumulate,
-//            store f32 (through padded staging rows, coalesced) or bf16
+//            lanes and half of the columns), scale, write 32 x 128-byte blocks
+//            into swizzled staging rows and hand them to TMA tile stores (the
+//            adding form for C += ...); with a residual operand the block goes
+//            through padded staging rows and coalesced f32 loads / stores instead
 // Tile 128 x 256 x 64; either operand may be K-major or MN-major in memory, so
 // x.W^T, g.W and g^T.x all run on the same kernel without transposed copies.
 // When the output has too few tiles to fill the GPU the reduction axis is
@@ -24,22 +26,23 @@
 
 #include "common.cuh"
 #include "gemm.cuh"
+#include "tc_common.cuh"
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2, B_TILE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-constexpr int STAGE_LD = 20;                      // floats per staged epilogue row (16 + 4 of padding)
-constexpr int EPI_STAGE_BYTES = 8 * 32 * STAGE_LD * 4;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
-#ifndef OJC_DIRECT_BF16
-#define OJC_DIRECT_BF16 1
-#endif
+constexpr int STAGE_LD = 20;                      // floats per staged epilogue row (16 + 4 of padding), residual path
+constexpr int EPI_WARP_BYTES = 32 * 128;          // per epilogue warp: 32 rows of 128 bytes (one swizzled TMA-store box)
+constexpr int EPI_STAGE_BYTES = 8 * EPI_WARP_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + EPI_STAGE_BYTES + 256 /*barriers*/;
+static_assert(32 * STAGE_LD * 4 <= EPI_WARP_BYTES, "the padded residual-path rows share the store staging");
 constexpr int EPI_WARPS = 8;                     // two warps per TMEM lane quarter, each draining half of the columns
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 
 struct TcArgs {
   void* c; int c_bf16; int64_t ldc;
@@ -49,89 +52,37 @@ struct TcArgs {
   int splits, kblocks_per_split;
   float* partial;           // [splits][m][n] when splits > 1
   uint32_t* fault;
-  int epi_warps;            // 4: bf16 rows stored directly by one warp per lane quarter; 8: staged f32 path, two warps per quarter
+  int tma_store;            // finished blocks leave through TMA tile stores (no residual operand; split partials need m % 32 == 0)
+  int tiles_n_fast;         // tile order: 1 = neighbouring CTAs share an A row block (few column tiles), 0 = they share a B column block
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint64_t global_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+// Stores of finished 32-row blocks: TMA tile stores out of swizzled staging rows (the hardware clips at the matrix edge),
+// or the adding form for C += tile.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
-// Bounded wait: false (and the fault word raised) when the limit runs out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* fault, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  // the SM cycle counter bounds the wait (cheap to read; at most ~2 GHz, so the limit is at least two seconds)
-  const long long start = clock64();
-  while (true) {
-#pragma unroll 1
-    for (int spin = 0; spin < 32; ++spin) if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - start > WAIT_LIMIT_CYCLES) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor (128-byte swizzle). Bits: [0,14) start >> 4, [16,30) leading byte offset >> 4,
-// [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) layout type = 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// Instruction descriptor, kind::f16: D f32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), transpose bits 15/16
-// for MN-major operands, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-__device__ __forceinline__ uint32_t make_idesc(int a_mn, int b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
-      "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcArgs args) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
+               const TcArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;               // 128-byte swizzle atoms repeat every 1024 bytes
-  const uint32_t bar_base = tiles_base + STAGES * STAGE_BYTES;
+  const uint32_t epi_base = tiles_base + STAGES * STAGE_BYTES;       // 1024-aligned: the store boxes are swizzled too
+  const uint32_t bar_base = epi_base + EPI_STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bar_base - raw) + 8 * (2 * STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stage_all = reinterpret_cast<float*>(smem_raw + (bar_base - raw) + 256);
+  uint8_t* epi_ptr = smem_raw + (epi_base - raw);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (args.m + BM - 1) / BM, tiles_n = (args.n + BN - 1) / BN;
@@ -140,7 +91,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), args.epi_warps); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -148,9 +99,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  fence_before();
   __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
@@ -159,7 +110,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t it = 0;
       for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x) {
         const int split = u % args.splits, tile = u / args.splits;
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
@@ -176,7 +127,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(args.a_mn_major, args.b_mn_major);
+      const uint32_t idesc = make_idesc(BM, BN, args.a_mn_major, args.b_mn_major);
       // K-major: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO), one MMA step = 32 bytes along the row.
       // MN-major: 64-element column blocks BK*128 bytes apart (LBO), 8-row K groups 1024 bytes apart (SBO), one MMA step = 2 groups.
       const uint32_t a_lbo = args.a_mn_major ? BK * 128 : 0, b_lbo = args.b_mn_major ? BK * 128 : 0;
@@ -187,13 +138,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
         const int acc = local & 1;
         if (!mbar_wait(tempty_bar(acc), ((local >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full_bar(s), (it / STAGES) & 1, args.fault, abort_flag)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          fence_after();
           const uint32_t a_src = tiles_base + s * STAGE_BYTES, b_src = a_src + A_TILE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
@@ -207,45 +158,74 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         umma_commit(tfull_bar(acc));      // accumulator complete
       }
     }
-  } else if (warp < 2 + args.epi_warps) {
+  } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;         // TMEM lanes [32 * quarter, +32) are this warp's
-    float* stage = stage_all + (warp - 2) * 32 * STAGE_LD;
-    const int col_begin = args.epi_warps == 4 ? 0 : ((warp - 2) >> 2) * (BN / 2), col_end = args.epi_warps == 4 ? BN : col_begin + BN / 2;
+    const int col_begin = ((warp - 2) >> 2) * (BN / 2), col_end = col_begin + BN / 2;
+    uint8_t* stage_bytes = epi_ptr + (warp - 2) * EPI_WARP_BYTES;
+    const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
+    float* stage = reinterpret_cast<float*>(stage_bytes);
     uint32_t local = 0;
     for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x, ++local) {
       const int split = u % args.splits, tile = u / args.splits;
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
       const int acc = local & 1;
       if (!mbar_wait(tfull_bar(acc), (local >> 1) & 1, args.fault, abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      fence_after();
       const int row_base = tm * BM + quarter * 32;
+      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if (args.tma_store) {
+        // Each lane owns one accumulator row: it writes 128 bytes of it (64 bf16 or 32 f32 columns) into the warp's
+        // swizzled staging box, and lane 0 hands the 32 x 128-byte box to the TMA unit.
+        const bool bf = args.c_bf16 && args.splits == 1;
+        const int step = bf ? 64 : 32;
+        const int y = (args.splits > 1 ? split * args.m : 0) + row_base;
+#pragma unroll 1
+        for (int c0 = col_begin; c0 < col_end; c0 += step) {
+          uint32_t r[32], r2[32];
+          tmem_ld32(tsrc + c0, r);
+          if (bf) tmem_ld32(tsrc + c0 + 32, r2);
+          tmem_wait_ld();
+          if (lane == 0) bulk_wait_read();       // the previous box has left the staging rows
+          __syncwarp();
+          uint8_t* rowp = stage_bytes + lane * 128;
+          const float al = args.splits > 1 ? 1.0f : args.alpha;
+          if (bf) {
+#pragma unroll
+            for (int ci = 0; ci < 8; ++ci) {
+              const uint32_t* v = ci < 4 ? &r[ci * 8] : &r2[(ci - 4) * 8];
+              *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+                  make_uint4(pack2_bf16(al * __uint_as_float(v[0]), al * __uint_as_float(v[1])), pack2_bf16(al * __uint_as_float(v[2]), al * __uint_as_float(v[3])),
+                             pack2_bf16(al * __uint_as_float(v[4]), al * __uint_as_float(v[5])), pack2_bf16(al * __uint_as_float(v[6]), al * __uint_as_float(v[7])));
+            }
+          } else {
+#pragma unroll
+            for (int ci = 0; ci < 8; ++ci)
+              *reinterpret_cast<float4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+                  make_float4(al * __uint_as_float(r[ci * 4]), al * __uint_as_float(r[ci * 4 + 1]), al * __uint_as_float(r[ci * 4 + 2]), al * __uint_as_float(r[ci * 4 + 3]));
+          }
+          fence_async_smem();
+          __syncwarp();
+          const int x = tn * BN + c0;
+          if (lane == 0 && x < args.n && row_base < args.m) {
+            if (args.accumulate && args.splits == 1) tma_reduce_add_2d(&tmap_c, stage_addr, x, y);
+            else tma_store_2d(&tmap_c, stage_addr, x, y);
+            bulk_commit();
+          }
+        }
+        fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = col_begin; c0 < col_end; c0 += 32) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tmem_ld32(tsrc + c0, r);
+        tmem_wait_ld();
         const int col0 = tn * BN + c0;
-        if (OJC_DIRECT_BF16 && args.c_bf16 && args.splits == 1 && !args.residual) {
-          // bf16 output: each thread writes 64 contiguous bytes of its own row (two full 32-byte sectors)
-          const int row = row_base + lane;
-          if (row < args.m && col0 < args.n) {
-            bf16* dst = reinterpret_cast<bf16*>(args.c) + (int64_t)row * args.ldc + col0;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j >= args.n) break;
-              uint4 t;
-              t.x = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 1])) << 16);
-              t.y = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 2])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 3])) << 16);
-              t.z = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 4])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 5])) << 16);
-              t.w = (uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 6])) | ((uint32_t)f32_to_bf16_bits(args.alpha * __uint_as_float(r[j + 7])) << 16);
-              *reinterpret_cast<uint4*>(dst + j) = t;
-            }
-          }
-          continue;
-        }
-        // f32 output: each thread holds one accumulator row; pass the block, 16 columns at a time, through this warp's
+        // residual path: each thread holds one accumulator row; pass the block, 16 columns at a time, through this warp's
         // padded staging rows so the global accesses are row-contiguous across lanes (4 lanes x 16 bytes per row).
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -274,25 +254,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (args.accumulate) { const float4 t = *reinterpret_cast<const float4*>(dst); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
               *reinterpret_cast<float4*>(dst) = v;
             } else {
-              uint2 t;
-              t.x = (uint32_t)f32_to_bf16_bits(v.x) | ((uint32_t)f32_to_bf16_bits(v.y) << 16);
-              t.y = (uint32_t)f32_to_bf16_bits(v.z) | ((uint32_t)f32_to_bf16_bits(v.w) << 16);
-              *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.c) + o) = t;
+              *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.c) + o) = make_uint2(pack2_bf16(v.x, v.y), pack2_bf16(v.z, v.w));
             }
           }
         }
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (args.tma_store && lane == 0) bulk_wait_all();   // the staging rows must outlive the last store's read; its writes finish before the grid does
   }
   // Teardown: on an aborted run give copies in flight time to land before the shared memory goes away.
   if (*abort_flag) __nanosleep(200000);
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  fence_before();
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
@@ -318,13 +296,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // inner = extent of the contiguous axis, outer = the other one, ld = elements between outer steps.
 ojc_status make_tmap(ojc_backend* be, const char* op, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
-                     uint32_t box_outer) {
+                     uint32_t box_outer, bool f32 = false) {
   if (!be->tmap_encode) return ojc_fail(OJC_ERR_BACKEND, op, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[2] = {inner, outer};
-  cuuint64_t gstride[1] = {ld * 2};
+  cuuint64_t gstride[1] = {ld * (f32 ? 4 : 2)};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estride[2] = {1, 1};
-  CUresult r = ((EncodeTiledFn)be->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+  CUresult r = ((EncodeTiledFn)be->tmap_encode)(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return ojc_fail(OJC_ERR_BACKEND, op, "cuTensorMapEncodeTiled refused the operand (code " + std::to_string((int)r) + ")");
@@ -389,11 +367,19 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   args.a_mn_major = amn; args.b_mn_major = bmn;
   args.alpha = alpha; args.accumulate = accumulate ? 1 : 0; args.residual = residual;
   args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev;
-  args.epi_warps = (OJC_DIRECT_BF16 && args.c_bf16 && splits == 1 && !residual) ? 4 : EPI_WARPS;
   if (splits > 1) {
     void* ws = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)splits * m * n * 4, &ws));
     args.partial = (float*)ws;
+  }
+  // Neighbouring CTAs work on neighbouring tiles: walk the shorter tile axis fastest so the long operand streams from HBM once.
+  args.tiles_n_fast = ((n + BN - 1) / BN) <= ((m + BM - 1) / BM) ? 1 : 0;
+  args.tma_store = (!residual && (splits == 1 || m % 32 == 0) && n >= 64) ? 1 : 0;   // narrower outputs than a store box take the row path
+  CUtensorMap tc = ta;   // unused unless tma_store
+  if (args.tma_store) {
+    if (splits > 1) OJC_TRY(make_tmap(be, op, &tc, args.partial, (uint64_t)n, (uint64_t)splits * (uint64_t)m, (uint64_t)n, 32, 32, true));
+    else if (args.c_bf16) OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 64, 32, false));
+    else OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 32, 32, true));
   }
   int grid = tiles * splits < be->sm_count ? tiles * splits : be->sm_count;
   ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k};
@@ -402,7 +388,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }
     OJC_CUDA(be, cudaEventRecord(sample.start, be->stream), op);
   }
-  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, args);
+  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
   OJC_LAUNCHED(be, op);
   if (be->profile_gemm) {
     OJC_CUDA(be, cudaEventRecord(sample.stop, be->stream), op);

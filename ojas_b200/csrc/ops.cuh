@@ -25,3 +25,10 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
 ojc_status gate_apply_forward(ojc_backend* be, const bf16* z, int zld, const float* bias, const bf16* attn, bf16* out, float* scales, int64_t rows, int heads, int dh);
 ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16* attn, const bf16* gout, bf16* gattn, bf16* gz, int zld, float* gbias, int64_t rows,
                                int heads, int dh);
+// row-strided forms for column slices of a [rows, ld] buffer
+ojc_status swiglu_rows_forward(ojc_backend* be, const bf16* au, int64_t ld, bf16* m, int64_t rows, int64_t f);
+ojc_status swiglu_rows_backward(ojc_backend* be, const bf16* au, const bf16* gm, bf16* gau, int64_t ld, int64_t rows, int64_t f);
+ojc_status vres_rows_forward(ojc_backend* be, const bf16* v, int64_t ldv, const bf16* v0, int64_t ld0, const float* lambda, bf16* y, int64_t rows, int64_t cols);
+ojc_status vres_rows_backward(ojc_backend* be, const bf16* v, int64_t ldv, const bf16* v0, int64_t ld0, const float* lambda, const bf16* gy, bf16* gv, int64_t ldg,
+                              float* acc, bool first, float* glambda, int64_t rows, int64_t cols);
+ojc_status vres_root_backward(ojc_backend* be, const float* acc, const bf16* g, bf16* out, int64_t ldo, int64_t rows, int64_t cols);

@@ -1,13 +1,13 @@
-// Causal attention forward on the Blackwell tensor cores (tcgen05 + TMEM), head_dim 64, bf16 operands.
+// Causal attention on the Blackwell tensor cores (tcgen05 + TMEM), head_dim 64, bf16 operands.
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the visible key blocks of 128:
-//   warp 4   TMA producer: Q once, then K (two stages) and V tiles, 128-byte swizzle, no multicast
+// Forward: one CTA owns 128 query rows of one (batch, head) and walks the visible key blocks of 128:
+//   warp 4   TMA producer: Q once, then (K, V) pairs into two stages, 128-byte swizzle, every CTA fetching its own tiles
 //   warp 5   allocates 256 TMEM columns and issues the MMAs: S = Q K^T (M128 N128 K64, both K-major) into columns
-//            [0,128), then PV = P V (M128 N64 K128, P K-major from shared memory, V MN-major) into columns [128,192)
-//   warps 0-3  one thread per query row (= TMEM lane): read S, online softmax in the log2 domain, write P as bf16 into
-//            the swizzled shared-memory A-operand layout, then add PV into the f32 output row kept in registers
-//            (rescaled whenever the running maximum moves), finally normalise, store O and lse.
-// Two CTAs fit on an SM (96 KB of shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+//            [0,128), then O += P V (M128 N64 K128, P K-major from shared memory, V MN-major) into columns [128,192)
+//   warps 0-3  one thread per query row (= TMEM lane): read the S row once, softmax in the log2 domain against a row
+//            scale that moves only when the maximum outgrew it by 2^8 (then O is rescaled in place in TMEM), write P as
+//            bf16 into the swizzled shared-memory A-operand layout; at the end normalise O from TMEM, store O and lse.
+// Two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
 // Every mbarrier wait is bounded; on expiry the CTA raises the fault word, drains and frees its TMEM.
 #include "sdpa.cuh"
 #include "tc_common.cuh"
@@ -18,11 +18,12 @@ using namespace tc;
 
 constexpr int BM = 128, BN = 128, D = 64;
 constexpr int TILE_BYTES = 128 * D * 2;                       // 16 KB: 128 rows of 128 bytes
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 4 * TILE_BYTES, OFF_BAR = 6 * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;
+constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 5 * TILE_BYTES, OFF_BAR = 7 * TILE_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 128;                     // 112 KB + barriers: two CTAs per SM
 constexpr int NTHREADS = 192, BWD_THREADS = 320;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
-enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL, B_VEMPTY, B_SFULL, B_PREADY, B_PVFULL, B_COUNT };
+constexpr float RESCALE_STEP = 8.0f;                          // log2 units the row maximum may run ahead of the scale in use
+enum { B_QFULL = 0, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL, B_PREADY, B_PVFULL, B_COUNT };
 
 struct FwdArgs {
   SdpaView<bf16> out;
@@ -40,10 +41,10 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
 
 __global__ void __launch_bounds__(NTHREADS, 2)
 sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }   // the swizzled tiles need 1024-byte alignment (whole CTA leaves)
+  uint8_t* base_ptr = smem_raw;
   auto bar = [&](int i) { return base + OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_BAR + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -70,18 +71,16 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer: Q, then (K, V) pairs two blocks ahead
     if (lane == 0) {
       mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
       load_tile(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
       for (int j = 0; j < nblocks && !*abort_flag; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(bar(B_KEMPTY0 + s), ((j >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
-        mbar_expect_tx(bar(B_KFULL0 + s), TILE_BYTES);
-        load_tile(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KFULL0 + s), args.h_first, hk, j * BN, b);
-        if (!mbar_wait(bar(B_VEMPTY), (j & 1) ^ 1, args.fault, abort_flag)) break;
-        mbar_expect_tx(bar(B_VFULL), TILE_BYTES);
-        load_tile(base + OFF_V, &tm_v, bar(B_VFULL), args.h_first, hk, j * BN, b);
+        if (!mbar_wait(bar(B_KVEMPTY0 + s), ((j >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(B_KVFULL0 + s), 2 * TILE_BYTES);
+        load_tile(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
+        load_tile(base + OFF_V + s * TILE_BYTES, &tm_v, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
       }
     }
   } else if (warp == 5) {
@@ -91,24 +90,23 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       bool ok = mbar_wait(bar(B_QFULL), 0, args.fault, abort_flag);
       for (int j = 0; j < nblocks && ok && !*abort_flag; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(bar(B_KFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) break;
+        if (!mbar_wait(bar(B_KVFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) break;
         fence_after();
         // S = Q K^T: both operands K-major rows of 128 bytes, 8-row groups 1024 bytes apart, one step = 32 bytes.
         // The S columns are free: every softmax thread arrived on B_PREADY for block j - 1 after its last S read.
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           umma(tmem_base, make_desc(base + OFF_Q + kk * 32, 0, 1024), make_desc(base + OFF_K + s * TILE_BYTES + kk * 32, 0, 1024), idesc_s, kk > 0);
-        umma_commit(bar(B_KEMPTY0 + s));
         umma_commit(bar(B_SFULL));
         if (!mbar_wait(bar(B_PREADY), j & 1, args.fault, abort_flag)) break;
-        if (!mbar_wait(bar(B_VFULL), j & 1, args.fault, abort_flag)) break;
         fence_after();
-        // PV = P V: P is two K-major halves of 64 keys (16 KB apart); V is MN-major (one 64-wide block), 16 keys = 2048 bytes.
+        // O += P V: P is two K-major halves of 64 keys (16 KB apart); V is MN-major (one 64-wide block), 16 keys = 2048 bytes.
+        // O stays in TMEM for the whole walk; the softmax rows rescale it in place when their maximum moves.
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          umma(tmem_base + 128, make_desc(base + OFF_P + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024), make_desc(base + OFF_V + kk * 2048, 1024, 1024),
-               idesc_pv, kk > 0);
-        umma_commit(bar(B_VEMPTY));
+          umma(tmem_base + 128, make_desc(base + OFF_P + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024),
+               make_desc(base + OFF_V + s * TILE_BYTES + kk * 2048, 1024, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(B_KVEMPTY0 + s));
         umma_commit(bar(B_PVFULL));
       }
     }
@@ -118,88 +116,93 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const int row = q0 + tid;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
     const float sl2 = args.scale * LOG2E;
-    float m = -INFINITY, l = 0.0f, o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.0f;
+    float m = 0.0f, l = 0.0f;                     // m: the maximum the probabilities are scaled by (log2 domain), set by block 0
     uint8_t* p_row = base_ptr + OFF_P + tid * 128;
     bool ok = true;
     for (int j = 0; j < nblocks && ok && !*abort_flag; ++j) {
       if (!mbar_wait(bar(B_SFULL), j & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
       const int key0 = j * BN;
-      const bool diag = key0 + BN > q0;           // only blocks touching the diagonal or the sequence end need masking
-      const bool tail = key0 + BN > args.time;
-      const bool masked = diag || tail;
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + c * 32, r);
-        tmem_wait_ld();
-        if (!masked) {
+      const bool masked = key0 + BN > q0 || key0 + BN > args.time;   // only blocks touching the diagonal or the sequence end need masking
+      uint32_t r[BN];                                                  // the whole S row of this block: one TMEM pass
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
+      for (int c = 0; c < BN / 32; ++c) tmem_ld32(lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_wait_ld();
+      if (masked) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = key0 + c * 32 + e;
-            if (key <= row && key < args.time) mx = fmaxf(mx, __uint_as_float(r[e]));
-          }
+        for (int e = 0; e < BN; ++e) {
+          const int key = key0 + e;
+          if (!(key <= row && key < args.time)) r[e] = 0xff800000u;   // -inf: exp2 gives an exact zero
         }
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four chains instead of one 128-deep dependency
+#pragma unroll
+      for (int e = 0; e < BN; e += 4) {
+        mx4[0] = fmaxf(mx4[0], __uint_as_float(r[e])); mx4[1] = fmaxf(mx4[1], __uint_as_float(r[e + 1]));
+        mx4[2] = fmaxf(mx4[2], __uint_as_float(r[e + 2])); mx4[3] = fmaxf(mx4[3], __uint_as_float(r[e + 3]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= sl2;                                   // the scale is positive: max(s) * scale = max(s * scale)
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-      const float corr = fast_exp2(m - m_use);
-      float rowsum = 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + c * 32, r);
-        tmem_wait_ld();
+      // The scale moves only when some row of the warp outgrew it by RESCALE_STEP (the TMEM accesses are warp-wide);
+      // block 0 holds key 0, visible to every row, so m is finite from then on.
+      const bool grow = j == 0 || mx > m + RESCALE_STEP;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = j == 0 ? (mx == -INFINITY ? 0.0f : mx) : fmaxf(m, mx);
+        const float corr = j == 0 ? 0.0f : fast_exp2(m - m_new);
+        m = m_new;
+        l *= corr;
+        if (j > 0) {
+          // O of blocks 0..j-1 must have landed before it is rescaled in place
+          if (!mbar_wait(bar(B_PVFULL), (j - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float p[8];
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(lane_base + 128 + c * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            p[e] = fast_exp2(fmaf(__uint_as_float(r[g * 8 + e]), sl2, -m_use));
-            if (masked) { const int key = key0 + c * 32 + g * 8 + e; if (!(key <= row && key < args.time)) p[e] = 0.0f; }
-            rowsum += p[e];
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+            tmem_st32(lane_base + 128 + c * 32, o);
           }
-          const int ci = c * 4 + g;               // 16-byte chunk of this row's 128 keys; the swizzle XORs it with row % 8
-          *reinterpret_cast<uint4*>(p_row + (ci >> 3) * TILE_BYTES + (((ci & 7) ^ (tid & 7)) << 4)) =
-              make_uint4(pack2_bf16(p[0], p[1]), pack2_bf16(p[2], p[3]), pack2_bf16(p[4], p[5]), pack2_bf16(p[6], p[7]));
+          tmem_wait_st();
         }
       }
-      l = l * corr + rowsum;
-      m = m_new;
+      float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int ci = 0; ci < BN / 8; ++ci) {
+        float p[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { p[e] = fast_exp2(fmaf(__uint_as_float(r[ci * 8 + e]), sl2, -m)); rs4[e & 3] += p[e]; }
+        // 16-byte chunk ci of this row's 128 keys; the 128-byte swizzle XORs the chunk index with row % 8
+        *reinterpret_cast<uint4*>(p_row + (ci >> 3) * TILE_BYTES + (((ci & 7) ^ (tid & 7)) << 4)) =
+            make_uint4(pack2_bf16(p[0], p[1]), pack2_bf16(p[2], p[3]), pack2_bf16(p[4], p[5]), pack2_bf16(p[6], p[7]));
+      }
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       fence_before();
       fence_async_smem();
       mbar_arrive(bar(B_PREADY));
-#pragma unroll
-      for (int i = 0; i < D; ++i) o[i] *= corr;   // overlaps the PV MMAs
-      if (!mbar_wait(bar(B_PVFULL), j & 1, args.fault, abort_flag)) { ok = false; break; }
+    }
+    if (ok && mbar_wait(bar(B_PVFULL), (nblocks - 1) & 1, args.fault, abort_flag)) {
       fence_after();
+      const float inv = 1.0f / l;
+      bf16* dst = row < args.time ? args.out.row(b, h, row) : nullptr;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + 128 + c * 32, r);
+        uint32_t o[32];
+        tmem_ld32(lane_base + 128 + c * 32, o);
         tmem_wait_ld();
+        if (dst) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] += __uint_as_float(r[e]);
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) =
+                make_uint4(pack2_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv), pack2_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                           pack2_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv), pack2_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+        }
       }
-      fence_before();
-    }
-    if (ok && row < args.time) {
-      const float inv = 1.0f / l;
-      bf16* dst = args.out.row(b, h, row);
-#pragma unroll
-      for (int i = 0; i < D; i += 8) {
-        *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack2_bf16(o[i] * inv, o[i + 1] * inv), pack2_bf16(o[i + 2] * inv, o[i + 3] * inv),
-                                                        pack2_bf16(o[i + 4] * inv, o[i + 5] * inv), pack2_bf16(o[i + 6] * inv, o[i + 7] * inv));
+      if (dst) {
+        args.lse[((int64_t)b * args.heads + h) * args.time + row] = (m + log2f(l)) * LN2;
+        if (!(l > 0.0f) || !isfinite(l) || !isfinite(m)) raise_fault(args.fault, OP_SDPA);
       }
-      args.lse[((int64_t)b * args.heads + h) * args.time + row] = (m + log2f(l)) * LN2;
-      if (!(l > 0.0f) || !isfinite(l) || !isfinite(m)) raise_fault(args.fault, OP_SDPA);
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -229,10 +232,6 @@ struct BwdArgs {
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void store_chunk(uint8_t* row_ptr, int ci, int tid, const float (&v)[8]) {
-  *reinterpret_cast<uint4*>(row_ptr + (ci >> 3) * TILE_BYTES + (((ci & 7) ^ (tid & 7)) << 4)) =
-      make_uint4(pack2_bf16(v[0], v[1]), pack2_bf16(v[2], v[3]), pack2_bf16(v[4], v[5]), pack2_bf16(v[6], v[7]));
-}
 template <int COLS>
 __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr) {
 #pragma unroll
@@ -251,11 +250,19 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr) {
   }
 }
 
+// Both backward kernels walk their inner dimension in steps of SUB = 64 with the S / dP accumulators double-buffered in
+// TMEM, so the tensor pipe forms step i + 1 while the eight compute warps turn step i into P and dS.
+constexpr int SUB = 64;
+constexpr int SUB_BYTES = SUB * D * 2;         // 8 KB: 64 rows of q / dO (or k / v)
+constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
+constexpr int IN_STAGES = 4;
+
 // ---- dK, dV
-constexpr int KV_OFF_K = 0, KV_OFF_V = TILE_BYTES, KV_OFF_Q = 2 * TILE_BYTES, KV_OFF_G = 4 * TILE_BYTES, KV_OFF_P = 6 * TILE_BYTES, KV_OFF_DS = 8 * TILE_BYTES,
-              KV_OFF_STAT = 10 * TILE_BYTES, KV_OFF_BAR = KV_OFF_STAT + 2 * 2 * 128 * 4;
-constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 128 + 1024;
-enum { KB_KVFULL = 0, KB_QDFULL0, KB_QDFULL1, KB_QDEMPTY0, KB_QDEMPTY1, KB_SFULL, KB_PREADY, KB_DONE, KB_COUNT };
+constexpr int KV_OFF_K = 0, KV_OFF_V = TILE_BYTES, KV_OFF_Q = 2 * TILE_BYTES, KV_OFF_G = KV_OFF_Q + IN_STAGES * SUB_BYTES, KV_OFF_P = KV_OFF_G + IN_STAGES * SUB_BYTES,
+              KV_OFF_DS = KV_OFF_P + 2 * PT_BYTES, KV_OFF_STAT = KV_OFF_DS + 2 * PT_BYTES, KV_OFF_BAR = KV_OFF_STAT + IN_STAGES * 2 * SUB * 4;
+constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 256 + 1024;
+enum { KB_KVFULL = 0, KB_INFULL0, KB_INEMPTY0 = KB_INFULL0 + IN_STAGES, KB_SFULL0 = KB_INEMPTY0 + IN_STAGES, KB_PREADY0 = KB_SFULL0 + 2, KB_PFREE0 = KB_PREADY0 + 2,
+       KB_DONE = KB_PFREE0 + 2, KB_COUNT };
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -267,16 +274,16 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   auto bar = [&](int i) { return base + KV_OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + KV_OFF_BAR + 8 * KB_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stat = reinterpret_cast<float*>(base_ptr + KV_OFF_STAT);   // [2 buffers][lse 128 | dr 128]
+  const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse 64 | dr 64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k0 = blockIdx.x * BN;
   const int plane = blockIdx.y, b = plane / args.kv_heads, hk = plane % args.kv_heads, rep = args.heads / args.kv_heads;
-  const int q_blocks = (args.time - k0 + BM - 1) / BM;      // query blocks k0, k0 + 128, ... (k0 is a multiple of 128)
-  const int iters = rep * q_blocks;
+  const int q_subs = (args.time - k0 + SUB - 1) / SUB;      // query steps k0, k0 + 64, ... (k0 is a multiple of 128)
+  const int iters = rep * q_subs;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < KB_COUNT; ++i) mbar_init(bar(i), i == KB_PREADY ? 256 : 1);
+    for (int i = 0; i < KB_COUNT; ++i) mbar_init(bar(i), (i >= KB_PREADY0 && i < KB_PREADY0 + 2) ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -288,6 +295,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: step buffers t = 0, 1 at 128 t: S^T [0,64) and dP^T [64,128); dV [256,320); dK [320,384)
 
   if (warp == 8) {
     if (lane == 0) {
@@ -295,86 +303,96 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       load_tile(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
       load_tile(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
       for (int it = 0; it < iters && !*abort_flag; ++it) {
-        const int s = it & 1, h = hk * rep + it / q_blocks, q0 = k0 + (it % q_blocks) * BM;
-        if (!mbar_wait(bar(KB_QDEMPTY0 + s), ((it >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
-        // the block's row statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
-        const uint32_t stat_bytes = (uint32_t)min(BM, args.time - q0) * 4u;
+        const int s = it % IN_STAGES, h = hk * rep + it / q_subs, q0 = k0 + (it % q_subs) * SUB;
+        if (!mbar_wait(bar(KB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
+        // the step's row statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
+        const uint32_t stat_bytes = (uint32_t)min(SUB, args.time - q0) * 4u;
         const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
-        mbar_expect_tx(bar(KB_QDFULL0 + s), 2 * TILE_BYTES + 2 * stat_bytes);
-        load_tile(base + KV_OFF_Q + s * TILE_BYTES, &tm_q, bar(KB_QDFULL0 + s), args.h_first, h, q0, b);
-        load_tile(base + KV_OFF_G + s * TILE_BYTES, &tm_g, bar(KB_QDFULL0 + s), args.h_first, h, q0, b);
-        bulk_load(base + KV_OFF_STAT + s * 1024, args.lse + idx, stat_bytes, bar(KB_QDFULL0 + s));
-        bulk_load(base + KV_OFF_STAT + s * 1024 + 512, args.dr + idx, stat_bytes, bar(KB_QDFULL0 + s));
+        mbar_expect_tx(bar(KB_INFULL0 + s), 2 * SUB_BYTES + 2 * stat_bytes);
+        load_tile(base + KV_OFF_Q + s * SUB_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
+        load_tile(base + KV_OFF_G + s * SUB_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
+        bulk_load(base + KV_OFF_STAT + s * 512, args.lse + idx, stat_bytes, bar(KB_INFULL0 + s));
+        bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
       }
     }
   } else if (warp == 9) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(BN, BM, 0, 0), idesc_o = make_idesc(BN, D, 0, 1);
-      bool ok = mbar_wait(bar(KB_KVFULL), 0, args.fault, abort_flag);
+      const uint32_t idesc_s = make_idesc(BN, SUB, 0, 0), idesc_o = make_idesc(BN, D, 0, 1);
+      // S^T = K Q^T and dP^T = V dO^T of step i into TMEM buffer i & 1
+      auto issue_s = [&](int i) {
+        const uint32_t qs = base + KV_OFF_Q + (i % IN_STAGES) * SUB_BYTES, gs = base + KV_OFF_G + (i % IN_STAGES) * SUB_BYTES, tm = tmem_base + (i & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma(tm, make_desc(base + KV_OFF_K + kk * 32, 0, 1024), make_desc(qs + kk * 32, 0, 1024), idesc_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma(tm + 64, make_desc(base + KV_OFF_V + kk * 32, 0, 1024), make_desc(gs + kk * 32, 0, 1024), idesc_s, kk > 0);
+        umma_commit(bar(KB_SFULL0 + (i & 1)));
+      };
+      bool ok = mbar_wait(bar(KB_KVFULL), 0, args.fault, abort_flag) && mbar_wait(bar(KB_INFULL0), 0, args.fault, abort_flag);
+      if (ok) { fence_after(); issue_s(0); }
       for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(bar(KB_QDFULL0 + s), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        if (it + 1 < iters) {
+          // buffer (it + 1) & 1 is free: the compute warps arrived on PREADY of step it - 1 after their last read of it
+          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+          issue_s(it + 1);
+        }
+        if (!mbar_wait(bar(KB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
         fence_after();
-        const uint32_t qs = base + KV_OFF_Q + s * TILE_BYTES, gs = base + KV_OFF_G + s * TILE_BYTES;
+        const uint32_t qs = base + KV_OFF_Q + (it % IN_STAGES) * SUB_BYTES, gs = base + KV_OFF_G + (it % IN_STAGES) * SUB_BYTES;
+        const uint32_t ps = base + KV_OFF_P + (it & 1) * PT_BYTES, ds = base + KV_OFF_DS + (it & 1) * PT_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)   // S^T = K Q^T
-          umma(tmem_base, make_desc(base + KV_OFF_K + kk * 32, 0, 1024), make_desc(qs + kk * 32, 0, 1024), idesc_s, kk > 0);
+        for (int kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand: 16 queries = 2048 bytes)
+          umma(tmem_base + 256, make_desc(ps + kk * 32, 0, 1024), make_desc(gs + kk * 2048, 1024, 1024), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)   // dP^T = V dO^T
-          umma(tmem_base + 128, make_desc(base + KV_OFF_V + kk * 32, 0, 1024), make_desc(gs + kk * 32, 0, 1024), idesc_s, kk > 0);
-        umma_commit(bar(KB_SFULL));
-        if (!mbar_wait(bar(KB_PREADY), it & 1, args.fault, abort_flag)) { ok = false; break; }
-        fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand)
-          umma(tmem_base + 256, make_desc(base + KV_OFF_P + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024), make_desc(gs + kk * 2048, 1024, 1024), idesc_o,
-               (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk)  // dK += dS^T Q
-          umma(tmem_base + 320, make_desc(base + KV_OFF_DS + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024), make_desc(qs + kk * 2048, 1024, 1024), idesc_o,
-               (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(KB_QDEMPTY0 + s));
+        for (int kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
+          umma(tmem_base + 320, make_desc(ds + kk * 32, 0, 1024), make_desc(qs + kk * 2048, 1024, 1024), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(KB_INEMPTY0 + it % IN_STAGES));
+        umma_commit(bar(KB_PFREE0 + (it & 1)));
       }
       if (ok) umma_commit(bar(KB_DONE));
     }
   } else {
-    // two warpgroups share the 128 TMEM lanes (a warp reaches lanes 32 * (warp % 4) ..): group 0 takes query columns [0,64), group 1 [64,128)
+    // two warpgroups share the 128 TMEM lanes (a warp reaches lanes 32 * (warp % 4) ..): group `half` takes 32 of the step's 64 query columns
     const int tid = threadIdx.x & 127, half = warp >> 2, key = k0 + tid;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
-    uint8_t* p_row = base_ptr + KV_OFF_P + tid * 128;
-    uint8_t* ds_row = base_ptr + KV_OFF_DS + tid * 128;
     bool ok = true;
     for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
-      const int q0 = k0 + (it % q_blocks) * BM;
-      const float* st = stat + (it & 1) * 256;   // lse[128] | dr[128] of this query block, landed with the Q / dO tiles
-      if (!mbar_wait(bar(KB_SFULL), it & 1, args.fault, abort_flag)) { ok = false; break; }
+      const int q0 = k0 + (it % q_subs) * SUB, t = it & 1;
+      const float* st = stat + (it % IN_STAGES) * 128;   // lse[64] | dr[64] of this step, landed with the q / dO tiles
+      if (!mbar_wait(bar(KB_SFULL0 + t), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      // the P / dS buffer of step it - 2 must have been consumed by its dV / dK MMAs
+      if (it >= 2 && !mbar_wait(bar(KB_PFREE0 + t), ((it >> 1) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
-      const bool masked = q0 == k0 || q0 + BM > args.time || k0 + BN > args.time;   // diagonal block or a ragged end
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(lane_base + c * 32, rs);
-        tmem_ld32(lane_base + 128 + c * 32, rp);
-        tmem_wait_ld();
+      const bool masked = q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time;   // diagonal steps or a ragged end
+      uint32_t rs[32], rp[32];
+      tmem_ld32(lane_base + t * 128 + half * 32, rs);
+      tmem_ld32(lane_base + t * 128 + 64 + half * 32, rp);
+      tmem_wait_ld();
+      uint8_t* p_row = base_ptr + KV_OFF_P + t * PT_BYTES + tid * 128;
+      uint8_t* ds_row = base_ptr + KV_OFF_DS + t * PT_BYTES + tid * 128;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float pv[8], dv[8];
+      for (int g = 0; g < 4; ++g) {
+        float pv[8], dv[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int qc = c * 32 + g * 8 + e;
-            float p = fast_exp2(fmaf(__uint_as_float(rs[g * 8 + e]), sl2, -st[qc] * LOG2E));
-            if (masked && !(key < args.time && q0 + qc < args.time && key <= q0 + qc)) p = 0.0f;
-            pv[e] = p;
-            dv[e] = p * (__uint_as_float(rp[g * 8 + e]) - st[128 + qc]) * args.scale;
-          }
-          store_chunk(p_row, c * 4 + g, tid, pv);
-          store_chunk(ds_row, c * 4 + g, tid, dv);
+        for (int e = 0; e < 8; ++e) {
+          const int qc = half * 32 + g * 8 + e;
+          const float p = fast_exp2(fmaf(__uint_as_float(rs[g * 8 + e]), sl2, -st[qc] * LOG2E));
+          const float ds = p * (__uint_as_float(rp[g * 8 + e]) - st[SUB + qc]) * args.scale;
+          // rows past the sequence end carry no statistics (whatever the buffer held): select, never multiply by zero
+          const bool vis = !masked || (key < args.time && q0 + qc < args.time && key <= q0 + qc);
+          pv[e] = vis ? p : 0.0f;
+          dv[e] = vis ? ds : 0.0f;
         }
+        const int ci = half * 4 + g;             // 16-byte chunk of the 128-byte row; the swizzle XORs it with row % 8
+        *reinterpret_cast<uint4*>(p_row + ((ci ^ (tid & 7)) << 4)) =
+            make_uint4(pack2_bf16(pv[0], pv[1]), pack2_bf16(pv[2], pv[3]), pack2_bf16(pv[4], pv[5]), pack2_bf16(pv[6], pv[7]));
+        *reinterpret_cast<uint4*>(ds_row + ((ci ^ (tid & 7)) << 4)) =
+            make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7]));
       }
       fence_before();
       fence_async_smem();
-      mbar_arrive(bar(KB_PREADY));
+      mbar_arrive(bar(KB_PREADY0 + t));
     }
     if (ok && mbar_wait(bar(KB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
@@ -392,9 +410,11 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 }
 
 // ---- dQ
-constexpr int DQ_OFF_Q = 0, DQ_OFF_G = TILE_BYTES, DQ_OFF_K = 2 * TILE_BYTES, DQ_OFF_V = 4 * TILE_BYTES, DQ_OFF_DS = 6 * TILE_BYTES, DQ_OFF_BAR = 8 * TILE_BYTES;
-constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 128 + 1024;
-enum { QB_QDFULL = 0, QB_KVFULL0, QB_KVFULL1, QB_KVEMPTY0, QB_KVEMPTY1, QB_SFULL, QB_PREADY, QB_DONE, QB_COUNT };
+constexpr int DQ_OFF_Q = 0, DQ_OFF_G = TILE_BYTES, DQ_OFF_K = 2 * TILE_BYTES, DQ_OFF_V = DQ_OFF_K + IN_STAGES * SUB_BYTES, DQ_OFF_DS = DQ_OFF_V + IN_STAGES * SUB_BYTES,
+              DQ_OFF_BAR = DQ_OFF_DS + 2 * PT_BYTES;
+constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 256 + 1024;
+enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL0 = QB_INEMPTY0 + IN_STAGES, QB_PREADY0 = QB_SFULL0 + 2, QB_PFREE0 = QB_PREADY0 + 2,
+       QB_DONE = QB_PFREE0 + 2, QB_COUNT };
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -412,10 +432,10 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   const int q0 = qt * BM;
   const int plane = blockIdx.y, b = plane / args.heads, h = plane % args.heads, hk = h / (args.heads / args.kv_heads);
   const int n_end = min(args.time, q0 + BM);
-  const int nblocks = (n_end + BN - 1) / BN;
+  const int iters = (n_end + SUB - 1) / SUB;     // key steps 0, 64, ...
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < QB_COUNT; ++i) mbar_init(bar(i), i == QB_PREADY ? 256 : 1);
+    for (int i = 0; i < QB_COUNT; ++i) mbar_init(bar(i), (i >= QB_PREADY0 && i < QB_PREADY0 + 2) ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -427,81 +447,86 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: step buffers t = 0, 1 at 128 t: S [0,64) and dP [64,128); dQ [256,320)
 
   if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(bar(QB_QDFULL), 2 * TILE_BYTES);
       load_tile(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
       load_tile(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
-      for (int j = 0; j < nblocks && !*abort_flag; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(bar(QB_KVEMPTY0 + s), ((j >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
-        mbar_expect_tx(bar(QB_KVFULL0 + s), 2 * TILE_BYTES);
-        load_tile(base + DQ_OFF_K + s * TILE_BYTES, &tm_k, bar(QB_KVFULL0 + s), args.h_first, hk, j * BN, b);
-        load_tile(base + DQ_OFF_V + s * TILE_BYTES, &tm_v, bar(QB_KVFULL0 + s), args.h_first, hk, j * BN, b);
+      for (int it = 0; it < iters && !*abort_flag; ++it) {
+        const int s = it % IN_STAGES;
+        if (!mbar_wait(bar(QB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(QB_INFULL0 + s), 2 * SUB_BYTES);
+        load_tile(base + DQ_OFF_K + s * SUB_BYTES, &tm_k, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
+        load_tile(base + DQ_OFF_V + s * SUB_BYTES, &tm_v, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
       }
     }
   } else if (warp == 9) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(BM, BN, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
-      bool ok = mbar_wait(bar(QB_QDFULL), 0, args.fault, abort_flag);
-      for (int j = 0; j < nblocks && ok && !*abort_flag; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(bar(QB_KVFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      const uint32_t idesc_s = make_idesc(BM, SUB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
+      auto issue_s = [&](int i) {   // S = Q K^T and dP = dO V^T of step i into TMEM buffer i & 1
+        const uint32_t ks = base + DQ_OFF_K + (i % IN_STAGES) * SUB_BYTES, vs = base + DQ_OFF_V + (i % IN_STAGES) * SUB_BYTES, tm = tmem_base + (i & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma(tm, make_desc(base + DQ_OFF_Q + kk * 32, 0, 1024), make_desc(ks + kk * 32, 0, 1024), idesc_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma(tm + 64, make_desc(base + DQ_OFF_G + kk * 32, 0, 1024), make_desc(vs + kk * 32, 0, 1024), idesc_s, kk > 0);
+        umma_commit(bar(QB_SFULL0 + (i & 1)));
+      };
+      bool ok = mbar_wait(bar(QB_QDFULL), 0, args.fault, abort_flag) && mbar_wait(bar(QB_INFULL0), 0, args.fault, abort_flag);
+      if (ok) { fence_after(); issue_s(0); }
+      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+        if (it + 1 < iters) {
+          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+          issue_s(it + 1);
+        }
+        if (!mbar_wait(bar(QB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
         fence_after();
-        const uint32_t ks = base + DQ_OFF_K + s * TILE_BYTES, vs = base + DQ_OFF_V + s * TILE_BYTES;
+        const uint32_t ks = base + DQ_OFF_K + (it % IN_STAGES) * SUB_BYTES, ds = base + DQ_OFF_DS + (it & 1) * PT_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)   // S = Q K^T
-          umma(tmem_base, make_desc(base + DQ_OFF_Q + kk * 32, 0, 1024), make_desc(ks + kk * 32, 0, 1024), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)   // dP = dO V^T
-          umma(tmem_base + 128, make_desc(base + DQ_OFF_G + kk * 32, 0, 1024), make_desc(vs + kk * 32, 0, 1024), idesc_s, kk > 0);
-        umma_commit(bar(QB_SFULL));
-        if (!mbar_wait(bar(QB_PREADY), j & 1, args.fault, abort_flag)) { ok = false; break; }
-        fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand)
-          umma(tmem_base + 256, make_desc(base + DQ_OFF_DS + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024), make_desc(ks + kk * 2048, 1024, 1024), idesc_o,
-               (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(QB_KVEMPTY0 + s));
+        for (int kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
+          umma(tmem_base + 256, make_desc(ds + kk * 32, 0, 1024), make_desc(ks + kk * 2048, 1024, 1024), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(QB_INEMPTY0 + it % IN_STAGES));
+        umma_commit(bar(QB_PFREE0 + (it & 1)));
       }
       if (ok) umma_commit(bar(QB_DONE));
     }
   } else {
-    const int tid = threadIdx.x & 127, half = warp >> 2, row = q0 + tid;   // warpgroup `half` takes key columns [64 * half, 64 * half + 64)
+    const int tid = threadIdx.x & 127, half = warp >> 2, row = q0 + tid;   // warpgroup `half` takes 32 of the step's 64 key columns
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
     const int64_t idx = ((int64_t)b * args.heads + h) * args.time + row;
     const float lse_row = row < args.time ? args.lse[idx] * LOG2E : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
-    uint8_t* ds_row = base_ptr + DQ_OFF_DS + tid * 128;
     bool ok = true;
-    for (int j = 0; j < nblocks && ok && !*abort_flag; ++j) {
-      if (!mbar_wait(bar(QB_SFULL), j & 1, args.fault, abort_flag)) { ok = false; break; }
+    for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+      const int t = it & 1, key0 = it * SUB + half * 32;
+      if (!mbar_wait(bar(QB_SFULL0 + t), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      if (it >= 2 && !mbar_wait(bar(QB_PFREE0 + t), ((it >> 1) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
-      const int key0 = j * BN;
-      const bool diag = key0 + BN > q0, tail = key0 + BN > args.time;
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(lane_base + c * 32, rs);
-        tmem_ld32(lane_base + 128 + c * 32, rp);
-        tmem_wait_ld();
+      const bool masked = it * SUB + SUB > q0 || it * SUB + SUB > args.time;
+      uint32_t rs[32], rp[32];
+      tmem_ld32(lane_base + t * 128 + half * 32, rs);
+      tmem_ld32(lane_base + t * 128 + 64 + half * 32, rp);
+      tmem_wait_ld();
+      uint8_t* ds_row = base_ptr + DQ_OFF_DS + t * PT_BYTES + tid * 128;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float dv[8];
+      for (int g = 0; g < 4; ++g) {
+        float dv[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int key = key0 + c * 32 + g * 8 + e;
-            float p = fast_exp2(fmaf(__uint_as_float(rs[g * 8 + e]), sl2, -lse_row));
-            if ((diag || tail) && !(key <= row && key < args.time)) p = 0.0f;
-            dv[e] = p * (__uint_as_float(rp[g * 8 + e]) - dr_row) * args.scale;
-          }
-          store_chunk(ds_row, c * 4 + g, tid, dv);
+        for (int e = 0; e < 8; ++e) {
+          const int key = key0 + g * 8 + e;
+          const float p = fast_exp2(fmaf(__uint_as_float(rs[g * 8 + e]), sl2, -lse_row));
+          const bool vis = !masked || (key <= row && key < args.time);
+          dv[e] = vis ? p * (__uint_as_float(rp[g * 8 + e]) - dr_row) * args.scale : 0.0f;
         }
+        const int ci = half * 4 + g;
+        *reinterpret_cast<uint4*>(ds_row + ((ci ^ (tid & 7)) << 4)) =
+            make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7]));
       }
       fence_before();
       fence_async_smem();
-      mbar_arrive(bar(QB_PREADY));
+      mbar_arrive(bar(QB_PREADY0 + t));
     }
     if (ok && mbar_wait(bar(QB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
@@ -520,14 +545,14 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// A [B, H, T, dh] view (any batch / head / time strides, dh contiguous) as a 4-D tensor map whose tiles are 128 time steps of one head.
-ojc_status make_map(ojc_backend* be, const char* op, CUtensorMap* map, const ojc_tensor* t, bool h_first) {
+// A [B, H, T, dh] view (any batch / head / time strides, dh contiguous) as a 4-D tensor map whose tiles are `rows` time steps of one head.
+ojc_status make_map(ojc_backend* be, const char* op, CUtensorMap* map, const ojc_tensor* t, bool h_first, uint32_t rows = 128) {
   const uint64_t B = t->shape[0], H = t->shape[1], T = t->shape[2], dh = t->shape[3];
   cuuint64_t gdim[4], gstride[3];
   cuuint32_t box[4], estride[4] = {1, 1, 1, 1};
   gdim[0] = dh; box[0] = (cuuint32_t)dh;
-  if (h_first) { gdim[1] = H; gstride[0] = t->stride[1] * 2; box[1] = 1; gdim[2] = T; gstride[1] = t->stride[2] * 2; box[2] = 128; }
-  else { gdim[1] = T; gstride[0] = t->stride[2] * 2; box[1] = 128; gdim[2] = H; gstride[1] = t->stride[1] * 2; box[2] = 1; }
+  if (h_first) { gdim[1] = H; gstride[0] = t->stride[1] * 2; box[1] = 1; gdim[2] = T; gstride[1] = t->stride[2] * 2; box[2] = rows; }
+  else { gdim[1] = T; gstride[0] = t->stride[2] * 2; box[1] = rows; gdim[2] = H; gstride[1] = t->stride[1] * 2; box[2] = 1; }
   gdim[3] = B; gstride[2] = t->stride[0] * 2; box[3] = 1;
   CUresult r = ((EncodeTiledFn)be->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t->data, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -573,11 +598,16 @@ ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc
                                  ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, const float* dr) {
   const char* op = "causal_sdpa_backward";
   const bool hf = q->stride[1] < q->stride[2];
-  CUtensorMap mq, mk, mv, mg;
+  // whole 128-row tiles for the operand a CTA keeps, 64-row tiles for the one it walks
+  CUtensorMap mq, mk, mv, mg, mq_s, mk_s, mv_s, mg_s;
   OJC_TRY(make_map(be, op, &mq, q, hf));
   OJC_TRY(make_map(be, op, &mk, k, hf));
   OJC_TRY(make_map(be, op, &mv, v, hf));
   OJC_TRY(make_map(be, op, &mg, gout, hf));
+  OJC_TRY(make_map(be, op, &mq_s, q, hf, SUB));
+  OJC_TRY(make_map(be, op, &mk_s, k, hf, SUB));
+  OJC_TRY(make_map(be, op, &mv_s, v, hf, SUB));
+  OJC_TRY(make_map(be, op, &mg_s, gout, hf, SUB));
   static bool attr = false;
   if (!attr) {
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM_BYTES), op);
@@ -589,11 +619,11 @@ ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc
   a.g0 = SdpaView<bf16>{(bf16*)gk->data, gk->stride[0], gk->stride[1], gk->stride[2]};
   a.g1 = SdpaView<bf16>{(bf16*)gv->data, gv->stride[0], gv->stride[1], gv->stride[2]};
   dim3 grid_k((d.time + BN - 1) / BN, d.batch * d.kv_heads);
-  sdpa_bwd_dkv_tcgen05_kernel<<<grid_k, BWD_THREADS, KV_SMEM_BYTES, be->stream>>>(mq, mk, mv, mg, a);
+  sdpa_bwd_dkv_tcgen05_kernel<<<grid_k, BWD_THREADS, KV_SMEM_BYTES, be->stream>>>(mq_s, mk, mv, mg_s, a);
   OJC_LAUNCHED(be, op);
   a.g0 = SdpaView<bf16>{(bf16*)gq->data, gq->stride[0], gq->stride[1], gq->stride[2]};
   dim3 grid_q((d.time + BM - 1) / BM, d.batch * d.heads);
-  sdpa_bwd_dq_tcgen05_kernel<<<grid_q, BWD_THREADS, DQ_SMEM_BYTES, be->stream>>>(mq, mk, mv, mg, a);
+  sdpa_bwd_dq_tcgen05_kernel<<<grid_q, BWD_THREADS, DQ_SMEM_BYTES, be->stream>>>(mq, mk_s, mv_s, mg, a);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }

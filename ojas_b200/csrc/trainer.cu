@@ -41,9 +41,10 @@ ojc_tensor T4(void* p, int32_t dt, int64_t a, int64_t b, int64_t c, int64_t d) {
   t.stride[3] = 1; t.stride[2] = d; t.stride[1] = c * d; t.stride[0] = b * c * d; return t;
 }
 // [B,T,H,dh] storage seen as [B,H,T,dh]
-ojc_tensor TBHTD(void* p, int32_t dt, int64_t b, int64_t t, int64_t h, int64_t d) {
+ojc_tensor TBHTD(void* p, int32_t dt, int64_t b, int64_t t, int64_t h, int64_t d, int64_t token_stride = 0) {
+  const int64_t ts = token_stride ? token_stride : h * d;   // a column slice of a wider [tokens, ld] buffer keeps its row stride
   ojc_tensor x{}; x.data = p; x.dtype = dt; x.rank = 4; x.shape[0] = b; x.shape[1] = h; x.shape[2] = t; x.shape[3] = d;
-  x.stride[0] = t * h * d; x.stride[1] = d; x.stride[2] = h * d; x.stride[3] = 1; return x;
+  x.stride[0] = t * ts; x.stride[1] = d; x.stride[2] = ts; x.stride[3] = 1; return x;
 }
 
 }  // namespace
@@ -68,6 +69,10 @@ struct ojc_trainer {
   float* gate_gw = nullptr;                     // [gate_ld, d] padded weight gradient
   int gate_ld = 0;                              // 0: the gate runs on the per-row kernels
   bool fused_qk = false;
+  // bf16 tier: q/k/v come from one GEMM over the adjacent weight slots [q_proj; k_proj; v_proj] and ffn gate/up from one over
+  // [gate; up]; the consumers read column slices with these row strides (0: separate buffers)
+  bool fused_lin = false;
+  int64_t ld_qkv = 0, ld_au = 0;
   uint64_t step = 0;
   bool poisoned = false, grads_ready = false;
   struct Bucket { int64_t offset, floats; int first_param; cudaEvent_t ready; bool recorded; };
@@ -160,12 +165,18 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
     ojc_tensor x = T2(a.x, OJC_F32, N, d), h = T2(a.h, A, N, d);
     ojc_tensor n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d);
     OJC_TRY(rms_forward_impl(be, &x, &n1, eps, &h));
-    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, qw, nullptr));
-    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_K)), A, a.k, A, N, d, kvw, nullptr));
-    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_V)), A, a.rawv, A, N, d, kvw, nullptr));
+    const bool fl = tr->fused_lin;
+    const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;   // token strides of q and of k / raw v
+    if (fl) {
+      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, tr->ld_qkv, nullptr));
+    } else {
+      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, qw, nullptr));
+      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_K)), A, a.k, A, N, d, kvw, nullptr));
+      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_V)), A, a.rawv, A, N, d, kvw, nullptr));
+    }
     if (tr->fused_qk) {
-      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.q, qw, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (bf16*)a.qr, qw, N, (int)H, (int)dh, (int)T, eps));
-      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.k, kvw, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (bf16*)a.kr, kvw, N, (int)Hkv, (int)dh, (int)T, eps));
+      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.q, sq, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (bf16*)a.qr, qw, N, (int)H, (int)dh, (int)T, eps));
+      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.k, skv, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (bf16*)a.kr, kvw, N, (int)Hkv, (int)dh, (int)T, eps));
     } else {
       ojc_tensor q = T2(a.q, A, N * H, dh), qn = T2(tr->qn, A, N * H, dh), qnw = T1(tr->W(tr->P(l, P_QN)), OJC_F32, dh);
       ojc_tensor k = T2(a.k, A, N * Hkv, dh), kn = T2(tr->kn, A, N * Hkv, dh), knw = T1(tr->W(tr->P(l, P_KN)), OJC_F32, dh);
@@ -175,12 +186,15 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
       OJC_TRY(rope_impl(be, "rope_half_split_forward", &qn4, &cos_t, &sin_t, &qr4, 0));
       OJC_TRY(rope_impl(be, "rope_half_split_forward", &kn4, &cos_t, &sin_t, &kr4, 0));
     }
-    if (l > 0) {
+    if (l > 0 && fl) {
+      OJC_TRY(vres_rows_forward(be, (const bf16*)a.rawv, skv, (const bf16*)tr->acts[0].rawv, skv, tr->W(tr->P(l, P_LAMBDA)), (bf16*)a.v, N, kvw));
+    } else if (l > 0) {
       ojc_tensor rv = T1(a.rawv, A, N * kvw), v0 = T1(tr->acts[0].rawv, A, N * kvw), lam = T1(tr->W(tr->P(l, P_LAMBDA)), OJC_F32, 1), v = T1(a.v, A, N * kvw);
       OJC_TRY(ojc_value_residual_blend_forward(be, &rv, &v0, &lam, &v));
     }
     {
-      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), v = TBHTD(l > 0 ? a.v : a.rawv, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+      ojc_tensor v = l > 0 ? TBHTD(a.v, A, B, T, Hkv, dh) : TBHTD(a.rawv, A, B, T, Hkv, dh, skv);
       ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
       lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
       OJC_TRY(ojc_causal_sdpa_forward(be, &q, &k, &v, s.window, &y, &lse));
@@ -199,6 +213,12 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
     {
       ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), h2 = T2(a.h2, A, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d);
       OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2));
+    }
+    if (fl) {
+      OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, tr->ld_au, nullptr));
+      OJC_TRY(swiglu_rows_forward(be, (const bf16*)a.a, tr->ld_au, (bf16*)a.m, N, F));
+      OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, a.x1));
+      continue;
     }
     OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, F, nullptr));
     OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FU)), A, a.u, A, N, d, F, nullptr));
@@ -259,7 +279,10 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     // x2 = x1 + down(m)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
     OJC_TRY(linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false));
-    if ((N * F) % 4 == 0) OJC_TRY(swiglu_backward_impl(be, a.a, a.u, tr->g_m, tr->g_a, tr->g_u, A, N * F));
+    const bool fl = tr->fused_lin;
+    const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;
+    if (fl) OJC_TRY(swiglu_rows_backward(be, (const bf16*)a.a, (const bf16*)tr->g_m, (bf16*)tr->g_a, tr->ld_au, N, F));
+    else if ((N * F) % 4 == 0) OJC_TRY(swiglu_backward_impl(be, a.a, a.u, tr->g_m, tr->g_a, tr->g_u, A, N * F));
     else {
       ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), gm = T1(tr->g_m, A, N * F), ga = T1(tr->g_a, A, N * F), gu = T1(tr->g_u, A, N * F);
       ojc_tensor sil = T1(a.m, A, N * F);  // silu(a) recomputed into the slot of m, which is no longer needed
@@ -267,10 +290,15 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       OJC_TRY(ojc_mul_backward(be, &sil, &tu, &gm, &ga, &gu));  // ga = g_silu for now
       OJC_TRY(ojc_silu_backward(be, &ta, &ga, &ga));
     }
-    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FU)), A, tr->g_u, A, tr->g_h2, OJC_F32, N, d, F, false));
-    OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_u, A, tr->G(tr->P(l, P_FU)), N, d, F, false));
-    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FG)), A, tr->g_a, A, tr->g_h2, OJC_F32, N, d, F, true));
-    OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, F, false));
+    if (fl) {
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FG)), A, tr->g_a, A, tr->g_h2, OJC_F32, N, d, tr->ld_au, false));
+      OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, tr->ld_au, false));
+    } else {
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FU)), A, tr->g_u, A, tr->g_h2, OJC_F32, N, d, F, false));
+      OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_u, A, tr->G(tr->P(l, P_FU)), N, d, F, false));
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FG)), A, tr->g_a, A, tr->g_h2, OJC_F32, N, d, F, true));
+      OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, F, false));
+    }
     {
       ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d), gy = T2(tr->g_h2, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn2 = T1(tr->G(tr->P(l, P_NORM2)), OJC_F32, d);
@@ -292,14 +320,24 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       OJC_TRY(gate_backward_impl(be, &h, &gw, &gb, &y, &gyg, &sc, &gh, tr->G(tr->P(l, P_GW)), tr->G(tr->P(l, P_GB)), &gy, false));
     }
     {
-      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), v = TBHTD(l > 0 ? a.v : a.rawv, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+      ojc_tensor v = l > 0 ? TBHTD(a.v, A, B, T, Hkv, dh) : TBHTD(a.rawv, A, B, T, Hkv, dh, skv);
       ojc_tensor gy = TBHTD(tr->g_y, A, B, T, H, dh), gq = TBHTD(tr->g_qr, A, B, T, H, dh), gk = TBHTD(tr->g_kr, A, B, T, Hkv, dh), gv = TBHTD(tr->g_v, A, B, T, Hkv, dh);
       ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
       lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
       OJC_TRY(ojc_causal_sdpa_backward(be, &q, &k, &v, &y, &lse, &gy, s.window, &gq, &gk, &gv));
     }
     const void* g_rawv = tr->g_v;
-    if (l > 0) {
+    if (fl) {
+      if (l > 0) {
+        OJC_TRY(vres_rows_backward(be, (const bf16*)a.rawv, skv, (const bf16*)tr->acts[0].rawv, skv, tr->W(tr->P(l, P_LAMBDA)), (const bf16*)tr->g_v,
+                                   (bf16*)tr->g_rawv, skv, tr->gv0_acc, !have_v0, tr->G(tr->P(l, P_LAMBDA)), N, kvw));
+        have_v0 = true;
+      } else {
+        OJC_TRY(vres_root_backward(be, have_v0 ? tr->gv0_acc : nullptr, (const bf16*)tr->g_v, (bf16*)tr->g_rawv, skv, N, kvw));
+      }
+      g_rawv = tr->g_rawv;
+    } else if (l > 0) {
       ojc_tensor rv = T1(a.rawv, A, N * kvw), v0 = T1(tr->acts[0].rawv, A, N * kvw), lam = T1(tr->W(tr->P(l, P_LAMBDA)), OJC_F32, 1), gv = T1(tr->g_v, A, N * kvw);
       ojc_tensor grv = T1(tr->g_rawv, A, N * kvw), gv0 = T1(tr->g_v0l, A, N * kvw);
       OJC_TRY(vres_backward_impl(be, &rv, &v0, &lam, &gv, &grv, &gv0, tr->G(tr->P(l, P_LAMBDA)), false));
@@ -314,9 +352,9 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       g_rawv = tr->g_rawv;
     }
     if (tr->fused_qk) {
-      OJC_TRY(qk_norm_rope_backward(be, (const bf16*)a.k, kvw, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (const bf16*)tr->g_kr, kvw, (bf16*)tr->g_k, kvw,
+      OJC_TRY(qk_norm_rope_backward(be, (const bf16*)a.k, skv, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (const bf16*)tr->g_kr, kvw, (bf16*)tr->g_k, skv,
                                     tr->G(tr->P(l, P_KN)), N, (int)Hkv, (int)dh, (int)T, eps));
-      OJC_TRY(qk_norm_rope_backward(be, (const bf16*)a.q, qw, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (const bf16*)tr->g_qr, qw, (bf16*)tr->g_q, qw,
+      OJC_TRY(qk_norm_rope_backward(be, (const bf16*)a.q, sq, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (const bf16*)tr->g_qr, qw, (bf16*)tr->g_q, sq,
                                     tr->G(tr->P(l, P_QN)), N, (int)H, (int)dh, (int)T, eps));
     } else {
       ojc_tensor gkr = T4(tr->g_kr, A, B, T, Hkv, dh), gkn = T4(tr->g_kn, A, B, T, Hkv, dh), gqr = T4(tr->g_qr, A, B, T, H, dh), gqn = T4(tr->g_qn, A, B, T, H, dh);
@@ -329,12 +367,18 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       ojc_tensor gqnw = T1(tr->G(tr->P(l, P_QN)), OJC_F32, dh);
       OJC_TRY(rms_backward_impl(be, &q, &qnw, &gqn2, eps, &gq, &gqnw, false, false));
     }
-    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_V)), A, g_rawv, A, tr->g_h, OJC_F32, N, d, kvw, true));
-    OJC_TRY(linear_backward_weight_impl(be, a.h, A, g_rawv, A, tr->G(tr->P(l, P_V)), N, d, kvw, false));
-    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_K)), A, tr->g_k, A, tr->g_h, OJC_F32, N, d, kvw, true));
-    OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_k, A, tr->G(tr->P(l, P_K)), N, d, kvw, false));
-    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_Q)), A, tr->g_q, A, tr->g_h, OJC_F32, N, d, qw, true));
-    OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, qw, false));
+    if (fl) {
+      // d/dh += [gq | gk | gv] . [Wq; Wk; Wv], and the three weight gradients as one [ld_qkv, d] block
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_Q)), A, tr->g_q, A, tr->g_h, OJC_F32, N, d, tr->ld_qkv, true));
+      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, tr->ld_qkv, false));
+    } else {
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_V)), A, g_rawv, A, tr->g_h, OJC_F32, N, d, kvw, true));
+      OJC_TRY(linear_backward_weight_impl(be, a.h, A, g_rawv, A, tr->G(tr->P(l, P_V)), N, d, kvw, false));
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_K)), A, tr->g_k, A, tr->g_h, OJC_F32, N, d, kvw, true));
+      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_k, A, tr->G(tr->P(l, P_K)), N, d, kvw, false));
+      OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_Q)), A, tr->g_q, A, tr->g_h, OJC_F32, N, d, qw, true));
+      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, qw, false));
+    }
     {
       ojc_tensor x = T2(a.x, OJC_F32, N, d), n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn1 = T1(tr->G(tr->P(l, P_NORM1)), OJC_F32, d);
@@ -384,22 +428,41 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
   if (tr->act_dt == OJC_BF16) { TAKE(tr->mirror, tr->flat_n * 2); }
   for (float* p : {tr->w, tr->g, tr->m1, tr->m2}) if ((st = ojc_fill_zero(be, p, (uint64_t)tr->flat_n * 4)) != OJC_OK) return fail(st);
   if (tr->mirror && (st = ojc_fill_zero(be, tr->mirror, (uint64_t)tr->flat_n * 2)) != OJC_OK) return fail(st);
+  if (tr->act_dt == OJC_BF16) {
+    tr->fused_qk = qk_norm_rope_supported((int)dh) && qw % 8 == 0 && kvw % 8 == 0;
+    // the concatenated-weight GEMMs need the q/k/v (gate/up) slots back to back, i.e. no 64-float slot padding between them
+    tr->fused_lin = tr->fused_qk && F % 8 == 0 && d % 8 == 0 && (qw * d) % 64 == 0 && (kvw * d) % 64 == 0 && (F * d) % 64 == 0;
+    if (tr->fused_lin) { tr->ld_qkv = qw + 2 * kvw; tr->ld_au = 2 * F; }
+  }
+  const bool fl = tr->fused_lin;
   tr->acts.resize(L);
   for (int64_t l = 0; l < L; ++l) {
     LayerActs& a = tr->acts[l];
     TAKE(a.x, N * d * 4); TAKE(a.x1, N * d * 4); TAKE(a.lse, tr->B * H * tr->T * 4); TAKE(a.scales, N * H * 4);
-    TAKE(a.h, N * d * es); TAKE(a.q, N * qw * es); TAKE(a.k, N * kvw * es); TAKE(a.rawv, N * kvw * es); TAKE(a.qr, N * qw * es); TAKE(a.kr, N * kvw * es);
+    TAKE(a.h, N * d * es); TAKE(a.qr, N * qw * es); TAKE(a.kr, N * kvw * es);
+    if (fl) {
+      TAKE(a.q, N * tr->ld_qkv * es); a.k = (bf16*)a.q + qw; a.rawv = (bf16*)a.q + qw + kvw;
+      TAKE(a.a, N * tr->ld_au * es); a.u = (bf16*)a.a + F;
+    } else {
+      TAKE(a.q, N * qw * es); TAKE(a.k, N * kvw * es); TAKE(a.rawv, N * kvw * es); TAKE(a.a, N * F * es); TAKE(a.u, N * F * es);
+    }
     a.v = nullptr;
     if (l > 0) { TAKE(a.v, N * kvw * es); }
-    TAKE(a.y, N * qw * es); TAKE(a.yg, N * qw * es); TAKE(a.h2, N * d * es); TAKE(a.a, N * F * es); TAKE(a.u, N * F * es); TAKE(a.m, N * F * es);
+    TAKE(a.y, N * qw * es); TAKE(a.yg, N * qw * es); TAKE(a.h2, N * d * es); TAKE(a.m, N * F * es);
   }
   TAKE(tr->x_final, N * d * 4); TAKE(tr->gx, N * d * 4); TAKE(tr->g_h, N * d * 4); TAKE(tr->g_h2, N * d * 4); TAKE(tr->gv0_acc, N * kvw * 4); TAKE(tr->stats, 256);
-  TAKE(tr->hf, N * d * es); TAKE(tr->gx_b, N * d * 2); TAKE(tr->g_m, N * F * es); TAKE(tr->g_a, N * F * es); TAKE(tr->g_u, N * F * es);
+  TAKE(tr->hf, N * d * es); TAKE(tr->gx_b, N * d * 2); TAKE(tr->g_m, N * F * es);
   TAKE(tr->g_yg, N * qw * es); TAKE(tr->g_y, N * qw * es); TAKE(tr->g_qr, N * qw * es); TAKE(tr->g_kr, N * kvw * es); TAKE(tr->g_v, N * kvw * es);
-  TAKE(tr->g_qn, N * qw * es); TAKE(tr->g_kn, N * kvw * es); TAKE(tr->g_q, N * qw * es); TAKE(tr->g_k, N * kvw * es); TAKE(tr->g_rawv, N * kvw * es);
-  TAKE(tr->g_v0l, N * kvw * es); TAKE(tr->qn, N * qw * es); TAKE(tr->kn, N * kvw * es);
+  if (fl) {
+    TAKE(tr->g_a, N * tr->ld_au * es); tr->g_u = (bf16*)tr->g_a + F;
+    TAKE(tr->g_q, N * tr->ld_qkv * es); tr->g_k = (bf16*)tr->g_q + qw; tr->g_rawv = (bf16*)tr->g_q + qw + kvw;
+  } else {
+    TAKE(tr->g_a, N * F * es); TAKE(tr->g_u, N * F * es);
+    TAKE(tr->g_q, N * qw * es); TAKE(tr->g_k, N * kvw * es); TAKE(tr->g_rawv, N * kvw * es);
+  }
+  if (!tr->fused_qk) { TAKE(tr->g_qn, N * qw * es); TAKE(tr->g_kn, N * kvw * es); TAKE(tr->qn, N * qw * es); TAKE(tr->kn, N * kvw * es); }
+  if (!fl) { TAKE(tr->g_v0l, N * kvw * es); }
   if (tr->act_dt == OJC_BF16) {
-    tr->fused_qk = qk_norm_rope_supported((int)dh) && qw % 8 == 0 && kvw % 8 == 0;
     const int64_t ld = (H + 7) & ~int64_t(7);
     const Param& gwp = tr->P(0, P_GW);
     const bool per_ok = dh % 8 == 0 && (dh / 8) <= 32 && (((dh / 8) & ((dh / 8) - 1)) == 0);
