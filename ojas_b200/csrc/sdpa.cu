@@ -226,6 +226,11 @@ ojc_status sdpa_backward_f32tier(ojc_backend* be, const ojc_tensor* q, const ojc
   });
 }
 
+// 16-byte row loads: aligned base and strides
+static bool strides_ok_for_rows(const ojc_tensor* t) {
+  return (reinterpret_cast<uintptr_t>(t->data) & 15) == 0 && t->stride[3] == 1 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 && t->stride[2] % 8 == 0;
+}
+
 static ojc_status like(const char* op, const char* what, const ojc_tensor* t, const ojc_tensor* ref) {
   OJC_TRY(check_tensor(op, what, t, false));
   if (!same_shape(t, ref) || t->dtype != ref->dtype || t->stride[3] != 1) return ojc_fail(OJC_ERR_SHAPE, op, std::string(what) + " must match its operand (contiguous head_dim)");
@@ -260,11 +265,9 @@ ojc_status ojc_causal_sdpa_backward(ojc_backend* be, const ojc_tensor* q, const 
   OJC_TRY(check_tensor(op, "lse", lse));
   if (lse->dtype != OJC_F32 || numel(lse) != (int64_t)d.batch * d.heads * d.time) return ojc_fail(OJC_ERR_SHAPE, op, "lse must be F32 [B,H,T]");
   void* dr = nullptr;
-  OJC_TRY(ojc_scratch(be, (uint64_t)d.batch * d.heads * d.time * 4, &dr));
-  if (sdpa_tcgen05_bwd_eligible(be, q, k, v, gout, gq, gk, gv, window, d) && out->dtype == OJC_BF16 && out->stride[3] == 1) {
-    OJC_TRY(sdpa_dr(be, out, gout, (float*)dr, d));
-    return sdpa_backward_tcgen05(be, q, k, v, (const float*)lse->data, gout, gq, gk, gv, d, (const float*)dr);
-  }
+  OJC_TRY(ojc_scratch(be, (uint64_t)d.batch * d.heads * d.time * 8, &dr));   // Dr, and room for the tcgen05 path's scaled lse
+  if (sdpa_tcgen05_bwd_eligible(be, q, k, v, gout, gq, gk, gv, window, d) && out->dtype == OJC_BF16 && strides_ok_for_rows(out) && strides_ok_for_rows(gout))
+    return sdpa_backward_tcgen05(be, q, k, v, out, (const float*)lse->data, gout, gq, gk, gv, d, (float*)dr);
   if (sdpa_tc_eligible(q, k, v, out, d)) return sdpa_backward_tc(be, q, k, v, out, (const float*)lse->data, gout, window, gq, gk, gv, d, (float*)dr);
   return sdpa_backward_f32tier(be, q, k, v, out, (const float*)lse->data, gout, window, gq, gk, gv, d, (float*)dr);
 }

@@ -27,6 +27,6 @@ bool sdpa_tcgen05_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tenso
 ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, ojc_tensor* out, float* lse, const SdpaDims& d);
 bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* gout, const ojc_tensor* gq,
                                const ojc_tensor* gk, const ojc_tensor* gv, int64_t window, const SdpaDims& d);
-ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const float* lse, const ojc_tensor* gout,
-                                 ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, const float* dr);
+ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
+                                 const ojc_tensor* gout, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* work);
 ojc_status sdpa_dr(ojc_backend* be, const ojc_tensor* out, const ojc_tensor* gout, float* dr, const SdpaDims& d);

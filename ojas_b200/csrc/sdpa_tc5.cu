@@ -23,6 +23,8 @@ constexpr int SMEM_BYTES = OFF_BAR + 128;                     // 112 KB + barrie
 constexpr int NTHREADS = 192, BWD_THREADS = 320;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_STEP = 8.0f;                          // log2 units the row maximum may run ahead of the scale in use
+constexpr uint32_t HI = desc_hi(1024);                        // every operand here: 8-row groups 1024 bytes apart
+constexpr uint32_t KSTEP = 32 >> 4, MNSTEP = 2048 >> 4, TILE16 = TILE_BYTES >> 4;   // descriptor low-word increments
 enum { B_QFULL = 0, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL, B_PREADY, B_PVFULL, B_COUNT };
 
 struct FwdArgs {
@@ -70,12 +72,13 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // A failed wait has already set the abort flag, which every other wait polls: the loops need no check of their own.
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer: Q, then (K, V) pairs two blocks ahead
     if (lane == 0) {
       mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
       load_tile(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
-      for (int j = 0; j < nblocks && !*abort_flag; ++j) {
+      for (int j = 0; j < nblocks; ++j) {
         const int s = j & 1;
         if (!mbar_wait(bar(B_KVEMPTY0 + s), ((j >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
         mbar_expect_tx(bar(B_KVFULL0 + s), 2 * TILE_BYTES);
@@ -87,25 +90,24 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BM, BN, 0, 0), idesc_pv = make_idesc(BM, D, 0, 1);
+      // descriptor low words: K-major operands step 32 bytes per MMA, the MN-major V steps 16 keys = 2048 bytes
+      const uint32_t q_lo = desc_lo(base + OFF_Q, 0), k_lo = desc_lo(base + OFF_K, 0), p_lo = desc_lo(base + OFF_P, 0), v_lo = desc_lo(base + OFF_V, 1024);
       bool ok = mbar_wait(bar(B_QFULL), 0, args.fault, abort_flag);
-      for (int j = 0; j < nblocks && ok && !*abort_flag; ++j) {
-        const int s = j & 1;
+      for (int j = 0; j < nblocks && ok; ++j) {
+        const uint32_t s = j & 1;
         if (!mbar_wait(bar(B_KVFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) break;
         fence_after();
-        // S = Q K^T: both operands K-major rows of 128 bytes, 8-row groups 1024 bytes apart, one step = 32 bytes.
-        // The S columns are free: every softmax thread arrived on B_PREADY for block j - 1 after its last S read.
+        // S = Q K^T. The S columns are free: every softmax thread arrived on B_PREADY for block j - 1 after its last S read.
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma(tmem_base, make_desc(base + OFF_Q + kk * 32, 0, 1024), make_desc(base + OFF_K + s * TILE_BYTES + kk * 32, 0, 1024), idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base, q_lo + kk * KSTEP, k_lo + s * TILE16 + kk * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(B_SFULL));
         if (!mbar_wait(bar(B_PREADY), j & 1, args.fault, abort_flag)) break;
         fence_after();
-        // O += P V: P is two K-major halves of 64 keys (16 KB apart); V is MN-major (one 64-wide block), 16 keys = 2048 bytes.
+        // O += P V: P is two K-major halves of 64 keys (16 KB apart); V is MN-major (one 64-wide block).
         // O stays in TMEM for the whole walk; the softmax rows rescale it in place when their maximum moves.
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma(tmem_base + 128, make_desc(base + OFF_P + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 0, 1024),
-               make_desc(base + OFF_V + s * TILE_BYTES + kk * 2048, 1024, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        for (uint32_t kk = 0; kk < BN / 16; ++kk)
+          umma_lh(tmem_base + 128, p_lo + (kk >> 2) * TILE16 + (kk & 3) * KSTEP, v_lo + s * TILE16 + kk * MNSTEP, HI, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(B_KVEMPTY0 + s));
         umma_commit(bar(B_PVFULL));
       }
@@ -119,7 +121,7 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     float m = 0.0f, l = 0.0f;                     // m: the maximum the probabilities are scaled by (log2 domain), set by block 0
     uint8_t* p_row = base_ptr + OFF_P + tid * 128;
     bool ok = true;
-    for (int j = 0; j < nblocks && ok && !*abort_flag; ++j) {
+    for (int j = 0; j < nblocks; ++j) {
       if (!mbar_wait(bar(B_SFULL), j & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
       const int key0 = j * BN;
@@ -215,25 +217,47 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 }
 
 // ================================================================================================ backward
-// Two kernels, each recomputing P from lse (no atomics, one writer per gradient element):
-//   dK/dV: a CTA owns 128 keys and walks the query blocks that see them; S^T = K Q^T and dP^T = V dO^T land in TMEM,
-//          the 128 threads (one per key) form P^T and dS^T and write them as swizzled bf16 A operands, and
+// A prepass writes Dr = rowsum(dO . O) and lse * log2(e); then two kernels, each recomputing P from lse (no atomics,
+// one writer per gradient element):
+//   dK/dV: a CTA owns 128 keys and walks the queries that see them; S^T = K Q^T and dP^T = V dO^T land in TMEM,
+//          the threads (one key row each) form P^T and dS^T and write them as swizzled bf16 A operands, and
 //          dV += P^T dO, dK += dS^T Q accumulate in TMEM across the whole walk (query heads of a GQA group included).
-//   dQ:    a CTA owns 128 queries and walks the key blocks: S = Q K^T, dP = dO V^T, dS -> shared memory, dQ += dS K in TMEM.
+//   dQ:    a CTA owns 128 queries and walks the keys: S = Q K^T, dP = dO V^T, dS -> shared memory, dQ += dS K in TMEM.
+// Both walk in steps of SUB = 64 with the S / dP accumulators double-buffered in TMEM, so the tensor pipe forms step
+// i + 1 while the eight compute warps turn step i into P and dS. dS is kept unscaled; the softmax scale multiplies
+// dK and dQ once, on the way out.
 struct BwdArgs {
   SdpaView<bf16> g0, g1;          // dK, dV  or  dQ (g1 unused)
-  const float* lse;
+  const float* lse2;              // lse * log2(e)
   const float* dr;
   int heads, kv_heads, time, h_first;
   float scale;
   uint32_t* fault;
 };
 
+// Dr[b,h,t] = sum_d dO . O and lse2 = lse * log2(e): eight threads per row, 16-byte loads.
+__global__ void sdpa_bwd_prep_kernel(SdpaView<const bf16> out, SdpaView<const bf16> gout, const float* __restrict__ lse, float* __restrict__ dr,
+                                     float* __restrict__ lse2, int heads, int time, int64_t rows) {
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = min(gid >> 3, rows - 1);
+  const int part = (int)(gid & 7);
+  const int t = (int)(r % time), h = (int)((r / time) % heads), b = (int)(r / ((int64_t)time * heads));
+  const uint4 o = *reinterpret_cast<const uint4*>(out.row(b, h, t) + part * 8), g = *reinterpret_cast<const uint4*>(gout.row(b, h, t) + part * 8);
+  const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, gw[4] = {g.x, g.y, g.z, g.w};
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    acc += __uint_as_float(ow[i] << 16) * __uint_as_float(gw[i] << 16) + __uint_as_float(ow[i] & 0xffff0000u) * __uint_as_float(gw[i] & 0xffff0000u);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1); acc += __shfl_xor_sync(0xffffffffu, acc, 2); acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (part == 0 && (gid >> 3) < rows) { dr[r] = acc; lse2[r] = lse[r] * LOG2E; }
+}
+
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// COLS accumulator columns of this thread's TMEM lane -> bf16, scaled
 template <int COLS>
-__device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr) {
+__device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr, float mul) {
 #pragma unroll
   for (int c = 0; c < COLS / 32; ++c) {
     uint32_t r[32];
@@ -241,21 +265,43 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr) {
     tmem_wait_ld();
     if (dst) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 8) {
+      for (int i = 0; i < 32; i += 8)
         *reinterpret_cast<uint4*>(dst + c * 32 + i) =
-            make_uint4(pack2_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), pack2_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
-                       pack2_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])), pack2_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
-      }
+            make_uint4(pack2_bf16(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul), pack2_bf16(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul),
+                       pack2_bf16(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul), pack2_bf16(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul));
     }
   }
 }
 
-// Both backward kernels walk their inner dimension in steps of SUB = 64 with the S / dP accumulators double-buffered in
-// TMEM, so the tensor pipe forms step i + 1 while the eight compute warps turn step i into P and dS.
 constexpr int SUB = 64;
 constexpr int SUB_BYTES = SUB * D * 2;         // 8 KB: 64 rows of q / dO (or k / v)
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
 constexpr int IN_STAGES = 4;
+constexpr uint32_t SUB16 = SUB_BYTES >> 4, PT16 = PT_BYTES >> 4;
+
+// One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; l2, dd: the columns' (dK/dV) or
+// the row's (dQ) statistics; vis(e): column e is visible. Writes the 16-byte chunks of P (optional) and dS.
+template <bool MASKED, bool WRITE_P, class L2, class DD, class VIS>
+__device__ __forceinline__ void bwd_step(const uint32_t (&s)[32], const uint32_t (&dp)[32], float sl2, L2&& l2, DD&& dd, VIS&& vis, uint8_t* p_row, uint8_t* ds_row,
+                                         int half, int tid) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float pv[8], dv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = g * 8 + e;
+      const float p = fast_exp2(fmaf(__uint_as_float(s[c]), sl2, -l2(c)));
+      const float ds = p * (__uint_as_float(dp[c]) - dd(c));
+      // masked columns: select, never multiply by zero (rows past the sequence end carry whatever the buffers held)
+      pv[e] = (!MASKED || vis(c)) ? p : 0.0f;
+      dv[e] = (!MASKED || vis(c)) ? ds : 0.0f;
+    }
+    const int ci = half * 4 + g;             // 16-byte chunk of the 128-byte row; the swizzle XORs it with row % 8
+    if (WRITE_P)
+      *reinterpret_cast<uint4*>(p_row + ((ci ^ (tid & 7)) << 4)) = make_uint4(pack2_bf16(pv[0], pv[1]), pack2_bf16(pv[2], pv[3]), pack2_bf16(pv[4], pv[5]), pack2_bf16(pv[6], pv[7]));
+    *reinterpret_cast<uint4*>(ds_row + ((ci ^ (tid & 7)) << 4)) = make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7]));
+  }
+}
 
 // ---- dK, dV
 constexpr int KV_OFF_K = 0, KV_OFF_V = TILE_BYTES, KV_OFF_Q = 2 * TILE_BYTES, KV_OFF_G = KV_OFF_Q + IN_STAGES * SUB_BYTES, KV_OFF_P = KV_OFF_G + IN_STAGES * SUB_BYTES,
@@ -274,7 +320,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   auto bar = [&](int i) { return base + KV_OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + KV_OFF_BAR + 8 * KB_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse 64 | dr 64]
+  const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse2 64 | dr 64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k0 = blockIdx.x * BN;
@@ -302,8 +348,9 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       mbar_expect_tx(bar(KB_KVFULL), 2 * TILE_BYTES);
       load_tile(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
       load_tile(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
-      for (int it = 0; it < iters && !*abort_flag; ++it) {
-        const int s = it % IN_STAGES, h = hk * rep + it / q_subs, q0 = k0 + (it % q_subs) * SUB;
+      int h = hk * rep, q0 = k0;
+      for (int it = 0; it < iters; ++it) {
+        const int s = it % IN_STAGES;
         if (!mbar_wait(bar(KB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
         // the step's row statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
         const uint32_t stat_bytes = (uint32_t)min(SUB, args.time - q0) * 4u;
@@ -311,45 +358,49 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         mbar_expect_tx(bar(KB_INFULL0 + s), 2 * SUB_BYTES + 2 * stat_bytes);
         load_tile(base + KV_OFF_Q + s * SUB_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
         load_tile(base + KV_OFF_G + s * SUB_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
-        bulk_load(base + KV_OFF_STAT + s * 512, args.lse + idx, stat_bytes, bar(KB_INFULL0 + s));
+        bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
         bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
+        q0 += SUB;
+        if (q0 >= args.time) { q0 = k0; ++h; }   // next query head of the group
       }
     }
   } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BN, SUB, 0, 0), idesc_o = make_idesc(BN, D, 0, 1);
+      const uint32_t k_lo = desc_lo(base + KV_OFF_K, 0), v_lo = desc_lo(base + KV_OFF_V, 0), q_lo = desc_lo(base + KV_OFF_Q, 0), g_lo = desc_lo(base + KV_OFF_G, 0);
+      const uint32_t qm_lo = desc_lo(base + KV_OFF_Q, 1024), gm_lo = desc_lo(base + KV_OFF_G, 1024);   // the same tiles as MN-major B operands
+      const uint32_t p_lo = desc_lo(base + KV_OFF_P, 0), ds_lo = desc_lo(base + KV_OFF_DS, 0);
       // S^T = K Q^T and dP^T = V dO^T of step i into TMEM buffer i & 1
-      auto issue_s = [&](int i) {
-        const uint32_t qs = base + KV_OFF_Q + (i % IN_STAGES) * SUB_BYTES, gs = base + KV_OFF_G + (i % IN_STAGES) * SUB_BYTES, tm = tmem_base + (i & 1) * 128;
+      auto issue_s = [&](uint32_t i) {
+        const uint32_t st = (i % IN_STAGES) * SUB16, tm = tmem_base + (i & 1) * 128;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) umma(tm, make_desc(base + KV_OFF_K + kk * 32, 0, 1024), make_desc(qs + kk * 32, 0, 1024), idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm, k_lo + kk * KSTEP, q_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) umma(tm + 64, make_desc(base + KV_OFF_V + kk * 32, 0, 1024), make_desc(gs + kk * 32, 0, 1024), idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm + 64, v_lo + kk * KSTEP, g_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(KB_SFULL0 + (i & 1)));
       };
       bool ok = mbar_wait(bar(KB_KVFULL), 0, args.fault, abort_flag) && mbar_wait(bar(KB_INFULL0), 0, args.fault, abort_flag);
       if (ok) { fence_after(); issue_s(0); }
-      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
-        if (it + 1 < iters) {
+      for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
+        if (it + 1 < (uint32_t)iters) {
           // buffer (it + 1) & 1 is free: the compute warps arrived on PREADY of step it - 1 after their last read of it
-          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
           fence_after();
           issue_s(it + 1);
         }
-        if (!mbar_wait(bar(KB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar(KB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t qs = base + KV_OFF_Q + (it % IN_STAGES) * SUB_BYTES, gs = base + KV_OFF_G + (it % IN_STAGES) * SUB_BYTES;
-        const uint32_t ps = base + KV_OFF_P + (it & 1) * PT_BYTES, ds = base + KV_OFF_DS + (it & 1) * PT_BYTES;
+        const uint32_t st = (it % IN_STAGES) * SUB16, pt = (it & 1) * PT16;
 #pragma unroll
-        for (int kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand: 16 queries = 2048 bytes)
-          umma(tmem_base + 256, make_desc(ps + kk * 32, 0, 1024), make_desc(gs + kk * 2048, 1024, 1024), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand: 16 queries = 2048 bytes)
+          umma_lh(tmem_base + 256, p_lo + pt + kk * KSTEP, gm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
-          umma(tmem_base + 320, make_desc(ds + kk * 32, 0, 1024), make_desc(qs + kk * 2048, 1024, 1024), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
+          umma_lh(tmem_base + 320, ds_lo + pt + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(KB_INEMPTY0 + it % IN_STAGES));
         umma_commit(bar(KB_PFREE0 + (it & 1)));
+        if (it + 1 == (uint32_t)iters) umma_commit(bar(KB_DONE));
       }
-      if (ok) umma_commit(bar(KB_DONE));
     }
   } else {
     // two warpgroups share the 128 TMEM lanes (a warp reaches lanes 32 * (warp % 4) ..): group `half` takes 32 of the step's 64 query columns
@@ -357,47 +408,42 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
     bool ok = true;
-    for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
-      const int q0 = k0 + (it % q_subs) * SUB, t = it & 1;
-      const float* st = stat + (it % IN_STAGES) * 128;   // lse[64] | dr[64] of this step, landed with the q / dO tiles
+    int q0 = k0;
+    for (int it = 0; it < iters; ++it) {
+      const int t = it & 1;
+      const float* st = stat + (it % IN_STAGES) * 128 + half * 32;   // lse2[64] | dr[64] of this step, landed with the q / dO tiles
       if (!mbar_wait(bar(KB_SFULL0 + t), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
       // the P / dS buffer of step it - 2 must have been consumed by its dV / dK MMAs
       if (it >= 2 && !mbar_wait(bar(KB_PFREE0 + t), ((it >> 1) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
-      const bool masked = q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time;   // diagonal steps or a ragged end
       uint32_t rs[32], rp[32];
       tmem_ld32(lane_base + t * 128 + half * 32, rs);
       tmem_ld32(lane_base + t * 128 + 64 + half * 32, rp);
+      float l2[32], dd[32];
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(st + c), d4 = *reinterpret_cast<const float4*>(st + SUB + c);
+        l2[c] = a.x; l2[c + 1] = a.y; l2[c + 2] = a.z; l2[c + 3] = a.w; dd[c] = d4.x; dd[c + 1] = d4.y; dd[c + 2] = d4.z; dd[c + 3] = d4.w;
+      }
       tmem_wait_ld();
       uint8_t* p_row = base_ptr + KV_OFF_P + t * PT_BYTES + tid * 128;
       uint8_t* ds_row = base_ptr + KV_OFF_DS + t * PT_BYTES + tid * 128;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        float pv[8], dv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int qc = half * 32 + g * 8 + e;
-          const float p = fast_exp2(fmaf(__uint_as_float(rs[g * 8 + e]), sl2, -st[qc] * LOG2E));
-          const float ds = p * (__uint_as_float(rp[g * 8 + e]) - st[SUB + qc]) * args.scale;
-          // rows past the sequence end carry no statistics (whatever the buffer held): select, never multiply by zero
-          const bool vis = !masked || (key < args.time && q0 + qc < args.time && key <= q0 + qc);
-          pv[e] = vis ? p : 0.0f;
-          dv[e] = vis ? ds : 0.0f;
-        }
-        const int ci = half * 4 + g;             // 16-byte chunk of the 128-byte row; the swizzle XORs it with row % 8
-        *reinterpret_cast<uint4*>(p_row + ((ci ^ (tid & 7)) << 4)) =
-            make_uint4(pack2_bf16(pv[0], pv[1]), pack2_bf16(pv[2], pv[3]), pack2_bf16(pv[4], pv[5]), pack2_bf16(pv[6], pv[7]));
-        *reinterpret_cast<uint4*>(ds_row + ((ci ^ (tid & 7)) << 4)) =
-            make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7]));
-      }
+      const int qb = q0 + half * 32;
+      auto fl2 = [&](int c) { return l2[c]; };
+      auto fdd = [&](int c) { return dd[c]; };
+      auto vis = [&](int c) { return key < args.time && qb + c < args.time && key <= qb + c; };
+      if (q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time) bwd_step<true, true>(rs, rp, sl2, fl2, fdd, vis, p_row, ds_row, half, tid);   // diagonal steps or a ragged end
+      else bwd_step<false, true>(rs, rp, sl2, fl2, fdd, vis, p_row, ds_row, half, tid);
       fence_before();
       fence_async_smem();
       mbar_arrive(bar(KB_PREADY0 + t));
+      q0 += SUB;
+      if (q0 >= args.time) q0 = k0;
     }
     if (ok && mbar_wait(bar(KB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
-      if (half == 0) store_row_bf16<D>(key < args.time ? args.g1.row(b, hk, key) : nullptr, lane_base + 256);   // dV
-      else store_row_bf16<D>(key < args.time ? args.g0.row(b, hk, key) : nullptr, lane_base + 320);             // dK
+      if (half == 0) store_row_bf16<D>(key < args.time ? args.g1.row(b, hk, key) : nullptr, lane_base + 256, 1.0f);     // dV
+      else store_row_bf16<D>(key < args.time ? args.g0.row(b, hk, key) : nullptr, lane_base + 320, args.scale);         // dK
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -454,7 +500,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       mbar_expect_tx(bar(QB_QDFULL), 2 * TILE_BYTES);
       load_tile(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
       load_tile(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
-      for (int it = 0; it < iters && !*abort_flag; ++it) {
+      for (int it = 0; it < iters; ++it) {
         const int s = it % IN_STAGES;
         if (!mbar_wait(bar(QB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
         mbar_expect_tx(bar(QB_INFULL0 + s), 2 * SUB_BYTES);
@@ -465,72 +511,64 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BM, SUB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
-      auto issue_s = [&](int i) {   // S = Q K^T and dP = dO V^T of step i into TMEM buffer i & 1
-        const uint32_t ks = base + DQ_OFF_K + (i % IN_STAGES) * SUB_BYTES, vs = base + DQ_OFF_V + (i % IN_STAGES) * SUB_BYTES, tm = tmem_base + (i & 1) * 128;
+      const uint32_t q_lo = desc_lo(base + DQ_OFF_Q, 0), g_lo = desc_lo(base + DQ_OFF_G, 0), k_lo = desc_lo(base + DQ_OFF_K, 0), v_lo = desc_lo(base + DQ_OFF_V, 0);
+      const uint32_t km_lo = desc_lo(base + DQ_OFF_K, 1024), ds_lo = desc_lo(base + DQ_OFF_DS, 0);
+      auto issue_s = [&](uint32_t i) {   // S = Q K^T and dP = dO V^T of step i into TMEM buffer i & 1
+        const uint32_t st = (i % IN_STAGES) * SUB16, tm = tmem_base + (i & 1) * 128;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) umma(tm, make_desc(base + DQ_OFF_Q + kk * 32, 0, 1024), make_desc(ks + kk * 32, 0, 1024), idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm, q_lo + kk * KSTEP, k_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) umma(tm + 64, make_desc(base + DQ_OFF_G + kk * 32, 0, 1024), make_desc(vs + kk * 32, 0, 1024), idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm + 64, g_lo + kk * KSTEP, v_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(QB_SFULL0 + (i & 1)));
       };
       bool ok = mbar_wait(bar(QB_QDFULL), 0, args.fault, abort_flag) && mbar_wait(bar(QB_INFULL0), 0, args.fault, abort_flag);
       if (ok) { fence_after(); issue_s(0); }
-      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
-        if (it + 1 < iters) {
-          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) { ok = false; break; }
+      for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
+        if (it + 1 < (uint32_t)iters) {
+          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
           fence_after();
           issue_s(it + 1);
         }
-        if (!mbar_wait(bar(QB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar(QB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t ks = base + DQ_OFF_K + (it % IN_STAGES) * SUB_BYTES, ds = base + DQ_OFF_DS + (it & 1) * PT_BYTES;
+        const uint32_t st = (it % IN_STAGES) * SUB16, pt = (it & 1) * PT16;
 #pragma unroll
-        for (int kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
-          umma(tmem_base + 256, make_desc(ds + kk * 32, 0, 1024), make_desc(ks + kk * 2048, 1024, 1024), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
+          umma_lh(tmem_base + 256, ds_lo + pt + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(QB_INEMPTY0 + it % IN_STAGES));
         umma_commit(bar(QB_PFREE0 + (it & 1)));
+        if (it + 1 == (uint32_t)iters) umma_commit(bar(QB_DONE));
       }
-      if (ok) umma_commit(bar(QB_DONE));
     }
   } else {
     const int tid = threadIdx.x & 127, half = warp >> 2, row = q0 + tid;   // warpgroup `half` takes 32 of the step's 64 key columns
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
     const int64_t idx = ((int64_t)b * args.heads + h) * args.time + row;
-    const float lse_row = row < args.time ? args.lse[idx] * LOG2E : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
+    const float lse_row = row < args.time ? args.lse2[idx] : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
     bool ok = true;
-    for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+    for (int it = 0; it < iters; ++it) {
       const int t = it & 1, key0 = it * SUB + half * 32;
       if (!mbar_wait(bar(QB_SFULL0 + t), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
       if (it >= 2 && !mbar_wait(bar(QB_PFREE0 + t), ((it >> 1) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
-      const bool masked = it * SUB + SUB > q0 || it * SUB + SUB > args.time;
       uint32_t rs[32], rp[32];
       tmem_ld32(lane_base + t * 128 + half * 32, rs);
       tmem_ld32(lane_base + t * 128 + 64 + half * 32, rp);
       tmem_wait_ld();
       uint8_t* ds_row = base_ptr + DQ_OFF_DS + t * PT_BYTES + tid * 128;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        float dv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int key = key0 + g * 8 + e;
-          const float p = fast_exp2(fmaf(__uint_as_float(rs[g * 8 + e]), sl2, -lse_row));
-          const bool vis = !masked || (key <= row && key < args.time);
-          dv[e] = vis ? p * (__uint_as_float(rp[g * 8 + e]) - dr_row) * args.scale : 0.0f;
-        }
-        const int ci = half * 4 + g;
-        *reinterpret_cast<uint4*>(ds_row + ((ci ^ (tid & 7)) << 4)) =
-            make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7]));
-      }
+      auto fl2 = [&](int) { return lse_row; };
+      auto fdd = [&](int) { return dr_row; };
+      auto vis = [&](int c) { return key0 + c <= row && key0 + c < args.time; };
+      if (it * SUB + SUB > q0 || it * SUB + SUB > args.time) bwd_step<true, false>(rs, rp, sl2, fl2, fdd, vis, nullptr, ds_row, half, tid);
+      else bwd_step<false, false>(rs, rp, sl2, fl2, fdd, vis, nullptr, ds_row, half, tid);
       fence_before();
       fence_async_smem();
       mbar_arrive(bar(QB_PREADY0 + t));
     }
     if (ok && mbar_wait(bar(QB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
-      store_row_bf16<32>(row < args.time ? args.g0.row(b, h, row) + half * 32 : nullptr, lane_base + 256 + half * 32);
+      store_row_bf16<32>(row < args.time ? args.g0.row(b, h, row) + half * 32 : nullptr, lane_base + 256 + half * 32, args.scale);
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -593,10 +631,16 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
   return OJC_OK;
 }
 
-// Dr = rowsum(dO . O) must already be in `dr`. Eligibility is the forward's plus the gradient views.
-ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const float* lse, const ojc_tensor* gout,
-                                 ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, const float* dr) {
+// `work` holds 2 * B * H * T floats (Dr and lse * log2(e), filled by the prepass). Eligibility is the forward's plus the gradient views.
+ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
+                                 const ojc_tensor* gout, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* work) {
   const char* op = "causal_sdpa_backward";
+  const int64_t rows = (int64_t)d.batch * d.heads * d.time;
+  float *dr = work, *lse2 = work + rows;
+  sdpa_bwd_prep_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, be->stream>>>(
+      SdpaView<const bf16>{(const bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]},
+      SdpaView<const bf16>{(const bf16*)gout->data, gout->stride[0], gout->stride[1], gout->stride[2]}, lse, dr, lse2, d.heads, d.time, rows);
+  OJC_LAUNCHED(be, op);
   const bool hf = q->stride[1] < q->stride[2];
   // whole 128-row tiles for the operand a CTA keeps, 64-row tiles for the one it walks
   CUtensorMap mq, mk, mv, mg, mq_s, mk_s, mv_s, mg_s;
@@ -615,7 +659,7 @@ ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc
     attr = true;
   }
   BwdArgs a;
-  a.lse = lse; a.dr = dr; a.heads = d.heads; a.kv_heads = d.kv_heads; a.time = d.time; a.h_first = hf ? 1 : 0; a.scale = d.scale; a.fault = be->fault_dev;
+  a.lse2 = lse2; a.dr = dr; a.heads = d.heads; a.kv_heads = d.kv_heads; a.time = d.time; a.h_first = hf ? 1 : 0; a.scale = d.scale; a.fault = be->fault_dev;
   a.g0 = SdpaView<bf16>{(bf16*)gk->data, gk->stride[0], gk->stride[1], gk->stride[2]};
   a.g1 = SdpaView<bf16>{(bf16*)gv->data, gv->stride[0], gv->stride[1], gv->stride[2]};
   dim3 grid_k((d.time + BN - 1) / BN, d.batch * d.kv_heads);
