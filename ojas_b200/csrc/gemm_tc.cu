@@ -353,11 +353,19 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   }
   const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
   const int kblocks = (int)((k + BK - 1) / BK);
+  // Split the reduction axis when the output tiles alone leave SMs idle: estimate each split count's time as the math at
+  // the wave efficiency its units reach plus the partial round trip through memory, and take the cheapest (each split
+  // keeps at least 8 k-blocks).
   int splits = 1;
-  if (tiles * 2 <= be->sm_count && kblocks >= 16) {
-    splits = be->sm_count / tiles;
-    if (splits > kblocks / 8) splits = kblocks / 8;
-    if (splits < 1) splits = 1;
+  if (kblocks >= 16) {
+    const double flops = 2.0 * (double)m * (double)n * (double)k;
+    double best = 1e30;
+    for (int sp = 1; sp <= 16 && kblocks / sp >= 8; ++sp) {
+      const int units = tiles * sp, waves = (units + be->sm_count - 1) / be->sm_count;
+      const double eff = (double)units / ((double)waves * be->sm_count);
+      const double t = flops / (1.5e15 * eff) + (sp > 1 ? (double)sp * (double)m * (double)n * 8.0 / 6.0e12 : 0.0);
+      if (t < best * 0.97) { best = t; splits = sp; }
+    }
   }
   int per = (kblocks + splits - 1) / splits;
   splits = (kblocks + per - 1) / per;

@@ -13,9 +13,9 @@ static ojc_status linear_dims(const char* op, const ojc_tensor* x, const ojc_ten
 }
 
 ojc_status linear_forward_impl(ojc_backend* be, const void* x, int32_t x_dt, const void* w, int32_t w_dt, void* y, int32_t y_dt, int64_t rows, int64_t kin,
-                               int64_t nout, const float* residual) {
+                               int64_t nout, const float* residual, bool accumulate) {
   GemmOperand a{x, x_dt, kin, 1}, b{w, w_dt, 1, kin};
-  return gemm_auto(be, "linear_forward", a, b, y, y_dt, nout, rows, nout, kin, 1.0f, false, residual);
+  return gemm_auto(be, "linear_forward", a, b, y, y_dt, nout, rows, nout, kin, 1.0f, accumulate, residual);
 }
 ojc_status linear_backward_input_impl(ojc_backend* be, const void* w, int32_t w_dt, const void* gy, int32_t g_dt, void* gx, int32_t gx_dt, int64_t rows,
                                       int64_t kin, int64_t nout, bool accumulate) {

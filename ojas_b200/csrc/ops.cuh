@@ -4,9 +4,10 @@
 
 ojc_status embedding_backward_impl(ojc_backend* be, const uint32_t* ids, const void* grad, int32_t grad_dtype, float* out, int64_t tokens, int64_t vocab,
                                    int64_t dim, bool accumulate);
-ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, float eps, ojc_tensor* y);
+// copy (optional, F32 rows like x): also receives the input rows
+ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, float eps, ojc_tensor* y, float* copy = nullptr);
 ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, const ojc_tensor* gy, float eps, ojc_tensor* gx, ojc_tensor* gw,
-                             bool accumulate_gw, bool accumulate_gx);
+                             bool accumulate_gw, bool accumulate_gx, bf16* gx_b = nullptr);   // gx_b (optional): a bf16 copy of grad_x
 ojc_status rope_impl(ojc_backend* be, const char* op, const ojc_tensor* x, const ojc_tensor* cos_t, const ojc_tensor* sin_t, ojc_tensor* y, int backward);
 ojc_status vres_backward_impl(ojc_backend* be, const ojc_tensor* v, const ojc_tensor* v0, const ojc_tensor* lambda, const ojc_tensor* gy, ojc_tensor* gv,
                               ojc_tensor* gv0, float* glambda, bool accumulate_lambda);

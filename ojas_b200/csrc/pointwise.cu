@@ -172,7 +172,7 @@ ojc_status embedding_backward_impl(ojc_backend* be, const uint32_t* ids, const v
 // rstd = 1 / sqrt(mean(x^2) + eps)  (ojas-cpu/src/norm.rs:24-56,193-204).
 template <int ITERS, class TX, class TO>
 __global__ void rms_forward_kernel(const TX* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y, int64_t rows,
-                                   int dim, float eps, uint32_t* fault) {
+                                   int dim, float eps, uint32_t* fault, float* __restrict__ copy) {
   const int lane = threadIdx.x & 31;
   int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t rstride = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -190,6 +190,10 @@ __global__ void rms_forward_kernel(const TX* __restrict__ x, const float* __rest
     if (!(isfinite(denom) && denom > 0.0f && isfinite(rstd))) { if (lane == 0) raise_fault(fault, OP_RMS_NORM); }
 #pragma unroll
     for (int j = 0; j < ITERS; ++j) { int c = lane + 32 * j; if (c < dim) stf(y, row * dim + c, xv[j] * rstd * wv[j]); }
+    if (copy) {   // the residual stream's next buffer starts as a copy of this one (the following projection adds into it)
+#pragma unroll
+      for (int j = 0; j < ITERS; ++j) { int c = lane + 32 * j; if (c < dim) copy[row * dim + c] = xv[j]; }
+    }
   }
 }
 
@@ -199,7 +203,7 @@ __global__ void rms_forward_kernel(const TX* __restrict__ x, const float* __rest
 // the partials in block order.
 template <int ITERS, class TX, class TG, class TO>
 __global__ void rms_backward_kernel(const TX* __restrict__ x, const float* __restrict__ w, const TG* __restrict__ gy,
-                                    TO* __restrict__ gx, float* __restrict__ part, int64_t rows, int dim, float eps, int gx_accumulate) {
+                                    TO* __restrict__ gx, float* __restrict__ part, int64_t rows, int dim, float eps, int gx_accumulate, bf16* __restrict__ gx_b) {
   extern __shared__ float smem[];  // [warps][dim]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   int64_t row = (int64_t)blockIdx.x * nwarps + warp;
@@ -230,7 +234,8 @@ __global__ void rms_backward_kernel(const TX* __restrict__ x, const float* __res
       int c = lane + 32 * j;
       float xhat = xv[j] * rstd;
       dw[j] += gv[j] * xhat;
-      if (c < dim) stf(gx, row * dim + c, (gv[j] * wv[j] - xhat * mean) * rstd + old[j]);
+      const float out = (gv[j] * wv[j] - xhat * mean) * rstd + old[j];
+      if (c < dim) { stf(gx, row * dim + c, out); if (gx_b) gx_b[row * dim + c] = __float2bfloat16_rn(out); }   // gx_b: the matmul-operand copy
     }
   }
 #pragma unroll
@@ -274,7 +279,7 @@ template <class F> static ojc_status dispatch_iters(const char* op, int dim, F&&
   return ojc_fail(OJC_ERR_UNSUPPORTED, op, "row width above 2048 is not supported");
 }
 
-ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, float eps, ojc_tensor* y) {
+ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, float eps, ojc_tensor* y, float* copy) {
   const char* op = "rms_norm_forward";
   OJC_ALIVE(be, op);
   OJC_TRY(check_tensor(op, "x", x)); OJC_TRY(check_tensor(op, "weight", w)); OJC_TRY(check_tensor(op, "y", y));
@@ -284,18 +289,19 @@ ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tens
   const int64_t n = numel(x);
   if (n == 0 || dim == 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
   const int64_t rows = n / dim;
+  if (copy && x->dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "the row copy is F32 like its source");
   return dispatch_float(op, x->dtype, [&](auto tx) { return dispatch_float(op, y->dtype, [&](auto to) {
     return dispatch_iters(op, dim, [&](auto it) {
       using TX = decltype(tx); using TO = decltype(to); constexpr int IT = decltype(it)::value;
       int grid = elementwise_grid(be, rows * 32, 256);
-      rms_forward_kernel<IT, TX, TO><<<grid, 256, 0, be->stream>>>((const TX*)x->data, (const float*)w->data, (TO*)y->data, rows, dim, eps, be->fault_dev);
+      rms_forward_kernel<IT, TX, TO><<<grid, 256, 0, be->stream>>>((const TX*)x->data, (const float*)w->data, (TO*)y->data, rows, dim, eps, be->fault_dev, copy);
       OJC_LAUNCHED(be, op);
       return OJC_OK;
     }); }); });
 }
 
 ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* w, const ojc_tensor* gy, float eps,
-                             ojc_tensor* gx, ojc_tensor* gw, bool accumulate_gw, bool accumulate_gx) {
+                             ojc_tensor* gx, ojc_tensor* gw, bool accumulate_gw, bool accumulate_gx, bf16* gx_b) {
   const char* op = "rms_norm_backward";
   OJC_ALIVE(be, op);
   OJC_TRY(check_tensor(op, "x", x)); OJC_TRY(check_tensor(op, "weight", w)); OJC_TRY(check_tensor(op, "grad_y", gy));
@@ -317,7 +323,7 @@ ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_ten
     return dispatch_iters(op, dim, [&](auto it) {
       using TX = decltype(tx); constexpr int IT = decltype(it)::value;
       rms_backward_kernel<IT, TX, TX, TX><<<(unsigned)blocks, warps * 32, warps * dim * 4, be->stream>>>(
-          (const TX*)x->data, (const float*)w->data, (const TX*)gy->data, (TX*)gx->data, (float*)part, rows, dim, eps, accumulate_gx ? 1 : 0);
+          (const TX*)x->data, (const float*)w->data, (const TX*)gy->data, (TX*)gx->data, (float*)part, rows, dim, eps, accumulate_gx ? 1 : 0, gx_b);
       OJC_LAUNCHED(be, op);
       return OJC_OK;
     }); }));
@@ -865,7 +871,7 @@ extern "C" ojc_status ojc_rms_norm_backward_noalloc(void* cuda_stream, const flo
     constexpr int IT = decltype(it)::value;
     // every launched block overwrites its own row of the workspace and the finish kernel reads exactly those rows,
     // so nothing left by an earlier call is ever read and nothing needs clearing
-    rms_backward_kernel<IT, float, float, float><<<(unsigned)blocks, warps * 32, warps * (int)dim * 4, stream>>>(x, weight, grad_y, grad_x, part, rows, (int)dim, eps, 0);
+    rms_backward_kernel<IT, float, float, float><<<(unsigned)blocks, warps * 32, warps * (int)dim * 4, stream>>>(x, weight, grad_y, grad_x, part, rows, (int)dim, eps, 0, nullptr);
     return OJC_OK;
   });
   if (st != OJC_OK) return st;

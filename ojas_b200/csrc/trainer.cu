@@ -164,7 +164,10 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
     float* x_next = (l + 1 < L) ? tr->acts[l + 1].x : tr->x_final;
     ojc_tensor x = T2(a.x, OJC_F32, N, d), h = T2(a.h, A, N, d);
     ojc_tensor n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d);
-    OJC_TRY(rms_forward_impl(be, &x, &n1, eps, &h));
+    // bf16 tier: the residual stream's next buffer starts as a copy of this one and the projection adds into it (the
+    // GEMM's adding tile stores), instead of reading a separate residual operand in the epilogue
+    const bool add_in_place = A == OJC_BF16;
+    OJC_TRY(rms_forward_impl(be, &x, &n1, eps, &h, add_in_place ? a.x1 : nullptr));
     const bool fl = tr->fused_lin;
     const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;   // token strides of q and of k / raw v
     if (fl) {
@@ -209,15 +212,15 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
       ojc_tensor y = T2(a.y, A, N * H, dh), yg = T2(a.yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H);
       OJC_TRY(ojc_per_head_sigmoid_gate_forward(be, &h2d, &gw, &gb, &y, &yg, &sc));
     }
-    OJC_TRY(linear_forward_impl(be, a.yg, A, tr->WM(tr->P(l, P_O)), A, a.x1, OJC_F32, N, qw, d, a.x));  // x1 = x + o_proj(yg)
+    OJC_TRY(linear_forward_impl(be, a.yg, A, tr->WM(tr->P(l, P_O)), A, a.x1, OJC_F32, N, qw, d, add_in_place ? nullptr : a.x, add_in_place));  // x1 = x + o_proj(yg)
     {
       ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), h2 = T2(a.h2, A, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d);
-      OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2));
+      OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2, add_in_place ? x_next : nullptr));
     }
     if (fl) {
       OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, tr->ld_au, nullptr));
       OJC_TRY(swiglu_rows_forward(be, (const bf16*)a.a, tr->ld_au, (bf16*)a.m, N, F));
-      OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, a.x1));
+      OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, nullptr, true));  // x2 = x1 + down(m)
       continue;
     }
     OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, F, nullptr));
@@ -228,7 +231,7 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
       OJC_TRY(ojc_silu_forward(be, &ta, &tm));
       OJC_TRY(ojc_mul_forward(be, &tm, &tu, &tm));
     }
-    OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, a.x1));  // x2 = x1 + down(m)
+    OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, add_in_place ? nullptr : a.x1, add_in_place));  // x2 = x1 + down(m)
   }
   ojc_tensor xf = T2(tr->x_final, OJC_F32, N, d), hf = T2(tr->hf, A, N, d), nf = T1(tr->W(tr->params.back()), OJC_F32, d);
   return rms_forward_impl(be, &xf, &nf, eps, &hf);
@@ -262,20 +265,14 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   {
     ojc_tensor xf = T2(tr->x_final, OJC_F32, N, d), nf = T1(tr->W(tr->params.back()), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
     ojc_tensor gnf = T1(tr->G(tr->params.back()), OJC_F32, d);
-    OJC_TRY(rms_backward_impl(be, &xf, &nf, &gy, eps, &gx, &gnf, false, false));
+    OJC_TRY(rms_backward_impl(be, &xf, &nf, &gy, eps, &gx, &gnf, false, false, A == OJC_BF16 ? (bf16*)tr->gx_b : nullptr));
   }
   OJC_TRY(record_ready(tr, (int)tr->params.size() - 1));
-  // the residual gradient as a matmul operand: f32 in the f32 tier, a bf16 copy under autocast
-  auto residual_operand = [&]() -> ojc_status {
-    if (!bf) return OJC_OK;
-    ojc_tensor src = T1(tr->gx, OJC_F32, N * d), dst = T1(tr->gx_b, OJC_BF16, N * d);
-    return ojc_to_bf16(be, &src, &dst);
-  };
+  // the residual gradient as a matmul operand: f32 in the f32 tier, the bf16 copy the norm backward kernels write under autocast
   const void* gxo = bf ? tr->gx_b : (void*)tr->gx;
   bool have_v0 = false;
   for (int64_t l = L - 1; l >= 0; --l) {
     LayerActs& a = tr->acts[l];
-    OJC_TRY(residual_operand());
     // x2 = x1 + down(m)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
     OJC_TRY(linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false));
@@ -302,9 +299,8 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     {
       ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d), gy = T2(tr->g_h2, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn2 = T1(tr->G(tr->P(l, P_NORM2)), OJC_F32, d);
-      OJC_TRY(rms_backward_impl(be, &x1, &n2, &gy, eps, &gx, &gn2, false, true));  // gx now holds d/dx1
+      OJC_TRY(rms_backward_impl(be, &x1, &n2, &gy, eps, &gx, &gn2, false, true, bf ? (bf16*)tr->gx_b : nullptr));  // gx now holds d/dx1
     }
-    OJC_TRY(residual_operand());
     // x1 = x + o_proj(yg)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_O)), A, gxo, A, tr->g_yg, A, N, qw, d, false));
     OJC_TRY(linear_backward_weight_impl(be, a.yg, A, gxo, A, tr->G(tr->P(l, P_O)), N, qw, d, false));
@@ -382,7 +378,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     {
       ojc_tensor x = T2(a.x, OJC_F32, N, d), n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn1 = T1(tr->G(tr->P(l, P_NORM1)), OJC_F32, d);
-      OJC_TRY(rms_backward_impl(be, &x, &n1, &gy, eps, &gx, &gn1, false, true));
+      OJC_TRY(rms_backward_impl(be, &x, &n1, &gy, eps, &gx, &gn1, false, true, bf ? (bf16*)tr->gx_b : nullptr));
     }
     if (l == 0 && s.n_layer > 0) OJC_TRY(ojc_fill_zero(be, tr->G(tr->P(0, P_LAMBDA)), 4));  // layer 0's lambda never trains (names.rs:262-268)
     OJC_TRY(record_ready(tr, 1 + (int)l * P_PER_BLOCK));
