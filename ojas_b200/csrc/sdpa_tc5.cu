@@ -223,9 +223,9 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 //          the threads (one key row each) form P^T and dS^T and write them as swizzled bf16 A operands, and
 //          dV += P^T dO, dK += dS^T Q accumulate in TMEM across the whole walk (query heads of a GQA group included).
 //   dQ:    a CTA owns 128 queries and walks the keys: S = Q K^T, dP = dO V^T, dS -> shared memory, dQ += dS K in TMEM.
-// Both walk in steps of SUB = 64 with the S / dP accumulators double-buffered in TMEM, so the tensor pipe forms step
-// i + 1 while the eight compute warps turn step i into P and dS. dS is kept unscaled; the softmax scale multiplies
-// dK and dQ once, on the way out.
+// Both walk in steps of SUB = 64 and take 256 TMEM columns and under 100 KB of shared memory, so two CTAs share an SM:
+// while one CTA's eight compute warps turn a step into P and dS, the other's MMAs run, and a CTA's prologue and final
+// stores hide behind its neighbour's walk. dS is kept unscaled; the softmax scale multiplies dK and dQ once, on the way out.
 struct BwdArgs {
   SdpaView<bf16> g0, g1;          // dK, dV  or  dQ (g1 unused)
   const float* lse2;              // lse * log2(e)
@@ -276,8 +276,8 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr, float 
 constexpr int SUB = 64;
 constexpr int SUB_BYTES = SUB * D * 2;         // 8 KB: 64 rows of q / dO (or k / v)
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
-constexpr int IN_STAGES = 4;
-constexpr uint32_t SUB16 = SUB_BYTES >> 4, PT16 = PT_BYTES >> 4;
+constexpr int IN_STAGES = 2;
+constexpr uint32_t SUB16 = SUB_BYTES >> 4;
 
 // One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; l2, dd: the columns' (dK/dV) or
 // the row's (dQ) statistics; vis(e): column e is visible. Writes the 16-byte chunks of P (optional) and dS.
@@ -305,12 +305,11 @@ __device__ __forceinline__ void bwd_step(const uint32_t (&s)[32], const uint32_t
 
 // ---- dK, dV
 constexpr int KV_OFF_K = 0, KV_OFF_V = TILE_BYTES, KV_OFF_Q = 2 * TILE_BYTES, KV_OFF_G = KV_OFF_Q + IN_STAGES * SUB_BYTES, KV_OFF_P = KV_OFF_G + IN_STAGES * SUB_BYTES,
-              KV_OFF_DS = KV_OFF_P + 2 * PT_BYTES, KV_OFF_STAT = KV_OFF_DS + 2 * PT_BYTES, KV_OFF_BAR = KV_OFF_STAT + IN_STAGES * 2 * SUB * 4;
-constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 256 + 1024;
-enum { KB_KVFULL = 0, KB_INFULL0, KB_INEMPTY0 = KB_INFULL0 + IN_STAGES, KB_SFULL0 = KB_INEMPTY0 + IN_STAGES, KB_PREADY0 = KB_SFULL0 + 2, KB_PFREE0 = KB_PREADY0 + 2,
-       KB_DONE = KB_PFREE0 + 2, KB_COUNT };
+              KV_OFF_DS = KV_OFF_P + PT_BYTES, KV_OFF_STAT = KV_OFF_DS + PT_BYTES, KV_OFF_BAR = KV_OFF_STAT + IN_STAGES * 2 * SUB * 4;
+constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 128 + 1024;
+enum { KB_KVFULL = 0, KB_INFULL0, KB_INEMPTY0 = KB_INFULL0 + IN_STAGES, KB_SFULL = KB_INEMPTY0 + IN_STAGES, KB_PREADY, KB_DONE, KB_COUNT };
 
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 2)
 sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                             const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -329,19 +328,19 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   const int iters = rep * q_subs;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < KB_COUNT; ++i) mbar_init(bar(i), (i >= KB_PREADY0 && i < KB_PREADY0 + 2) ? 256 : 1);
+    for (int i = 0; i < KB_COUNT; ++i) mbar_init(bar(i), i == KB_PREADY ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 9) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: step buffers t = 0, 1 at 128 t: S^T [0,64) and dP^T [64,128); dV [256,320); dK [320,384)
+  // TMEM columns: S^T [0,64), dP^T [64,128), dV [128,192), dK [192,256)
 
   if (warp == 8) {
     if (lane == 0) {
@@ -370,36 +369,34 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       const uint32_t k_lo = desc_lo(base + KV_OFF_K, 0), v_lo = desc_lo(base + KV_OFF_V, 0), q_lo = desc_lo(base + KV_OFF_Q, 0), g_lo = desc_lo(base + KV_OFF_G, 0);
       const uint32_t qm_lo = desc_lo(base + KV_OFF_Q, 1024), gm_lo = desc_lo(base + KV_OFF_G, 1024);   // the same tiles as MN-major B operands
       const uint32_t p_lo = desc_lo(base + KV_OFF_P, 0), ds_lo = desc_lo(base + KV_OFF_DS, 0);
-      // S^T = K Q^T and dP^T = V dO^T of step i into TMEM buffer i & 1
+      // S^T = K Q^T and dP^T = V dO^T of step i. Their commit also covers the dV / dK MMAs of step i - 1 issued just before,
+      // so a compute thread that sees SFULL may overwrite P and dS.
       auto issue_s = [&](uint32_t i) {
-        const uint32_t st = (i % IN_STAGES) * SUB16, tm = tmem_base + (i & 1) * 128;
+        const uint32_t st = (i % IN_STAGES) * SUB16;
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm, k_lo + kk * KSTEP, q_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base, k_lo + kk * KSTEP, q_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm + 64, v_lo + kk * KSTEP, g_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
-        umma_commit(bar(KB_SFULL0 + (i & 1)));
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base + 64, v_lo + kk * KSTEP, g_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        umma_commit(bar(KB_SFULL));
       };
       bool ok = mbar_wait(bar(KB_KVFULL), 0, args.fault, abort_flag) && mbar_wait(bar(KB_INFULL0), 0, args.fault, abort_flag);
       if (ok) { fence_after(); issue_s(0); }
       for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
-        if (it + 1 < (uint32_t)iters) {
-          // buffer (it + 1) & 1 is free: the compute warps arrived on PREADY of step it - 1 after their last read of it
-          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
-          fence_after();
-          issue_s(it + 1);
-        }
-        if (!mbar_wait(bar(KB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) break;
+        // every compute thread has read S^T / dP^T of this step and written P / dS
+        if (!mbar_wait(bar(KB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t st = (it % IN_STAGES) * SUB16, pt = (it & 1) * PT16;
+        const uint32_t st = (it % IN_STAGES) * SUB16;
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand: 16 queries = 2048 bytes)
-          umma_lh(tmem_base + 256, p_lo + pt + kk * KSTEP, gm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_lh(tmem_base + 128, p_lo + kk * KSTEP, gm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
-          umma_lh(tmem_base + 320, ds_lo + pt + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_lh(tmem_base + 192, ds_lo + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(KB_INEMPTY0 + it % IN_STAGES));
-        umma_commit(bar(KB_PFREE0 + (it & 1)));
-        if (it + 1 == (uint32_t)iters) umma_commit(bar(KB_DONE));
+        if (it + 1 == (uint32_t)iters) { umma_commit(bar(KB_DONE)); break; }
+        if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
+        fence_after();
+        issue_s(it + 1);
       }
     }
   } else {
@@ -407,43 +404,34 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int tid = threadIdx.x & 127, half = warp >> 2, key = k0 + tid;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
+    uint8_t* p_row = base_ptr + KV_OFF_P + tid * 128;
+    uint8_t* ds_row = base_ptr + KV_OFF_DS + tid * 128;
     bool ok = true;
     int q0 = k0;
     for (int it = 0; it < iters; ++it) {
-      const int t = it & 1;
       const float* st = stat + (it % IN_STAGES) * 128 + half * 32;   // lse2[64] | dr[64] of this step, landed with the q / dO tiles
-      if (!mbar_wait(bar(KB_SFULL0 + t), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
-      // the P / dS buffer of step it - 2 must have been consumed by its dV / dK MMAs
-      if (it >= 2 && !mbar_wait(bar(KB_PFREE0 + t), ((it >> 1) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(bar(KB_SFULL), it & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
       uint32_t rs[32], rp[32];
-      tmem_ld32(lane_base + t * 128 + half * 32, rs);
-      tmem_ld32(lane_base + t * 128 + 64 + half * 32, rp);
-      float l2[32], dd[32];
-#pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(st + c), d4 = *reinterpret_cast<const float4*>(st + SUB + c);
-        l2[c] = a.x; l2[c + 1] = a.y; l2[c + 2] = a.z; l2[c + 3] = a.w; dd[c] = d4.x; dd[c + 1] = d4.y; dd[c + 2] = d4.z; dd[c + 3] = d4.w;
-      }
+      tmem_ld32(lane_base + half * 32, rs);
+      tmem_ld32(lane_base + 64 + half * 32, rp);
       tmem_wait_ld();
-      uint8_t* p_row = base_ptr + KV_OFF_P + t * PT_BYTES + tid * 128;
-      uint8_t* ds_row = base_ptr + KV_OFF_DS + t * PT_BYTES + tid * 128;
       const int qb = q0 + half * 32;
-      auto fl2 = [&](int c) { return l2[c]; };
-      auto fdd = [&](int c) { return dd[c]; };
+      auto fl2 = [&](int c) { return st[c]; };
+      auto fdd = [&](int c) { return st[SUB + c]; };
       auto vis = [&](int c) { return key < args.time && qb + c < args.time && key <= qb + c; };
       if (q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time) bwd_step<true, true>(rs, rp, sl2, fl2, fdd, vis, p_row, ds_row, half, tid);   // diagonal steps or a ragged end
       else bwd_step<false, true>(rs, rp, sl2, fl2, fdd, vis, p_row, ds_row, half, tid);
       fence_before();
       fence_async_smem();
-      mbar_arrive(bar(KB_PREADY0 + t));
+      mbar_arrive(bar(KB_PREADY));
       q0 += SUB;
       if (q0 >= args.time) q0 = k0;
     }
     if (ok && mbar_wait(bar(KB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
-      if (half == 0) store_row_bf16<D>(key < args.time ? args.g1.row(b, hk, key) : nullptr, lane_base + 256, 1.0f);     // dV
-      else store_row_bf16<D>(key < args.time ? args.g0.row(b, hk, key) : nullptr, lane_base + 320, args.scale);         // dK
+      if (half == 0) store_row_bf16<D>(key < args.time ? args.g1.row(b, hk, key) : nullptr, lane_base + 128, 1.0f);     // dV
+      else store_row_bf16<D>(key < args.time ? args.g0.row(b, hk, key) : nullptr, lane_base + 192, args.scale);         // dK
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -451,18 +439,17 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   __syncthreads();
   if (warp == 9) {
     fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
 // ---- dQ
 constexpr int DQ_OFF_Q = 0, DQ_OFF_G = TILE_BYTES, DQ_OFF_K = 2 * TILE_BYTES, DQ_OFF_V = DQ_OFF_K + IN_STAGES * SUB_BYTES, DQ_OFF_DS = DQ_OFF_V + IN_STAGES * SUB_BYTES,
-              DQ_OFF_BAR = DQ_OFF_DS + 2 * PT_BYTES;
-constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 256 + 1024;
-enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL0 = QB_INEMPTY0 + IN_STAGES, QB_PREADY0 = QB_SFULL0 + 2, QB_PFREE0 = QB_PREADY0 + 2,
-       QB_DONE = QB_PFREE0 + 2, QB_COUNT };
+              DQ_OFF_BAR = DQ_OFF_DS + PT_BYTES;
+constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 128 + 1024;
+enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL = QB_INEMPTY0 + IN_STAGES, QB_PREADY, QB_DONE, QB_COUNT };
 
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 2)
 sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -481,19 +468,19 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   const int iters = (n_end + SUB - 1) / SUB;     // key steps 0, 64, ...
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < QB_COUNT; ++i) mbar_init(bar(i), (i >= QB_PREADY0 && i < QB_PREADY0 + 2) ? 256 : 1);
+    for (int i = 0; i < QB_COUNT; ++i) mbar_init(bar(i), i == QB_PREADY ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 9) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: step buffers t = 0, 1 at 128 t: S [0,64) and dP [64,128); dQ [256,320)
+  // TMEM columns: S [0,64), dP [64,128), dQ [128,192)
 
   if (warp == 8) {
     if (lane == 0) {
@@ -513,31 +500,30 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       const uint32_t idesc_s = make_idesc(BM, SUB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
       const uint32_t q_lo = desc_lo(base + DQ_OFF_Q, 0), g_lo = desc_lo(base + DQ_OFF_G, 0), k_lo = desc_lo(base + DQ_OFF_K, 0), v_lo = desc_lo(base + DQ_OFF_V, 0);
       const uint32_t km_lo = desc_lo(base + DQ_OFF_K, 1024), ds_lo = desc_lo(base + DQ_OFF_DS, 0);
-      auto issue_s = [&](uint32_t i) {   // S = Q K^T and dP = dO V^T of step i into TMEM buffer i & 1
-        const uint32_t st = (i % IN_STAGES) * SUB16, tm = tmem_base + (i & 1) * 128;
+      // S = Q K^T and dP = dO V^T of step i; the commit also covers the dQ MMAs of step i - 1 issued just before, so a
+      // compute thread that sees SFULL may overwrite dS.
+      auto issue_s = [&](uint32_t i) {
+        const uint32_t st = (i % IN_STAGES) * SUB16;
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm, q_lo + kk * KSTEP, k_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base, q_lo + kk * KSTEP, k_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tm + 64, g_lo + kk * KSTEP, v_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
-        umma_commit(bar(QB_SFULL0 + (i & 1)));
+        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base + 64, g_lo + kk * KSTEP, v_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        umma_commit(bar(QB_SFULL));
       };
       bool ok = mbar_wait(bar(QB_QDFULL), 0, args.fault, abort_flag) && mbar_wait(bar(QB_INFULL0), 0, args.fault, abort_flag);
       if (ok) { fence_after(); issue_s(0); }
       for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
-        if (it + 1 < (uint32_t)iters) {
-          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
-          fence_after();
-          issue_s(it + 1);
-        }
-        if (!mbar_wait(bar(QB_PREADY0 + (it & 1)), (it >> 1) & 1, args.fault, abort_flag)) break;
+        if (!mbar_wait(bar(QB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t st = (it % IN_STAGES) * SUB16, pt = (it & 1) * PT16;
+        const uint32_t st = (it % IN_STAGES) * SUB16;
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
-          umma_lh(tmem_base + 256, ds_lo + pt + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_lh(tmem_base + 128, ds_lo + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(QB_INEMPTY0 + it % IN_STAGES));
-        umma_commit(bar(QB_PFREE0 + (it & 1)));
-        if (it + 1 == (uint32_t)iters) umma_commit(bar(QB_DONE));
+        if (it + 1 == (uint32_t)iters) { umma_commit(bar(QB_DONE)); break; }
+        if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
+        fence_after();
+        issue_s(it + 1);
       }
     }
   } else {
@@ -546,17 +532,16 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const float sl2 = args.scale * LOG2E;
     const int64_t idx = ((int64_t)b * args.heads + h) * args.time + row;
     const float lse_row = row < args.time ? args.lse2[idx] : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
+    uint8_t* ds_row = base_ptr + DQ_OFF_DS + tid * 128;
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
-      const int t = it & 1, key0 = it * SUB + half * 32;
-      if (!mbar_wait(bar(QB_SFULL0 + t), (it >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
-      if (it >= 2 && !mbar_wait(bar(QB_PFREE0 + t), ((it >> 1) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      const int key0 = it * SUB + half * 32;
+      if (!mbar_wait(bar(QB_SFULL), it & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
       uint32_t rs[32], rp[32];
-      tmem_ld32(lane_base + t * 128 + half * 32, rs);
-      tmem_ld32(lane_base + t * 128 + 64 + half * 32, rp);
+      tmem_ld32(lane_base + half * 32, rs);
+      tmem_ld32(lane_base + 64 + half * 32, rp);
       tmem_wait_ld();
-      uint8_t* ds_row = base_ptr + DQ_OFF_DS + t * PT_BYTES + tid * 128;
       auto fl2 = [&](int) { return lse_row; };
       auto fdd = [&](int) { return dr_row; };
       auto vis = [&](int c) { return key0 + c <= row && key0 + c < args.time; };
@@ -564,11 +549,11 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       else bwd_step<false, false>(rs, rp, sl2, fl2, fdd, vis, nullptr, ds_row, half, tid);
       fence_before();
       fence_async_smem();
-      mbar_arrive(bar(QB_PREADY0 + t));
+      mbar_arrive(bar(QB_PREADY));
     }
     if (ok && mbar_wait(bar(QB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
-      store_row_bf16<32>(row < args.time ? args.g0.row(b, h, row) + half * 32 : nullptr, lane_base + 256 + half * 32, args.scale);
+      store_row_bf16<32>(row < args.time ? args.g0.row(b, h, row) + half * 32 : nullptr, lane_base + 128 + half * 32, args.scale);
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -576,7 +561,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   __syncthreads();
   if (warp == 9) {
     fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
