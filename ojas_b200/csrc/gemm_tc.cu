@@ -68,6 +68,95 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Drains one warp's share of a finished accumulator tile: TMEM lanes [32 quarter, +32) x columns [col_begin, col_end)
+// starting at `tsrc`, destined for rows row_base.. and columns col_tile0.. of C (or of the split's partial).
+__device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int col_tile0, int split, int lane,
+                                           int col_begin, int col_end, uint8_t* stage_bytes, uint32_t stage_addr) {
+  float* stage = reinterpret_cast<float*>(stage_bytes);
+  if (args.tma_store) {
+    // Each lane owns one accumulator row: it writes 128 bytes of it (64 bf16 or 32 f32 columns) into the warp's
+    // swizzled staging box, and lane 0 hands the 32 x 128-byte box to the TMA unit.
+    const bool bf = args.c_bf16 && args.splits == 1;
+    const int step = bf ? 64 : 32;
+    const int y = (args.splits > 1 ? split * args.m : 0) + row_base;
+#pragma unroll 1
+    for (int c0 = col_begin; c0 < col_end; c0 += step) {
+      uint32_t r[32], r2[32];
+      tmem_ld32(tsrc + c0, r);
+      if (bf) tmem_ld32(tsrc + c0 + 32, r2);
+      tmem_wait_ld();
+      if (lane == 0) bulk_wait_read();       // the previous box has left the staging rows
+      __syncwarp();
+      uint8_t* rowp = stage_bytes + lane * 128;
+      const float al = args.splits > 1 ? 1.0f : args.alpha;
+      if (bf) {
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) {
+          const uint32_t* v = ci < 4 ? &r[ci * 8] : &r2[(ci - 4) * 8];
+          *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+              make_uint4(pack2_bf16(al * __uint_as_float(v[0]), al * __uint_as_float(v[1])), pack2_bf16(al * __uint_as_float(v[2]), al * __uint_as_float(v[3])),
+                         pack2_bf16(al * __uint_as_float(v[4]), al * __uint_as_float(v[5])), pack2_bf16(al * __uint_as_float(v[6]), al * __uint_as_float(v[7])));
+        }
+      } else {
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci)
+          *reinterpret_cast<float4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+              make_float4(al * __uint_as_float(r[ci * 4]), al * __uint_as_float(r[ci * 4 + 1]), al * __uint_as_float(r[ci * 4 + 2]), al * __uint_as_float(r[ci * 4 + 3]));
+      }
+      fence_async_smem();
+      __syncwarp();
+      const int x = col_tile0 + c0;
+      if (lane == 0 && x < args.n && row_base < args.m) {
+        if (args.accumulate && args.splits == 1) tma_reduce_add_2d(&tmap_c, stage_addr, x, y);
+        else tma_store_2d(&tmap_c, stage_addr, x, y);
+        bulk_commit();
+      }
+    }
+    return;
+  }
+#pragma unroll 1
+  for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld32(tsrc + c0, r);
+    tmem_wait_ld();
+    const int col0 = col_tile0 + c0;
+    // residual path: each thread holds one accumulator row; pass the block, 16 columns at a time, through this warp's
+    // padded staging rows so the global accesses are row-contiguous across lanes (4 lanes x 16 bytes per row).
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (half) __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(stage + lane * STAGE_LD + j) = make_float4(__uint_as_float(r[half * 16 + j]), __uint_as_float(r[half * 16 + j + 1]),
+                                                                               __uint_as_float(r[half * 16 + j + 2]), __uint_as_float(r[half * 16 + j + 3]));
+      __syncwarp();
+      const int cc = (lane & 3) * 4, gcol = col0 + half * 16 + cc;
+      if (gcol >= args.n) continue;
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int rr = it * 8 + (lane >> 2), grow = row_base + rr;
+        if (grow >= args.m) continue;
+        float4 v = *reinterpret_cast<const float4*>(stage + rr * STAGE_LD + cc);
+        if (args.splits > 1) {
+          *reinterpret_cast<float4*>(args.partial + ((int64_t)split * args.m + grow) * args.n + gcol) = v;
+          continue;
+        }
+        const int64_t o = (int64_t)grow * args.ldc + gcol;
+        v.x *= args.alpha; v.y *= args.alpha; v.z *= args.alpha; v.w *= args.alpha;
+        if (args.residual) { const float4 t = *reinterpret_cast<const float4*>(args.residual + o); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
+        if (!args.c_bf16) {
+          float* dst = reinterpret_cast<float*>(args.c) + o;
+          if (args.accumulate) { const float4 t = *reinterpret_cast<const float4*>(dst); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
+          *reinterpret_cast<float4*>(dst) = v;
+        } else {
+          *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.c) + o) = make_uint2(pack2_bf16(v.x, v.y), pack2_bf16(v.z, v.w));
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                const TcArgs args) {
@@ -164,7 +253,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int col_begin = ((warp - 2) >> 2) * (BN / 2), col_end = col_begin + BN / 2;
     uint8_t* stage_bytes = epi_ptr + (warp - 2) * EPI_WARP_BYTES;
     const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
-    float* stage = reinterpret_cast<float*>(stage_bytes);
     uint32_t local = 0;
     for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x, ++local) {
       const int split = u % args.splits, tile = u / args.splits;
@@ -174,91 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       fence_after();
       const int row_base = tm * BM + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      if (args.tma_store) {
-        // Each lane owns one accumulator row: it writes 128 bytes of it (64 bf16 or 32 f32 columns) into the warp's
-        // swizzled staging box, and lane 0 hands the 32 x 128-byte box to the TMA unit.
-        const bool bf = args.c_bf16 && args.splits == 1;
-        const int step = bf ? 64 : 32;
-        const int y = (args.splits > 1 ? split * args.m : 0) + row_base;
-#pragma unroll 1
-        for (int c0 = col_begin; c0 < col_end; c0 += step) {
-          uint32_t r[32], r2[32];
-          tmem_ld32(tsrc + c0, r);
-          if (bf) tmem_ld32(tsrc + c0 + 32, r2);
-          tmem_wait_ld();
-          if (lane == 0) bulk_wait_read();       // the previous box has left the staging rows
-          __syncwarp();
-          uint8_t* rowp = stage_bytes + lane * 128;
-          const float al = args.splits > 1 ? 1.0f : args.alpha;
-          if (bf) {
-#pragma unroll
-            for (int ci = 0; ci < 8; ++ci) {
-              const uint32_t* v = ci < 4 ? &r[ci * 8] : &r2[(ci - 4) * 8];
-              *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
-                  make_uint4(pack2_bf16(al * __uint_as_float(v[0]), al * __uint_as_float(v[1])), pack2_bf16(al * __uint_as_float(v[2]), al * __uint_as_float(v[3])),
-                             pack2_bf16(al * __uint_as_float(v[4]), al * __uint_as_float(v[5])), pack2_bf16(al * __uint_as_float(v[6]), al * __uint_as_float(v[7])));
-            }
-          } else {
-#pragma unroll
-            for (int ci = 0; ci < 8; ++ci)
-              *reinterpret_cast<float4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
-                  make_float4(al * __uint_as_float(r[ci * 4]), al * __uint_as_float(r[ci * 4 + 1]), al * __uint_as_float(r[ci * 4 + 2]), al * __uint_as_float(r[ci * 4 + 3]));
-          }
-          fence_async_smem();
-          __syncwarp();
-          const int x = tn * BN + c0;
-          if (lane == 0 && x < args.n && row_base < args.m) {
-            if (args.accumulate && args.splits == 1) tma_reduce_add_2d(&tmap_c, stage_addr, x, y);
-            else tma_store_2d(&tmap_c, stage_addr, x, y);
-            bulk_commit();
-          }
-        }
-        fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(acc));
-        continue;
-      }
-#pragma unroll 1
-      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tsrc + c0, r);
-        tmem_wait_ld();
-        const int col0 = tn * BN + c0;
-        // residual path: each thread holds one accumulator row; pass the block, 16 columns at a time, through this warp's
-        // padded staging rows so the global accesses are row-contiguous across lanes (4 lanes x 16 bytes per row).
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if (half) __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 16; j += 4)
-            *reinterpret_cast<float4*>(stage + lane * STAGE_LD + j) = make_float4(__uint_as_float(r[half * 16 + j]), __uint_as_float(r[half * 16 + j + 1]),
-                                                                                   __uint_as_float(r[half * 16 + j + 2]), __uint_as_float(r[half * 16 + j + 3]));
-          __syncwarp();
-          const int cc = (lane & 3) * 4, gcol = col0 + half * 16 + cc;
-          if (gcol >= args.n) continue;
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int rr = it * 8 + (lane >> 2), grow = row_base + rr;
-            if (grow >= args.m) continue;
-            float4 v = *reinterpret_cast<const float4*>(stage + rr * STAGE_LD + cc);
-            if (args.splits > 1) {
-              *reinterpret_cast<float4*>(args.partial + ((int64_t)split * args.m + grow) * args.n + gcol) = v;
-              continue;
-            }
-            const int64_t o = (int64_t)grow * args.ldc + gcol;
-            v.x *= args.alpha; v.y *= args.alpha; v.z *= args.alpha; v.w *= args.alpha;
-            if (args.residual) { const float4 t = *reinterpret_cast<const float4*>(args.residual + o); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
-            if (!args.c_bf16) {
-              float* dst = reinterpret_cast<float*>(args.c) + o;
-              if (args.accumulate) { const float4 t = *reinterpret_cast<const float4*>(dst); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
-              *reinterpret_cast<float4*>(dst) = v;
-            } else {
-              *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.c) + o) = make_uint2(pack2_bf16(v.x, v.y), pack2_bf16(v.z, v.w));
-            }
-          }
-        }
-      }
+      drain_tile(args, tmap_c, tsrc, row_base, tn * BN, split, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -272,6 +276,143 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The two-SM form: a cluster of two CTAs owns a 256 x 256 tile. Each CTA stages its own 128 rows of A and 128 columns
+// of B (32 KB per stage instead of 48 KB, six stages), one thread of the even CTA issues tcgen05.mma.cta_group::2
+// (M 256, N 256) and each SM's tensor core accumulates its 128 rows x 256 columns in its own TMEM. A third less
+// operand traffic from L2 per FLOP than the one-SM tile, and a deeper ring in the same shared memory.
+//   full[s]   (even CTA's copy) one arrive + the bytes of both CTAs' loads
+//   empty[s]  (each CTA's copy) the MMA thread's commit reaches both copies
+//   tfull[a]  (each CTA's copy) likewise; tempty[a] (even CTA's copy) collects the 16 epilogue warps of both CTAs
+constexpr int STAGES2 = 6, BM2 = 256, BN2 = 256;
+constexpr int A2_TILE_BYTES = 128 * BK * 2, B2_TILE_BYTES = 128 * BK * 2, STAGE2_BYTES = A2_TILE_BYTES + B2_TILE_BYTES;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + EPI_STAGE_BYTES + 256;
+static_assert(SMEM2_BYTES <= 232448, "shared memory per CTA");
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
+                const TcArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;               // the same offset in both CTAs (same kernel, same layout)
+  const uint32_t epi_base = tiles_base + STAGES2 * STAGE2_BYTES;
+  const uint32_t bar_base = epi_base + EPI_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bar_base - raw) + 8 * (2 * STAGES2 + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_ptr = smem_raw + (epi_base - raw);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                          // 0: the CTA that issues the MMAs
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int tiles_m = (args.m + BM2 - 1) / BM2, tiles_n = (args.n + BN2 - 1) / BN2;
+  const int units = tiles_m * tiles_n * args.splits;
+  const int kblocks_total = (args.k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * EPI_WARPS); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // the same warp of both CTAs
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  cluster_sync_all();                                               // both CTAs' barriers exist before anyone arrives on a peer's
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (each CTA loads its own halves)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int u = pair; u < units; u += npairs) {
+        const int split = u % args.splits, tile = u / args.splits;
+        const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
+        const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
+        const int row0 = tm * BM2 + (int)rank * 128, col0 = tn * BN2 + (int)rank * 128;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES2;
+          if (!mbar_wait(empty_bar(s), ((it / STAGES2) & 1) ^ 1, args.fault, abort_flag)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE2_BYTES);
+          const uint32_t a_dst = tiles_base + s * STAGE2_BYTES, b_dst = a_dst + A2_TILE_BYTES;
+          if (!args.a_mn_major) tma_load_2d_pair(a_dst, &tmap_a, full_bar(s), kb * BK, row0);
+          else for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmap_a, full_bar(s), row0 + j * 64, kb * BK);
+          if (!args.b_mn_major) tma_load_2d_pair(b_dst, &tmap_b, full_bar(s), kb * BK, col0);
+          else for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &tmap_b, full_bar(s), col0 + j * 64, kb * BK);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(BM2, BN2, args.a_mn_major, args.b_mn_major);
+      const uint32_t a_lbo = args.a_mn_major ? BK * 128 : 0, b_lbo = args.b_mn_major ? BK * 128 : 0;
+      const uint32_t a_step = args.a_mn_major ? 2048 : 32, b_step = args.b_mn_major ? 2048 : 32;
+      uint32_t it = 0, local = 0;
+      for (int u = pair; u < units; u += npairs, ++local) {
+        const int split = u % args.splits;
+        const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
+        const int acc = local & 1;
+        if (!mbar_wait(tempty_bar(acc), ((local >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
+        fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN2;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES2;
+          if (!mbar_wait(full_bar(s), (it / STAGES2) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+          const uint32_t a_src = tiles_base + s * STAGE2_BYTES, b_src = a_src + A2_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_pair(tmem_d, make_desc(a_src + kk * a_step, a_lbo, 1024), make_desc(b_src + kk * b_step, b_lbo, 1024), idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          umma_commit_pair(empty_bar(s));      // frees the stage in both CTAs when these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar(acc));      // accumulators complete in both CTAs
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+    const int quarter = warp & 3;
+    const int col_begin = ((warp - 2) >> 2) * (BN2 / 2), col_end = col_begin + BN2 / 2;
+    uint8_t* stage_bytes = epi_ptr + (warp - 2) * EPI_WARP_BYTES;
+    const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
+    uint32_t local = 0;
+    for (int u = pair; u < units; u += npairs, ++local) {
+      const int split = u % args.splits, tile = u / args.splits;
+      const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
+      const int acc = local & 1;
+      if (!mbar_wait(tfull_bar(acc), (local >> 1) & 1, args.fault, abort_flag)) break;
+      fence_after();
+      const int row_base = tm * BM2 + (int)rank * 128 + quarter * 32;
+      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
+      drain_tile(args, tmap_c, tsrc, row_base, tn * BN2, split, lane, col_begin, col_end, stage_bytes, stage_addr);
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
+    }
+    if (args.tma_store && lane == 0) bulk_wait_all();
+  }
+  // Teardown: neither CTA may leave while its partner can still reach its shared memory, barriers or tensor memory.
+  if (*abort_flag) __nanosleep(200000);
+  fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -340,10 +481,24 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   if (accumulate && c_dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "accumulation needs an F32 output");
   int amn, bmn; int64_t lda, ldb;
   operand_ok(a, true, &amn, &lda); operand_ok(b, false, &bmn, &ldb);
+  // Two-SM tiles (256 x 256 per CTA pair) whenever the output is at least one such tile; the one-SM kernel keeps the rest.
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)(be->sm_count & ~1)); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.attrs = attr; cfg.numAttrs = 1;
+    int n_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tc2_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n_clusters = 0; }
+    max_pairs = n_clusters;
+  }
+  const bool two_sm = max_pairs > 0 && m >= BM2 && n >= BN2;
+  const int tile_m = two_sm ? BM2 : BM, tile_n = two_sm ? BN2 : BN, workers = two_sm ? max_pairs : be->sm_count;
   CUtensorMap ta, tb;
-  if (!amn) OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)k, (uint64_t)m, (uint64_t)lda, 64, BM));
+  if (!amn) OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)k, (uint64_t)m, (uint64_t)lda, 64, 128));
   else OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)m, (uint64_t)k, (uint64_t)lda, 64, BK));
-  if (!bmn) OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, 64, BN));
+  if (!bmn) OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, 64, two_sm ? 128 : BN));
   else OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, 64, BK));
 
   static bool attr_set = false;
@@ -351,7 +506,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
     attr_set = true;
   }
-  const int tiles = (int)(((m + BM - 1) / BM) * ((n + BN - 1) / BN));
+  const int tiles = (int)(((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n));
   const int kblocks = (int)((k + BK - 1) / BK);
   // Split the reduction axis when the output tiles alone leave SMs idle: estimate each split count's time as the math at
   // the wave efficiency its units reach plus the partial round trip through memory, and take the cheapest (each split
@@ -361,8 +516,8 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     const double flops = 2.0 * (double)m * (double)n * (double)k;
     double best = 1e30;
     for (int sp = 1; sp <= 16 && kblocks / sp >= 8; ++sp) {
-      const int units = tiles * sp, waves = (units + be->sm_count - 1) / be->sm_count;
-      const double eff = (double)units / ((double)waves * be->sm_count);
+      const int units = tiles * sp, waves = (units + workers - 1) / workers;
+      const double eff = (double)units / ((double)waves * workers);
       const double t = flops / (1.5e15 * eff) + (sp > 1 ? (double)sp * (double)m * (double)n * 8.0 / 6.0e12 : 0.0);
       if (t < best * 0.97) { best = t; splits = sp; }
     }
@@ -381,7 +536,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     args.partial = (float*)ws;
   }
   // Neighbouring CTAs work on neighbouring tiles: walk the shorter tile axis fastest so the long operand streams from HBM once.
-  args.tiles_n_fast = ((n + BN - 1) / BN) <= ((m + BM - 1) / BM) ? 1 : 0;
+  args.tiles_n_fast = ((n + tile_n - 1) / tile_n) <= ((m + tile_m - 1) / tile_m) ? 1 : 0;
   args.tma_store = (!residual && (splits == 1 || m % 32 == 0) && n >= 64) ? 1 : 0;   // narrower outputs than a store box take the row path
   CUtensorMap tc = ta;   // unused unless tma_store
   if (args.tma_store) {
@@ -389,14 +544,16 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     else if (args.c_bf16) OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 64, 32, false));
     else OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 32, 32, true));
   }
-  int grid = tiles * splits < be->sm_count ? tiles * splits : be->sm_count;
+  int grid = tiles * splits < workers ? tiles * splits : workers;
+  if (two_sm) grid *= 2;
   ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k};
   if (be->profile_gemm) {
     if (!be->event_pool.empty()) { sample.start = be->event_pool.back().first; sample.stop = be->event_pool.back().second; be->event_pool.pop_back(); }
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }
     OJC_CUDA(be, cudaEventRecord(sample.start, be->stream), op);
   }
-  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
+  if (two_sm) gemm_tc2_kernel<<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, args);
+  else gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
   OJC_LAUNCHED(be, op);
   if (be->profile_gemm) {
     OJC_CUDA(be, cudaEventRecord(sample.stop, be->stream), op);

@@ -48,7 +48,9 @@ def test_linear_f32_tier(be, rows, kin, nout):
     assert rel(be.linear_backward_input(dw, dgy).numpy(), ogx) <= GRAD_TOL
 
 
-TC_SHAPES = [(128, 64, 256), (64, 64, 64), (200, 136, 520), (256, 768, 768), (1024, 768, 2048), (384, 2048, 768), (8, 8, 8), (130, 72, 264), (2048, 256, 4096)]
+# outputs of at least 256 x 256 take the two-SM kernel (CTA pairs), smaller ones the one-SM kernel; ragged edges on both
+TC_SHAPES = [(128, 64, 256), (64, 64, 64), (200, 136, 520), (256, 768, 768), (1024, 768, 2048), (384, 2048, 768), (8, 8, 8), (130, 72, 264), (2048, 256, 4096),
+             (300, 136, 520), (513, 72, 264), (640, 1024, 392)]
 
 
 @pytest.mark.parametrize("rows,kin,nout", TC_SHAPES)
