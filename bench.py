@@ -27,9 +27,11 @@ sys.path.insert(0, str(ROOT))
 
 BATCH, SEQ = 32, 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tc_kernel, averaged over the step's GEMM launches
-# (profiles/gemm_tc_kernel_124m_step.md); None until a capture exists.
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size GEMM launch of the step, the q/k/v projection
+# [32768 x 768] x [768 x 2304] -> bf16 (profiles/gemm_tc2_kernel_qkv_32768x768x2304.md): 53.9 MB read + 96.7 MB written
+# against 205.0 MB of algorithmic bytes (the tail of the output is still in L2 when the kernel ends).
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = 150_663_424
+GEMM_TRAFFIC_LAUNCH = "q/k/v projection 32768x768x2304 bf16: algorithmic 205.0 MB per launch"
 
 
 def peaks() -> tuple[dict, str]:
@@ -277,10 +279,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     }
     if gemm_ms > 0:
         achieved = gemm_flops / (gemm_ms / 1000.0) / 1e12
-        line["roofline"] = {"kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM, all launches of the timed steps)", "bound": "tensor", "achieved": achieved,
+        line["roofline"] = {"kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM, two-SM and one-SM tiles; all launches of the timed steps)", "bound": "tensor",
+                            "achieved": achieved,
                             "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops_sustained"],
                             "peak_source": f"bf16_tflops_sustained, of {pk_kind}", "launches": int(gemm_launches), "share_of_step_time": gemm_ms / ms,
-                            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH}
+                            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "traffic_launch": GEMM_TRAFFIC_LAUNCH}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         rate, cores, sample, _ = cpu_step_rate(20.0, 1, 0)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}

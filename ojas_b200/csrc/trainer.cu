@@ -575,18 +575,33 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
   auto run = [&]() -> ojc_status {
     OJC_TRY(grad_norm_device(be, &gp, &glen, 1, clip ? tr->cfg.grad_clip : -1.0f, tr->stats + 1));
     const float* scale = clip ? tr->stats + 2 : nullptr;
+    // AdamW is element-wise with one configuration per group, so neighbouring AdamW slots go out as one launch over the
+    // flat buffers (the zero padding between slots stays zero: p = g = m = v = 0 is a fixed point of the update).
+    // the hybrid recipe runs AdamW without decay on embeddings and vectors (ADAM_HYBRID_WEIGHT_DECAY, ojas-cpu/src/train.rs:31-37)
+    const ojc_adamw_config ac{tr->cfg.adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.optimizer == 1 ? 0.0 : tr->cfg.adam_weight_decay};
+    int64_t run_begin = -1, run_end = -1;
+    auto flush = [&]() -> ojc_status {
+      if (run_begin < 0) return OJC_OK;
+      bf16* mir = tr->mirror ? tr->mirror + run_begin : nullptr;
+      ojc_status r = adamw_device(be, tr->w + run_begin, tr->g + run_begin, tr->m1 + run_begin, tr->m2 + run_begin, mir, run_end - run_begin, tr->step, ac, scale);
+      run_begin = run_end = -1;
+      return r;
+    };
     for (const Param& p : tr->params) {
-      if (!p.trains) continue;
-      bf16* mir = tr->mirror ? tr->mirror + p.offset : nullptr;
+      const int64_t slot_end = p.offset + ((p.n + 63) & ~int64_t(63));
+      if (!p.trains) { OJC_TRY(flush()); continue; }
       if (tr->cfg.optimizer == 1 && p.group == GROUP_MUON) {
+        OJC_TRY(flush());
+        bf16* mir = tr->mirror ? tr->mirror + p.offset : nullptr;
         ojc_muon_config mc{tr->cfg.matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
         OJC_TRY(muon_device(be, tr->W(p), tr->G(p), tr->m1 + p.offset, mir, p.shape[0], p.shape[1], mc, scale));
       } else {
-        // the hybrid recipe runs AdamW without decay on embeddings and vectors (ADAM_HYBRID_WEIGHT_DECAY, ojas-cpu/src/train.rs:31-37)
-        ojc_adamw_config ac{tr->cfg.adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.optimizer == 1 ? 0.0 : tr->cfg.adam_weight_decay};
-        OJC_TRY(adamw_device(be, tr->W(p), tr->G(p), tr->m1 + p.offset, tr->m2 + p.offset, mir, p.n, tr->step, ac, scale));
+        if (run_begin < 0) run_begin = p.offset;
+        else if (p.offset != run_end) { OJC_TRY(flush()); run_begin = p.offset; }
+        run_end = slot_end;
       }
     }
+    OJC_TRY(flush());
     return OJC_OK;
   };
   ojc_status st = run();
