@@ -305,6 +305,61 @@ __global__ void vres_root_backward_kernel(const float* __restrict__ acc, const b
   }
 }
 
+// ---- RMSNorm backward over the f32 residual stream, 128-bit accesses: a warp per row, lane l owns float4 columns
+// 4 (l + 32 j). Same arithmetic as rms_backward_kernel (dot = sum (g w)(x rstd); dX = (g w - xhat dot/dim) rstd; per-block
+// partial dW in shared memory, finished by the fixed-order column sum). Optional second f32 output accumulation and a
+// bf16 copy of dX (the operand of the next matmul).
+template <int J>
+__global__ void rms_backward_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ gy, float* __restrict__ gx,
+                                         bf16* __restrict__ gx_b, float* __restrict__ part, int64_t rows, float eps, int gx_accumulate) {
+  constexpr int DIM = 128 * J;
+  extern __shared__ float smem[];  // [warps][DIM]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float4 wv[J], dw[J];
+#pragma unroll
+  for (int j = 0; j < J; ++j) { wv[j] = *reinterpret_cast<const float4*>(w + 4 * (lane + 32 * j)); dw[j] = make_float4(0.f, 0.f, 0.f, 0.f); }
+  const float inv_dim = 1.0f / (float)DIM;
+  for (int64_t row = (int64_t)blockIdx.x * nwarps + warp; row < rows; row += (int64_t)gridDim.x * nwarps) {
+    const float* xr = x + row * DIM; const float* gr = gy + row * DIM; float* or_ = gx + row * DIM;
+    float4 xv[J], gv[J], old[J];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = 4 * (lane + 32 * j);
+      xv[j] = *reinterpret_cast<const float4*>(xr + c);
+      gv[j] = *reinterpret_cast<const float4*>(gr + c);
+      old[j] = gx_accumulate ? *reinterpret_cast<const float4*>(or_ + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+    }
+    ss = row_sum<32>(ss);
+    const float rstd = 1.0f / sqrtf(ss * inv_dim + eps);
+    float dot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j)
+      dot += (gv[j].x * wv[j].x) * (xv[j].x * rstd) + (gv[j].y * wv[j].y) * (xv[j].y * rstd) + (gv[j].z * wv[j].z) * (xv[j].z * rstd) + (gv[j].w * wv[j].w) * (xv[j].w * rstd);
+    dot = row_sum<32>(dot);
+    const float mean = dot * inv_dim;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = 4 * (lane + 32 * j);
+      const float4 xh = make_float4(xv[j].x * rstd, xv[j].y * rstd, xv[j].z * rstd, xv[j].w * rstd);
+      dw[j].x += gv[j].x * xh.x; dw[j].y += gv[j].y * xh.y; dw[j].z += gv[j].z * xh.z; dw[j].w += gv[j].w * xh.w;
+      const float4 o = make_float4((gv[j].x * wv[j].x - xh.x * mean) * rstd + old[j].x, (gv[j].y * wv[j].y - xh.y * mean) * rstd + old[j].y,
+                                   (gv[j].z * wv[j].z - xh.z * mean) * rstd + old[j].z, (gv[j].w * wv[j].w - xh.w * mean) * rstd + old[j].w);
+      *reinterpret_cast<float4*>(or_ + c) = o;
+      if (gx_b) *reinterpret_cast<uint2*>(gx_b + row * DIM + c) = make_uint2(pack2(o.x, o.y), pack2(o.z, o.w));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < J; ++j) *reinterpret_cast<float4*>(smem + warp * DIM + 4 * (lane + 32 * j)) = dw[j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < DIM; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int wi = 0; wi < nwarps; ++wi) acc += smem[wi * DIM + c];
+    part[(int64_t)blockIdx.x * DIM + c] = acc;
+  }
+}
+
 template <class F> ojc_status dispatch_tpr(const char* op, int dh, F&& f) {
   switch (dh) {
     case 16: return f(std::integral_constant<int, 1>());
@@ -418,6 +473,25 @@ ojc_status vres_root_backward(ojc_backend* be, const float* acc, const bf16* g, 
   const char* op = "value_residual_blend_backward";
   if (cols % 8 != 0 || ldo % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
   vres_root_backward_kernel<<<elementwise_grid(be, rows * (cols / 8), 256), 256, 0, be->stream>>>(acc, g, out, ldo, rows, (int)(cols / 8));
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+
+bool rms_backward_rows_supported(int64_t dim) { return dim == 512 || dim == 768 || dim == 1024 || dim == 2048; }
+// part: [blocks, dim] scratch from the caller; returns the block count through *blocks_out for the column sum.
+ojc_status rms_backward_rows(ojc_backend* be, const float* x, const float* w, const float* gy, float* gx, bf16* gx_b, float* part, int64_t rows, int64_t dim,
+                             float eps, bool accumulate_gx, int blocks) {
+  const char* op = "rms_norm_backward";
+  const int warps = 4;
+  const size_t smem = (size_t)warps * dim * 4;
+#define OJC_RMS_ROWS(J) rms_backward_rows_kernel<J><<<blocks, warps * 32, smem, be->stream>>>(x, w, gy, gx, gx_b, part, rows, eps, accumulate_gx ? 1 : 0)
+  if (dim == 512) OJC_RMS_ROWS(4);
+  else if (dim == 768) OJC_RMS_ROWS(6);
+  else if (dim == 1024) OJC_RMS_ROWS(8);
+  else if (dim == 2048) OJC_RMS_ROWS(16);
+  else return ojc_fail(OJC_ERR_UNSUPPORTED, op, "row width outside the vectorized forms");
+#undef OJC_RMS_ROWS
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }

@@ -416,19 +416,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   }
 }
 
-// Sum the split-K partials in split order, then apply alpha / residual / accumulate.
+// Sum the split-K partials in split order, then apply alpha / residual / accumulate. n is a multiple of 8, so rows split
+// into whole float4 groups.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, void* c, int c_bf16, int64_t ldc, int m, int n, float alpha,
                                      int accumulate, const float* __restrict__ residual) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total = (int64_t)m * n, stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < total; i += stride) {
-    float acc = 0.0f;
-    for (int s = 0; s < splits; ++s) acc += partial[(int64_t)s * total + i];
-    const int64_t o = (i / n) * ldc + (i % n);
-    float v = alpha * acc;
-    if (residual) v += residual[o];
-    if (c_bf16) { reinterpret_cast<bf16*>(c)[o] = __float2bfloat16_rn(v); }
-    else { float* dst = reinterpret_cast<float*>(c) + o; *dst = accumulate ? *dst + v : v; }
+  const int n4 = n >> 2;
+  const int64_t total4 = (int64_t)m * n4, plane4 = total4;
+  const float4* part4 = reinterpret_cast<const float4*>(partial);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 acc = part4[i];
+    for (int s = 1; s < splits; ++s) { const float4 t = part4[(int64_t)s * plane4 + i]; acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w; }
+    const int64_t row = i / n4, o = row * ldc + (i - row * n4) * 4;
+    float4 v = make_float4(alpha * acc.x, alpha * acc.y, alpha * acc.z, alpha * acc.w);
+    if (residual) { const float4 t = *reinterpret_cast<const float4*>(residual + o); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
+    if (c_bf16) {
+      *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(c) + o) = make_uint2(pack2_bf16(v.x, v.y), pack2_bf16(v.z, v.w));
+    } else {
+      float* dst = reinterpret_cast<float*>(c) + o;
+      if (accumulate) { const float4 t = *reinterpret_cast<const float4*>(dst); v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w; }
+      *reinterpret_cast<float4*>(dst) = v;
+    }
   }
 }
 
@@ -560,7 +567,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
     be->gemm_samples.push_back(sample);
   }
   if (splits > 1) {
-    splitk_reduce_kernel<<<elementwise_grid(be, m * n, 256), 256, 0, be->stream>>>(args.partial, splits, c, args.c_bf16, ldc, (int)m, (int)n, alpha,
+    splitk_reduce_kernel<<<elementwise_grid(be, m * n / 4, 256), 256, 0, be->stream>>>(args.partial, splits, c, args.c_bf16, ldc, (int)m, (int)n, alpha,
                                                                                    args.accumulate, residual);
     OJC_LAUNCHED(be, op);
   }

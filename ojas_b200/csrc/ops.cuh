@@ -33,3 +33,6 @@ ojc_status vres_rows_forward(ojc_backend* be, const bf16* v, int64_t ldv, const 
 ojc_status vres_rows_backward(ojc_backend* be, const bf16* v, int64_t ldv, const bf16* v0, int64_t ld0, const float* lambda, const bf16* gy, bf16* gv, int64_t ldg,
                               float* acc, bool first, float* glambda, int64_t rows, int64_t cols);
 ojc_status vres_root_backward(ojc_backend* be, const float* acc, const bf16* g, bf16* out, int64_t ldo, int64_t rows, int64_t cols);
+bool rms_backward_rows_supported(int64_t dim);
+ojc_status rms_backward_rows(ojc_backend* be, const float* x, const float* w, const float* gy, float* gx, bf16* gx_b, float* part, int64_t rows, int64_t dim,
+                             float eps, bool accumulate_gx, int blocks);
