@@ -1,4 +1,4 @@
-// Causal attention on the Blackwell tensor cores (tcgen05 + TMEM), head_dim 64, bf16 operands.
+// Causal attention on the Blackwell tensor cores (tcgen05 + TMEM), head_dim 64 or 128, bf16 operands.
 //
 // Forward: one CTA owns 128 query rows of one (batch, head) and walks the visible key blocks of 128:
 //   warp 4   TMA producer: Q once, then (K, V) pairs into two stages, 128-byte swizzle, every CTA fetching its own tiles
@@ -7,7 +7,9 @@
 //   warps 0-3  one thread per query row (= TMEM lane): read the S row once, softmax in the log2 domain against a row
 //            scale that moves only when the maximum outgrew it by 2^8 (then O is rescaled in place in TMEM), write P as
 //            bf16 into the swizzled shared-memory A-operand layout; at the end normalise O from TMEM, store O and lse.
-// Two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// At head_dim 64 two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one CTA's softmax overlaps
+// the other's MMAs; at head_dim 128 the tiles take 192 KB and one CTA owns the SM. Rows wider than 128 bytes are kept as
+// 64-column sub-tiles (one 128-byte swizzle span each), 16 KB apart for 128-row tiles and 8 KB apart for 64-row tiles.
 // Every mbarrier wait is bounded; on expiry the CTA raises the fault word, drains and frees its TMEM.
 #include "sdpa.cuh"
 #include "tc_common.cuh"
@@ -16,15 +18,20 @@ namespace {
 
 using namespace tc;
 
-constexpr int BM = 128, BN = 128, D = 64;
-constexpr int TILE_BYTES = 128 * D * 2;                       // 16 KB: 128 rows of 128 bytes
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 5 * TILE_BYTES, OFF_BAR = 7 * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 128;                     // 112 KB + barriers: two CTAs per SM
+constexpr int BM = 128, BN = 128;
+constexpr int ST128 = 128 * 128, ST64 = 64 * 128;              // bytes of one 64-column sub-tile of a 128-row / 64-row tile
+constexpr int P_BYTES = 128 * BN * 2;                         // 32 KB: P as two 64-key halves
 constexpr int NTHREADS = 192, BWD_THREADS = 320;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_STEP = 8.0f;                          // log2 units the row maximum may run ahead of the scale in use
 constexpr uint32_t HI = desc_hi(1024);                        // every operand here: 8-row groups 1024 bytes apart
-constexpr uint32_t KSTEP = 32 >> 4, MNSTEP = 2048 >> 4, TILE16 = TILE_BYTES >> 4;   // descriptor low-word increments
+constexpr uint32_t KSTEP = 32 >> 4, MNSTEP = 2048 >> 4, ST128_16 = ST128 >> 4, ST64_16 = ST64 >> 4;   // descriptor low-word increments
+template <int D> struct Fwd {
+  static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128;
+  static constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 5 * TILE_BYTES, OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 128;              // D 64: 112 KB (two CTAs per SM); D 128: 192 KB
+  static constexpr int CTAS = D == 64 ? 2 : 1;
+};
 enum { B_QFULL = 0, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL, B_PREADY, B_PVFULL, B_COUNT };
 
 struct FwdArgs {
@@ -36,17 +43,26 @@ struct FwdArgs {
   uint32_t* fault;
 };
 
+// one `ROWS`-row tile of a head as NSUB 64-column boxes
+template <int NSUB, int ROWS>
 __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int h_first, int h, int t0, int b) {
-  if (h_first) tma_load_4d(dst, map, bar, 0, h, t0, b);
-  else tma_load_4d(dst, map, bar, 0, t0, h, b);
+#pragma unroll
+  for (int i = 0; i < NSUB; ++i) {
+    if (h_first) tma_load_4d(dst + i * ROWS * 128, map, bar, 64 * i, h, t0, b);
+    else tma_load_4d(dst + i * ROWS * 128, map, bar, 64 * i, t0, h, b);
+  }
 }
 
-__global__ void __launch_bounds__(NTHREADS, 2)
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, Fwd<D>::CTAS)
 sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }   // the swizzled tiles need 1024-byte alignment (whole CTA leaves)
   uint8_t* base_ptr = smem_raw;
+  using C = Fwd<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, OFF_Q = C::OFF_Q, OFF_K = C::OFF_K, OFF_V = C::OFF_V, OFF_P = C::OFF_P, OFF_BAR = C::OFF_BAR;
+  constexpr uint32_t TILE16 = TILE_BYTES >> 4;
   auto bar = [&](int i) { return base + OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_BAR + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -77,13 +93,13 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     // ------------------------------------------------------------------ TMA producer: Q, then (K, V) pairs two blocks ahead
     if (lane == 0) {
       mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
-      load_tile(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
+      load_tile<NSUB, 128>(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
       for (int j = 0; j < nblocks; ++j) {
         const int s = j & 1;
         if (!mbar_wait(bar(B_KVEMPTY0 + s), ((j >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
         mbar_expect_tx(bar(B_KVFULL0 + s), 2 * TILE_BYTES);
-        load_tile(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
-        load_tile(base + OFF_V + s * TILE_BYTES, &tm_v, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
+        load_tile<NSUB, 128>(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
+        load_tile<NSUB, 128>(base + OFF_V + s * TILE_BYTES, &tm_v, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
       }
     }
   } else if (warp == 5) {
@@ -91,7 +107,8 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BM, BN, 0, 0), idesc_pv = make_idesc(BM, D, 0, 1);
       // descriptor low words: K-major operands step 32 bytes per MMA, the MN-major V steps 16 keys = 2048 bytes
-      const uint32_t q_lo = desc_lo(base + OFF_Q, 0), k_lo = desc_lo(base + OFF_K, 0), p_lo = desc_lo(base + OFF_P, 0), v_lo = desc_lo(base + OFF_V, 1024);
+      // (V as the MN-major B operand: its 64-wide column blocks are the sub-tiles, ST128 bytes apart)
+      const uint32_t q_lo = desc_lo(base + OFF_Q, 0), k_lo = desc_lo(base + OFF_K, 0), p_lo = desc_lo(base + OFF_P, 0), v_lo = desc_lo(base + OFF_V, ST128);
       bool ok = mbar_wait(bar(B_QFULL), 0, args.fault, abort_flag);
       for (int j = 0; j < nblocks && ok; ++j) {
         const uint32_t s = j & 1;
@@ -99,7 +116,8 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         fence_after();
         // S = Q K^T. The S columns are free: every softmax thread arrived on B_PREADY for block j - 1 after its last S read.
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base, q_lo + kk * KSTEP, k_lo + s * TILE16 + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base, q_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + s * TILE16 + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(B_SFULL));
         if (!mbar_wait(bar(B_PREADY), j & 1, args.fault, abort_flag)) break;
         fence_after();
@@ -107,7 +125,7 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         // O stays in TMEM for the whole walk; the softmax rows rescale it in place when their maximum moves.
 #pragma unroll
         for (uint32_t kk = 0; kk < BN / 16; ++kk)
-          umma_lh(tmem_base + 128, p_lo + (kk >> 2) * TILE16 + (kk & 3) * KSTEP, v_lo + s * TILE16 + kk * MNSTEP, HI, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_lh(tmem_base + 128, p_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, v_lo + s * TILE16 + kk * MNSTEP, HI, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(B_KVEMPTY0 + s));
         umma_commit(bar(B_PVFULL));
       }
@@ -176,7 +194,7 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
         for (int e = 0; e < 8; ++e) { p[e] = fast_exp2(fmaf(__uint_as_float(r[ci * 8 + e]), sl2, -m)); rs4[e & 3] += p[e]; }
         // 16-byte chunk ci of this row's 128 keys; the 128-byte swizzle XORs the chunk index with row % 8
-        *reinterpret_cast<uint4*>(p_row + (ci >> 3) * TILE_BYTES + (((ci & 7) ^ (tid & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(p_row + (ci >> 3) * ST128 + (((ci & 7) ^ (tid & 7)) << 4)) =
             make_uint4(pack2_bf16(p[0], p[1]), pack2_bf16(p[2], p[3]), pack2_bf16(p[4], p[5]), pack2_bf16(p[6], p[7]));
       }
       l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
@@ -235,12 +253,14 @@ struct BwdArgs {
   uint32_t* fault;
 };
 
-// Dr[b,h,t] = sum_d dO . O and lse2 = lse * log2(e): eight threads per row, 16-byte loads.
+// Dr[b,h,t] = sum_d dO . O and lse2 = lse * log2(e): D / 8 threads per row, 16-byte loads.
+template <int D>
 __global__ void sdpa_bwd_prep_kernel(SdpaView<const bf16> out, SdpaView<const bf16> gout, const float* __restrict__ lse, float* __restrict__ dr,
                                      float* __restrict__ lse2, int heads, int time, int64_t rows) {
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t r = min(gid >> 3, rows - 1);
-  const int part = (int)(gid & 7);
+  constexpr int TPR = D / 8;
+  const int64_t r = min(gid / TPR, rows - 1);
+  const int part = (int)(gid % TPR);
   const int t = (int)(r % time), h = (int)((r / time) % heads), b = (int)(r / ((int64_t)time * heads));
   const uint4 o = *reinterpret_cast<const uint4*>(out.row(b, h, t) + part * 8), g = *reinterpret_cast<const uint4*>(gout.row(b, h, t) + part * 8);
   const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, gw[4] = {g.x, g.y, g.z, g.w};
@@ -248,8 +268,9 @@ __global__ void sdpa_bwd_prep_kernel(SdpaView<const bf16> out, SdpaView<const bf
 #pragma unroll
   for (int i = 0; i < 4; ++i)
     acc += __uint_as_float(ow[i] << 16) * __uint_as_float(gw[i] << 16) + __uint_as_float(ow[i] & 0xffff0000u) * __uint_as_float(gw[i] & 0xffff0000u);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1); acc += __shfl_xor_sync(0xffffffffu, acc, 2); acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-  if (part == 0 && (gid >> 3) < rows) { dr[r] = acc; lse2[r] = lse[r] * LOG2E; }
+#pragma unroll
+  for (int o = 1; o < TPR; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (part == 0 && gid / TPR < rows) { dr[r] = acc; lse2[r] = lse[r] * LOG2E; }
 }
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -274,10 +295,8 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr, float 
 }
 
 constexpr int SUB = 64;
-constexpr int SUB_BYTES = SUB * D * 2;         // 8 KB: 64 rows of q / dO (or k / v)
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
 constexpr int IN_STAGES = 2;
-constexpr uint32_t SUB16 = SUB_BYTES >> 4;
 
 // One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; l2, dd: the columns' (dK/dV) or
 // the row's (dQ) statistics; vis(e): column e is visible. Writes the 16-byte chunks of P (optional) and dS.
@@ -304,18 +323,28 @@ __device__ __forceinline__ void bwd_step(const uint32_t (&s)[32], const uint32_t
 }
 
 // ---- dK, dV
-constexpr int KV_OFF_K = 0, KV_OFF_V = TILE_BYTES, KV_OFF_Q = 2 * TILE_BYTES, KV_OFF_G = KV_OFF_Q + IN_STAGES * SUB_BYTES, KV_OFF_P = KV_OFF_G + IN_STAGES * SUB_BYTES,
-              KV_OFF_DS = KV_OFF_P + PT_BYTES, KV_OFF_STAT = KV_OFF_DS + PT_BYTES, KV_OFF_BAR = KV_OFF_STAT + IN_STAGES * 2 * SUB * 4;
-constexpr int KV_SMEM_BYTES = KV_OFF_BAR + 128 + 1024;
+template <int D> struct Dkv {
+  static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128, STEP_BYTES = NSUB * ST64;   // K / V tile; one step of q or dO
+  static constexpr int OFF_K = 0, OFF_V = TILE_BYTES, OFF_Q = 2 * TILE_BYTES, OFF_G = OFF_Q + IN_STAGES * STEP_BYTES, OFF_P = OFF_G + IN_STAGES * STEP_BYTES,
+                       OFF_DS = OFF_P + PT_BYTES, OFF_STAT = OFF_DS + PT_BYTES, OFF_BAR = OFF_STAT + IN_STAGES * 2 * SUB * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;       // D 64: 98 KB (two CTAs per SM); D 128: 162 KB
+  static constexpr int TMEM_COLS = D == 64 ? 256 : 512;         // S^T 64 + dP^T 64 + dV D + dK D
+  static constexpr int CTAS = D == 64 ? 2 : 1;
+};
 enum { KB_KVFULL = 0, KB_INFULL0, KB_INEMPTY0 = KB_INFULL0 + IN_STAGES, KB_SFULL = KB_INEMPTY0 + IN_STAGES, KB_PREADY, KB_DONE, KB_COUNT };
 
-__global__ void __launch_bounds__(BWD_THREADS, 2)
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, Dkv<D>::CTAS)
 sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                             const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
+  using C = Dkv<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STEP_BYTES = C::STEP_BYTES, KV_OFF_K = C::OFF_K, KV_OFF_V = C::OFF_V, KV_OFF_Q = C::OFF_Q, KV_OFF_G = C::OFF_G,
+                KV_OFF_P = C::OFF_P, KV_OFF_DS = C::OFF_DS, KV_OFF_STAT = C::OFF_STAT, KV_OFF_BAR = C::OFF_BAR;
+  constexpr uint32_t STEP16 = STEP_BYTES >> 4, TCOLS = C::TMEM_COLS;
   auto bar = [&](int i) { return base + KV_OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + KV_OFF_BAR + 8 * KB_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -333,20 +362,20 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 9) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: S^T [0,64), dP^T [64,128), dV [128,192), dK [192,256)
+  // TMEM columns: S^T [0,64), dP^T [64,128), dV [128,128+D), dK [128+D,128+2D)
 
   if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(bar(KB_KVFULL), 2 * TILE_BYTES);
-      load_tile(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
-      load_tile(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
+      load_tile<NSUB, 128>(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
+      load_tile<NSUB, 128>(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
       int h = hk * rep, q0 = k0;
       for (int it = 0; it < iters; ++it) {
         const int s = it % IN_STAGES;
@@ -354,9 +383,9 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         // the step's row statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
         const uint32_t stat_bytes = (uint32_t)min(SUB, args.time - q0) * 4u;
         const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
-        mbar_expect_tx(bar(KB_INFULL0 + s), 2 * SUB_BYTES + 2 * stat_bytes);
-        load_tile(base + KV_OFF_Q + s * SUB_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
-        load_tile(base + KV_OFF_G + s * SUB_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
+        mbar_expect_tx(bar(KB_INFULL0 + s), 2 * STEP_BYTES + 2 * stat_bytes);
+        load_tile<NSUB, 64>(base + KV_OFF_Q + s * STEP_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
+        load_tile<NSUB, 64>(base + KV_OFF_G + s * STEP_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
         bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
         bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
         q0 += SUB;
@@ -367,16 +396,18 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BN, SUB, 0, 0), idesc_o = make_idesc(BN, D, 0, 1);
       const uint32_t k_lo = desc_lo(base + KV_OFF_K, 0), v_lo = desc_lo(base + KV_OFF_V, 0), q_lo = desc_lo(base + KV_OFF_Q, 0), g_lo = desc_lo(base + KV_OFF_G, 0);
-      const uint32_t qm_lo = desc_lo(base + KV_OFF_Q, 1024), gm_lo = desc_lo(base + KV_OFF_G, 1024);   // the same tiles as MN-major B operands
+      const uint32_t qm_lo = desc_lo(base + KV_OFF_Q, ST64), gm_lo = desc_lo(base + KV_OFF_G, ST64);   // the same tiles as MN-major B operands (64-wide blocks ST64 apart)
       const uint32_t p_lo = desc_lo(base + KV_OFF_P, 0), ds_lo = desc_lo(base + KV_OFF_DS, 0);
       // S^T = K Q^T and dP^T = V dO^T of step i. Their commit also covers the dV / dK MMAs of step i - 1 issued just before,
       // so a compute thread that sees SFULL may overwrite P and dS.
       auto issue_s = [&](uint32_t i) {
-        const uint32_t st = (i % IN_STAGES) * SUB16;
+        const uint32_t st = (i % IN_STAGES) * STEP16;
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base, k_lo + kk * KSTEP, q_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base, k_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, q_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base + 64, v_lo + kk * KSTEP, g_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base + 64, v_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, g_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(KB_SFULL));
       };
       bool ok = mbar_wait(bar(KB_KVFULL), 0, args.fault, abort_flag) && mbar_wait(bar(KB_INFULL0), 0, args.fault, abort_flag);
@@ -385,13 +416,13 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         // every compute thread has read S^T / dP^T of this step and written P / dS
         if (!mbar_wait(bar(KB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t st = (it % IN_STAGES) * SUB16;
+        const uint32_t st = (it % IN_STAGES) * STEP16;
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand: 16 queries = 2048 bytes)
           umma_lh(tmem_base + 128, p_lo + kk * KSTEP, gm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
-          umma_lh(tmem_base + 192, ds_lo + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_lh(tmem_base + 128 + D, ds_lo + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(KB_INEMPTY0 + it % IN_STAGES));
         if (it + 1 == (uint32_t)iters) { umma_commit(bar(KB_DONE)); break; }
         if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
@@ -431,7 +462,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     if (ok && mbar_wait(bar(KB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
       if (half == 0) store_row_bf16<D>(key < args.time ? args.g1.row(b, hk, key) : nullptr, lane_base + 128, 1.0f);     // dV
-      else store_row_bf16<D>(key < args.time ? args.g0.row(b, hk, key) : nullptr, lane_base + 192, args.scale);         // dK
+      else store_row_bf16<D>(key < args.time ? args.g0.row(b, hk, key) : nullptr, lane_base + 128 + D, args.scale);         // dK
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -439,23 +470,32 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   __syncthreads();
   if (warp == 9) {
     fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TCOLS) : "memory");
   }
 }
 
 // ---- dQ
-constexpr int DQ_OFF_Q = 0, DQ_OFF_G = TILE_BYTES, DQ_OFF_K = 2 * TILE_BYTES, DQ_OFF_V = DQ_OFF_K + IN_STAGES * SUB_BYTES, DQ_OFF_DS = DQ_OFF_V + IN_STAGES * SUB_BYTES,
-              DQ_OFF_BAR = DQ_OFF_DS + PT_BYTES;
-constexpr int DQ_SMEM_BYTES = DQ_OFF_BAR + 128 + 1024;
+template <int D> struct Dq {
+  static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128, STEP_BYTES = NSUB * ST64;   // q / dO tile; one step of k or v
+  static constexpr int OFF_Q = 0, OFF_G = TILE_BYTES, OFF_K = 2 * TILE_BYTES, OFF_V = OFF_K + IN_STAGES * STEP_BYTES, OFF_DS = OFF_V + IN_STAGES * STEP_BYTES,
+                       OFF_BAR = OFF_DS + PT_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;       // D 64: 81 KB (two CTAs per SM); D 128: 145 KB
+  static constexpr int CTAS = D == 64 ? 2 : 1;
+};
 enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL = QB_INEMPTY0 + IN_STAGES, QB_PREADY, QB_DONE, QB_COUNT };
 
-__global__ void __launch_bounds__(BWD_THREADS, 2)
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, Dq<D>::CTAS)
 sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
+  using C = Dq<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STEP_BYTES = C::STEP_BYTES, DQ_OFF_Q = C::OFF_Q, DQ_OFF_G = C::OFF_G, DQ_OFF_K = C::OFF_K, DQ_OFF_V = C::OFF_V,
+                DQ_OFF_DS = C::OFF_DS, DQ_OFF_BAR = C::OFF_BAR;
+  constexpr uint32_t STEP16 = STEP_BYTES >> 4;
   auto bar = [&](int i) { return base + DQ_OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + DQ_OFF_BAR + 8 * QB_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -480,34 +520,36 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: S [0,64), dP [64,128), dQ [128,192)
+  // TMEM columns: S [0,64), dP [64,128), dQ [128,128+D)
 
   if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(bar(QB_QDFULL), 2 * TILE_BYTES);
-      load_tile(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
-      load_tile(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
+      load_tile<NSUB, 128>(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
+      load_tile<NSUB, 128>(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
       for (int it = 0; it < iters; ++it) {
         const int s = it % IN_STAGES;
         if (!mbar_wait(bar(QB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
-        mbar_expect_tx(bar(QB_INFULL0 + s), 2 * SUB_BYTES);
-        load_tile(base + DQ_OFF_K + s * SUB_BYTES, &tm_k, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
-        load_tile(base + DQ_OFF_V + s * SUB_BYTES, &tm_v, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
+        mbar_expect_tx(bar(QB_INFULL0 + s), 2 * STEP_BYTES);
+        load_tile<NSUB, 64>(base + DQ_OFF_K + s * STEP_BYTES, &tm_k, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
+        load_tile<NSUB, 64>(base + DQ_OFF_V + s * STEP_BYTES, &tm_v, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
       }
     }
   } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BM, SUB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
       const uint32_t q_lo = desc_lo(base + DQ_OFF_Q, 0), g_lo = desc_lo(base + DQ_OFF_G, 0), k_lo = desc_lo(base + DQ_OFF_K, 0), v_lo = desc_lo(base + DQ_OFF_V, 0);
-      const uint32_t km_lo = desc_lo(base + DQ_OFF_K, 1024), ds_lo = desc_lo(base + DQ_OFF_DS, 0);
+      const uint32_t km_lo = desc_lo(base + DQ_OFF_K, ST64), ds_lo = desc_lo(base + DQ_OFF_DS, 0);
       // S = Q K^T and dP = dO V^T of step i; the commit also covers the dQ MMAs of step i - 1 issued just before, so a
       // compute thread that sees SFULL may overwrite dS.
       auto issue_s = [&](uint32_t i) {
-        const uint32_t st = (i % IN_STAGES) * SUB16;
+        const uint32_t st = (i % IN_STAGES) * STEP16;
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base, q_lo + kk * KSTEP, k_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base, q_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
 #pragma unroll
-        for (uint32_t kk = 0; kk < D / 16; ++kk) umma_lh(tmem_base + 64, g_lo + kk * KSTEP, v_lo + st + kk * KSTEP, HI, idesc_s, kk > 0);
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base + 64, g_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, v_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(QB_SFULL));
       };
       bool ok = mbar_wait(bar(QB_QDFULL), 0, args.fault, abort_flag) && mbar_wait(bar(QB_INFULL0), 0, args.fault, abort_flag);
@@ -515,7 +557,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
         if (!mbar_wait(bar(QB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t st = (it % IN_STAGES) * SUB16;
+        const uint32_t st = (it % IN_STAGES) * STEP16;
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
           umma_lh(tmem_base + 128, ds_lo + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
@@ -553,7 +595,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     }
     if (ok && mbar_wait(bar(QB_DONE), 0, args.fault, abort_flag)) {
       fence_after();
-      store_row_bf16<32>(row < args.time ? args.g0.row(b, h, row) + half * 32 : nullptr, lane_base + 128 + half * 32, args.scale);
+      store_row_bf16<D / 2>(row < args.time ? args.g0.row(b, h, row) + half * (D / 2) : nullptr, lane_base + 128 + half * (D / 2), args.scale);
     }
   }
   if (*abort_flag) __nanosleep(200000);
@@ -568,12 +610,13 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// A [B, H, T, dh] view (any batch / head / time strides, dh contiguous) as a 4-D tensor map whose tiles are `rows` time steps of one head.
+// A [B, H, T, dh] view (any batch / head / time strides, dh contiguous) as a 4-D tensor map whose boxes are `rows` time steps x 64
+// columns of one head (one 128-byte swizzle span per row).
 ojc_status make_map(ojc_backend* be, const char* op, CUtensorMap* map, const ojc_tensor* t, bool h_first, uint32_t rows = 128) {
   const uint64_t B = t->shape[0], H = t->shape[1], T = t->shape[2], dh = t->shape[3];
   cuuint64_t gdim[4], gstride[3];
   cuuint32_t box[4], estride[4] = {1, 1, 1, 1};
-  gdim[0] = dh; box[0] = (cuuint32_t)dh;
+  gdim[0] = dh; box[0] = 64;
   if (h_first) { gdim[1] = H; gstride[0] = t->stride[1] * 2; box[1] = 1; gdim[2] = T; gstride[1] = t->stride[2] * 2; box[2] = rows; }
   else { gdim[1] = T; gstride[0] = t->stride[2] * 2; box[1] = rows; gdim[2] = H; gstride[1] = t->stride[1] * 2; box[2] = 1; }
   gdim[3] = B; gstride[2] = t->stride[0] * 2; box[3] = 1;
@@ -591,11 +634,20 @@ bool strides_ok(const ojc_tensor* t) {
 }  // namespace
 
 bool sdpa_tcgen05_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, int64_t window, const SdpaDims& d) {
-  if (!be->tmap_encode || q->dtype != OJC_BF16 || d.dim != D || window >= 0) return false;
+  if (!be->tmap_encode || q->dtype != OJC_BF16 || (d.dim != 64 && d.dim != 128) || window >= 0) return false;
   if (!strides_ok(q) || !strides_ok(k) || !strides_ok(v) || !strides_ok(out)) return false;
   // one dimension order for all three maps: heads inside time, or time inside heads
   const bool hf = q->stride[1] < q->stride[2];
   return (k->stride[1] < k->stride[2]) == hf && (v->stride[1] < v->stride[2]) == hf;
+}
+
+template <int D>
+static ojc_status launch_fwd(ojc_backend* be, const char* op, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& args, dim3 grid) {
+  static bool attr = false;
+  if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwd_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd<D>::SMEM_BYTES), op); attr = true; }
+  sdpa_fwd_tcgen05_kernel<D><<<grid, NTHREADS, Fwd<D>::SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
 }
 
 ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, ojc_tensor* out, float* lse, const SdpaDims& d) {
@@ -605,13 +657,34 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
   OJC_TRY(make_map(be, op, &mq, q, hf));
   OJC_TRY(make_map(be, op, &mk, k, hf));
   OJC_TRY(make_map(be, op, &mv, v, hf));
-  static bool attr = false;
-  if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwd_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op); attr = true; }
   FwdArgs args;
   args.out = SdpaView<bf16>{(bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]};
   args.lse = lse; args.heads = d.heads; args.kv_heads = d.kv_heads; args.time = d.time; args.h_first = hf ? 1 : 0; args.scale = d.scale; args.fault = be->fault_dev;
   dim3 grid((d.time + BM - 1) / BM, d.batch * d.heads);
-  sdpa_fwd_tcgen05_kernel<<<grid, NTHREADS, SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
+  return d.dim == 64 ? launch_fwd<64>(be, op, mq, mk, mv, args, grid) : launch_fwd<128>(be, op, mq, mk, mv, args, grid);
+}
+
+template <int D>
+static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* out, const float* lse, const ojc_tensor* gout, float* dr, float* lse2, int64_t rows,
+                             const CUtensorMap (&m)[8], BwdArgs a, const ojc_tensor* gq, const ojc_tensor* gk, const ojc_tensor* gv, const SdpaDims& d) {
+  static bool attr = false;
+  if (!attr) {
+    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dkv<D>::SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);
+    attr = true;
+  }
+  sdpa_bwd_prep_kernel<D><<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, be->stream>>>(
+      SdpaView<const bf16>{(const bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]},
+      SdpaView<const bf16>{(const bf16*)gout->data, gout->stride[0], gout->stride[1], gout->stride[2]}, lse, dr, lse2, d.heads, d.time, rows);
+  OJC_LAUNCHED(be, op);
+  a.g0 = SdpaView<bf16>{(bf16*)gk->data, gk->stride[0], gk->stride[1], gk->stride[2]};
+  a.g1 = SdpaView<bf16>{(bf16*)gv->data, gv->stride[0], gv->stride[1], gv->stride[2]};
+  dim3 grid_k((d.time + BN - 1) / BN, d.batch * d.kv_heads);
+  sdpa_bwd_dkv_tcgen05_kernel<D><<<grid_k, BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);   // q, dO in 64-row steps
+  OJC_LAUNCHED(be, op);
+  a.g0 = SdpaView<bf16>{(bf16*)gq->data, gq->stride[0], gq->stride[1], gq->stride[2]};
+  dim3 grid_q((d.time + BM - 1) / BM, d.batch * d.heads);
+  sdpa_bwd_dq_tcgen05_kernel<D><<<grid_q, BWD_THREADS, Dq<D>::SMEM_BYTES, be->stream>>>(m[0], m[5], m[6], m[3], a);      // k, v in 64-row steps
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }
@@ -622,39 +695,14 @@ ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc
   const char* op = "causal_sdpa_backward";
   const int64_t rows = (int64_t)d.batch * d.heads * d.time;
   float *dr = work, *lse2 = work + rows;
-  sdpa_bwd_prep_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, be->stream>>>(
-      SdpaView<const bf16>{(const bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]},
-      SdpaView<const bf16>{(const bf16*)gout->data, gout->stride[0], gout->stride[1], gout->stride[2]}, lse, dr, lse2, d.heads, d.time, rows);
-  OJC_LAUNCHED(be, op);
   const bool hf = q->stride[1] < q->stride[2];
-  // whole 128-row tiles for the operand a CTA keeps, 64-row tiles for the one it walks
-  CUtensorMap mq, mk, mv, mg, mq_s, mk_s, mv_s, mg_s;
-  OJC_TRY(make_map(be, op, &mq, q, hf));
-  OJC_TRY(make_map(be, op, &mk, k, hf));
-  OJC_TRY(make_map(be, op, &mv, v, hf));
-  OJC_TRY(make_map(be, op, &mg, gout, hf));
-  OJC_TRY(make_map(be, op, &mq_s, q, hf, SUB));
-  OJC_TRY(make_map(be, op, &mk_s, k, hf, SUB));
-  OJC_TRY(make_map(be, op, &mv_s, v, hf, SUB));
-  OJC_TRY(make_map(be, op, &mg_s, gout, hf, SUB));
-  static bool attr = false;
-  if (!attr) {
-    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM_BYTES), op);
-    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_BYTES), op);
-    attr = true;
-  }
+  // maps 0-3: q, k, v, dO in 128-row tiles (the operand a CTA keeps); 4-7: the same in 64-row steps (the one it walks)
+  CUtensorMap m[8];
+  const ojc_tensor* src[4] = {q, k, v, gout};
+  for (int i = 0; i < 4; ++i) { OJC_TRY(make_map(be, op, &m[i], src[i], hf)); OJC_TRY(make_map(be, op, &m[4 + i], src[i], hf, SUB)); }
   BwdArgs a;
   a.lse2 = lse2; a.dr = dr; a.heads = d.heads; a.kv_heads = d.kv_heads; a.time = d.time; a.h_first = hf ? 1 : 0; a.scale = d.scale; a.fault = be->fault_dev;
-  a.g0 = SdpaView<bf16>{(bf16*)gk->data, gk->stride[0], gk->stride[1], gk->stride[2]};
-  a.g1 = SdpaView<bf16>{(bf16*)gv->data, gv->stride[0], gv->stride[1], gv->stride[2]};
-  dim3 grid_k((d.time + BN - 1) / BN, d.batch * d.kv_heads);
-  sdpa_bwd_dkv_tcgen05_kernel<<<grid_k, BWD_THREADS, KV_SMEM_BYTES, be->stream>>>(mq_s, mk, mv, mg_s, a);
-  OJC_LAUNCHED(be, op);
-  a.g0 = SdpaView<bf16>{(bf16*)gq->data, gq->stride[0], gq->stride[1], gq->stride[2]};
-  dim3 grid_q((d.time + BM - 1) / BM, d.batch * d.heads);
-  sdpa_bwd_dq_tcgen05_kernel<<<grid_q, BWD_THREADS, DQ_SMEM_BYTES, be->stream>>>(mq, mk_s, mv_s, mg, a);
-  OJC_LAUNCHED(be, op);
-  return OJC_OK;
+  return d.dim == 64 ? launch_bwd<64>(be, op, out, lse, gout, dr, lse2, rows, m, a, gq, gk, gv, d) : launch_bwd<128>(be, op, out, lse, gout, dr, lse2, rows, m, a, gq, gk, gv, d);
 }
 
 bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* gout, const ojc_tensor* gq,
