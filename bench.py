@@ -284,6 +284,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                             "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops_sustained"],
                             "peak_source": f"bf16_tflops_sustained, of {pk_kind}", "launches": int(gemm_launches), "share_of_step_time": gemm_ms / ms,
                             "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "traffic_launch": GEMM_TRAFFIC_LAUNCH}
+    if rank == 0 and world == 1 and not args.no_sdpa:
+        line["sdpa_standalone"] = sdpa_standalone(be, main, pk["bf16_tflops"])
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         rate, cores, sample, _ = cpu_step_rate(20.0, 1, 0)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
@@ -295,6 +297,47 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def sdpa_standalone(be, main_stream, peak_tflops: float) -> dict:
+    """BASELINE's standalone attention case: causal SDPA forward + backward on bf16 [B 8, H 16, T 4096, D 128], N(0,1) inputs
+    (seeded numpy draws), timed with CUDA events on the library's stream. FLOPs: forward 4 B H T^2 D / 2 (causal half),
+    backward 2.5x (the recompute of S is counted once, as in the step's MFU)."""
+    import ctypes as C
+    import torch
+    from ojas_b200 import DType
+    from ojas_b200._lib import lib
+    from ojas_b200.backend import _check, _p
+    B, H, T, D = 8, 16, 4096, 128
+    rng = np.random.default_rng(4)
+
+    def draw():
+        return be.upload(rng.standard_normal((B, T, H, D), dtype=np.float32), DType.BF16).permuted((0, 2, 1, 3))
+
+    q, k, v, g = draw(), draw(), draw(), draw()
+    out = be.empty((B, T, H, D), DType.BF16).permuted((0, 2, 1, 3))
+    lse = be.empty((B, H, T))
+    gq, gk, gv = (be.empty((B, T, H, D), DType.BF16).permuted((0, 2, 1, 3)) for _ in range(3))
+    fwd = lambda: _check(lib.ojc_causal_sdpa_forward(be._handle, _p(q), _p(k), _p(v), C.c_int64(-1), _p(out), _p(lse)))
+    bwd = lambda: _check(lib.ojc_causal_sdpa_backward(be._handle, _p(q), _p(k), _p(v), _p(out), _p(lse), _p(g), C.c_int64(-1), _p(gq), _p(gk), _p(gv)))
+    flops = 4.0 * B * H * T * T * D / 2
+    res = {"shape": [B, H, T, D], "dtype": "bf16"}
+    for name, fn, mult in (("fwd", fwd, 1.0), ("bwd", bwd, 2.5)):
+        for _ in range(3):
+            fn()
+        be.sync()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(main_stream)
+        for _ in range(5):
+            fn()
+        b_.record(main_stream)
+        be.sync()
+        ms = a.elapsed_time(b_) / 5
+        res[name + "_ms"] = ms
+        res[name + "_tflops"] = flops * mult / ms / 1e9
+    res["fwd_bwd_tflops"] = flops * 3.5 / (res["fwd_ms"] + res["bwd_ms"]) / 1e9
+    res["frac_of_peak"] = res["fwd_bwd_tflops"] / peak_tflops
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -302,6 +345,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the bounded CPU sample (the default run reports it)")
+    ap.add_argument("--no-sdpa", action="store_true", help="skip the standalone attention case [8,16,4096,128]")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (used for profiler captures)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

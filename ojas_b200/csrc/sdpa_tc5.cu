@@ -53,6 +53,102 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
   }
 }
 
+// The softmax role of one 128-row query tile: thread `tid` owns row q0 + tid (TMEM lane tid). s_addr / o_addr: this thread's
+// lane in the S and O accumulators; p_row: its row of the P operand buffer.
+template <int D>
+__device__ __forceinline__ void softmax_tile(const FwdArgs& args, int b, int h, int q0, int tid, int nblocks, uint32_t s_addr, uint32_t o_addr, uint8_t* p_row,
+                                             uint32_t bar_sfull, uint32_t bar_pready, uint32_t bar_pvfull, volatile int* abort_flag) {
+  const int row = q0 + tid;
+  const float sl2 = args.scale * LOG2E;
+  float m = 0.0f, l = 0.0f;                     // m: the maximum the probabilities are scaled by (log2 domain), set by block 0
+  bool ok = true;
+  for (int j = 0; j < nblocks; ++j) {
+    if (!mbar_wait(bar_sfull, j & 1, args.fault, abort_flag)) { ok = false; break; }
+    fence_after();
+    const int key0 = j * BN;
+    const bool masked = key0 + BN > q0 || key0 + BN > args.time;   // only blocks touching the diagonal or the sequence end need masking
+    uint32_t r[BN];                                                  // the whole S row of this block: one TMEM pass
+#pragma unroll
+    for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+    tmem_wait_ld();
+    if (masked) {
+#pragma unroll
+      for (int e = 0; e < BN; ++e) {
+        const int key = key0 + e;
+        if (!(key <= row && key < args.time)) r[e] = 0xff800000u;   // -inf: exp2 gives an exact zero
+      }
+    }
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four chains instead of one 128-deep dependency
+#pragma unroll
+    for (int e = 0; e < BN; e += 4) {
+      mx4[0] = fmaxf(mx4[0], __uint_as_float(r[e])); mx4[1] = fmaxf(mx4[1], __uint_as_float(r[e + 1]));
+      mx4[2] = fmaxf(mx4[2], __uint_as_float(r[e + 2])); mx4[3] = fmaxf(mx4[3], __uint_as_float(r[e + 3]));
+    }
+    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    mx *= sl2;                                   // the scale is positive: max(s) * scale = max(s * scale)
+    // The scale moves only when some row of the warp outgrew it by RESCALE_STEP (the TMEM accesses are warp-wide);
+    // block 0 holds key 0, visible to every row, so m is finite from then on.
+    const bool grow = j == 0 || mx > m + RESCALE_STEP;
+    if (__any_sync(0xffffffffu, grow)) {
+      const float m_new = j == 0 ? (mx == -INFINITY ? 0.0f : mx) : fmaxf(m, mx);
+      const float corr = j == 0 ? 0.0f : fast_exp2(m - m_new);
+      m = m_new;
+      l *= corr;
+      if (j > 0) {
+        // O of blocks 0..j-1 must have landed before it is rescaled in place
+        if (!mbar_wait(bar_pvfull, (j - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tmem_st32(o_addr + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+    }
+    float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int ci = 0; ci < BN / 8; ++ci) {
+      float p[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { p[e] = fast_exp2(fmaf(__uint_as_float(r[ci * 8 + e]), sl2, -m)); rs4[e & 3] += p[e]; }
+      // 16-byte chunk ci of this row's 128 keys; the 128-byte swizzle XORs the chunk index with row % 8
+      *reinterpret_cast<uint4*>(p_row + (ci >> 3) * ST128 + (((ci & 7) ^ (tid & 7)) << 4)) =
+          make_uint4(pack2_bf16(p[0], p[1]), pack2_bf16(p[2], p[3]), pack2_bf16(p[4], p[5]), pack2_bf16(p[6], p[7]));
+    }
+    l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+    fence_before();
+    fence_async_smem();
+    mbar_arrive(bar_pready);
+  }
+  if (ok && mbar_wait(bar_pvfull, (nblocks - 1) & 1, args.fault, abort_flag)) {
+    fence_after();
+    const float inv = 1.0f / l;
+    bf16* dst = row < args.time ? args.out.row(b, h, row) : nullptr;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld32(o_addr + c * 32, o);
+      tmem_wait_ld();
+      if (dst) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(dst + c * 32 + i) =
+              make_uint4(pack2_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv), pack2_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                         pack2_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv), pack2_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+      }
+    }
+    if (dst) {
+      args.lse[((int64_t)b * args.heads + h) * args.time + row] = (m + log2f(l)) * LN2;
+      if (!(l > 0.0f) || !isfinite(l) || !isfinite(m)) raise_fault(args.fault, OP_SDPA);
+    }
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, Fwd<D>::CTAS)
 sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
@@ -132,98 +228,9 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ softmax + output rows (warps 0..3)
-    const int tid = threadIdx.x;                  // query row within the tile = TMEM lane
-    const int row = q0 + tid;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const float sl2 = args.scale * LOG2E;
-    float m = 0.0f, l = 0.0f;                     // m: the maximum the probabilities are scaled by (log2 domain), set by block 0
-    uint8_t* p_row = base_ptr + OFF_P + tid * 128;
-    bool ok = true;
-    for (int j = 0; j < nblocks; ++j) {
-      if (!mbar_wait(bar(B_SFULL), j & 1, args.fault, abort_flag)) { ok = false; break; }
-      fence_after();
-      const int key0 = j * BN;
-      const bool masked = key0 + BN > q0 || key0 + BN > args.time;   // only blocks touching the diagonal or the sequence end need masking
-      uint32_t r[BN];                                                  // the whole S row of this block: one TMEM pass
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld32(lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-      tmem_wait_ld();
-      if (masked) {
-#pragma unroll
-        for (int e = 0; e < BN; ++e) {
-          const int key = key0 + e;
-          if (!(key <= row && key < args.time)) r[e] = 0xff800000u;   // -inf: exp2 gives an exact zero
-        }
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four chains instead of one 128-deep dependency
-#pragma unroll
-      for (int e = 0; e < BN; e += 4) {
-        mx4[0] = fmaxf(mx4[0], __uint_as_float(r[e])); mx4[1] = fmaxf(mx4[1], __uint_as_float(r[e + 1]));
-        mx4[2] = fmaxf(mx4[2], __uint_as_float(r[e + 2])); mx4[3] = fmaxf(mx4[3], __uint_as_float(r[e + 3]));
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx *= sl2;                                   // the scale is positive: max(s) * scale = max(s * scale)
-      // The scale moves only when some row of the warp outgrew it by RESCALE_STEP (the TMEM accesses are warp-wide);
-      // block 0 holds key 0, visible to every row, so m is finite from then on.
-      const bool grow = j == 0 || mx > m + RESCALE_STEP;
-      if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = j == 0 ? (mx == -INFINITY ? 0.0f : mx) : fmaxf(m, mx);
-        const float corr = j == 0 ? 0.0f : fast_exp2(m - m_new);
-        m = m_new;
-        l *= corr;
-        if (j > 0) {
-          // O of blocks 0..j-1 must have landed before it is rescaled in place
-          if (!mbar_wait(bar(B_PVFULL), (j - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
-          fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(lane_base + 128 + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
-            tmem_st32(lane_base + 128 + c * 32, o);
-          }
-          tmem_wait_st();
-        }
-      }
-      float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-      for (int ci = 0; ci < BN / 8; ++ci) {
-        float p[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { p[e] = fast_exp2(fmaf(__uint_as_float(r[ci * 8 + e]), sl2, -m)); rs4[e & 3] += p[e]; }
-        // 16-byte chunk ci of this row's 128 keys; the 128-byte swizzle XORs the chunk index with row % 8
-        *reinterpret_cast<uint4*>(p_row + (ci >> 3) * ST128 + (((ci & 7) ^ (tid & 7)) << 4)) =
-            make_uint4(pack2_bf16(p[0], p[1]), pack2_bf16(p[2], p[3]), pack2_bf16(p[4], p[5]), pack2_bf16(p[6], p[7]));
-      }
-      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      fence_before();
-      fence_async_smem();
-      mbar_arrive(bar(B_PREADY));
-    }
-    if (ok && mbar_wait(bar(B_PVFULL), (nblocks - 1) & 1, args.fault, abort_flag)) {
-      fence_after();
-      const float inv = 1.0f / l;
-      bf16* dst = row < args.time ? args.out.row(b, h, row) : nullptr;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(lane_base + 128 + c * 32, o);
-        tmem_wait_ld();
-        if (dst) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8)
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) =
-                make_uint4(pack2_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv), pack2_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
-                           pack2_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv), pack2_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
-        }
-      }
-      if (dst) {
-        args.lse[((int64_t)b * args.heads + h) * args.time + row] = (m + log2f(l)) * LN2;
-        if (!(l > 0.0f) || !isfinite(l) || !isfinite(m)) raise_fault(args.fault, OP_SDPA);
-      }
-    }
+    softmax_tile<D>(args, b, h, q0, threadIdx.x, nblocks, lane_base, lane_base + 128, base_ptr + OFF_P + threadIdx.x * 128, bar(B_SFULL), bar(B_PREADY), bar(B_PVFULL),
+                    abort_flag);
   }
   if (*abort_flag) __nanosleep(200000);
   fence_before();

@@ -165,6 +165,39 @@ def test_config1_bf16_autocast_loss_within_one_percent(be, c1):
     tr.close()
 
 
+def test_bf16_autocast_loss_curve_tracks_the_f32_oracle_over_200_steps(be):
+    """North-star gate for bf16 autocast: the loss curve stays within 2% of the CPU reference's over 200 optimizer steps
+    (same seed, same weights, same batches). A small model so the strict-order oracle runs 200 steps in well under a minute."""
+    from ojas_b200 import ModelSpec
+    kw = dict(vocab=512, n_embd=128, n_layer=2, n_head=2, n_kv_head=2, head_dim=64, hidden=256, max_seq=64)
+    ospec = orc.Spec(**kw)
+    params = [p.copy() for p in orc.init_params(ospec, 0, normal_everywhere=True)]
+    table = orc.param_table(ospec)
+    rng = orc.SplitMix64(7)
+    b, t, nbatch, steps, lr = 4, 64, 16, 200, 1e-3
+    draws = np.array([rng.below(512) for _ in range(nbatch * b * (t + 1))], np.uint32).reshape(nbatch, b, t + 1)
+    tr = make_trainer(be, ModelSpec(**kw), {info.name: v for info, v in zip(table, params)}, b, t, autocast_bf16=True, optimizer="adamw", adam_lr=lr,
+                      adam_weight_decay=0.1, grad_clip=1.0)
+    moments = [(np.zeros(p.size, np.float32), np.zeros(p.size, np.float32)) for p in params]
+    worst, first, last = 0.0, None, None
+    for step in range(steps):
+        x, y = draws[step % nbatch, :, :-1].copy(), draws[step % nbatch, :, 1:].copy()
+        oloss, grads, _ = orc.forward_loss(ospec, params, x, y)
+        norm = float(orc.grad_norm(grads))
+        scale = min(1.0, 1.0 / (norm + 1e-6))
+        for info, p, g, (m, v) in zip(table, params, grads, moments):
+            if info.trains:
+                flat = p.reshape(-1)
+                orc.adamw_step(flat, (g.ravel() * np.float32(scale)).astype(np.float32) if scale < 1.0 else g.ravel(), m, v, step, lr, weight_decay=0.1)
+        rep = tr.step(x, y)
+        worst = max(worst, abs(rep.loss - oloss) / oloss)
+        first = oloss if first is None else first
+        last = oloss
+    tr.close()
+    assert last < 0.5 * first, (first, last)   # the curve actually moves: 6.25 -> about 1.7 (the batches repeat every 16 steps)
+    assert worst <= 2e-2, worst
+
+
 def test_muon_hybrid_step_matches_the_oracle_grouping(be, golden_dir):
     """Trainer semantics: Muon NS5 on rank-2 hidden weights, AdamW without decay on the embedding and vectors, clip 1.0."""
     params, _ = load(golden_dir / "tiny/trace_ns5_f32.safetensors")
