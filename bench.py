@@ -196,12 +196,13 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     be = CudaBackend(local_rank, 150 << 30)
     spec = ModelSpec(**spec_kwargs())
     cfg = TrainConfig(autocast_bf16=True, optimizer="adamw", adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=0.0, loss_seed=1.0 / world)
-    tr = Trainer(be, spec, cfg, BATCH, SEQ)
+    batch = args.batch   # 32 (the workload); smaller only for profiler captures, and the line then says so
+    tr = Trainer(be, spec, cfg, batch, SEQ)
     tr.set_params(init_weights(tr.params, 0))  # identical weights on every rank
     reducer = BucketAllReduce(be, tr, torch.device("cuda", local_rank)) if world > 1 else None
 
     n_batches = 4
-    batches = token_batches(n_batches, BATCH, SEQ, spec.vocab, 1 + rank)  # a distinct id stream per rank
+    batches = token_batches(n_batches, batch, SEQ, spec.vocab, 1 + rank)  # a distinct id stream per rank
     dev = [(be.upload(x), be.upload(y)) for x, y in batches]
     pinned = []
     for x, y in batches:
@@ -262,17 +263,17 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         step_e2e(0)
         e2e_ms, _ = timed(step_e2e, args.steps)
 
-    tokens = BATCH * SEQ * world
+    tokens = batch * SEQ * world
     value = tokens * args.steps / (ms / 1000.0)
     pk, pk_kind = peaks()
     fpt = spec.flops_per_token(SEQ)
     line = {
         "metric": "nanolab_gpt_124m_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(world),
+        "config": workload_config(world) if batch == BATCH else {"workload": f"PROFILER CASE, not the benchmark workload: micro-batch {batch}"},
         "mfu": value * fpt / (world * pk["bf16_tflops"] * 1e12), "mfu_vs_sustained": value * fpt / (world * pk["bf16_tflops_sustained"] * 1e12),
         "flops_per_token": fpt, "final_loss": rep.loss if rep else None,
-        "e2e": {"value": tokens * args.steps / (e2e_ms / 1000.0) if e2e_ms else None, "unit": "tokens/s", "h2d_bytes_per_step": 2 * BATCH * SEQ * 4,
+        "e2e": {"value": tokens * args.steps / (e2e_ms / 1000.0) if e2e_ms else None, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * SEQ * 4,
                 "d2h_bytes_per_step": 12 + 8},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
@@ -345,6 +346,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the bounded CPU sample (the default run reports it)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="micro-batch per GPU; anything but 32 is a reduced case for profiler captures only")
     ap.add_argument("--no-sdpa", action="store_true", help="skip the standalone attention case [8,16,4096,128]")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (used for profiler captures)")
     args = ap.parse_args()

@@ -32,47 +32,50 @@ template <int TPR> __device__ __forceinline__ float row_sum(float v) {
 }
 
 // y = rope(rms_norm(x) * w). x, y: [tokens, heads, dh] with a token stride (so a column slice of a wider buffer works);
-// TPR = dh / 16 threads per row, each owning columns [8 part, 8 part + 8) of both halves, i.e. whole rotation pairs.
+// TPR = dh / 16 threads per token, each owning columns [8 part, 8 part + 8) of both halves, i.e. whole rotation pairs,
+// and walking the heads: the weight, cosine and sine values it needs are the same for every head of its token.
 template <int TPR>
 __global__ void qk_norm_rope_forward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
-                                            const float* __restrict__ sin_t, bf16* __restrict__ y, int64_t ys, int64_t rows, int heads, int time, float eps) {
+                                            const float* __restrict__ sin_t, bf16* __restrict__ y, int64_t ys, int64_t tokens, int heads, int time, float eps) {
   constexpr int DH = 16 * TPR, HALF = 8 * TPR;
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int part = (int)(gid % TPR);
-  const int64_t row_raw = gid / TPR;
-  const bool live = row_raw < rows;
-  const int64_t row = live ? row_raw : rows - 1;
-  const int64_t token = row / heads;
-  const int head = (int)(row % heads), t = (int)(token % time), c0 = part * 8;
-  const bf16* src = x + token * xs + (int64_t)head * DH;
-  float a[8], b[8], wa[8], wb[8], c1[8], c2[8], s1[8], s2[8];
-  load8(src + c0, a); load8(src + HALF + c0, b);
+  const int64_t tok_raw = gid / TPR;
+  const bool live = tok_raw < tokens;
+  const int64_t token = live ? tok_raw : tokens - 1;
+  const int t = (int)(token % time), c0 = part * 8;
+  float wa[8], wb[8], c1[8], c2[8], s1[8], s2[8];
   load8f(w + c0, wa); load8f(w + HALF + c0, wb);
   load8f(cos_t + (int64_t)t * DH + c0, c1); load8f(cos_t + (int64_t)t * DH + HALF + c0, c2);
   load8f(sin_t + (int64_t)t * DH + c0, s1); load8f(sin_t + (int64_t)t * DH + HALF + c0, s2);
-  float ss = 0.0f;
+  const bf16* src = x + token * xs + c0;
+  bf16* dst = y + token * ys + c0;
+#pragma unroll 4
+  for (int head = 0; head < heads; ++head) {
+    float a[8], b[8];
+    load8(src + head * DH, a); load8(src + head * DH + HALF, b);
+    float ss = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-  ss = row_sum<TPR>(ss);
-  const float rstd = 1.0f / sqrtf(ss / (float)DH + eps);
-  float y1[8], y2[8];
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    ss = row_sum<TPR>(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)DH + eps);
+    float y1[8], y2[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float an = a[i] * rstd * wa[i], bn = b[i] * rstd * wb[i];
-    y1[i] = an * c1[i] - bn * s1[i];
-    y2[i] = bn * c2[i] + an * s2[i];
-  }
-  if (live) {
-    bf16* dst = y + token * ys + (int64_t)head * DH;
-    store8(dst + c0, y1); store8(dst + HALF + c0, y2);
+    for (int i = 0; i < 8; ++i) {
+      const float an = a[i] * rstd * wa[i], bn = b[i] * rstd * wb[i];
+      y1[i] = an * c1[i] - bn * s1[i];
+      y2[i] = bn * c2[i] + an * s2[i];
+    }
+    if (live) { store8(dst + head * DH, y1); store8(dst + head * DH + HALF, y2); }
   }
 }
 
-// Backward of the above from the saved pre-norm x: rope backward, then RMSNorm backward; dW partials per block.
+// Backward of the above from the saved pre-norm x: rope backward, then RMSNorm backward; dW partials per block. The same
+// thread-per-(token, part) walk over the heads; the weight-gradient terms accumulate in registers across heads and tokens.
 template <int TPR>
 __global__ void qk_norm_rope_backward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
                                              const float* __restrict__ sin_t, const bf16* __restrict__ gy, int64_t gys, bf16* __restrict__ gx, int64_t gxs,
-                                             float* __restrict__ part_out, int64_t rows, int heads, int time, float eps) {
+                                             float* __restrict__ part_out, int64_t tokens, int heads, int time, float eps) {
   constexpr int DH = 16 * TPR, HALF = 8 * TPR;
   extern __shared__ float red[];  // [threads][16]
   const int part = threadIdx.x % TPR;
@@ -81,44 +84,47 @@ __global__ void qk_norm_rope_backward_kernel(const bf16* __restrict__ x, int64_t
   load8f(w + c0, wa); load8f(w + HALF + c0, wb);
 #pragma unroll
   for (int i = 0; i < 8; ++i) { dwa[i] = 0.0f; dwb[i] = 0.0f; }
-  const int64_t rows_per_pass = (int64_t)gridDim.x * (blockDim.x / TPR);
-  const int64_t passes = (rows + rows_per_pass - 1) / rows_per_pass;
+  const int64_t tok_per_pass = (int64_t)gridDim.x * (blockDim.x / TPR);
+  const int64_t passes = (tokens + tok_per_pass - 1) / tok_per_pass;
   for (int64_t pass = 0; pass < passes; ++pass) {
-    const int64_t row_raw = pass * rows_per_pass + (int64_t)blockIdx.x * (blockDim.x / TPR) + threadIdx.x / TPR;
-    const bool live = row_raw < rows;
-    const int64_t row = live ? row_raw : rows - 1;
-    const int64_t token = row / heads;
-    const int head = (int)(row % heads), t = (int)(token % time);
-    float a[8], b[8], ga[8], gb[8], c1[8], c2[8], s1[8], s2[8];
-    load8(x + token * xs + (int64_t)head * DH + c0, a); load8(x + token * xs + (int64_t)head * DH + HALF + c0, b);
-    load8(gy + token * gys + (int64_t)head * DH + c0, ga); load8(gy + token * gys + (int64_t)head * DH + HALF + c0, gb);
+    const int64_t tok_raw = pass * tok_per_pass + (int64_t)blockIdx.x * (blockDim.x / TPR) + threadIdx.x / TPR;
+    const bool live = tok_raw < tokens;
+    const int64_t token = live ? tok_raw : tokens - 1;
+    const int t = (int)(token % time);
+    float c1[8], c2[8], s1[8], s2[8];
     load8f(cos_t + (int64_t)t * DH + c0, c1); load8f(cos_t + (int64_t)t * DH + HALF + c0, c2);
     load8f(sin_t + (int64_t)t * DH + c0, s1); load8f(sin_t + (int64_t)t * DH + HALF + c0, s2);
-    float ss = 0.0f;
+    const bf16* xsrc = x + token * xs + c0;
+    const bf16* gsrc = gy + token * gys + c0;
+    bf16* dst = gx + token * gxs + c0;
+#pragma unroll 2
+    for (int head = 0; head < heads; ++head) {
+      float a[8], b[8], ga[8], gb[8];
+      load8(xsrc + head * DH, a); load8(xsrc + head * DH + HALF, b);
+      load8(gsrc + head * DH, ga); load8(gsrc + head * DH + HALF, gb);
+      float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-    ss = row_sum<TPR>(ss);
-    const float rstd = 1.0f / sqrtf(ss / (float)DH + eps);
-    float da[8], db[8], dot = 0.0f;
+      for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+      ss = row_sum<TPR>(ss);
+      const float rstd = 1.0f / sqrtf(ss / (float)DH + eps);
+      float da[8], db[8], dot = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      da[i] = ga[i] * c1[i] + gb[i] * s2[i];    // d/d(an): rope backward (ojas-cpu/src/norm.rs:303-306)
-      db[i] = -ga[i] * s1[i] + gb[i] * c2[i];
-      a[i] *= rstd; b[i] *= rstd;               // x hat
-      dot += (da[i] * wa[i]) * a[i] + (db[i] * wb[i]) * b[i];
-    }
-    dot = row_sum<TPR>(dot);
-    const float mean = dot / (float)DH;
-    float oa[8], ob[8];
+      for (int i = 0; i < 8; ++i) {
+        da[i] = ga[i] * c1[i] + gb[i] * s2[i];    // d/d(an): rope backward (ojas-cpu/src/norm.rs:303-306)
+        db[i] = -ga[i] * s1[i] + gb[i] * c2[i];
+        a[i] *= rstd; b[i] *= rstd;               // x hat
+        dot += (da[i] * wa[i]) * a[i] + (db[i] * wb[i]) * b[i];
+      }
+      dot = row_sum<TPR>(dot);
+      const float mean = dot / (float)DH;
+      float oa[8], ob[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      oa[i] = (da[i] * wa[i] - a[i] * mean) * rstd;
-      ob[i] = (db[i] * wb[i] - b[i] * mean) * rstd;
-      if (live) { dwa[i] += da[i] * a[i]; dwb[i] += db[i] * b[i]; }
-    }
-    if (live) {
-      bf16* dst = gx + token * gxs + (int64_t)head * DH;
-      store8(dst + c0, oa); store8(dst + HALF + c0, ob);
+      for (int i = 0; i < 8; ++i) {
+        oa[i] = (da[i] * wa[i] - a[i] * mean) * rstd;
+        ob[i] = (db[i] * wb[i] - b[i] * mean) * rstd;
+        if (live) { dwa[i] += da[i] * a[i]; dwb[i] += db[i] * b[i]; }
+      }
+      if (live) { store8(dst + head * DH, oa); store8(dst + head * DH + HALF, ob); }
     }
   }
 #pragma unroll
@@ -360,6 +366,39 @@ __global__ void rms_backward_rows_kernel(const float* __restrict__ x, const floa
   }
 }
 
+// ---- RMSNorm forward over the f32 residual stream to a bf16 operand, 128-bit accesses (a warp per row, lane l owns float4
+// columns 4 (l + 32 j)); optionally also copies the row into the stream's next buffer.
+template <int J>
+__global__ void rms_forward_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, bf16* __restrict__ y, float* __restrict__ copy, int64_t rows,
+                                        float eps, uint32_t* fault) {
+  constexpr int DIM = 128 * J;
+  const int lane = threadIdx.x & 31;
+  float4 wv[J];
+#pragma unroll
+  for (int j = 0; j < J; ++j) wv[j] = *reinterpret_cast<const float4*>(w + 4 * (lane + 32 * j));
+  const int64_t rstride = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += rstride) {
+    const float* xr = x + row * DIM;
+    float4 xv[J];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      xv[j] = *reinterpret_cast<const float4*>(xr + 4 * (lane + 32 * j));
+      ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+    }
+    ss = row_sum<32>(ss);
+    const float denom = ss / (float)DIM + eps;
+    const float rstd = 1.0f / sqrtf(denom);
+    if (!(isfinite(denom) && denom > 0.0f && isfinite(rstd))) { if (lane == 0) raise_fault(fault, OP_RMS_NORM); }
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = 4 * (lane + 32 * j);
+      *reinterpret_cast<uint2*>(y + row * DIM + c) = make_uint2(pack2(xv[j].x * rstd * wv[j].x, xv[j].y * rstd * wv[j].y), pack2(xv[j].z * rstd * wv[j].z, xv[j].w * rstd * wv[j].w));
+      if (copy) *reinterpret_cast<float4*>(copy + row * DIM + c) = xv[j];
+    }
+  }
+}
+
 template <class F> ojc_status dispatch_tpr(const char* op, int dh, F&& f) {
   switch (dh) {
     case 16: return f(std::integral_constant<int, 1>());
@@ -382,8 +421,8 @@ ojc_status qk_norm_rope_forward(ojc_backend* be, const bf16* x, int64_t xs, cons
   if (rows == 0) return OJC_OK;
   return dispatch_tpr(op, dh, [&](auto tpr) {
     constexpr int TPR = decltype(tpr)::value;
-    const int64_t threads = rows * TPR;
-    qk_norm_rope_forward_kernel<TPR><<<(unsigned)((threads + 255) / 256), 256, 0, be->stream>>>(x, xs, w, cos_t, sin_t, y, ys, rows, heads, time, eps);
+    const int64_t threads = tokens * TPR;   // one thread per (token, 16-column part), walking the heads
+    qk_norm_rope_forward_kernel<TPR><<<(unsigned)((threads + 127) / 128), 128, 0, be->stream>>>(x, xs, w, cos_t, sin_t, y, ys, tokens, heads, time, eps);
     OJC_LAUNCHED(be, op);
     return OJC_OK;
   });
@@ -396,12 +435,12 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
   if (rows == 0) return OJC_OK;
   return dispatch_tpr(op, dh, [&](auto tpr) {
     constexpr int TPR = decltype(tpr)::value;
-    const int rows_per_block = 256 / TPR;
-    int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+    const int tokens_per_block = 128 / TPR;
+    int64_t blocks = (tokens + tokens_per_block - 1) / tokens_per_block;
     if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
     void* part = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)blocks * dh * 4, &part));
-    qk_norm_rope_backward_kernel<TPR><<<(unsigned)blocks, 256, 256 * 16 * 4, be->stream>>>(x, xs, w, cos_t, sin_t, gy, gys, gx, gxs, (float*)part, rows, heads, time, eps);
+    qk_norm_rope_backward_kernel<TPR><<<(unsigned)blocks, 128, 128 * 16 * 4, be->stream>>>(x, xs, w, cos_t, sin_t, gy, gys, gx, gxs, (float*)part, tokens, heads, time, eps);
     OJC_LAUNCHED(be, op);
     fused_column_sum_kernel<<<(dh + 31) / 32, 256, 0, be->stream>>>((const float*)part, gw, (int)blocks, dh);
     OJC_LAUNCHED(be, op);
@@ -492,6 +531,20 @@ ojc_status rms_backward_rows(ojc_backend* be, const float* x, const float* w, co
   else if (dim == 2048) OJC_RMS_ROWS(16);
   else return ojc_fail(OJC_ERR_UNSUPPORTED, op, "row width outside the vectorized forms");
 #undef OJC_RMS_ROWS
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+ojc_status rms_forward_rows(ojc_backend* be, const float* x, const float* w, bf16* y, float* copy, int64_t rows, int64_t dim, float eps) {
+  const char* op = "rms_norm_forward";
+  const int grid = elementwise_grid(be, rows * 32, 256);
+#define OJC_RMS_FWD(J) rms_forward_rows_kernel<J><<<grid, 256, 0, be->stream>>>(x, w, y, copy, rows, eps, be->fault_dev)
+  if (dim == 512) OJC_RMS_FWD(4);
+  else if (dim == 768) OJC_RMS_FWD(6);
+  else if (dim == 1024) OJC_RMS_FWD(8);
+  else if (dim == 2048) OJC_RMS_FWD(16);
+  else return ojc_fail(OJC_ERR_UNSUPPORTED, op, "row width outside the vectorized forms");
+#undef OJC_RMS_FWD
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }

@@ -36,3 +36,4 @@ ojc_status vres_root_backward(ojc_backend* be, const float* acc, const bf16* g, 
 bool rms_backward_rows_supported(int64_t dim);
 ojc_status rms_backward_rows(ojc_backend* be, const float* x, const float* w, const float* gy, float* gx, bf16* gx_b, float* part, int64_t rows, int64_t dim,
                              float eps, bool accumulate_gx, int blocks);
+ojc_status rms_forward_rows(ojc_backend* be, const float* x, const float* w, bf16* y, float* copy, int64_t rows, int64_t dim, float eps);

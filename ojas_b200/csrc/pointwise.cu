@@ -290,6 +290,9 @@ ojc_status rms_forward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_tens
   if (n == 0 || dim == 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
   const int64_t rows = n / dim;
   if (copy && x->dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "the row copy is F32 like its source");
+  if (x->dtype == OJC_F32 && y->dtype == OJC_BF16 && rms_backward_rows_supported(dim) &&
+      ((reinterpret_cast<uintptr_t>(x->data) | reinterpret_cast<uintptr_t>(y->data) | reinterpret_cast<uintptr_t>(w->data) | reinterpret_cast<uintptr_t>(copy)) & 15) == 0)
+    return rms_forward_rows(be, (const float*)x->data, (const float*)w->data, (bf16*)y->data, copy, rows, dim, eps);   // the bf16 step's residual-stream form
   return dispatch_float(op, x->dtype, [&](auto tx) { return dispatch_float(op, y->dtype, [&](auto to) {
     return dispatch_iters(op, dim, [&](auto it) {
       using TX = decltype(tx); using TO = decltype(to); constexpr int IT = decltype(it)::value;
