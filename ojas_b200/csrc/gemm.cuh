@@ -21,3 +21,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
 // Tensor-core kernel when both operands are bf16 and eligible, the f32 tier otherwise.
 ojc_status gemm_auto(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
                      int64_t n, int64_t k, float alpha, bool accumulate, const float* residual);
+// `batch` independent products of one shape on the tensor-core kernels: matrix i of A / B / C starts a_bs / b_bs / c_bs elements
+// after matrix i - 1 (the operand views describe matrix 0). No residual operand; at least 64 output columns.
+ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
+                           int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual);

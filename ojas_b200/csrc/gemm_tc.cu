@@ -52,25 +52,27 @@ struct TcArgs {
   int splits, kblocks_per_split;
   float* partial;           // [splits][m][n] when splits > 1
   uint32_t* fault;
+  int batch;                // independent matrices: a unit is (matrix, tile, split); batch > 1 needs tma_store and splits == 1
   int tma_store;            // finished blocks leave through TMA tile stores (no residual operand; split partials need m % 32 == 0)
   int tiles_n_fast;         // tile order: 1 = neighbouring CTAs share an A row block (few column tiles), 0 = they share a B column block
 };
 
 // Stores of finished 32-row blocks: TMA tile stores out of swizzled staging rows (the hardware clips at the matrix edge),
 // or the adding form for C += tile.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+// (every map is 3-D: columns, rows, matrix of the batch)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
 }
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Drains one warp's share of a finished accumulator tile: TMEM lanes [32 quarter, +32) x columns [col_begin, col_end)
-// starting at `tsrc`, destined for rows row_base.. and columns col_tile0.. of C (or of the split's partial).
-__device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int col_tile0, int split, int lane,
+// starting at `tsrc`, destined for rows row_base.. and columns col_tile0.. of matrix bz of C (or of the split's partial).
+__device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int col_tile0, int split, int bz, int lane,
                                            int col_begin, int col_end, uint8_t* stage_bytes, uint32_t stage_addr) {
   float* stage = reinterpret_cast<float*>(stage_bytes);
   if (args.tma_store) {
@@ -107,8 +109,8 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
       __syncwarp();
       const int x = col_tile0 + c0;
       if (lane == 0 && x < args.n && row_base < args.m) {
-        if (args.accumulate && args.splits == 1) tma_reduce_add_2d(&tmap_c, stage_addr, x, y);
-        else tma_store_2d(&tmap_c, stage_addr, x, y);
+        if (args.accumulate && args.splits == 1) tma_reduce_add_3d(&tmap_c, stage_addr, x, y, bz);
+        else tma_store_3d(&tmap_c, stage_addr, x, y, bz);
         bulk_commit();
       }
     }
@@ -175,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (args.m + BM - 1) / BM, tiles_n = (args.n + BN - 1) / BN;
-  const int units = tiles_m * tiles_n * args.splits;
+  const int units_per_matrix = tiles_m * tiles_n * args.splits, units = units_per_matrix * args.batch;
   const int kblocks_total = (args.k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -198,7 +200,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x) {
-        const int split = u % args.splits, tile = u / args.splits;
+        const int bz = u / units_per_matrix, ub = u - bz * units_per_matrix;
+        const int split = ub % args.splits, tile = ub / args.splits;
         const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -206,10 +209,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t a_dst = tiles_base + s * STAGE_BYTES, b_dst = a_dst + A_TILE_BYTES;
-          if (!args.a_mn_major) tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * BK, tm * BM);
-          else for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmap_a, full_bar(s), tm * BM + j * 64, kb * BK);
-          if (!args.b_mn_major) tma_load_2d(b_dst, &tmap_b, full_bar(s), kb * BK, tn * BN);
-          else for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmap_b, full_bar(s), tn * BN + j * 64, kb * BK);
+          if (!args.a_mn_major) tma_load_3d(a_dst, &tmap_a, full_bar(s), kb * BK, tm * BM, bz);
+          else for (int j = 0; j < BM / 64; ++j) tma_load_3d(a_dst + j * (BK * 128), &tmap_a, full_bar(s), tm * BM + j * 64, kb * BK, bz);
+          if (!args.b_mn_major) tma_load_3d(b_dst, &tmap_b, full_bar(s), kb * BK, tn * BN, bz);
+          else for (int j = 0; j < BN / 64; ++j) tma_load_3d(b_dst + j * (BK * 128), &tmap_b, full_bar(s), tn * BN + j * 64, kb * BK, bz);
         }
       }
     }
@@ -223,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t a_step = args.a_mn_major ? 2048 : 32, b_step = args.b_mn_major ? 2048 : 32;
       uint32_t it = 0, local = 0;
       for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x, ++local) {
-        const int split = u % args.splits;
+        const int split = (u % units_per_matrix) % args.splits;
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
         const int acc = local & 1;
         if (!mbar_wait(tempty_bar(acc), ((local >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
@@ -255,14 +258,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
     uint32_t local = 0;
     for (int u = blockIdx.x; u < units && !*abort_flag; u += gridDim.x, ++local) {
-      const int split = u % args.splits, tile = u / args.splits;
+      const int bz = u / units_per_matrix, ub = u - bz * units_per_matrix;
+      const int split = ub % args.splits, tile = ub / args.splits;
       const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
       const int acc = local & 1;
       if (!mbar_wait(tfull_bar(acc), (local >> 1) & 1, args.fault, abort_flag)) break;
       fence_after();
       const int row_base = tm * BM + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      drain_tile(args, tmap_c, tsrc, row_base, tn * BN, split, lane, col_begin, col_end, stage_bytes, stage_addr);
+      drain_tile(args, tmap_c, tsrc, row_base, tn * BN, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -312,7 +316,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const uint32_t rank = cluster_ctarank();                          // 0: the CTA that issues the MMAs
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
   const int tiles_m = (args.m + BM2 - 1) / BM2, tiles_n = (args.n + BN2 - 1) / BN2;
-  const int units = tiles_m * tiles_n * args.splits;
+  const int units_per_matrix = tiles_m * tiles_n * args.splits, units = units_per_matrix * args.batch;
   const int kblocks_total = (args.k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -336,7 +340,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       for (int u = pair; u < units; u += npairs) {
-        const int split = u % args.splits, tile = u / args.splits;
+        const int bz = u / units_per_matrix, ub = u - bz * units_per_matrix;
+        const int split = ub % args.splits, tile = ub / args.splits;
         const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
         const int row0 = tm * BM2 + (int)rank * 128, col0 = tn * BN2 + (int)rank * 128;
@@ -346,10 +351,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           if (!mbar_wait(empty_bar(s), ((it / STAGES2) & 1) ^ 1, args.fault, abort_flag)) { ok = false; break; }
           if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE2_BYTES);
           const uint32_t a_dst = tiles_base + s * STAGE2_BYTES, b_dst = a_dst + A2_TILE_BYTES;
-          if (!args.a_mn_major) tma_load_2d_pair(a_dst, &tmap_a, full_bar(s), kb * BK, row0);
-          else for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), &tmap_a, full_bar(s), row0 + j * 64, kb * BK);
-          if (!args.b_mn_major) tma_load_2d_pair(b_dst, &tmap_b, full_bar(s), kb * BK, col0);
-          else for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * (BK * 128), &tmap_b, full_bar(s), col0 + j * 64, kb * BK);
+          if (!args.a_mn_major) tma_load_3d_pair(a_dst, &tmap_a, full_bar(s), kb * BK, row0, bz);
+          else for (int j = 0; j < 2; ++j) tma_load_3d_pair(a_dst + j * (BK * 128), &tmap_a, full_bar(s), row0 + j * 64, kb * BK, bz);
+          if (!args.b_mn_major) tma_load_3d_pair(b_dst, &tmap_b, full_bar(s), kb * BK, col0, bz);
+          else for (int j = 0; j < 2; ++j) tma_load_3d_pair(b_dst + j * (BK * 128), &tmap_b, full_bar(s), col0 + j * 64, kb * BK, bz);
         }
         if (!ok) break;
       }
@@ -362,7 +367,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t a_step = args.a_mn_major ? 2048 : 32, b_step = args.b_mn_major ? 2048 : 32;
       uint32_t it = 0, local = 0;
       for (int u = pair; u < units; u += npairs, ++local) {
-        const int split = u % args.splits;
+        const int split = (u % units_per_matrix) % args.splits;
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
         const int acc = local & 1;
         if (!mbar_wait(tempty_bar(acc), ((local >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
@@ -391,14 +396,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
     uint32_t local = 0;
     for (int u = pair; u < units; u += npairs, ++local) {
-      const int split = u % args.splits, tile = u / args.splits;
+      const int bz = u / units_per_matrix, ub = u - bz * units_per_matrix;
+      const int split = ub % args.splits, tile = ub / args.splits;
       const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
       const int acc = local & 1;
       if (!mbar_wait(tfull_bar(acc), (local >> 1) & 1, args.fault, abort_flag)) break;
       fence_after();
       const int row_base = tm * BM2 + (int)rank * 128 + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
-      drain_tile(args, tmap_c, tsrc, row_base, tn * BN2, split, lane, col_begin, col_end, stage_bytes, stage_addr);
+      drain_tile(args, tmap_c, tsrc, row_base, tn * BN2, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
@@ -442,15 +448,18 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// inner = extent of the contiguous axis, outer = the other one, ld = elements between outer steps.
+// inner = extent of the contiguous axis, outer = the other one, ld = elements between outer steps; `batch` matrices
+// `batch_stride` elements apart form the third dimension (1 and any stride for a single matrix).
 ojc_status make_tmap(ojc_backend* be, const char* op, CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
-                     uint32_t box_outer, bool f32 = false) {
+                     uint32_t box_outer, bool f32 = false, uint64_t batch = 1, uint64_t batch_stride = 0) {
   if (!be->tmap_encode) return ojc_fail(OJC_ERR_BACKEND, op, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[2] = {inner, outer};
-  cuuint64_t gstride[1] = {ld * (f32 ? 4 : 2)};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estride[2] = {1, 1};
-  CUresult r = ((EncodeTiledFn)be->tmap_encode)(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+  const uint64_t es = f32 ? 4 : 2;
+  if (batch <= 1) { batch = 1; batch_stride = ld * outer; }
+  cuuint64_t gdim[3] = {inner, outer, batch};
+  cuuint64_t gstride[2] = {ld * es, batch_stride * es};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = ((EncodeTiledFn)be->tmap_encode)(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstride, box, estride,
                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return ojc_fail(OJC_ERR_BACKEND, op, "cuTensorMapEncodeTiled refused the operand (code " + std::to_string((int)r) + ")");
@@ -484,8 +493,17 @@ bool gemm_tc_eligible(const GemmOperand& a, const GemmOperand& b, const void* c,
 
 ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
                    int64_t n, int64_t k, float alpha, bool accumulate, const float* residual) {
+  return gemm_tc_batched(be, op, a, b, c, c_dtype, ldc, m, n, k, 1, 0, 0, 0, alpha, accumulate, residual);
+}
+
+// `batch` independent products of the same shape; matrix i of A / B / C starts a_bs / b_bs / c_bs elements after matrix i - 1.
+ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
+                           int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual) {
   if (!gemm_tc_eligible(a, b, c, c_dtype, ldc, m, n, k)) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "operands break the tensor-core kernel's alignment rules");
   if (accumulate && c_dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "accumulation needs an F32 output");
+  if (batch < 1 || batch > 65535) return ojc_fail(OJC_ERR_SHAPE, op, "batch count out of range");
+  if (batch > 1 && (a_bs % 8 != 0 || b_bs % 8 != 0 || c_bs % 8 != 0 || residual || n < 64))
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "a batched product needs 16-byte aligned matrix strides, no residual operand and at least 64 output columns");
   int amn, bmn; int64_t lda, ldb;
   operand_ok(a, true, &amn, &lda); operand_ok(b, false, &bmn, &ldb);
   // Two-SM tiles (256 x 256 per CTA pair) whenever the output is at least one such tile; the one-SM kernel keeps the rest.
@@ -503,23 +521,23 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   const bool two_sm = max_pairs > 0 && m >= BM2 && n >= BN2;
   const int tile_m = two_sm ? BM2 : BM, tile_n = two_sm ? BN2 : BN, workers = two_sm ? max_pairs : be->sm_count;
   CUtensorMap ta, tb;
-  if (!amn) OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)k, (uint64_t)m, (uint64_t)lda, 64, 128));
-  else OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)m, (uint64_t)k, (uint64_t)lda, 64, BK));
-  if (!bmn) OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, 64, two_sm ? 128 : BN));
-  else OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, 64, BK));
+  if (!amn) OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)k, (uint64_t)m, (uint64_t)lda, 64, 128, false, batch, a_bs));
+  else OJC_TRY(make_tmap(be, op, &ta, a.ptr, (uint64_t)m, (uint64_t)k, (uint64_t)lda, 64, BK, false, batch, a_bs));
+  if (!bmn) OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, 64, two_sm ? 128 : BN, false, batch, b_bs));
+  else OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, 64, BK, false, batch, b_bs));
 
   static bool attr_set = false;
   if (!attr_set) {
     OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
     attr_set = true;
   }
-  const int tiles = (int)(((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n));
+  const int tiles = (int)(((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n) * batch);   // units before any split
   const int kblocks = (int)((k + BK - 1) / BK);
   // Split the reduction axis when the output tiles alone leave SMs idle: estimate each split count's time as the math at
   // the wave efficiency its units reach plus the partial round trip through memory, and take the cheapest (each split
   // keeps at least 8 k-blocks).
   int splits = 1;
-  if (kblocks >= 16) {
+  if (kblocks >= 16 && batch == 1) {
     const double flops = 2.0 * (double)m * (double)n * (double)k;
     double best = 1e30;
     for (int sp = 1; sp <= 16 && kblocks / sp >= 8; ++sp) {
@@ -536,7 +554,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   args.m = (int)m; args.n = (int)n; args.k = (int)k;
   args.a_mn_major = amn; args.b_mn_major = bmn;
   args.alpha = alpha; args.accumulate = accumulate ? 1 : 0; args.residual = residual;
-  args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev;
+  args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev; args.batch = (int)batch;
   if (splits > 1) {
     void* ws = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)splits * m * n * 4, &ws));
@@ -548,12 +566,14 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
   CUtensorMap tc = ta;   // unused unless tma_store
   if (args.tma_store) {
     if (splits > 1) OJC_TRY(make_tmap(be, op, &tc, args.partial, (uint64_t)n, (uint64_t)splits * (uint64_t)m, (uint64_t)n, 32, 32, true));
-    else if (args.c_bf16) OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 64, 32, false));
-    else OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 32, 32, true));
+    else if (args.c_bf16) OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 64, 32, false, batch, c_bs));
+    else OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 32, 32, true, batch, c_bs));
+  } else if (batch > 1) {
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "a batched product needs the tile-store epilogue");
   }
   int grid = tiles * splits < workers ? tiles * splits : workers;
   if (two_sm) grid *= 2;
-  ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k};
+  ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k * (double)batch};
   if (be->profile_gemm) {
     if (!be->event_pool.empty()) { sample.start = be->event_pool.back().first; sample.stop = be->event_pool.back().second; be->event_pool.pop_back(); }
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }

@@ -78,11 +78,18 @@ __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
   }
 }
 
+// Muon works on groups of same-shape matrices: blockIdx.y picks the matrix, the pointer table travels by value.
+constexpr int MUON_MAX_BATCH = 48;
+struct MuonBatch { const float* g[MUON_MAX_BATCH]; float* mom[MUON_MAX_BATCH]; float* p[MUON_MAX_BATCH]; bf16* mirror[MUON_MAX_BATCH]; };
+
 // buf = mu * mom + g; u = nesterov ? fma(mu, buf, g) : buf; mom = buf (ojas-cpu/src/optim.rs:684-712).
-// Also the block partial of sum u^2 (of the bf16-rounded u when ns5 runs in bf16).
-__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ mom, float* __restrict__ u, int64_t n, float mu, int nesterov,
-                                     int round_u, const float* __restrict__ grad_scale, double* __restrict__ part, uint32_t* fault) {
+// Also the block partial of sum u^2 (of the bf16-rounded u when ns5 runs in bf16). u: [batch][n], part: [batch][gridDim.x].
+__global__ void muon_momentum_kernel(const MuonBatch mb, float* __restrict__ u_all, int64_t n, float mu, int nesterov, int round_u,
+                                     const float* __restrict__ grad_scale, double* __restrict__ part, uint32_t* fault) {
   __shared__ float red[32];
+  const float* __restrict__ g = mb.g[blockIdx.y];
+  float* __restrict__ mom = mb.mom[blockIdx.y];
+  float* __restrict__ u = u_all + (int64_t)blockIdx.y * n;
   float gs = 1.0f;
   if (grad_scale) { gs = grad_scale[0]; if (!(gs < 1.0f)) gs = 1.0f; }
   const int64_t base = (int64_t)blockIdx.x * NORM_CHUNK;
@@ -100,16 +107,30 @@ __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restr
     acc = fmaf(ui, ui, acc);
   }
   float t = block_sum(acc, red);
-  if (threadIdx.x == 0) { if (!isfinite(t)) raise_fault(fault, OP_MUON); part[blockIdx.x] = (double)t; }
+  if (threadIdx.x == 0) { if (!isfinite(t)) raise_fault(fault, OP_MUON); part[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = (double)t; }
+}
+
+// norm[matrix] = f32 of the f64 square root of its partial sums, added in the order norm_finish_kernel uses
+__global__ void muon_norm_kernel(const double* __restrict__ part, int64_t nparts, float* __restrict__ norm) {
+  __shared__ double red[256];
+  const double* p = part + (int64_t)blockIdx.x * nparts;
+  double acc = 0.0;
+  for (int64_t i = threadIdx.x; i < nparts; i += blockDim.x) acc += p[i];
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = blockDim.x / 2; s > 0; s >>= 1) { if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s]; __syncthreads(); }
+  if (threadIdx.x == 0) norm[blockIdx.x] = (float)sqrt(red[0]);
 }
 
 // X = u / (norm + 1e-7), written in the wide orientation (transposed when rows > cols), as TX (f32 or bf16).
 // In bf16 mode the norm, norm + eps and the quotient are each rounded (ojas-cpu/src/optim.rs:893-910).
 template <class TX>
-__global__ void muon_normalize_kernel(const float* __restrict__ u, const float* __restrict__ norm, TX* __restrict__ x, int rows, int cols, int tall, int bf16_mode) {
-  const float nrm = norm[0];
-  const float denom = bf16_mode ? round_bf16(round_bf16(nrm) + 1e-7f) : nrm + 1e-7f;
+__global__ void muon_normalize_kernel(const float* __restrict__ u_all, const float* __restrict__ norm, TX* __restrict__ x_all, int rows, int cols, int tall, int bf16_mode) {
   const int64_t n = (int64_t)rows * cols;
+  const float* __restrict__ u = u_all + (int64_t)blockIdx.y * n;
+  TX* __restrict__ x = x_all + (int64_t)blockIdx.y * n;
+  const float nrm = norm[blockIdx.y];
+  const float denom = bf16_mode ? round_bf16(round_bf16(nrm) + 1e-7f) : nrm + 1e-7f;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
     int64_t r = i / cols, c = i % cols;
@@ -144,9 +165,11 @@ __global__ void ns_combine_x_kernel(const T* __restrict__ x, T* __restrict__ bx,
 
 // p = fma(alpha, X, p * decay) with X read back through the transpose when the matrix was tall (optim.rs:718-736).
 template <class TX>
-__global__ void muon_apply_kernel(float* __restrict__ p, const TX* __restrict__ x, bf16* __restrict__ mirror, int rows, int cols, int tall, float alpha,
-                                  float decay, int decays, uint32_t* fault) {
+__global__ void muon_apply_kernel(const MuonBatch mb, const TX* __restrict__ x_all, int rows, int cols, int tall, float alpha, float decay, int decays, uint32_t* fault) {
   const int64_t n = (int64_t)rows * cols;
+  float* __restrict__ p = mb.p[blockIdx.y];
+  bf16* __restrict__ mirror = mb.mirror[blockIdx.y];
+  const TX* __restrict__ x = x_all + (int64_t)blockIdx.y * n;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
     int64_t r = i / cols, c = i % cols;
@@ -157,6 +180,55 @@ __global__ void muon_apply_kernel(float* __restrict__ p, const TX* __restrict__ 
     p[i] = np;
     if (mirror) mirror[i] = __float2bfloat16_rn(np);
   }
+}
+
+// The five Newton-Schulz iterations of one small matrix (r <= 32 rows after the wide orientation) inside one CTA: X lives
+// in shared memory as f32 (holding bf16-rounded values in bf16 mode), A = X X^T, A2 = A A, B = b A + c A2, X <- a X + B X,
+// with the same rounding points as the per-product path (every product and every combine rounds to bf16 in bf16 mode).
+// blockIdx.x = matrix. Dot products are warp-strided over k and added by shuffles.
+template <class TX>
+__global__ void muon_small_ns5_kernel(TX* __restrict__ x_all, int r, int c, float acoef, float bcoef, float ccoef, int bf16_mode, uint32_t* fault) {
+  extern __shared__ float sm[];
+  float* X = sm;                       // [r][c]
+  float* BX = X + (size_t)r * c;       // [r][c]
+  float* A = BX + (size_t)r * c;       // [32][33]
+  float* B = A + 32 * 33;              // [32][33]
+  TX* x = x_all + (int64_t)blockIdx.x * r * c;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int n = r * c;
+  auto rnd = [&](float v) { return bf16_mode ? round_bf16(v) : v; };
+  for (int i = tid; i < n; i += blockDim.x) X[i] = ldf(x, i);
+  __syncthreads();
+  for (int it = 0; it < 5; ++it) {
+    for (int pair = warp; pair < r * r; pair += nwarps) {          // A = X X^T
+      const int i = pair / r, j = pair % r;
+      float acc = 0.0f;
+      for (int k = lane; k < c; k += 32) acc = fmaf(X[i * c + k], X[j * c + k], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) A[i * 33 + j] = rnd(acc);
+    }
+    __syncthreads();
+    for (int e = tid; e < r * r; e += blockDim.x) {                // B = b A + c (A A)
+      const int i = e / r, j = e % r;
+      float acc = 0.0f;
+      for (int k = 0; k < r; ++k) acc = fmaf(A[i * 33 + k], A[k * 33 + j], acc);
+      const float a2 = rnd(acc), av = A[i * 33 + j];
+      B[i * 33 + j] = bf16_mode ? round_bf16(round_bf16(bcoef * av) + round_bf16(ccoef * a2)) : bcoef * av + ccoef * a2;
+    }
+    __syncthreads();
+    for (int e = tid; e < n; e += blockDim.x) {                    // X <- a X + B X
+      const int i = e / c, k = e % c;
+      float acc = 0.0f;
+      for (int j = 0; j < r; ++j) acc = fmaf(B[i * 33 + j], X[j * c + k], acc);
+      const float bx = rnd(acc), xv = X[e];
+      const float out = bf16_mode ? round_bf16(round_bf16(acoef * xv) + bx) : acoef * xv + bx;
+      if (!isfinite(out)) raise_fault(fault, OP_MUON);
+      BX[e] = out;
+    }
+    __syncthreads();
+    float* t = X; X = BX; BX = t;
+  }
+  for (int i = tid; i < n; i += blockDim.x) stf(x, i, X[i]);
 }
 
 double pow_u64(double base, uint64_t e) {  // ojas-core/src/backend.rs:244-257
@@ -229,71 +301,107 @@ ojc_status adamw_device(ojc_backend* be, float* p, const float* g, float* m, flo
   return OJC_OK;
 }
 
-uint64_t muon_scratch_bytes(int64_t rows, int64_t cols, bool bf16_mode) {
+static uint64_t muon_group_scratch_bytes(int64_t rows, int64_t cols, bool bf16_mode, int64_t batch) {
   const int64_t r = rows < cols ? rows : cols, n = rows * cols;
   const uint64_t es = bf16_mode ? 2 : 4;
   auto al = [](uint64_t b) { return (b + 255) & ~uint64_t(255); };
-  return al(n * 4) /*u*/ + 2 * al(n * es) /*x, bx*/ + 2 * al((uint64_t)r * r * es) /*A, A2*/ + al(norm_partials(n) * 8) + 256;
+  return al(batch * n * 4) /*u*/ + 2 * al(batch * n * es) /*x, bx*/ + 2 * al((uint64_t)batch * r * r * es) /*A, A2*/ + al(batch * norm_partials(n) * 8) + al(batch * 4);
 }
+uint64_t muon_scratch_bytes(int64_t rows, int64_t cols, bool bf16_mode) { return muon_group_scratch_bytes(rows, cols, bf16_mode, 1); }
 
-ojc_status muon_device(ojc_backend* be, float* p, const float* g, float* mom, bf16* mirror, int64_t rows, int64_t cols, const ojc_muon_config& cfg,
-                       const float* grad_scale_dev) {
+// One Muon NS5 step for `batch` matrices of one shape (ojas-cpu/src/optim.rs:684-985 per matrix). The element-wise phases
+// run as one launch over the group; the three products of each Newton-Schulz iteration run as batched tensor-core GEMMs
+// when the operands are bf16 and eligible, as one GEMM per matrix otherwise.
+ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* const* g, float* const* mom, bf16* const* mirror, int64_t batch, int64_t rows,
+                             int64_t cols, const ojc_muon_config& cfg, const float* grad_scale_dev) {
   const char* op = "muon_ns5_step";
   if (!std::isfinite(cfg.lr) || !std::isfinite(cfg.momentum) || !std::isfinite(cfg.weight_decay)) return ojc_fail(OJC_ERR_NON_FINITE, op, "a configuration scalar is not finite");
   if (cfg.lr < 0.0 || cfg.momentum < 0.0 || cfg.weight_decay < 0.0) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "lr, momentum or weight_decay is negative");
   if (rows <= 0 || cols <= 0) return ojc_fail(OJC_ERR_SHAPE, op, "empty tensor");
+  if (batch < 1 || batch > MUON_MAX_BATCH) return ojc_fail(OJC_ERR_SHAPE, op, "group size out of range");
   const bool bf = cfg.ns5_bf16 != 0, tall = rows > cols;
   const int64_t r = tall ? cols : rows, c = tall ? rows : cols, n = rows * cols;
   const int32_t dt = bf ? OJC_BF16 : OJC_F32;
   const uint64_t es = bf ? 2 : 4;
   auto al = [](uint64_t b) { return (b + 255) & ~uint64_t(255); };
+  MuonBatch mb{};
+  for (int64_t i = 0; i < batch; ++i) { mb.g[i] = g[i]; mb.mom[i] = mom[i]; mb.p[i] = p[i]; mb.mirror[i] = mirror ? mirror[i] : nullptr; }
   void* ws = nullptr;
-  OJC_TRY(ojc_alloc(be, muon_scratch_bytes(rows, cols, bf), &ws));
+  OJC_TRY(ojc_alloc(be, muon_group_scratch_bytes(rows, cols, bf, batch), &ws));
   char* cur = (char*)ws;
-  float* u = (float*)cur; cur += al(n * 4);
-  void* x = cur; cur += al(n * es);
-  void* bx = cur; cur += al(n * es);
-  void* am = cur; cur += al((uint64_t)r * r * es);
-  void* a2 = cur; cur += al((uint64_t)r * r * es);
-  double* part = (double*)cur; cur += al(norm_partials(n) * 8);
+  float* u = (float*)cur; cur += al(batch * n * 4);
+  void* x = cur; cur += al(batch * n * es);
+  void* bx = cur; cur += al(batch * n * es);
+  void* am = cur; cur += al((uint64_t)batch * r * r * es);
+  void* a2 = cur; cur += al((uint64_t)batch * r * r * es);
+  double* part = (double*)cur; cur += al(batch * norm_partials(n) * 8);
   float* norm = (float*)cur;
   ojc_status st = OJC_OK;
+  // C_i = A_i . B_i for every matrix of the group
+  auto product = [&](const GemmOperand& ga, const GemmOperand& gb, void* cptr, int64_t m_, int64_t n_, int64_t k_, int64_t a_bs, int64_t b_bs, int64_t c_bs) -> ojc_status {
+    if (batch > 1 && bf && n_ >= 64 && a_bs % 8 == 0 && b_bs % 8 == 0 && c_bs % 8 == 0 && gemm_tc_eligible(ga, gb, cptr, dt, n_, m_, n_, k_))
+      return gemm_tc_batched(be, op, ga, gb, cptr, dt, n_, m_, n_, k_, batch, a_bs, b_bs, c_bs, 1.0f, false, nullptr);
+    for (int64_t i = 0; i < batch; ++i) {
+      GemmOperand ai{(const char*)ga.ptr + i * a_bs * es, ga.dtype, ga.rs, ga.cs}, bi{(const char*)gb.ptr + i * b_bs * es, gb.dtype, gb.rs, gb.cs};
+      OJC_TRY(gemm_auto(be, op, ai, bi, (char*)cptr + i * c_bs * es, dt, n_, m_, n_, k_, 1.0f, false, nullptr));
+    }
+    return OJC_OK;
+  };
   auto run = [&]() -> ojc_status {
     const int64_t parts = norm_partials(n);
-    muon_momentum_kernel<<<(unsigned)parts, 256, 0, be->stream>>>(g, mom, u, n, (float)cfg.momentum, cfg.nesterov, bf ? 1 : 0, grad_scale_dev, part, be->fault_dev);
+    const unsigned nb = (unsigned)batch;
+    muon_momentum_kernel<<<dim3((unsigned)parts, nb), 256, 0, be->stream>>>(mb, u, n, (float)cfg.momentum, cfg.nesterov, bf ? 1 : 0, grad_scale_dev, part, be->fault_dev);
     OJC_LAUNCHED(be, op);
-    norm_finish_kernel<<<1, 256, 0, be->stream>>>(part, parts, -1.0f, norm);
+    muon_norm_kernel<<<nb, 256, 0, be->stream>>>(part, parts, norm);
     OJC_LAUNCHED(be, op);
-    const int grid = elementwise_grid(be, n, 256), grid_a = elementwise_grid(be, r * r, 256);
-    if (bf) muon_normalize_kernel<bf16><<<grid, 256, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, tall, 1);
-    else muon_normalize_kernel<float><<<grid, 256, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, tall, 0);
+    const int grid = elementwise_grid(be, n, 256), grid_all = elementwise_grid(be, n * batch, 256), grid_a = elementwise_grid(be, r * r * batch, 256);
+    if (bf) muon_normalize_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, tall, 1);
+    else muon_normalize_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, tall, 0);
     OJC_LAUNCHED(be, op);
     const float a = (float)3.4445, b = (float)-4.7750, cc = (float)2.0315;  // MUON_NS5_{A,B,C}, ojas-core/src/backend.rs:144-146
-    for (int it = 0; it < 5; ++it) {
+    const size_t small_smem = ((size_t)2 * r * c + 2 * 32 * 33) * 4;
+    const bool small = batch > 1 && r <= 32 && small_smem <= 200 * 1024;     // e.g. the [heads, d] gate weights: one CTA per matrix
+    if (small) {
+      static bool attr = false;
+      if (!attr) {
+        OJC_CUDA(be, cudaFuncSetAttribute(muon_small_ns5_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), op);
+        OJC_CUDA(be, cudaFuncSetAttribute(muon_small_ns5_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), op);
+        attr = true;
+      }
+      if (bf) muon_small_ns5_kernel<bf16><<<nb, 512, small_smem, be->stream>>>((bf16*)x, (int)r, (int)c, a, b, cc, 1, be->fault_dev);
+      else muon_small_ns5_kernel<float><<<nb, 512, small_smem, be->stream>>>((float*)x, (int)r, (int)c, a, b, cc, 0, be->fault_dev);
+      OJC_LAUNCHED(be, op);
+    }
+    for (int it = 0; it < 5 && !small; ++it) {
       GemmOperand xk{x, dt, c, 1}, xt{x, dt, 1, c}, xn{x, dt, c, 1};
-      OJC_TRY(gemm_auto(be, op, xk, xt, am, dt, r, r, r, c, 1.0f, false, nullptr));                       // A = X X^T
+      OJC_TRY(product(xk, xt, am, r, r, c, n, n, r * r));                                                  // A = X X^T
       GemmOperand ak{am, dt, r, 1}, an{am, dt, r, 1};
-      OJC_TRY(gemm_auto(be, op, ak, an, a2, dt, r, r, r, r, 1.0f, false, nullptr));                      // A2 = A A
-      if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r, b, cc, 1);
-      else ns_combine_a_kernel<float><<<grid_a, 256, 0, be->stream>>>((const float*)am, (float*)a2, r * r, b, cc, 0);
+      OJC_TRY(product(ak, an, a2, r, r, r, r * r, r * r, r * r));                                          // A2 = A A
+      if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r * batch, b, cc, 1);
+      else ns_combine_a_kernel<float><<<grid_a, 256, 0, be->stream>>>((const float*)am, (float*)a2, r * r * batch, b, cc, 0);
       OJC_LAUNCHED(be, op);
       GemmOperand bk{a2, dt, r, 1};
-      OJC_TRY(gemm_auto(be, op, bk, xn, bx, dt, c, r, c, r, 1.0f, false, nullptr));                      // BX = B X
-      if (bf) ns_combine_x_kernel<bf16><<<grid, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n, a, 1, be->fault_dev);
-      else ns_combine_x_kernel<float><<<grid, 256, 0, be->stream>>>((const float*)x, (float*)bx, n, a, 0, be->fault_dev);
+      OJC_TRY(product(bk, xn, bx, r, c, r, r * r, n, n));                                                  // BX = B X
+      if (bf) ns_combine_x_kernel<bf16><<<grid_all, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n * batch, a, 1, be->fault_dev);
+      else ns_combine_x_kernel<float><<<grid_all, 256, 0, be->stream>>>((const float*)x, (float*)bx, n * batch, a, 0, be->fault_dev);
       OJC_LAUNCHED(be, op);
       std::swap(x, bx);
     }
     const double scale = std::sqrt(std::max(1.0, (double)rows / (double)cols));
     const float alpha = (float)(-cfg.lr * scale), decay = (float)(1.0 - cfg.lr * cfg.weight_decay);
-    if (bf) muon_apply_kernel<bf16><<<grid, 256, 0, be->stream>>>(p, (const bf16*)x, mirror, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
-    else muon_apply_kernel<float><<<grid, 256, 0, be->stream>>>(p, (const float*)x, mirror, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    if (bf) muon_apply_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    else muon_apply_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     OJC_LAUNCHED(be, op);
     return OJC_OK;
   };
   st = run();
   ojc_free(be, ws);
   return st;
+}
+
+ojc_status muon_device(ojc_backend* be, float* p, const float* g, float* mom, bf16* mirror, int64_t rows, int64_t cols, const ojc_muon_config& cfg,
+                       const float* grad_scale_dev) {
+  return muon_group_device(be, &p, &g, &mom, mirror ? &mirror : nullptr, 1, rows, cols, cfg, grad_scale_dev);
 }
 
 extern "C" {

@@ -12,3 +12,6 @@ ojc_status adamw_device(ojc_backend* be, float* p, const float* g, float* m, flo
 ojc_status muon_device(ojc_backend* be, float* p, const float* g, float* mom, bf16* mirror, int64_t rows, int64_t cols, const ojc_muon_config& cfg,
                        const float* grad_scale_dev);
 uint64_t muon_scratch_bytes(int64_t rows, int64_t cols, bool bf16_mode);
+// the same step for up to 48 matrices of one shape at once (pointer tables of length `batch`; mirror may be null)
+ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* const* g, float* const* mom, bf16* const* mirror, int64_t batch, int64_t rows,
+                             int64_t cols, const ojc_muon_config& cfg, const float* grad_scale_dev);

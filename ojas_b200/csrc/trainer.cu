@@ -8,6 +8,7 @@
 // Under bf16 autocast the rounding points follow ojas-core/src/autocast.rs: the residual stream, norm statistics,
 // loss, weight gradients and optimizer state stay f32; matmul-class operands and activation outputs are bf16.
 // Permutes are views: attention reads and writes [B,T,H,dh] storage through [B,H,T,dh] strides.
+#include <algorithm>
 #include <cstring>
 
 #include "ce.cuh"
@@ -587,14 +588,17 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
       run_begin = run_end = -1;
       return r;
     };
+    // Muon matrices are stepped in groups of one shape (batched Newton-Schulz products): gather them here, in table order
+    std::vector<std::pair<std::pair<int64_t, int64_t>, std::vector<const Param*>>> muon_groups;
     for (const Param& p : tr->params) {
       const int64_t slot_end = p.offset + ((p.n + 63) & ~int64_t(63));
       if (!p.trains) { OJC_TRY(flush()); continue; }
       if (tr->cfg.optimizer == 1 && p.group == GROUP_MUON) {
         OJC_TRY(flush());
-        bf16* mir = tr->mirror ? tr->mirror + p.offset : nullptr;
-        ojc_muon_config mc{tr->cfg.matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
-        OJC_TRY(muon_device(be, tr->W(p), tr->G(p), tr->m1 + p.offset, mir, p.shape[0], p.shape[1], mc, scale));
+        const std::pair<int64_t, int64_t> shape{p.shape[0], p.shape[1]};
+        auto it = std::find_if(muon_groups.begin(), muon_groups.end(), [&](const auto& gr) { return gr.first == shape; });
+        if (it == muon_groups.end()) { muon_groups.push_back({shape, {}}); it = muon_groups.end() - 1; }
+        it->second.push_back(&p);
       } else {
         if (run_begin < 0) run_begin = p.offset;
         else if (p.offset != run_end) { OJC_TRY(flush()); run_begin = p.offset; }
@@ -602,6 +606,19 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
       }
     }
     OJC_TRY(flush());
+    const ojc_muon_config mc{tr->cfg.matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
+    for (const auto& gr : muon_groups) {
+      const size_t chunk = 48;   // the group kernels' pointer table
+      for (size_t first = 0; first < gr.second.size(); first += chunk) {
+        const size_t count = std::min(chunk, gr.second.size() - first);
+        std::vector<float*> pp(count), mm(count); std::vector<const float*> gg(count); std::vector<bf16*> mir(count);
+        for (size_t i = 0; i < count; ++i) {
+          const Param& q = *gr.second[first + i];
+          pp[i] = tr->W(q); gg[i] = tr->G(q); mm[i] = tr->m1 + q.offset; mir[i] = tr->mirror ? tr->mirror + q.offset : nullptr;
+        }
+        OJC_TRY(muon_group_device(be, pp.data(), gg.data(), mm.data(), tr->mirror ? mir.data() : nullptr, (int64_t)count, gr.first.first, gr.first.second, mc, scale));
+      }
+    }
     return OJC_OK;
   };
   ojc_status st = run();

@@ -227,6 +227,43 @@ def test_muon_hybrid_step_matches_the_oracle_grouping(be, golden_dir):
     tr.close()
 
 
+def test_muon_bf16_groups_run_as_batched_tensor_core_products(be):
+    """ns5 in bf16 on a model whose matrices are wide enough for the tcgen05 kernels: the step driver steps each shape group
+    (8 of 128x128, 4 of 256x128 tall, 2 of 128x256) with batched products. Checked against the oracle's bf16 NS5 per matrix;
+    the momentum buffer, formed before any product, is compared through the second step's update."""
+    from ojas_b200 import ModelSpec
+    kw = dict(vocab=512, n_embd=128, n_layer=2, n_head=2, n_kv_head=2, head_dim=64, hidden=256, max_seq=64)
+    ospec = orc.Spec(**kw)
+    table = orc.param_table(ospec)
+    params = orc.init_params(ospec, 3, normal_everywhere=True)
+    rng = orc.SplitMix64(11)
+    b, t = 4, 64
+    draws = np.array([rng.below(512) for _ in range(b * (t + 1))], np.uint32).reshape(b, t + 1)
+    x, y = draws[:, :-1].copy(), draws[:, 1:].copy()
+    _, grads, _ = orc.forward_loss(ospec, params, x, y)
+    clipped = [g.copy() for g in grads]
+    orc.clip_grad_norm(clipped, 1.0)
+    want = []
+    for info, p, g in zip(table, params, clipped):
+        q = p.copy()
+        if info.trains and info.group == 1:
+            orc.muon_ns5_step(q, g, np.zeros_like(q), lr=0.025, momentum=0.95, weight_decay=0.1, bf16=True)
+        elif info.trains:
+            orc.adamw_step(q.reshape(-1), g.ravel(), np.zeros(q.size, np.float32), np.zeros(q.size, np.float32), 0, 6e-4, weight_decay=0.0)
+        want.append(q)
+    tr = make_trainer(be, ModelSpec(**kw), {i.name: v for i, v in zip(table, params)}, b, t, optimizer="muon", muon_momentum=0.95, ns5_bf16=True, grad_clip=1.0)
+    tr.step(x, y)
+    worst = 0.0
+    for i, (info, p) in enumerate(zip(table, tr.params)):
+        if not p.trains:
+            continue
+        err = normwise(tr.get_param(i) - params[i] + 1e-30, want[i] - params[i] + 1e-30)
+        worst = max(worst, err) if info.group == 1 else worst
+        assert err <= (3e-2 if info.group == 1 else 2e-3), (p.name, err)   # bf16 products: tensor-core vs strict summation order
+    assert worst > 0.0
+    tr.close()
+
+
 def test_out_of_range_token_is_refused_before_any_launch(be):
     from ojas_b200 import ModelSpec, OjasError, TrainConfig, Trainer
     spec = ModelSpec(vocab=64, n_embd=32, n_layer=1, n_head=2, n_kv_head=2, head_dim=16, hidden=64, max_seq=8)
