@@ -173,9 +173,11 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus: int) -> dict:
+def workload_config(n_gpus: int, optimizer: str = "adamw") -> dict:
+    opt = ("AdamW(lr 3e-4, betas 0.9/0.95, eps 1e-8, wd 0.1) on every tensor" if optimizer == "adamw" else
+           "Muon NS5 bf16 (lr 0.025, momentum 0.95, wd 0.1, Nesterov) on 2-D hidden weights + AdamW(lr 6e-4, wd 0) on embedding and vectors, clip 1.0")
     return {"workload": "nanolab GPT-124M train step (ModelSpec::nanolab_124m, hidden 2048): 12 layers, d 768, 12x64 heads, vocab 50304, seq 1024, "
-                        "micro-batch 32 per GPU, bf16 autocast, AdamW(lr 3e-4, betas 0.9/0.95, eps 1e-8, wd 0.1) on every tensor",
+                        "micro-batch 32 per GPU, bf16 autocast, " + opt,
             "global_batch": BATCH * n_gpus, "seq_len": SEQ, "parallelism": f"dp{n_gpus}",
             "l2": "inputs larger than L2: one step streams about 14 GB of activations, weights and optimizer state"}
 
@@ -195,7 +197,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     be = CudaBackend(local_rank, 150 << 30)
     spec = ModelSpec(**spec_kwargs())
-    cfg = TrainConfig(autocast_bf16=True, optimizer="adamw", adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=0.0, loss_seed=1.0 / world)
+    if args.optimizer == "muon":   # BASELINE's data-parallel recipe: Muon NS5 on the 2-D hidden weights, AdamW on embedding and vectors, clip 1.0
+        cfg = TrainConfig(autocast_bf16=True, optimizer="muon", adam_lr=6e-4, adam_weight_decay=0.0, matrix_lr=0.025, muon_momentum=0.95, muon_weight_decay=0.1,
+                          ns5_bf16=True, grad_clip=1.0, loss_seed=1.0 / world)
+    else:
+        cfg = TrainConfig(autocast_bf16=True, optimizer="adamw", adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=0.0, loss_seed=1.0 / world)
     batch = args.batch   # 32 (the workload); smaller only for profiler captures, and the line then says so
     tr = Trainer(be, spec, cfg, batch, SEQ)
     tr.set_params(init_weights(tr.params, 0))  # identical weights on every rank
@@ -270,7 +276,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     line = {
         "metric": "nanolab_gpt_124m_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(world) if batch == BATCH else {"workload": f"PROFILER CASE, not the benchmark workload: micro-batch {batch}"},
+        "config": workload_config(world, args.optimizer) if batch == BATCH else {"workload": f"PROFILER CASE, not the benchmark workload: micro-batch {batch}"},
         "mfu": value * fpt / (world * pk["bf16_tflops"] * 1e12), "mfu_vs_sustained": value * fpt / (world * pk["bf16_tflops_sustained"] * 1e12),
         "flops_per_token": fpt, "final_loss": rep.loss if rep else None,
         "e2e": {"value": tokens * args.steps / (e2e_ms / 1000.0) if e2e_ms else None, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * SEQ * 4,
@@ -346,6 +352,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the bounded CPU sample (the default run reports it)")
+    ap.add_argument("--optimizer", default="adamw", choices=["adamw", "muon"], help="adamw: the headline workload; muon: the Muon NS5 + AdamW recipe of the data-parallel configs")
     ap.add_argument("--batch", type=int, default=BATCH, help="micro-batch per GPU; anything but 32 is a reduced case for profiler captures only")
     ap.add_argument("--no-sdpa", action="store_true", help="skip the standalone attention case [8,16,4096,128]")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (used for profiler captures)")

@@ -97,6 +97,11 @@ ojc_status ojc_to_bf16(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);    
 ojc_status ojc_to_f32(ojc_backend* be, const ojc_tensor* x, ojc_tensor* y);     /* BF16 -> F32 */
 
 /* ---- BackendModule ops of the block (backend.rs:1609-2634) */
+/* Data feed, device half (next to the path: ojas-data/src/sampler.rs:245-290, BatchSampler::next_batch's read loop). The token
+   stream is resident in device memory as stored (u16 or u32); the host sampler supplies `rows` window starts and the kernel writes
+   x[r] = tokens[start_r, start_r + seq), y[r] = tokens[start_r + 1, start_r + seq + 1) as U32. Every window is bounds-checked first. */
+ojc_status ojc_gather_token_windows(ojc_backend* be, const void* tokens_dev, int32_t bytes_per_token, uint64_t n_tokens, const int64_t* starts_host,
+                                    int64_t rows, int64_t seq, ojc_tensor* x, ojc_tensor* y);
 ojc_status ojc_embedding_forward(ojc_backend* be, const ojc_tensor* table, const ojc_tensor* ids, ojc_tensor* out);          /* :1615 */
 ojc_status ojc_embedding_backward(ojc_backend* be, const ojc_tensor* table_shape, const ojc_tensor* ids, const ojc_tensor* grad_out, ojc_tensor* grad_table); /* :1621 */
 ojc_status ojc_linear_forward(ojc_backend* be, const ojc_tensor* x, const ojc_tensor* weight, ojc_tensor* y);               /* :1628 y = x W^T */
