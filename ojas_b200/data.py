@@ -152,9 +152,17 @@ class TokenBin:
         return np.frombuffer(raw, dtype="<u2" if self.width == 2 else "<u4").astype(np.uint32)
 
     def raw_tokens(self) -> np.ndarray:
-        """The whole stream in its stored width (for the device-resident feed)."""
-        return np.fromfile(os.fdopen(os.dup(self._fd), "rb", closefd=True), dtype="<u2" if self.width == 2 else "<u4", count=self.len_tokens,
-                           offset=self.data_offset)
+        """The whole stream in its stored width (for the device-resident feed). Positioned reads, in 256 MB pieces:
+        the file's own cursor is neither used nor moved."""
+        out = np.empty(self.len_tokens, dtype="<u2" if self.width == 2 else "<u4")
+        view, total, done, piece = out.view(np.uint8), self.len_tokens * self.width, 0, 256 << 20
+        while done < total:
+            raw = os.pread(self._fd, min(piece, total - done), self.data_offset + done)
+            if not raw:
+                raise DataError("token read: short read")
+            view[done:done + len(raw)] = np.frombuffer(raw, np.uint8)
+            done += len(raw)
+        return out
 
 
 class BatchSampler:

@@ -113,7 +113,7 @@ def test_token_bin_layouts(tmp_path):
     a, b = TokenBin.open(tmp_path / "a.bin", "fineweb"), TokenBin.open(tmp_path / "b.bin", "fineweb")
     assert (a.width, b.width, len(a), len(b), a.data_offset) == (2, 4, 300, 300, FINEWEB_HEADER_BYTES)
     assert np.array_equal(a.read_u32(10, 20), t16[10:30]) and np.array_equal(b.read_u32(280, 20), t32[280:300])
-    assert np.array_equal(b.raw_tokens(), t32)
+    assert np.array_equal(b.raw_tokens(), t32) and np.array_equal(b.raw_tokens(), t32)   # positioned: a second read starts at token 0 too
     with pytest.raises(DataError, match="expected u16"):
         TokenBin.open(tmp_path / "b.bin", "fineweb_u16")
     write_bin(tmp_path / "c.bin", 10, 2, fineweb=True, magic=123)
