@@ -257,13 +257,18 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     for i in range(max(args.warmup, 3)):
         step_resident(i)
-    be.profile_gemm(True)
     launches0 = be.kernel_launches()
     with ClockSampler(local_rank) as clocks:
         ms, rep = timed(step_resident, args.steps)
     launches = be.kernel_launches() - launches0
+    # Roofline pass: the same K steps again with the weight-gradient GEMMs folded back into the one stream, so every GEMM launch
+    # is bracketed by CUDA events with the GPU to itself (in the timed region above they share the SMs with the dX chain).
+    tr.overlap_weight_grads(False)
+    be.profile_gemm(True)
+    roof_ms, _ = timed(step_resident, args.steps)
     gemm_ms, gemm_flops, gemm_launches = be.profile_gemm_read()
     be.profile_gemm(False)
+    tr.overlap_weight_grads(True)
     e2e_ms = None
     if not args.no_e2e:
         step_e2e(0)
@@ -289,7 +294,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         line["roofline"] = {"kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM, two-SM and one-SM tiles; all launches of the timed steps)", "bound": "tensor",
                             "achieved": achieved,
                             "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops_sustained"],
-                            "peak_source": f"bf16_tflops_sustained, of {pk_kind}", "launches": int(gemm_launches), "share_of_step_time": gemm_ms / ms,
+                            "peak_source": f"bf16_tflops_sustained, of {pk_kind}", "launches": int(gemm_launches), "share_of_step_time": gemm_ms / roof_ms,
+                            "pass": f"second pass of the same {args.steps} steps on one stream ({roof_ms / args.steps:.2f} ms per step)",
                             "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH, "traffic_launch": GEMM_TRAFFIC_LAUNCH}
     if rank == 0 and world == 1 and not args.no_sdpa:
         line["sdpa_standalone"] = sdpa_standalone(be, main, pk["bf16_tflops"])

@@ -199,6 +199,9 @@ ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, con
 ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* logits_host);          /* forward_logits, block.rs:407-416; [batch*seq, vocab] */
 /* Data-parallel extension (new; the reference has no distributed code): gradients live in contiguous buckets; the
  * caller all-reduces each bucket (NCCL) between ojc_trainer_gradients and ojc_trainer_apply. */
+/* Under bf16 autocast the weight-gradient GEMMs of backward run on a second stream beside the dX chain (same kernels, same
+   results bit for bit). enable = 0 folds them back into the one stream, e.g. to time each GEMM with the GPU to itself. */
+ojc_status ojc_trainer_overlap_weight_grads(ojc_trainer* tr, int32_t enable);
 int64_t ojc_trainer_bucket_count(ojc_trainer* tr);
 ojc_status ojc_trainer_bucket(ojc_trainer* tr, int64_t index, void** device_ptr, uint64_t* floats);
 ojc_status ojc_trainer_bucket_ready_event(ojc_trainer* tr, int64_t index, void** cuda_event);          /* recorded when the bucket's last gradient is written */

@@ -575,6 +575,10 @@ class Trainer:
         _check(lib.ojc_trainer_apply(self._h, C.byref(norm) if read_norm else None))
         return norm.value if read_norm else None
 
+    def overlap_weight_grads(self, enable: bool) -> None:
+        """Run (default) or do not run the weight-gradient GEMMs on the second stream; results are the same bits either way."""
+        _check(lib.ojc_trainer_overlap_weight_grads(self._h, C.c_int32(int(enable))))
+
     def finish(self) -> StepReport:
         rep = _lib.StepReport()
         _check(lib.ojc_trainer_finish(self._h, C.byref(rep)))

@@ -9,6 +9,7 @@
 // loss, weight gradients and optimizer state stay f32; matmul-class operands and activation outputs are bf16.
 // Permutes are views: attention reads and writes [B,T,H,dh] storage through [B,H,T,dh] strides.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "ce.cuh"
@@ -76,6 +77,13 @@ struct ojc_trainer {
   int64_t ld_qkv = 0, ld_au = 0;
   uint64_t step = 0;
   bool poisoned = false, grads_ready = false;
+  // Weight gradients (their GEMMs, split-K sums and copies) run on a second stream with its own workspace while the main
+  // stream walks on through the dX chain: nothing downstream reads them before the optimizer.
+  cudaStream_t side_stream = nullptr;
+  bool side_enabled = true;
+  cudaEvent_t ev_main = nullptr, ev_side = nullptr;
+  void* side_scratch = nullptr;
+  uint64_t side_scratch_bytes = 0;
   struct Bucket { int64_t offset, floats; int first_param; cudaEvent_t ready; bool recorded; };
   std::vector<Bucket> buckets;
 
@@ -248,6 +256,18 @@ ojc_status record_ready(ojc_trainer* tr, int first_param_done) {
   return OJC_OK;
 }
 
+// While alive, library calls issue on the trainer's side stream with the side workspace (the step driver is single-threaded).
+struct SideLane {
+  ojc_trainer* tr; bool profile;
+  explicit SideLane(ojc_trainer* t) : tr(t), profile(t->be->profile_gemm) { swap(); tr->be->profile_gemm = false; }
+  ~SideLane() { swap(); tr->be->profile_gemm = profile; }
+  void swap() {
+    std::swap(tr->be->stream, tr->side_stream);
+    std::swap(tr->be->scratch, tr->side_scratch);
+    std::swap(tr->be->scratch_bytes, tr->side_scratch_bytes);
+  }
+};
+
 // ---------------------------------------------------------------------------------------------- backward
 ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev) {
   ojc_backend* be = tr->be;
@@ -272,11 +292,27 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   // the residual gradient as a matmul operand: f32 in the f32 tier, the bf16 copy the norm backward kernels write under autocast
   const void* gxo = bf ? tr->gx_b : (void*)tr->gx;
   bool have_v0 = false;
+  // fn's inputs are final on the main stream now; run it on the side lane (or in place when there is none)
+  const bool lane = bf && tr->side_stream != nullptr && tr->side_enabled;
+  auto on_side = [&](auto&& fn) -> ojc_status {
+    if (!lane) return fn();
+    OJC_CUDA(be, cudaEventRecord(tr->ev_main, be->stream), "side_lane");
+    OJC_CUDA(be, cudaStreamWaitEvent(tr->side_stream, tr->ev_main, 0), "side_lane");
+    SideLane guard(tr);
+    return fn();
+  };
+  // the main stream goes no further until the side lane has drained (before a buffer the lane still reads is rewritten)
+  auto join_side = [&]() -> ojc_status {
+    if (!lane) return OJC_OK;
+    OJC_CUDA(be, cudaEventRecord(tr->ev_side, tr->side_stream), "side_lane");
+    OJC_CUDA(be, cudaStreamWaitEvent(be->stream, tr->ev_side, 0), "side_lane");
+    return OJC_OK;
+  };
   for (int64_t l = L - 1; l >= 0; --l) {
     LayerActs& a = tr->acts[l];
     // x2 = x1 + down(m)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
-    OJC_TRY(linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false));
+    OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false); }));
     const bool fl = tr->fused_lin;
     const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;
     if (fl) OJC_TRY(swiglu_rows_backward(be, (const bf16*)a.a, (const bf16*)tr->g_m, (bf16*)tr->g_a, tr->ld_au, N, F));
@@ -290,27 +326,31 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     }
     if (fl) {
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FG)), A, tr->g_a, A, tr->g_h2, OJC_F32, N, d, tr->ld_au, false));
-      OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, tr->ld_au, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, tr->ld_au, false); }));
     } else {
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FU)), A, tr->g_u, A, tr->g_h2, OJC_F32, N, d, F, false));
-      OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_u, A, tr->G(tr->P(l, P_FU)), N, d, F, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h2, A, tr->g_u, A, tr->G(tr->P(l, P_FU)), N, d, F, false); }));
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FG)), A, tr->g_a, A, tr->g_h2, OJC_F32, N, d, F, true));
-      OJC_TRY(linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, F, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h2, A, tr->g_a, A, tr->G(tr->P(l, P_FG)), N, d, F, false); }));
     }
     {
       ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d), gy = T2(tr->g_h2, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn2 = T1(tr->G(tr->P(l, P_NORM2)), OJC_F32, d);
+      OJC_TRY(join_side());   // the down-projection's weight gradient still reads the bf16 residual gradient this rewrites
       OJC_TRY(rms_backward_impl(be, &x1, &n2, &gy, eps, &gx, &gn2, false, true, bf ? (bf16*)tr->gx_b : nullptr));  // gx now holds d/dx1
     }
     // x1 = x + o_proj(yg)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_O)), A, gxo, A, tr->g_yg, A, N, qw, d, false));
-    OJC_TRY(linear_backward_weight_impl(be, a.yg, A, gxo, A, tr->G(tr->P(l, P_O)), N, qw, d, false));
+    OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.yg, A, gxo, A, tr->G(tr->P(l, P_O)), N, qw, d, false); }));
     if (tr->gate_ld) {
       const int ld = tr->gate_ld;
       OJC_TRY(gate_apply_backward(be, a.scales, (const bf16*)a.y, (const bf16*)tr->g_yg, (bf16*)tr->g_y, tr->gate_gz, ld, tr->G(tr->P(l, P_GB)), N, (int)H, (int)dh));
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_GW)), A, tr->gate_gz, A, tr->g_h, OJC_F32, N, d, ld, false));   // d/dh = gz . Wg (padding columns of gz are zero)
-      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->gate_gz, A, tr->gate_gw, N, d, ld, false));                          // [ld, d]; rows past H are zero
-      OJC_CUDA(be, cudaMemcpyAsync(tr->G(tr->P(l, P_GW)), tr->gate_gw, (size_t)H * d * 4, cudaMemcpyDeviceToDevice, be->stream), "per_head_sigmoid_gate_backward");
+      OJC_TRY(on_side([&]() -> ojc_status {
+        OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->gate_gz, A, tr->gate_gw, N, d, ld, false));                        // [ld, d]; rows past H are zero
+        OJC_CUDA(be, cudaMemcpyAsync(tr->G(tr->P(l, P_GW)), tr->gate_gw, (size_t)H * d * 4, cudaMemcpyDeviceToDevice, be->stream), "per_head_sigmoid_gate_backward");
+        return OJC_OK;
+      }));
     } else {
       ojc_tensor h = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
       ojc_tensor y = T2(a.y, A, N * H, dh), gyg = T2(tr->g_yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H), gh = T2(tr->g_h, OJC_F32, N, d), gy = T2(tr->g_y, A, N * H, dh);
@@ -367,18 +407,19 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     if (fl) {
       // d/dh += [gq | gk | gv] . [Wq; Wk; Wv], and the three weight gradients as one [ld_qkv, d] block
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_Q)), A, tr->g_q, A, tr->g_h, OJC_F32, N, d, tr->ld_qkv, true));
-      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, tr->ld_qkv, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, tr->ld_qkv, false); }));
     } else {
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_V)), A, g_rawv, A, tr->g_h, OJC_F32, N, d, kvw, true));
-      OJC_TRY(linear_backward_weight_impl(be, a.h, A, g_rawv, A, tr->G(tr->P(l, P_V)), N, d, kvw, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h, A, g_rawv, A, tr->G(tr->P(l, P_V)), N, d, kvw, false); }));
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_K)), A, tr->g_k, A, tr->g_h, OJC_F32, N, d, kvw, true));
-      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_k, A, tr->G(tr->P(l, P_K)), N, d, kvw, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h, A, tr->g_k, A, tr->G(tr->P(l, P_K)), N, d, kvw, false); }));
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_Q)), A, tr->g_q, A, tr->g_h, OJC_F32, N, d, qw, true));
-      OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, qw, false));
+      OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.h, A, tr->g_q, A, tr->G(tr->P(l, P_Q)), N, d, qw, false); }));
     }
     {
       ojc_tensor x = T2(a.x, OJC_F32, N, d), n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn1 = T1(tr->G(tr->P(l, P_NORM1)), OJC_F32, d);
+      OJC_TRY(join_side());   // every weight gradient of this layer is in: the buffers the lane read may be rewritten, the bucket events may fire
       OJC_TRY(rms_backward_impl(be, &x, &n1, &gy, eps, &gx, &gn1, false, true, bf ? (bf16*)tr->gx_b : nullptr));
     }
     if (l == 0 && s.n_layer > 0) OJC_TRY(ojc_fill_zero(be, tr->G(tr->P(0, P_LAMBDA)), 4));  // layer 0's lambda never trains (names.rs:262-268)
@@ -488,6 +529,13 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
     end = tr->params[first].offset;
     last = first - 1;
   }
+  const char* lane_env = getenv("OJC_SIDE_LANE");
+  if (tr->act_dt == OJC_BF16 && !(lane_env && lane_env[0] == '0')) {
+    if (cudaStreamCreateWithFlags(&tr->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&tr->ev_main, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&tr->ev_side, cudaEventDisableTiming) != cudaSuccess)
+      return fail(ojc_fail(OJC_ERR_BACKEND, op, "cannot create the weight-gradient stream"));
+  }
   *out = tr;
   return OJC_OK;
 }
@@ -495,6 +543,10 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
 ojc_status ojc_trainer_close(ojc_trainer* tr) {
   if (!tr) return OJC_OK;
   if (tr->be && tr->be->stream) cudaStreamSynchronize(tr->be->stream);
+  if (tr->side_stream) { cudaStreamSynchronize(tr->side_stream); cudaStreamDestroy(tr->side_stream); }
+  if (tr->ev_main) cudaEventDestroy(tr->ev_main);
+  if (tr->ev_side) cudaEventDestroy(tr->ev_side);
+  if (tr->side_scratch) cudaFree(tr->side_scratch);
   for (void* p : tr->owned) ojc_free(tr->be, p);
   for (auto& b : tr->buckets) if (b.ready) cudaEventDestroy(b.ready);
   delete tr;
@@ -672,6 +724,12 @@ ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* 
   if (st == OJC_OK) st = ojc_download(tr->be, logits_host, logits, (uint64_t)tr->N * V * 4);
   ojc_free(tr->be, logits);
   return st;
+}
+
+ojc_status ojc_trainer_overlap_weight_grads(ojc_trainer* tr, int32_t enable) {
+  OJC_TRY(check_live(tr, "trainer_overlap_weight_grads"));
+  tr->side_enabled = enable != 0;
+  return OJC_OK;
 }
 
 int64_t ojc_trainer_bucket_count(ojc_trainer* tr) { return tr ? (int64_t)tr->buckets.size() : 0; }

@@ -264,6 +264,30 @@ def test_muon_bf16_groups_run_as_batched_tensor_core_products(be):
     tr.close()
 
 
+def test_weight_gradients_on_the_side_stream_are_the_same_bits(be, c1, monkeypatch):
+    """Under bf16 autocast the weight-gradient GEMMs run on a second stream beside the dX chain. Same kernels, same split
+    counts, only the stream differs: every gradient, the loss and the stepped parameters must equal the one-stream run bit for bit."""
+    from ojas_b200 import ModelSpec
+    kw, params, x, y, _, _, _ = c1
+    by_name = {p.name: v for p, v in zip(orc.param_table(orc.Spec(**kw)), params)}
+    runs = []
+    for lane in ("0", "1"):
+        monkeypatch.setenv("OJC_SIDE_LANE", lane)
+        tr = make_trainer(be, ModelSpec(**kw), by_name, 8, 256, autocast_bf16=True, optimizer="adamw", adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=1.0)
+        loss = tr.gradients(x, y)
+        grads = [tr.get_grad(i).copy() for i in range(len(tr.params))]
+        for _ in range(3):
+            tr.step(x, y)
+        runs.append((loss, grads, [tr.get_param(i).copy() for i in range(len(tr.params))]))
+        tr.close()
+    (l0, g0, p0), (l1, g1, p1) = runs
+    assert l0 == l1
+    for a, b in zip(g0, g1):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    for a, b in zip(p0, p1):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
 def test_out_of_range_token_is_refused_before_any_launch(be):
     from ojas_b200 import ModelSpec, OjasError, TrainConfig, Trainer
     spec = ModelSpec(vocab=64, n_embd=32, n_layer=1, n_head=2, n_kv_head=2, head_dim=16, hidden=64, max_seq=8)
