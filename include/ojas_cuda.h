@@ -188,6 +188,13 @@ ojc_status ojc_trainer_param_info(ojc_trainer* tr, int64_t index, char* name, in
 ojc_status ojc_trainer_set_param(ojc_trainer* tr, int64_t index, const float* host, uint64_t count);   /* also refreshes the bf16 mirror */
 ojc_status ojc_trainer_get_param(ojc_trainer* tr, int64_t index, float* host, uint64_t count);
 ojc_status ojc_trainer_get_grad(ojc_trainer* tr, int64_t index, float* host, uint64_t count);          /* after ojc_trainer_gradients */
+/* Checkpoint support (Trainer::save / resume_from, ojas-model/src/checkpoint.rs:527-700): the optimizer state of one parameter and
+ * the completed-step count. slot 0: Muon momentum of a matrix (optimizer 1) or AdamW first moment; slot 1: AdamW second moment.
+ * A frozen parameter, or slot 1 of a Muon matrix, is OutOfRange. */
+ojc_status ojc_trainer_get_moment(ojc_trainer* tr, int64_t index, int32_t slot, float* host, uint64_t count);
+ojc_status ojc_trainer_set_moment(ojc_trainer* tr, int64_t index, int32_t slot, const float* host, uint64_t count);
+uint64_t ojc_trainer_steps_done(ojc_trainer* tr);
+ojc_status ojc_trainer_set_steps_done(ojc_trainer* tr, uint64_t step);
 /* forward + fused CE + backward on host ids/targets [batch*seq] (copied in from the caller's pinned or pageable memory);
  * gradients stay on the device. loss_out may be NULL (no readback). */
 ojc_status ojc_trainer_gradients(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, float* loss_out);

@@ -32,7 +32,7 @@ template <int D> struct Fwd {
   static constexpr int SMEM_BYTES = OFF_BAR + 128;              // D 64: 112 KB (two CTAs per SM); D 128: 192 KB
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
-enum { B_QFULL = 0, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL, B_PREADY, B_PVFULL, B_COUNT };
+enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_SFULL, B_SFREE, B_PREADY, B_PHALF, B_PVFULL, B_COUNT };
 
 struct FwdArgs {
   SdpaView<bf16> out;
@@ -57,7 +57,7 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
 // lane in the S and O accumulators; p_row: its row of the P operand buffer.
 template <int D>
 __device__ __forceinline__ void softmax_tile(const FwdArgs& args, int b, int h, int q0, int tid, int nblocks, uint32_t s_addr, uint32_t o_addr, uint8_t* p_row,
-                                             uint32_t bar_sfull, uint32_t bar_pready, uint32_t bar_pvfull, volatile int* abort_flag) {
+                                             uint32_t bar_sfull, uint32_t bar_sfree, uint32_t bar_pready, uint32_t bar_phalf, uint32_t bar_pvfull, volatile int* abort_flag) {
   const int row = q0 + tid;
   const float sl2 = args.scale * LOG2E;
   float m = 0.0f, l = 0.0f;                     // m: the maximum the probabilities are scaled by (log2 domain), set by block 0
@@ -71,12 +71,14 @@ __device__ __forceinline__ void softmax_tile(const FwdArgs& args, int b, int h, 
 #pragma unroll
     for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
     tmem_wait_ld();
+    // The S columns are free as soon as the row sits in registers: the MMA warp computes the next block's S during this one's softmax.
+    fence_before();
+    mbar_arrive(bar_sfree);
     if (masked) {
+      const int last = min(row, args.time - 1) - key0;              // last visible key of this block, relative
 #pragma unroll
-      for (int e = 0; e < BN; ++e) {
-        const int key = key0 + e;
-        if (!(key <= row && key < args.time)) r[e] = 0xff800000u;   // -inf: exp2 gives an exact zero
-      }
+      for (int e = 0; e < BN; ++e)
+        if (e > last) r[e] = 0xff800000u;                           // -inf: exp2 gives an exact zero
     }
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four chains instead of one 128-deep dependency
 #pragma unroll
@@ -113,6 +115,10 @@ __device__ __forceinline__ void softmax_tile(const FwdArgs& args, int b, int h, 
     float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int ci = 0; ci < BN / 8; ++ci) {
+      // P is one buffer: the previous block's P V must have read a 64-key half before this block overwrites it
+      if (j > 0 && (ci & 7) == 0) {
+        if (!mbar_wait(ci == 0 ? bar_phalf : bar_pvfull, (j - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      }
       float p[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) { p[e] = fast_exp2(fmaf(__uint_as_float(r[ci * 8 + e]), sl2, -m)); rs4[e & 3] += p[e]; }
@@ -120,8 +126,9 @@ __device__ __forceinline__ void softmax_tile(const FwdArgs& args, int b, int h, 
       *reinterpret_cast<uint4*>(p_row + (ci >> 3) * ST128 + (((ci & 7) ^ (tid & 7)) << 4)) =
           make_uint4(pack2_bf16(p[0], p[1]), pack2_bf16(p[2], p[3]), pack2_bf16(p[4], p[5]), pack2_bf16(p[6], p[7]));
     }
+    if (!ok) break;
     l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-    fence_before();
+    fence_before();                              // orders a rescale's TMEM stores before the P V the arrival releases
     fence_async_smem();
     mbar_arrive(bar_pready);
   }
@@ -171,7 +178,7 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const int nblocks = (n_end + BN - 1) / BN;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), i == B_PREADY ? 128 : 1);
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i == B_PREADY || i == B_SFREE) ? 128 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -186,16 +193,20 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   // A failed wait has already set the abort flag, which every other wait polls: the loops need no check of their own.
   if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer: Q, then (K, V) pairs two blocks ahead
+    // ------------------------------------------------------------------ TMA producer: Q, then K and V tiles, two stages each
     if (lane == 0) {
       mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
       load_tile<NSUB, 128>(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
       for (int j = 0; j < nblocks; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(bar(B_KVEMPTY0 + s), ((j >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
-        mbar_expect_tx(bar(B_KVFULL0 + s), 2 * TILE_BYTES);
-        load_tile<NSUB, 128>(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
-        load_tile<NSUB, 128>(base + OFF_V + s * TILE_BYTES, &tm_v, bar(B_KVFULL0 + s), args.h_first, hk, j * BN, b);
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        // a K stage is free once the S product that read it finished, a V stage once its P V finished
+        if (!mbar_wait(bar(B_KEMPTY0 + s), ph, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(B_KFULL0 + s), TILE_BYTES);
+        load_tile<NSUB, 128>(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KFULL0 + s), args.h_first, hk, j * BN, b);
+        if (!mbar_wait(bar(B_VEMPTY0 + s), ph, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(B_VFULL0 + s), TILE_BYTES);
+        load_tile<NSUB, 128>(base + OFF_V + s * TILE_BYTES, &tm_v, bar(B_VFULL0 + s), args.h_first, hk, j * BN, b);
       }
     }
   } else if (warp == 5) {
@@ -205,32 +216,47 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       // descriptor low words: K-major operands step 32 bytes per MMA, the MN-major V steps 16 keys = 2048 bytes
       // (V as the MN-major B operand: its 64-wide column blocks are the sub-tiles, ST128 bytes apart)
       const uint32_t q_lo = desc_lo(base + OFF_Q, 0), k_lo = desc_lo(base + OFF_K, 0), p_lo = desc_lo(base + OFF_P, 0), v_lo = desc_lo(base + OFF_V, ST128);
-      bool ok = mbar_wait(bar(B_QFULL), 0, args.fault, abort_flag);
-      for (int j = 0; j < nblocks && ok; ++j) {
+      // S(j) = Q K(j)^T into the one S accumulator; the caller has made sure its columns are free
+      auto issue_s = [&](int j) -> bool {
         const uint32_t s = j & 1;
-        if (!mbar_wait(bar(B_KVFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) break;
+        if (!mbar_wait(bar(B_KFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) return false;
         fence_after();
-        // S = Q K^T. The S columns are free: every softmax thread arrived on B_PREADY for block j - 1 after its last S read.
 #pragma unroll
         for (uint32_t kk = 0; kk < D / 16; ++kk)
           umma_lh(tmem_base, q_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + s * TILE16 + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
         umma_commit(bar(B_SFULL));
+        umma_commit(bar(B_KEMPTY0 + s));
+        return true;
+      };
+      bool ok = mbar_wait(bar(B_QFULL), 0, args.fault, abort_flag) && issue_s(0);
+      for (int j = 0; j < nblocks && ok; ++j) {
+        const uint32_t s = j & 1;
+        // S(j + 1) as soon as the softmax rows hold S(j) in registers: it runs under block j's softmax
+        if (j + 1 < nblocks) {
+          if (!mbar_wait(bar(B_SFREE), j & 1, args.fault, abort_flag)) break;
+          fence_after();
+          if (!issue_s(j + 1)) break;
+        }
         if (!mbar_wait(bar(B_PREADY), j & 1, args.fault, abort_flag)) break;
+        if (!mbar_wait(bar(B_VFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) break;
         fence_after();
         // O += P V: P is two K-major halves of 64 keys (16 KB apart); V is MN-major (one 64-wide block).
         // O stays in TMEM for the whole walk; the softmax rows rescale it in place when their maximum moves.
+        // The first half of P is handed back after four of the eight MMAs, so the next block's softmax can start writing.
 #pragma unroll
-        for (uint32_t kk = 0; kk < BN / 16; ++kk)
+        for (uint32_t kk = 0; kk < BN / 16; ++kk) {
           umma_lh(tmem_base + 128, p_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, v_lo + s * TILE16 + kk * MNSTEP, HI, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(B_KVEMPTY0 + s));
+          if (kk == BN / 32 - 1) umma_commit(bar(B_PHALF));
+        }
+        umma_commit(bar(B_VEMPTY0 + s));
         umma_commit(bar(B_PVFULL));
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + output rows (warps 0..3)
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-    softmax_tile<D>(args, b, h, q0, threadIdx.x, nblocks, lane_base, lane_base + 128, base_ptr + OFF_P + threadIdx.x * 128, bar(B_SFULL), bar(B_PREADY), bar(B_PVFULL),
-                    abort_flag);
+    softmax_tile<D>(args, b, h, q0, threadIdx.x, nblocks, lane_base, lane_base + 128, base_ptr + OFF_P + threadIdx.x * 128, bar(B_SFULL), bar(B_SFREE), bar(B_PREADY),
+                    bar(B_PHALF), bar(B_PVFULL), abort_flag);
   }
   if (*abort_flag) __nanosleep(200000);
   fence_before();

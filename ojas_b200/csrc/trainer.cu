@@ -593,6 +593,41 @@ ojc_status ojc_trainer_get_grad(ojc_trainer* tr, int64_t index, float* host, uin
   return ojc_download(tr->be, host, tr->G(p), count * 4);
 }
 
+// Optimizer state of one parameter for the checkpoint directory (ojas-model/src/checkpoint.rs:225-243): slot 0 is the Muon
+// momentum of a matrix or the AdamW first moment of an embedding / vector, slot 1 the AdamW second moment.
+static ojc_status moment_slot(ojc_trainer* tr, const char* op, int64_t index, int32_t slot, uint64_t count, float** out) {
+  if (!tr || index < 0 || index >= (int64_t)tr->params.size()) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "parameter index out of range");
+  const Param& p = tr->params[index];
+  if ((int64_t)count != p.n) return ojc_fail(OJC_ERR_SHAPE, op, "element count does not match the parameter");
+  if (!p.trains) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "a frozen parameter has no optimizer state");
+  const bool muon = tr->cfg.optimizer == 1 && p.group == GROUP_MUON;
+  if (slot < 0 || slot > 1 || (slot == 1 && muon)) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "no such moment for this parameter's optimizer group");
+  *out = (slot == 0 ? tr->m1 : tr->m2) + p.offset;
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_get_moment(ojc_trainer* tr, int64_t index, int32_t slot, float* host, uint64_t count) {
+  float* dev = nullptr;
+  OJC_TRY(moment_slot(tr, "trainer_get_moment", index, slot, count, &dev));
+  return ojc_download(tr->be, host, dev, count * 4);
+}
+
+ojc_status ojc_trainer_set_moment(ojc_trainer* tr, int64_t index, int32_t slot, const float* host, uint64_t count) {
+  OJC_TRY(check_live(tr, "trainer_set_moment"));
+  float* dev = nullptr;
+  OJC_TRY(moment_slot(tr, "trainer_set_moment", index, slot, count, &dev));
+  return ojc_upload(tr->be, dev, host, count * 4);
+}
+
+uint64_t ojc_trainer_steps_done(ojc_trainer* tr) { return tr ? tr->step : 0; }
+
+ojc_status ojc_trainer_set_steps_done(ojc_trainer* tr, uint64_t step) {
+  OJC_TRY(check_live(tr, "trainer_set_steps_done"));
+  if (step == UINT64_MAX) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "trainer_set_steps_done", "step count u64::MAX has no successor");   // next_step, ojas-core/src/backend.rs:220-224
+  tr->step = step;
+  return OJC_OK;
+}
+
 ojc_status ojc_trainer_gradients_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev) {
   const char* op = "trainer_gradients";
   OJC_TRY(check_live(tr, op));
