@@ -11,6 +11,8 @@
 // the other's MMAs; at head_dim 128 the tiles take 192 KB and one CTA owns the SM. Rows wider than 128 bytes are kept as
 // 64-column sub-tiles (one 128-byte swizzle span each), 16 KB apart for 128-row tiles and 8 KB apart for 64-row tiles.
 // Every mbarrier wait is bounded; on expiry the CTA raises the fault word, drains and frees its TMEM.
+#include <algorithm>
+
 #include "sdpa.cuh"
 #include "tc_common.cuh"
 
@@ -38,10 +40,24 @@ struct FwdArgs {
   SdpaView<bf16> out;
   float* lse;
   int heads, kv_heads, time;
+  int planes, group; // batch * heads, and planes per L2 group: the grid is one dimension (tile_order)
   int h_first;      // tensor-map dimension order: 1 = (dh, H, T, B), 0 = (dh, T, H, B)
   float scale;
   uint32_t* fault;
 };
+
+// Block order. Planes (batch x head) go in groups small enough for their tensors to stay in L2; inside a group the long
+// tiles of all its planes come first, so the blocks that start last are short and the SMs drain together. `rank` counts
+// tiles from the longest one.
+struct TileOrder { int rank, plane; };
+__device__ __forceinline__ TileOrder tile_order(int block, int planes, int group, int tiles) {
+  const int g = block / (group * tiles), first = g * group, in_group = min(group, planes - first), within = block - g * group * tiles;
+  return TileOrder{within / in_group, first + within % in_group};
+}
+__host__ inline int planes_per_group(int64_t time, int64_t dim, int planes) {
+  const int64_t per_plane = 4 * time * dim * 2;              // q, k, v and one more tensor of the plane, bf16
+  return (int)std::max<int64_t>(1, std::min<int64_t>(planes, (32ll << 20) / per_plane));
+}
 
 // one `ROWS`-row tile of a head as NSUB 64-column boxes
 template <int NSUB, int ROWS>
@@ -171,16 +187,31 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;   // long (late) query tiles first
+  const int tiles = gridDim.x / args.planes;
+  const TileOrder ord = tile_order(blockIdx.x, args.planes, args.group, tiles);
+  const int qt = tiles - 1 - ord.rank;         // late query tiles see the most keys
   const int q0 = qt * BM;
-  const int plane = blockIdx.y, b = plane / args.heads, h = plane % args.heads, hk = h / (args.heads / args.kv_heads);
+  const int plane = ord.plane, b = plane / args.heads, h = plane % args.heads, hk = h / (args.heads / args.kv_heads);
   const int n_end = min(args.time, q0 + BM);
   const int nblocks = (n_end + BN - 1) / BN;
 
-  if (threadIdx.x == 0) {
+  // The producer thread sets the barriers up and sends the first loads on their way before the CTA-wide sync, so their
+  // latency runs under the TMEM allocation.
+  auto load_kv = [&](int j) {
+    const int s = j & 1;
+    mbar_expect_tx(bar(B_KFULL0 + s), TILE_BYTES);
+    load_tile<NSUB, 128>(base + OFF_K + s * TILE_BYTES, &tm_k, bar(B_KFULL0 + s), args.h_first, hk, j * BN, b);
+    mbar_expect_tx(bar(B_VFULL0 + s), TILE_BYTES);
+    load_tile<NSUB, 128>(base + OFF_V + s * TILE_BYTES, &tm_v, bar(B_VFULL0 + s), args.h_first, hk, j * BN, b);
+  };
+  if (warp == 4 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
     for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i == B_PREADY || i == B_SFREE) ? 128 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
+    load_tile<NSUB, 128>(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
+    for (int j = 0; j < min(2, nblocks); ++j) load_kv(j);
   }
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
@@ -193,11 +224,9 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   // A failed wait has already set the abort flag, which every other wait polls: the loops need no check of their own.
   if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer: Q, then K and V tiles, two stages each
+    // ------------------------------------------------------------------ TMA producer: K and V tiles from block 2 on, two stages each
     if (lane == 0) {
-      mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
-      load_tile<NSUB, 128>(base + OFF_Q, &tm_q, bar(B_QFULL), args.h_first, h, q0, b);
-      for (int j = 0; j < nblocks; ++j) {
+      for (int j = 2; j < nblocks; ++j) {
         const int s = j & 1;
         const uint32_t ph = ((j >> 1) & 1) ^ 1;
         // a K stage is free once the S product that read it finished, a V stage once its P V finished
@@ -282,6 +311,7 @@ struct BwdArgs {
   const float* lse2;              // lse * log2(e)
   const float* dr;
   int heads, kv_heads, time, h_first;
+  int planes, group;              // of this launch: batch * kv_heads (dK/dV) or batch * heads (dQ); planes per L2 group
   float scale;
   uint32_t* fault;
 };
@@ -331,28 +361,31 @@ constexpr int SUB = 64;
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
 constexpr int IN_STAGES = 2;
 
-// One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; l2, dd: the columns' (dK/dV) or
-// the row's (dQ) statistics; vis(e): column e is visible. Writes the 16-byte chunks of P (optional) and dS.
-template <bool MASKED, bool WRITE_P, class L2, class DD, class VIS>
-__device__ __forceinline__ void bwd_step(const uint32_t (&s)[32], const uint32_t (&dp)[32], float sl2, L2&& l2, DD&& dd, VIS&& vis, uint8_t* p_row, uint8_t* ds_row,
-                                         int half, int tid) {
+// One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; stats: the columns' (dK/dV) or
+// the row's (dQ) statistics, eight columns at a time; vis(e): column e is visible. emit(g, p, ds) takes the packed bf16 results, eight columns
+// (one 16-byte chunk each of P and dS) at a time: kept in registers or stored, as the caller's pipeline wants.
+template <bool MASKED, class STATS, class VIS, class EMIT>
+__device__ __forceinline__ void bwd_step(const uint32_t (&s)[32], const uint32_t (&dp)[32], float sl2, STATS&& stats, VIS&& vis, EMIT&& emit) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    float pv[8], dv[8];
+    float pv[8], dv[8], l2[8], dd[8];
+    stats(g, l2, dd);                            // lse * log2(e) and Dr of columns 8g .. 8g + 7
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int c = g * 8 + e;
-      const float p = fast_exp2(fmaf(__uint_as_float(s[c]), sl2, -l2(c)));
-      const float ds = p * (__uint_as_float(dp[c]) - dd(c));
+      const float p = fast_exp2(fmaf(__uint_as_float(s[c]), sl2, -l2[e]));
+      const float ds = p * (__uint_as_float(dp[c]) - dd[e]);
       // masked columns: select, never multiply by zero (rows past the sequence end carry whatever the buffers held)
       pv[e] = (!MASKED || vis(c)) ? p : 0.0f;
       dv[e] = (!MASKED || vis(c)) ? ds : 0.0f;
     }
-    const int ci = half * 4 + g;             // 16-byte chunk of the 128-byte row; the swizzle XORs it with row % 8
-    if (WRITE_P)
-      *reinterpret_cast<uint4*>(p_row + ((ci ^ (tid & 7)) << 4)) = make_uint4(pack2_bf16(pv[0], pv[1]), pack2_bf16(pv[2], pv[3]), pack2_bf16(pv[4], pv[5]), pack2_bf16(pv[6], pv[7]));
-    *reinterpret_cast<uint4*>(ds_row + ((ci ^ (tid & 7)) << 4)) = make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7]));
+    emit(g, make_uint4(pack2_bf16(pv[0], pv[1]), pack2_bf16(pv[2], pv[3]), pack2_bf16(pv[4], pv[5]), pack2_bf16(pv[6], pv[7])),
+         make_uint4(pack2_bf16(dv[0], dv[1]), pack2_bf16(dv[2], dv[3]), pack2_bf16(dv[4], dv[5]), pack2_bf16(dv[6], dv[7])));
   }
+}
+// 16-byte chunk half * 4 + g of a thread's 128-byte row; the swizzle XORs the chunk index with row % 8
+__device__ __forceinline__ void store_chunk(uint8_t* row, const uint4& v, int half, int g, int tid) {
+  *reinterpret_cast<uint4*>(row + (((half * 4 + g) ^ (tid & 7)) << 4)) = v;
 }
 
 // ---- dK, dV
@@ -364,7 +397,7 @@ template <int D> struct Dkv {
   static constexpr int TMEM_COLS = D == 64 ? 256 : 512;         // S^T 64 + dP^T 64 + dV D + dK D
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
-enum { KB_KVFULL = 0, KB_INFULL0, KB_INEMPTY0 = KB_INFULL0 + IN_STAGES, KB_SFULL = KB_INEMPTY0 + IN_STAGES, KB_PREADY, KB_DONE, KB_COUNT };
+enum { KB_KVFULL = 0, KB_INFULL0, KB_INEMPTY0 = KB_INFULL0 + IN_STAGES, KB_SFULL = KB_INEMPTY0 + IN_STAGES, KB_SFREE, KB_PREADY, KB_PFREE, KB_DONE, KB_COUNT };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dkv<D>::CTAS)
@@ -384,15 +417,34 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse2 64 | dr 64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k0 = blockIdx.x * BN;
-  const int plane = blockIdx.y, b = plane / args.kv_heads, hk = plane % args.kv_heads, rep = args.heads / args.kv_heads;
+  const TileOrder ord = tile_order(blockIdx.x, args.planes, args.group, gridDim.x / args.planes);
+  const int k0 = ord.rank * BN;                // early key tiles see the most queries
+  const int plane = ord.plane, b = plane / args.kv_heads, hk = plane % args.kv_heads, rep = args.heads / args.kv_heads;
   const int q_subs = (args.time - k0 + SUB - 1) / SUB;      // query steps k0, k0 + 64, ... (k0 is a multiple of 128)
   const int iters = rep * q_subs;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < KB_COUNT; ++i) mbar_init(bar(i), i == KB_PREADY ? 256 : 1);
+  // step `it` of the walk: query head hk * rep + it / q_subs, queries from k0 + (it % q_subs) * SUB; the step's row
+  // statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
+  auto load_step = [&](int it) {
+    const int s = it % IN_STAGES, h = hk * rep + it / q_subs, q0 = k0 + (it % q_subs) * SUB;
+    const uint32_t stat_bytes = (uint32_t)min(SUB, args.time - q0) * 4u;
+    const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
+    mbar_expect_tx(bar(KB_INFULL0 + s), 2 * STEP_BYTES + 2 * stat_bytes);
+    load_tile<NSUB, 64>(base + KV_OFF_Q + s * STEP_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
+    load_tile<NSUB, 64>(base + KV_OFF_G + s * STEP_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
+    bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
+    bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
+  };
+  // the producer thread sets the barriers up and starts the first loads before the CTA-wide sync
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_g);
+    for (int i = 0; i < KB_COUNT; ++i) mbar_init(bar(i), (i == KB_PREADY || i == KB_SFREE) ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(bar(KB_KVFULL), 2 * TILE_BYTES);
+    load_tile<NSUB, 128>(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
+    load_tile<NSUB, 128>(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
+    for (int it = 0; it < min(IN_STAGES, iters); ++it) load_step(it);
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS) : "memory");
@@ -406,23 +458,9 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 
   if (warp == 8) {
     if (lane == 0) {
-      mbar_expect_tx(bar(KB_KVFULL), 2 * TILE_BYTES);
-      load_tile<NSUB, 128>(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
-      load_tile<NSUB, 128>(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
-      int h = hk * rep, q0 = k0;
-      for (int it = 0; it < iters; ++it) {
-        const int s = it % IN_STAGES;
-        if (!mbar_wait(bar(KB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
-        // the step's row statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
-        const uint32_t stat_bytes = (uint32_t)min(SUB, args.time - q0) * 4u;
-        const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
-        mbar_expect_tx(bar(KB_INFULL0 + s), 2 * STEP_BYTES + 2 * stat_bytes);
-        load_tile<NSUB, 64>(base + KV_OFF_Q + s * STEP_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
-        load_tile<NSUB, 64>(base + KV_OFF_G + s * STEP_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
-        bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
-        bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
-        q0 += SUB;
-        if (q0 >= args.time) { q0 = k0; ++h; }   // next query head of the group
+      for (int it = IN_STAGES; it < iters; ++it) {
+        if (!mbar_wait(bar(KB_INEMPTY0 + it % IN_STAGES), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
+        load_step(it);
       }
     }
   } else if (warp == 9) {
@@ -431,8 +469,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       const uint32_t k_lo = desc_lo(base + KV_OFF_K, 0), v_lo = desc_lo(base + KV_OFF_V, 0), q_lo = desc_lo(base + KV_OFF_Q, 0), g_lo = desc_lo(base + KV_OFF_G, 0);
       const uint32_t qm_lo = desc_lo(base + KV_OFF_Q, ST64), gm_lo = desc_lo(base + KV_OFF_G, ST64);   // the same tiles as MN-major B operands (64-wide blocks ST64 apart)
       const uint32_t p_lo = desc_lo(base + KV_OFF_P, 0), ds_lo = desc_lo(base + KV_OFF_DS, 0);
-      // S^T = K Q^T and dP^T = V dO^T of step i. Their commit also covers the dV / dK MMAs of step i - 1 issued just before,
-      // so a compute thread that sees SFULL may overwrite P and dS.
+      // S^T = K Q^T and dP^T = V dO^T of step i
       auto issue_s = [&](uint32_t i) {
         const uint32_t st = (i % IN_STAGES) * STEP16;
 #pragma unroll
@@ -446,7 +483,19 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       bool ok = mbar_wait(bar(KB_KVFULL), 0, args.fault, abort_flag) && mbar_wait(bar(KB_INFULL0), 0, args.fault, abort_flag);
       if (ok) { fence_after(); issue_s(0); }
       for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
-        // every compute thread has read S^T / dP^T of this step and written P / dS
+        // Two CTAs per SM (head_dim 64): the next step's S^T / dP^T go out as soon as every compute thread holds this
+        // step's in registers, ahead of this step's dV / dK, so the tensor pipe works through the threads' exp and pack
+        // phase. One CTA per SM (head_dim 128): dV / dK first, which hands the input stage back to the loads sooner.
+        auto next_s = [&]() -> bool {
+          if (it + 1 >= (uint32_t)iters) return true;
+          if (!mbar_wait(bar(KB_SFREE), it & 1, args.fault, abort_flag)) return false;
+          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) return false;
+          fence_after();
+          issue_s(it + 1);
+          return true;
+        };
+        if (C::CTAS == 2 && !next_s()) break;
+        // every compute thread has written P / dS of this step
         if (!mbar_wait(bar(KB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
         const uint32_t st = (it % IN_STAGES) * STEP16;
@@ -457,10 +506,9 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
           umma_lh(tmem_base + 128 + D, ds_lo + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(KB_INEMPTY0 + it % IN_STAGES));
-        if (it + 1 == (uint32_t)iters) { umma_commit(bar(KB_DONE)); break; }
-        if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
-        fence_after();
-        issue_s(it + 1);
+        umma_commit(bar(KB_PFREE));               // P and dS may be overwritten
+        if (it + 1 == (uint32_t)iters) umma_commit(bar(KB_DONE));
+        if (C::CTAS == 1 && !next_s()) break;
       }
     }
   } else {
@@ -480,13 +528,33 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       tmem_ld32(lane_base + half * 32, rs);
       tmem_ld32(lane_base + 64 + half * 32, rp);
       tmem_wait_ld();
-      const int qb = q0 + half * 32;
-      auto fl2 = [&](int c) { return st[c]; };
-      auto fdd = [&](int c) { return st[SUB + c]; };
-      auto vis = [&](int c) { return key < args.time && qb + c < args.time && key <= qb + c; };
-      if (q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time) bwd_step<true, true>(rs, rp, sl2, fl2, fdd, vis, p_row, ds_row, half, tid);   // diagonal steps or a ragged end
-      else bwd_step<false, true>(rs, rp, sl2, fl2, fdd, vis, p_row, ds_row, half, tid);
       fence_before();
+      mbar_arrive(bar(KB_SFREE));                // the accumulator columns may take the next step
+      const int qb = q0 + half * 32;
+      // every thread of the warp reads the same statistics: 16-byte broadcast loads, four per eight columns
+      auto stats = [&](int g, float (&l2)[8], float (&dd)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(st + g * 8), b = *reinterpret_cast<const float4*>(st + g * 8 + 4);
+        const float4 c = *reinterpret_cast<const float4*>(st + SUB + g * 8), d = *reinterpret_cast<const float4*>(st + SUB + g * 8 + 4);
+        l2[0] = a.x; l2[1] = a.y; l2[2] = a.z; l2[3] = a.w; l2[4] = b.x; l2[5] = b.y; l2[6] = b.z; l2[7] = b.w;
+        dd[0] = c.x; dd[1] = c.y; dd[2] = c.z; dd[3] = c.w; dd[4] = d.x; dd[5] = d.y; dd[6] = d.z; dd[7] = d.w;
+      };
+      auto vis = [&](int c) { return key < args.time && qb + c < args.time && key <= qb + c; };
+      const bool masked = q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time;   // diagonal steps or a ragged end
+      // P and dS are free once the previous step's dV / dK MMAs have read them. With two CTAs per SM those run behind the
+      // next S^T / dP^T, so the results wait in registers and the wait comes last; with one CTA per SM they finished before
+      // this step's S^T was issued, and each chunk is stored as it is formed.
+      if (C::CTAS == 2) {
+        uint4 pp[4], dsp[4];
+        auto keep = [&](int g, const uint4& p, const uint4& ds) { pp[g] = p; dsp[g] = ds; };
+        if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, keep); else bwd_step<false>(rs, rp, sl2, stats, vis, keep);
+        if (it > 0 && !mbar_wait(bar(KB_PFREE), (it - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) { store_chunk(p_row, pp[g], half, g, tid); store_chunk(ds_row, dsp[g], half, g, tid); }
+      } else {
+        if (it > 0 && !mbar_wait(bar(KB_PFREE), (it - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        auto put = [&](int g, const uint4& p, const uint4& ds) { store_chunk(p_row, p, half, g, tid); store_chunk(ds_row, ds, half, g, tid); };
+        if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, put); else bwd_step<false>(rs, rp, sl2, stats, vis, put);
+      }
       fence_async_smem();
       mbar_arrive(bar(KB_PREADY));
       q0 += SUB;
@@ -515,7 +583,7 @@ template <int D> struct Dq {
   static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;       // D 64: 81 KB (two CTAs per SM); D 128: 145 KB
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
-enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL = QB_INEMPTY0 + IN_STAGES, QB_PREADY, QB_DONE, QB_COUNT };
+enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL = QB_INEMPTY0 + IN_STAGES, QB_SFREE, QB_PREADY, QB_PFREE, QB_DONE, QB_COUNT };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dq<D>::CTAS)
@@ -534,16 +602,29 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
+  const TileOrder ord = tile_order(blockIdx.x, args.planes, args.group, gridDim.x / args.planes);
+  const int qt = gridDim.x / args.planes - 1 - ord.rank;
   const int q0 = qt * BM;
-  const int plane = blockIdx.y, b = plane / args.heads, h = plane % args.heads, hk = h / (args.heads / args.kv_heads);
+  const int plane = ord.plane, b = plane / args.heads, h = plane % args.heads, hk = h / (args.heads / args.kv_heads);
   const int n_end = min(args.time, q0 + BM);
   const int iters = (n_end + SUB - 1) / SUB;     // key steps 0, 64, ...
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < QB_COUNT; ++i) mbar_init(bar(i), i == QB_PREADY ? 256 : 1);
+  auto load_step = [&](int it) {
+    const int s = it % IN_STAGES;
+    mbar_expect_tx(bar(QB_INFULL0 + s), 2 * STEP_BYTES);
+    load_tile<NSUB, 64>(base + DQ_OFF_K + s * STEP_BYTES, &tm_k, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
+    load_tile<NSUB, 64>(base + DQ_OFF_V + s * STEP_BYTES, &tm_v, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
+  };
+  // the producer thread sets the barriers up and starts the first loads before the CTA-wide sync
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_g);
+    for (int i = 0; i < QB_COUNT; ++i) mbar_init(bar(i), (i == QB_PREADY || i == QB_SFREE) ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(bar(QB_QDFULL), 2 * TILE_BYTES);
+    load_tile<NSUB, 128>(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
+    load_tile<NSUB, 128>(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
+    for (int it = 0; it < min(IN_STAGES, iters); ++it) load_step(it);
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
@@ -557,15 +638,9 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 
   if (warp == 8) {
     if (lane == 0) {
-      mbar_expect_tx(bar(QB_QDFULL), 2 * TILE_BYTES);
-      load_tile<NSUB, 128>(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
-      load_tile<NSUB, 128>(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
-      for (int it = 0; it < iters; ++it) {
-        const int s = it % IN_STAGES;
-        if (!mbar_wait(bar(QB_INEMPTY0 + s), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
-        mbar_expect_tx(bar(QB_INFULL0 + s), 2 * STEP_BYTES);
-        load_tile<NSUB, 64>(base + DQ_OFF_K + s * STEP_BYTES, &tm_k, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
-        load_tile<NSUB, 64>(base + DQ_OFF_V + s * STEP_BYTES, &tm_v, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
+      for (int it = IN_STAGES; it < iters; ++it) {
+        if (!mbar_wait(bar(QB_INEMPTY0 + it % IN_STAGES), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
+        load_step(it);
       }
     }
   } else if (warp == 9) {
@@ -573,8 +648,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       const uint32_t idesc_s = make_idesc(BM, SUB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
       const uint32_t q_lo = desc_lo(base + DQ_OFF_Q, 0), g_lo = desc_lo(base + DQ_OFF_G, 0), k_lo = desc_lo(base + DQ_OFF_K, 0), v_lo = desc_lo(base + DQ_OFF_V, 0);
       const uint32_t km_lo = desc_lo(base + DQ_OFF_K, ST64), ds_lo = desc_lo(base + DQ_OFF_DS, 0);
-      // S = Q K^T and dP = dO V^T of step i; the commit also covers the dQ MMAs of step i - 1 issued just before, so a
-      // compute thread that sees SFULL may overwrite dS.
+      // S = Q K^T and dP = dO V^T of step i
       auto issue_s = [&](uint32_t i) {
         const uint32_t st = (i % IN_STAGES) * STEP16;
 #pragma unroll
@@ -588,6 +662,16 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       bool ok = mbar_wait(bar(QB_QDFULL), 0, args.fault, abort_flag) && mbar_wait(bar(QB_INFULL0), 0, args.fault, abort_flag);
       if (ok) { fence_after(); issue_s(0); }
       for (uint32_t it = 0; it < (uint32_t)iters && ok; ++it) {
+        // the next step's S / dP: ahead of this step's dQ with two CTAs per SM, after it with one (see the dK/dV kernel)
+        auto next_s = [&]() -> bool {
+          if (it + 1 >= (uint32_t)iters) return true;
+          if (!mbar_wait(bar(QB_SFREE), it & 1, args.fault, abort_flag)) return false;
+          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) return false;
+          fence_after();
+          issue_s(it + 1);
+          return true;
+        };
+        if (C::CTAS == 2 && !next_s()) break;
         if (!mbar_wait(bar(QB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
         const uint32_t st = (it % IN_STAGES) * STEP16;
@@ -595,10 +679,9 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
           umma_lh(tmem_base + 128, ds_lo + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(QB_INEMPTY0 + it % IN_STAGES));
-        if (it + 1 == (uint32_t)iters) { umma_commit(bar(QB_DONE)); break; }
-        if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) break;
-        fence_after();
-        issue_s(it + 1);
+        umma_commit(bar(QB_PFREE));               // dS may be overwritten
+        if (it + 1 == (uint32_t)iters) umma_commit(bar(QB_DONE));
+        if (C::CTAS == 1 && !next_s()) break;
       }
     }
   } else {
@@ -617,12 +700,26 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       tmem_ld32(lane_base + half * 32, rs);
       tmem_ld32(lane_base + 64 + half * 32, rp);
       tmem_wait_ld();
-      auto fl2 = [&](int) { return lse_row; };
-      auto fdd = [&](int) { return dr_row; };
-      auto vis = [&](int c) { return key0 + c <= row && key0 + c < args.time; };
-      if (it * SUB + SUB > q0 || it * SUB + SUB > args.time) bwd_step<true, false>(rs, rp, sl2, fl2, fdd, vis, nullptr, ds_row, half, tid);
-      else bwd_step<false, false>(rs, rp, sl2, fl2, fdd, vis, nullptr, ds_row, half, tid);
       fence_before();
+      mbar_arrive(bar(QB_SFREE));
+      auto stats = [&](int, float (&l2)[8], float (&dd)[8]) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { l2[e] = lse_row; dd[e] = dr_row; }
+      };
+      auto vis = [&](int c) { return key0 + c <= row && key0 + c < args.time; };
+      const bool masked = it * SUB + SUB > q0 || it * SUB + SUB > args.time;
+      if (C::CTAS == 2) {                           // as in the dK/dV kernel: keep, wait late, store
+        uint4 dsp[4];
+        auto keep = [&](int g, const uint4&, const uint4& ds) { dsp[g] = ds; };
+        if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, keep); else bwd_step<false>(rs, rp, sl2, stats, vis, keep);
+        if (it > 0 && !mbar_wait(bar(QB_PFREE), (it - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) store_chunk(ds_row, dsp[g], half, g, tid);
+      } else {
+        if (it > 0 && !mbar_wait(bar(QB_PFREE), (it - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        auto put = [&](int g, const uint4&, const uint4& ds) { store_chunk(ds_row, ds, half, g, tid); };
+        if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, put); else bwd_step<false>(rs, rp, sl2, stats, vis, put);
+      }
       fence_async_smem();
       mbar_arrive(bar(QB_PREADY));
     }
@@ -693,7 +790,9 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
   FwdArgs args;
   args.out = SdpaView<bf16>{(bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]};
   args.lse = lse; args.heads = d.heads; args.kv_heads = d.kv_heads; args.time = d.time; args.h_first = hf ? 1 : 0; args.scale = d.scale; args.fault = be->fault_dev;
-  dim3 grid((d.time + BM - 1) / BM, d.batch * d.heads);
+  args.planes = d.batch * d.heads;
+  args.group = planes_per_group(d.time, d.dim, args.planes);
+  dim3 grid((unsigned)(((d.time + BM - 1) / BM) * args.planes));
   return d.dim == 64 ? launch_fwd<64>(be, op, mq, mk, mv, args, grid) : launch_fwd<128>(be, op, mq, mk, mv, args, grid);
 }
 
@@ -712,11 +811,15 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
   OJC_LAUNCHED(be, op);
   a.g0 = SdpaView<bf16>{(bf16*)gk->data, gk->stride[0], gk->stride[1], gk->stride[2]};
   a.g1 = SdpaView<bf16>{(bf16*)gv->data, gv->stride[0], gv->stride[1], gv->stride[2]};
-  dim3 grid_k((d.time + BN - 1) / BN, d.batch * d.kv_heads);
+  a.planes = d.batch * d.kv_heads;
+  a.group = planes_per_group(d.time, d.dim, a.planes);
+  dim3 grid_k((unsigned)(((d.time + BN - 1) / BN) * a.planes));
   sdpa_bwd_dkv_tcgen05_kernel<D><<<grid_k, BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);   // q, dO in 64-row steps
   OJC_LAUNCHED(be, op);
   a.g0 = SdpaView<bf16>{(bf16*)gq->data, gq->stride[0], gq->stride[1], gq->stride[2]};
-  dim3 grid_q((d.time + BM - 1) / BM, d.batch * d.heads);
+  a.planes = d.batch * d.heads;
+  a.group = planes_per_group(d.time, d.dim, a.planes);
+  dim3 grid_q((unsigned)(((d.time + BM - 1) / BM) * a.planes));
   sdpa_bwd_dq_tcgen05_kernel<D><<<grid_q, BWD_THREADS, Dq<D>::SMEM_BYTES, be->stream>>>(m[0], m[5], m[6], m[3], a);      // k, v in 64-row steps
   OJC_LAUNCHED(be, op);
   return OJC_OK;
