@@ -70,6 +70,9 @@ ojc_status ojc_open(int32_t device_ordinal, uint64_t budget_bytes, ojc_backend**
 ojc_status ojc_close(ojc_backend* be);
 const char* ojc_last_error(void);
 const char* ojc_status_name(int32_t status);
+/* FNV-1a (offset 0xcbf29ce484222325 to start) over host bytes, continuing from `hash`: the run id of Trainer::new
+ * (ojas-model/src/trainer.rs:436-456) hashes the config texts and every parameter's f32 bytes. */
+uint64_t ojc_fnv1a64(uint64_t hash, const void* bytes, uint64_t count);
 ojc_status ojc_alloc(ojc_backend* be, uint64_t bytes, void** out);              /* charges the budget (budget.rs:65) */
 ojc_status ojc_free(ojc_backend* be, void* ptr);                                /* refunds it */
 ojc_status ojc_budget(ojc_backend* be, uint64_t* cap, uint64_t* live, uint64_t* peak); /* Budget::{cap,live,peak_bytes} budget.rs:19-240 */

@@ -50,6 +50,9 @@ def load() -> C.CDLL:
     lib.ojc_stream.restype = C.c_void_p
     lib.ojc_kernel_launches.restype = C.c_uint64
     lib.ojc_trainer_param_count.restype = C.c_int64
+    lib.ojc_trainer_steps_done.restype = C.c_uint64
+    lib.ojc_fnv1a64.restype = C.c_uint64
+    lib.ojc_fnv1a64.argtypes = [C.c_uint64, C.c_void_p, C.c_uint64]
     lib.ojc_trainer_bucket_count.restype = C.c_int64
     return lib
 

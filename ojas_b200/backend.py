@@ -558,6 +558,24 @@ class Trainer:
         _check(lib.ojc_trainer_get_grad(self._h, C.c_int64(index), C.c_void_p(out.ctypes.data), C.c_uint64(out.size)))
         return out
 
+    def get_moment(self, index: int, slot: int) -> np.ndarray:
+        """Optimizer state of one parameter: slot 0 is the Muon momentum or the AdamW first moment, slot 1 the AdamW second."""
+        out = np.empty(self.params[index].shape, np.float32)
+        _check(lib.ojc_trainer_get_moment(self._h, C.c_int64(index), C.c_int32(slot), C.c_void_p(out.ctypes.data), C.c_uint64(out.size)))
+        return out
+
+    def set_moment(self, index: int, slot: int, values: np.ndarray):
+        v = np.ascontiguousarray(values, np.float32)
+        _check(lib.ojc_trainer_set_moment(self._h, C.c_int64(index), C.c_int32(slot), C.c_void_p(v.ctypes.data), C.c_uint64(v.size)))
+
+    @property
+    def steps_done(self) -> int:
+        return int(lib.ojc_trainer_steps_done(self._h))
+
+    @steps_done.setter
+    def steps_done(self, step: int):
+        _check(lib.ojc_trainer_set_steps_done(self._h, C.c_uint64(step)))
+
     @staticmethod
     def _ids(a) -> np.ndarray:
         return np.ascontiguousarray(a, np.uint32)

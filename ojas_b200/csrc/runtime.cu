@@ -71,6 +71,13 @@ static void release_cache(ojc_backend* be) {
 extern "C" {
 
 const char* ojc_last_error(void) { return g_last_error.c_str(); }
+// FNV-1a over host bytes, continuing from `hash` (the run id of ojas-model/src/trainer.rs:436-456 hashes every parameter)
+uint64_t ojc_fnv1a64(uint64_t hash, const void* bytes, uint64_t count) {
+  const uint8_t* p = static_cast<const uint8_t*>(bytes);
+  for (uint64_t i = 0; i < count; ++i) hash = (hash ^ p[i]) * 0x100000001b3ull;
+  return hash;
+}
+
 const char* ojc_status_name(int32_t s) { return (s >= 0 && s <= OJC_ERR_NO_DEVICE) ? kStatusNames[s] : "Unknown"; }
 
 ojc_status ojc_open(int32_t ordinal, uint64_t budget_bytes, ojc_backend** out) {

@@ -359,7 +359,8 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr, float 
 
 constexpr int SUB = 64;
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
-constexpr int IN_STAGES = 2;
+constexpr int IN_STAGES = 2;          // q / dO stages of the dK/dV kernel (a third does not fit beside a second CTA at head_dim 64)
+constexpr int DQ_STAGES = 3;          // k / v stages of the dQ kernel
 
 // One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; stats: the columns' (dK/dV) or
 // the row's (dQ) statistics, eight columns at a time; vis(e): column e is visible. emit(g, p, ds) takes the packed bf16 results, eight columns
@@ -578,12 +579,12 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 // ---- dQ
 template <int D> struct Dq {
   static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128, STEP_BYTES = NSUB * ST64;   // q / dO tile; one step of k or v
-  static constexpr int OFF_Q = 0, OFF_G = TILE_BYTES, OFF_K = 2 * TILE_BYTES, OFF_V = OFF_K + IN_STAGES * STEP_BYTES, OFF_DS = OFF_V + IN_STAGES * STEP_BYTES,
+  static constexpr int OFF_Q = 0, OFF_G = TILE_BYTES, OFF_K = 2 * TILE_BYTES, OFF_V = OFF_K + DQ_STAGES * STEP_BYTES, OFF_DS = OFF_V + DQ_STAGES * STEP_BYTES,
                        OFF_BAR = OFF_DS + PT_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;       // D 64: 81 KB (two CTAs per SM); D 128: 145 KB
+  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;       // D 64: 97 KB (two CTAs per SM); D 128: 177 KB
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
-enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + IN_STAGES, QB_SFULL = QB_INEMPTY0 + IN_STAGES, QB_SFREE, QB_PREADY, QB_PFREE, QB_DONE, QB_COUNT };
+enum { QB_QDFULL = 0, QB_INFULL0, QB_INEMPTY0 = QB_INFULL0 + DQ_STAGES, QB_SFULL = QB_INEMPTY0 + DQ_STAGES, QB_SFREE, QB_PREADY, QB_PFREE, QB_DONE, QB_COUNT };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dq<D>::CTAS)
@@ -610,7 +611,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   const int iters = (n_end + SUB - 1) / SUB;     // key steps 0, 64, ...
 
   auto load_step = [&](int it) {
-    const int s = it % IN_STAGES;
+    const int s = it % DQ_STAGES;
     mbar_expect_tx(bar(QB_INFULL0 + s), 2 * STEP_BYTES);
     load_tile<NSUB, 64>(base + DQ_OFF_K + s * STEP_BYTES, &tm_k, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
     load_tile<NSUB, 64>(base + DQ_OFF_V + s * STEP_BYTES, &tm_v, bar(QB_INFULL0 + s), args.h_first, hk, it * SUB, b);
@@ -624,7 +625,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     mbar_expect_tx(bar(QB_QDFULL), 2 * TILE_BYTES);
     load_tile<NSUB, 128>(base + DQ_OFF_Q, &tm_q, bar(QB_QDFULL), args.h_first, h, q0, b);
     load_tile<NSUB, 128>(base + DQ_OFF_G, &tm_g, bar(QB_QDFULL), args.h_first, h, q0, b);
-    for (int it = 0; it < min(IN_STAGES, iters); ++it) load_step(it);
+    for (int it = 0; it < min(DQ_STAGES, iters); ++it) load_step(it);
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
@@ -638,8 +639,8 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 
   if (warp == 8) {
     if (lane == 0) {
-      for (int it = IN_STAGES; it < iters; ++it) {
-        if (!mbar_wait(bar(QB_INEMPTY0 + it % IN_STAGES), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
+      for (int it = DQ_STAGES; it < iters; ++it) {
+        if (!mbar_wait(bar(QB_INEMPTY0 + it % DQ_STAGES), ((it / DQ_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
         load_step(it);
       }
     }
@@ -650,7 +651,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       const uint32_t km_lo = desc_lo(base + DQ_OFF_K, ST64), ds_lo = desc_lo(base + DQ_OFF_DS, 0);
       // S = Q K^T and dP = dO V^T of step i
       auto issue_s = [&](uint32_t i) {
-        const uint32_t st = (i % IN_STAGES) * STEP16;
+        const uint32_t st = (i % DQ_STAGES) * STEP16;
 #pragma unroll
         for (uint32_t kk = 0; kk < D / 16; ++kk)
           umma_lh(tmem_base, q_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
@@ -666,7 +667,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         auto next_s = [&]() -> bool {
           if (it + 1 >= (uint32_t)iters) return true;
           if (!mbar_wait(bar(QB_SFREE), it & 1, args.fault, abort_flag)) return false;
-          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) return false;
+          if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % DQ_STAGES), ((it + 1) / DQ_STAGES) & 1, args.fault, abort_flag)) return false;
           fence_after();
           issue_s(it + 1);
           return true;
@@ -674,11 +675,11 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         if (C::CTAS == 2 && !next_s()) break;
         if (!mbar_wait(bar(QB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t st = (it % IN_STAGES) * STEP16;
+        const uint32_t st = (it % DQ_STAGES) * STEP16;
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dQ += dS K   (K as the MN-major B operand: 16 keys = 2048 bytes)
           umma_lh(tmem_base + 128, ds_lo + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(QB_INEMPTY0 + it % IN_STAGES));
+        umma_commit(bar(QB_INEMPTY0 + it % DQ_STAGES));
         umma_commit(bar(QB_PFREE));               // dS may be overwritten
         if (it + 1 == (uint32_t)iters) umma_commit(bar(QB_DONE));
         if (C::CTAS == 1 && !next_s()) break;

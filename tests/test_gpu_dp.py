@@ -1,0 +1,99 @@
+"""Data parallelism on real GPUs (NCCL, one process per GPU): needs at least two devices, skipped otherwise.
+
+Two ranks run the step driver on their own micro-batches with the backward seeded by 1/world, exchange the gradient
+buckets (ojas_b200/dp.py) and apply the optimizer. Checked: the reduced gradients equal the CPU oracle's sum of the two
+seeded micro-batch gradients (the reference's K = 2 accumulation, ojas-model/src/trainer.rs:892-1001) at the f32 gate,
+and after two steps both ranks hold the same parameter bits. Under bf16 autocast the weight gradients are written on the
+driver's second stream, so this also covers the ordering of that stream against the bucket-ready events.
+"""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parents[1]
+
+WORKER = r"""
+import json, os, sys
+import numpy as np
+import torch, torch.distributed as dist
+from safetensors import safe_open
+sys.path.insert(0, os.environ["OJAS_ROOT"])
+from ojas_b200 import CudaBackend, TrainConfig, Trainer, checkpoint as ck
+from ojas_b200.dp import BucketAllReduce
+
+rank, world, out = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), os.environ["OJAS_OUT"]
+autocast = os.environ["OJAS_AUTOCAST"] == "1"
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+f = safe_open(os.path.join(os.environ["OJAS_ROOT"], "tests", "golden", "tiny", "init.safetensors"), "np")
+spec = ck.spec_from_json(f.metadata()["ojas.spec"])
+be = CudaBackend(rank, 8 << 30)
+tr = Trainer(be, spec, TrainConfig(optimizer="muon", autocast_bf16=autocast, ns5_bf16=autocast, loss_seed=1.0 / world), 2, 32)
+tr.set_params([f.get_tensor(p.name) for p in tr.params])
+reducer = BucketAllReduce(be, tr, torch.device("cuda", rank))
+rng = np.random.default_rng(100 + rank)
+result = {}
+for step in range(2):
+    b = rng.integers(0, spec.vocab, (2, 33), dtype=np.uint32)
+    ids, tg = be.upload(np.ascontiguousarray(b[:, :-1])), be.upload(np.ascontiguousarray(b[:, 1:]))
+    tr.gradients_device(ids, tg)
+    reducer.exchange()
+    be.sync()
+    if step == 0:
+        result.update({"g." + p.name: tr.get_grad(i) for i, p in enumerate(tr.params) if p.trains})
+        result["batch"] = b
+    tr.apply(read_norm=False)
+    tr.finish()
+result.update({"p." + p.name: tr.get_param(i) for i, p in enumerate(tr.params)})
+np.savez(os.path.join(out, f"rank{rank}.npz"), **result)
+dist.barrier()
+tr.close(); be.close()
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.parametrize("autocast", [False, True])
+def test_two_ranks_reduce_to_the_accumulated_gradient_and_stay_bit_identical(tmp_path, golden_dir, autocast):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from safetensors import safe_open
+    from oracle import oracle as orc
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, OJAS_ROOT=str(ROOT), OJAS_OUT=str(tmp_path), OJAS_AUTOCAST="1" if autocast else "0", NCCL_NVLS_ENABLE="0")
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29533" if autocast else "29532", str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-4000:]
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    names = [k for k in r0.files if k.startswith("p.")]
+    assert names and all(r0[k].tobytes() == r1[k].tobytes() for k in names), "ranks diverged"
+    grads = [k for k in r0.files if k.startswith("g.")]
+    assert all(r0[k].tobytes() == r1[k].tobytes() for k in grads), "ranks hold different reduced gradients"
+
+    f = safe_open(str(golden_dir / "tiny" / "init.safetensors"), "np")
+    s = json.loads(f.metadata()["ojas.spec"])
+    spec = orc.Spec(vocab=s["vocab"], n_embd=s["n_embd"], n_layer=s["n_layer"], n_head=s["n_head"], n_kv_head=s["n_kv_head"], head_dim=s["head_dim"],
+                    hidden=s["hidden"], max_seq=s["max_seq"], window=s.get("window"), rope_base=s["rope_base"], rms_eps=s["rms_eps"])
+    table = [p.name for p in orc.param_table(spec)]
+    params = [f.get_tensor(name) for name in table]
+    total = None
+    for r in (r0, r1):
+        b = r["batch"]
+        _, g, _ = orc.forward_loss(spec, params, b[:, :-1], b[:, 1:], seed=0.5)
+        total = [a.copy() for a in g] if total is None else [a + c for a, c in zip(total, g)]
+    total = dict(zip(table, total))
+    tol = 3e-2 if autocast else 1e-4
+    for k in grads:
+        want, got = total[k[2:]].astype(np.float64).ravel(), r0[k].astype(np.float64).ravel()
+        if not np.any(want):
+            assert not np.any(got), k
+        else:
+            assert np.linalg.norm(got - want) / np.linalg.norm(want) <= tol, (k, np.linalg.norm(got - want) / np.linalg.norm(want))
