@@ -359,7 +359,7 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr, float 
 
 constexpr int SUB = 64;
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
-constexpr int IN_STAGES = 2;          // q / dO stages of the dK/dV kernel (a third does not fit beside a second CTA at head_dim 64)
+constexpr int IN_STAGES = 3;          // q / dO stages of the dK/dV kernel
 constexpr int DQ_STAGES = 3;          // k / v stages of the dQ kernel
 
 // One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; stats: the columns' (dK/dV) or
@@ -393,8 +393,13 @@ __device__ __forceinline__ void store_chunk(uint8_t* row, const uint4& v, int ha
 template <int D> struct Dkv {
   static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128, STEP_BYTES = NSUB * ST64;   // K / V tile; one step of q or dO
   static constexpr int OFF_K = 0, OFF_V = TILE_BYTES, OFF_Q = 2 * TILE_BYTES, OFF_G = OFF_Q + IN_STAGES * STEP_BYTES, OFF_P = OFF_G + IN_STAGES * STEP_BYTES,
-                       OFF_DS = OFF_P + PT_BYTES, OFF_STAT = OFF_DS + PT_BYTES, OFF_BAR = OFF_STAT + IN_STAGES * 2 * SUB * 4;
-  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;       // D 64: 98 KB (two CTAs per SM); D 128: 162 KB
+                       OFF_DS = OFF_P + PT_BYTES, OFF_STAT = OFF_DS + PT_BYTES;
+  // Row statistics of a step (lse * log2 e and Dr of its 64 queries). One CTA per SM: they ride into shared memory with the
+  // step's tiles. Two CTAs per SM: no room is left (112 KB of tiles + barriers fill the SM's half to the last kilobyte), so
+  // the compute warps keep them in registers and shuffle them round.
+  static constexpr bool STATS_IN_SMEM = D != 64;
+  static constexpr int OFF_BAR = OFF_STAT + (STATS_IN_SMEM ? IN_STAGES * 2 * SUB * 4 : 0);
+  static constexpr int SMEM_BYTES = OFF_BAR + 128;              // D 64: 112 KB + 128; D 128: 193.6 KB
   static constexpr int TMEM_COLS = D == 64 ? 256 : 512;         // S^T 64 + dP^T 64 + dV D + dK D
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
@@ -404,10 +409,10 @@ template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dkv<D>::CTAS)
 sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                             const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }   // the swizzled tiles need 1024-byte alignment (whole CTA leaves)
+  uint8_t* base_ptr = smem_raw;
   using C = Dkv<D>;
   constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STEP_BYTES = C::STEP_BYTES, KV_OFF_K = C::OFF_K, KV_OFF_V = C::OFF_V, KV_OFF_Q = C::OFF_Q, KV_OFF_G = C::OFF_G,
                 KV_OFF_P = C::OFF_P, KV_OFF_DS = C::OFF_DS, KV_OFF_STAT = C::OFF_STAT, KV_OFF_BAR = C::OFF_BAR;
@@ -415,7 +420,6 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   auto bar = [&](int i) { return base + KV_OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + KV_OFF_BAR + 8 * KB_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse2 64 | dr 64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TileOrder ord = tile_order(blockIdx.x, args.planes, args.group, gridDim.x / args.planes);
@@ -424,17 +428,19 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   const int q_subs = (args.time - k0 + SUB - 1) / SUB;      // query steps k0, k0 + 64, ... (k0 is a multiple of 128)
   const int iters = rep * q_subs;
 
-  // step `it` of the walk: query head hk * rep + it / q_subs, queries from k0 + (it % q_subs) * SUB; the step's row
-  // statistics ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
+  // step `it` of the walk: query head hk * rep + it / q_subs, queries from k0 + (it % q_subs) * SUB
   auto load_step = [&](int it) {
     const int s = it % IN_STAGES, h = hk * rep + it / q_subs, q0 = k0 + (it % q_subs) * SUB;
-    const uint32_t stat_bytes = (uint32_t)min(SUB, args.time - q0) * 4u;
-    const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
+    // statistics in shared memory ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
+    const uint32_t stat_bytes = C::STATS_IN_SMEM ? (uint32_t)min(SUB, args.time - q0) * 4u : 0u;
     mbar_expect_tx(bar(KB_INFULL0 + s), 2 * STEP_BYTES + 2 * stat_bytes);
     load_tile<NSUB, 64>(base + KV_OFF_Q + s * STEP_BYTES, &tm_q, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
     load_tile<NSUB, 64>(base + KV_OFF_G + s * STEP_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
-    bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
-    bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
+    if (C::STATS_IN_SMEM) {
+      const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
+      bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
+      bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
+    }
   };
   // the producer thread sets the barriers up and starts the first loads before the CTA-wide sync
   if (warp == 8 && lane == 0) {
@@ -489,7 +495,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         // phase. One CTA per SM (head_dim 128): dV / dK first, which hands the input stage back to the loads sooner.
         auto next_s = [&]() -> bool {
           if (it + 1 >= (uint32_t)iters) return true;
-          if (!mbar_wait(bar(KB_SFREE), it & 1, args.fault, abort_flag)) return false;
+          if (C::CTAS == 2 && !mbar_wait(bar(KB_SFREE), it & 1, args.fault, abort_flag)) return false;
           if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) return false;
           fence_after();
           issue_s(it + 1);
@@ -521,29 +527,45 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     uint8_t* ds_row = base_ptr + KV_OFF_DS + tid * 128;
     bool ok = true;
     int q0 = k0;
+    // Statistics kept out of shared memory: lane c of a warp holds those of column c of its half, fetched one step
+    // ahead, and the warp shuffles them round as the columns come up.
+    const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse2 64 | dr 64] when in shared memory
+    auto stat_of = [&](int it, float& l2, float& dr) {
+      const int h = hk * rep + it / q_subs, q = k0 + (it % q_subs) * SUB + half * 32 + lane;
+      const bool in = !C::STATS_IN_SMEM && it < iters && q < args.time;
+      const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q;
+      l2 = in ? args.lse2[idx] : INFINITY;
+      dr = in ? args.dr[idx] : 0.0f;
+    };
+    float my_l2, my_dr, next_l2, next_dr;
+    stat_of(0, my_l2, my_dr);
     for (int it = 0; it < iters; ++it) {
-      const float* st = stat + (it % IN_STAGES) * 128 + half * 32;   // lse2[64] | dr[64] of this step, landed with the q / dO tiles
+      stat_of(it + 1, next_l2, next_dr);
       if (!mbar_wait(bar(KB_SFULL), it & 1, args.fault, abort_flag)) { ok = false; break; }
       fence_after();
       uint32_t rs[32], rp[32];
       tmem_ld32(lane_base + half * 32, rs);
       tmem_ld32(lane_base + 64 + half * 32, rp);
       tmem_wait_ld();
-      fence_before();
-      mbar_arrive(bar(KB_SFREE));                // the accumulator columns may take the next step
+      if (C::CTAS == 2) { fence_before(); mbar_arrive(bar(KB_SFREE)); }   // the accumulator columns may take the next step
       const int qb = q0 + half * 32;
-      // every thread of the warp reads the same statistics: 16-byte broadcast loads, four per eight columns
+      const float* st = stat + (it % IN_STAGES) * 128 + half * 32;
       auto stats = [&](int g, float (&l2)[8], float (&dd)[8]) {
-        const float4 a = *reinterpret_cast<const float4*>(st + g * 8), b = *reinterpret_cast<const float4*>(st + g * 8 + 4);
-        const float4 c = *reinterpret_cast<const float4*>(st + SUB + g * 8), d = *reinterpret_cast<const float4*>(st + SUB + g * 8 + 4);
-        l2[0] = a.x; l2[1] = a.y; l2[2] = a.z; l2[3] = a.w; l2[4] = b.x; l2[5] = b.y; l2[6] = b.z; l2[7] = b.w;
-        dd[0] = c.x; dd[1] = c.y; dd[2] = c.z; dd[3] = c.w; dd[4] = d.x; dd[5] = d.y; dd[6] = d.z; dd[7] = d.w;
+        if (C::STATS_IN_SMEM) {                    // every thread of the warp reads the same values: 16-byte broadcast loads
+          const float4 a = *reinterpret_cast<const float4*>(st + g * 8), b4 = *reinterpret_cast<const float4*>(st + g * 8 + 4);
+          const float4 c = *reinterpret_cast<const float4*>(st + SUB + g * 8), d = *reinterpret_cast<const float4*>(st + SUB + g * 8 + 4);
+          l2[0] = a.x; l2[1] = a.y; l2[2] = a.z; l2[3] = a.w; l2[4] = b4.x; l2[5] = b4.y; l2[6] = b4.z; l2[7] = b4.w;
+          dd[0] = c.x; dd[1] = c.y; dd[2] = c.z; dd[3] = c.w; dd[4] = d.x; dd[5] = d.y; dd[6] = d.z; dd[7] = d.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { l2[e] = __shfl_sync(0xffffffffu, my_l2, g * 8 + e); dd[e] = __shfl_sync(0xffffffffu, my_dr, g * 8 + e); }
+        }
       };
       auto vis = [&](int c) { return key < args.time && qb + c < args.time && key <= qb + c; };
       const bool masked = q0 < k0 + BN || q0 + SUB > args.time || k0 + BN > args.time;   // diagonal steps or a ragged end
       // P and dS are free once the previous step's dV / dK MMAs have read them. With two CTAs per SM those run behind the
-      // next S^T / dP^T, so the results wait in registers and the wait comes last; with one CTA per SM they finished before
-      // this step's S^T was issued, and each chunk is stored as it is formed.
+      // next S^T / dP^T, so the results wait in registers and the wait comes last; with one CTA per SM they were issued before
+      // this step's S^T, whose commit (SFULL) covers them, and each chunk is stored as it is formed.
       if (C::CTAS == 2) {
         uint4 pp[4], dsp[4];
         auto keep = [&](int g, const uint4& p, const uint4& ds) { pp[g] = p; dsp[g] = ds; };
@@ -552,12 +574,12 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 #pragma unroll
         for (int g = 0; g < 4; ++g) { store_chunk(p_row, pp[g], half, g, tid); store_chunk(ds_row, dsp[g], half, g, tid); }
       } else {
-        if (it > 0 && !mbar_wait(bar(KB_PFREE), (it - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
         auto put = [&](int g, const uint4& p, const uint4& ds) { store_chunk(p_row, p, half, g, tid); store_chunk(ds_row, ds, half, g, tid); };
         if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, put); else bwd_step<false>(rs, rp, sl2, stats, vis, put);
       }
       fence_async_smem();
       mbar_arrive(bar(KB_PREADY));
+      my_l2 = next_l2; my_dr = next_dr;
       q0 += SUB;
       if (q0 >= args.time) q0 = k0;
     }
@@ -666,7 +688,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         // the next step's S / dP: ahead of this step's dQ with two CTAs per SM, after it with one (see the dK/dV kernel)
         auto next_s = [&]() -> bool {
           if (it + 1 >= (uint32_t)iters) return true;
-          if (!mbar_wait(bar(QB_SFREE), it & 1, args.fault, abort_flag)) return false;
+          if (C::CTAS == 2 && !mbar_wait(bar(QB_SFREE), it & 1, args.fault, abort_flag)) return false;
           if (!mbar_wait(bar(QB_INFULL0 + (it + 1) % DQ_STAGES), ((it + 1) / DQ_STAGES) & 1, args.fault, abort_flag)) return false;
           fence_after();
           issue_s(it + 1);
@@ -701,8 +723,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       tmem_ld32(lane_base + half * 32, rs);
       tmem_ld32(lane_base + 64 + half * 32, rp);
       tmem_wait_ld();
-      fence_before();
-      mbar_arrive(bar(QB_SFREE));
+      if (C::CTAS == 2) { fence_before(); mbar_arrive(bar(QB_SFREE)); }
       auto stats = [&](int, float (&l2)[8], float (&dd)[8]) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) { l2[e] = lse_row; dd[e] = dr_row; }
@@ -717,7 +738,6 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
 #pragma unroll
         for (int g = 0; g < 4; ++g) store_chunk(ds_row, dsp[g], half, g, tid);
       } else {
-        if (it > 0 && !mbar_wait(bar(QB_PFREE), (it - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
         auto put = [&](int g, const uint4&, const uint4& ds) { store_chunk(ds_row, ds, half, g, tid); };
         if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, put); else bwd_step<false>(rs, rp, sl2, stats, vis, put);
       }
