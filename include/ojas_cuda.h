@@ -148,6 +148,17 @@ ojc_status ojc_linear_cross_entropy_mean(ojc_backend* be, const ojc_tensor* x, c
 ojc_status ojc_cross_entropy_mean_forward(ojc_backend* be, const ojc_tensor* logits, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, ojc_tensor* loss);      /* :2452 */
 ojc_status ojc_cross_entropy_mean_backward(ojc_backend* be, const ojc_tensor* logits, const ojc_tensor* targets, int32_t has_ignore, uint32_t ignore, ojc_tensor* grad_logits); /* :2461 */
 ojc_status ojc_argmax_rows(ojc_backend* be, const ojc_tensor* x, ojc_tensor* out_u32);                                       /* :1525 ties -> lowest column */
+/* ---- decode / eval ops on the same backend (the "next" rows after the training step)
+ * topk_rows (ojas-core/src/backend.rs:1553-1612): the k leaders of each row of x [rows, cols] by rank_logits (:186-195): value
+ * descending with +0.0 and -0.0 one value and -inf after every finite value, then column ascending. values F32 [rows, k], ids U32
+ * [rows, k]. NaN or +inf in a row surfaces as NonFinite at the next sync; k > 1024 is Unsupported (as the Metal and wgpu kernels).
+ * kv_cache_write (:2556-2565): src [B, Tn, Hkv, D] into the ring cache [B, Tcap, Hkv, D], position at + t to slot (at + t) % Tcap.
+ * cached_attention_forward (:2521-2554): q [B, Tq, H, D] against kv_len cached positions; query i sits at kv_len - Tq + i and sees
+ * positions 0..=p or the last `window` of them (window -1: none), oldest first; head h reads KV head h / (H / Hkv); out [B, Tq, H, D]. */
+ojc_status ojc_topk_rows(ojc_backend* be, const ojc_tensor* x, int64_t k, ojc_tensor* values, ojc_tensor* ids_u32);
+ojc_status ojc_kv_cache_write(ojc_backend* be, ojc_tensor* cache, const ojc_tensor* src, uint64_t at);
+ojc_status ojc_cached_attention_forward(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k_cache, const ojc_tensor* v_cache, uint64_t kv_len, int64_t window,
+                                        ojc_tensor* out);
 
 /* ---- gradient plumbing and optimizers */
 ojc_status ojc_accumulate_grad(ojc_backend* be, ojc_tensor* acc, const ojc_tensor* grad);                                    /* :1483 acc += grad */

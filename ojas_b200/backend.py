@@ -411,6 +411,21 @@ class CudaBackend:
         _check(lib.ojc_argmax_rows(self._handle, _p(x), _p(out)))
         return out
 
+    # ---- decode / eval ops
+    def topk_rows(self, x, k: int):
+        """(values F32 [rows, k], ids U32 [rows, k]) ranked as rank_logits ranks (value descending, then column ascending)."""
+        values, ids = self.empty((x.shape[0], k), DType.F32), self.empty((x.shape[0], k), DType.U32)
+        _check(lib.ojc_topk_rows(self._handle, _p(x), C.c_int64(k), _p(values), _p(ids)))
+        return values, ids
+
+    def kv_cache_write(self, cache: Tensor, src: Tensor, at: int):
+        _check(lib.ojc_kv_cache_write(self._handle, _p(cache), _p(src), C.c_uint64(at)))
+
+    def cached_attention_forward(self, q, k_cache, v_cache, kv_len: int, window: int | None = None):
+        out = self.empty(q.shape, DType.F32)
+        _check(lib.ojc_cached_attention_forward(self._handle, _p(q), _p(k_cache), _p(v_cache), C.c_uint64(kv_len), C.c_int64(-1 if window is None else window), _p(out)))
+        return out
+
     # ---- in-place gradient plumbing and optimizers
     def accumulate_grad(self, acc: Tensor, grad: Tensor):
         _check(lib.ojc_accumulate_grad(self._handle, _p(acc), _p(grad)))

@@ -20,6 +20,7 @@ typedef __nv_bfloat16 bf16;
 enum OjcOp : uint32_t {
   OP_NONE = 0, OP_EMBEDDING, OP_LINEAR, OP_RMS_NORM, OP_ROPE, OP_VRES, OP_SDPA, OP_GATE, OP_SILU, OP_MUL,
   OP_ADD, OP_LINEAR_CE, OP_CE, OP_ACCUMULATE, OP_SCALE, OP_CLIP, OP_ADAMW, OP_MUON, OP_ARGMAX, OP_CAST, OP_GEMM_WAIT,
+  OP_CACHED_ATTN, OP_TOPK,
   OP_ID_RANGE,  // a token id or target outside the vocabulary: reported as OutOfRange
   OP_COUNT
 };

@@ -769,7 +769,7 @@ ojc_status ojc_per_head_sigmoid_gate_forward(ojc_backend* be, const ojc_tensor* 
                                              ojc_tensor* out, ojc_tensor* scales) {
   const char* op = "per_head_sigmoid_gate_forward";
   OJC_ALIVE(be, op);
-  int64_t rows; int din, heads, dh;
+  int64_t rows = 0; int din = 0, heads = 0, dh = 0;
   OJC_TRY(gate_dims(op, input, weight, bias, attn, &rows, &din, &heads, &dh));
   OJC_TRY(check_tensor(op, "out", out));
   if (numel(out) != numel(attn)) return ojc_fail(OJC_ERR_SHAPE, op, "out must match attn");
@@ -790,7 +790,7 @@ ojc_status ojc_per_head_sigmoid_gate_forward(ojc_backend* be, const ojc_tensor* 
 ojc_status gate_backward_impl(ojc_backend* be, const ojc_tensor* input, const ojc_tensor* weight, const ojc_tensor* bias, const ojc_tensor* attn, const ojc_tensor* gout,
                               const ojc_tensor* saved, ojc_tensor* ginput, float* gweight, float* gbias, ojc_tensor* gattn, bool accumulate_w) {
   const char* op = "per_head_sigmoid_gate_backward";
-  int64_t rows; int din, heads, dh;
+  int64_t rows = 0; int din = 0, heads = 0, dh = 0;
   OJC_TRY(gate_dims(op, input, weight, bias, attn, &rows, &din, &heads, &dh));
   if (heads > 64) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "more than 64 heads");
   const int64_t rows_per_chunk = 256;

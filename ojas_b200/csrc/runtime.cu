@@ -18,7 +18,8 @@ static const char* kOpNames[OP_COUNT] = {"none", "embedding", "linear", "rms_nor
                                          "causal_sdpa", "per_head_sigmoid_gate", "silu", "mul", "residual_add",
                                          "linear_cross_entropy_mean", "cross_entropy_mean", "accumulate_grad",
                                          "scale_grad", "clip_grad_norm", "adamw_step", "muon_ns5_step", "argmax_rows",
-                                         "cast", "gemm_pipeline_wait", "token id or target"};
+                                         "cast", "gemm_pipeline_wait", "cached_attention_forward", "topk_rows",
+                                         "token id or target"};
 const char* ojc_op_name(uint32_t op) { return op < OP_COUNT ? kOpNames[op] : "unknown"; }
 
 ojc_status ojc_fail(ojc_status st, const char* op, const std::string& detail) {

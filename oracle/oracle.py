@@ -308,6 +308,46 @@ def argmax_rows(x):
     return out
 
 
+def topk_rows(x, k):
+    """ojas-core/src/backend.rs:1571-1612 with rank_logits (:186-195): value descending, +0.0 and -0.0 one value, -inf after
+    every finite value, then column ascending. NaN or +inf in a row is refused."""
+    x = _f(x)
+    if np.isnan(x).any() or np.isposinf(x).any():
+        raise OracleError("topk_rows", 2)
+    rows, cols = x.shape
+    key = np.where(x == 0.0, np.float32(0.0), x)
+    # a stable sort of the negated key keeps equal values in column order
+    order = np.argsort(-key.astype(np.float64), axis=1, kind="stable")[:, :k]
+    return np.take_along_axis(x, order, axis=1), order.astype(np.uint32)
+
+
+def kv_cache_write(cache, src, at):
+    """ojas-cpu/src/kv.rs (kv_cache_write): position at + t of src [B, Tn, Hkv, D] goes to slot (at + t) % Tcap, in place."""
+    cap = cache.shape[1]
+    for t in range(src.shape[1]):
+        cache[:, (at + t) % cap] = src[:, t]
+    return cache
+
+
+def cached_attention_forward(q, k_cache, v_cache, kv_len, window=None):
+    """ojas-cpu/src/kv.rs:107-200: each query row runs the per-row kernel of causal_sdpa_forward over its visible positions,
+    oldest first. Restated through that kernel: the ring is unrolled into positions first .. kv_len - 1, the new queries are
+    the last Tq rows of a causal problem over them (earlier rows get zero queries and are dropped), under the same window."""
+    q, k_cache, v_cache = _f(q), _f(k_cache), _f(v_cache)
+    b, tq, h, d = q.shape
+    cap, hkv = k_cache.shape[1], k_cache.shape[2]
+    w = window if (window is not None and window < kv_len) else None
+    first = max(0, kv_len - tq + 1 - w) if w else 0          # the oldest position any query reads
+    pos = np.arange(first, kv_len)
+    k = np.ascontiguousarray(k_cache[:, pos % cap].transpose(0, 2, 1, 3))      # [B, Hkv, n, D]
+    v = np.ascontiguousarray(v_cache[:, pos % cap].transpose(0, 2, 1, 3))
+    n = len(pos)
+    qf = np.zeros((b, h, n, d), np.float32)
+    qf[:, :, n - tq:] = q.transpose(0, 2, 1, 3)
+    out, _ = causal_sdpa_forward(qf, k, v, window=w)
+    return np.ascontiguousarray(out[:, :, n - tq:].transpose(0, 2, 1, 3))
+
+
 def _ptr_array(arrs):
     return (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
 

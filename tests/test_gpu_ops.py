@@ -366,3 +366,101 @@ def test_budget_refuses_instead_of_clamping():
     del t
     assert small.budget()["live"] == 0
     small.close()
+
+
+# ---- decode / eval ops (the rows after the training step): top-k leaders, KV-cache ring, cached attention
+def test_topk_rows_ranks_like_rank_logits_bit_for_bit(be):
+    from ojas_b200 import OjasError
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((6, 50304)).astype(np.float32)
+    x[0, :40] = 3.5                      # a run of ties at the top: lowest columns win, in column order
+    x[1, 7] = x[1, 4000] = x[1, 123] = 9.0
+    x[2, 100:300] = -np.inf              # masked logits rank after every finite value
+    x[3] = 0.0
+    x[3, ::2] = -0.0                     # +0.0 and -0.0 are one value: columns 0, 1, 2, ...; the value bits stay the row's own
+    x[4] = -np.inf
+    x[4, 9] = -1.0
+    for k in (1, 5, 50, 64, 1000, 1024):
+        values, ids = be.topk_rows(be.upload(x), k)
+        want_v, want_i = orc.topk_rows(x, k)
+        assert np.array_equal(ids.numpy(), want_i), k
+        assert values.numpy().tobytes() == want_v.tobytes(), k
+    small = rng.standard_normal((3, 17)).astype(np.float32)
+    values, ids = be.topk_rows(be.upload(small), 17)            # k = cols: a full sort
+    assert np.array_equal(ids.numpy(), orc.topk_rows(small, 17)[1])
+    for bad_k in (0, 18, 2000):
+        with pytest.raises(OjasError) as e:
+            be.topk_rows(be.upload(small if bad_k < 100 else x), bad_k)
+        assert e.value.kind == ("Unsupported" if bad_k == 2000 else "OutOfRange")
+    bad = small.copy()
+    bad[1, 3] = np.inf
+    be.topk_rows(be.upload(bad), 2)
+    with pytest.raises(OjasError) as e:
+        be.sync()
+    assert e.value.kind == "NonFinite"
+
+
+def test_kv_cache_write_is_a_ring_and_refuses_what_the_validator_refuses(be):
+    from ojas_b200 import OjasError
+    rng = np.random.default_rng(6)
+    cache = rng.standard_normal((2, 8, 3, 16)).astype(np.float32)
+    dev = be.upload(cache)
+    want = cache.copy()
+    for at, tn in ((0, 5), (5, 6), (11, 1), (12, 8), (100, 3)):          # wraps, single positions, a full turn
+        src = rng.standard_normal((2, tn, 3, 16)).astype(np.float32)
+        be.kv_cache_write(dev, be.upload(src), at)
+        orc.kv_cache_write(want, src, at)
+        assert dev.numpy().tobytes() == want.tobytes(), (at, tn)
+    odd = be.upload(rng.standard_normal((1, 4, 1, 3)).astype(np.float32))      # a 3-float step takes the scalar path
+    src = rng.standard_normal((1, 2, 1, 3)).astype(np.float32)
+    be.kv_cache_write(odd, be.upload(src), 3)
+    assert np.array_equal(odd.numpy()[0, 3], src[0, 0]) and np.array_equal(odd.numpy()[0, 0], src[0, 1])
+    with pytest.raises(OjasError) as e:
+        be.kv_cache_write(dev, be.upload(np.zeros((2, 9, 3, 16), np.float32)), 0)
+    assert e.value.kind == "OutOfRange"
+    with pytest.raises(OjasError) as e:
+        be.kv_cache_write(dev, be.upload(np.zeros((2, 2, 2, 16), np.float32)), 0)
+    assert e.value.kind == "Shape"
+
+
+@pytest.mark.parametrize("case", [
+    dict(b=2, tq=1, h=4, hkv=4, d=64, cap=64, kv_len=37, window=None),      # one decode step on a prefix
+    dict(b=1, tq=5, h=6, hkv=2, d=32, cap=48, kv_len=48, window=None),      # prefill onto a non-empty cache, GQA, full ring
+    dict(b=2, tq=3, h=4, hkv=2, d=16, cap=16, kv_len=70, window=8),         # a ring that wrapped, sliding window
+    dict(b=1, tq=4, h=2, hkv=1, d=128, cap=300, kv_len=4, window=None),     # kv_len == Tq: equals causal_sdpa_forward
+    dict(b=1, tq=2, h=2, hkv=2, d=64, cap=1024, kv_len=900, window=1000),   # a window wider than the history is no window
+])
+def test_cached_attention_matches_the_per_row_kernel(be, case):
+    c = case
+    rng = np.random.default_rng(7)
+    q = rng.standard_normal((c["b"], c["tq"], c["h"], c["d"])).astype(np.float32)
+    kc = rng.standard_normal((c["b"], c["cap"], c["hkv"], c["d"])).astype(np.float32)
+    vc = rng.standard_normal((c["b"], c["cap"], c["hkv"], c["d"])).astype(np.float32)
+    if c["kv_len"] < c["cap"]:
+        kc[:, c["kv_len"]:] = np.nan          # slots no query reads may hold anything (ojas-cpu/src/kv.rs:4-7)
+        vc[:, c["kv_len"]:] = np.inf
+    got = be.cached_attention_forward(be.upload(q), be.upload(kc), be.upload(vc), c["kv_len"], c["window"]).numpy()
+    be.sync()
+    want = orc.cached_attention_forward(q, np.nan_to_num(kc, nan=0.0, posinf=0.0), np.nan_to_num(vc, nan=0.0, posinf=0.0), c["kv_len"], c["window"])
+    assert got.shape == want.shape and rel(got, want) <= 1e-5, rel(got, want)
+    if c["kv_len"] == c["tq"]:           # the documented identity with causal_sdpa_forward after the layout permute
+        k = np.ascontiguousarray(kc[:, :c["kv_len"]].transpose(0, 2, 1, 3)); v = np.ascontiguousarray(vc[:, :c["kv_len"]].transpose(0, 2, 1, 3))
+        ref, _ = orc.causal_sdpa_forward(np.ascontiguousarray(q.transpose(0, 2, 1, 3)), k, v)
+        assert np.array_equal(want, ref.transpose(0, 2, 1, 3))
+
+
+def test_cached_attention_refusals(be):
+    from ojas_b200 import OjasError
+    q = be.upload(np.zeros((1, 2, 4, 16), np.float32))
+    kc = be.upload(np.zeros((1, 8, 2, 16), np.float32))
+    for kv_len, window, kind in ((1, None, "OutOfRange"), (9, None, "OutOfRange"), (20, 8, "OutOfRange"), (8, 0, "Shape")):
+        with pytest.raises(OjasError) as e:
+            be.cached_attention_forward(q, kc, kc, kv_len, window)
+        assert e.value.kind == kind, (kv_len, window)
+    assert be.cached_attention_forward(q, kc, kc, 20, 7).shape == (1, 2, 4, 16)      # span 2 + 7 - 1 = 8 positions fit the ring
+    poisoned = np.zeros((1, 8, 2, 16), np.float32)
+    poisoned[0, 3, 1, 2] = np.nan
+    be.cached_attention_forward(q, be.upload(poisoned), kc, 8, None)
+    with pytest.raises(OjasError) as e:
+        be.sync()
+    assert e.value.kind == "NonFinite"
