@@ -192,6 +192,8 @@ typedef struct ojc_train_config {          /* TrainConfig, ojas-model/src/traine
   int32_t has_ignore; uint32_t ignore_index;
   int64_t ce_chunk_rows;                   /* rows of one fused-CE logits tile (0: default) */
   float loss_seed;                         /* backward seed w_i (MicroWeights, trainer.rs:1083-1119); 1/world under data parallelism */
+  int32_t checkpoint_blocks;               /* ActivationCheckpoint::Blocks (ojas-model/src/block.rs:323-336): keep only each block's input and recompute the block in
+                                            * backward; same bits as without, about a third more forward work, activation memory of two blocks instead of n_layer */
 } ojc_train_config;
 typedef struct ojc_step_report { float loss; float grad_norm; uint64_t step; uint64_t tokens; } ojc_step_report; /* StepReport trainer.rs:281-297 */
 typedef struct ojc_trainer ojc_trainer;

@@ -506,11 +506,12 @@ class TrainConfig:
     ignore_index: int | None = None
     ce_chunk_rows: int = 0
     loss_seed: float = 1.0
+    checkpoint_blocks: bool = False      # ActivationCheckpoint::Blocks: recompute each block in backward from its saved input
 
     def c(self):
         return _lib.TrainConfig(int(self.autocast_bf16), 0 if self.optimizer == "adamw" else 1, self.adam_lr, self.adam_beta1, self.adam_beta2, self.adam_eps,
                                 self.adam_weight_decay, self.matrix_lr, self.muon_momentum, self.muon_weight_decay, int(self.ns5_bf16), self.grad_clip,
-                                int(self.ignore_index is not None), self.ignore_index or 0, self.ce_chunk_rows, self.loss_seed)
+                                int(self.ignore_index is not None), self.ignore_index or 0, self.ce_chunk_rows, self.loss_seed, int(self.checkpoint_blocks))
 
 
 @dataclass

@@ -156,6 +156,92 @@ ojc_status refresh_mirror(ojc_trainer* tr, const Param& p) {
 }
 
 // ---------------------------------------------------------------------------------------------- forward
+// One block's forward from its saved input acts[l].x: writes the block's activations and the next block's input. Also the
+// recompute step of activation checkpointing (ActivationCheckpoint::Blocks, ojas-model/src/block.rs:323-336), where it
+// reproduces the same bits the forward pass wrote.
+ojc_status block_forward(ojc_trainer* tr, int64_t l) {
+  ojc_backend* be = tr->be;
+  const ojc_model_spec& s = tr->spec;
+  const int64_t d = s.n_embd, H = s.n_head, Hkv = s.n_kv_head, dh = s.head_dim, F = s.hidden, N = tr->N, B = tr->B, T = tr->T;
+  const int64_t qw = H * dh, kvw = Hkv * dh, L = s.n_layer;
+  const int32_t A = tr->act_dt;
+  const float eps = s.rms_eps;
+  ojc_tensor cos_t = T2(tr->cos_t, OJC_F32, T, dh), sin_t = T2(tr->sin_t, OJC_F32, T, dh);
+  LayerActs& a = tr->acts[l];
+  float* x_next = (l + 1 < L) ? tr->acts[l + 1].x : tr->x_final;
+  ojc_tensor x = T2(a.x, OJC_F32, N, d), h = T2(a.h, A, N, d);
+  ojc_tensor n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d);
+  // bf16 tier: the residual stream's next buffer starts as a copy of this one and the projection adds into it (the
+  // GEMM's adding tile stores), instead of reading a separate residual operand in the epilogue
+  const bool add_in_place = A == OJC_BF16;
+  OJC_TRY(rms_forward_impl(be, &x, &n1, eps, &h, add_in_place ? a.x1 : nullptr));
+  const bool fl = tr->fused_lin;
+  const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;   // token strides of q and of k / raw v
+  if (fl) {
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, tr->ld_qkv, nullptr));
+  } else {
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, qw, nullptr));
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_K)), A, a.k, A, N, d, kvw, nullptr));
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_V)), A, a.rawv, A, N, d, kvw, nullptr));
+  }
+  if (tr->fused_qk) {
+    OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.q, sq, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (bf16*)a.qr, qw, N, (int)H, (int)dh, (int)T, eps));
+    OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.k, skv, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (bf16*)a.kr, kvw, N, (int)Hkv, (int)dh, (int)T, eps));
+  } else {
+    ojc_tensor q = T2(a.q, A, N * H, dh), qn = T2(tr->qn, A, N * H, dh), qnw = T1(tr->W(tr->P(l, P_QN)), OJC_F32, dh);
+    ojc_tensor k = T2(a.k, A, N * Hkv, dh), kn = T2(tr->kn, A, N * Hkv, dh), knw = T1(tr->W(tr->P(l, P_KN)), OJC_F32, dh);
+    OJC_TRY(rms_forward_impl(be, &q, &qnw, eps, &qn));
+    OJC_TRY(rms_forward_impl(be, &k, &knw, eps, &kn));
+    ojc_tensor qn4 = T4(tr->qn, A, B, T, H, dh), qr4 = T4(a.qr, A, B, T, H, dh), kn4 = T4(tr->kn, A, B, T, Hkv, dh), kr4 = T4(a.kr, A, B, T, Hkv, dh);
+    OJC_TRY(rope_impl(be, "rope_half_split_forward", &qn4, &cos_t, &sin_t, &qr4, 0));
+    OJC_TRY(rope_impl(be, "rope_half_split_forward", &kn4, &cos_t, &sin_t, &kr4, 0));
+  }
+  if (l > 0 && fl) {
+    OJC_TRY(vres_rows_forward(be, (const bf16*)a.rawv, skv, (const bf16*)tr->acts[0].rawv, skv, tr->W(tr->P(l, P_LAMBDA)), (bf16*)a.v, N, kvw));
+  } else if (l > 0) {
+    ojc_tensor rv = T1(a.rawv, A, N * kvw), v0 = T1(tr->acts[0].rawv, A, N * kvw), lam = T1(tr->W(tr->P(l, P_LAMBDA)), OJC_F32, 1), v = T1(a.v, A, N * kvw);
+    OJC_TRY(ojc_value_residual_blend_forward(be, &rv, &v0, &lam, &v));
+  }
+  {
+    ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
+    ojc_tensor v = l > 0 ? TBHTD(a.v, A, B, T, Hkv, dh) : TBHTD(a.rawv, A, B, T, Hkv, dh, skv);
+    ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
+    lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
+    OJC_TRY(ojc_causal_sdpa_forward(be, &q, &k, &v, s.window, &y, &lse));
+  }
+  if (tr->gate_ld) {
+    // gate logits as a skinny GEMM over the weight rows [0, gate_ld) (rows past H are the next parameters' mirror
+    // values: their columns are never read), then the pointwise half
+    OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_GW)), A, tr->gate_z, A, N, d, tr->gate_ld, nullptr));
+    OJC_TRY(gate_apply_forward(be, tr->gate_z, tr->gate_ld, tr->W(tr->P(l, P_GB)), (const bf16*)a.y, (bf16*)a.yg, a.scales, N, (int)H, (int)dh));
+  } else {
+    ojc_tensor h2d = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
+    ojc_tensor y = T2(a.y, A, N * H, dh), yg = T2(a.yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H);
+    OJC_TRY(ojc_per_head_sigmoid_gate_forward(be, &h2d, &gw, &gb, &y, &yg, &sc));
+  }
+  OJC_TRY(linear_forward_impl(be, a.yg, A, tr->WM(tr->P(l, P_O)), A, a.x1, OJC_F32, N, qw, d, add_in_place ? nullptr : a.x, add_in_place));  // x1 = x + o_proj(yg)
+  {
+    ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), h2 = T2(a.h2, A, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d);
+    OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2, add_in_place ? x_next : nullptr));
+  }
+  if (fl) {
+    OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, tr->ld_au, nullptr));
+    OJC_TRY(swiglu_rows_forward(be, (const bf16*)a.a, tr->ld_au, (bf16*)a.m, N, F));
+    OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, nullptr, true));  // x2 = x1 + down(m)
+    return OJC_OK;
+  }
+  OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, F, nullptr));
+  OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FU)), A, a.u, A, N, d, F, nullptr));
+  if ((N * F) % 4 == 0) OJC_TRY(swiglu_forward_impl(be, a.a, a.u, a.m, A, N * F));
+  else {
+    ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), tm = T1(a.m, A, N * F);
+    OJC_TRY(ojc_silu_forward(be, &ta, &tm));
+    OJC_TRY(ojc_mul_forward(be, &tm, &tu, &tm));
+  }
+  OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, add_in_place ? nullptr : a.x1, add_in_place));  // x2 = x1 + down(m)
+  return OJC_OK;
+}
+
 ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
   ojc_backend* be = tr->be;
   const ojc_model_spec& s = tr->spec;
@@ -168,80 +254,7 @@ ojc_status forward_hidden(ojc_trainer* tr, const uint32_t* ids_dev) {
     ojc_tensor table = T2(tr->w + tr->params[0].offset, OJC_F32, s.vocab, d), ids = T1((void*)ids_dev, OJC_U32, N), out = T2(tr->acts[0].x, OJC_F32, N, d);
     OJC_TRY(ojc_embedding_forward(be, &table, &ids, &out));
   }
-  for (int64_t l = 0; l < L; ++l) {
-    LayerActs& a = tr->acts[l];
-    float* x_next = (l + 1 < L) ? tr->acts[l + 1].x : tr->x_final;
-    ojc_tensor x = T2(a.x, OJC_F32, N, d), h = T2(a.h, A, N, d);
-    ojc_tensor n1 = T1(tr->W(tr->P(l, P_NORM1)), OJC_F32, d);
-    // bf16 tier: the residual stream's next buffer starts as a copy of this one and the projection adds into it (the
-    // GEMM's adding tile stores), instead of reading a separate residual operand in the epilogue
-    const bool add_in_place = A == OJC_BF16;
-    OJC_TRY(rms_forward_impl(be, &x, &n1, eps, &h, add_in_place ? a.x1 : nullptr));
-    const bool fl = tr->fused_lin;
-    const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;   // token strides of q and of k / raw v
-    if (fl) {
-      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, tr->ld_qkv, nullptr));
-    } else {
-      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_Q)), A, a.q, A, N, d, qw, nullptr));
-      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_K)), A, a.k, A, N, d, kvw, nullptr));
-      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_V)), A, a.rawv, A, N, d, kvw, nullptr));
-    }
-    if (tr->fused_qk) {
-      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.q, sq, tr->W(tr->P(l, P_QN)), tr->cos_t, tr->sin_t, (bf16*)a.qr, qw, N, (int)H, (int)dh, (int)T, eps));
-      OJC_TRY(qk_norm_rope_forward(be, (const bf16*)a.k, skv, tr->W(tr->P(l, P_KN)), tr->cos_t, tr->sin_t, (bf16*)a.kr, kvw, N, (int)Hkv, (int)dh, (int)T, eps));
-    } else {
-      ojc_tensor q = T2(a.q, A, N * H, dh), qn = T2(tr->qn, A, N * H, dh), qnw = T1(tr->W(tr->P(l, P_QN)), OJC_F32, dh);
-      ojc_tensor k = T2(a.k, A, N * Hkv, dh), kn = T2(tr->kn, A, N * Hkv, dh), knw = T1(tr->W(tr->P(l, P_KN)), OJC_F32, dh);
-      OJC_TRY(rms_forward_impl(be, &q, &qnw, eps, &qn));
-      OJC_TRY(rms_forward_impl(be, &k, &knw, eps, &kn));
-      ojc_tensor qn4 = T4(tr->qn, A, B, T, H, dh), qr4 = T4(a.qr, A, B, T, H, dh), kn4 = T4(tr->kn, A, B, T, Hkv, dh), kr4 = T4(a.kr, A, B, T, Hkv, dh);
-      OJC_TRY(rope_impl(be, "rope_half_split_forward", &qn4, &cos_t, &sin_t, &qr4, 0));
-      OJC_TRY(rope_impl(be, "rope_half_split_forward", &kn4, &cos_t, &sin_t, &kr4, 0));
-    }
-    if (l > 0 && fl) {
-      OJC_TRY(vres_rows_forward(be, (const bf16*)a.rawv, skv, (const bf16*)tr->acts[0].rawv, skv, tr->W(tr->P(l, P_LAMBDA)), (bf16*)a.v, N, kvw));
-    } else if (l > 0) {
-      ojc_tensor rv = T1(a.rawv, A, N * kvw), v0 = T1(tr->acts[0].rawv, A, N * kvw), lam = T1(tr->W(tr->P(l, P_LAMBDA)), OJC_F32, 1), v = T1(a.v, A, N * kvw);
-      OJC_TRY(ojc_value_residual_blend_forward(be, &rv, &v0, &lam, &v));
-    }
-    {
-      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
-      ojc_tensor v = l > 0 ? TBHTD(a.v, A, B, T, Hkv, dh) : TBHTD(a.rawv, A, B, T, Hkv, dh, skv);
-      ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
-      lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
-      OJC_TRY(ojc_causal_sdpa_forward(be, &q, &k, &v, s.window, &y, &lse));
-    }
-    if (tr->gate_ld) {
-      // gate logits as a skinny GEMM over the weight rows [0, gate_ld) (rows past H are the next parameters' mirror
-      // values: their columns are never read), then the pointwise half
-      OJC_TRY(linear_forward_impl(be, a.h, A, tr->WM(tr->P(l, P_GW)), A, tr->gate_z, A, N, d, tr->gate_ld, nullptr));
-      OJC_TRY(gate_apply_forward(be, tr->gate_z, tr->gate_ld, tr->W(tr->P(l, P_GB)), (const bf16*)a.y, (bf16*)a.yg, a.scales, N, (int)H, (int)dh));
-    } else {
-      ojc_tensor h2d = T2(a.h, A, N, d), gw = T2((void*)tr->WM(tr->P(l, P_GW)), A, H, d), gb = T1(tr->W(tr->P(l, P_GB)), OJC_F32, H);
-      ojc_tensor y = T2(a.y, A, N * H, dh), yg = T2(a.yg, A, N * H, dh), sc = T2(a.scales, OJC_F32, N, H);
-      OJC_TRY(ojc_per_head_sigmoid_gate_forward(be, &h2d, &gw, &gb, &y, &yg, &sc));
-    }
-    OJC_TRY(linear_forward_impl(be, a.yg, A, tr->WM(tr->P(l, P_O)), A, a.x1, OJC_F32, N, qw, d, add_in_place ? nullptr : a.x, add_in_place));  // x1 = x + o_proj(yg)
-    {
-      ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), h2 = T2(a.h2, A, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d);
-      OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2, add_in_place ? x_next : nullptr));
-    }
-    if (fl) {
-      OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, tr->ld_au, nullptr));
-      OJC_TRY(swiglu_rows_forward(be, (const bf16*)a.a, tr->ld_au, (bf16*)a.m, N, F));
-      OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, nullptr, true));  // x2 = x1 + down(m)
-      continue;
-    }
-    OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, F, nullptr));
-    OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FU)), A, a.u, A, N, d, F, nullptr));
-    if ((N * F) % 4 == 0) OJC_TRY(swiglu_forward_impl(be, a.a, a.u, a.m, A, N * F));
-    else {
-      ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), tm = T1(a.m, A, N * F);
-      OJC_TRY(ojc_silu_forward(be, &ta, &tm));
-      OJC_TRY(ojc_mul_forward(be, &tm, &tu, &tm));
-    }
-    OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, add_in_place ? nullptr : a.x1, add_in_place));  // x2 = x1 + down(m)
-  }
+  for (int64_t l = 0; l < L; ++l) OJC_TRY(block_forward(tr, l));
   ojc_tensor xf = T2(tr->x_final, OJC_F32, N, d), hf = T2(tr->hf, A, N, d), nf = T1(tr->W(tr->params.back()), OJC_F32, d);
   return rms_forward_impl(be, &xf, &nf, eps, &hf);
 }
@@ -310,6 +323,13 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   };
   for (int64_t l = L - 1; l >= 0; --l) {
     LayerActs& a = tr->acts[l];
+    // Activation checkpointing: only the block inputs were kept, every block works in the same activation buffers. The last
+    // block's are still in place from the forward pass; the others are recomputed here (same kernels, same bits), after the
+    // side lane has finished reading the previous occupant's. Block 0 keeps buffers of its own.
+    if (tr->cfg.checkpoint_blocks && l + 1 < L && l > 0) {
+      OJC_TRY(join_side());
+      OJC_TRY(block_forward(tr, l));
+    }
     // x2 = x1 + down(m)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
     OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false); }));
@@ -476,6 +496,11 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
   tr->acts.resize(L);
   for (int64_t l = 0; l < L; ++l) {
     LayerActs& a = tr->acts[l];
+    if (tr->cfg.checkpoint_blocks && l > 0) {
+      // every block shares block 1's buffers (block 0 keeps its own q / k / raw v: raw v of block 0 feeds every block's value
+      // residual); only the block input is per block
+      if (l > 1) { a = tr->acts[1]; TAKE(a.x, N * d * 4); continue; }
+    }
     TAKE(a.x, N * d * 4); TAKE(a.x1, N * d * 4); TAKE(a.lse, tr->B * H * tr->T * 4); TAKE(a.scales, N * H * 4);
     TAKE(a.h, N * d * es); TAKE(a.qr, N * qw * es); TAKE(a.kr, N * kvw * es);
     if (fl) {

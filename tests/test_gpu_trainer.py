@@ -299,3 +299,35 @@ def test_out_of_range_token_is_refused_before_any_launch(be):
         tr.gradients(ids, ids)
     assert e.value.kind == "OutOfRange" and be.kernel_launches() == launches
     tr.close()
+
+
+@pytest.mark.parametrize("autocast", [False, True])
+def test_activation_checkpointing_recomputes_the_same_bits_in_less_memory(be, golden_dir, autocast):
+    """ActivationCheckpoint::Blocks (ojas-model/src/block.rs:323-336): only block inputs are kept and each block is recomputed in
+    backward. The kernels are deterministic, so losses, gradients and the stepped parameters equal the plain run bit for bit."""
+    from ojas_b200 import ModelSpec, TrainConfig, Trainer
+    spec = ModelSpec(vocab=512, n_embd=128, n_layer=5, n_head=2, n_kv_head=1, head_dim=64, hidden=256, max_seq=128)
+    ospec = orc.Spec(vocab=512, n_embd=128, n_layer=5, n_head=2, n_kv_head=1, head_dim=64, hidden=256, max_seq=128)
+    weights = orc.init_params(ospec, 3, normal_everywhere=True)
+    rng = np.random.default_rng(8)
+    batches = [rng.integers(0, 512, (4, 129), dtype=np.uint32) for _ in range(3)]
+    runs = []
+    for ckpt in (False, True):
+        live_before = be.budget()["live"]
+        tr = Trainer(be, spec, TrainConfig(optimizer="muon", autocast_bf16=autocast, ns5_bf16=autocast, checkpoint_blocks=ckpt), 4, 128)
+        held = be.budget()["live"] - live_before
+        tr.set_params(weights)
+        losses = []
+        for i, b in enumerate(batches):
+            if i == 0:
+                losses.append(tr.gradients(b[:, :-1], b[:, 1:]))
+                grads = [tr.get_grad(j) for j, p in enumerate(tr.params) if p.trains]
+                tr.apply()
+            else:
+                losses.append(tr.step(b[:, :-1], b[:, 1:]).loss)
+        runs.append((losses, grads, [tr.get_param(j) for j in range(len(tr.params))], held))
+        tr.close()
+    (l0, g0, p0, m0), (l1, g1, p1, m1) = runs
+    assert l0 == l1
+    assert all(a.tobytes() == b.tobytes() for a, b in zip(g0, g1)) and all(a.tobytes() == b.tobytes() for a, b in zip(p0, p1))
+    assert m1 < 0.85 * m0, (m0, m1)      # five blocks of activations became two plus five block inputs (the rest is parameters, moments, gradients)
