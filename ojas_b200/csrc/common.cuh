@@ -46,12 +46,22 @@ struct ojc_backend {
   struct GemmSample { cudaEvent_t start, stop; double flops; };
   std::vector<GemmSample> gemm_samples;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> event_pool;
+  // Finishing lane for two-stage reductions (per-block partials, then a few blocks that sum them into a weight gradient).
+  // The finishing kernels are tiny and nothing reads their result before the optimizer, so a step driver may point this
+  // at a second stream: the partials then come from the lane's own pool (the main workspace is reused by the next op) and
+  // the finishing kernel runs on the lane's stream behind an event. The owner resets `used` wherever it joins the lane.
+  struct FinishLane { cudaStream_t stream = nullptr; cudaEvent_t ev = nullptr; char* pool = nullptr; uint64_t pool_bytes = 0, used = 0; bool active = false; } finish;
 };
 
 ojc_status ojc_fail(ojc_status st, const char* op, const std::string& detail);
 ojc_status ojc_cuda_check(ojc_backend* be, cudaError_t err, const char* op);
 // Library workspace of at least `bytes` (256-byte aligned); contents are undefined.
 ojc_status ojc_scratch(ojc_backend* be, uint64_t bytes, void** out);
+// Workspace for the partials of a two-stage reduction and the stream its finishing kernel goes on. Without an active
+// finishing lane (or when its pool is full) that is the main workspace and the main stream. With one, call
+// ojc_finish_stream after the producing kernel was launched: it orders the lane behind the main stream's work so far.
+ojc_status ojc_partials(ojc_backend* be, uint64_t bytes, void** out, bool* on_lane);
+ojc_status ojc_finish_stream(ojc_backend* be, bool on_lane, cudaStream_t* stream);
 
 #define OJC_TRY(expr) do { ojc_status st__ = (expr); if (st__ != OJC_OK) return st__; } while (0)
 #define OJC_CUDA(be, expr, op) OJC_TRY(ojc_cuda_check((be), (expr), (op)))

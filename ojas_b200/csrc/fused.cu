@@ -439,10 +439,13 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
     int64_t blocks = (tokens + tokens_per_block - 1) / tokens_per_block;
     if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
     void* part = nullptr;
-    OJC_TRY(ojc_scratch(be, (uint64_t)blocks * dh * 4, &part));
+    bool on_lane = false;
+    cudaStream_t fs = nullptr;
+    OJC_TRY(ojc_partials(be, (uint64_t)blocks * dh * 4, &part, &on_lane));
     qk_norm_rope_backward_kernel<TPR><<<(unsigned)blocks, 128, 128 * 16 * 4, be->stream>>>(x, xs, w, cos_t, sin_t, gy, gys, gx, gxs, (float*)part, tokens, heads, time, eps);
     OJC_LAUNCHED(be, op);
-    fused_column_sum_kernel<<<(dh + 31) / 32, 256, 0, be->stream>>>((const float*)part, gw, (int)blocks, dh);
+    OJC_TRY(ojc_finish_stream(be, on_lane, &fs));
+    fused_column_sum_kernel<<<(dh + 31) / 32, 256, 0, fs>>>((const float*)part, gw, (int)blocks, dh);
     OJC_LAUNCHED(be, op);
     return OJC_OK;
   });
@@ -466,10 +469,13 @@ ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16*
   int64_t blocks = (rows + warps - 1) / warps;
   if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
   void* part = nullptr;
-  OJC_TRY(ojc_scratch(be, (uint64_t)blocks * heads * 4, &part));
+  bool on_lane = false;
+  cudaStream_t fs = nullptr;
+  OJC_TRY(ojc_partials(be, (uint64_t)blocks * heads * 4, &part, &on_lane));
   gate_apply_backward_kernel<<<(unsigned)blocks, warps * 32, warps * heads * 4, be->stream>>>(scales, attn, gout, gattn, gz, zld, (float*)part, rows, heads, dh);
   OJC_LAUNCHED(be, op);
-  fused_column_sum_kernel<<<(heads + 31) / 32, 256, 0, be->stream>>>((const float*)part, gbias, (int)blocks, heads);
+  OJC_TRY(ojc_finish_stream(be, on_lane, &fs));
+  fused_column_sum_kernel<<<(heads + 31) / 32, 256, 0, fs>>>((const float*)part, gbias, (int)blocks, heads);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }

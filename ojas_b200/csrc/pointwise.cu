@@ -319,16 +319,19 @@ ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_ten
   const int warps = dim > 512 ? 4 : 8;
   int64_t blocks = (rows + warps - 1) / warps;
   if (blocks > be->sm_count * 4) blocks = be->sm_count * 4;
-  void* part = nullptr;
-  OJC_TRY(ojc_scratch(be, (uint64_t)blocks * dim * 4, &part));
   if (x->dtype != gy->dtype || x->dtype != gx->dtype) return ojc_fail(OJC_ERR_DTYPE, op, "x, grad_y and grad_x must share a dtype");
+  void* part = nullptr;
+  bool on_lane = false;
+  cudaStream_t fs = nullptr;
+  OJC_TRY(ojc_partials(be, (uint64_t)blocks * dim * 4, &part, &on_lane));
   const bool aligned = ((reinterpret_cast<uintptr_t>(x->data) | reinterpret_cast<uintptr_t>(gy->data) | reinterpret_cast<uintptr_t>(gx->data) |
                          reinterpret_cast<uintptr_t>(w->data) | reinterpret_cast<uintptr_t>(gx_b)) & 15) == 0;
   if (gx_b && x->dtype == OJC_F32 && aligned && rms_backward_rows_supported(dim)) {
     // the residual-stream form of the bf16 step: 128-bit accesses, same arithmetic
     OJC_TRY(rms_backward_rows(be, (const float*)x->data, (const float*)w->data, (const float*)gy->data, (float*)gx->data, gx_b, (float*)part, rows, dim, eps,
                               accumulate_gx, (int)blocks));
-    column_sum_finish_kernel<<<(dim + 31) / 32, 256, 0, be->stream>>>((const float*)part, (float*)gw->data, (int)blocks, dim, accumulate_gw ? 1 : 0);
+    OJC_TRY(ojc_finish_stream(be, on_lane, &fs));
+    column_sum_finish_kernel<<<(dim + 31) / 32, 256, 0, fs>>>((const float*)part, (float*)gw->data, (int)blocks, dim, accumulate_gw ? 1 : 0);
     OJC_LAUNCHED(be, op);
     return OJC_OK;
   }
@@ -340,7 +343,8 @@ ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_ten
       OJC_LAUNCHED(be, op);
       return OJC_OK;
     }); }));
-  column_sum_finish_kernel<<<(dim + 31) / 32, 256, 0, be->stream>>>((const float*)part, (float*)gw->data, (int)blocks, dim, accumulate_gw ? 1 : 0);
+  OJC_TRY(ojc_finish_stream(be, on_lane, &fs));
+  column_sum_finish_kernel<<<(dim + 31) / 32, 256, 0, fs>>>((const float*)part, (float*)gw->data, (int)blocks, dim, accumulate_gw ? 1 : 0);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }

@@ -286,6 +286,25 @@ ojc_status ojc_fill_zero(ojc_backend* be, void* ptr, uint64_t bytes) {
 
 }  // extern "C"
 
+ojc_status ojc_partials(ojc_backend* be, uint64_t bytes, void** out, bool* on_lane) {
+  ojc_backend::FinishLane& f = be->finish;
+  const uint64_t need = (bytes + 255) & ~uint64_t(255);
+  *on_lane = f.active && f.stream != be->stream && f.used + need <= f.pool_bytes;
+  if (!*on_lane) return ojc_scratch(be, bytes, out);
+  *out = f.pool + f.used;
+  f.used += need;
+  return OJC_OK;
+}
+
+ojc_status ojc_finish_stream(ojc_backend* be, bool on_lane, cudaStream_t* stream) {
+  *stream = be->stream;
+  if (!on_lane) return OJC_OK;
+  OJC_CUDA(be, cudaEventRecord(be->finish.ev, be->stream), "finish_lane");
+  OJC_CUDA(be, cudaStreamWaitEvent(be->finish.stream, be->finish.ev, 0), "finish_lane");
+  *stream = be->finish.stream;
+  return OJC_OK;
+}
+
 ojc_status ojc_scratch(ojc_backend* be, uint64_t bytes, void** out) {
   if (bytes > be->scratch_bytes) {
     // The old workspace may still be read by queued kernels: drain the stream before replacing it.

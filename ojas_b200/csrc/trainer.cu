@@ -81,7 +81,9 @@ struct ojc_trainer {
   // stream walks on through the dX chain: nothing downstream reads them before the optimizer.
   cudaStream_t side_stream = nullptr;
   bool side_enabled = true;
-  cudaEvent_t ev_main = nullptr, ev_side = nullptr;
+  cudaEvent_t ev_main = nullptr, ev_side = nullptr, ev_finish = nullptr;
+  void* finish_pool = nullptr;                  // partial sums of the small weight-gradient reductions finished on the side stream
+  static constexpr uint64_t FINISH_POOL_BYTES = 16ull << 20;
   void* side_scratch = nullptr;
   uint64_t side_scratch_bytes = 0;
   struct Bucket { int64_t offset, floats; int first_param; cudaEvent_t ready; bool recorded; };
@@ -319,7 +321,22 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     if (!lane) return OJC_OK;
     OJC_CUDA(be, cudaEventRecord(tr->ev_side, tr->side_stream), "side_lane");
     OJC_CUDA(be, cudaStreamWaitEvent(be->stream, tr->ev_side, 0), "side_lane");
+    be->finish.used = 0;     // every finishing kernel queued so far is ordered before what the main stream does next
     return OJC_OK;
+  };
+  // The small finishing reductions of the norm, QK-norm and gate-bias gradients (a few blocks each) go to the side lane too.
+  struct FinishScope {
+    ojc_backend* be;
+    FinishScope(ojc_backend* b, ojc_trainer* t, bool on) : be(b) {
+      if (on) { be->finish.stream = t->side_stream; be->finish.ev = t->ev_finish; be->finish.pool = (char*)t->finish_pool; be->finish.pool_bytes = ojc_trainer::FINISH_POOL_BYTES; be->finish.used = 0; be->finish.active = true; }
+    }
+    ~FinishScope() { be->finish.active = false; }
+  } finish_scope(be, tr, lane);
+  // a bucket's event must also cover the lane's work: join before the first event a call records
+  auto ready = [&](int first_param_done) -> ojc_status {
+    for (auto& b : tr->buckets)
+      if (!b.recorded && b.first_param >= first_param_done && b.first_param != 0) { OJC_TRY(join_side()); break; }
+    return record_ready(tr, first_param_done);
   };
   for (int64_t l = L - 1; l >= 0; --l) {
     LayerActs& a = tr->acts[l];
@@ -443,9 +460,10 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       OJC_TRY(rms_backward_impl(be, &x, &n1, &gy, eps, &gx, &gn1, false, true, bf ? (bf16*)tr->gx_b : nullptr));
     }
     if (l == 0 && s.n_layer > 0) OJC_TRY(ojc_fill_zero(be, tr->G(tr->P(0, P_LAMBDA)), 4));  // layer 0's lambda never trains (names.rs:262-268)
-    OJC_TRY(record_ready(tr, 1 + (int)l * P_PER_BLOCK));
+    OJC_TRY(ready(1 + (int)l * P_PER_BLOCK));
   }
   OJC_TRY(embedding_backward_impl(be, ids_dev, tr->gx, OJC_F32, tr->G(tok), N, V, d, true));
+  OJC_TRY(join_side());   // the last finishing reductions: every gradient is final on the main stream from here
   for (auto& b : tr->buckets) if (b.first_param == 0) OJC_CUDA(be, cudaEventRecord(b.ready, be->stream), "bucket_ready");
   return OJC_OK;
 }
@@ -558,7 +576,9 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
   if (tr->act_dt == OJC_BF16 && !(lane_env && lane_env[0] == '0')) {
     if (cudaStreamCreateWithFlags(&tr->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&tr->ev_main, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&tr->ev_side, cudaEventDisableTiming) != cudaSuccess)
+        cudaEventCreateWithFlags(&tr->ev_side, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&tr->ev_finish, cudaEventDisableTiming) != cudaSuccess ||
+        cudaMalloc(&tr->finish_pool, ojc_trainer::FINISH_POOL_BYTES) != cudaSuccess)
       return fail(ojc_fail(OJC_ERR_BACKEND, op, "cannot create the weight-gradient stream"));
   }
   *out = tr;
@@ -572,6 +592,8 @@ ojc_status ojc_trainer_close(ojc_trainer* tr) {
   if (tr->ev_main) cudaEventDestroy(tr->ev_main);
   if (tr->ev_side) cudaEventDestroy(tr->ev_side);
   if (tr->side_scratch) cudaFree(tr->side_scratch);
+  if (tr->ev_finish) cudaEventDestroy(tr->ev_finish);
+  if (tr->finish_pool) cudaFree(tr->finish_pool);
   for (void* p : tr->owned) ojc_free(tr->be, p);
   for (auto& b : tr->buckets) if (b.ready) cudaEventDestroy(b.ready);
   delete tr;
