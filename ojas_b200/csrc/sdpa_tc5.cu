@@ -1,12 +1,17 @@
 // Causal attention on the Blackwell tensor cores (tcgen05 + TMEM), head_dim 64 or 128, bf16 operands.
 //
 // Forward: one CTA owns 128 query rows of one (batch, head) and walks the visible key blocks of 128:
-//   warp 4   TMA producer: Q once, then (K, V) pairs into two stages, 128-byte swizzle, every CTA fetching its own tiles
+//   warp 4   TMA producer: Q once, then K and V tiles on separate two-stage rings (a K stage is free after its Q K^T, a V
+//            stage after its P V), 128-byte swizzle, every CTA fetching its own tiles; the first loads go out before the
+//            CTA-wide sync
 //   warp 5   allocates 256 TMEM columns and issues the MMAs: S = Q K^T (M128 N128 K64, both K-major) into columns
-//            [0,128), then O += P V (M128 N64 K128, P K-major from shared memory, V MN-major) into columns [128,192)
-//   warps 0-3  one thread per query row (= TMEM lane): read the S row once, softmax in the log2 domain against a row
-//            scale that moves only when the maximum outgrew it by 2^8 (then O is rescaled in place in TMEM), write P as
-//            bf16 into the swizzled shared-memory A-operand layout; at the end normalise O from TMEM, store O and lse.
+//            [0,128), then O += P V (M128 N64 K128, P K-major from shared memory, V MN-major) into columns [128,192);
+//            S of block j + 1 is issued as soon as the softmax rows hold S of block j in registers
+//   warps 0-3  one thread per query row (= TMEM lane): read the S row once and hand the columns back, softmax in the log2
+//            domain against a row scale that moves only when the maximum outgrew it by 2^8 (then O is rescaled in place
+//            in TMEM), write P as bf16 into the swizzled shared-memory A-operand layout (the one P buffer comes back from
+//            the previous P V in two 64-key halves); at the end normalise O from TMEM, store O and lse.
+// Blocks are ordered long tiles first inside groups of planes small enough to stay in L2 (tile_order).
 // At head_dim 64 two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one CTA's softmax overlaps
 // the other's MMAs; at head_dim 128 the tiles take 192 KB and one CTA owns the SM. Rows wider than 128 bytes are kept as
 // 64-column sub-tiles (one 128-byte swizzle span each), 16 KB apart for 128-row tiles and 8 KB apart for 64-row tiles.
@@ -303,9 +308,10 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 //          the threads (one key row each) form P^T and dS^T and write them as swizzled bf16 A operands, and
 //          dV += P^T dO, dK += dS^T Q accumulate in TMEM across the whole walk (query heads of a GQA group included).
 //   dQ:    a CTA owns 128 queries and walks the keys: S = Q K^T, dP = dO V^T, dS -> shared memory, dQ += dS K in TMEM.
-// Both walk in steps of SUB = 64 and take 256 TMEM columns and under 100 KB of shared memory, so two CTAs share an SM:
-// while one CTA's eight compute warps turn a step into P and dS, the other's MMAs run, and a CTA's prologue and final
-// stores hide behind its neighbour's walk. dS is kept unscaled; the softmax scale multiplies dK and dQ once, on the way out.
+// Both walk in steps of SUB = 64 over three input stages. At head_dim 64 each takes 256 TMEM columns and at most 112 KB of
+// shared memory, so two CTAs share an SM: while one CTA's eight compute warps turn a step into P and dS, the other's MMAs
+// run, the next step's S / dP MMAs go out as soon as this step's sit in registers, and a CTA's prologue and final stores
+// hide behind its neighbour's walk. dS is kept unscaled; the softmax scale multiplies dK and dQ once, on the way out.
 struct BwdArgs {
   SdpaView<bf16> g0, g1;          // dK, dV  or  dQ (g1 unused)
   const float* lse2;              // lse * log2(e)
