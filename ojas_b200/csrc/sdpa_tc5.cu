@@ -365,7 +365,7 @@ __device__ __forceinline__ void store_row_bf16(bf16* dst, uint32_t taddr, float 
 
 constexpr int SUB = 64;
 constexpr int PT_BYTES = 128 * SUB * 2;        // 16 KB: 128 rows x 64 columns of P or dS (one 128-byte swizzled row each)
-constexpr int IN_STAGES = 3;          // q / dO stages of the dK/dV kernel
+constexpr int IN_STAGES = 3;          // most q / dO stages the dK/dV kernel rings (its barrier table is laid out for these)
 constexpr int DQ_STAGES = 3;          // k / v stages of the dQ kernel
 
 // One step of a compute thread: 32 columns of its row. s, dp: the thread's S and dP values; stats: the columns' (dK/dV) or
@@ -397,15 +397,16 @@ __device__ __forceinline__ void store_chunk(uint8_t* row, const uint4& v, int ha
 
 // ---- dK, dV
 template <int D> struct Dkv {
+  static constexpr int STAGES = D == 64 ? IN_STAGES : 2;       // head_dim 128 (one CTA per SM) measured the same on two as on three
   static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128, STEP_BYTES = NSUB * ST64;   // K / V tile; one step of q or dO
-  static constexpr int OFF_K = 0, OFF_V = TILE_BYTES, OFF_Q = 2 * TILE_BYTES, OFF_G = OFF_Q + IN_STAGES * STEP_BYTES, OFF_P = OFF_G + IN_STAGES * STEP_BYTES,
+  static constexpr int OFF_K = 0, OFF_V = TILE_BYTES, OFF_Q = 2 * TILE_BYTES, OFF_G = OFF_Q + STAGES * STEP_BYTES, OFF_P = OFF_G + STAGES * STEP_BYTES,
                        OFF_DS = OFF_P + PT_BYTES, OFF_STAT = OFF_DS + PT_BYTES;
   // Row statistics of a step (lse * log2 e and Dr of its 64 queries). One CTA per SM: they ride into shared memory with the
   // step's tiles. Two CTAs per SM: no room is left (112 KB of tiles + barriers fill the SM's half to the last kilobyte), so
   // the compute warps keep them in registers and shuffle them round.
   static constexpr bool STATS_IN_SMEM = D != 64;
-  static constexpr int OFF_BAR = OFF_STAT + (STATS_IN_SMEM ? IN_STAGES * 2 * SUB * 4 : 0);
-  static constexpr int SMEM_BYTES = OFF_BAR + 128;              // D 64: 112 KB + 128; D 128: 193.6 KB
+  static constexpr int OFF_BAR = OFF_STAT + (STATS_IN_SMEM ? STAGES * 2 * SUB * 4 : 0);
+  static constexpr int SMEM_BYTES = OFF_BAR + 128;              // D 64: 112 KB + 128; D 128: 161 KB
   static constexpr int TMEM_COLS = D == 64 ? 256 : 512;         // S^T 64 + dP^T 64 + dV D + dK D
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
@@ -436,7 +437,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 
   // step `it` of the walk: query head hk * rep + it / q_subs, queries from k0 + (it % q_subs) * SUB
   auto load_step = [&](int it) {
-    const int s = it % IN_STAGES, h = hk * rep + it / q_subs, q0 = k0 + (it % q_subs) * SUB;
+    const int s = it % C::STAGES, h = hk * rep + it / q_subs, q0 = k0 + (it % q_subs) * SUB;
     // statistics in shared memory ride on the same barrier (time is a multiple of 4, so the copies are whole 16-byte units)
     const uint32_t stat_bytes = C::STATS_IN_SMEM ? (uint32_t)min(SUB, args.time - q0) * 4u : 0u;
     mbar_expect_tx(bar(KB_INFULL0 + s), 2 * STEP_BYTES + 2 * stat_bytes);
@@ -457,7 +458,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     mbar_expect_tx(bar(KB_KVFULL), 2 * TILE_BYTES);
     load_tile<NSUB, 128>(base + KV_OFF_K, &tm_k, bar(KB_KVFULL), args.h_first, hk, k0, b);
     load_tile<NSUB, 128>(base + KV_OFF_V, &tm_v, bar(KB_KVFULL), args.h_first, hk, k0, b);
-    for (int it = 0; it < min(IN_STAGES, iters); ++it) load_step(it);
+    for (int it = 0; it < min(C::STAGES, iters); ++it) load_step(it);
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS) : "memory");
@@ -471,8 +472,8 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 
   if (warp == 8) {
     if (lane == 0) {
-      for (int it = IN_STAGES; it < iters; ++it) {
-        if (!mbar_wait(bar(KB_INEMPTY0 + it % IN_STAGES), ((it / IN_STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
+      for (int it = C::STAGES; it < iters; ++it) {
+        if (!mbar_wait(bar(KB_INEMPTY0 + it % C::STAGES), ((it / C::STAGES) & 1) ^ 1, args.fault, abort_flag)) break;
         load_step(it);
       }
     }
@@ -484,7 +485,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       const uint32_t p_lo = desc_lo(base + KV_OFF_P, 0), ds_lo = desc_lo(base + KV_OFF_DS, 0);
       // S^T = K Q^T and dP^T = V dO^T of step i
       auto issue_s = [&](uint32_t i) {
-        const uint32_t st = (i % IN_STAGES) * STEP16;
+        const uint32_t st = (i % C::STAGES) * STEP16;
 #pragma unroll
         for (uint32_t kk = 0; kk < D / 16; ++kk)
           umma_lh(tmem_base, k_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, q_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
@@ -502,7 +503,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         auto next_s = [&]() -> bool {
           if (it + 1 >= (uint32_t)iters) return true;
           if (C::CTAS == 2 && !mbar_wait(bar(KB_SFREE), it & 1, args.fault, abort_flag)) return false;
-          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % IN_STAGES), ((it + 1) / IN_STAGES) & 1, args.fault, abort_flag)) return false;
+          if (!mbar_wait(bar(KB_INFULL0 + (it + 1) % C::STAGES), ((it + 1) / C::STAGES) & 1, args.fault, abort_flag)) return false;
           fence_after();
           issue_s(it + 1);
           return true;
@@ -511,14 +512,14 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         // every compute thread has written P / dS of this step
         if (!mbar_wait(bar(KB_PREADY), it & 1, args.fault, abort_flag)) break;
         fence_after();
-        const uint32_t st = (it % IN_STAGES) * STEP16;
+        const uint32_t st = (it % C::STAGES) * STEP16;
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO   (dO as the MN-major B operand: 16 queries = 2048 bytes)
           umma_lh(tmem_base + 128, p_lo + kk * KSTEP, gm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
           umma_lh(tmem_base + 128 + D, ds_lo + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(KB_INEMPTY0 + it % IN_STAGES));
+        umma_commit(bar(KB_INEMPTY0 + it % C::STAGES));
         umma_commit(bar(KB_PFREE));               // P and dS may be overwritten
         if (it + 1 == (uint32_t)iters) umma_commit(bar(KB_DONE));
         if (C::CTAS == 1 && !next_s()) break;
@@ -555,7 +556,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       tmem_wait_ld();
       if (C::CTAS == 2) { fence_before(); mbar_arrive(bar(KB_SFREE)); }   // the accumulator columns may take the next step
       const int qb = q0 + half * 32;
-      const float* st = stat + (it % IN_STAGES) * 128 + half * 32;
+      const float* st = stat + (it % C::STAGES) * 128 + half * 32;
       auto stats = [&](int g, float (&l2)[8], float (&dd)[8]) {
         if (C::STATS_IN_SMEM) {                    // every thread of the warp reads the same values: 16-byte broadcast loads
           const float4 a = *reinterpret_cast<const float4*>(st + g * 8), b4 = *reinterpret_cast<const float4*>(st + g * 8 + 4);
