@@ -176,8 +176,10 @@ __global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, c
 
 // dAttn = gOut * g; gz[row, h] = (sum_dh gOut * attn) * g (1 - g), written as bf16 [rows, zld] with zero padding columns
 // (the operand of the two gate GEMMs) and as f32 partial column sums for the bias gradient. One warp per row.
+// With `dr`: also Dr[b, h, t] = sum_dh dAttn * attn = g * (sum_dh gOut * attn), the row statistic the attention backward needs
+// (rows are tokens b * time + t), which saves that op a pass over attn and dAttn.
 __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, const bf16* __restrict__ attn, const bf16* __restrict__ gout, bf16* __restrict__ gattn,
-                                           bf16* __restrict__ gz, int zld, float* __restrict__ part_out, int64_t rows, int heads, int dh) {
+                                           bf16* __restrict__ gz, int zld, float* __restrict__ part_out, int64_t rows, int heads, int dh, float* __restrict__ dr, int time) {
   extern __shared__ float red[];  // [warps][heads]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int per = dh / 8;                 // 16-byte chunks per head
@@ -205,6 +207,7 @@ __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, con
         const float zg = dot * g * (1.0f - g);
         gz[row * zld + h] = __float2bfloat16_rn(zg);
         mine[h] += zg;
+        if (dr) dr[((row / time) * heads + h) * (int64_t)time + row % time] = dot * g;
       }
     }
     for (int h = heads + lane; h < zld; h += 32) gz[row * zld + h] = __float2bfloat16_rn(0.0f);
@@ -461,7 +464,7 @@ ojc_status gate_apply_forward(ojc_backend* be, const bf16* z, int zld, const flo
 }
 
 ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16* attn, const bf16* gout, bf16* gattn, bf16* gz, int zld, float* gbias, int64_t rows,
-                               int heads, int dh) {
+                               int heads, int dh, float* dr, int time) {
   const char* op = "per_head_sigmoid_gate_backward";
   const int per = dh / 8;
   if (dh % 8 != 0 || per > 32 || (per & (per - 1)) != 0) return ojc_fail(OJC_ERR_UNSUPPORTED_HEAD_DIM, op, "head_dim must be 8, 16, 32, 64, 128 or 256");
@@ -472,7 +475,7 @@ ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16*
   bool on_lane = false;
   cudaStream_t fs = nullptr;
   OJC_TRY(ojc_partials(be, (uint64_t)blocks * heads * 4, &part, &on_lane));
-  gate_apply_backward_kernel<<<(unsigned)blocks, warps * 32, warps * heads * 4, be->stream>>>(scales, attn, gout, gattn, gz, zld, (float*)part, rows, heads, dh);
+  gate_apply_backward_kernel<<<(unsigned)blocks, warps * 32, warps * heads * 4, be->stream>>>(scales, attn, gout, gattn, gz, zld, (float*)part, rows, heads, dh, dr, time > 0 ? time : 1);
   OJC_LAUNCHED(be, op);
   OJC_TRY(ojc_finish_stream(be, on_lane, &fs));
   fused_column_sum_kernel<<<(heads + 31) / 32, 256, 0, fs>>>((const float*)part, gbias, (int)blocks, heads);

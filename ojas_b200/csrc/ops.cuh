@@ -25,7 +25,7 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
                                  bf16* gx, int64_t gxs, float* gw, int64_t tokens, int heads, int dh, int time, float eps);
 ojc_status gate_apply_forward(ojc_backend* be, const bf16* z, int zld, const float* bias, const bf16* attn, bf16* out, float* scales, int64_t rows, int heads, int dh);
 ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16* attn, const bf16* gout, bf16* gattn, bf16* gz, int zld, float* gbias, int64_t rows,
-                               int heads, int dh);
+                               int heads, int dh, float* dr = nullptr, int time = 0);   // dr: also Dr[b, h, t] of the attention backward, rows = b * time + t
 // row-strided forms for column slices of a [rows, ld] buffer
 ojc_status swiglu_rows_forward(ojc_backend* be, const bf16* au, int64_t ld, bf16* m, int64_t rows, int64_t f);
 ojc_status swiglu_rows_backward(ojc_backend* be, const bf16* au, const bf16* gm, bf16* gau, int64_t ld, int64_t rows, int64_t f);

@@ -272,6 +272,28 @@ ojc_status ojc_causal_sdpa_backward(ojc_backend* be, const ojc_tensor* q, const 
   return sdpa_backward_f32tier(be, q, k, v, out, (const float*)lse->data, gout, window, gq, gk, gv, d, (float*)dr);
 }
 
+}  // extern "C"
+
+bool sdpa_backward_takes_dr(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const ojc_tensor* gout,
+                            const ojc_tensor* gq, const ojc_tensor* gk, const ojc_tensor* gv, int64_t window) {
+  SdpaDims d;
+  if (sdpa_check("causal_sdpa_backward", q, k, v, &d) != OJC_OK) return false;
+  return sdpa_tcgen05_bwd_eligible(be, q, k, v, gout, gq, gk, gv, window, d) && out->dtype == OJC_BF16 && strides_ok_for_rows(out) && strides_ok_for_rows(gout);
+}
+
+ojc_status sdpa_backward_with_dr(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const ojc_tensor* lse,
+                                 const ojc_tensor* gout, int64_t window, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const float* dr, bool* taken) {
+  *taken = false;
+  if (!sdpa_backward_takes_dr(be, q, k, v, out, gout, gq, gk, gv, window)) return OJC_OK;
+  SdpaDims d;
+  OJC_TRY(sdpa_check("causal_sdpa_backward", q, k, v, &d));
+  if (lse->dtype != OJC_F32 || numel(lse) != (int64_t)d.batch * d.heads * d.time) return ojc_fail(OJC_ERR_SHAPE, "causal_sdpa_backward", "lse must be F32 [B,H,T]");
+  *taken = true;
+  return sdpa_backward_tcgen05(be, q, k, v, out, (const float*)lse->data, gout, gq, gk, gv, d, nullptr, dr);
+}
+
+extern "C" {
+
 // The backward that never trusts a saved (possibly bf16-rounded) output: it reruns the forward for O and lse in
 // workspace first, so Dr = dO . O cancels the row sum exactly (ojas-core/src/autocast.rs:1200-1254).
 ojc_status ojc_causal_sdpa_backward_recompute(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* gout,

@@ -314,7 +314,7 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 // hide behind its neighbour's walk. dS is kept unscaled; the softmax scale multiplies dK and dQ once, on the way out.
 struct BwdArgs {
   SdpaView<bf16> g0, g1;          // dK, dV  or  dQ (g1 unused)
-  const float* lse2;              // lse * log2(e)
+  const float* lse;               // natural-log row sums of the forward; the kernels scale them by log2(e) where they read them
   const float* dr;
   int heads, kv_heads, time, h_first;
   int planes, group;              // of this launch: batch * kv_heads (dK/dV) or batch * heads (dQ); planes per L2 group
@@ -322,10 +322,11 @@ struct BwdArgs {
   uint32_t* fault;
 };
 
-// Dr[b,h,t] = sum_d dO . O and lse2 = lse * log2(e): D / 8 threads per row, 16-byte loads.
+// Dr[b,h,t] = sum_d dO . O: D / 8 threads per row, 16-byte loads. Skipped when the caller already has Dr (the gate's
+// backward forms the same dot product).
 template <int D>
-__global__ void sdpa_bwd_prep_kernel(SdpaView<const bf16> out, SdpaView<const bf16> gout, const float* __restrict__ lse, float* __restrict__ dr,
-                                     float* __restrict__ lse2, int heads, int time, int64_t rows) {
+__global__ void sdpa_bwd_prep_kernel(SdpaView<const bf16> out, SdpaView<const bf16> gout, float* __restrict__ dr,
+                                     int heads, int time, int64_t rows) {
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   constexpr int TPR = D / 8;
   const int64_t r = min(gid / TPR, rows - 1);
@@ -339,7 +340,7 @@ __global__ void sdpa_bwd_prep_kernel(SdpaView<const bf16> out, SdpaView<const bf
     acc += __uint_as_float(ow[i] << 16) * __uint_as_float(gw[i] << 16) + __uint_as_float(ow[i] & 0xffff0000u) * __uint_as_float(gw[i] & 0xffff0000u);
 #pragma unroll
   for (int o = 1; o < TPR; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (part == 0 && gid / TPR < rows) { dr[r] = acc; lse2[r] = lse[r] * LOG2E; }
+  if (part == 0 && gid / TPR < rows) dr[r] = acc;
 }
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -445,7 +446,7 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     load_tile<NSUB, 64>(base + KV_OFF_G + s * STEP_BYTES, &tm_g, bar(KB_INFULL0 + s), args.h_first, h, q0, b);
     if (C::STATS_IN_SMEM) {
       const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q0;
-      bulk_load(base + KV_OFF_STAT + s * 512, args.lse2 + idx, stat_bytes, bar(KB_INFULL0 + s));
+      bulk_load(base + KV_OFF_STAT + s * 512, args.lse + idx, stat_bytes, bar(KB_INFULL0 + s));
       bulk_load(base + KV_OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KB_INFULL0 + s));
     }
   };
@@ -536,12 +537,12 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     int q0 = k0;
     // Statistics kept out of shared memory: lane c of a warp holds those of column c of its half, fetched one step
     // ahead, and the warp shuffles them round as the columns come up.
-    const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse2 64 | dr 64] when in shared memory
+    const float* stat = reinterpret_cast<const float*>(base_ptr + KV_OFF_STAT);   // [stage][lse 64 | dr 64] when in shared memory
     auto stat_of = [&](int it, float& l2, float& dr) {
       const int h = hk * rep + it / q_subs, q = k0 + (it % q_subs) * SUB + half * 32 + lane;
       const bool in = !C::STATS_IN_SMEM && it < iters && q < args.time;
       const int64_t idx = ((int64_t)b * args.heads + h) * args.time + q;
-      l2 = in ? args.lse2[idx] : INFINITY;
+      l2 = in ? args.lse[idx] * LOG2E : INFINITY;
       dr = in ? args.dr[idx] : 0.0f;
     };
     float my_l2, my_dr, next_l2, next_dr;
@@ -561,7 +562,8 @@ sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         if (C::STATS_IN_SMEM) {                    // every thread of the warp reads the same values: 16-byte broadcast loads
           const float4 a = *reinterpret_cast<const float4*>(st + g * 8), b4 = *reinterpret_cast<const float4*>(st + g * 8 + 4);
           const float4 c = *reinterpret_cast<const float4*>(st + SUB + g * 8), d = *reinterpret_cast<const float4*>(st + SUB + g * 8 + 4);
-          l2[0] = a.x; l2[1] = a.y; l2[2] = a.z; l2[3] = a.w; l2[4] = b4.x; l2[5] = b4.y; l2[6] = b4.z; l2[7] = b4.w;
+          l2[0] = a.x * LOG2E; l2[1] = a.y * LOG2E; l2[2] = a.z * LOG2E; l2[3] = a.w * LOG2E;
+          l2[4] = b4.x * LOG2E; l2[5] = b4.y * LOG2E; l2[6] = b4.z * LOG2E; l2[7] = b4.w * LOG2E;
           dd[0] = c.x; dd[1] = c.y; dd[2] = c.z; dd[3] = c.w; dd[4] = d.x; dd[5] = d.y; dd[6] = d.z; dd[7] = d.w;
         } else {
 #pragma unroll
@@ -719,7 +721,7 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
     const int64_t idx = ((int64_t)b * args.heads + h) * args.time + row;
-    const float lse_row = row < args.time ? args.lse2[idx] : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
+    const float lse_row = row < args.time ? args.lse[idx] * LOG2E : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
     uint8_t* ds_row = base_ptr + DQ_OFF_DS + tid * 128;
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
@@ -825,7 +827,7 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
 }
 
 template <int D>
-static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* out, const float* lse, const ojc_tensor* gout, float* dr, float* lse2, int64_t rows,
+static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* out, const ojc_tensor* gout, float* dr_work, int64_t rows,
                              const CUtensorMap (&m)[8], BwdArgs a, const ojc_tensor* gq, const ojc_tensor* gk, const ojc_tensor* gv, const SdpaDims& d) {
   static bool attr = false;
   if (!attr) {
@@ -833,10 +835,12 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);
     attr = true;
   }
-  sdpa_bwd_prep_kernel<D><<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, be->stream>>>(
-      SdpaView<const bf16>{(const bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]},
-      SdpaView<const bf16>{(const bf16*)gout->data, gout->stride[0], gout->stride[1], gout->stride[2]}, lse, dr, lse2, d.heads, d.time, rows);
-  OJC_LAUNCHED(be, op);
+  if (dr_work) {   // the caller has no Dr of its own
+    sdpa_bwd_prep_kernel<D><<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, be->stream>>>(
+        SdpaView<const bf16>{(const bf16*)out->data, out->stride[0], out->stride[1], out->stride[2]},
+        SdpaView<const bf16>{(const bf16*)gout->data, gout->stride[0], gout->stride[1], gout->stride[2]}, dr_work, d.heads, d.time, rows);
+    OJC_LAUNCHED(be, op);
+  }
   a.g0 = SdpaView<bf16>{(bf16*)gk->data, gk->stride[0], gk->stride[1], gk->stride[2]};
   a.g1 = SdpaView<bf16>{(bf16*)gv->data, gv->stride[0], gv->stride[1], gv->stride[2]};
   a.planes = d.batch * d.kv_heads;
@@ -853,20 +857,21 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
   return OJC_OK;
 }
 
-// `work` holds 2 * B * H * T floats (Dr and lse * log2(e), filled by the prepass). Eligibility is the forward's plus the gradient views.
+// `work` holds B * H * T floats for Dr = rowsum(dO . O), filled by the prepass, unless the caller passes `dr_given` (Dr it
+// already has, [B, H, T]). Eligibility is the forward's plus the gradient views.
 ojc_status sdpa_backward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* out, const float* lse,
-                                 const ojc_tensor* gout, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* work) {
+                                 const ojc_tensor* gout, ojc_tensor* gq, ojc_tensor* gk, ojc_tensor* gv, const SdpaDims& d, float* work, const float* dr_given) {
   const char* op = "causal_sdpa_backward";
   const int64_t rows = (int64_t)d.batch * d.heads * d.time;
-  float *dr = work, *lse2 = work + rows;
   const bool hf = q->stride[1] < q->stride[2];
   // maps 0-3: q, k, v, dO in 128-row tiles (the operand a CTA keeps); 4-7: the same in 64-row steps (the one it walks)
   CUtensorMap m[8];
   const ojc_tensor* src[4] = {q, k, v, gout};
   for (int i = 0; i < 4; ++i) { OJC_TRY(make_map(be, op, &m[i], src[i], hf)); OJC_TRY(make_map(be, op, &m[4 + i], src[i], hf, SUB)); }
   BwdArgs a;
-  a.lse2 = lse2; a.dr = dr; a.heads = d.heads; a.kv_heads = d.kv_heads; a.time = d.time; a.h_first = hf ? 1 : 0; a.scale = d.scale; a.fault = be->fault_dev;
-  return d.dim == 64 ? launch_bwd<64>(be, op, out, lse, gout, dr, lse2, rows, m, a, gq, gk, gv, d) : launch_bwd<128>(be, op, out, lse, gout, dr, lse2, rows, m, a, gq, gk, gv, d);
+  a.lse = lse; a.dr = dr_given ? dr_given : work; a.heads = d.heads; a.kv_heads = d.kv_heads; a.time = d.time; a.h_first = hf ? 1 : 0; a.scale = d.scale; a.fault = be->fault_dev;
+  float* prep = dr_given ? nullptr : work;
+  return d.dim == 64 ? launch_bwd<64>(be, op, out, gout, prep, rows, m, a, gq, gk, gv, d) : launch_bwd<128>(be, op, out, gout, prep, rows, m, a, gq, gk, gv, d);
 }
 
 bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tensor* k, const ojc_tensor* v, const ojc_tensor* gout, const ojc_tensor* gq,

@@ -17,6 +17,7 @@
 #include "linear.cuh"
 #include "ops.cuh"
 #include "optim.cuh"
+#include "sdpa.cuh"
 
 namespace {
 
@@ -67,6 +68,7 @@ struct ojc_trainer {
   void *hf = nullptr, *gx_b = nullptr, *g_m = nullptr, *g_a = nullptr, *g_u = nullptr, *g_yg = nullptr, *g_y = nullptr, *g_qr = nullptr, *g_kr = nullptr,
        *g_v = nullptr, *g_qn = nullptr, *g_kn = nullptr, *g_q = nullptr, *g_k = nullptr, *g_rawv = nullptr, *g_v0l = nullptr, *qn = nullptr, *kn = nullptr;
   uint32_t *ids = nullptr, *targets = nullptr;
+  float* dr = nullptr;                          // [B, H, T] rowsum(dO . O): written by the gate's backward, read by the attention backward
   bf16 *gate_z = nullptr, *gate_gz = nullptr;   // [N, gate_ld] logits / logit gradients of the gate GEMMs (bf16 tier)
   float* gate_gw = nullptr;                     // [gate_ld, d] padded weight gradient
   int gate_ld = 0;                              // 0: the gate runs on the per-row kernels
@@ -379,9 +381,16 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     // x1 = x + o_proj(yg)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_O)), A, gxo, A, tr->g_yg, A, N, qw, d, false));
     OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.yg, A, gxo, A, tr->G(tr->P(l, P_O)), N, qw, d, false); }));
+    // the attention backward's operands, built early: when its tensor-core path will run, the gate's backward (which forms the
+    // same dot product) hands it Dr = rowsum(dO . O) and the pass over O and dO that would compute it is dropped
+    ojc_tensor at_q = TBHTD(a.qr, A, B, T, H, dh), at_k = TBHTD(a.kr, A, B, T, Hkv, dh), at_y = TBHTD(a.y, A, B, T, H, dh);
+    ojc_tensor at_v = l > 0 ? TBHTD(a.v, A, B, T, Hkv, dh) : TBHTD(a.rawv, A, B, T, Hkv, dh, skv);
+    ojc_tensor at_gy = TBHTD(tr->g_y, A, B, T, H, dh), at_gq = TBHTD(tr->g_qr, A, B, T, H, dh), at_gk = TBHTD(tr->g_kr, A, B, T, Hkv, dh), at_gv = TBHTD(tr->g_v, A, B, T, Hkv, dh);
+    const bool dr_from_gate = tr->gate_ld && tr->dr && sdpa_backward_takes_dr(be, &at_q, &at_k, &at_v, &at_y, &at_gy, &at_gq, &at_gk, &at_gv, s.window);
     if (tr->gate_ld) {
       const int ld = tr->gate_ld;
-      OJC_TRY(gate_apply_backward(be, a.scales, (const bf16*)a.y, (const bf16*)tr->g_yg, (bf16*)tr->g_y, tr->gate_gz, ld, tr->G(tr->P(l, P_GB)), N, (int)H, (int)dh));
+      OJC_TRY(gate_apply_backward(be, a.scales, (const bf16*)a.y, (const bf16*)tr->g_yg, (bf16*)tr->g_y, tr->gate_gz, ld, tr->G(tr->P(l, P_GB)), N, (int)H, (int)dh,
+                                  dr_from_gate ? tr->dr : nullptr, (int)T));
       OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_GW)), A, tr->gate_gz, A, tr->g_h, OJC_F32, N, d, ld, false));   // d/dh = gz . Wg (padding columns of gz are zero)
       OJC_TRY(on_side([&]() -> ojc_status {
         OJC_TRY(linear_backward_weight_impl(be, a.h, A, tr->gate_gz, A, tr->gate_gw, N, d, ld, false));                        // [ld, d]; rows past H are zero
@@ -394,12 +403,11 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       OJC_TRY(gate_backward_impl(be, &h, &gw, &gb, &y, &gyg, &sc, &gh, tr->G(tr->P(l, P_GW)), tr->G(tr->P(l, P_GB)), &gy, false));
     }
     {
-      ojc_tensor q = TBHTD(a.qr, A, B, T, H, dh), k = TBHTD(a.kr, A, B, T, Hkv, dh), y = TBHTD(a.y, A, B, T, H, dh);
-      ojc_tensor v = l > 0 ? TBHTD(a.v, A, B, T, Hkv, dh) : TBHTD(a.rawv, A, B, T, Hkv, dh, skv);
-      ojc_tensor gy = TBHTD(tr->g_y, A, B, T, H, dh), gq = TBHTD(tr->g_qr, A, B, T, H, dh), gk = TBHTD(tr->g_kr, A, B, T, Hkv, dh), gv = TBHTD(tr->g_v, A, B, T, Hkv, dh);
       ojc_tensor lse = T1(a.lse, OJC_F32, B * H * T);
       lse.rank = 3; lse.shape[0] = B; lse.shape[1] = H; lse.shape[2] = T; lse.stride[0] = H * T; lse.stride[1] = T; lse.stride[2] = 1;
-      OJC_TRY(ojc_causal_sdpa_backward(be, &q, &k, &v, &y, &lse, &gy, s.window, &gq, &gk, &gv));
+      bool taken = false;
+      if (dr_from_gate) OJC_TRY(sdpa_backward_with_dr(be, &at_q, &at_k, &at_v, &at_y, &lse, &at_gy, s.window, &at_gq, &at_gk, &at_gv, tr->dr, &taken));
+      if (!taken) OJC_TRY(ojc_causal_sdpa_backward(be, &at_q, &at_k, &at_v, &at_y, &lse, &at_gy, s.window, &at_gq, &at_gk, &at_gv));
     }
     const void* g_rawv = tr->g_v;
     if (fl) {
@@ -549,7 +557,7 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
     const bool per_ok = dh % 8 == 0 && (dh / 8) <= 32 && (((dh / 8) & ((dh / 8) - 1)) == 0);
     if (per_ok && d % 8 == 0 && tr->P(L - 1, P_GW).offset + ld * d <= tr->flat_n && gwp.n == H * d) {
       tr->gate_ld = (int)ld;
-      TAKE(tr->gate_z, N * ld * 2); TAKE(tr->gate_gz, N * ld * 2); TAKE(tr->gate_gw, ld * d * 4);
+      TAKE(tr->gate_z, N * ld * 2); TAKE(tr->gate_gz, N * ld * 2); TAKE(tr->gate_gw, ld * d * 4); TAKE(tr->dr, tr->B * H * tr->T * 4);
     }
   }
   TAKE(tr->cos_t, tr->T * dh * 4); TAKE(tr->sin_t, tr->T * dh * 4); TAKE(tr->ids, N * 4); TAKE(tr->targets, N * 4);
