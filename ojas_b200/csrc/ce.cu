@@ -210,7 +210,7 @@ ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const vo
   const char* op = "linear_cross_entropy_mean";
   const bool bf = x_dt == OJC_BF16 && w_dt == OJC_BF16;
   const int32_t g_dt = bf ? OJC_BF16 : OJC_F32;
-  if (chunk_rows <= 0) chunk_rows = bf ? 4096 : 1024;
+  if (chunk_rows <= 0) chunk_rows = bf ? 8192 : 1024;   // bf16 tier: 8192-row tiles measured 1% of the 124M step faster than 4096 (half the accumulating dW passes), 16384 no better
   if (chunk_rows > rows) chunk_rows = rows;
   const bool want = gx || gw;
   const int64_t ldl = (vocab + 7) & ~int64_t(7);  // keep tile rows 16-byte aligned for the tensor-core kernels
