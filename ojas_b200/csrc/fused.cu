@@ -74,7 +74,7 @@ __global__ void qk_norm_rope_forward_kernel(const bf16* __restrict__ x, int64_t 
 // Backward of the above from the saved pre-norm x: rope backward, then RMSNorm backward; dW partials per block. The same
 // thread-per-(token, part) walk over the heads; the weight-gradient terms accumulate in registers across heads and tokens.
 template <int TPR, int HL>
-__global__ void qk_norm_rope_backward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
+__global__ void __launch_bounds__(128, 4) qk_norm_rope_backward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
                                              const float* __restrict__ sin_t, const bf16* __restrict__ gy, int64_t gys, bf16* __restrict__ gx, int64_t gxs,
                                              float* __restrict__ part_out, int64_t tokens, int heads, int time, float eps) {
   constexpr int DH = 16 * TPR, HALF = 8 * TPR;
