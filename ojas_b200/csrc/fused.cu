@@ -445,7 +445,7 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
   if (rows == 0) return OJC_OK;
   return dispatch_tpr(op, dh, [&](auto tpr) {
     constexpr int TPR = decltype(tpr)::value;
-    const int hl = 1;   // the backward measured faster with each thread walking all heads of its token (45.6 vs 49.6 us at 12 x 64); the forward the other way (23.2 vs 28.7 us)
+    const int hl = 1;   // the backward measured faster with each thread walking all heads of its token (42 vs 46 us at 12 x 64); the forward the other way (23 vs 29 us)
     const int tokens_per_block = 128 / (TPR * hl);
     int64_t blocks = (tokens + tokens_per_block - 1) / tokens_per_block;
     if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
