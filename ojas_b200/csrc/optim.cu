@@ -140,6 +140,88 @@ __global__ void muon_normalize_kernel(const float* __restrict__ u_all, const flo
   }
 }
 
+// Tall matrices (rows > cols) run Newton-Schulz on the transpose: X^T[c, r] = u[r, c] / denom, and the update reads X^T back.
+// Both directions go through a 32 x 32 shared-memory tile so that reads and writes are row-contiguous on both sides.
+// grid (cols / 32, rows / 32, matrices), block (32, 8).
+template <class TX>
+__global__ void muon_normalize_tall_kernel(const float* __restrict__ u_all, const float* __restrict__ norm, TX* __restrict__ x_all, int rows, int cols, int bf16_mode) {
+  __shared__ float tile[32][33];
+  const int64_t n = (int64_t)rows * cols;
+  const float* __restrict__ u = u_all + (int64_t)blockIdx.z * n;
+  TX* __restrict__ x = x_all + (int64_t)blockIdx.z * n;
+  const float nrm = norm[blockIdx.z];
+  const float denom = bf16_mode ? round_bf16(round_bf16(nrm) + 1e-7f) : nrm + 1e-7f;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = u[(int64_t)r * cols + c] / denom;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) stf(x, (int64_t)c * rows + r, tile[threadIdx.x][j]);
+  }
+}
+template <class TX>
+__global__ void muon_apply_tall_kernel(const MuonBatch mb, const TX* __restrict__ x_all, int rows, int cols, float alpha, float decay, int decays, uint32_t* fault) {
+  __shared__ float tile[32][33];
+  const int64_t n = (int64_t)rows * cols;
+  float* __restrict__ p = mb.p[blockIdx.z];
+  bf16* __restrict__ mirror = mb.mirror[blockIdx.z];
+  const TX* __restrict__ x = x_all + (int64_t)blockIdx.z * n;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = ldf(x, (int64_t)c * rows + r);
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r >= rows || c >= cols) continue;
+    const int64_t i = (int64_t)r * cols + c;
+    const float base = decays ? p[i] * decay : p[i];
+    const float np = fmaf(alpha, tile[threadIdx.x][j], base);
+    if (!isfinite(np)) { raise_fault(fault, OP_MUON); continue; }
+    p[i] = np;
+    if (mirror) mirror[i] = __float2bfloat16_rn(np);
+  }
+}
+
+// eight bf16 values per 16-byte access for the bf16 forms below (same arithmetic and roundings as the scalar kernels)
+__device__ __forceinline__ void unpack8(const uint4& t, float (&v)[8]) {
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w[i] = (uint32_t)f32_to_bf16_bits(v[2 * i]) | ((uint32_t)f32_to_bf16_bits(v[2 * i + 1]) << 16);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__global__ void ns_combine_a_bf16x8_kernel(const uint4* __restrict__ a, uint4* __restrict__ a2, int64_t n8, float bcoef, float ccoef) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n8; i += stride) {
+    float av[8], a2v[8], r[8];
+    unpack8(a[i], av); unpack8(a2[i], a2v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r[k] = round_bf16(round_bf16(bcoef * av[k]) + round_bf16(ccoef * a2v[k]));
+    a2[i] = pack8(r);
+  }
+}
+__global__ void ns_combine_x_bf16x8_kernel(const uint4* __restrict__ x, uint4* __restrict__ bx, int64_t n8, float acoef, uint32_t* fault) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  bool bad = false;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n8; i += stride) {
+    float xv[8], bv[8], r[8];
+    unpack8(x[i], xv); unpack8(bx[i], bv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { r[k] = round_bf16(round_bf16(acoef * xv[k]) + bv[k]); bad |= !isfinite(r[k]); }
+    bx[i] = pack8(r);
+  }
+  if (bad) raise_fault(fault, OP_MUON);
+}
+
 // out = b * A + c * A2 (A2 overwritten), every scalar multiple and the sum rounded in bf16 mode (optim.rs:947-957).
 template <class T>
 __global__ void ns_combine_a_kernel(const T* __restrict__ a, T* __restrict__ a2, int64_t n, float bcoef, float ccoef, int bf16_mode) {
@@ -355,7 +437,11 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
     muon_norm_kernel<<<nb, 256, 0, be->stream>>>(part, parts, norm);
     OJC_LAUNCHED(be, op);
     const int grid = elementwise_grid(be, n, 256), grid_all = elementwise_grid(be, n * batch, 256), grid_a = elementwise_grid(be, r * r * batch, 256);
-    if (bf) muon_normalize_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, tall, 1);
+    const dim3 tgrid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), nb), tblock(32, 8);
+    const bool tiled = tall && nb <= 65535 && (rows + 31) / 32 <= 65535;
+    if (tiled && bf) muon_normalize_tall_kernel<bf16><<<tgrid, tblock, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, 1);
+    else if (tiled) muon_normalize_tall_kernel<float><<<tgrid, tblock, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, 0);
+    else if (bf) muon_normalize_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, tall, 1);
     else muon_normalize_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, tall, 0);
     OJC_LAUNCHED(be, op);
     const float a = (float)3.4445, b = (float)-4.7750, cc = (float)2.0315;  // MUON_NS5_{A,B,C}, ojas-core/src/backend.rs:144-146
@@ -377,19 +463,25 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
       OJC_TRY(product(xk, xt, am, r, r, c, n, n, r * r));                                                  // A = X X^T
       GemmOperand ak{am, dt, r, 1}, an{am, dt, r, 1};
       OJC_TRY(product(ak, an, a2, r, r, r, r * r, r * r, r * r));                                          // A2 = A A
-      if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r * batch, b, cc, 1);
+      const bool v8a = bf && (r * r * batch) % 8 == 0 && (((uintptr_t)am | (uintptr_t)a2) & 15) == 0;
+      const bool v8x = bf && (n * batch) % 8 == 0 && (((uintptr_t)x | (uintptr_t)bx) & 15) == 0;
+      if (v8a) ns_combine_a_bf16x8_kernel<<<elementwise_grid(be, r * r * batch / 8, 256), 256, 0, be->stream>>>((const uint4*)am, (uint4*)a2, r * r * batch / 8, b, cc);
+      else if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r * batch, b, cc, 1);
       else ns_combine_a_kernel<float><<<grid_a, 256, 0, be->stream>>>((const float*)am, (float*)a2, r * r * batch, b, cc, 0);
       OJC_LAUNCHED(be, op);
       GemmOperand bk{a2, dt, r, 1};
       OJC_TRY(product(bk, xn, bx, r, c, r, r * r, n, n));                                                  // BX = B X
-      if (bf) ns_combine_x_kernel<bf16><<<grid_all, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n * batch, a, 1, be->fault_dev);
+      if (v8x) ns_combine_x_bf16x8_kernel<<<elementwise_grid(be, n * batch / 8, 256), 256, 0, be->stream>>>((const uint4*)x, (uint4*)bx, n * batch / 8, a, be->fault_dev);
+      else if (bf) ns_combine_x_kernel<bf16><<<grid_all, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n * batch, a, 1, be->fault_dev);
       else ns_combine_x_kernel<float><<<grid_all, 256, 0, be->stream>>>((const float*)x, (float*)bx, n * batch, a, 0, be->fault_dev);
       OJC_LAUNCHED(be, op);
       std::swap(x, bx);
     }
     const double scale = std::sqrt(std::max(1.0, (double)rows / (double)cols));
     const float alpha = (float)(-cfg.lr * scale), decay = (float)(1.0 - cfg.lr * cfg.weight_decay);
-    if (bf) muon_apply_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    if (tiled && bf) muon_apply_tall_kernel<bf16><<<tgrid, tblock, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    else if (tiled) muon_apply_tall_kernel<float><<<tgrid, tblock, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    else if (bf) muon_apply_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     else muon_apply_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     OJC_LAUNCHED(be, op);
     return OJC_OK;
