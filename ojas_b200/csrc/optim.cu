@@ -187,6 +187,39 @@ __global__ void muon_apply_tall_kernel(const MuonBatch mb, const TX* __restrict_
   }
 }
 
+// Wide matrices in bf16 mode, four elements per thread (n % 4 == 0): the same arithmetic as the scalar kernels.
+__global__ void muon_normalize_bf16x4_kernel(const float* __restrict__ u_all, const float* __restrict__ norm, bf16* __restrict__ x_all, int64_t n) {
+  const float4* __restrict__ u = reinterpret_cast<const float4*>(u_all + (int64_t)blockIdx.y * n);
+  uint2* __restrict__ x = reinterpret_cast<uint2*>(x_all + (int64_t)blockIdx.y * n);
+  const float nrm = norm[blockIdx.y];
+  const float denom = round_bf16(round_bf16(nrm) + 1e-7f);
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n / 4; i += stride) {
+    const float4 v = u[i];
+    x[i] = make_uint2((uint32_t)f32_to_bf16_bits(v.x / denom) | ((uint32_t)f32_to_bf16_bits(v.y / denom) << 16),
+                      (uint32_t)f32_to_bf16_bits(v.z / denom) | ((uint32_t)f32_to_bf16_bits(v.w / denom) << 16));
+  }
+}
+__global__ void muon_apply_bf16x4_kernel(const MuonBatch mb, const bf16* __restrict__ x_all, int64_t n, float alpha, float decay, int decays, uint32_t* fault) {
+  float4* __restrict__ p = reinterpret_cast<float4*>(mb.p[blockIdx.y]);
+  uint2* __restrict__ mirror = reinterpret_cast<uint2*>(mb.mirror[blockIdx.y]);
+  const uint2* __restrict__ x = reinterpret_cast<const uint2*>(x_all + (int64_t)blockIdx.y * n);
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n / 4; i += stride) {
+    const uint2 xv = x[i];
+    const float o[4] = {__uint_as_float(xv.x << 16), __uint_as_float(xv.x & 0xffff0000u), __uint_as_float(xv.y << 16), __uint_as_float(xv.y & 0xffff0000u)};
+    float4 pv = p[i];
+    float np[4] = {pv.x, pv.y, pv.z, pv.w};
+    bool bad = false;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { np[k] = fmaf(alpha, o[k], decays ? np[k] * decay : np[k]); bad |= !isfinite(np[k]); }
+    if (bad) { raise_fault(fault, OP_MUON); continue; }   // as the scalar kernel: a non-finite update is not stored
+    p[i] = make_float4(np[0], np[1], np[2], np[3]);
+    if (mirror) mirror[i] = make_uint2((uint32_t)f32_to_bf16_bits(np[0]) | ((uint32_t)f32_to_bf16_bits(np[1]) << 16),
+                                       (uint32_t)f32_to_bf16_bits(np[2]) | ((uint32_t)f32_to_bf16_bits(np[3]) << 16));
+  }
+}
+
 // eight bf16 values per 16-byte access for the bf16 forms below (same arithmetic and roundings as the scalar kernels)
 __device__ __forceinline__ void unpack8(const uint4& t, float (&v)[8]) {
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
@@ -437,10 +470,13 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
     muon_norm_kernel<<<nb, 256, 0, be->stream>>>(part, parts, norm);
     OJC_LAUNCHED(be, op);
     const int grid = elementwise_grid(be, n, 256), grid_all = elementwise_grid(be, n * batch, 256), grid_a = elementwise_grid(be, r * r * batch, 256);
+    bool mirrors_aligned = ((uintptr_t)u & 15) == 0 && ((uintptr_t)x & 7) == 0;
+    for (int64_t i = 0; i < batch; ++i) mirrors_aligned = mirrors_aligned && ((uintptr_t)mb.p[i] & 15) == 0 && ((uintptr_t)mb.mirror[i] & 7) == 0;
     const dim3 tgrid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), nb), tblock(32, 8);
     const bool tiled = tall && nb <= 65535 && (rows + 31) / 32 <= 65535;
     if (tiled && bf) muon_normalize_tall_kernel<bf16><<<tgrid, tblock, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, 1);
     else if (tiled) muon_normalize_tall_kernel<float><<<tgrid, tblock, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, 0);
+    else if (bf && !tall && n % 4 == 0 && mirrors_aligned) muon_normalize_bf16x4_kernel<<<dim3(elementwise_grid(be, n / 4, 256), nb), 256, 0, be->stream>>>(u, norm, (bf16*)x, n);
     else if (bf) muon_normalize_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (bf16*)x, (int)rows, (int)cols, tall, 1);
     else muon_normalize_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(u, norm, (float*)x, (int)rows, (int)cols, tall, 0);
     OJC_LAUNCHED(be, op);
@@ -481,6 +517,7 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
     const float alpha = (float)(-cfg.lr * scale), decay = (float)(1.0 - cfg.lr * cfg.weight_decay);
     if (tiled && bf) muon_apply_tall_kernel<bf16><<<tgrid, tblock, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     else if (tiled) muon_apply_tall_kernel<float><<<tgrid, tblock, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    else if (bf && !tall && n % 4 == 0 && mirrors_aligned) muon_apply_bf16x4_kernel<<<dim3(elementwise_grid(be, n / 4, 256), nb), 256, 0, be->stream>>>(mb, (const bf16*)x, n, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     else if (bf) muon_apply_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     else muon_apply_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
     OJC_LAUNCHED(be, op);
