@@ -23,5 +23,11 @@ ojc_status gemm_auto(ojc_backend* be, const char* op, const GemmOperand& a, cons
                      int64_t n, int64_t k, float alpha, bool accumulate, const float* residual);
 // `batch` independent products of one shape on the tensor-core kernels: matrix i of A / B / C starts a_bs / b_bs / c_bs elements
 // after matrix i - 1 (the operand views describe matrix 0). No residual operand; at least 64 output columns.
+// An optional epilogue for the Newton-Schulz products in bf16 mode: C = bf16(bf16(src_mul * src) + bf16(acc_mul * bf16(A.B))), with `src`
+// a bf16 matrix of C's shape (leading dimension src_ld, matrix stride src_bs). It is the combine step the iteration would otherwise run
+// as a kernel of its own after the product, with the same rounding points (ojas-cpu/src/optim.rs:947-974). Needs a bf16 output,
+// alpha 1, no accumulation or split, src_ld % 8 == 0 and a 16-byte aligned src; a non-finite result raises the Muon fault.
+struct NsCombine { const void* src; int64_t src_ld, src_bs; float src_mul, acc_mul; };
 ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
-                           int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual);
+                           int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual,
+                           const NsCombine* combine = nullptr);

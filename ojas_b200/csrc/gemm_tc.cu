@@ -54,6 +54,7 @@ struct TcArgs {
   uint32_t* fault;
   int batch;                // independent matrices: a unit is (matrix, tile, split); batch > 1 needs tma_store and splits == 1
   int tma_store;            // finished blocks leave through TMA tile stores (no residual operand; split partials need m % 32 == 0)
+  const bf16* ns_src; int64_t ns_ld, ns_bs; float ns_src_mul, ns_acc_mul;   // Newton-Schulz combine epilogue (NsCombine); ns_src null: none
   int tiles_n_fast;         // tile order: 1 = neighbouring CTAs share an A row block (few column tiles), 0 = they share a B column block
 };
 
@@ -91,7 +92,37 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
       __syncwarp();
       uint8_t* rowp = stage_bytes + lane * 128;
       const float al = args.splits > 1 ? 1.0f : args.alpha;
-      if (bf) {
+      if (bf && args.ns_src) {
+        // C = bf16(bf16(src_mul * src) + bf16(acc_mul * bf16(acc))): this lane's row, 64 columns from c0
+        const int grow = row_base + lane, gcol = col_tile0 + c0;
+        const bf16* srow = args.ns_src + (int64_t)bz * args.ns_bs + (int64_t)grow * args.ns_ld + gcol;
+        const bool whole = grow < args.m && gcol + 64 <= args.n;
+        auto rb = [](float x) { return __uint_as_float(pack2_bf16(0.0f, x) & 0xffff0000u); };
+        bool bad = false;
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) {
+          const uint32_t* v = ci < 4 ? &r[ci * 8] : &r2[(ci - 4) * 8];
+          float sv[8];
+          if (whole) {
+            const uint4 t = *reinterpret_cast<const uint4*>(srow + ci * 8);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { sv[2 * e] = __uint_as_float(w[e] << 16); sv[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[e] = (grow < args.m && gcol + ci * 8 + e < args.n) ? __bfloat162float(srow[ci * 8 + e]) : 0.0f;
+          }
+          float o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            o[e] = rb(rb(args.ns_src_mul * sv[e]) + rb(args.ns_acc_mul * rb(__uint_as_float(v[e]))));
+            bad |= !isfinite(o[e]);
+          }
+          *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+              make_uint4(pack2_bf16(o[0], o[1]), pack2_bf16(o[2], o[3]), pack2_bf16(o[4], o[5]), pack2_bf16(o[6], o[7]));
+        }
+        if (bad && grow < args.m) raise_fault(args.fault, OP_MUON);
+      } else if (bf) {
 #pragma unroll
         for (int ci = 0; ci < 8; ++ci) {
           const uint32_t* v = ci < 4 ? &r[ci * 8] : &r2[(ci - 4) * 8];
@@ -498,8 +529,11 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
 
 // `batch` independent products of the same shape; matrix i of A / B / C starts a_bs / b_bs / c_bs elements after matrix i - 1.
 ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
-                           int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual) {
+                           int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual,
+                           const NsCombine* combine) {
   if (!gemm_tc_eligible(a, b, c, c_dtype, ldc, m, n, k)) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "operands break the tensor-core kernel's alignment rules");
+  if (combine && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine->src_ld % 8 != 0 || combine->src_bs % 8 != 0 || ((uintptr_t)combine->src & 15) != 0 || n < 64))
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the combine epilogue needs a bf16 output, alpha 1, no accumulation and an aligned source");
   if (accumulate && c_dtype != OJC_F32) return ojc_fail(OJC_ERR_DTYPE, op, "accumulation needs an F32 output");
   if (batch < 1 || batch > 65535) return ojc_fail(OJC_ERR_SHAPE, op, "batch count out of range");
   if (batch > 1 && (a_bs % 8 != 0 || b_bs % 8 != 0 || c_bs % 8 != 0 || residual || n < 64))
@@ -537,7 +571,7 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   // the wave efficiency its units reach plus the partial round trip through memory, and take the cheapest (each split
   // keeps at least 8 k-blocks).
   int splits = 1;
-  if (kblocks >= 16 && batch == 1) {
+  if (kblocks >= 16 && batch == 1 && !combine) {
     const double flops = 2.0 * (double)m * (double)n * (double)k;
     double best = 1e30;
     for (int sp = 1; sp <= 16 && kblocks / sp >= 8; ++sp) {
@@ -555,6 +589,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   args.a_mn_major = amn; args.b_mn_major = bmn;
   args.alpha = alpha; args.accumulate = accumulate ? 1 : 0; args.residual = residual;
   args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev; args.batch = (int)batch;
+  args.ns_src = combine ? (const bf16*)combine->src : nullptr; args.ns_ld = combine ? combine->src_ld : 0; args.ns_bs = combine ? combine->src_bs : 0;
+  args.ns_src_mul = combine ? combine->src_mul : 0.0f; args.ns_acc_mul = combine ? combine->acc_mul : 0.0f;
   if (splits > 1) {
     void* ws = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)splits * m * n * 4, &ws));

@@ -453,9 +453,15 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
   float* norm = (float*)cur;
   ojc_status st = OJC_OK;
   // C_i = A_i . B_i for every matrix of the group
-  auto product = [&](const GemmOperand& ga, const GemmOperand& gb, void* cptr, int64_t m_, int64_t n_, int64_t k_, int64_t a_bs, int64_t b_bs, int64_t c_bs) -> ojc_status {
-    if (batch > 1 && bf && n_ >= 64 && a_bs % 8 == 0 && b_bs % 8 == 0 && c_bs % 8 == 0 && gemm_tc_eligible(ga, gb, cptr, dt, n_, m_, n_, k_))
-      return gemm_tc_batched(be, op, ga, gb, cptr, dt, n_, m_, n_, k_, batch, a_bs, b_bs, c_bs, 1.0f, false, nullptr);
+  // `comb`: the combine that follows this product; *fused says whether the product's epilogue did it (tensor-core path only)
+  auto product = [&](const GemmOperand& ga, const GemmOperand& gb, void* cptr, int64_t m_, int64_t n_, int64_t k_, int64_t a_bs, int64_t b_bs, int64_t c_bs,
+                     const NsCombine* comb = nullptr, bool* fused = nullptr) -> ojc_status {
+    if (fused) *fused = false;
+    if (batch > 1 && bf && n_ >= 64 && a_bs % 8 == 0 && b_bs % 8 == 0 && c_bs % 8 == 0 && gemm_tc_eligible(ga, gb, cptr, dt, n_, m_, n_, k_)) {
+      const bool can = comb && comb->src_ld % 8 == 0 && comb->src_bs % 8 == 0 && ((uintptr_t)comb->src & 15) == 0;
+      if (fused) *fused = can;
+      return gemm_tc_batched(be, op, ga, gb, cptr, dt, n_, m_, n_, k_, batch, a_bs, b_bs, c_bs, 1.0f, false, nullptr, can ? comb : nullptr);
+    }
     for (int64_t i = 0; i < batch; ++i) {
       GemmOperand ai{(const char*)ga.ptr + i * a_bs * es, ga.dtype, ga.rs, ga.cs}, bi{(const char*)gb.ptr + i * b_bs * es, gb.dtype, gb.rs, gb.cs};
       OJC_TRY(gemm_auto(be, op, ai, bi, (char*)cptr + i * c_bs * es, dt, n_, m_, n_, k_, 1.0f, false, nullptr));
@@ -498,19 +504,26 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
       GemmOperand xk{x, dt, c, 1}, xt{x, dt, 1, c}, xn{x, dt, c, 1};
       OJC_TRY(product(xk, xt, am, r, r, c, n, n, r * r));                                                  // A = X X^T
       GemmOperand ak{am, dt, r, 1}, an{am, dt, r, 1};
-      OJC_TRY(product(ak, an, a2, r, r, r, r * r, r * r, r * r));                                          // A2 = A A
-      const bool v8a = bf && (r * r * batch) % 8 == 0 && (((uintptr_t)am | (uintptr_t)a2) & 15) == 0;
-      const bool v8x = bf && (n * batch) % 8 == 0 && (((uintptr_t)x | (uintptr_t)bx) & 15) == 0;
-      if (v8a) ns_combine_a_bf16x8_kernel<<<elementwise_grid(be, r * r * batch / 8, 256), 256, 0, be->stream>>>((const uint4*)am, (uint4*)a2, r * r * batch / 8, b, cc);
-      else if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r * batch, b, cc, 1);
-      else ns_combine_a_kernel<float><<<grid_a, 256, 0, be->stream>>>((const float*)am, (float*)a2, r * r * batch, b, cc, 0);
-      OJC_LAUNCHED(be, op);
+      bool fused_a = false, fused_x = false;
+      const NsCombine comb_a{am, r, r * r, b, cc};                                                          // B = b A + c (A A)
+      OJC_TRY(product(ak, an, a2, r, r, r, r * r, r * r, r * r, bf ? &comb_a : nullptr, &fused_a));           // A2 = A A (-> B in the epilogue)
+      if (!fused_a) {
+        const bool v8a = bf && (r * r * batch) % 8 == 0 && (((uintptr_t)am | (uintptr_t)a2) & 15) == 0;
+        if (v8a) ns_combine_a_bf16x8_kernel<<<elementwise_grid(be, r * r * batch / 8, 256), 256, 0, be->stream>>>((const uint4*)am, (uint4*)a2, r * r * batch / 8, b, cc);
+        else if (bf) ns_combine_a_kernel<bf16><<<grid_a, 256, 0, be->stream>>>((const bf16*)am, (bf16*)a2, r * r * batch, b, cc, 1);
+        else ns_combine_a_kernel<float><<<grid_a, 256, 0, be->stream>>>((const float*)am, (float*)a2, r * r * batch, b, cc, 0);
+        OJC_LAUNCHED(be, op);
+      }
       GemmOperand bk{a2, dt, r, 1};
-      OJC_TRY(product(bk, xn, bx, r, c, r, r * r, n, n));                                                  // BX = B X
-      if (v8x) ns_combine_x_bf16x8_kernel<<<elementwise_grid(be, n * batch / 8, 256), 256, 0, be->stream>>>((const uint4*)x, (uint4*)bx, n * batch / 8, a, be->fault_dev);
-      else if (bf) ns_combine_x_kernel<bf16><<<grid_all, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n * batch, a, 1, be->fault_dev);
-      else ns_combine_x_kernel<float><<<grid_all, 256, 0, be->stream>>>((const float*)x, (float*)bx, n * batch, a, 0, be->fault_dev);
-      OJC_LAUNCHED(be, op);
+      const NsCombine comb_x{x, c, n, a, 1.0f};                                                             // X <- a X + B X
+      OJC_TRY(product(bk, xn, bx, r, c, r, r * r, n, n, bf ? &comb_x : nullptr, &fused_x));                   // BX = B X (-> the new X in the epilogue)
+      if (!fused_x) {
+        const bool v8x = bf && (n * batch) % 8 == 0 && (((uintptr_t)x | (uintptr_t)bx) & 15) == 0;
+        if (v8x) ns_combine_x_bf16x8_kernel<<<elementwise_grid(be, n * batch / 8, 256), 256, 0, be->stream>>>((const uint4*)x, (uint4*)bx, n * batch / 8, a, be->fault_dev);
+        else if (bf) ns_combine_x_kernel<bf16><<<grid_all, 256, 0, be->stream>>>((const bf16*)x, (bf16*)bx, n * batch, a, 1, be->fault_dev);
+        else ns_combine_x_kernel<float><<<grid_all, 256, 0, be->stream>>>((const float*)x, (float*)bx, n * batch, a, 0, be->fault_dev);
+        OJC_LAUNCHED(be, op);
+      }
       std::swap(x, bx);
     }
     const double scale = std::sqrt(std::max(1.0, (double)rows / (double)cols));
