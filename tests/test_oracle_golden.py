@@ -113,3 +113,14 @@ def test_exp_exact_pins(golden_dir):
     assert np.array_equal(got, want)
     assert orc.exp_exact(0.0) == 1.0 and orc.exp_exact(float("inf")) == float("inf") and orc.exp_exact(-1e9) == 0.0
     assert np.isnan(orc.exp_exact(float("nan")))
+
+
+def test_rms_norm_f64_fixture():
+    """ojas-oracle/fixtures/rms_norm_f64.json: one row against the f64 formula x * w / sqrt(mean(x^2) + eps), eps 1e-6."""
+    x = np.array([[0.5, -1.25, 0.75, 2.0]], np.float32)
+    w = np.array([1.0, 0.5, -1.0, 1.5], np.float32)
+    want = np.array([0.39605889293691887, -0.4950736161711486, -0.5940883394053783, 2.3763533576215132])
+    got = orc.rms_norm_forward(x, w, 1e-6)
+    assert np.abs(got[0].astype(np.float64) - want).max() <= 2e-7
+    ref = x[0].astype(np.float64) * w / np.sqrt(np.mean(x[0].astype(np.float64) ** 2) + 1e-6)
+    assert np.abs(ref - want).max() <= 1e-15
