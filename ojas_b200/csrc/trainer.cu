@@ -65,7 +65,7 @@ struct ojc_trainer {
   std::vector<LayerActs> acts;
   std::vector<void*> owned;
   float *cos_t = nullptr, *sin_t = nullptr, *x_final = nullptr, *gx = nullptr, *g_h = nullptr, *g_h2 = nullptr, *gv0_acc = nullptr, *stats = nullptr;
-  void *hf = nullptr, *gx_b = nullptr, *g_m = nullptr, *g_a = nullptr, *g_u = nullptr, *g_yg = nullptr, *g_y = nullptr, *g_qr = nullptr, *g_kr = nullptr,
+  void *hf = nullptr, *gx_b = nullptr, *gx_b2 = nullptr, *g_m = nullptr, *g_a = nullptr, *g_u = nullptr, *g_yg = nullptr, *g_y = nullptr, *g_qr = nullptr, *g_kr = nullptr,
        *g_v = nullptr, *g_qn = nullptr, *g_kn = nullptr, *g_q = nullptr, *g_k = nullptr, *g_rawv = nullptr, *g_v0l = nullptr, *qn = nullptr, *kn = nullptr;
   uint32_t *ids = nullptr, *targets = nullptr;
   float* dr = nullptr;                          // [B, H, T] rowsum(dO . O): written by the gate's backward, read by the attention backward
@@ -307,6 +307,9 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   }
   OJC_TRY(record_ready(tr, (int)tr->params.size() - 1));
   // the residual gradient as a matmul operand: f32 in the f32 tier, the bf16 copy the norm backward kernels write under autocast
+  // Under autocast the bf16 copy alternates between two buffers: the one the block's second norm writes (read by the output
+  // projection's gradients) and the one the first norm writes (read by the next block's down-projection gradients), so the
+  // weight gradients still running on the side lane never read a buffer the main stream is about to rewrite mid-block.
   const void* gxo = bf ? tr->gx_b : (void*)tr->gx;
   bool have_v0 = false;
   // fn's inputs are final on the main stream now; run it on the side lane (or in place when there is none)
@@ -358,6 +361,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     else if ((N * F) % 4 == 0) OJC_TRY(swiglu_backward_impl(be, a.a, a.u, tr->g_m, tr->g_a, tr->g_u, A, N * F));
     else {
       ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), gm = T1(tr->g_m, A, N * F), ga = T1(tr->g_a, A, N * F), gu = T1(tr->g_u, A, N * F);
+      OJC_TRY(join_side());                // the down-projection's weight gradient on the side lane still reads m
       ojc_tensor sil = T1(a.m, A, N * F);  // silu(a) recomputed into the slot of m, which is no longer needed
       OJC_TRY(ojc_silu_forward(be, &ta, &sil));
       OJC_TRY(ojc_mul_backward(be, &sil, &tu, &gm, &ga, &gu));  // ga = g_silu for now
@@ -375,8 +379,8 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     {
       ojc_tensor x1 = T2(a.x1, OJC_F32, N, d), n2 = T1(tr->W(tr->P(l, P_NORM2)), OJC_F32, d), gy = T2(tr->g_h2, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
       ojc_tensor gn2 = T1(tr->G(tr->P(l, P_NORM2)), OJC_F32, d);
-      OJC_TRY(join_side());   // the down-projection's weight gradient still reads the bf16 residual gradient this rewrites
-      OJC_TRY(rms_backward_impl(be, &x1, &n2, &gy, eps, &gx, &gn2, false, true, bf ? (bf16*)tr->gx_b : nullptr));  // gx now holds d/dx1
+      OJC_TRY(rms_backward_impl(be, &x1, &n2, &gy, eps, &gx, &gn2, false, true, bf ? (bf16*)tr->gx_b2 : nullptr));  // gx now holds d/dx1
+      if (bf) gxo = tr->gx_b2;
     }
     // x1 = x + o_proj(yg)
     OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_O)), A, gxo, A, tr->g_yg, A, N, qw, d, false));
@@ -466,6 +470,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       ojc_tensor gn1 = T1(tr->G(tr->P(l, P_NORM1)), OJC_F32, d);
       OJC_TRY(join_side());   // every weight gradient of this layer is in: the buffers the lane read may be rewritten, the bucket events may fire
       OJC_TRY(rms_backward_impl(be, &x, &n1, &gy, eps, &gx, &gn1, false, true, bf ? (bf16*)tr->gx_b : nullptr));
+      if (bf) gxo = tr->gx_b;
     }
     if (l == 0 && s.n_layer > 0) OJC_TRY(ojc_fill_zero(be, tr->G(tr->P(0, P_LAMBDA)), 4));  // layer 0's lambda never trains (names.rs:262-268)
     OJC_TRY(ready(1 + (int)l * P_PER_BLOCK));
@@ -540,7 +545,7 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
     TAKE(a.y, N * qw * es); TAKE(a.yg, N * qw * es); TAKE(a.h2, N * d * es); TAKE(a.m, N * F * es);
   }
   TAKE(tr->x_final, N * d * 4); TAKE(tr->gx, N * d * 4); TAKE(tr->g_h, N * d * 4); TAKE(tr->g_h2, N * d * 4); TAKE(tr->gv0_acc, N * kvw * 4); TAKE(tr->stats, 256);
-  TAKE(tr->hf, N * d * es); TAKE(tr->gx_b, N * d * 2); TAKE(tr->g_m, N * F * es);
+  TAKE(tr->hf, N * d * es); TAKE(tr->gx_b, N * d * 2); TAKE(tr->gx_b2, N * d * 2); TAKE(tr->g_m, N * F * es);
   TAKE(tr->g_yg, N * qw * es); TAKE(tr->g_y, N * qw * es); TAKE(tr->g_qr, N * qw * es); TAKE(tr->g_kr, N * kvw * es); TAKE(tr->g_v, N * kvw * es);
   if (fl) {
     TAKE(tr->g_a, N * tr->ld_au * es); tr->g_u = (bf16*)tr->g_a + F;
