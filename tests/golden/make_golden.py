@@ -1,7 +1,7 @@
 """Collects the reference's own golden vectors for the training-step path into tests/golden/.
 
 Run once where the reference checkout is mounted (it is not present where the
-GPU tests run):  python tests/golden/make_golden.py /root/reference
+GPU tests run):  python tests/golden/make_golden.py <path to the ojas checkout>
 
 Sources (all are test data of the reference, not code):
   ojas-cpu/tests/exact_golden.rs:206-276      FNV-1a digests of Exact outputs -> exact_golden_digests.json
@@ -40,7 +40,9 @@ def torch_ref(ref: Path) -> None:
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the ojas checkout>")
+    ref = Path(sys.argv[1])
     digests(ref)
     shutil.copyfile(ref / "ojas-core/src/exp_exact_pins.txt", HERE / "exp_exact_pins.txt")
     (HERE / "tiny").mkdir(exist_ok=True)
