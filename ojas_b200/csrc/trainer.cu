@@ -79,6 +79,10 @@ struct ojc_trainer {
   int64_t ld_qkv = 0, ld_au = 0;
   uint64_t step = 0;
   bool poisoned = false, grads_ready = false;
+  // One-call steps with AdamW on every tensor and no clipping: a block's parameters are stepped on the side lane as soon as its
+  // gradients are final, under the rest of backward (nothing later reads them); apply() then skips [eager_begin, eager_end).
+  bool eager_request = false;
+  int64_t eager_begin = 0, eager_end = 0;
   // Weight gradients (their GEMMs, split-K sums and copies) run on a second stream with its own workspace while the main
   // stream walks on through the dX chain: nothing downstream reads them before the optimizer.
   cudaStream_t side_stream = nullptr;
@@ -314,6 +318,8 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   bool have_v0 = false;
   // fn's inputs are final on the main stream now; run it on the side lane (or in place when there is none)
   const bool lane = bf && tr->side_stream != nullptr && tr->side_enabled;
+  const bool eager = lane && tr->eager_request && tr->cfg.optimizer == 0 && !(tr->cfg.grad_clip > 0.0f) && L > 0;
+  tr->eager_begin = tr->eager_end = eager ? tr->params.back().offset : 0;   // grows downwards block by block
   auto on_side = [&](auto&& fn) -> ojc_status {
     if (!lane) return fn();
     OJC_CUDA(be, cudaEventRecord(tr->ev_main, be->stream), "side_lane");
@@ -474,6 +480,27 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     }
     if (l == 0 && s.n_layer > 0) OJC_TRY(ojc_fill_zero(be, tr->G(tr->P(0, P_LAMBDA)), 4));  // layer 0's lambda never trains (names.rs:262-268)
     OJC_TRY(ready(1 + (int)l * P_PER_BLOCK));
+    if (eager) {
+      // this block's slots [begin, end) of the flat buffers; a frozen parameter (block 0's lambda) is stepped around
+      const int first = 1 + (int)l * P_PER_BLOCK;
+      const int64_t end = tr->params[first + P_PER_BLOCK].offset;
+      int64_t begin = tr->params[first].offset;
+      const ojc_adamw_config ac{tr->cfg.adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.adam_weight_decay};
+      OJC_TRY(on_side([&]() -> ojc_status {
+        auto run_range = [&](int64_t b0, int64_t b1) -> ojc_status {
+          if (b1 <= b0) return OJC_OK;
+          return adamw_device(be, tr->w + b0, tr->g + b0, tr->m1 + b0, tr->m2 + b0, tr->mirror ? tr->mirror + b0 : nullptr, b1 - b0, tr->step, ac, nullptr);
+        };
+        for (int i = first; i < first + P_PER_BLOCK; ++i) {
+          const Param& q = tr->params[i];
+          if (q.trains) continue;
+          OJC_TRY(run_range(begin, q.offset));
+          begin = tr->params[i + 1].offset;
+        }
+        return run_range(begin, end);
+      }));
+      tr->eager_begin = tr->params[first].offset;
+    }
   }
   OJC_TRY(embedding_backward_impl(be, ids_dev, tr->gx, OJC_F32, tr->G(tok), N, V, d, true));
   OJC_TRY(join_side());   // the last finishing reductions: every gradient is final on the main stream from here
@@ -739,7 +766,7 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
     std::vector<std::pair<std::pair<int64_t, int64_t>, std::vector<const Param*>>> muon_groups;
     for (const Param& p : tr->params) {
       const int64_t slot_end = p.offset + ((p.n + 63) & ~int64_t(63));
-      if (!p.trains) { OJC_TRY(flush()); continue; }
+      if (!p.trains || (p.offset >= tr->eager_begin && p.offset < tr->eager_end)) { OJC_TRY(flush()); continue; }   // frozen, or stepped during backward
       if (tr->cfg.optimizer == 1 && p.group == GROUP_MUON) {
         OJC_TRY(flush());
         const std::pair<int64_t, int64_t> shape{p.shape[0], p.shape[1]};
@@ -772,6 +799,7 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
   if (st != OJC_OK) { tr->poisoned = true; return st; }
   tr->step += 1;
   tr->grads_ready = false;
+  tr->eager_begin = tr->eager_end = 0;
   if (grad_norm_out) {
     st = ojc_download(be, grad_norm_out, tr->stats + 1, 4);
     if (st != OJC_OK) tr->poisoned = true;
@@ -794,13 +822,19 @@ ojc_status ojc_trainer_finish(ojc_trainer* tr, ojc_step_report* report) {
 }
 
 ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev, ojc_step_report* report) {
-  OJC_TRY(ojc_trainer_gradients_device(tr, ids_dev, targets_dev));
+  if (tr) tr->eager_request = true;        // gradients and apply in one call: the optimizer may start during backward
+  ojc_status st = ojc_trainer_gradients_device(tr, ids_dev, targets_dev);
+  if (tr) tr->eager_request = false;
+  if (st != OJC_OK) { if (tr && tr->eager_end > tr->eager_begin) tr->poisoned = true; return st; }
   OJC_TRY(ojc_trainer_apply(tr, nullptr));
   return finish_step(tr, report);
 }
 
 ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, ojc_step_report* report) {
-  OJC_TRY(ojc_trainer_gradients(tr, ids_host, targets_host, nullptr));
+  if (tr) tr->eager_request = true;
+  ojc_status st = ojc_trainer_gradients(tr, ids_host, targets_host, nullptr);
+  if (tr) tr->eager_request = false;
+  if (st != OJC_OK) { if (tr && tr->eager_end > tr->eager_begin) tr->poisoned = true; return st; }
   OJC_TRY(ojc_trainer_apply(tr, nullptr));
   return finish_step(tr, report);
 }
