@@ -469,3 +469,90 @@ def forward_loss(spec: Spec, params, ids, targets, ignore=None, seed=1.0, want_g
 
 def set_threads(n: int) -> None:
     os.environ["OMP_NUM_THREADS"] = str(n)
+
+
+# ------------------------------------------------------------------ trainer (host logic of one optimizer step)
+COSINE_FLOOR_FRAC = 0.1          # ojas-cpu/src/schedule.rs:27
+MUON_MOMENTUM, MUON_WEIGHT_DECAY, ADAM_HYBRID_WEIGHT_DECAY = 0.99, 0.1, 0.0   # ojas-cpu/src/train.rs:31-37
+MAX_CONSECUTIVE_SKIPS = 8        # ojas-model/src/trainer.rs:81
+
+
+def lr_multiplier(schedule: str, warmup: int, total: int, step: int, decay_frac: float = 0.2) -> float:
+    """LrSchedule::multiplier (ojas-cpu/src/schedule.rs:66-90 cosine, 163-199 wsd): every line an f64 operation in the
+    reference's order. A step past `total` is refused by wsd and clamped by cosine."""
+    import math
+    if step < warmup:
+        return (float(step) + 1.0) / float(warmup)
+    if schedule == "cosine":
+        span = float(total) - float(warmup)
+        denom = 1.0 if span < 1.0 else span
+        t = min(max((float(step) - float(warmup)) / denom, 0.0), 1.0)
+        return COSINE_FLOOR_FRAC + (1.0 - COSINE_FLOOR_FRAC) * 0.5 * (1.0 + math.cos(math.pi * t))
+    if schedule == "wsd":
+        if step > total:
+            raise OracleError("wsd_schedule", 3)
+        decay_steps = int(decay_frac * float(total))
+        decay_start = total - decay_steps
+        if step < decay_start:
+            return 1.0
+        frac = float(step - decay_start) / float(max(decay_steps, 1))
+        return COSINE_FLOOR_FRAC + (1.0 - COSINE_FLOOR_FRAC) * (1.0 - frac)
+    raise ValueError(schedule)
+
+
+def micro_weights(counts):
+    """MicroWeights::new (ojas-model/src/trainer.rs:1083-1119): (f32 weights, uniform, run). No valid target at all is NonFinite."""
+    total = sum(counts)
+    live = [n for n in counts if n > 0]
+    if not live:
+        raise OracleError("Trainer::step", 4)
+    run, first = len(live), live[0]
+    uniform = all(n == 0 or n == first for n in counts)
+    weights = [np.float32(0.0) if n == 0 else (np.float32(1.0) / np.float32(run) if uniform else np.float32(float(n) / float(total))) for n in counts]
+    return weights, uniform, run
+
+
+class TrainerOracle:
+    """Trainer::run (ojas-model/src/trainer.rs:754-1046) on the CPU oracle: K micro-batches seeded by MicroWeights, gradients
+    summed in f32 in micro-batch order, global-norm clip, then per slot Muon NS5 (rank-2 hidden weights) or AdamW without decay
+    (embedding, vectors) at the schedule's learning rates; a non-finite norm leaves everything unchanged."""
+
+    def __init__(self, spec: Spec, params, schedule=("cosine", 0, 1), matrix_lr=0.025, adam_lr=6e-4, grad_clip=1.0, ns5_bf16=False,
+                 muon_momentum=MUON_MOMENTUM, ignore=None):
+        self.spec, self.table = spec, param_table(spec)
+        self.params = [np.array(p, np.float32, copy=True) for p in params]
+        self.schedule, self.matrix_lr, self.adam_lr, self.grad_clip = schedule, matrix_lr, adam_lr, grad_clip
+        self.ns5_bf16, self.muon_momentum, self.ignore = ns5_bf16, muon_momentum, ignore
+        self.m = [np.zeros_like(p) for p in self.params]
+        self.v = [np.zeros_like(p) for p in self.params]
+        self.step = 0
+
+    def run(self, batches):
+        """batches: [(x [B, T], y [B, T])]; returns (loss, grad_norm, lr_multiplier)."""
+        kind, warmup, total = self.schedule[:3]
+        mult = lr_multiplier(kind, warmup, total, self.step, *self.schedule[3:])
+        counts = [int(np.count_nonzero(_u(y) != self.ignore)) if self.ignore is not None else int(np.asarray(y).size) for _, y in batches]
+        weights, uniform, run = micro_weights(counts)
+        acc, loss_sum = None, None
+        for (x, y), w in zip(batches, weights):
+            if w == 0.0:
+                continue
+            loss, grads, _ = forward_loss(self.spec, self.params, x, y, ignore=self.ignore, seed=float(w))
+            acc = grads if acc is None else [(a + g).astype(np.float32) for a, g in zip(acc, grads)]
+            lv = np.float32(loss) if uniform or w == 1.0 else np.float32(np.float32(loss) * w)
+            loss_sum = lv if loss_sum is None else np.float32(loss_sum + lv)
+        train = [i for i, info in enumerate(self.table) if info.trains]
+        flat = [np.ascontiguousarray(acc[i]) for i in train]
+        norm = clip_grad_norm(flat, self.grad_clip)
+        if not np.isfinite(norm):
+            raise OracleError("clip_grad_norm", 4)
+        for i, g in zip(train, flat):
+            info, p = self.table[i], self.params[i]
+            if info.group == 1:
+                muon_ns5_step(p, g.reshape(p.shape), self.m[i], lr=self.matrix_lr * mult, momentum=self.muon_momentum, weight_decay=MUON_WEIGHT_DECAY,
+                              bf16=self.ns5_bf16)
+            else:
+                adamw_step(p.reshape(-1), g.ravel(), self.m[i].reshape(-1), self.v[i].reshape(-1), self.step, self.adam_lr * mult, weight_decay=ADAM_HYBRID_WEIGHT_DECAY)
+        self.step += 1
+        loss = np.float32(loss_sum / np.float32(run)) if uniform else loss_sum
+        return float(loss), float(norm), mult

@@ -7,6 +7,8 @@ Sources (all are test data of the reference, not code):
   ojas-cpu/tests/exact_golden.rs:206-276      FNV-1a digests of Exact outputs -> exact_golden_digests.json
   ojas-core/src/exp_exact_pins.txt            correctly rounded exp pins       -> exp_exact_pins.txt
   ojas-oracle/fixtures/tiny/*.safetensors     torch goldens of the tiny model  -> tiny/
+  ojas-oracle/fixtures/tiny/{tokens.bin,batch_starts.json,lr_schedules.json,autocast_gap.json}
+                                              inputs and side gates of the 40-step trainer traces -> tiny/
   ojas-oracle/fixtures/variants/*.safetensors GQA / sliding-window variants    -> variants/
   ojas-cpu/tests/torch_ref/data.rs            torch-2.13 bits, one-head step   -> torch_ref.json
 """
@@ -46,8 +48,12 @@ def main() -> None:
     digests(ref)
     shutil.copyfile(ref / "ojas-core/src/exp_exact_pins.txt", HERE / "exp_exact_pins.txt")
     (HERE / "tiny").mkdir(exist_ok=True)
-    for name in ("init", "forward", "grads_init", "grads_step5", "trace_ns5_f32", "muon_step_bf16"):
+    for name in ("init", "forward", "grads_init", "grads_step5", "trace_ns5_f32", "trace_ns5_bf16", "muon_step_bf16"):
         shutil.copyfile(ref / f"ojas-oracle/fixtures/tiny/{name}.safetensors", HERE / "tiny" / f"{name}.safetensors")
+    # the trainer traces' inputs and side gates: the token stream and the sampler's window starts the 40 steps read, the
+    # schedule multipliers, torch's own autocast gap on the trace, and the f64 RMSNorm fixture
+    for name in ("tokens.bin", "batch_starts.json", "lr_schedules.json", "autocast_gap.json"):
+        shutil.copyfile(ref / f"ojas-oracle/fixtures/tiny/{name}", HERE / "tiny" / name)
     (HERE / "variants").mkdir(exist_ok=True)
     for name in ("gqa", "swa"):
         shutil.copyfile(ref / f"ojas-oracle/fixtures/variants/{name}.safetensors", HERE / "variants" / f"{name}.safetensors")
