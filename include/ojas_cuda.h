@@ -194,8 +194,14 @@ typedef struct ojc_train_config {          /* TrainConfig, ojas-model/src/traine
   float loss_seed;                         /* backward seed w_i (MicroWeights, trainer.rs:1083-1119); 1/world under data parallelism */
   int32_t checkpoint_blocks;               /* ActivationCheckpoint::Blocks (ojas-model/src/block.rs:323-336): keep only each block's input and recompute the block in
                                             * backward; same bits as without, about a third more forward work, activation memory of two blocks instead of n_layer */
+  int32_t schedule;                        /* LrSchedule (ojas-cpu/src/schedule.rs:205-226): 0 none (multiplier 1 at every step), 1 Cosine, 2 Wsd */
+  uint64_t warmup_steps, total_steps;      /* total_steps 0 is refused for Cosine and Wsd (schedule.rs:42-47,127-133) */
+  double decay_frac;                       /* Wsd only, in [0, 1] (WSD_DECAY_FRAC 0.2, schedule.rs:94) */
+  int32_t on_nonfinite;                    /* NonFinitePolicy (trainer.rs:85-91): 0 Abort (keep the data cursor), 1 SkipBatch (move it past the step's batches) */
 } ojc_train_config;
-typedef struct ojc_step_report { float loss; float grad_norm; uint64_t step; uint64_t tokens; } ojc_step_report; /* StepReport trainer.rs:281-297 */
+/* StepReport (trainer.rs:281-297). loss is the token-weighted mean of the micro-batch losses, grad_norm the global norm before clipping,
+ * lr_multiplier the schedule's factor on every group's peak learning rate, step the completed steps after this one. */
+typedef struct ojc_step_report { float loss; float grad_norm; uint64_t step; uint64_t tokens; double lr_multiplier; } ojc_step_report;
 typedef struct ojc_trainer ojc_trainer;
 ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const ojc_train_config* cfg, int64_t batch, int64_t seq, ojc_trainer** out);
 ojc_status ojc_trainer_close(ojc_trainer* tr);
@@ -219,6 +225,30 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out);            
 ojc_status ojc_trainer_finish(ojc_trainer* tr, ojc_step_report* report);                               /* Trainer::finish (trainer.rs:1031): sync + the one readback (loss, norm, fault word) */
 ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uint32_t* targets_host, ojc_step_report* report); /* gradients + apply + the one loss readback */
 ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev, ojc_step_report* report);
+/* Trainer::step_tokens / Trainer::run (trainer.rs:713-890): ONE optimizer step over k caller-supplied micro-batches of [batch, seq] host ids and
+ * targets. Micro-batch i seeds its backward with MicroWeights' w_i (its share of the step's valid targets; 1/run when every non-empty micro-batch
+ * counts the same, trainer.rs:1083-1119) times the config's loss_seed, gradients are summed in f32 in micro-batch order (accumulate_grad), a
+ * micro-batch whose targets are all ignored only has its ids checked. Then clip, the schedule's learning rates, Muon / AdamW, and the one readback.
+ * Refusals before any work: Poisoned, a step past a Wsd schedule or at u64::MAX (OutOfRange), k outside 1..=2^24 (OutOfRange), an id outside the
+ * vocabulary (OutOfRange), no valid target at all (NonFinite), no room for the optimizer's scratch (CapacityExceeded). A non-finite loss or
+ * gradient norm is found on the device before the first update: the optimizer kernels leave parameters, moments and the step count as they were,
+ * the call returns NonFinite and the trainer stays Ready (trainer.rs:824-838). Only a failure inside the update poisons. */
+ojc_status ojc_trainer_run(ojc_trainer* tr, const uint32_t* const* ids_host, const uint32_t* const* targets_host, int64_t k, ojc_step_report* report);
+/* The first half of ojc_trainer_run (refusals, k forward/backward passes, accumulation), for callers that exchange gradient buckets between
+ * it and ojc_trainer_apply + ojc_trainer_finish. */
+ojc_status ojc_trainer_run_gradients(ojc_trainer* tr, const uint32_t* const* ids_host, const uint32_t* const* targets_host, int64_t k);
+/* What Trainer::step does with a failed run (trainer.rs:686-708), for the host that owns the sampler: given the status ojc_trainer_run returned,
+ * *advance_cursor says whether the data cursor moves past the step's batches (only a NonFinite on a Ready trainer under SkipBatch), and the return
+ * value is the status to surface: run_status itself, or OutOfRange once 8 skips in a row (MAX_CONSECUTIVE_SKIPS, trainer.rs:81) were already
+ * taken, in which case the cursor stays. Any committed step clears the count. */
+ojc_status ojc_trainer_resolve_failure(ojc_trainer* tr, ojc_status run_status, int32_t* advance_cursor);
+int32_t ojc_trainer_state(ojc_trainer* tr);                                                              /* TrainState (trainer.rs:93-98): 0 Ready, 1 Poisoned */
+/* LrSchedule::multiplier at a 0-based step (schedule.rs:66-90,163-199), every operation in f64 in nanolab's order. */
+ojc_status ojc_lr_multiplier(const ojc_train_config* cfg, uint64_t step, double* multiplier);
+/* Host-made failure for tests of the trainer's state machine (the job of the reference's Probe<B> test double, ojas-model/tests/common/mod.rs:647:
+ * fail the n-th call of a chosen op). where 1: the next gradient pass fails after its forward, before anything the trainer owns changed;
+ * where 2: the next optimizer phase fails after its first update kernel. One shot; no device fault is involved. */
+ojc_status ojc_trainer_inject_failure(ojc_trainer* tr, int32_t where);
 ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* logits_host);          /* forward_logits, block.rs:407-416; [batch*seq, vocab] */
 /* Data-parallel extension (new; the reference has no distributed code): gradients live in contiguous buckets; the
  * caller all-reduces each bucket (NCCL) between ojc_trainer_gradients and ojc_trainer_apply. */

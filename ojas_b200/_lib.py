@@ -33,11 +33,12 @@ class TrainConfig(C.Structure):
                 ("adam_lr", C.c_double), ("adam_beta1", C.c_double), ("adam_beta2", C.c_double), ("adam_eps", C.c_double), ("adam_weight_decay", C.c_double),
                 ("matrix_lr", C.c_double), ("muon_momentum", C.c_double), ("muon_weight_decay", C.c_double),
                 ("ns5_bf16", C.c_int32), ("grad_clip", C.c_float), ("has_ignore", C.c_int32), ("ignore_index", C.c_uint32),
-                ("ce_chunk_rows", C.c_int64), ("loss_seed", C.c_float), ("checkpoint_blocks", C.c_int32)]
+                ("ce_chunk_rows", C.c_int64), ("loss_seed", C.c_float), ("checkpoint_blocks", C.c_int32),
+                ("schedule", C.c_int32), ("warmup_steps", C.c_uint64), ("total_steps", C.c_uint64), ("decay_frac", C.c_double), ("on_nonfinite", C.c_int32)]
 
 
 class StepReport(C.Structure):
-    _fields_ = [("loss", C.c_float), ("grad_norm", C.c_float), ("step", C.c_uint64), ("tokens", C.c_uint64)]
+    _fields_ = [("loss", C.c_float), ("grad_norm", C.c_float), ("step", C.c_uint64), ("tokens", C.c_uint64), ("lr_multiplier", C.c_double)]
 
 
 def load() -> C.CDLL:

@@ -507,11 +507,24 @@ class TrainConfig:
     ce_chunk_rows: int = 0
     loss_seed: float = 1.0
     checkpoint_blocks: bool = False      # ActivationCheckpoint::Blocks: recompute each block in backward from its saved input
+    schedule: str = "none"               # LrSchedule (ojas-cpu/src/schedule.rs:205-226): "none" (multiplier 1), "cosine" or "wsd"
+    warmup_steps: int = 0
+    total_steps: int = 0
+    decay_frac: float = 0.2              # WSD_DECAY_FRAC
+    on_nonfinite: str = "abort"          # NonFinitePolicy (trainer.rs:85-91): "abort" or "skip_batch"
 
     def c(self):
         return _lib.TrainConfig(int(self.autocast_bf16), 0 if self.optimizer == "adamw" else 1, self.adam_lr, self.adam_beta1, self.adam_beta2, self.adam_eps,
                                 self.adam_weight_decay, self.matrix_lr, self.muon_momentum, self.muon_weight_decay, int(self.ns5_bf16), self.grad_clip,
-                                int(self.ignore_index is not None), self.ignore_index or 0, self.ce_chunk_rows, self.loss_seed, int(self.checkpoint_blocks))
+                                int(self.ignore_index is not None), self.ignore_index or 0, self.ce_chunk_rows, self.loss_seed, int(self.checkpoint_blocks),
+                                {"none": 0, "cosine": 1, "wsd": 2}[self.schedule], self.warmup_steps, self.total_steps, self.decay_frac,
+                                {"abort": 0, "skip_batch": 1}[self.on_nonfinite])
+
+    def lr_multiplier(self, step: int) -> float:
+        """LrSchedule::multiplier at a 0-based step, computed by the library (f64, nanolab's order of operations)."""
+        out, cc = C.c_double(), self.c()
+        _check(lib.ojc_lr_multiplier(C.byref(cc), C.c_uint64(step), C.byref(out)))
+        return out.value
 
 
 @dataclass
@@ -528,6 +541,7 @@ class StepReport:
     grad_norm: float
     step: int
     tokens: int
+    lr_multiplier: float = 1.0
 
 
 class Trainer:
@@ -616,25 +630,73 @@ class Trainer:
     def finish(self) -> StepReport:
         rep = _lib.StepReport()
         _check(lib.ojc_trainer_finish(self._h, C.byref(rep)))
-        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens)
+        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens, rep.lr_multiplier)
 
     def step(self, ids, targets) -> StepReport:
         ids, targets = self._ids(ids), self._ids(targets)
         assert ids.size == self.batch * self.seq == targets.size
         rep = _lib.StepReport()
         _check(lib.ojc_trainer_step(self._h, C.c_void_p(ids.ctypes.data), C.c_void_p(targets.ctypes.data), C.byref(rep)))
-        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens)
+        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens, rep.lr_multiplier)
+
+    def _batch_ptrs(self, batches):
+        xs = [self._ids(x) for x, _ in batches]
+        ys = [self._ids(y) for _, y in batches]
+        for a in xs + ys:
+            assert a.size == self.batch * self.seq
+        px = (C.c_void_p * len(xs))(*[a.ctypes.data for a in xs])
+        py = (C.c_void_p * len(ys))(*[a.ctypes.data for a in ys])
+        return xs, ys, px, py
+
+    def run(self, batches) -> StepReport:
+        """Trainer::step_tokens (trainer.rs:713-720): one optimizer step over K micro-batches [(ids, targets)], each [batch, seq]."""
+        keep = self._batch_ptrs(batches)
+        rep = _lib.StepReport()
+        _check(lib.ojc_trainer_run(self._h, keep[2], keep[3], C.c_int64(len(batches)), C.byref(rep)))
+        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens, rep.lr_multiplier)
+
+    def run_gradients(self, batches) -> None:
+        """The gradient half of run(): K forward/backward passes summed into the gradient buckets; apply() and finish() complete the step."""
+        keep = self._batch_ptrs(batches)
+        _check(lib.ojc_trainer_run_gradients(self._h, keep[2], keep[3], C.c_int64(len(batches))))
+
+    def step_sampled(self, sampler, bin_, accum: int = 1) -> StepReport:
+        """Trainer::step (trainer.rs:672-711): draw `accum` micro-batches from the sampler, run them, and move the sampler's cursor
+        past them on success, or on a NonFinite step under NonFinitePolicy::SkipBatch (at most 8 in a row); any other failure
+        leaves the cursor where it was."""
+        saved = (sampler.epoch, sampler.ordinal)
+        batches = [sampler.next_batch(bin_) for _ in range(accum)]
+        try:
+            return self.run(batches)
+        except OjasError as err:
+            advance = C.c_int32(0)
+            final = lib.ojc_trainer_resolve_failure(self._h, C.c_int32(err.status), C.byref(advance))
+            if not advance.value:
+                sampler.epoch, sampler.ordinal = saved
+            if final != err.status:
+                _check(final)
+            raise
+
+    @property
+    def state(self) -> str:
+        """TrainState (trainer.rs:93-98)."""
+        return "Poisoned" if lib.ojc_trainer_state(self._h) else "Ready"
+
+    def inject_failure(self, where: str) -> None:
+        """Host-made failure for tests: 'gradients' fails the next gradient pass after its forward, 'optimizer' the next optimizer phase
+        after its first update kernel."""
+        _check(lib.ojc_trainer_inject_failure(self._h, C.c_int32({"none": 0, "gradients": 1, "optimizer": 2}[where])))
 
     def step_host_ptrs(self, ids_ptr: int, targets_ptr: int) -> StepReport:
         """Same as step() for caller-owned (for example pinned) host buffers given by address."""
         rep = _lib.StepReport()
         _check(lib.ojc_trainer_step(self._h, C.c_void_p(ids_ptr), C.c_void_p(targets_ptr), C.byref(rep)))
-        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens)
+        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens, rep.lr_multiplier)
 
     def step_device(self, ids: Tensor, targets: Tensor) -> StepReport:
         rep = _lib.StepReport()
         _check(lib.ojc_trainer_step_device(self._h, C.c_void_p(ids.ptr), C.c_void_p(targets.ptr), C.byref(rep)))
-        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens)
+        return StepReport(rep.loss, rep.grad_norm, rep.step, rep.tokens, rep.lr_multiplier)
 
     def gradients_device(self, ids: Tensor, targets: Tensor):
         _check(lib.ojc_trainer_gradients_device(self._h, C.c_void_p(ids.ptr), C.c_void_p(targets.ptr)))

@@ -17,6 +17,17 @@ typedef __nv_bfloat16 bf16;
 // Op ids written into the deferred fault word (first faulting op wins), in the
 // spirit of the reference's fault.wgsl / deferred-fault contract
 // (ojas-core/src/backend.rs:963-973).
+// Grids whose block count is also the number of partial sums of a reduction are sized from this constant (the B200's SM count),
+// not from the opened device: the order a gradient is summed in, and so its bits, is then a function of the shape alone
+// (the reference's rule for its device kernels: grid a function of shape, ojas-cuda/README.md:131-134).
+constexpr int REDUCE_SMS = 148;
+
+// Function attributes (dynamic shared-memory limits, cluster occupancy) belong to a device, not to the process: a flag or a
+// value cached for them is kept per device ordinal, so a second backend opened on another GPU sets its own.
+constexpr int OJC_MAX_DEVICES = 64;
+struct PerDeviceFlag { bool set[OJC_MAX_DEVICES] = {}; bool& operator[](int device) { return set[(unsigned)device % OJC_MAX_DEVICES]; } };
+struct PerDeviceInt { int v[OJC_MAX_DEVICES]; explicit PerDeviceInt(int init) { for (int& x : v) x = init; } int& operator[](int device) { return v[(unsigned)device % OJC_MAX_DEVICES]; } };
+
 enum OjcOp : uint32_t {
   OP_NONE = 0, OP_EMBEDDING, OP_LINEAR, OP_RMS_NORM, OP_ROPE, OP_VRES, OP_SDPA, OP_GATE, OP_SILU, OP_MUL,
   OP_ADD, OP_LINEAR_CE, OP_CE, OP_ACCUMULATE, OP_SCALE, OP_CLIP, OP_ADAMW, OP_MUON, OP_ARGMAX, OP_CAST, OP_GEMM_WAIT,
@@ -40,7 +51,7 @@ struct ojc_backend {
   std::multimap<uint64_t, void*> free_blocks;                 // rounded bytes -> ptr
   void* scratch = nullptr;                 // grows on demand; library-internal workspace (not charged to the caller's tensors)
   uint64_t scratch_bytes = 0;
-  int sm_count = 148;
+  int sm_count = 148;                      // the opened device's; sizes persistent grids only (never a reduction's partial count, see REDUCE_SMS)
   void* tmap_encode = nullptr;             // cuTensorMapEncodeTiled, resolved once
   bool profile_gemm = false;               // bracket tensor-core GEMM launches with events
   struct GemmSample { cudaEvent_t start, stop; double flops; };

@@ -229,8 +229,9 @@ ojc_status ojc_cached_attention_forward(ojc_backend* be, const ojc_tensor* q, co
   const int64_t widest = w > 0 ? std::min(len, w) : len;
   const size_t smem = (size_t)(dh + widest + 32) * 4;
   if (smem > 200 * 1024) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "more than ~51,000 visible positions per query are not supported by this kernel");
-  static size_t attr = 0;
-  if (smem > 48 * 1024 && smem > attr) {
+  static PerDeviceInt attr_of(0);
+  int& attr = attr_of[be->device];
+  if (smem > 48 * 1024 && smem > (size_t)attr) {
     OJC_CUDA(be, cudaFuncSetAttribute(cached_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), op);
     attr = 200 * 1024;
   }

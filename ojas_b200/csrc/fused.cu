@@ -448,7 +448,7 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
     const int hl = 1;   // the backward measured faster with each thread walking all heads of its token (42 vs 46 us at 12 x 64); the forward the other way (23 vs 29 us)
     const int tokens_per_block = 128 / (TPR * hl);
     int64_t blocks = (tokens + tokens_per_block - 1) / tokens_per_block;
-    if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
+    if (blocks > (int64_t)REDUCE_SMS * 8) blocks = (int64_t)REDUCE_SMS * 8;
     void* part = nullptr;
     bool on_lane = false;
     cudaStream_t fs = nullptr;
@@ -479,7 +479,7 @@ ojc_status gate_apply_backward(ojc_backend* be, const float* scales, const bf16*
   if (dh % 8 != 0 || per > 32 || (per & (per - 1)) != 0) return ojc_fail(OJC_ERR_UNSUPPORTED_HEAD_DIM, op, "head_dim must be 8, 16, 32, 64, 128 or 256");
   const int warps = 8;
   int64_t blocks = (rows + warps - 1) / warps;
-  if (blocks > (int64_t)be->sm_count * 8) blocks = (int64_t)be->sm_count * 8;
+  if (blocks > (int64_t)REDUCE_SMS * 8) blocks = (int64_t)REDUCE_SMS * 8;
   void* part = nullptr;
   bool on_lane = false;
   cudaStream_t fs = nullptr;
@@ -517,7 +517,7 @@ ojc_status vres_rows_backward(ojc_backend* be, const bf16* v, int64_t ldv, const
                               float* acc, bool first, float* glambda, int64_t rows, int64_t cols) {
   const char* op = "value_residual_blend_backward";
   if (cols % 8 != 0 || ldv % 8 != 0 || ld0 % 8 != 0 || ldg % 8 != 0) return ojc_fail(OJC_ERR_SHAPE, op, "widths must be multiples of 8");
-  const int blocks = be->sm_count * 4;
+  const int blocks = REDUCE_SMS * 4;
   void* part = nullptr;
   OJC_TRY(ojc_scratch(be, (uint64_t)blocks * 8, &part));
   vres_rows_backward_kernel<<<blocks, 256, 0, be->stream>>>(v, ldv, v0, ld0, lambda, gy, gv, ldg, acc, first ? 1 : 0, (double*)part, rows, (int)(cols / 8));

@@ -541,7 +541,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   int amn, bmn; int64_t lda, ldb;
   operand_ok(a, true, &amn, &lda); operand_ok(b, false, &bmn, &ldb);
   // Two-SM tiles (256 x 256 per CTA pair) whenever the output is at least one such tile; the one-SM kernel keeps the rest.
-  static int max_pairs = -1;
+  static PerDeviceInt max_pairs_of(-1);
+  int& max_pairs = max_pairs_of[be->device];
   if (max_pairs < 0) {
     OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
     cudaLaunchConfig_t cfg = {};
@@ -560,7 +561,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   if (!bmn) OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, 64, two_sm ? 128 : BN, false, batch, b_bs));
   else OJC_TRY(make_tmap(be, op, &tb, b.ptr, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, 64, BK, false, batch, b_bs));
 
-  static bool attr_set = false;
+  static PerDeviceFlag attr_set_of;
+  bool& attr_set = attr_set_of[be->device];
   if (!attr_set) {
     OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
     attr_set = true;

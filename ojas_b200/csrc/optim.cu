@@ -57,7 +57,7 @@ struct AdamWords { float decay, one_minus_b1, beta2, one_minus_b2, step_size, bc
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, bf16* __restrict__ mirror,
                              int64_t n, AdamWords w, const float* __restrict__ grad_scale, uint32_t* fault) {
   float gs = 1.0f;
-  if (grad_scale) { gs = grad_scale[0]; if (!(gs < 1.0f)) gs = 1.0f; }
+  if (grad_scale) { gs = grad_scale[0]; if (gs < 0.0f) return; if (!(gs < 1.0f)) gs = 1.0f; }   // a negative scale calls the step off (STEP_CALLED_OFF)
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
     const float pi = p[i];
@@ -91,7 +91,8 @@ __global__ void muon_momentum_kernel(const MuonBatch mb, float* __restrict__ u_a
   float* __restrict__ mom = mb.mom[blockIdx.y];
   float* __restrict__ u = u_all + (int64_t)blockIdx.y * n;
   float gs = 1.0f;
-  if (grad_scale) { gs = grad_scale[0]; if (!(gs < 1.0f)) gs = 1.0f; }
+  bool off = false;     // a called-off step still forms u (the later kernels read it) but leaves the momentum buffer alone
+  if (grad_scale) { gs = grad_scale[0]; off = gs < 0.0f; if (!(gs < 1.0f) || off) gs = 1.0f; }
   const int64_t base = (int64_t)blockIdx.x * NORM_CHUNK;
   float acc = 0.0f;
   for (int i = threadIdx.x; i < NORM_CHUNK; i += blockDim.x) {
@@ -102,12 +103,12 @@ __global__ void muon_momentum_kernel(const MuonBatch mb, float* __restrict__ u_a
     const float buf = mu * mom[idx] + gi;
     float ui = nesterov ? fmaf(mu, buf, gi) : buf;
     if (round_u) ui = round_bf16(ui);
-    mom[idx] = buf;
+    if (!off) mom[idx] = buf;
     u[idx] = ui;
     acc = fmaf(ui, ui, acc);
   }
   float t = block_sum(acc, red);
-  if (threadIdx.x == 0) { if (!isfinite(t)) raise_fault(fault, OP_MUON); part[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = (double)t; }
+  if (threadIdx.x == 0) { if (!isfinite(t) && !off) raise_fault(fault, OP_MUON); part[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = (double)t; }
 }
 
 // norm[matrix] = f32 of the f64 square root of its partial sums, added in the order norm_finish_kernel uses
@@ -163,8 +164,10 @@ __global__ void muon_normalize_tall_kernel(const float* __restrict__ u_all, cons
   }
 }
 template <class TX>
-__global__ void muon_apply_tall_kernel(const MuonBatch mb, const TX* __restrict__ x_all, int rows, int cols, float alpha, float decay, int decays, uint32_t* fault) {
+__global__ void muon_apply_tall_kernel(const MuonBatch mb, const TX* __restrict__ x_all, int rows, int cols, float alpha, float decay, int decays, uint32_t* fault,
+                                       const float* __restrict__ gate) {
   __shared__ float tile[32][33];
+  if (gate && gate[0] < 0.0f) return;
   const int64_t n = (int64_t)rows * cols;
   float* __restrict__ p = mb.p[blockIdx.z];
   bf16* __restrict__ mirror = mb.mirror[blockIdx.z];
@@ -200,7 +203,9 @@ __global__ void muon_normalize_bf16x4_kernel(const float* __restrict__ u_all, co
                       (uint32_t)f32_to_bf16_bits(v.z / denom) | ((uint32_t)f32_to_bf16_bits(v.w / denom) << 16));
   }
 }
-__global__ void muon_apply_bf16x4_kernel(const MuonBatch mb, const bf16* __restrict__ x_all, int64_t n, float alpha, float decay, int decays, uint32_t* fault) {
+__global__ void muon_apply_bf16x4_kernel(const MuonBatch mb, const bf16* __restrict__ x_all, int64_t n, float alpha, float decay, int decays, uint32_t* fault,
+                                         const float* __restrict__ gate) {
+  if (gate && gate[0] < 0.0f) return;
   float4* __restrict__ p = reinterpret_cast<float4*>(mb.p[blockIdx.y]);
   uint2* __restrict__ mirror = reinterpret_cast<uint2*>(mb.mirror[blockIdx.y]);
   const uint2* __restrict__ x = reinterpret_cast<const uint2*>(x_all + (int64_t)blockIdx.y * n);
@@ -280,7 +285,9 @@ __global__ void ns_combine_x_kernel(const T* __restrict__ x, T* __restrict__ bx,
 
 // p = fma(alpha, X, p * decay) with X read back through the transpose when the matrix was tall (optim.rs:718-736).
 template <class TX>
-__global__ void muon_apply_kernel(const MuonBatch mb, const TX* __restrict__ x_all, int rows, int cols, int tall, float alpha, float decay, int decays, uint32_t* fault) {
+__global__ void muon_apply_kernel(const MuonBatch mb, const TX* __restrict__ x_all, int rows, int cols, int tall, float alpha, float decay, int decays, uint32_t* fault,
+                                  const float* __restrict__ gate) {
+  if (gate && gate[0] < 0.0f) return;
   const int64_t n = (int64_t)rows * cols;
   float* __restrict__ p = mb.p[blockIdx.y];
   bf16* __restrict__ mirror = mb.mirror[blockIdx.y];
@@ -490,7 +497,8 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
     const size_t small_smem = ((size_t)2 * r * c + 2 * 32 * 33) * 4;
     const bool small = batch > 1 && r <= 32 && small_smem <= 200 * 1024;     // e.g. the [heads, d] gate weights: one CTA per matrix
     if (small) {
-      static bool attr = false;
+      static PerDeviceFlag attr_of;
+      bool& attr = attr_of[be->device];
       if (!attr) {
         OJC_CUDA(be, cudaFuncSetAttribute(muon_small_ns5_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), op);
         OJC_CUDA(be, cudaFuncSetAttribute(muon_small_ns5_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), op);
@@ -528,11 +536,11 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
     }
     const double scale = std::sqrt(std::max(1.0, (double)rows / (double)cols));
     const float alpha = (float)(-cfg.lr * scale), decay = (float)(1.0 - cfg.lr * cfg.weight_decay);
-    if (tiled && bf) muon_apply_tall_kernel<bf16><<<tgrid, tblock, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
-    else if (tiled) muon_apply_tall_kernel<float><<<tgrid, tblock, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
-    else if (bf && !tall && n % 4 == 0 && mirrors_aligned) muon_apply_bf16x4_kernel<<<dim3(elementwise_grid(be, n / 4, 256), nb), 256, 0, be->stream>>>(mb, (const bf16*)x, n, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
-    else if (bf) muon_apply_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
-    else muon_apply_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev);
+    if (tiled && bf) muon_apply_tall_kernel<bf16><<<tgrid, tblock, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev, grad_scale_dev);
+    else if (tiled) muon_apply_tall_kernel<float><<<tgrid, tblock, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev, grad_scale_dev);
+    else if (bf && !tall && n % 4 == 0 && mirrors_aligned) muon_apply_bf16x4_kernel<<<dim3(elementwise_grid(be, n / 4, 256), nb), 256, 0, be->stream>>>(mb, (const bf16*)x, n, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev, grad_scale_dev);
+    else if (bf) muon_apply_kernel<bf16><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const bf16*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev, grad_scale_dev);
+    else muon_apply_kernel<float><<<dim3(grid, nb), 256, 0, be->stream>>>(mb, (const float*)x, (int)rows, (int)cols, tall, alpha, decay, cfg.weight_decay != 0.0, be->fault_dev, grad_scale_dev);
     OJC_LAUNCHED(be, op);
     return OJC_OK;
   };

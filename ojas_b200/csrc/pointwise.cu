@@ -10,10 +10,12 @@
 #include "ops.cuh"
 
 // ======================================================================== elementwise
-enum EwOp { EW_SILU, EW_SILU_BWD, EW_MUL, EW_ADD, EW_COPY, EW_ROUND_BF16, EW_SCALE };
+enum EwOp { EW_SILU, EW_SILU_BWD, EW_MUL, EW_ADD, EW_COPY, EW_ROUND_BF16, EW_SCALE, EW_ACCUM };
+// EW_ACCUM is accumulate_grad (ojas-cpu/src/accum.rs:33-115): acc + grad, where a sum that is not finite is not stored and raises the
+// deferred fault word instead (the reference refuses the call with NonFinite and leaves acc untouched).
 
 template <int OP, class TA, class TB, class TO>
-__global__ void ew_kernel(const TA* __restrict__ a, const TB* __restrict__ b, TO* __restrict__ out, int64_t n, float s) {
+__global__ void ew_kernel(const TA* __restrict__ a, const TB* __restrict__ b, TO* __restrict__ out, int64_t n, float s, uint32_t* fault) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
@@ -22,6 +24,7 @@ __global__ void ew_kernel(const TA* __restrict__ a, const TB* __restrict__ b, TO
     else if (OP == EW_SILU_BWD) { float g = ldf(b, i), sg = sigmoidf_(x); r = g * sg * (1.0f + x * (1.0f - sg)); }
     else if (OP == EW_MUL) r = x * ldf(b, i);
     else if (OP == EW_ADD) r = x + ldf(b, i);
+    else if (OP == EW_ACCUM) { r = x + ldf(b, i); if (!isfinite(r)) { raise_fault(fault, OP_ACCUMULATE); continue; } }
     else if (OP == EW_ROUND_BF16) r = round_bf16(x);
     else if (OP == EW_SCALE) r = x * s;
     else r = x;
@@ -50,23 +53,26 @@ template <> struct Vec4<bf16> {
 };
 
 template <int OP, class TA, class TB, class TO>
-__global__ void ew_kernel_v4(const TA* __restrict__ a, const TB* __restrict__ b, TO* __restrict__ out, int64_t n4, float s) {
+__global__ void ew_kernel_v4(const TA* __restrict__ a, const TB* __restrict__ b, TO* __restrict__ out, int64_t n4, float s, uint32_t* fault) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n4; i += stride) {
     float x[4], y[4], r[4];
     Vec4<TA>::ld(a, i, x);
-    if (OP == EW_SILU_BWD || OP == EW_MUL || OP == EW_ADD) Vec4<TB>::ld(b, i, y);
+    if (OP == EW_SILU_BWD || OP == EW_MUL || OP == EW_ADD || OP == EW_ACCUM) Vec4<TB>::ld(b, i, y);
+    bool bad = false;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       if (OP == EW_SILU) r[k] = x[k] * sigmoidf_(x[k]);
       else if (OP == EW_SILU_BWD) { float sg = sigmoidf_(x[k]); r[k] = y[k] * sg * (1.0f + x[k] * (1.0f - sg)); }
       else if (OP == EW_MUL) r[k] = x[k] * y[k];
       else if (OP == EW_ADD) r[k] = x[k] + y[k];
+      else if (OP == EW_ACCUM) { r[k] = x[k] + y[k]; if (!isfinite(r[k])) { bad = true; r[k] = x[k]; } }
       else if (OP == EW_ROUND_BF16) r[k] = round_bf16(x[k]);
       else if (OP == EW_SCALE) r[k] = x[k] * s;
       else r[k] = x[k];
     }
+    if (OP == EW_ACCUM && bad) raise_fault(fault, OP_ACCUMULATE);
     Vec4<TO>::st(out, i, r);
   }
 }
@@ -89,8 +95,8 @@ static ojc_status launch_ew(ojc_backend* be, const char* op, const ojc_tensor* a
         using TA = decltype(ta); using TB = decltype(tb); using TO = decltype(to);
         const TA* ap = (const TA*)a->data; const TB* bp = (const TB*)bb->data; TO* op_ = (TO*)out->data;
         bool vec = (n % 4 == 0) && aligned16(ap) && aligned16(bp) && aligned16(op_);
-        if (vec) ew_kernel_v4<OP, TA, TB, TO><<<elementwise_grid(be, n / 4, 256), 256, 0, be->stream>>>(ap, bp, op_, n / 4, s);
-        else ew_kernel<OP, TA, TB, TO><<<elementwise_grid(be, n, 256), 256, 0, be->stream>>>(ap, bp, op_, n, s);
+        if (vec) ew_kernel_v4<OP, TA, TB, TO><<<elementwise_grid(be, n / 4, 256), 256, 0, be->stream>>>(ap, bp, op_, n / 4, s, be->fault_dev);
+        else ew_kernel<OP, TA, TB, TO><<<elementwise_grid(be, n, 256), 256, 0, be->stream>>>(ap, bp, op_, n, s, be->fault_dev);
         OJC_LAUNCHED(be, op);
         return OJC_OK;
       });
@@ -318,7 +324,7 @@ ojc_status rms_backward_impl(ojc_backend* be, const ojc_tensor* x, const ojc_ten
   const int64_t rows = n / dim;
   const int warps = dim > 512 ? 4 : 8;
   int64_t blocks = (rows + warps - 1) / warps;
-  if (blocks > be->sm_count * 4) blocks = be->sm_count * 4;
+  if (blocks > REDUCE_SMS * 4) blocks = REDUCE_SMS * 4;
   if (x->dtype != gy->dtype || x->dtype != gx->dtype) return ojc_fail(OJC_ERR_DTYPE, op, "x, grad_y and grad_x must share a dtype");
   void* part = nullptr;
   bool on_lane = false;
@@ -617,7 +623,7 @@ ojc_status ojc_residual_add_backward(ojc_backend* be, const ojc_tensor* g, ojc_t
 }
 ojc_status ojc_accumulate_grad(ojc_backend* be, ojc_tensor* acc, const ojc_tensor* grad) {
   if (acc && grad && !same_shape(acc, grad)) return ojc_fail(OJC_ERR_SHAPE, "accumulate_grad", "shapes differ");
-  return launch_ew<EW_ADD>(be, "accumulate_grad", acc, grad, acc);
+  return launch_ew<EW_ACCUM>(be, "accumulate_grad", acc, grad, acc);
 }
 ojc_status ojc_scale_grad(ojc_backend* be, ojc_tensor* grad, float scale) {
   if (!isfinite(scale)) return ojc_fail(OJC_ERR_NON_FINITE, "scale_grad", "scale is not finite");
@@ -706,7 +712,7 @@ ojc_status vres_backward_impl(ojc_backend* be, const ojc_tensor* v, const ojc_te
                               ojc_tensor* gv0, float* glambda, bool accumulate_lambda) {
   const char* op = "value_residual_blend_backward";
   const int64_t n = numel(v);
-  int blocks = be->sm_count * 4;
+  int blocks = REDUCE_SMS * 4;
   void* part = nullptr;
   OJC_TRY(ojc_scratch(be, (uint64_t)blocks * 8, &part));
   if (v->dtype != v0->dtype || gy->dtype != gv->dtype) return ojc_fail(OJC_ERR_DTYPE, op, "v/v0 and grad_y/grad_v must pair up in dtype");
@@ -878,9 +884,7 @@ extern "C" ojc_status ojc_rms_norm_backward_noalloc(void* cuda_stream, const flo
   float* part = g_rms_noalloc_ptr[device];
   const int warps = dim > 512 ? 4 : 8;
   int64_t blocks = (rows + warps - 1) / warps;
-  int sms = 0;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) { cudaGetLastError(); sms = 148; }
-  if (blocks > (int64_t)sms * 4) blocks = (int64_t)sms * 4;
+  if (blocks > (int64_t)REDUCE_SMS * 4) blocks = (int64_t)REDUCE_SMS * 4;
   if (blocks * dim > NOALLOC_PART_FLOATS) blocks = NOALLOC_PART_FLOATS / dim;  // fewer, longer blocks rather than a larger workspace
   if (blocks < 1 || rows > (int64_t)INT32_MAX * warps) return ojc_fail(OJC_ERR_CAPACITY_EXCEEDED, op, "the problem does not fit the fixed 2 MiB workspace");
   cudaStream_t stream = (cudaStream_t)cuda_stream;

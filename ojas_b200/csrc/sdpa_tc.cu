@@ -347,7 +347,8 @@ ojc_status sdpa_forward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tenso
   const int w = window < 0 ? -1 : (int)std::min<int64_t>(window, INT32_MAX);
   dim3 grid((d.time + BM - 1) / BM, d.batch * d.heads);
   const size_t smem = (size_t)(BM + 2 * BN) * (d.dim + 8) * 2;
-  static bool attr64 = false, attr128 = false;
+  static PerDeviceFlag attr64_of, attr128_of;
+  bool &attr64 = attr64_of[be->device], &attr128 = attr128_of[be->device];
   if (d.dim == 64) {
     if (!attr64) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), op); attr64 = true; }
     sdpa_fwd_tc_kernel<64><<<grid, NTHREADS, smem, be->stream>>>(view_of<const bf16>(q), view_of<const bf16>(k), view_of<const bf16>(v), view_of<bf16>(out), lse,
@@ -381,7 +382,8 @@ ojc_status sdpa_backward_tc(ojc_backend* be, const ojc_tensor* q, const ojc_tens
   }
   dim3 grid_k((d.time + BN - 1) / BN, d.batch * d.kv_heads), grid_q((d.time + BM - 1) / BM, d.batch * d.heads);
   const size_t smem_k = (size_t)2 * BM * (d.dim + 8) * 2 + 2 * BM * 4, smem_q = (size_t)2 * BN * (d.dim + 8) * 2;
-  static bool attr = false;
+  static PerDeviceFlag attr_of;
+  bool& attr = attr_of[be->device];
   if (!attr) {
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)2 * BM * 136 * 2 + 2 * BM * 4)), op);
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)2 * BN * 136 * 2)), op);

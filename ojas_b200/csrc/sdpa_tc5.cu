@@ -803,7 +803,8 @@ bool sdpa_tcgen05_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tenso
 
 template <int D>
 static ojc_status launch_fwd(ojc_backend* be, const char* op, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& args, dim3 grid) {
-  static bool attr = false;
+  static PerDeviceFlag attr_of;
+  bool& attr = attr_of[be->device];
   if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwd_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd<D>::SMEM_BYTES), op); attr = true; }
   sdpa_fwd_tcgen05_kernel<D><<<grid, NTHREADS, Fwd<D>::SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
   OJC_LAUNCHED(be, op);
@@ -829,7 +830,8 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
 template <int D>
 static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* out, const ojc_tensor* gout, float* dr_work, int64_t rows,
                              const CUtensorMap (&m)[8], BwdArgs a, const ojc_tensor* gq, const ojc_tensor* gk, const ojc_tensor* gv, const SdpaDims& d) {
-  static bool attr = false;
+  static PerDeviceFlag attr_of;
+  bool& attr = attr_of[be->device];
   if (!attr) {
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dkv<D>::SMEM_BYTES), op);
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);

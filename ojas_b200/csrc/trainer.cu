@@ -79,6 +79,17 @@ struct ojc_trainer {
   int64_t ld_qkv = 0, ld_au = 0;
   uint64_t step = 0;
   bool poisoned = false, grads_ready = false;
+  // One step over K micro-batches (Trainer::run): the running gradient sum of micro-batches 0..i-1 while micro-batch i's backward
+  // writes g, the backward seed of the pass in flight, which stats slot holds the step's loss, and what the report needs.
+  float* gacc = nullptr;
+  float seed_now = 1.0f;
+  int loss_slot = 0;
+  double lr_mult = 1.0;
+  float loss_div = 1.0f;
+  uint64_t run_tokens = 0;
+  uint32_t consecutive_skips = 0;
+  bool eager_used = false;                      // this step's blocks were stepped during backward, before the norm was known
+  int inject = 0;                               // ojc_trainer_inject_failure
   // One-call steps with AdamW on every tensor and no clipping: a block's parameters are stepped on the side lane as soon as its
   // gradients are final, under the rest of backward (nothing later reads them); apply() then skips [eager_begin, eager_end).
   bool eager_request = false;
@@ -303,7 +314,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   for (auto& b : tr->buckets) b.recorded = false;
   // fused tied-head loss: both gradients come out of the forward call (ojas-autograd/src/tape.rs:1766-1779)
   OJC_TRY(linear_ce_impl(be, tr->hf, A, tr->WM(tok), A, targets_dev, N, d, V, tr->cfg.has_ignore, tr->cfg.ignore_index, tr->cfg.ce_chunk_rows, tr->stats, tr->g_h,
-                         OJC_F32, tr->G(tok), false, tr->cfg.loss_seed));
+                         OJC_F32, tr->G(tok), false, tr->seed_now));
   {
     ojc_tensor xf = T2(tr->x_final, OJC_F32, N, d), nf = T1(tr->W(tr->params.back()), OJC_F32, d), gy = T2(tr->g_h, OJC_F32, N, d), gx = T2(tr->gx, OJC_F32, N, d);
     ojc_tensor gnf = T1(tr->G(tr->params.back()), OJC_F32, d);
@@ -318,7 +329,9 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   bool have_v0 = false;
   // fn's inputs are final on the main stream now; run it on the side lane (or in place when there is none)
   const bool lane = bf && tr->side_stream != nullptr && tr->side_enabled;
-  const bool eager = lane && tr->eager_request && tr->cfg.optimizer == 0 && !(tr->cfg.grad_clip > 0.0f) && L > 0;
+  // (only under NonFinitePolicy::Abort: a non-finite gradient found after blocks were stepped poisons the trainer)
+  const bool eager = lane && tr->eager_request && tr->cfg.optimizer == 0 && !(tr->cfg.grad_clip > 0.0f) && L > 0 && tr->cfg.on_nonfinite == 0;
+  tr->eager_used = eager;
   tr->eager_begin = tr->eager_end = eager ? tr->params.back().offset : 0;   // grows downwards block by block
   auto on_side = [&](auto&& fn) -> ojc_status {
     if (!lane) return fn();
@@ -485,7 +498,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       const int first = 1 + (int)l * P_PER_BLOCK;
       const int64_t end = tr->params[first + P_PER_BLOCK].offset;
       int64_t begin = tr->params[first].offset;
-      const ojc_adamw_config ac{tr->cfg.adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.adam_weight_decay};
+      const ojc_adamw_config ac{tr->cfg.adam_lr * tr->lr_mult, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.adam_weight_decay};
       OJC_TRY(on_side([&]() -> ojc_status {
         auto run_range = [&](int64_t b0, int64_t b1) -> ojc_status {
           if (b1 <= b0) return OJC_OK;
@@ -505,6 +518,71 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   OJC_TRY(embedding_backward_impl(be, ids_dev, tr->gx, OJC_F32, tr->G(tok), N, V, d, true));
   OJC_TRY(join_side());   // the last finishing reductions: every gradient is final on the main stream from here
   for (auto& b : tr->buckets) if (b.first_param == 0) OJC_CUDA(be, cudaEventRecord(b.ready, be->stream), "bucket_ready");
+  return OJC_OK;
+}
+
+// stats layout (device floats): [0] loss of the pass in flight, [1] gradient norm, [2] clip scale, or STEP_CALLED_OFF, [3] steps called
+// off since the host last looked, [4] sum of the step's micro-batch losses.
+constexpr float STEP_CALLED_OFF = -1.0f;
+
+// Trainer::gradients' loss sum (trainer.rs:975-988): the first micro-batch's loss starts it, the others are added in f32;
+// each is scaled by its weight first when the weights are not uniform.
+__global__ void loss_sum_kernel(float* stats, float weight, int first, int scaled) {
+  const float l = scaled ? stats[0] * weight : stats[0];
+  stats[4] = first ? l : stats[4] + l;
+}
+
+// The reference finds a non-finite gradient in clip_grad_norm, before any update (trainer.rs:824-838). Here nothing waits for the
+// host: when the norm or the loss is not finite, the scale every optimizer kernel reads becomes STEP_CALLED_OFF, which makes
+// them return without writing, and the count of called-off steps goes up for the host's one readback.
+__global__ void step_gate_kernel(float* stats, int loss_slot) {
+  if (!isfinite(stats[1]) || !isfinite(stats[loss_slot])) { stats[2] = STEP_CALLED_OFF; stats[3] += 1.0f; }
+}
+
+// LrSchedule::multiplier (ojas-cpu/src/schedule.rs:66-90 cosine, 163-199 wsd): f64, nanolab's order of operations.
+ojc_status schedule_multiplier(const ojc_train_config& c, uint64_t step, double* out) {
+  const char* op = c.schedule == 2 ? "wsd_schedule" : "cosine_schedule";
+  constexpr uint64_t F64_INT_MAX = 1ull << 53;
+  constexpr double FLOOR = 0.1;    // COSINE_FLOOR_FRAC, schedule.rs:27
+  *out = 1.0;
+  if (c.schedule == 0) return OJC_OK;
+  if (c.schedule != 1 && c.schedule != 2) return ojc_fail(OJC_ERR_UNSUPPORTED, "lr_schedule", "schedule must be 0 (none), 1 (cosine) or 2 (wsd)");
+  if (c.total_steps == 0) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "total steps 0");
+  if (c.warmup_steps > F64_INT_MAX || c.total_steps > F64_INT_MAX) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "a step count is not an exact f64 integer");
+  if (c.schedule == 2 && !(std::isfinite(c.decay_frac) && c.decay_frac >= 0.0 && c.decay_frac <= 1.0)) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "decay fraction is outside [0, 1]");
+  if (step == UINT64_MAX) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "step counter is u64::MAX");
+  if (step + 1 > F64_INT_MAX) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "the step is not an exact f64 integer");
+  const double step_f = (double)step, warmup = (double)c.warmup_steps;
+  if (c.schedule == 2 && step > c.total_steps) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "the step is past the schedule's steps");
+  if (step < c.warmup_steps) { *out = (step_f + 1.0) / warmup; return OJC_OK; }
+  double m;
+  if (c.schedule == 1) {
+    const double span = (double)c.total_steps - warmup, denom = span < 1.0 ? 1.0 : span;
+    double t = (step_f - warmup) / denom;
+    t = t < 0.0 ? 0.0 : (t > 1.0 ? 1.0 : t);
+    m = FLOOR + (1.0 - FLOOR) * 0.5 * (1.0 + std::cos(3.14159265358979323846 * t));
+  } else {
+    const uint64_t decay_steps = (uint64_t)(c.decay_frac * (double)c.total_steps), decay_start = c.total_steps - decay_steps;
+    if (step < decay_start) return OJC_OK;
+    const double frac = (double)(step - decay_start) / (double)std::max<uint64_t>(decay_steps, 1);
+    m = FLOOR + (1.0 - FLOOR) * (1.0 - frac);
+  }
+  if (!std::isfinite(m)) return ojc_fail(OJC_ERR_NON_FINITE, op, "the multiplier is not finite");
+  *out = m;
+  return OJC_OK;
+}
+
+// scaled_lr (schedule.rs:235-245)
+ojc_status scaled_lr(double initial, double mult, double* out) {
+  const double lr = initial * mult;
+  if (!(std::isfinite(initial) && std::isfinite(mult) && std::isfinite(lr))) return ojc_fail(OJC_ERR_NON_FINITE, "cosine_schedule", "a learning rate is not finite");
+  *out = lr;
+  return OJC_OK;
+}
+
+ojc_status check_ids(const uint32_t* ids, int64_t n, int64_t vocab) {
+  // check_ids, ojas-model/src/trainer.rs:1054-1065 and ojas-cpu/src/pointwise.rs:285-295: refused on the host, before anything is launched
+  for (int64_t i = 0; i < n; ++i) if (ids[i] >= (uint64_t)vocab) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "embedding_forward", "token id outside the vocabulary");
   return OJC_OK;
 }
 
@@ -533,6 +611,12 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
   tr->be = be; tr->spec = s; tr->cfg = *cfg; tr->B = batch; tr->T = seq; tr->N = batch * seq;
   tr->act_dt = cfg->autocast_bf16 ? OJC_BF16 : OJC_F32;
   if (tr->cfg.loss_seed == 0.0f) tr->cfg.loss_seed = 1.0f;
+  {
+    double m = 1.0;     // a schedule the first step would refuse (total 0, decay fraction outside [0, 1]) is refused here (CosineSchedule::new, schedule.rs:42-55)
+    ojc_status sst = schedule_multiplier(tr->cfg, 0, &m);
+    if (sst != OJC_OK) { delete tr; return sst; }
+    if (cfg->on_nonfinite != 0 && cfg->on_nonfinite != 1) { delete tr; return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "on_nonfinite must be 0 (abort) or 1 (skip_batch)"); }
+  }
   build_table(tr);
   const int64_t d = s.n_embd, H = s.n_head, Hkv = s.n_kv_head, dh = s.head_dim, F = s.hidden, N = tr->N, L = s.n_layer;
   const int64_t qw = H * dh, kvw = Hkv * dh;
@@ -612,8 +696,7 @@ ojc_status ojc_trainer_open(ojc_backend* be, const ojc_model_spec* spec, const o
     end = tr->params[first].offset;
     last = first - 1;
   }
-  const char* lane_env = getenv("OJC_SIDE_LANE");
-  if (tr->act_dt == OJC_BF16 && !(lane_env && lane_env[0] == '0')) {
+  if (tr->act_dt == OJC_BF16) {
     if (cudaStreamCreateWithFlags(&tr->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&tr->ev_main, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&tr->ev_side, cudaEventDisableTiming) != cudaSuccess ||
@@ -715,12 +798,28 @@ ojc_status ojc_trainer_set_steps_done(ojc_trainer* tr, uint64_t step) {
   return OJC_OK;
 }
 
+// One forward + backward pass with the seed in tr->seed_now. A host-made failure (ojc_trainer_inject_failure, where 1) fires after
+// the forward: nothing the trainer owns (parameters, moments, step count) has changed by then.
+static ojc_status gradient_pass(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev) {
+  OJC_TRY(forward_hidden(tr, ids_dev));
+  if (tr->inject == 1) { tr->inject = 0; return ojc_fail(OJC_ERR_BACKEND, "trainer_gradients", "injected failure after the forward pass"); }
+  return backward(tr, ids_dev, targets_dev);
+}
+
+// The schedule's multiplier for the step about to be taken; refusals leave everything unchanged (Trainer::run, trainer.rs:757-759).
+static ojc_status begin_step(ojc_trainer* tr) {
+  OJC_TRY(schedule_multiplier(tr->cfg, tr->step, &tr->lr_mult));
+  if (tr->step == UINT64_MAX) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "Trainer::step", "step count u64::MAX has no successor");   // next_step, ojas-core/src/backend.rs:220-224
+  return OJC_OK;
+}
+
 ojc_status ojc_trainer_gradients_device(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* targets_dev) {
   const char* op = "trainer_gradients";
   OJC_TRY(check_live(tr, op));
   if (!ids_dev || !targets_dev) return ojc_fail(OJC_ERR_PLACEMENT, op, "ids and targets must be device pointers");
-  OJC_TRY(forward_hidden(tr, ids_dev));
-  OJC_TRY(backward(tr, ids_dev, targets_dev));
+  OJC_TRY(begin_step(tr));
+  tr->seed_now = tr->cfg.loss_seed; tr->loss_slot = 0; tr->loss_div = 1.0f; tr->run_tokens = (uint64_t)tr->N;
+  OJC_TRY(gradient_pass(tr, ids_dev, targets_dev));
   tr->grads_ready = true;
   return OJC_OK;
 }
@@ -729,14 +828,87 @@ ojc_status ojc_trainer_gradients(ojc_trainer* tr, const uint32_t* ids_host, cons
   const char* op = "trainer_gradients";
   OJC_TRY(check_live(tr, op));
   if (!ids_host || !targets_host) return ojc_fail(OJC_ERR_BACKEND, op, "null ids or targets");
-  // token ids are range-checked on the host before anything is launched (check_ids, ojas-cpu/src/pointwise.rs:285-295)
-  for (int64_t i = 0; i < tr->N; ++i) if (ids_host[i] >= (uint64_t)tr->spec.vocab) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "embedding_forward", "token id outside the vocabulary");
+  OJC_TRY(check_ids(ids_host, tr->N, tr->spec.vocab));
   OJC_CUDA(tr->be, cudaMemcpyAsync(tr->ids, ids_host, (size_t)tr->N * 4, cudaMemcpyHostToDevice, tr->be->stream), op);
   OJC_CUDA(tr->be, cudaMemcpyAsync(tr->targets, targets_host, (size_t)tr->N * 4, cudaMemcpyHostToDevice, tr->be->stream), op);
   OJC_TRY(ojc_trainer_gradients_device(tr, tr->ids, tr->targets));
   if (loss_out) OJC_TRY(ojc_download(tr->be, loss_out, tr->stats, 4));
   return OJC_OK;
 }
+
+// MicroWeights::new (ojas-model/src/trainer.rs:1083-1119)
+struct MicroWeights { std::vector<float> w; bool uniform = true; int64_t run = 0; };
+static ojc_status micro_weights(const std::vector<uint64_t>& counts, MicroWeights* out) {
+  const char* op = "Trainer::step";
+  uint64_t total = 0, first = 0;
+  for (uint64_t n : counts) {
+    if (total + n < total) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "valid target count overflows u64");
+    total += n;
+    if (n > 0) { if (!first) first = n; out->run += 1; }
+  }
+  if (!first) return ojc_fail(OJC_ERR_NON_FINITE, op, "no micro-batch has a valid target: the mean has no denominator");
+  for (uint64_t n : counts) out->uniform = out->uniform && (n == 0 || n == first);
+  for (uint64_t n : counts) out->w.push_back(n == 0 ? 0.0f : (out->uniform ? 1.0f / (float)out->run : (float)((double)n / (double)total)));
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_run_gradients(ojc_trainer* tr, const uint32_t* const* ids_host, const uint32_t* const* targets_host, int64_t k) {
+  const char* op = "Trainer::step";
+  OJC_TRY(check_live(tr, op));
+  ojc_backend* be = tr->be;
+  // every refusal that does not depend on the data comes before any work (trainer.rs:754-815)
+  OJC_TRY(begin_step(tr));
+  constexpr int64_t MAX_ACCUM = 1ll << 24;   // trainer.rs:75
+  if (k <= 0 || k > MAX_ACCUM) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "the number of micro-batches must be in 1..=2^24");
+  if (!ids_host || !targets_host) return ojc_fail(OJC_ERR_BACKEND, op, "null ids or targets");
+  for (int64_t i = 0; i < k; ++i) if (!ids_host[i] || !targets_host[i]) return ojc_fail(OJC_ERR_BACKEND, op, "null ids or targets");
+  std::vector<uint64_t> counts((size_t)k);
+  bool any = false;
+  for (int64_t i = 0; i < k; ++i) {
+    uint64_t n = 0;
+    for (int64_t j = 0; j < tr->N; ++j) n += !(tr->cfg.has_ignore && targets_host[i][j] == tr->cfg.ignore_index);   // valid_targets, trainer.rs:1049-1051
+    counts[i] = n; any = any || n > 0;
+  }
+  // with no valid target anywhere the ids are checked first, so a corrupt batch is OutOfRange and never a skippable NonFinite
+  if (!any) for (int64_t i = 0; i < k; ++i) OJC_TRY(check_ids(ids_host[i], tr->N, tr->spec.vocab));
+  MicroWeights mw;
+  OJC_TRY(micro_weights(counts, &mw));
+  for (int64_t i = 0; i < k; ++i) OJC_TRY(check_ids(ids_host[i], tr->N, tr->spec.vocab));
+  if (tr->cfg.optimizer == 1) {
+    // preflight (trainer.rs:401-426,801-806): the largest Muon group's scratch must fit the budget before any work
+    uint64_t need = 0, cap = 0, live = 0;
+    for (const Param& p : tr->params) if (p.trains && p.group == GROUP_MUON) need = std::max<uint64_t>(need, muon_scratch_bytes(p.shape[0], p.shape[1], tr->cfg.ns5_bf16 != 0));
+    OJC_TRY(ojc_budget(be, &cap, &live, nullptr));
+    if (need > cap - std::min(cap, live)) return ojc_fail(OJC_ERR_CAPACITY_EXCEEDED, op, "no room for the optimizer's scratch");
+  }
+  if (k > 1 && !tr->gacc) OJC_TRY(take_as(tr, (uint64_t)tr->flat_n * 4, &tr->gacc));
+  tr->loss_slot = 4; tr->loss_div = mw.uniform ? (float)mw.run : 1.0f; tr->run_tokens = (uint64_t)k * (uint64_t)tr->N;
+  tr->grads_ready = false;
+  int64_t last = -1, done = 0;
+  for (int64_t i = 0; i < k; ++i) if (mw.w[i] != 0.0f) last = i;
+  ojc_tensor acc = T1(tr->gacc, OJC_F32, tr->flat_n), g = T1(tr->g, OJC_F32, tr->flat_n);
+  for (int64_t i = 0; i < k; ++i) {
+    if (mw.w[i] == 0.0f) continue;          // no valid target: contributes nothing and is not run (trainer.rs:925-931)
+    OJC_CUDA(be, cudaMemcpyAsync(tr->ids, ids_host[i], (size_t)tr->N * 4, cudaMemcpyHostToDevice, be->stream), op);
+    OJC_CUDA(be, cudaMemcpyAsync(tr->targets, targets_host[i], (size_t)tr->N * 4, cudaMemcpyHostToDevice, be->stream), op);
+    tr->seed_now = mw.w[i] * tr->cfg.loss_seed;
+    OJC_TRY(gradient_pass(tr, tr->ids, tr->targets));
+    // accumulate_grad in micro-batch order (trainer.rs:969-974): the sum of the earlier micro-batches waits in gacc while a backward
+    // writes g; the last one adds the two into g, where the buckets, the clip and the optimizer read (a + b == b + a bit for bit)
+    if (done > 0 && i == last) OJC_TRY(ojc_accumulate_grad(be, &g, &acc));
+    else if (done > 0) OJC_TRY(ojc_accumulate_grad(be, &acc, &g));
+    else if (i != last) OJC_CUDA(be, cudaMemcpyAsync(tr->gacc, tr->g, (size_t)tr->flat_n * 4, cudaMemcpyDeviceToDevice, be->stream), op);
+    loss_sum_kernel<<<1, 1, 0, be->stream>>>(tr->stats, mw.w[i], done == 0, !mw.uniform && mw.w[i] != 1.0f);
+    OJC_LAUNCHED(be, op);
+    done += 1;
+  }
+  // the bucket events of the last backward predate the final sum: a data-parallel exchange must wait for it
+  if (done > 1) for (auto& b : tr->buckets) OJC_CUDA(be, cudaEventRecord(b.ready, be->stream), "bucket_ready");
+  tr->grads_ready = true;
+  return OJC_OK;
+}
+
+static ojc_status finish_step(ojc_trainer* tr, ojc_step_report* report);
 
 ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
   const char* op = "trainer_apply";
@@ -746,20 +918,34 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
   const float* gp = tr->g;
   const int64_t glen = tr->flat_n;
   const bool clip = tr->cfg.grad_clip > 0.0f;
+  // this step's learning rates (optimizer_configs, trainer.rs:860-883); a refusal here leaves everything unchanged
+  OJC_TRY(begin_step(tr));
+  double adam_lr = 0.0, matrix_lr = 0.0;
+  OJC_TRY(scaled_lr(tr->cfg.adam_lr, tr->lr_mult, &adam_lr));
+  OJC_TRY(scaled_lr(tr->cfg.matrix_lr, tr->lr_mult, &matrix_lr));
   // stats[0] loss, [1] grad norm, [2] clip scale. A failure from here on leaves parameters partly stepped: poison.
   auto run = [&]() -> ojc_status {
     OJC_TRY(grad_norm_device(be, &gp, &glen, 1, clip ? tr->cfg.grad_clip : -1.0f, tr->stats + 1));
-    const float* scale = clip ? tr->stats + 2 : nullptr;
+    step_gate_kernel<<<1, 1, 0, be->stream>>>(tr->stats, tr->loss_slot);
+    OJC_LAUNCHED(be, op);
+    const float* scale = tr->stats + 2;     // 1 without clipping; STEP_CALLED_OFF when the norm or the loss is not finite
+    bool first_update = true;
+    auto injected = [&]() -> ojc_status {
+      if (!first_update || tr->inject != 2) { first_update = false; return OJC_OK; }
+      tr->inject = 0;
+      return ojc_fail(OJC_ERR_BACKEND, op, "injected failure inside the optimizer phase");
+    };
     // AdamW is element-wise with one configuration per group, so neighbouring AdamW slots go out as one launch over the
     // flat buffers (the zero padding between slots stays zero: p = g = m = v = 0 is a fixed point of the update).
     // the hybrid recipe runs AdamW without decay on embeddings and vectors (ADAM_HYBRID_WEIGHT_DECAY, ojas-cpu/src/train.rs:31-37)
-    const ojc_adamw_config ac{tr->cfg.adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.optimizer == 1 ? 0.0 : tr->cfg.adam_weight_decay};
+    const ojc_adamw_config ac{adam_lr, tr->cfg.adam_beta1, tr->cfg.adam_beta2, tr->cfg.adam_eps, tr->cfg.optimizer == 1 ? 0.0 : tr->cfg.adam_weight_decay};
     int64_t run_begin = -1, run_end = -1;
     auto flush = [&]() -> ojc_status {
       if (run_begin < 0) return OJC_OK;
       bf16* mir = tr->mirror ? tr->mirror + run_begin : nullptr;
       ojc_status r = adamw_device(be, tr->w + run_begin, tr->g + run_begin, tr->m1 + run_begin, tr->m2 + run_begin, mir, run_end - run_begin, tr->step, ac, scale);
       run_begin = run_end = -1;
+      if (r == OJC_OK) r = injected();
       return r;
     };
     // Muon matrices are stepped in groups of one shape (batched Newton-Schulz products): gather them here, in table order
@@ -780,7 +966,7 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
       }
     }
     OJC_TRY(flush());
-    const ojc_muon_config mc{tr->cfg.matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
+    const ojc_muon_config mc{matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
     for (const auto& gr : muon_groups) {
       const size_t chunk = 48;   // the group kernels' pointer table
       for (size_t first = 0; first < gr.second.size(); first += chunk) {
@@ -791,6 +977,7 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
           pp[i] = tr->W(q); gg[i] = tr->G(q); mm[i] = tr->m1 + q.offset; mir[i] = tr->mirror ? tr->mirror + q.offset : nullptr;
         }
         OJC_TRY(muon_group_device(be, pp.data(), gg.data(), mm.data(), tr->mirror ? mir.data() : nullptr, (int64_t)count, gr.first.first, gr.first.second, mc, scale));
+        OJC_TRY(injected());
       }
     }
     return OJC_OK;
@@ -801,18 +988,34 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
   tr->grads_ready = false;
   tr->eager_begin = tr->eager_end = 0;
   if (grad_norm_out) {
-    st = ojc_download(be, grad_norm_out, tr->stats + 1, 4);
-    if (st != OJC_OK) tr->poisoned = true;
+    ojc_step_report rep{};
+    st = finish_step(tr, &rep);
+    *grad_norm_out = rep.grad_norm;
   }
   return st;
 }
 
+// The one readback of the step: loss, norm, the called-off count and the deferred fault word (Trainer::finish, trainer.rs:1031-1046).
 static ojc_status finish_step(ojc_trainer* tr, ojc_step_report* report) {
-  // the one readback of the step: loss, norm and the deferred fault word (Trainer::finish, trainer.rs:1031-1046)
-  float host[3] = {0, 0, 1};
-  ojc_status st = ojc_download(tr->be, host, tr->stats, 12);
+  float host[5] = {0, 0, 1, 0, 0};
+  ojc_status st = ojc_download(tr->be, host, tr->stats, 20);
+  const uint64_t called_off = host[3] > 0.0f ? (uint64_t)host[3] : 0;
+  if (report) {
+    report->loss = host[tr->loss_slot] / tr->loss_div;     // MicroWeights::report (trainer.rs:1122-1129)
+    report->grad_norm = host[1]; report->tokens = tr->run_tokens; report->lr_multiplier = tr->lr_mult;
+  }
+  if (called_off && (st == OJC_OK || st == OJC_ERR_NON_FINITE)) {
+    // the optimizer kernels returned without writing: parameters, moments and the step count are what they were
+    cudaMemsetAsync(tr->stats + 3, 0, 4, tr->be->stream);
+    tr->step -= std::min<uint64_t>(called_off, tr->step);
+    if (report) report->step = tr->step;
+    if (tr->eager_used) tr->poisoned = true;               // some blocks had been stepped under backward already
+    return st == OJC_OK ? ojc_fail(OJC_ERR_NON_FINITE, "Trainer::step", "the loss or the gradient norm is not finite; no parameter was updated") : st;
+  }
   if (st != OJC_OK) { tr->poisoned = true; return st; }
-  if (report) { report->loss = host[0]; report->grad_norm = host[1]; report->step = tr->step; report->tokens = (uint64_t)tr->N; }
+  if (report) report->step = tr->step;
+  if (!std::isfinite(host[tr->loss_slot])) { tr->poisoned = true; return ojc_fail(OJC_ERR_NON_FINITE, "Trainer::step", "the loss is not finite"); }
+  tr->consecutive_skips = 0;     // any committed step ends a run of skips (trainer.rs:849-850)
   return OJC_OK;
 }
 
@@ -837,6 +1040,40 @@ ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uin
   if (st != OJC_OK) { if (tr && tr->eager_end > tr->eager_begin) tr->poisoned = true; return st; }
   OJC_TRY(ojc_trainer_apply(tr, nullptr));
   return finish_step(tr, report);
+}
+
+ojc_status ojc_trainer_run(ojc_trainer* tr, const uint32_t* const* ids_host, const uint32_t* const* targets_host, int64_t k, ojc_step_report* report) {
+  OJC_TRY(ojc_trainer_run_gradients(tr, ids_host, targets_host, k));
+  OJC_TRY(ojc_trainer_apply(tr, nullptr));
+  return finish_step(tr, report);
+}
+
+ojc_status ojc_trainer_resolve_failure(ojc_trainer* tr, ojc_status run_status, int32_t* advance_cursor) {
+  if (advance_cursor) *advance_cursor = 0;
+  if (!tr) return ojc_fail(OJC_ERR_BACKEND, "Trainer::step", "null trainer");
+  if (run_status == OJC_OK) { if (advance_cursor) *advance_cursor = 1; return OJC_OK; }
+  const bool skippable = !tr->poisoned && tr->cfg.on_nonfinite == 1 && run_status == OJC_ERR_NON_FINITE;
+  if (!skippable) return run_status;
+  constexpr uint32_t MAX_CONSECUTIVE_SKIPS = 8;   // trainer.rs:81
+  if (tr->consecutive_skips >= MAX_CONSECUTIVE_SKIPS)
+    return ojc_fail(OJC_ERR_OUT_OF_RANGE, "Trainer::step", "9 consecutive non-finite steps under SkipBatch; the run is not recovering");
+  if (advance_cursor) *advance_cursor = 1;
+  tr->consecutive_skips += 1;
+  return run_status;
+}
+
+int32_t ojc_trainer_state(ojc_trainer* tr) { return tr && tr->poisoned ? 1 : 0; }
+
+ojc_status ojc_lr_multiplier(const ojc_train_config* cfg, uint64_t step, double* multiplier) {
+  if (!cfg || !multiplier) return ojc_fail(OJC_ERR_BACKEND, "lr_schedule", "null argument");
+  return schedule_multiplier(*cfg, step, multiplier);
+}
+
+ojc_status ojc_trainer_inject_failure(ojc_trainer* tr, int32_t where) {
+  OJC_TRY(check_live(tr, "trainer_inject_failure"));
+  if (where < 0 || where > 2) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "trainer_inject_failure", "where must be 0 (none), 1 (gradient pass) or 2 (optimizer phase)");
+  tr->inject = where;
+  return OJC_OK;
 }
 
 ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* logits_host) {

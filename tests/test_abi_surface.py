@@ -40,3 +40,24 @@ def test_flops_per_token_matches_the_scope_table():
     assert spec.matmul_params() == 123_678_720
     assert abs(spec.flops_per_token(1024) - 7.9870e8) / 7.9870e8 < 1e-4
     assert ModelSpec.nanolab_124m(hidden=3072).matmul_params() == 151_990_272
+
+
+def test_schedule_multipliers_of_the_library_match_nanolab(golden_dir):
+    """ojc_lr_multiplier is host arithmetic (no device): pinned to the reference's schedule fixture at LR_MULT_REL_TOL 1e-12
+    (ojas-oracle/src/parity.rs:60) and to the refusals of ojas-cpu/src/schedule.rs."""
+    import json
+    from ojas_b200 import OjasError, TrainConfig
+    fx = json.loads((golden_dir / "tiny/lr_schedules.json").read_text())
+    for name in ("acceptance_cosine", "acceptance_wsd", "tiny_cosine", "tiny_wsd"):
+        s = fx[name]
+        cfg = TrainConfig(schedule=s["schedule"], warmup_steps=s["warmup_steps"], total_steps=s["total_steps"], decay_frac=s["wsd_decay_frac"])
+        for step, want in enumerate(s["multipliers"]):
+            assert abs(cfg.lr_multiplier(step) - want) <= 1e-12 * abs(want), (name, step)
+    assert TrainConfig().lr_multiplier(123) == 1.0
+    assert TrainConfig(schedule="cosine", total_steps=10).lr_multiplier(0) == 1.0        # warmup 0: the decay branch at t = 0
+    assert abs(TrainConfig(schedule="cosine", total_steps=10).lr_multiplier(5000) - 0.1) < 1e-15
+    for bad, step in ((TrainConfig(schedule="wsd", total_steps=10), 11), (TrainConfig(schedule="cosine", total_steps=0), 0),
+                      (TrainConfig(schedule="wsd", total_steps=10, decay_frac=1.5), 0), (TrainConfig(schedule="cosine", total_steps=10), (1 << 64) - 1)):
+        with pytest.raises(OjasError) as e:
+            bad.lr_multiplier(step)
+        assert e.value.kind == "OutOfRange"

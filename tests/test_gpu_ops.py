@@ -464,3 +464,78 @@ def test_cached_attention_refusals(be):
     with pytest.raises(OjasError) as e:
         be.sync()
     assert e.value.kind == "NonFinite"
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_fused_linear_cross_entropy_with_ignore_and_a_collapsed_row(be, bf16):
+    """The fused tied-head loss with an ignore index and a row whose softmax rounds to one-hot (the target-excluded form of
+    ojas-cpu/src/fused_ce.rs:22-29): loss, both gradients, zero gradient rows where the target is ignored; every target ignored
+    has no mean (NonFinite at the next sync)."""
+    from ojas_b200 import DType, OjasError
+    rows, dim, vocab, ignore = 300, 64, 1000, 11
+    x, w = rnd(1, (rows, dim)), rnd(2, (vocab, dim), 0.3)
+    rng = orc.SplitMix64(3)
+    targets = np.array([ignore if i % 7 == 2 else rng.below(vocab) for i in range(rows)], np.uint32)
+    x[5] = 24.0 * w[targets[5]] / np.linalg.norm(w[targets[5]])     # one logit far above the rest: the row collapses
+    if bf16:
+        x, w = orc.round_bf16(x), orc.round_bf16(w)
+    oloss, ogx, ogw = orc.linear_cross_entropy_mean(x, w, targets, ignore=ignore)
+    dt = DType.BF16 if bf16 else DType.F32
+    loss, gx, gw = be.linear_cross_entropy_mean(be.upload(x, dt), be.upload(w, dt), be.upload(targets), ignore_index=ignore, chunk=(128, 0), grad_input_dtype=DType.F32)
+    assert abs(loss.numpy()[0] - oloss) <= (1e-4 if bf16 else FWD_TOL) * abs(oloss)
+    tol = 1e-2 if bf16 else GRAD_TOL
+    assert rel(gx.numpy(), ogx) <= tol and rel(gw.numpy(), ogw) <= tol
+    assert not np.any(gx.numpy()[targets == ignore])
+    with pytest.raises(OjasError) as e:
+        be.linear_cross_entropy_mean(be.upload(x, dt), be.upload(w, dt), be.upload(np.full(rows, ignore, np.uint32)), ignore_index=ignore)
+        be.sync()
+    assert e.value.kind == "NonFinite"
+
+
+def test_linear_backward_input_on_the_tensor_core_tier(be):
+    from ojas_b200 import DType
+    rows, kin, nout = 384, 768, 520
+    w, gy = orc.round_bf16(rnd(12, (nout, kin), 0.5)), orc.round_bf16(rnd(13, (rows, nout), 0.5))
+    ogx = orc.gemm(gy, w)
+    gx = be.linear_backward_input(be.upload(w, DType.BF16), be.upload(gy, DType.BF16), out_dtype=DType.F32)
+    assert rel(gx.numpy(), ogx) <= FWD_TOL
+
+
+def test_accumulate_grad_refuses_a_non_finite_sum(be):
+    """accumulate_grad never stores a sum that is not finite (ojas-cpu/src/accum.rs:33-115); on the device the refusal is the deferred
+    fault the next sync reports, and the elements whose sums are finite are the ordinary sums."""
+    from ojas_b200 import OjasError
+    for n in (4096, 4099):                      # the 128-bit and the scalar forms
+        a, g = rnd(1, (n,)), rnd(2, (n,))
+        a[17], g[100], g[200] = 3.0e38, np.inf, np.nan
+        g[17] = 3.0e38                           # finite operands, overflowing sum
+        acc = be.upload(a)
+        be.accumulate_grad(acc, be.upload(g))
+        with pytest.raises(OjasError) as e:
+            be.sync()
+        assert e.value.kind == "NonFinite" and "accumulate_grad" in str(e.value)
+        got, bad = acc.numpy(), np.array([17, 100, 200])
+        assert np.array_equal(got[bad], a[bad])
+        keep = np.ones(n, bool); keep[bad] = False
+        assert np.array_equal(got[keep], (a + g)[keep])
+    be.sync()                                    # reported once: the fault word is clear again
+
+
+def test_optimizer_scratch_bytes_bounds_what_a_step_takes(be):
+    """optimizer_scratch_bytes (ojas-core/src/backend.rs:953) is the preflight bound of Trainer::new (trainer.rs:401-426): AdamW takes
+    none, a Muon step's peak above the live bytes stays within the bound for both Newton-Schulz precisions."""
+    from ojas_b200 import MuonNs5Config
+    assert be.optimizer_scratch_bytes("adamw", 768, 2048) == 0
+    for rows, cols in ((768, 768), (2048, 768), (12, 768), (768, 2048)):
+        bound = be.optimizer_scratch_bytes("muon", rows, cols)
+        assert bound >= rows * cols * 4
+        for bf in (False, True):
+            p, g, m = be.upload(rnd(1, (rows, cols), 0.02)), be.upload(rnd(2, (rows, cols), 0.01)), be.zeros((rows, cols))
+            be.sync()
+            live = be.budget()["live"]
+            import ctypes as C
+            from ojas_b200._lib import lib
+            lib.ojc_reset_peak(be._handle)
+            be.muon_ns5_step(p, g, m, MuonNs5Config(0.025, 0.95, 0.1, True, bf))
+            be.sync()
+            assert be.budget()["peak"] - live <= bound, (rows, cols, bf)

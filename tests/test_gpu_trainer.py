@@ -265,7 +265,7 @@ def test_muon_bf16_groups_run_as_batched_tensor_core_products(be):
 
 
 @pytest.mark.parametrize("clip", [1.0, 0.0])
-def test_weight_gradients_on_the_side_stream_are_the_same_bits(be, c1, monkeypatch, clip):
+def test_weight_gradients_on_the_side_stream_are_the_same_bits(be, c1, clip):
     """Under bf16 autocast the weight-gradient GEMMs run on a second stream beside the dX chain. Same kernels, same split
     counts, only the stream differs: every gradient, the loss and the stepped parameters must equal the one-stream run bit for bit.
     Without clipping (clip 0) a one-call AdamW step also updates each block on that stream while backward is still running."""
@@ -273,9 +273,9 @@ def test_weight_gradients_on_the_side_stream_are_the_same_bits(be, c1, monkeypat
     kw, params, x, y, _, _, _ = c1
     by_name = {p.name: v for p, v in zip(orc.param_table(orc.Spec(**kw)), params)}
     runs = []
-    for lane in ("0", "1"):
-        monkeypatch.setenv("OJC_SIDE_LANE", lane)
+    for lane in (False, True):
         tr = make_trainer(be, ModelSpec(**kw), by_name, 8, 256, autocast_bf16=True, optimizer="adamw", adam_lr=3e-4, adam_weight_decay=0.1, grad_clip=clip)
+        tr.overlap_weight_grads(lane)
         loss = tr.gradients(x, y)
         grads = [tr.get_grad(i).copy() for i in range(len(tr.params))]
         for _ in range(3):

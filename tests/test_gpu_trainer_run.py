@@ -1,0 +1,287 @@
+"""The reference's device model-parity suite (ojas-model/tests/oracle_parity.rs:391-507, run there under GPU_GATES :83-110) on
+this backend's step driver: the 5-step torch traces with gradient norms and schedule multipliers, the 40-step loss curves of both
+Newton-Schulz precisions, and the bf16-autocast divergence bound; then the trainer's state machine (ojas-model/tests/trainer.rs):
+a non-finite step changes nothing, SkipBatch moves the cursor at most eight times in a row, a failure before the optimizer leaves
+the trainer Ready and one inside it poisons.
+
+Gates (ojas-oracle/src/parity.rs:29-74 with the device overrides of oracle_parity.rs:83-110): trace loss |d| <= 1e-4 nats, trace
+parameters 1e-4 normwise (5e-2 under bf16 NS5), gradient norm 2e-4 relative, multiplier 1e-12 relative, curve 5e-4 for steps 1-10
+and 2e-3 after, last loss at least 1 nat under ln V, autocast divergence max(2e-3, 2 x torch's own worst gap)."""
+import json
+import math
+
+import numpy as np
+import pytest
+from safetensors import safe_open
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TRACE_LOSS_ABS, TRACE_PARAM, TRACE_BF16_PARAM, GRAD_NORM_REL = 1e-4, 1e-4, 5e-2, 2e-4
+CURVE_EARLY_ABS, CURVE_EARLY_STEPS, CURVE_LATE_ABS, CURVE_MIN_DROP, AUTOCAST_GAP_FACTOR = 5e-4, 10, 2e-3, 1.0, 2.0
+
+
+@pytest.fixture(scope="module")
+def be():
+    from ojas_b200 import CudaBackend
+    backend = CudaBackend(0, 16 << 30)
+    yield backend
+    backend.close()
+
+
+def load(path):
+    f = safe_open(str(path), "np")
+    return {k: f.get_tensor(k) for k in f.keys()}, f.metadata()
+
+
+def tiny(golden_dir):
+    from ojas_b200 import ModelSpec
+    init, meta = load(golden_dir / "tiny/init.safetensors")
+    s = json.loads(meta["ojas.spec"])
+    kw = {k: s[k] for k in ("vocab", "n_embd", "n_layer", "n_head", "n_kv_head", "head_dim", "hidden", "max_seq", "rope_base", "rms_eps")}
+    return ModelSpec(**kw), orc.Spec(**kw), init
+
+
+def trace(golden_dir, ns5):
+    want, meta = load(golden_dir / f"tiny/trace_ns5_{ns5}.safetensors")
+    info = json.loads(meta["ojas.oracle"])
+    return want, info, info["config"]
+
+
+def train_config(cfg, **over):
+    """The trainer config of oracle_parity.rs:137-176 from the fixture's nanolab config."""
+    from ojas_b200 import TrainConfig
+    kw = dict(optimizer="muon", matrix_lr=cfg["matrix_lr"], adam_lr=cfg["lr"], muon_momentum=cfg["muon_momentum"], muon_weight_decay=cfg["weight_decay"],
+              adam_beta1=cfg["beta1"], adam_beta2=cfg["beta2"], adam_eps=cfg["eps"], grad_clip=cfg["grad_clip"], schedule=cfg["schedule"],
+              warmup_steps=cfg["warmup_steps"], total_steps=cfg["lr_max_steps"] or cfg["max_steps"], decay_frac=cfg["wsd_decay_frac"])
+    kw.update(over)
+    return TrainConfig(**kw)
+
+
+def open_trainer(be, spec, init, cfg, tcfg):
+    from ojas_b200 import Trainer
+    from ojas_b200.data import BatchSampler, TokenBin
+    tr = Trainer(be, spec, tcfg, cfg["batch_size"], cfg["block_size"])
+    tr.set_params([init[p.name] for p in tr.params])
+    return tr
+
+
+def feed(golden_dir, cfg):
+    from ojas_b200.data import BatchSampler, TokenBin
+    bin_ = TokenBin.open(golden_dir / "tiny/tokens.bin")
+    return bin_, BatchSampler(len(bin_), cfg["block_size"], cfg["batch_size"], cfg["seed"])
+
+
+def run_steps(be, golden_dir, ns5, steps, **over):
+    spec, _, init = tiny(golden_dir)
+    want, info, cfg = trace(golden_dir, ns5)
+    tr = open_trainer(be, spec, init, cfg, train_config(cfg, ns5_bf16=ns5 == "bf16", **over))
+    bin_, sampler = feed(golden_dir, cfg)
+    reports = [tr.step_sampled(sampler, bin_, cfg["grad_accum"]) for _ in range(steps)]
+    return tr, reports, want, info
+
+
+@pytest.mark.parametrize("ns5", ["f32", "bf16"])
+def test_five_step_trace_with_grad_norms_and_schedule(be, golden_dir, ns5):
+    tr, reports, want, info = run_steps(be, golden_dir, ns5, 5)
+    for i, r in enumerate(reports):
+        assert abs(r.loss - info["mean_loss"][i]) <= TRACE_LOSS_ABS, (i, r.loss, info["mean_loss"][i])
+        assert abs(r.grad_norm - info["grad_norm"][i]) <= GRAD_NORM_REL * info["grad_norm"][i], (i, r.grad_norm)
+        assert abs(r.lr_multiplier - info["lr_mult"][i]) <= 1e-12 * abs(info["lr_mult"][i]), (i, r.lr_multiplier)
+        assert r.step == i + 1 and r.tokens == 2 * 2 * 32
+    tol = TRACE_PARAM if ns5 == "f32" else TRACE_BF16_PARAM
+    for i, p in enumerate(tr.params):
+        w = want[p.name].astype(np.float64)
+        got = tr.get_param(i)
+        if not np.any(w):
+            assert not np.any(got), p.name
+        else:
+            assert np.linalg.norm(got - w) / np.linalg.norm(w) <= tol, (p.name, np.linalg.norm(got - w) / np.linalg.norm(w))
+    tr.close()
+
+
+def check_curve(losses, want, vocab):
+    for i, (g, w) in enumerate(zip(losses, want)):
+        assert abs(g - w) <= (CURVE_EARLY_ABS if i < CURVE_EARLY_STEPS else CURVE_LATE_ABS), (i + 1, g, w)
+    assert math.log(vocab) - losses[-1] >= CURVE_MIN_DROP
+
+
+@pytest.mark.parametrize("ns5", ["f32", "bf16"])
+def test_forty_step_curve(be, golden_dir, ns5):
+    tr, reports, _, info = run_steps(be, golden_dir, ns5, 40)
+    check_curve([r.loss for r in reports], info["mean_loss"], tr.spec.vocab)
+    tr.close()
+
+
+def test_autocast_bf16_loss_divergence_is_bounded(be, golden_dir):
+    """check_autocast_divergence (parity.rs:645-700): this backend's bf16-autocast run against its own f32 run on the f32-NS5 trace."""
+    gap = json.loads((golden_dir / "tiny/autocast_gap.json").read_text())
+    torch_worst = max(abs(a - b) for a, b in zip(gap["f32_mean_loss"], gap["bf16_mean_loss"]))
+    bound = max(CURVE_LATE_ABS, AUTOCAST_GAP_FACTOR * torch_worst)
+    runs = []
+    for autocast in (False, True):
+        tr, reports, _, _ = run_steps(be, golden_dir, "f32", 40, autocast_bf16=autocast)
+        runs.append([r.loss for r in reports])
+        vocab = tr.spec.vocab
+        tr.close()
+    f32, bf16 = runs
+    assert f32 != bf16
+    assert all(np.isfinite(f32)) and all(np.isfinite(bf16))
+    worst = max(abs(a - b) for a, b in zip(f32, bf16))
+    assert worst <= bound, (worst, bound)
+    assert bf16[-1] <= math.log(vocab) - CURVE_MIN_DROP
+
+
+def test_uneven_micro_batches_are_weighted_by_their_valid_targets(be, golden_dir):
+    """MicroWeights with an ignore index (trainer.rs:1083-1119): weights n_i / N, losses scaled on the device, an all-ignored
+    micro-batch only has its ids checked. Against the oracle's restatement of Trainer::run, two steps."""
+    spec, ospec, init = tiny(golden_dir)
+    _, _, cfg = trace(golden_dir, "f32")
+    bin_, sampler = feed(golden_dir, cfg)
+    table = orc.param_table(ospec)
+    ignore = 7
+    otr = orc.TrainerOracle(ospec, [init[i.name] for i in table], schedule=("wsd", 1, 10, 0.5), ignore=ignore)
+    tr = open_trainer(be, spec, init, cfg, train_config(cfg, schedule="wsd", warmup_steps=1, total_steps=10, decay_frac=0.5, ignore_index=ignore))
+    for step in range(2):
+        batches = [sampler.next_batch(bin_) for _ in range(3)]
+        batches = [(x, y.copy()) for x, y in batches]
+        batches[0][1][0, :20] = ignore                # 44 of 64 targets count
+        batches[1][1][:] = ignore                     # none: skipped
+        want_loss, want_norm, want_mult = otr.run(batches)
+        rep = tr.run(batches)
+        assert abs(rep.loss - want_loss) <= 1e-5 * abs(want_loss) and abs(rep.grad_norm - want_norm) <= 1e-4 * want_norm
+        assert rep.lr_multiplier == want_mult and rep.tokens == 3 * 64
+    for i, p in enumerate(tr.params):
+        w = otr.params[i].astype(np.float64)
+        assert np.linalg.norm(tr.get_param(i) - w) <= 1e-4 * max(np.linalg.norm(w), 1e-30), p.name
+    tr.close()
+
+
+def state_of(tr):
+    out = [tr.get_param(i).tobytes() for i in range(len(tr.params))]
+    for i, p in enumerate(tr.params):
+        if p.trains:
+            out.append(tr.get_moment(i, 0).tobytes())
+            if p.group == "adamw":
+                out.append(tr.get_moment(i, 1).tobytes())
+    return out
+
+
+@pytest.mark.parametrize("autocast", [False, True])
+def test_a_non_finite_gradient_changes_nothing_and_the_trainer_stays_ready(be, golden_dir, autocast):
+    """Trainer::run refuses a non-finite gradient norm before any update (trainer.rs:824-838). Here the optimizer kernels find it on
+    the device and return without writing: parameters, moments and the step count keep their bits, the call reports NonFinite, and the
+    next step with finite inputs trains."""
+    from ojas_b200 import OjasError
+    spec, _, init = tiny(golden_dir)
+    _, _, cfg = trace(golden_dir, "f32")
+    tr = open_trainer(be, spec, init, cfg, train_config(cfg, autocast_bf16=autocast, ns5_bf16=autocast))
+    bin_, sampler = feed(golden_dir, cfg)
+    tr.step_sampled(sampler, bin_, 2)                                  # moments are no longer zero
+    norm1 = next(i for i, p in enumerate(tr.params) if p.name == "blocks.0.norm1.weight")
+    good = tr.get_param(norm1)
+    bad = good.copy()
+    bad[3] = np.nan
+    tr.set_param(norm1, bad)
+    before, cursor = state_of(tr), sampler.cursor()
+    with pytest.raises(OjasError) as e:
+        tr.step_sampled(sampler, bin_, 2)
+    assert e.value.kind == "NonFinite" and tr.state == "Ready" and tr.steps_done == 1
+    assert state_of(tr) == before
+    assert sampler.cursor() == cursor                                   # NonFinitePolicy::Abort keeps the cursor: the next step retries the batches
+    tr.set_param(norm1, good)
+    rep = tr.step_sampled(sampler, bin_, 2)
+    assert rep.step == 2 and np.isfinite(rep.loss)
+    tr.close()
+
+
+def test_skip_batch_moves_the_cursor_at_most_eight_times_in_a_row(be, golden_dir):
+    """NonFinitePolicy::SkipBatch (trainer.rs:686-708): each non-finite step still returns the error but the cursor moves past its
+    batches; the ninth in a row is OutOfRange and keeps the cursor; a committed step clears the count."""
+    from ojas_b200 import OjasError
+    spec, _, init = tiny(golden_dir)
+    _, _, cfg = trace(golden_dir, "f32")
+    tr = open_trainer(be, spec, init, cfg, train_config(cfg, on_nonfinite="skip_batch"))
+    bin_, sampler = feed(golden_dir, cfg)
+    norm1 = next(i for i, p in enumerate(tr.params) if p.name == "blocks.0.norm1.weight")
+    good = tr.get_param(norm1)
+    bad = good.copy()
+    bad[0] = np.inf
+    tr.set_param(norm1, bad)
+    for n in range(8):
+        cursor = sampler.cursor()
+        with pytest.raises(OjasError) as e:
+            tr.step_sampled(sampler, bin_, 2)
+        assert e.value.kind == "NonFinite" and sampler.cursor() != cursor and tr.state == "Ready"
+    cursor = sampler.cursor()
+    with pytest.raises(OjasError) as e:
+        tr.step_sampled(sampler, bin_, 2)
+    assert e.value.kind == "OutOfRange" and sampler.cursor() == cursor
+    tr.set_param(norm1, good)
+    assert tr.step_sampled(sampler, bin_, 2).step == 1                  # clears the run of skips
+    tr.set_param(norm1, bad)
+    with pytest.raises(OjasError) as e:
+        tr.step_sampled(sampler, bin_, 2)
+    assert e.value.kind == "NonFinite"
+    tr.close()
+
+
+def test_a_failure_before_the_optimizer_changes_nothing_and_one_inside_it_poisons(be, golden_dir):
+    """ojas-model/tests/trainer.rs with the Probe double (tests/common/mod.rs:647): here the failure is made on the host by the
+    driver's own injection point; no device fault is involved."""
+    from ojas_b200 import OjasError
+    spec, _, init = tiny(golden_dir)
+    _, _, cfg = trace(golden_dir, "f32")
+    tr = open_trainer(be, spec, init, cfg, train_config(cfg))
+    bin_, sampler = feed(golden_dir, cfg)
+    tr.step_sampled(sampler, bin_, 2)
+    before, cursor = state_of(tr), sampler.cursor()
+    tr.inject_failure("gradients")
+    with pytest.raises(OjasError) as e:
+        tr.step_sampled(sampler, bin_, 2)
+    assert e.value.kind == "Backend" and tr.state == "Ready" and tr.steps_done == 1 and state_of(tr) == before and sampler.cursor() == cursor
+    assert tr.step_sampled(sampler, bin_, 2).step == 2                 # the same batches, retried
+    tr.inject_failure("optimizer")
+    with pytest.raises(OjasError):
+        tr.step_sampled(sampler, bin_, 2)
+    assert tr.state == "Poisoned"
+    with pytest.raises(OjasError) as e:
+        tr.step_sampled(sampler, bin_, 2)
+    assert e.value.kind == "Poisoned"
+    with pytest.raises(OjasError) as e:
+        tr.gradients(np.zeros((2, 32), np.uint32), np.zeros((2, 32), np.uint32))
+    assert e.value.kind == "Poisoned"
+    tr.close()
+
+
+def test_refusals_come_before_any_work(be, golden_dir):
+    from ojas_b200 import OjasError, TrainConfig, Trainer
+    spec, _, init = tiny(golden_dir)
+    _, _, cfg = trace(golden_dir, "f32")
+    tr = open_trainer(be, spec, init, cfg, train_config(cfg, schedule="wsd", total_steps=3, warmup_steps=0, ignore_index=5))
+    bin_, sampler = feed(golden_dir, cfg)
+    x, y = sampler.next_batch(bin_)
+    launches = be.kernel_launches()
+    with pytest.raises(OjasError) as e:
+        tr.run([])                                                      # no micro-batch
+    assert e.value.kind == "OutOfRange"
+    with pytest.raises(OjasError) as e:
+        tr.run([(x, np.full_like(y, 5))])                               # every target ignored: the mean has no denominator
+    assert e.value.kind == "NonFinite"
+    bad = x.copy()
+    bad[1, 3] = spec.vocab
+    with pytest.raises(OjasError) as e:
+        tr.run([(bad, np.full_like(y, 5))])                             # ...but a corrupt id among them is OutOfRange first
+    assert e.value.kind == "OutOfRange"
+    with pytest.raises(OjasError) as e:
+        tr.run([(x, y), (bad, y)])
+    assert e.value.kind == "OutOfRange" and be.kernel_launches() == launches and tr.state == "Ready"
+    tr.steps_done = 4                                                   # past the wsd schedule's three steps
+    with pytest.raises(OjasError) as e:
+        tr.run([(x, y)])
+    assert e.value.kind == "OutOfRange" and be.kernel_launches() == launches
+    tr.close()
+    with pytest.raises(OjasError) as e:
+        Trainer(be, spec, TrainConfig(schedule="cosine", total_steps=0), 2, 32)
+    assert e.value.kind == "OutOfRange"
