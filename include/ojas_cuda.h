@@ -256,6 +256,37 @@ ojc_status ojc_trainer_logits(ojc_trainer* tr, const uint32_t* ids_host, float* 
    results bit for bit). enable = 0 folds them back into the one stream, e.g. to time each GEMM with the GPU to itself. */
 ojc_status ojc_trainer_overlap_weight_grads(ojc_trainer* tr, int32_t enable);
 int64_t ojc_trainer_bucket_count(ojc_trainer* tr);
+/* The communicator of the data-parallel step (no counterpart in the reference, which has no distributed code; what it keeps is the
+ * arithmetic of K-micro-batch accumulation, trainer.rs:916-1001, with K = world). NCCL is loaded with dlopen at the first call, so a
+ * host that never calls these needs no NCCL. One process per GPU: rank 0 makes a 128-byte id with ojc_comm_unique_id and hands it to
+ * the other ranks by any means of its own (a file, a socket, an environment variable); every rank then calls ojc_comm_init.
+ * ojc_allreduce_start queues one in-place f32 sum per gradient bucket on the communicator's own stream, each behind the bucket's
+ * ready event, so the exchange runs under the rest of backward; ojc_allreduce_wait makes the backend's stream wait for the last one
+ * (the host does not block) and reports an error NCCL met asynchronously. A collective that never completes surfaces as WaitTimeout
+ * from the next bounded host wait (ojc_sync / ojc_download / ojc_trainer_finish). */
+typedef struct ojc_comm ojc_comm;
+ojc_status ojc_comm_unique_id(uint8_t* id128);
+ojc_status ojc_comm_init(ojc_backend* be, int32_t rank, int32_t world, const uint8_t* id128, ojc_comm** out);
+ojc_status ojc_comm_destroy(ojc_comm* comm);
+int32_t ojc_comm_rank(ojc_comm* comm);
+int32_t ojc_comm_world(ojc_comm* comm);
+ojc_status ojc_comm_check(ojc_comm* comm);                                                              /* an asynchronous NCCL error since the last call; never blocks */
+ojc_status ojc_allreduce_start(ojc_comm* comm, ojc_trainer* tr);
+ojc_status ojc_allreduce_wait(ojc_comm* comm, ojc_trainer* tr);
+ojc_status ojc_comm_allreduce(ojc_comm* comm, void* device_data, uint64_t count, int32_t dtype, int32_t op); /* in place on the backend's stream; op 0 sum, 1 max, 2 min */
+ojc_status ojc_comm_broadcast_many(ojc_comm* comm, void* const* device_ptrs, const uint64_t* counts, const int32_t* roots, int64_t n, int32_t dtype); /* one group */
+/* Gives the trainer the communicator: ojc_trainer_run / _step / _step_device then exchange the buckets themselves between backward and
+ * the optimizer (the config's loss_seed should be 1/world). shard_muon != 0 also splits the Muon phase: matrix j of each shape group is
+ * orthogonalised by rank j % world only and its new parameters are broadcast from there, so every rank holds the same parameters but a
+ * matrix's momentum lives on its owner (ojc_trainer_sync_moments broadcasts the momenta, e.g. before a checkpoint). comm NULL detaches. */
+ojc_status ojc_trainer_set_comm(ojc_trainer* tr, ojc_comm* comm, int32_t shard_muon);
+ojc_status ojc_trainer_sync_moments(ojc_trainer* tr);
+/* Device time the backend's stream spent waiting for the gradient exchange in the last finished step: from the end of backward to
+ * the first optimizer kernel, minus nothing (with the exchange fully hidden under backward it is the launch gap only). */
+ojc_status ojc_trainer_exposed_exchange_ms(ojc_trainer* tr, float* ms);
+/* FNV-1a over every parameter's f32 bytes in table order (device -> host copies, then ojc_fnv1a64): equal on every rank of a healthy
+ * data-parallel job. */
+ojc_status ojc_trainer_param_checksum(ojc_trainer* tr, uint64_t* hash);
 ojc_status ojc_trainer_bucket(ojc_trainer* tr, int64_t index, void** device_ptr, uint64_t* floats);
 ojc_status ojc_trainer_bucket_ready_event(ojc_trainer* tr, int64_t index, void** cuda_event);          /* recorded when the bucket's last gradient is written */
 

@@ -687,6 +687,29 @@ class Trainer:
         after its first update kernel."""
         _check(lib.ojc_trainer_inject_failure(self._h, C.c_int32({"none": 0, "gradients": 1, "optimizer": 2}[where])))
 
+    def set_comm(self, comm, shard_muon: bool = False) -> None:
+        """Attach a dp.Communicator (or None): step / step_device / run then sum the gradient buckets across ranks between backward and
+        the optimizer. shard_muon splits the Muon phase: each rank orthogonalises every world-th matrix of a shape group and the new
+        parameters are broadcast from their owners."""
+        _check(lib.ojc_trainer_set_comm(self._h, comm._h if comm is not None else None, C.c_int32(int(shard_muon))))
+        self._comm = comm          # keeps the communicator alive as long as the trainer uses it
+
+    def sync_moments(self) -> None:
+        """Under shard_muon a matrix's momentum lives on its owner rank: broadcast every momentum from its owner (before a checkpoint)."""
+        _check(lib.ojc_trainer_sync_moments(self._h))
+
+    def exposed_exchange_ms(self) -> float:
+        """Device time the library's stream waited for the gradient exchange in the last finished step."""
+        out = C.c_float()
+        _check(lib.ojc_trainer_exposed_exchange_ms(self._h, C.byref(out)))
+        return out.value
+
+    def param_checksum(self) -> int:
+        """FNV-1a over every parameter's f32 bytes in table order: equal on every rank of a healthy data-parallel job."""
+        out = C.c_uint64()
+        _check(lib.ojc_trainer_param_checksum(self._h, C.byref(out)))
+        return out.value
+
     def step_host_ptrs(self, ids_ptr: int, targets_ptr: int) -> StepReport:
         """Same as step() for caller-owned (for example pinned) host buffers given by address."""
         rep = _lib.StepReport()

@@ -27,7 +27,8 @@ ojc_status gemm_auto(ojc_backend* be, const char* op, const GemmOperand& a, cons
 // a bf16 matrix of C's shape (leading dimension src_ld, matrix stride src_bs). It is the combine step the iteration would otherwise run
 // as a kernel of its own after the product, with the same rounding points (ojas-cpu/src/optim.rs:947-974). Needs a bf16 output,
 // alpha 1, no accumulation or split, src_ld % 8 == 0 and a 16-byte aligned src; a non-finite result raises the Muon fault.
+// allow_split = false keeps a single product's reduction in one piece too, so its bits equal those of the same product inside a batch.
 struct NsCombine { const void* src; int64_t src_ld, src_bs; float src_mul, acc_mul; };
 ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
                            int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual,
-                           const NsCombine* combine = nullptr);
+                           const NsCombine* combine = nullptr, bool allow_split = true);

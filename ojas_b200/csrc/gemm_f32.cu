@@ -1,7 +1,8 @@
-// f32-accurate GEMM tier on CUDA cores: C[m,n] (+)= alpha * sum_k A(i,k) B(k,j)
-// over strided views, f32 multiply-accumulate in ascending k per output. This
-// is the parity tier (and the fallback for shapes the tensor-core kernel's TMA
-// alignment rules exclude); the bf16 performance path is gemm_tc.cu.
+// f32 GEMM tier on CUDA cores: C[m,n] (+)= alpha * sum_k A(i,k) B(k,j) over strided views. Every output is the reference's
+// Exact chain ((0 + a0 b0) + a1 b1) + ... with k ascending and a separately rounded multiply and add per step
+// (ojas-cpu/src/gemm.rs:11-16,1044-1083), so with alpha 1 a product here has the bits of the CPU reference's. This is the
+// parity tier (and the fallback for shapes the tensor-core kernel's TMA alignment rules exclude); the bf16 performance
+// path is gemm_tc.cu.
 #include "common.cuh"
 #include "dispatch.cuh"
 #include "gemm.cuh"
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const TA* __restrict__ A,
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));   // never contracted into an fma
     }
     __syncthreads();
   }
@@ -66,9 +67,9 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const TA* __restrict__ A,
       int gn = n0 + tx * TN + j;
       if (gn >= n) continue;
       int64_t o = (int64_t)gm * ldc + gn;
-      float v = alpha * acc[i][j];
-      if (residual) v += residual[o];
-      if (accumulate) v += ldf(C, o);
+      float v = alpha == 1.0f ? acc[i][j] : alpha * acc[i][j];
+      if (residual) v = __fadd_rn(v, residual[o]);
+      if (accumulate) v = __fadd_rn(v, ldf(C, o));
       stf(C, o, v);
     }
   }

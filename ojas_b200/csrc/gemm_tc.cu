@@ -530,7 +530,7 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
 // `batch` independent products of the same shape; matrix i of A / B / C starts a_bs / b_bs / c_bs elements after matrix i - 1.
 ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
                            int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual,
-                           const NsCombine* combine) {
+                           const NsCombine* combine, bool allow_split) {
   if (!gemm_tc_eligible(a, b, c, c_dtype, ldc, m, n, k)) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "operands break the tensor-core kernel's alignment rules");
   if (combine && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine->src_ld % 8 != 0 || combine->src_bs % 8 != 0 || ((uintptr_t)combine->src & 15) != 0 || n < 64))
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the combine epilogue needs a bf16 output, alpha 1, no accumulation and an aligned source");
@@ -573,7 +573,7 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   // the wave efficiency its units reach plus the partial round trip through memory, and take the cheapest (each split
   // keeps at least 8 k-blocks).
   int splits = 1;
-  if (kblocks >= 16 && batch == 1 && !combine) {
+  if (kblocks >= 16 && batch == 1 && !combine && allow_split) {
     const double flops = 2.0 * (double)m * (double)n * (double)k;
     double best = 1e30;
     for (int sp = 1; sp <= 16 && kblocks / sp >= 8; ++sp) {

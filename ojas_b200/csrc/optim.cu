@@ -11,18 +11,34 @@ namespace {
 
 constexpr int NORM_CHUNK = 8192;  // elements per block of the sum-of-squares pass
 
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    v = threadIdx.x < (blockDim.x + 31) / 32 ? red[threadIdx.x] : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  }
+  return v;
+}
+
+
 __global__ void sumsq_partial_kernel(const float* __restrict__ x, int64_t n, double* __restrict__ part, uint32_t* fault, uint32_t op_id) {
-  __shared__ float red[32];
+  // squares and their sum in f64, as the reference's norm (ojas-cpu/src/optim.rs:96-126): an f32-summed norm is off in its last
+  // bit often enough to change the clip coefficient, and with it the last bit of every clipped gradient
+  __shared__ double red[32];
   const int64_t base = (int64_t)blockIdx.x * NORM_CHUNK;
-  float acc = 0.0f;
+  double acc = 0.0;
   for (int i = threadIdx.x; i < NORM_CHUNK; i += blockDim.x) {
     int64_t idx = base + i;
-    if (idx < n) { float v = x[idx]; acc = fmaf(v, v, acc); }
+    if (idx < n) { const double v = (double)x[idx]; acc += v * v; }
   }
-  float t = block_sum(acc, red);
+  const double t = block_sum_f64(acc, red);
   if (threadIdx.x == 0) {
     if (!isfinite(t)) raise_fault(fault, op_id);
-    part[blockIdx.x] = (double)t;
+    part[blockIdx.x] = t;
   }
 }
 
@@ -86,7 +102,7 @@ struct MuonBatch { const float* g[MUON_MAX_BATCH]; float* mom[MUON_MAX_BATCH]; f
 // Also the block partial of sum u^2 (of the bf16-rounded u when ns5 runs in bf16). u: [batch][n], part: [batch][gridDim.x].
 __global__ void muon_momentum_kernel(const MuonBatch mb, float* __restrict__ u_all, int64_t n, float mu, int nesterov, int round_u,
                                      const float* __restrict__ grad_scale, double* __restrict__ part, uint32_t* fault) {
-  __shared__ float red[32];
+  __shared__ double red[32];
   const float* __restrict__ g = mb.g[blockIdx.y];
   float* __restrict__ mom = mb.mom[blockIdx.y];
   float* __restrict__ u = u_all + (int64_t)blockIdx.y * n;
@@ -94,21 +110,23 @@ __global__ void muon_momentum_kernel(const MuonBatch mb, float* __restrict__ u_a
   bool off = false;     // a called-off step still forms u (the later kernels read it) but leaves the momentum buffer alone
   if (grad_scale) { gs = grad_scale[0]; off = gs < 0.0f; if (!(gs < 1.0f) || off) gs = 1.0f; }
   const int64_t base = (int64_t)blockIdx.x * NORM_CHUNK;
-  float acc = 0.0f;
+  // The Frobenius norm is summed in f64, as the reference does (optim.rs:893-900): the norm is rounded to bf16 under
+  // Ns5Precision::Bf16, where an f32-summed value that lands on the other side of a rounding boundary would rescale the whole matrix.
+  double acc = 0.0;
   for (int i = threadIdx.x; i < NORM_CHUNK; i += blockDim.x) {
     int64_t idx = base + i;
     if (idx >= n) break;
     float gi = g[idx];
     if (gs != 1.0f) gi *= gs;
-    const float buf = mu * mom[idx] + gi;
+    const float buf = __fadd_rn(__fmul_rn(mu, mom[idx]), gi);      // a multiply and an add, each rounded (optim.rs:684-700); only Nesterov's step is fused
     float ui = nesterov ? fmaf(mu, buf, gi) : buf;
     if (round_u) ui = round_bf16(ui);
     if (!off) mom[idx] = buf;
     u[idx] = ui;
-    acc = fmaf(ui, ui, acc);
+    acc += (double)ui * (double)ui;
   }
-  float t = block_sum(acc, red);
-  if (threadIdx.x == 0) { if (!isfinite(t) && !off) raise_fault(fault, OP_MUON); part[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = (double)t; }
+  const double t = block_sum_f64(acc, red);
+  if (threadIdx.x == 0) { if (!isfinite(t) && !off) raise_fault(fault, OP_MUON); part[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = t; }
 }
 
 // norm[matrix] = f32 of the f64 square root of its partial sums, added in the order norm_finish_kernel uses
@@ -316,34 +334,35 @@ __global__ void muon_small_ns5_kernel(TX* __restrict__ x_all, int r, int c, floa
   float* A = BX + (size_t)r * c;       // [32][33]
   float* B = A + 32 * 33;              // [32][33]
   TX* x = x_all + (int64_t)blockIdx.x * r * c;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int tid = threadIdx.x;
   const int n = r * c;
   auto rnd = [&](float v) { return bf16_mode ? round_bf16(v) : v; };
   for (int i = tid; i < n; i += blockDim.x) X[i] = ldf(x, i);
   __syncthreads();
   for (int it = 0; it < 5; ++it) {
-    for (int pair = warp; pair < r * r; pair += nwarps) {          // A = X X^T
+    // every product element is one chain over k ascending, a separately rounded multiply and add per step: the reference's
+    // Exact product (ojas-cpu/src/gemm.rs:11-16), so a small matrix steps to the same bits in f32 mode as well as in bf16 mode
+    for (int pair = tid; pair < r * r; pair += blockDim.x) {       // A = X X^T
       const int i = pair / r, j = pair % r;
       float acc = 0.0f;
-      for (int k = lane; k < c; k += 32) acc = fmaf(X[i * c + k], X[j * c + k], acc);
-      acc = warp_sum(acc);
-      if (lane == 0) A[i * 33 + j] = rnd(acc);
+      for (int k = 0; k < c; ++k) acc = __fadd_rn(acc, __fmul_rn(X[i * c + k], X[j * c + k]));
+      A[i * 33 + j] = rnd(acc);
     }
     __syncthreads();
     for (int e = tid; e < r * r; e += blockDim.x) {                // B = b A + c (A A)
       const int i = e / r, j = e % r;
       float acc = 0.0f;
-      for (int k = 0; k < r; ++k) acc = fmaf(A[i * 33 + k], A[k * 33 + j], acc);
+      for (int k = 0; k < r; ++k) acc = __fadd_rn(acc, __fmul_rn(A[i * 33 + k], A[k * 33 + j]));
       const float a2 = rnd(acc), av = A[i * 33 + j];
-      B[i * 33 + j] = bf16_mode ? round_bf16(round_bf16(bcoef * av) + round_bf16(ccoef * a2)) : bcoef * av + ccoef * a2;
+      B[i * 33 + j] = bf16_mode ? round_bf16(round_bf16(bcoef * av) + round_bf16(ccoef * a2)) : __fadd_rn(__fmul_rn(bcoef, av), __fmul_rn(ccoef, a2));
     }
     __syncthreads();
     for (int e = tid; e < n; e += blockDim.x) {                    // X <- a X + B X
       const int i = e / c, k = e % c;
       float acc = 0.0f;
-      for (int j = 0; j < r; ++j) acc = fmaf(B[i * 33 + j], X[j * c + k], acc);
+      for (int j = 0; j < r; ++j) acc = __fadd_rn(acc, __fmul_rn(B[i * 33 + j], X[j * c + k]));
       const float bx = rnd(acc), xv = X[e];
-      const float out = bf16_mode ? round_bf16(round_bf16(acoef * xv) + bx) : acoef * xv + bx;
+      const float out = bf16_mode ? round_bf16(round_bf16(acoef * xv) + bx) : __fadd_rn(__fmul_rn(acoef, xv), bx);
       if (!isfinite(out)) raise_fault(fault, OP_MUON);
       BX[e] = out;
     }
@@ -464,10 +483,12 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
   auto product = [&](const GemmOperand& ga, const GemmOperand& gb, void* cptr, int64_t m_, int64_t n_, int64_t k_, int64_t a_bs, int64_t b_bs, int64_t c_bs,
                      const NsCombine* comb = nullptr, bool* fused = nullptr) -> ojc_status {
     if (fused) *fused = false;
-    if (batch > 1 && bf && n_ >= 64 && a_bs % 8 == 0 && b_bs % 8 == 0 && c_bs % 8 == 0 && gemm_tc_eligible(ga, gb, cptr, dt, n_, m_, n_, k_)) {
+    // One matrix takes the same kernel, tiling and unsplit reduction as a group of them: a matrix's update must not depend on how
+    // many others of its shape are stepped with it (the groups shrink when the Muon phase is split across data-parallel ranks).
+    if (bf && n_ >= 64 && a_bs % 8 == 0 && b_bs % 8 == 0 && c_bs % 8 == 0 && gemm_tc_eligible(ga, gb, cptr, dt, n_, m_, n_, k_)) {
       const bool can = comb && comb->src_ld % 8 == 0 && comb->src_bs % 8 == 0 && ((uintptr_t)comb->src & 15) == 0;
       if (fused) *fused = can;
-      return gemm_tc_batched(be, op, ga, gb, cptr, dt, n_, m_, n_, k_, batch, a_bs, b_bs, c_bs, 1.0f, false, nullptr, can ? comb : nullptr);
+      return gemm_tc_batched(be, op, ga, gb, cptr, dt, n_, m_, n_, k_, batch, a_bs, b_bs, c_bs, 1.0f, false, nullptr, can ? comb : nullptr, false);
     }
     for (int64_t i = 0; i < batch; ++i) {
       GemmOperand ai{(const char*)ga.ptr + i * a_bs * es, ga.dtype, ga.rs, ga.cs}, bi{(const char*)gb.ptr + i * b_bs * es, gb.dtype, gb.rs, gb.cs};
@@ -495,7 +516,7 @@ ojc_status muon_group_device(ojc_backend* be, float* const* p, const float* cons
     OJC_LAUNCHED(be, op);
     const float a = (float)3.4445, b = (float)-4.7750, cc = (float)2.0315;  // MUON_NS5_{A,B,C}, ojas-core/src/backend.rs:144-146
     const size_t small_smem = ((size_t)2 * r * c + 2 * 32 * 33) * 4;
-    const bool small = batch > 1 && r <= 32 && small_smem <= 200 * 1024;     // e.g. the [heads, d] gate weights: one CTA per matrix
+    const bool small = r <= 32 && small_smem <= 200 * 1024;     // e.g. the [heads, d] gate weights: one CTA per matrix, alone or in a group
     if (small) {
       static PerDeviceFlag attr_of;
       bool& attr = attr_of[be->device];

@@ -90,6 +90,12 @@ struct ojc_trainer {
   uint32_t consecutive_skips = 0;
   bool eager_used = false;                      // this step's blocks were stepped during backward, before the norm was known
   int inject = 0;                               // ojc_trainer_inject_failure
+  // data-parallel: the communicator the one-call steps exchange the buckets through, whether the Muon phase is split across
+  // ranks, and the events that time how long the main stream waited for the exchange
+  ojc_comm* comm = nullptr;
+  bool shard_muon = false;
+  cudaEvent_t ev_bwd_end = nullptr, ev_exchanged = nullptr;
+  bool exchange_timed = false;
   // One-call steps with AdamW on every tensor and no clipping: a block's parameters are stepped on the side lane as soon as its
   // gradients are final, under the rest of backward (nothing later reads them); apply() then skips [eager_begin, eager_end).
   bool eager_request = false;
@@ -330,7 +336,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
   // fn's inputs are final on the main stream now; run it on the side lane (or in place when there is none)
   const bool lane = bf && tr->side_stream != nullptr && tr->side_enabled;
   // (only under NonFinitePolicy::Abort: a non-finite gradient found after blocks were stepped poisons the trainer)
-  const bool eager = lane && tr->eager_request && tr->cfg.optimizer == 0 && !(tr->cfg.grad_clip > 0.0f) && L > 0 && tr->cfg.on_nonfinite == 0;
+  const bool eager = lane && tr->eager_request && tr->cfg.optimizer == 0 && !(tr->cfg.grad_clip > 0.0f) && L > 0 && tr->cfg.on_nonfinite == 0 && !tr->comm;
   tr->eager_used = eager;
   tr->eager_begin = tr->eager_end = eager ? tr->params.back().offset : 0;   // grows downwards block by block
   auto on_side = [&](auto&& fn) -> ojc_status {
@@ -716,6 +722,8 @@ ojc_status ojc_trainer_close(ojc_trainer* tr) {
   if (tr->ev_side) cudaEventDestroy(tr->ev_side);
   if (tr->side_scratch) cudaFree(tr->side_scratch);
   if (tr->ev_finish) cudaEventDestroy(tr->ev_finish);
+  if (tr->ev_bwd_end) cudaEventDestroy(tr->ev_bwd_end);
+  if (tr->ev_exchanged) cudaEventDestroy(tr->ev_exchanged);
   if (tr->finish_pool) cudaFree(tr->finish_pool);
   for (void* p : tr->owned) ojc_free(tr->be, p);
   for (auto& b : tr->buckets) if (b.ready) cudaEventDestroy(b.ready);
@@ -910,6 +918,22 @@ ojc_status ojc_trainer_run_gradients(ojc_trainer* tr, const uint32_t* const* ids
 
 static ojc_status finish_step(ojc_trainer* tr, ojc_step_report* report);
 
+// Sum the gradient buckets across the ranks of the trainer's communicator (nothing to do without one).
+static ojc_status exchange(ojc_trainer* tr) {
+  if (!tr->comm || ojc_comm_world(tr->comm) <= 1) return OJC_OK;
+  ojc_backend* be = tr->be;
+  if (!tr->ev_bwd_end) {
+    OJC_CUDA(be, cudaEventCreate(&tr->ev_bwd_end), "exchange");
+    OJC_CUDA(be, cudaEventCreate(&tr->ev_exchanged), "exchange");
+  }
+  OJC_CUDA(be, cudaEventRecord(tr->ev_bwd_end, be->stream), "exchange");
+  OJC_TRY(ojc_allreduce_start(tr->comm, tr));
+  OJC_TRY(ojc_allreduce_wait(tr->comm, tr));
+  OJC_CUDA(be, cudaEventRecord(tr->ev_exchanged, be->stream), "exchange");
+  tr->exchange_timed = true;
+  return OJC_OK;
+}
+
 ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
   const char* op = "trainer_apply";
   OJC_TRY(check_live(tr, op));
@@ -967,7 +991,23 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
     }
     OJC_TRY(flush());
     const ojc_muon_config mc{matrix_lr, tr->cfg.muon_momentum, tr->cfg.muon_weight_decay, 1, tr->cfg.ns5_bf16};
-    for (const auto& gr : muon_groups) {
+    // Split across ranks: matrix j of a shape group belongs to rank j % world, which alone orthogonalises it; the others receive
+    // its new parameters afterwards (every rank saw the same reduced gradient and the same clip scale, so the result is what an
+    // unsplit step gives, and a called-off step broadcasts unchanged parameters).
+    const int world = tr->comm ? ojc_comm_world(tr->comm) : 1, me = tr->comm ? ojc_comm_rank(tr->comm) : 0;
+    const bool split = tr->shard_muon && world > 1;
+    std::vector<void*> bc_ptr; std::vector<uint64_t> bc_count; std::vector<int32_t> bc_root; std::vector<const Param*> received;
+    for (auto& gr : muon_groups) {
+      if (split) {
+        std::vector<const Param*> mine;
+        for (size_t j = 0; j < gr.second.size(); ++j) {
+          const Param* q = gr.second[j];
+          const int owner = (int)(j % (size_t)world);
+          bc_ptr.push_back(tr->W(*q)); bc_count.push_back((uint64_t)q->n); bc_root.push_back(owner);
+          if (owner == me) mine.push_back(q); else received.push_back(q);
+        }
+        gr.second.swap(mine);
+      }
       const size_t chunk = 48;   // the group kernels' pointer table
       for (size_t first = 0; first < gr.second.size(); first += chunk) {
         const size_t count = std::min(chunk, gr.second.size() - first);
@@ -979,6 +1019,10 @@ ojc_status ojc_trainer_apply(ojc_trainer* tr, float* grad_norm_out) {
         OJC_TRY(muon_group_device(be, pp.data(), gg.data(), mm.data(), tr->mirror ? mir.data() : nullptr, (int64_t)count, gr.first.first, gr.first.second, mc, scale));
         OJC_TRY(injected());
       }
+    }
+    if (split && !bc_ptr.empty()) {
+      OJC_TRY(ojc_comm_broadcast_many(tr->comm, bc_ptr.data(), bc_count.data(), bc_root.data(), (int64_t)bc_ptr.size(), OJC_F32));
+      for (const Param* q : received) OJC_TRY(refresh_mirror(tr, *q));
     }
     return OJC_OK;
   };
@@ -1029,6 +1073,7 @@ ojc_status ojc_trainer_step_device(ojc_trainer* tr, const uint32_t* ids_dev, con
   ojc_status st = ojc_trainer_gradients_device(tr, ids_dev, targets_dev);
   if (tr) tr->eager_request = false;
   if (st != OJC_OK) { if (tr && tr->eager_end > tr->eager_begin) tr->poisoned = true; return st; }
+  OJC_TRY(exchange(tr));
   OJC_TRY(ojc_trainer_apply(tr, nullptr));
   return finish_step(tr, report);
 }
@@ -1038,12 +1083,14 @@ ojc_status ojc_trainer_step(ojc_trainer* tr, const uint32_t* ids_host, const uin
   ojc_status st = ojc_trainer_gradients(tr, ids_host, targets_host, nullptr);
   if (tr) tr->eager_request = false;
   if (st != OJC_OK) { if (tr && tr->eager_end > tr->eager_begin) tr->poisoned = true; return st; }
+  OJC_TRY(exchange(tr));
   OJC_TRY(ojc_trainer_apply(tr, nullptr));
   return finish_step(tr, report);
 }
 
 ojc_status ojc_trainer_run(ojc_trainer* tr, const uint32_t* const* ids_host, const uint32_t* const* targets_host, int64_t k, ojc_step_report* report) {
   OJC_TRY(ojc_trainer_run_gradients(tr, ids_host, targets_host, k));
+  OJC_TRY(exchange(tr));
   OJC_TRY(ojc_trainer_apply(tr, nullptr));
   return finish_step(tr, report);
 }
@@ -1073,6 +1120,55 @@ ojc_status ojc_trainer_inject_failure(ojc_trainer* tr, int32_t where) {
   OJC_TRY(check_live(tr, "trainer_inject_failure"));
   if (where < 0 || where > 2) return ojc_fail(OJC_ERR_OUT_OF_RANGE, "trainer_inject_failure", "where must be 0 (none), 1 (gradient pass) or 2 (optimizer phase)");
   tr->inject = where;
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_set_comm(ojc_trainer* tr, ojc_comm* comm, int32_t shard_muon) {
+  OJC_TRY(check_live(tr, "trainer_set_comm"));
+  tr->comm = comm;
+  tr->shard_muon = comm != nullptr && shard_muon != 0;
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_sync_moments(ojc_trainer* tr) {
+  OJC_TRY(check_live(tr, "trainer_sync_moments"));
+  if (!tr->comm || !tr->shard_muon || ojc_comm_world(tr->comm) <= 1 || tr->cfg.optimizer != 1) return OJC_OK;
+  const int world = ojc_comm_world(tr->comm);
+  // the same walk as the optimizer phase: matrix j of a shape group belongs to rank j % world
+  std::vector<std::pair<std::pair<int64_t, int64_t>, int64_t>> seen;
+  std::vector<void*> ptr; std::vector<uint64_t> count; std::vector<int32_t> root;
+  for (const Param& p : tr->params) {
+    if (!p.trains || p.group != GROUP_MUON) continue;
+    const std::pair<int64_t, int64_t> shape{p.shape[0], p.shape[1]};
+    auto it = std::find_if(seen.begin(), seen.end(), [&](const auto& e) { return e.first == shape; });
+    if (it == seen.end()) { seen.push_back({shape, 0}); it = seen.end() - 1; }
+    ptr.push_back(tr->m1 + p.offset); count.push_back((uint64_t)p.n); root.push_back((int32_t)(it->second % world));
+    it->second += 1;
+  }
+  return ojc_comm_broadcast_many(tr->comm, ptr.data(), count.data(), root.data(), (int64_t)ptr.size(), OJC_F32);
+}
+
+ojc_status ojc_trainer_exposed_exchange_ms(ojc_trainer* tr, float* ms) {
+  const char* op = "trainer_exposed_exchange_ms";
+  if (!tr || !ms) return ojc_fail(OJC_ERR_BACKEND, op, "null argument");
+  *ms = 0.0f;
+  if (!tr->exchange_timed) return OJC_OK;
+  OJC_CUDA(tr->be, cudaEventSynchronize(tr->ev_exchanged), op);
+  OJC_CUDA(tr->be, cudaEventElapsedTime(ms, tr->ev_bwd_end, tr->ev_exchanged), op);
+  return OJC_OK;
+}
+
+ojc_status ojc_trainer_param_checksum(ojc_trainer* tr, uint64_t* hash) {
+  const char* op = "trainer_param_checksum";
+  if (!tr || !hash) return ojc_fail(OJC_ERR_BACKEND, op, "null argument");
+  uint64_t h = 0xcbf29ce484222325ull;
+  std::vector<float> host;
+  for (const Param& p : tr->params) {
+    host.resize((size_t)p.n);
+    OJC_TRY(ojc_download(tr->be, host.data(), tr->W(p), (uint64_t)p.n * 4));
+    h = ojc_fnv1a64(h, host.data(), (uint64_t)p.n * 4);
+  }
+  *hash = h;
   return OJC_OK;
 }
 

@@ -3,9 +3,66 @@
 Each rank runs the identical forward/backward on its own micro-batch with the backward seeded by 1/world, exactly the
 reference's K-micro-batch weighting (MicroWeights, ojas-model/src/trainer.rs:1083-1119); gradients are then summed across
 ranks bucket by bucket, after which every rank runs the same clip and optimizer and stays bit-identical to its peers.
-`torch.distributed` (NCCL on GPUs, gloo in the CPU tests) carries the collectives; no kernel here reads a peer's memory.
+The exchange itself lives behind the C ABI (ojc_comm_*, ojc_allreduce_start / _wait: NCCL reached with dlopen, include/ojas_cuda.h);
+`Communicator` is its ctypes face and needs only some way to hand rank 0's 128-byte id to the other ranks. `BucketAllReduce` is the
+same exchange carried by `torch.distributed` instead (gloo in the CPU tests). No kernel here reads a peer's memory.
 """
 from __future__ import annotations
+
+import ctypes as C
+
+
+class Communicator:
+    """ojc_comm: one NCCL communicator for a CudaBackend. `share_id(id_bytes_or_None) -> id_bytes` must return rank 0's id on every
+    rank (rank 0 passes its fresh id in, the others pass None): a torch.distributed broadcast, a file, a socket."""
+
+    def __init__(self, backend, rank: int, world: int, share_id):
+        from ._lib import lib
+        from .backend import _check
+        self._h = None
+        self.backend, self.rank, self.world = backend, rank, world
+        buf = (C.c_uint8 * 128)()
+        if rank == 0:
+            _check(lib.ojc_comm_unique_id(buf))
+        ident = share_id(bytes(buf) if rank == 0 else None)
+        assert len(ident) == 128
+        buf = (C.c_uint8 * 128).from_buffer_copy(ident)
+        h = C.c_void_p()
+        _check(lib.ojc_comm_init(backend._handle, C.c_int32(rank), C.c_int32(world), buf, C.byref(h)))
+        self._h = h
+
+    @staticmethod
+    def over_torch_distributed(backend, group=None) -> "Communicator":
+        """Rendezvous through an initialised torch.distributed process group of any backend (used for the id only)."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+
+        def share(ident):
+            box = [ident]
+            dist.broadcast_object_list(box, src=0, group=group)
+            return box[0]
+        return Communicator(backend, rank, world, share)
+
+    def allreduce_sum_f32(self, tensor) -> None:
+        """In place on a library tensor (F32), on the backend's stream."""
+        from ._lib import lib
+        from .backend import _check
+        _check(lib.ojc_comm_allreduce(self._h, C.c_void_p(tensor.ptr), C.c_uint64(tensor.numel), C.c_int32(0), C.c_int32(0)))
+
+    def check(self) -> None:
+        from ._lib import lib
+        from .backend import _check
+        _check(lib.ojc_comm_check(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            from ._lib import lib
+            if self.backend._handle:
+                lib.ojc_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
 
 
 def allreduce_sum_(tensors, group=None, async_op: bool = False):

@@ -93,6 +93,13 @@ typedef struct {
 enum { ORC_INIT_ZEROS = 0, ORC_INIT_ONES = 1, ORC_INIT_NORMAL = 2 };
 enum { ORC_GROUP_ADAMW = 0, ORC_GROUP_MUON = 1 };
 
+/* Timed CPU baseline only: Numerics::Fast arithmetic (fused multiply-add products on 6 x 16 register tiles, f32 AdamW) instead of the
+ * Exact contract every parity check uses, and the number of threads the parallel regions run on. */
+void orc_set_fast(int on);
+int orc_fast(void);
+int orc_set_threads(int n);
+int orc_max_threads(void);
+
 int64_t orc_param_count(const orc_spec* spec);
 int orc_param_info(const orc_spec* spec, int64_t index, char* name, int64_t name_cap, int64_t* rank,
                    int64_t* shape2, int* init_kind, int* group, int* trains);

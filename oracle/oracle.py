@@ -467,8 +467,19 @@ def forward_loss(spec: Spec, params, ids, targets, ignore=None, seed=1.0, want_g
     return np.float32(loss.value), grads, logits
 
 
-def set_threads(n: int) -> None:
-    os.environ["OMP_NUM_THREADS"] = str(n)
+def set_threads(n: int) -> int:
+    """Run every later parallel region on n threads (CpuBackend::with_threads), whatever OMP_NUM_THREADS said at start-up
+    (torch.distributed.run sets it to 1 for its children). Returns the count in force."""
+    return int(lib.orc_set_threads(C.c_int(n)))
+
+
+def max_threads() -> int:
+    return int(lib.orc_max_threads())
+
+
+def set_fast(on: bool) -> None:
+    """Numerics::Fast for the timed CPU baseline (fused multiply-add products, f32 AdamW). Parity checks never switch it on."""
+    lib.orc_set_fast(C.c_int(int(on)))
 
 
 # ------------------------------------------------------------------ trainer (host logic of one optimizer step)

@@ -97,3 +97,84 @@ def test_two_ranks_reduce_to_the_accumulated_gradient_and_stay_bit_identical(tmp
             assert not np.any(got), k
         else:
             assert np.linalg.norm(got - want) / np.linalg.norm(want) <= tol, (k, np.linalg.norm(got - want) / np.linalg.norm(want))
+
+
+COMM_WORKER = r"""
+import os, sys
+import numpy as np
+import torch.distributed as dist
+from safetensors import safe_open
+sys.path.insert(0, os.environ["OJAS_ROOT"])
+from ojas_b200 import CudaBackend, TrainConfig, Trainer, checkpoint as ck
+from ojas_b200.dp import Communicator
+
+rank, world, out = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), os.environ["OJAS_OUT"]
+dist.init_process_group("gloo")                      # carries the communicator's 128-byte id and nothing else
+f = safe_open(os.path.join(os.environ["OJAS_ROOT"], "tests", "golden", "tiny", "init.safetensors"), "np")
+spec = ck.spec_from_json(f.metadata()["ojas.spec"])
+be = CudaBackend(rank, 8 << 30)
+comm = Communicator.over_torch_distributed(be)
+rng = np.random.default_rng(7)
+batches = [rng.integers(0, spec.vocab, (2, 33), dtype=np.uint32) for _ in range(2 * 2 * world)]   # 2 steps x K 2 x world ranks
+result = {"batches": np.stack(batches)}
+for shard in (0, 1):
+    tr = Trainer(be, spec, TrainConfig(optimizer="muon", loss_seed=1.0 / world, schedule="cosine", warmup_steps=1, total_steps=4), 2, 32)
+    tr.set_params([f.get_tensor(p.name) for p in tr.params])
+    tr.set_comm(comm, shard_muon=bool(shard))
+    for step in range(2):
+        mine = [batches[step * 2 * world + rank * 2 + k] for k in range(2)]
+        rep = tr.run([(b[:, :-1], b[:, 1:]) for b in mine])
+        result[f"loss{shard}.{step}"] = np.float32(rep.loss)
+        result[f"norm{shard}.{step}"] = np.float32(rep.grad_norm)
+    result[f"exposed{shard}"] = np.float32(tr.exposed_exchange_ms())
+    result[f"sum{shard}"] = np.uint64(tr.param_checksum())
+    tr.sync_moments()
+    result.update({f"p{shard}." + p.name: tr.get_param(i) for i, p in enumerate(tr.params)})
+    result.update({f"m{shard}." + p.name: tr.get_moment(i, 0) for i, p in enumerate(tr.params) if p.trains})
+    tr.set_comm(None)
+    tr.close()
+np.savez(os.path.join(out, f"comm{rank}.npz"), **result)
+dist.barrier()
+comm.close(); be.close()
+dist.destroy_process_group()
+"""
+
+
+def test_the_library_communicator_runs_the_data_parallel_step_and_splits_muon(tmp_path, golden_dir):
+    """The exchange behind the C ABI (ojc_comm_*, NCCL by dlopen) with K = 2 micro-batches per rank on two ranks: parameters after two
+    steps equal the CPU oracle's Trainer::run over the four micro-batches of each step (the K = world x 2 accumulation the exchange
+    stands for) at the f32 gates, both ranks hold the same bits, and splitting the Muon phase across the ranks changes no bit."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from safetensors import safe_open
+    from oracle import oracle as orc
+    script = tmp_path / "comm_worker.py"
+    script.write_text(COMM_WORKER)
+    env = dict(os.environ, OJAS_ROOT=str(ROOT), OJAS_OUT=str(tmp_path), NCCL_NVLS_ENABLE="0")
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29534", str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-4000:]
+    r0, r1 = np.load(tmp_path / "comm0.npz"), np.load(tmp_path / "comm1.npz")
+    for shard in (0, 1):
+        keys = [k for k in r0.files if k.startswith((f"p{shard}.", f"m{shard}."))]
+        assert keys and all(r0[k].tobytes() == r1[k].tobytes() for k in keys), "ranks diverged"
+        assert r0[f"sum{shard}"] == r1[f"sum{shard}"] and r0[f"exposed{shard}"] >= 0.0
+    for k in [k for k in r0.files if k.startswith("p0.")]:
+        assert r0[k].tobytes() == r0["p1." + k[3:]].tobytes(), ("splitting Muon across ranks changed", k)
+    for k in [k for k in r0.files if k.startswith("m0.")]:
+        assert r0[k].tobytes() == r0["m1." + k[3:]].tobytes(), ("momentum after sync_moments differs", k)
+
+    f = safe_open(str(golden_dir / "tiny" / "init.safetensors"), "np")
+    s = json.loads(f.metadata()["ojas.spec"])
+    spec = orc.Spec(**{k: s[k] for k in ("vocab", "n_embd", "n_layer", "n_head", "n_kv_head", "head_dim", "hidden", "max_seq", "rope_base", "rms_eps")})
+    table = orc.param_table(spec)
+    otr = orc.TrainerOracle(spec, [f.get_tensor(i.name) for i in table], schedule=("cosine", 1, 4))
+    batches = r0["batches"]
+    for step in range(2):
+        loss, norm, _ = otr.run([(b[:, :-1], b[:, 1:]) for b in batches[step * 4:(step + 1) * 4]])
+        mean = 0.5 * (float(r0[f"loss0.{step}"]) + float(r1[f"loss0.{step}"]))      # each rank reports the mean of its own micro-batches
+        assert abs(mean - loss) <= 1e-5 * abs(loss) and abs(float(r0[f"norm0.{step}"]) - norm) <= 1e-4 * norm
+    for i, info in enumerate(table):
+        want, got = otr.params[i].astype(np.float64).ravel(), r0["p0." + info.name].astype(np.float64).ravel()
+        assert np.linalg.norm(got - want) <= 1e-4 * max(np.linalg.norm(want), 1e-30), info.name
