@@ -89,9 +89,16 @@ uint64_t ojc_kernel_launches(ojc_backend* be);                                  
 /* ---- instrumentation (no counterpart in the reference): when enabled, every tensor-core GEMM launch is bracketed by CUDA
  *      events on the backend's stream; the read call waits for the stream, returns the summed device time, the summed
  *      2*m*n*k and the launch count since the last read, and resets them. */
+ojc_status ojc_sdpa_forward_variant(int32_t one_tile);   /* 0: the library's choice of attention forward kernel; 1: always the one-query-tile kernel (for timing the two) */
 ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable);
 ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches);
 ojc_status ojc_stream_wait_event(ojc_backend* be, void* cuda_stream, void* cuda_event);  /* cuda_stream waits for an event recorded by this backend (NULL stream: the backend's own) */
+
+/* Self-test of the bounded device-side wait (no counterpart in the reference; its device-lost test traps the GPU, which this library
+ * never does): one small kernel waits, with the helper every tensor-pipeline role uses, on a barrier that nothing arrives on, for at
+ * most limit_cycles SM cycles (<= 2e8, about 0.1 s). Every thread must give up, the kernel ends in order, and the call returns
+ * WaitTimeout from the fault word it raised; the backend stays usable (WaitTimeout is retryable, error.rs:47-95). */
+ojc_status ojc_selftest_bounded_wait(ojc_backend* be, uint64_t limit_cycles, int32_t* threads_that_gave_up);
 
 /* ---- casts: BackendCore::{cast_bf16,to_bf16,to_f32} (backend.rs:982,1042,1070); RNE on the integer bits,
  *      NaN keeps sign + payload and sets the quiet bit (autocast.rs:89-96). */

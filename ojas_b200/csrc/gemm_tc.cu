@@ -638,3 +638,36 @@ ojc_status gemm_auto(ojc_backend* be, const char* op, const GemmOperand& a, cons
     return gemm_tc(be, op, a, b, c, c_dtype, ldc, m, n, k, alpha, accumulate, residual);
   return gemm_f32(be, op, a, b, c, c_dtype, ldc, m, n, k, alpha, accumulate, residual);
 }
+
+// ------------------------------------------------------------------------------------------------ bounded-wait self-test
+namespace {
+// The wait every tensor-pipeline role uses, on a barrier nothing ever arrives on, with a caller-chosen limit: the wait must give
+// up, raise the wait fault and let the CTA leave in order (no trap, no spin past the limit).
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles, uint32_t* fault, int* gave_up) {
+  __shared__ __align__(8) uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { tc::mbar_init(tc::smem_u32(&barrier), 1); abort_flag = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+  __syncthreads();
+  const bool ok = tc::mbar_wait_limit(tc::smem_u32(&barrier), 0, fault, &abort_flag, limit_cycles);
+  if (!ok) atomicAdd(gave_up, 1);
+  __syncthreads();
+}
+}  // namespace
+
+extern "C" ojc_status ojc_selftest_bounded_wait(ojc_backend* be, uint64_t limit_cycles, int32_t* threads_that_gave_up) {
+  const char* op = "selftest_bounded_wait";
+  OJC_ALIVE(be, op);
+  if (limit_cycles == 0 || limit_cycles > 200000000ull) return ojc_fail(OJC_ERR_OUT_OF_RANGE, op, "the limit must be between 1 and 2e8 cycles (about a tenth of a second)");
+  void* counter = nullptr;
+  OJC_TRY(ojc_alloc(be, 4, &counter));
+  ojc_status st = ojc_fill_zero(be, counter, 4);
+  if (st == OJC_OK) {
+    bounded_wait_selftest_kernel<<<1, 64, 0, be->stream>>>((long long)limit_cycles, be->fault_dev, (int*)counter);
+    st = ojc_cuda_check(be, cudaGetLastError(), op);
+  }
+  int32_t host = 0;
+  ojc_status rd = st == OJC_OK ? ojc_download(be, &host, counter, 4) : st;    // the sync point: reports the wait fault as WaitTimeout
+  if (threads_that_gave_up) *threads_that_gave_up = host;
+  ojc_free(be, counter);
+  return rd;
+}

@@ -301,6 +301,241 @@ sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   }
 }
 
+// ================================================================================================ forward, two query tiles per CTA
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and walks the key blocks of 128 once for both:
+//   warps 0-3  softmax rows of tile 0, warps 4-7 of tile 1 (one thread per query row; warp w reaches TMEM lanes 32 (w % 4) ..)
+//   warp 8     TMA producer: both Q tiles once, then K and V blocks on two-stage rings shared by the two tiles
+//   warp 9     allocates all 512 TMEM columns (S0 | S1 | O0 | O1) and issues the MMAs of both tiles in turn
+// P never passes through shared memory: a softmax thread packs its row of probabilities to bf16 and stores it with
+// tcgen05.st over the first 64 columns of its tile's S accumulator, and O += P V reads P as the A operand from TMEM. The
+// MMA warp issues P V of a tile and then that tile's next S (which overwrites the P it has just consumed: the tensor pipe
+// runs its instructions in order), so while one tile's rows are in their softmax the pipe works on the other tile.
+// Tile 1 sits one key block further down the diagonal than tile 0 and walks one block more.
+template <int D> struct Fwd2 {
+  static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128;
+  static constexpr int OFF_Q = 0, OFF_K = 2 * TILE_BYTES, OFF_V = 4 * TILE_BYTES, OFF_BAR = 6 * TILE_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;                // D 64: 96 KB; D 128: 192 KB
+  static constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + D;
+};
+constexpr int FWD2_THREADS = 320;
+enum { C_QFULL = 0, C_KFULL0, C_KFULL1, C_KEMPTY0, C_KEMPTY1, C_VFULL0, C_VFULL1, C_VEMPTY0, C_VEMPTY1, C_SFULL0, C_SFULL1, C_PREADY0, C_PREADY1, C_PVFULL0, C_PVFULL1, C_COUNT };
+
+// tcgen05.mma with the A operand in tensor memory (lane = row, two bf16 per 32-bit column, 8 columns per K = 16 step)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %4, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %5, p;\n\t}"
+               ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(hi), "r"(accumulate), "r"(idesc) : "memory");
+}
+
+// The softmax role of one query tile (rows q0 .. q0 + 127; thread `t` of the group owns row q0 + t = TMEM lane t).
+template <int D>
+__device__ __forceinline__ void softmax_tile2(const FwdArgs& args, int b, int h, int q0, int t, int nblocks, uint32_t s_addr, uint32_t o_addr,
+                                              uint32_t bar_sfull, uint32_t bar_pready, uint32_t bar_pvfull, volatile int* abort_flag) {
+  const int row = q0 + t;
+  const float sl2 = args.scale * LOG2E;
+  float m = 0.0f, l = 0.0f;
+  bool ok = true;
+  for (int j = 0; j < nblocks; ++j) {
+    if (!mbar_wait(bar_sfull, j & 1, args.fault, abort_flag)) { ok = false; break; }
+    fence_after();
+    const int key0 = j * BN;
+    const bool masked = key0 + BN > q0 || key0 + BN > args.time;
+    uint32_t r[BN];
+#pragma unroll
+    for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+    tmem_wait_ld();
+    if (masked) {
+      const int last = min(row, args.time - 1) - key0;
+#pragma unroll
+      for (int e = 0; e < BN; ++e)
+        if (e > last) r[e] = 0xff800000u;
+    }
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int e = 0; e < BN; e += 4) {
+      mx4[0] = fmaxf(mx4[0], __uint_as_float(r[e])); mx4[1] = fmaxf(mx4[1], __uint_as_float(r[e + 1]));
+      mx4[2] = fmaxf(mx4[2], __uint_as_float(r[e + 2])); mx4[3] = fmaxf(mx4[3], __uint_as_float(r[e + 3]));
+    }
+    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
+    const bool grow = j == 0 || mx > m + RESCALE_STEP;
+    if (__any_sync(0xffffffffu, grow)) {
+      const float m_new = j == 0 ? (mx == -INFINITY ? 0.0f : mx) : fmaxf(m, mx);
+      const float corr = j == 0 ? 0.0f : fast_exp2(m - m_new);
+      m = m_new;
+      l *= corr;
+      if (j > 0) {
+        if (!mbar_wait(bar_pvfull, (j - 1) & 1, args.fault, abort_flag)) { ok = false; break; }   // O of blocks 0..j-1 has landed
+        fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tmem_st32(o_addr + c * 32, o);
+        }
+      }
+    }
+    // P over the first 64 columns of this tile's S (every thread touches its own lane only, and S sits in registers)
+    float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t w[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(r[c * 64 + 2 * e]), sl2, -m)), p1 = fast_exp2(fmaf(__uint_as_float(r[c * 64 + 2 * e + 1]), sl2, -m));
+        rs4[e & 3] += p0 + p1;
+        w[e] = pack2_bf16(p0, p1);
+      }
+      tmem_st32(s_addr + c * 32, w);
+    }
+    l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+    tmem_wait_st();
+    fence_before();
+    mbar_arrive(bar_pready);
+  }
+  if (ok && nblocks > 0 && mbar_wait(bar_pvfull, (nblocks - 1) & 1, args.fault, abort_flag)) {
+    fence_after();
+    const float inv = 1.0f / l;
+    bf16* dst = row < args.time ? args.out.row(b, h, row) : nullptr;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld32(o_addr + c * 32, o);
+      tmem_wait_ld();
+      if (dst) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(dst + c * 32 + i) =
+              make_uint4(pack2_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv), pack2_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                         pack2_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv), pack2_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+      }
+    }
+    if (dst) {
+      args.lse[((int64_t)b * args.heads + h) * args.time + row] = (m + log2f(l)) * LN2;
+      if (!(l > 0.0f) || !isfinite(l) || !isfinite(m)) raise_fault(args.fault, OP_SDPA);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(FWD2_THREADS, 1)
+sdpa_fwd2_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }
+  using C = Fwd2<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES;
+  constexpr uint32_t TILE16 = TILE_BYTES >> 4;
+  auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + C::OFF_BAR + 8 * C_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = gridDim.x / args.planes;                 // 256-row tile pairs per plane
+  const TileOrder ord = tile_order(blockIdx.x, args.planes, args.group, tiles);
+  const int pt = tiles - 1 - ord.rank;                       // late pairs see the most keys
+  const int q0 = pt * 2 * BM;
+  const int plane = ord.plane, b = plane / args.heads, h = plane % args.heads, hk = h / (args.heads / args.kv_heads);
+  // key blocks each tile walks: up to and including its diagonal block (none for a tile past the end of the sequence)
+  const int n0 = (min(args.time, q0 + BM) + BN - 1) / BN;
+  const int n1 = q0 + BM < args.time ? (min(args.time, q0 + 2 * BM) + BN - 1) / BN : 0;
+  const int nmax = max(n0, n1);
+
+  auto load_kv = [&](int j) {
+    const int s = j & 1;
+    mbar_expect_tx(bar(C_KFULL0 + s), TILE_BYTES);
+    load_tile<NSUB, 128>(base + C::OFF_K + s * TILE_BYTES, &tm_k, bar(C_KFULL0 + s), args.h_first, hk, j * BN, b);
+    mbar_expect_tx(bar(C_VFULL0 + s), TILE_BYTES);
+    load_tile<NSUB, 128>(base + C::OFF_V + s * TILE_BYTES, &tm_v, bar(C_VFULL0 + s), args.h_first, hk, j * BN, b);
+  };
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+    for (int i = 0; i < C_COUNT; ++i) mbar_init(bar(i), (i == C_PREADY0 || i == C_PREADY1) ? 128 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(bar(C_QFULL), 2 * TILE_BYTES);
+    load_tile<NSUB, 128>(base + C::OFF_Q, &tm_q, bar(C_QFULL), args.h_first, h, q0, b);
+    load_tile<NSUB, 128>(base + C::OFF_Q + TILE_BYTES, &tm_q, bar(C_QFULL), args.h_first, h, q0 + BM, b);   // rows past the end read as zeros
+    for (int j = 0; j < min(2, nmax); ++j) load_kv(j);
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int j = 2; j < nmax; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(bar(C_KEMPTY0 + s), ph, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(C_KFULL0 + s), TILE_BYTES);
+        load_tile<NSUB, 128>(base + C::OFF_K + s * TILE_BYTES, &tm_k, bar(C_KFULL0 + s), args.h_first, hk, j * BN, b);
+        if (!mbar_wait(bar(C_VEMPTY0 + s), ph, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(C_VFULL0 + s), TILE_BYTES);
+        load_tile<NSUB, 128>(base + C::OFF_V + s * TILE_BYTES, &tm_v, bar(C_VFULL0 + s), args.h_first, hk, j * BN, b);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, 0, 0), idesc_pv = make_idesc(BM, D, 0, 1);
+      const uint32_t q_lo = desc_lo(base + C::OFF_Q, 0), k_lo = desc_lo(base + C::OFF_K, 0), v_lo = desc_lo(base + C::OFF_V, ST128);
+      const int nt[2] = {n0, n1};
+      const uint32_t col_s[2] = {C::COL_S0, C::COL_S1}, col_o[2] = {C::COL_O0, C::COL_O1};
+      // the last tile to read key block j releases its stage: tile 1 whenever it walks that block, tile 0 otherwise
+      auto last_user = [&](int g, int j) { return g == 1 ? true : j >= n1; };
+      auto issue_s = [&](int g, int j) -> bool {
+        const uint32_t s = j & 1;
+        if (!mbar_wait(bar(C_KFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) return false;
+        fence_after();
+#pragma unroll
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base + col_s[g], q_lo + g * TILE16 + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + s * TILE16 + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
+        umma_commit(bar(C_SFULL0 + g));
+        if (last_user(g, j)) umma_commit(bar(C_KEMPTY0 + s));
+        return true;
+      };
+      bool ok = mbar_wait(bar(C_QFULL), 0, args.fault, abort_flag);
+      for (int g = 0; g < 2 && ok; ++g) if (nt[g] > 0) ok = issue_s(g, 0);
+      for (int j = 0; j < nmax && ok; ++j) {
+        const uint32_t s = j & 1;
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (j >= nt[g]) continue;
+          if (!mbar_wait(bar(C_PREADY0 + g), j & 1, args.fault, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(C_VFULL0 + s), (j >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+          // O_g += P_g V: P from tensor memory (8 columns per 16 keys), V MN-major from shared memory
+#pragma unroll
+          for (uint32_t kk = 0; kk < BN / 16; ++kk)
+            umma_ts(tmem_base + col_o[g], tmem_base + col_s[g] + kk * 8, v_lo + s * TILE16 + kk * MNSTEP, HI, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar(C_PVFULL0 + g));
+          if (last_user(g, j)) umma_commit(bar(C_VEMPTY0 + s));
+          // this tile's next S overwrites the P just consumed; the pipe runs the two in issue order
+          if (j + 1 < nt[g]) ok = issue_s(g, j + 1);
+        }
+      }
+    }
+  } else {
+    const int g = warp >> 2, t = threadIdx.x & 127;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    softmax_tile2<D>(args, b, h, q0 + g * BM, t, g == 0 ? n0 : n1, lane_base + (g == 0 ? C::COL_S0 : C::COL_S1), lane_base + (g == 0 ? C::COL_O0 : C::COL_O1),
+                     bar(C_SFULL0 + g), bar(C_PREADY0 + g), bar(C_PVFULL0 + g), abort_flag);
+  }
+  if (*abort_flag) __nanosleep(200000);
+  fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // ================================================================================================ backward
 // A prepass writes Dr = rowsum(dO . O) and lse * log2(e); then two kernels, each recomputing P from lse (no atomics,
 // one writer per gradient element):
@@ -786,6 +1021,8 @@ ojc_status make_map(ojc_backend* be, const char* op, CUtensorMap* map, const ojc
   return OJC_OK;
 }
 
+bool g_sdpa_one_tile_forward = false;   // ojc_sdpa_forward_variant: time the one-tile kernel against the two-tile one
+
 bool strides_ok(const ojc_tensor* t) {
   return (reinterpret_cast<uintptr_t>(t->data) & 15) == 0 && t->stride[3] == 1 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 && t->stride[2] % 8 == 0 &&
          t->stride[0] > 0 && t->stride[1] > 0 && t->stride[2] > 0;
@@ -799,6 +1036,16 @@ bool sdpa_tcgen05_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_tenso
   // one dimension order for all three maps: heads inside time, or time inside heads
   const bool hf = q->stride[1] < q->stride[2];
   return (k->stride[1] < k->stride[2]) == hf && (v->stride[1] < v->stride[2]) == hf;
+}
+
+template <int D>
+static ojc_status launch_fwd2(ojc_backend* be, const char* op, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& args, dim3 grid) {
+  static PerDeviceFlag attr_of;
+  bool& attr = attr_of[be->device];
+  if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwd2_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2<D>::SMEM_BYTES), op); attr = true; }
+  sdpa_fwd2_tcgen05_kernel<D><<<grid, FWD2_THREADS, Fwd2<D>::SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
 }
 
 template <int D>
@@ -823,6 +1070,10 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
   args.lse = lse; args.heads = d.heads; args.kv_heads = d.kv_heads; args.time = d.time; args.h_first = hf ? 1 : 0; args.scale = d.scale; args.fault = be->fault_dev;
   args.planes = d.batch * d.heads;
   args.group = planes_per_group(d.time, d.dim, args.planes);
+  if (d.time > BM && !g_sdpa_one_tile_forward) {   // at least two query tiles: the two-tile kernel (P in tensor memory)
+    dim3 grid2((unsigned)(((d.time + 2 * BM - 1) / (2 * BM)) * args.planes));
+    return d.dim == 64 ? launch_fwd2<64>(be, op, mq, mk, mv, args, grid2) : launch_fwd2<128>(be, op, mq, mk, mv, args, grid2);
+  }
   dim3 grid((unsigned)(((d.time + BM - 1) / BM) * args.planes));
   return d.dim == 64 ? launch_fwd<64>(be, op, mq, mk, mv, args, grid) : launch_fwd<128>(be, op, mq, mk, mv, args, grid);
 }
@@ -882,3 +1133,7 @@ bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_t
   const bool hf = q->stride[1] < q->stride[2];
   return strides_ok(gq) && strides_ok(gk) && strides_ok(gv) && (gout->stride[1] < gout->stride[2]) == hf;
 }
+
+// Instrumentation (no counterpart in the reference): 0 = the library's choice (two query tiles per CTA whenever the sequence has two),
+// 1 = always the one-tile kernel. Lets the op benchmark time the two forward kernels against each other on the same inputs.
+extern "C" ojc_status ojc_sdpa_forward_variant(int32_t one_tile) { g_sdpa_one_tile_forward = one_tile != 0; return OJC_OK; }

@@ -23,17 +23,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: when the wall-clock limit runs out the caller's CTA is told to abort, the fault word is raised and
-// false comes back; every role then leaves its loop and the CTA tears down normally.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* fault, volatile int* abort_flag) {
+// Bounded wait: when the limit runs out the caller's CTA is told to abort, the fault word is raised and false comes back;
+// every role then leaves its loop and the CTA tears down normally. The limit is in SM cycles (cheap to read; at most ~2 GHz,
+// so the default is at least two seconds).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, uint32_t* fault, volatile int* abort_flag, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
-  // the SM cycle counter bounds the wait (cheap to read; at most ~2 GHz, so the limit is at least two seconds)
   const long long start = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;   // try_wait parks the thread in hardware for a short while: no issue slots burnt
     if (*abort_flag) return false;
-    if (clock64() - start > WAIT_LIMIT_CYCLES) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
+    if (clock64() - start > limit_cycles) { *abort_flag = 1; raise_fault(fault, OP_GEMM_WAIT); return false; }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* fault, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, fault, abort_flag, WAIT_LIMIT_CYCLES);
 }
 
 // fetches a tensor map into the descriptor cache ahead of its first use

@@ -541,3 +541,38 @@ def test_optimizer_scratch_bytes_bounds_what_a_step_takes(be):
             be.muon_ns5_step(p, g, m, MuonNs5Config(0.025, 0.95, 0.1, True, bf))
             be.sync()
             assert be.budget()["peak"] - live <= bound, (rows, cols, bf)
+
+
+def test_a_host_wait_that_runs_out_is_a_retryable_wait_timeout(be):
+    """Every host wait is bounded (RuntimeConfig::sync_timeout, ojas-cuda/src/runtime.rs:76): with a zero budget a sync behind queued
+    work reports WaitTimeout, nothing is lost, and the next sync with the default budget succeeds."""
+    from ojas_b200 import DType, OjasError
+    x, w = be.upload(orc.round_bf16(rnd(1, (8192, 4096))), DType.BF16), be.upload(orc.round_bf16(rnd(2, (4096, 4096))), DType.BF16)
+    be.sync()
+    be.set_sync_timeout_ms(0)
+    try:
+        ys = [be.linear_forward(x, w) for _ in range(40)]          # about 10 ms of queued GEMMs
+        with pytest.raises(OjasError) as e:
+            be.sync()
+        assert e.value.kind == "WaitTimeout" and e.value.retryable
+    finally:
+        be.set_sync_timeout_ms(60000)
+    be.sync()
+    want = orc.linear_forward(orc.round_bf16(rnd(1, (8192, 4096)))[:4], orc.round_bf16(rnd(2, (4096, 4096))))
+    assert rel(ys[-1].numpy()[:4], want) <= 4e-3
+
+
+def test_a_device_wait_that_runs_out_ends_the_kernel_in_order(be):
+    """The bounded mbarrier wait of the tensor-pipeline kernels on a barrier nothing arrives on, with a one-millisecond limit: every
+    thread gives up, the kernel returns, the next sync reports WaitTimeout, and the backend goes on working."""
+    import ctypes as C
+    from ojas_b200 import OjasError
+    from ojas_b200._lib import lib
+    from ojas_b200.backend import _check
+    gave_up = C.c_int32(-1)
+    with pytest.raises(OjasError) as e:
+        _check(lib.ojc_selftest_bounded_wait(be._handle, C.c_uint64(2_000_000), C.byref(gave_up)))
+    assert e.value.kind == "WaitTimeout" and gave_up.value == 64
+    be.sync()
+    a = be.upload(rnd(3, (64, 64)))
+    assert np.array_equal(be.residual_add_forward(a, a).numpy(), rnd(3, (64, 64)) * 2)
