@@ -1070,7 +1070,10 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
   args.lse = lse; args.heads = d.heads; args.kv_heads = d.kv_heads; args.time = d.time; args.h_first = hf ? 1 : 0; args.scale = d.scale; args.fault = be->fault_dev;
   args.planes = d.batch * d.heads;
   args.group = planes_per_group(d.time, d.dim, args.planes);
-  if (d.time > BM && !g_sdpa_one_tile_forward) {   // at least two query tiles: the two-tile kernel (P in tensor memory)
+  // Two query tiles per CTA (P in tensor memory) where it measured faster: head_dim 128, where one CTA owns the SM either way
+  // ([8,16,4096,128]: 671 us against 686 us). At head_dim 64 two one-tile CTAs share an SM and overlap each other's softmax, and
+  // the short walks of T = 1024 favour them (162 us against 181 us at B 32, H 12).
+  if (d.dim == 128 && d.time > BM && !g_sdpa_one_tile_forward) {
     dim3 grid2((unsigned)(((d.time + 2 * BM - 1) / (2 * BM)) * args.planes));
     return d.dim == 64 ? launch_fwd2<64>(be, op, mq, mk, mv, args, grid2) : launch_fwd2<128>(be, op, mq, mk, mv, args, grid2);
   }

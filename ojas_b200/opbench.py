@@ -1,7 +1,7 @@
 """Single-op timing through the C ABI, for profiling one kernel at a time.
 
     python -m ojas_b200.opbench gemm ROWS IN OUT [bf16|f32] [--reps N]     y = x W^T on BF16 operands (tcgen05 kernels)
-    python -m ojas_b200.opbench sdpa BATCH HEADS TIME HEAD_DIM [--reps N]  causal attention forward and backward (BF16)
+    python -m ojas_b200.opbench sdpa BATCH HEADS TIME HEAD_DIM [--reps N] [--one-tile]  causal attention forward and backward (BF16)
 
 Prints microseconds per call (CUDA events on the library's stream) and TFLOP/s. The operands are uninitialised device
 memory for gemm (timing does not depend on values) and seeded normal draws for sdpa (the softmax needs finite rows).
@@ -46,6 +46,7 @@ def sdpa(args) -> None:
     from .backend import _check, _p
     B, H, T, D = args.batch, args.heads, args.time, args.dim
     be = CudaBackend(0, 16 << 30)
+    _check(lib.ojc_sdpa_forward_variant(C.c_int32(int(args.one_tile))))
 
     def draw(seed):  # [B,T,H,D] storage viewed as [B,H,T,D], the layout the step driver uses
         return be.upload(np.random.default_rng(seed).standard_normal((B, T, H, D), dtype=np.float32), DType.BF16).permuted((0, 2, 1, 3))
@@ -74,6 +75,7 @@ def main() -> None:
     s = sub.add_parser("sdpa")
     s.add_argument("batch", type=int); s.add_argument("heads", type=int); s.add_argument("time", type=int); s.add_argument("dim", type=int)
     s.add_argument("--reps", type=int, default=10)
+    s.add_argument("--one-tile", action="store_true", help="time the one-query-tile forward kernel instead of the library's choice")
     s.set_defaults(fn=sdpa)
     args = ap.parse_args()
     args.fn(args)
