@@ -153,6 +153,86 @@ ce_rows_fast_kernel(const float* __restrict__ logits, int64_t ld, const uint32_t
   }
 }
 
+// The bf16 step's form: BF16 logits (the head GEMM's output, rounded once from its f32 accumulator, as a matmul output is under
+// torch's autocast) turned into the BF16 gradient IN PLACE: a thread reads the same 8-value groups in both passes and overwrites only
+// those, so no second tile exists. Statistics and the loss term are f32. 6 bytes per logit cross HBM for the head (GEMM write 2,
+// read 2, write 2) instead of 10 with an f32 tile and a separate gradient tile. Same row rules as above.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& t, float (&v)[8]) {
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+__global__ void __launch_bounds__(512, 2)
+ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
+                            const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
+  __shared__ float red[32];
+  constexpr float L2E = 1.4426950408889634f;
+  const int64_t row = blockIdx.x;
+  bf16* z = logits + row * ld;
+  const uint32_t target = targets[row];
+  const int64_t v8 = vocab >> 3;            // whole 16-byte groups; the tail (vocab % 8) is handled by scalar code
+  if ((has_ignore && target == ignore) || target >= vocab) {
+    if (threadIdx.x == 0) terms[row] = 0.0f;
+    if (want_grad) {
+      for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(0u, 0u, 0u, 0u);
+      for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) z[c] = __float2bfloat16_rn(0.0f);
+    }
+    return;
+  }
+  const float picked = __bfloat162float(z[target]);   // read before any thread overwrites the row
+  float tm = -INFINITY, ts = 0.0f;
+#pragma unroll 2
+  for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
+    float v[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(z + 8 * i), v);
+    float m8 = v[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) m8 = fmaxf(m8, v[e]);
+    m8 *= L2E;
+    if (m8 > tm) { ts *= ex2_fast(tm - m8); tm = m8; }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ts += ex2_fast(fmaf(v[e], L2E, -tm));
+  }
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) {
+    const float a = __bfloat162float(z[c]) * L2E;
+    if (a > tm) { ts *= ex2_fast(tm - a); tm = a; }
+    ts += ex2_fast(a - tm);
+  }
+  const float mx2 = block_max(tm, red);
+  const float sum = block_sum(tm == -INFINITY ? 0.0f : ts * ex2_fast(tm - mx2), red);
+  const float mx = mx2 * (1.0f / L2E);
+  if (!(isfinite(mx2) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
+  float other = 0.0f;
+  bool collapsed = false;
+  if (picked * L2E == mx2 && sum == 1.0f) {
+    float o = 0.0f;
+    for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += ex2_fast(__bfloat162float(z[c]) * L2E - mx2);
+    other = block_sum(o, red);
+    collapsed = other > 0.0f;
+  }
+  if (threadIdx.x == 0) terms[row] = collapsed ? log1pf(other) : (mx + logf(sum) - picked);
+  if (!want_grad) return;
+  const float denom = (float)valid[0];
+  const float inv = collapsed ? 1.0f / (1.0f + other) : 1.0f / sum;
+  const float k = inv / denom * seed;
+  __syncthreads();                          // every read of the row by the statistics is done
+#pragma unroll 2
+  for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
+    float v[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(z + 8 * i), v);
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(ex2_fast(fmaf(v[2 * e], L2E, -mx2)) * k, ex2_fast(fmaf(v[2 * e + 1], L2E, -mx2)) * k);
+    *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) z[c] = __float2bfloat16_rn(ex2_fast(fmaf(__bfloat162float(z[c]), L2E, -mx2)) * k);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const float gt = collapsed ? -(other * inv) / denom : (ex2_fast(fmaf(picked, L2E, -mx2)) * inv) / denom - 1.0f / denom;
+    z[target] = __float2bfloat16_rn(gt * seed);
+  }
+}
+
 // loss = (sum of the row terms, added in a fixed tree order) / n_valid
 __global__ void ce_loss_finish_kernel(const float* __restrict__ terms, int64_t rows, const uint32_t* __restrict__ valid, float* __restrict__ loss, uint32_t* fault) {
   __shared__ double red[256];
@@ -202,7 +282,7 @@ ojc_status ce_loss_finish(ojc_backend* be, const float* terms, int64_t rows, con
 }
 
 // The fused tied-head loss. x [rows, dim] and w [vocab, dim] share a dtype class (both F32: f32 tier with F32 logits
-// and F32 G; both BF16: tensor-core GEMMs, F32 logits, BF16 G). gx (same dtype as x, or F32) and gw (F32) are optional;
+// and F32 G; both BF16: tensor-core GEMMs, BF16 logits turned into BF16 G in place). gx (same dtype as x, or F32) and gw (F32) are optional;
 // gw_accumulate adds into gw (the tied embedding's gradient buffer). `seed` scales G, i.e. both gradients.
 ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const void* w, int32_t w_dt, const uint32_t* targets, int64_t rows, int64_t dim,
                           int64_t vocab, int has_ignore, uint32_t ignore, int64_t chunk_rows, float* loss_dev, void* gx, int32_t gx_dt, float* gw,
@@ -214,10 +294,11 @@ ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const vo
   if (chunk_rows > rows) chunk_rows = rows;
   const bool want = gx || gw;
   const int64_t ldl = (vocab + 7) & ~int64_t(7);  // keep tile rows 16-byte aligned for the tensor-core kernels
+  // bf16 tier: one BF16 tile holds the logits and then, in place, their gradient; f32 tier: an F32 logits tile and an F32 gradient tile
   void *logits = nullptr, *gbuf = nullptr, *small = nullptr;
-  OJC_TRY(ojc_alloc(be, (uint64_t)chunk_rows * ldl * 4, &logits));
+  OJC_TRY(ojc_alloc(be, (uint64_t)chunk_rows * ldl * (bf ? 2 : 4), &logits));
   ojc_status st = OJC_OK;
-  if (want) st = ojc_alloc(be, (uint64_t)chunk_rows * ldl * dtype_size(g_dt), &gbuf);
+  if (want && !bf) st = ojc_alloc(be, (uint64_t)chunk_rows * ldl * 4, &gbuf);
   if (st == OJC_OK) st = ojc_alloc(be, (uint64_t)rows * 4 + 256, &small);
   auto run = [&]() -> ojc_status {
     uint32_t* valid = (uint32_t*)small;
@@ -227,14 +308,22 @@ ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const vo
       const int64_t r = std::min(chunk_rows, rows - r0);
       const char* xc = (const char*)x + r0 * dim * dtype_size(x_dt);
       GemmOperand a{xc, x_dt, dim, 1}, b{w, w_dt, 1, dim};
-      OJC_TRY(gemm_auto(be, op, a, b, logits, OJC_F32, ldl, r, vocab, dim, 1.0f, false, nullptr));
-      OJC_TRY(ce_rows(be, logits, OJC_F32, ldl, targets + r0, r, vocab, has_ignore, ignore, valid, terms + r0, want ? gbuf : nullptr, g_dt, ldl, seed));
+      OJC_TRY(gemm_auto(be, op, a, b, logits, bf ? OJC_BF16 : OJC_F32, ldl, r, vocab, dim, 1.0f, false, nullptr));
+      void* g = gbuf;
+      if (bf) {
+        ce_rows_inplace_bf16_kernel<<<(unsigned)r, 512, 0, be->stream>>>((bf16*)logits, ldl, targets + r0, vocab, has_ignore, ignore, valid, terms + r0, want ? 1 : 0, seed,
+                                                                        be->fault_dev);
+        OJC_LAUNCHED(be, op);
+        g = logits;
+      } else {
+        OJC_TRY(ce_rows(be, logits, OJC_F32, ldl, targets + r0, r, vocab, has_ignore, ignore, valid, terms + r0, want ? gbuf : nullptr, g_dt, ldl, seed));
+      }
       if (gx) {  // dX_c = G . W
-        GemmOperand ga{gbuf, g_dt, ldl, 1}, wb{w, w_dt, dim, 1};
+        GemmOperand ga{g, g_dt, ldl, 1}, wb{w, w_dt, dim, 1};
         OJC_TRY(gemm_auto(be, op, ga, wb, (char*)gx + r0 * dim * dtype_size(gx_dt), gx_dt, dim, r, dim, vocab, 1.0f, false, nullptr));
       }
       if (gw) {  // dW += G^T . x_c (rows ascending across tiles)
-        GemmOperand gt{gbuf, g_dt, 1, ldl}, xb{xc, x_dt, dim, 1};
+        GemmOperand gt{g, g_dt, 1, ldl}, xb{xc, x_dt, dim, 1};
         OJC_TRY(gemm_auto(be, op, gt, xb, gw, OJC_F32, dim, vocab, dim, r, 1.0f, gw_accumulate || r0 > 0, nullptr));
       }
     }

@@ -291,7 +291,7 @@ def test_fused_linear_cross_entropy_bf16_tier(be):
     targets = np.array([rng.below(vocab) for _ in range(rows)], np.uint32)
     oloss, ogx, ogw = orc.linear_cross_entropy_mean(x, w, targets)
     loss, gx, gw = be.linear_cross_entropy_mean(be.upload(x, DType.BF16), be.upload(w, DType.BF16), be.upload(targets), chunk=(200, 0), grad_input_dtype=DType.F32)
-    assert abs(loss.numpy()[0] - oloss) <= 1e-4 * abs(oloss)
+    assert abs(loss.numpy()[0] - oloss) <= 5e-4 * abs(oloss)              # the logits tile is bf16 (one rounding of the f32 accumulator)
     assert rel(gx.numpy(), ogx) <= 1e-2 and rel(gw.numpy(), ogw) <= 1e-2  # d(logits) is rounded to bf16 before the two GEMMs
 
 
@@ -484,7 +484,7 @@ def test_fused_linear_cross_entropy_with_ignore_and_a_collapsed_row(be, bf16):
     oloss, ogx, ogw = orc.linear_cross_entropy_mean(x, w, targets, ignore=ignore)
     dt = DType.BF16 if bf16 else DType.F32
     loss, gx, gw = be.linear_cross_entropy_mean(be.upload(x, dt), be.upload(w, dt), be.upload(targets), ignore_index=ignore, chunk=(128, 0), grad_input_dtype=DType.F32)
-    assert abs(loss.numpy()[0] - oloss) <= (1e-4 if bf16 else FWD_TOL) * abs(oloss)
+    assert abs(loss.numpy()[0] - oloss) <= (5e-4 if bf16 else FWD_TOL) * abs(oloss)
     tol = 1e-2 if bf16 else GRAD_TOL
     assert rel(gx.numpy(), ogx) <= tol and rel(gw.numpy(), ogw) <= tol
     assert not np.any(gx.numpy()[targets == ignore])
