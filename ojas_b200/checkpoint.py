@@ -371,6 +371,7 @@ def save(trainer, directory, run_cfg: RunConfig, cursor: DataCursor, run: str) -
     # every byte is new space (the old checkpoint stays until the swap); 1 MiB per file for block rounding
     need = sum(8 + len(h) + n + (1 << 20) for h, n in (safetensors_header(model, model_meta), safetensors_header(optim, optim_meta))) + len(state) + (1 << 20)
     parent = directory.resolve().parent
+    recover_replaced_dir(directory)      # an earlier save of this name may have died mid-swap
     _check_save_target(directory)
     try:
         st = os.statvfs(parent)
@@ -401,11 +402,32 @@ def save(trainer, directory, run_cfg: RunConfig, cursor: DataCursor, run: str) -
         raise
 
 
+def recover_replaced_dir(directory) -> bool:
+    """What a save that died between its two renames left behind (ojas_io::recover_replaced_dir, ojas-io/src/replace.rs:372-378, which
+    Trainer::resume_from runs first, checkpoint.rs:699): the target was moved aside to `.<name>.old-<pid>` and the new directory never
+    took its place. With the target missing, the newest such sibling is moved back; with the target present, leftovers of finished or
+    abandoned saves (`.old-*`, and half-written `.stage-*` directories) are removed. The pid in the names is the dead process's, so
+    the scan goes by prefix. Returns whether the old checkpoint was restored."""
+    directory = Path(directory)
+    parent = directory.resolve().parent
+    if not parent.is_dir():
+        return False
+    olds = sorted((p for p in parent.glob(f".{directory.name}.old-*") if p.is_dir()), key=lambda p: p.stat().st_mtime)
+    restored = False
+    if not directory.exists() and olds:
+        os.rename(olds.pop(), directory)
+        restored = True
+    for leftover in olds + [p for p in parent.glob(f".{directory.name}.stage-*") if p.is_dir()]:
+        shutil.rmtree(leftover, ignore_errors=True)
+    return restored
+
+
 def resume(trainer, directory, run_cfg: RunConfig) -> tuple[DataCursor, str]:
     """Trainer::resume_from (checkpoint.rs:692-800) into an open trainer of the same spec: every check first, then the
     tensors, one at a time; returns the data cursor and the run id. `git_sha` may differ from the saved one; the train
     config and the tokenizer hash may not."""
     directory = Path(directory)
+    recover_replaced_dir(directory)
     for name in (STATE_FILE, MODEL_FILE, OPTIM_FILE):
         f = directory / name
         if f.is_symlink() or not f.is_file():

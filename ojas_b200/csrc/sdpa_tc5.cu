@@ -536,6 +536,251 @@ sdpa_fwd2_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
   }
 }
 
+// ================================================================================================ forward, persistent CTAs
+// The one-tile kernel's roles, kept alive over many query tiles. A CTA takes every gridDim.x-th tile of the long-tiles-first order
+// and runs them as one stream of key blocks: the producer keeps loading (the next tile's Q into the second Q buffer, its K and V
+// blocks onto the same two-stage rings) while the current tile is still in its last blocks, the MMA thread issues the next tile's first
+// S as soon as the softmax rows hold the current tile's last S in registers, and a tile's output rows are normalised and stored while
+// the tensor pipe is already on the next tile. TMEM is allocated once, barriers are set up once. P lives in tensor memory beside S
+// (S 128 columns, P 64, O D): no shared-memory P buffer, so at head_dim 64 two CTAs share an SM with 96 KB each.
+template <int D> struct FwdP {
+  static constexpr int NSUB = D / 64, TILE_BYTES = NSUB * ST128;
+  static constexpr int OFF_Q = 0, OFF_K = 2 * TILE_BYTES, OFF_V = 4 * TILE_BYTES, OFF_BAR = 6 * TILE_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr uint32_t COL_S = 0, COL_P = 128, COL_O = 192, TMEM_COLS = D == 64 ? 256 : 512;
+  static constexpr int CTAS = D == 64 ? 2 : 1;
+};
+enum { P_QFULL0 = 0, P_QFULL1, P_QEMPTY0, P_QEMPTY1, P_KFULL0, P_KFULL1, P_KEMPTY0, P_KEMPTY1, P_VFULL0, P_VFULL1, P_VEMPTY0, P_VEMPTY1, P_SFULL, P_SFREE, P_PREADY,
+       P_PVFULL, P_OFREE, P_COUNT };
+
+// the tile a CTA works on as item `i` of its list, and where it sits
+struct TileWalk {
+  int q0, b, h, hk, nblocks;
+  __device__ __forceinline__ bool set(const FwdArgs& args, int tiles, int total, int item) {
+    const int g = blockIdx.x + item * gridDim.x;
+    if (g >= total) return false;
+    const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
+    q0 = (tiles - 1 - ord.rank) * BM;
+    b = ord.plane / args.heads; h = ord.plane % args.heads; hk = h / (args.heads / args.kv_heads);
+    nblocks = (min(args.time, q0 + BM) + BN - 1) / BN;
+    return true;
+  }
+};
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, FwdP<D>::CTAS)
+sdpa_fwdp_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }
+  using C = FwdP<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES;
+  constexpr uint32_t TILE16 = TILE_BYTES >> 4;
+  auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + C::OFF_BAR + 8 * P_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = (args.time + BM - 1) / BM, total = tiles * args.planes;
+
+  if (warp == 4 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+    for (int i = 0; i < P_COUNT; ++i) mbar_init(bar(i), (i == P_PREADY || i == P_SFREE || i == P_OFREE) ? 128 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer: Q of tile i into buffer i & 1, K / V of block n into stage n & 1
+    if (lane == 0) {
+      TileWalk w;
+      int n = 0;
+      for (int i = 0; w.set(args, tiles, total, i); ++i) {
+        const int qs = i & 1;
+        if (i >= 2 && !mbar_wait(bar(P_QEMPTY0 + qs), ((i >> 1) & 1) ^ 1, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(P_QFULL0 + qs), TILE_BYTES);
+        load_tile<NSUB, 128>(base + C::OFF_Q + qs * TILE_BYTES, &tm_q, bar(P_QFULL0 + qs), args.h_first, w.h, w.q0, w.b);
+        bool ok = true;
+        for (int j = 0; j < w.nblocks && ok; ++j, ++n) {
+          const int s = n & 1;
+          const uint32_t ph = ((n >> 1) & 1) ^ 1;
+          if (n >= 2 && !mbar_wait(bar(P_KEMPTY0 + s), ph, args.fault, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(bar(P_KFULL0 + s), TILE_BYTES);
+          load_tile<NSUB, 128>(base + C::OFF_K + s * TILE_BYTES, &tm_k, bar(P_KFULL0 + s), args.h_first, w.hk, j * BN, w.b);
+          if (n >= 2 && !mbar_wait(bar(P_VEMPTY0 + s), ph, args.fault, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(bar(P_VFULL0 + s), TILE_BYTES);
+          load_tile<NSUB, 128>(base + C::OFF_V + s * TILE_BYTES, &tm_v, bar(P_VFULL0 + s), args.h_first, w.hk, j * BN, w.b);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer: S(n + 1) goes out under the softmax of block n, across tile boundaries too
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, 0, 0), idesc_pv = make_idesc(BM, D, 0, 1);
+      const uint32_t q_lo = desc_lo(base + C::OFF_Q, 0), k_lo = desc_lo(base + C::OFF_K, 0), v_lo = desc_lo(base + C::OFF_V, ST128);
+      // S of block `n` (block j of the tile in Q buffer qs); `last` = the tile's last S: its Q buffer is free afterwards
+      auto issue_s = [&](int n, int qs, int qi, int j, bool last) -> bool {
+        const uint32_t s = n & 1;
+        if (j == 0 && !mbar_wait(bar(P_QFULL0 + qs), (qi >> 1) & 1, args.fault, abort_flag)) return false;
+        if (!mbar_wait(bar(P_KFULL0 + s), (n >> 1) & 1, args.fault, abort_flag)) return false;
+        fence_after();
+#pragma unroll
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base + C::COL_S, q_lo + qs * TILE16 + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + s * TILE16 + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
+        umma_commit(bar(P_SFULL));
+        umma_commit(bar(P_KEMPTY0 + s));
+        if (last) umma_commit(bar(P_QEMPTY0 + qs));
+        return true;
+      };
+      TileWalk cur, nxt;
+      bool have = cur.set(args, tiles, total, 0);
+      bool ok = have && issue_s(0, 0, 0, 0, cur.nblocks == 1);
+      int n = 0;
+      for (int i = 0; have && ok; ++i) {
+        const bool more = nxt.set(args, tiles, total, i + 1);
+        for (int j = 0; j < cur.nblocks && ok; ++j, ++n) {
+          const uint32_t s = n & 1;
+          // the next S (of this tile, or block 0 of the next one) as soon as the softmax rows hold S(n) in registers
+          const bool within = j + 1 < cur.nblocks;
+          if (within || more) {
+            if (!mbar_wait(bar(P_SFREE), n & 1, args.fault, abort_flag)) { ok = false; break; }
+            fence_after();
+            ok = within ? issue_s(n + 1, i & 1, i, j + 1, j + 2 == cur.nblocks) : issue_s(n + 1, (i + 1) & 1, i + 1, 0, nxt.nblocks == 1);
+            if (!ok) break;
+          }
+          if (!mbar_wait(bar(P_PREADY), n & 1, args.fault, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(P_VFULL0 + s), (n >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+          // a tile's first P V overwrites O: the previous tile's rows must have read theirs
+          if (j == 0 && i > 0 && !mbar_wait(bar(P_OFREE), (i - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+#pragma unroll
+          for (uint32_t kk = 0; kk < BN / 16; ++kk)
+            umma_ts(tmem_base + C::COL_O, tmem_base + C::COL_P + kk * 8, v_lo + s * TILE16 + kk * MNSTEP, HI, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar(P_VEMPTY0 + s));
+          umma_commit(bar(P_PVFULL));
+        }
+        cur = nxt;
+        have = more;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output rows (warps 0..3): thread t owns row q0 + t of every tile
+    const int t = threadIdx.x;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t s_addr = lane_base + C::COL_S, p_addr = lane_base + C::COL_P, o_addr = lane_base + C::COL_O;
+    const float sl2 = args.scale * LOG2E;
+    TileWalk w;
+    int n = 0;
+    bool ok = true;
+    for (int i = 0; ok && w.set(args, tiles, total, i); ++i) {
+      const int row = w.q0 + t;
+      float m = 0.0f, l = 0.0f;
+      for (int j = 0; j < w.nblocks; ++j, ++n) {
+        if (!mbar_wait(bar(P_SFULL), n & 1, args.fault, abort_flag)) { ok = false; break; }
+        fence_after();
+        const int key0 = j * BN;
+        const bool masked = key0 + BN > w.q0 || key0 + BN > args.time;
+        uint32_t r[BN];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tmem_wait_ld();
+        fence_before();
+        mbar_arrive(bar(P_SFREE));               // the S columns are free: the next S runs under this softmax
+        if (masked) {
+          const int last = min(row, args.time - 1) - key0;
+#pragma unroll
+          for (int e = 0; e < BN; ++e)
+            if (e > last) r[e] = 0xff800000u;
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < BN; e += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(r[e])); mx4[1] = fmaxf(mx4[1], __uint_as_float(r[e + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(r[e + 2])); mx4[3] = fmaxf(mx4[3], __uint_as_float(r[e + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
+        const bool grow = j == 0 || mx > m + RESCALE_STEP;
+        const bool any_grow = __any_sync(0xffffffffu, grow);
+        float corr = 1.0f;
+        if (any_grow) {
+          const float m_new = j == 0 ? (mx == -INFINITY ? 0.0f : mx) : fmaxf(m, mx);
+          corr = j == 0 ? 0.0f : fast_exp2(m - m_new);
+          m = m_new;
+          l *= corr;
+        }
+        // the probabilities, packed, while the previous P V may still be reading the P columns
+        uint32_t pw[BN / 2];
+        float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int e = 0; e < BN / 2; ++e) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * e]), sl2, -m)), p1 = fast_exp2(fmaf(__uint_as_float(r[2 * e + 1]), sl2, -m));
+          rs4[e & 3] += p0 + p1;
+          pw[e] = pack2_bf16(p0, p1);
+        }
+        l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        // P V of the previous block (this tile's or the last of the previous tile) has read P and, for a rescale, has landed in O
+        if (n > 0 && !mbar_wait(bar(P_PVFULL), (n - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+        fence_after();
+        if (any_grow && j > 0) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+            tmem_st32(o_addr + c * 32, o);
+          }
+        }
+        tmem_st32(p_addr, *reinterpret_cast<uint32_t(*)[32]>(&pw[0]));
+        tmem_st32(p_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pw[32]));
+        tmem_wait_st();
+        fence_before();
+        mbar_arrive(bar(P_PREADY));
+      }
+      if (!ok) break;
+      // this tile's O: read it, hand the columns back, then normalise and store
+      if (!mbar_wait(bar(P_PVFULL), (n - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+      fence_after();
+      const float inv = 1.0f / l;
+      bf16* dst = row < args.time ? args.out.row(w.b, w.h, row) : nullptr;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + c * 32, o);
+        tmem_wait_ld();
+        if (c == D / 32 - 1) { fence_before(); mbar_arrive(bar(P_OFREE)); }
+        if (dst) {
+#pragma unroll
+          for (int q = 0; q < 32; q += 8)
+            *reinterpret_cast<uint4*>(dst + c * 32 + q) =
+                make_uint4(pack2_bf16(__uint_as_float(o[q]) * inv, __uint_as_float(o[q + 1]) * inv), pack2_bf16(__uint_as_float(o[q + 2]) * inv, __uint_as_float(o[q + 3]) * inv),
+                           pack2_bf16(__uint_as_float(o[q + 4]) * inv, __uint_as_float(o[q + 5]) * inv), pack2_bf16(__uint_as_float(o[q + 6]) * inv, __uint_as_float(o[q + 7]) * inv));
+        }
+      }
+      if (dst) {
+        args.lse[((int64_t)w.b * args.heads + w.h) * args.time + row] = (m + log2f(l)) * LN2;
+        if (!(l > 0.0f) || !isfinite(l) || !isfinite(m)) raise_fault(args.fault, OP_SDPA);
+      }
+    }
+  }
+  if (*abort_flag) __nanosleep(200000);
+  fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
 // ================================================================================================ backward
 // A prepass writes Dr = rowsum(dO . O) and lse * log2(e); then two kernels, each recomputing P from lse (no atomics,
 // one writer per gradient element):
@@ -1021,7 +1266,7 @@ ojc_status make_map(ojc_backend* be, const char* op, CUtensorMap* map, const ojc
   return OJC_OK;
 }
 
-bool g_sdpa_one_tile_forward = false;   // ojc_sdpa_forward_variant: time the one-tile kernel against the two-tile one
+int g_sdpa_forward_variant = 0;   // ojc_sdpa_forward_variant: 1 forces the one-tile, one-launch-per-tile kernel (timing the others against it)
 
 bool strides_ok(const ojc_tensor* t) {
   return (reinterpret_cast<uintptr_t>(t->data) & 15) == 0 && t->stride[3] == 1 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 && t->stride[2] % 8 == 0 &&
@@ -1044,6 +1289,17 @@ static ojc_status launch_fwd2(ojc_backend* be, const char* op, const CUtensorMap
   bool& attr = attr_of[be->device];
   if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwd2_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2<D>::SMEM_BYTES), op); attr = true; }
   sdpa_fwd2_tcgen05_kernel<D><<<grid, FWD2_THREADS, Fwd2<D>::SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
+  OJC_LAUNCHED(be, op);
+  return OJC_OK;
+}
+
+template <int D>
+static ojc_status launch_fwdp(ojc_backend* be, const char* op, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& args, int total_tiles) {
+  static PerDeviceFlag attr_of;
+  bool& attr = attr_of[be->device];
+  if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwdp_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdP<D>::SMEM_BYTES), op); attr = true; }
+  const int grid = std::min(total_tiles, be->sm_count * FwdP<D>::CTAS);
+  sdpa_fwdp_tcgen05_kernel<D><<<grid, NTHREADS, FwdP<D>::SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }
@@ -1073,11 +1329,12 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
   // Two query tiles per CTA (P in tensor memory) where it measured faster: head_dim 128, where one CTA owns the SM either way
   // ([8,16,4096,128]: 671 us against 686 us). At head_dim 64 two one-tile CTAs share an SM and overlap each other's softmax, and
   // the short walks of T = 1024 favour them (162 us against 181 us at B 32, H 12).
-  if (d.dim == 128 && d.time > BM && !g_sdpa_one_tile_forward) {
+  if (d.dim == 128 && d.time > BM && g_sdpa_forward_variant != 1) {
     dim3 grid2((unsigned)(((d.time + 2 * BM - 1) / (2 * BM)) * args.planes));
     return d.dim == 64 ? launch_fwd2<64>(be, op, mq, mk, mv, args, grid2) : launch_fwd2<128>(be, op, mq, mk, mv, args, grid2);
   }
   dim3 grid((unsigned)(((d.time + BM - 1) / BM) * args.planes));
+  if (d.dim == 64 && g_sdpa_forward_variant != 1 && grid.x > (unsigned)(be->sm_count * FwdP<64>::CTAS)) return launch_fwdp<64>(be, op, mq, mk, mv, args, (int)grid.x);
   return d.dim == 64 ? launch_fwd<64>(be, op, mq, mk, mv, args, grid) : launch_fwd<128>(be, op, mq, mk, mv, args, grid);
 }
 
@@ -1137,6 +1394,7 @@ bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_t
   return strides_ok(gq) && strides_ok(gk) && strides_ok(gv) && (gout->stride[1] < gout->stride[2]) == hf;
 }
 
-// Instrumentation (no counterpart in the reference): 0 = the library's choice (two query tiles per CTA whenever the sequence has two),
-// 1 = always the one-tile kernel. Lets the op benchmark time the two forward kernels against each other on the same inputs.
-extern "C" ojc_status ojc_sdpa_forward_variant(int32_t one_tile) { g_sdpa_one_tile_forward = one_tile != 0; return OJC_OK; }
+// Instrumentation (no counterpart in the reference): 0 = the library's choice (head_dim 128: two query tiles per CTA; head_dim 64:
+// persistent CTAs once there are more tiles than CTA slots), 1 = always the one-tile, one-CTA-per-tile kernel. Lets the op benchmark time
+// the forward kernels against each other on the same inputs.
+extern "C" ojc_status ojc_sdpa_forward_variant(int32_t one_tile) { g_sdpa_forward_variant = one_tile != 0 ? 1 : 0; return OJC_OK; }

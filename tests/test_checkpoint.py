@@ -158,6 +158,31 @@ def test_save_then_resume_restores_every_tensor_the_step_and_the_cursor(tmp_path
     assert ck.decode_state((target / ck.STATE_FILE).read_bytes())["step"] == 21 and [p.name for p in tmp_path.iterdir()] == ["ckpt"]
 
 
+def test_a_save_that_died_between_its_two_renames_is_recovered(tmp_path, host_pair):
+    """recover_replaced_dir (ojas-io/src/replace.rs:372-378): the old checkpoint was moved aside under another process's pid and the new
+    one never took its place. resume finds it by prefix and moves it back; a later save sweeps every leftover."""
+    import os
+    src, dst, cfg = host_pair
+    src.steps_done = 5
+    run = ck.compute_run_id(ck.spec_json(src.spec), cfg.to_json(), src.w)
+    target = tmp_path / "ckpt"
+    ck.save(src, target, cfg, DataCursor(0, 3), run)
+    os.rename(target, tmp_path / ".ckpt.old-424242")                 # the crash: first rename done, second never happened
+    (tmp_path / ".ckpt.stage-424242").mkdir()                        # ... and the half-written new directory is still there
+    (tmp_path / ".ckpt.stage-424242" / ck.MODEL_FILE).write_bytes(b"partial")
+    cursor, got_run = ck.resume(dst, target, cfg)
+    assert cursor == DataCursor(0, 3) and got_run == run and dst.steps_done == 5
+    assert [p.name for p in tmp_path.iterdir()] == ["ckpt"]
+    # with the target present, leftovers are swept and the checkpoint in place is the one that counts
+    (tmp_path / ".ckpt.old-7").mkdir()
+    assert ck.recover_replaced_dir(target) is False and [p.name for p in tmp_path.iterdir()] == ["ckpt"]
+    # a save over a died swap restores first, then replaces
+    os.rename(target, tmp_path / ".ckpt.old-99")
+    src.steps_done = 6
+    ck.save(src, target, cfg, DataCursor(0, 4), run)
+    assert ck.decode_state((target / ck.STATE_FILE).read_bytes())["step"] == 6 and [p.name for p in tmp_path.iterdir()] == ["ckpt"]
+
+
 def test_save_and_resume_refusals_leave_things_untouched(tmp_path, host_pair):
     src, dst, cfg = host_pair
     run = "00000000000000aa"

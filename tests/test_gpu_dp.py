@@ -178,3 +178,30 @@ def test_the_library_communicator_runs_the_data_parallel_step_and_splits_muon(tm
     for i, info in enumerate(table):
         want, got = otr.params[i].astype(np.float64).ravel(), r0["p0." + info.name].astype(np.float64).ravel()
         assert np.linalg.norm(got - want) <= 1e-4 * max(np.linalg.norm(want), 1e-30), info.name
+
+
+def test_two_backends_on_two_devices_in_one_process():
+    """Function attributes (dynamic shared-memory limits, cluster occupancy) are per device: a second backend on another GPU must set its
+    own, or its first tensor-core launch fails. One process, two devices, the kernels that need more than 48 KB of shared memory."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from oracle import oracle as orc
+    from ojas_b200 import CudaBackend, DType
+    x, w = orc.round_bf16(orc.SplitMix64(1).vec(512 * 256, 0.5).reshape(512, 256)), orc.round_bf16(orc.SplitMix64(2).vec(768 * 256, 0.5).reshape(768, 256))
+    q = orc.round_bf16(orc.init_normal("q", 5, 1.0, (1, 2, 384, 128)))
+    want_y = orc.linear_forward(x, w)
+    want_o, _ = orc.causal_sdpa_forward(q, q, q)
+    for device in (0, 1):
+        be = CudaBackend(device, 4 << 30)
+        try:
+            y = be.linear_forward(be.upload(x, DType.BF16), be.upload(w, DType.BF16), out_dtype=DType.F32).numpy()      # two-SM tcgen05 GEMM
+            assert np.linalg.norm(y - want_y) <= 1e-5 * np.linalg.norm(want_y), device
+            dq = be.upload(q, DType.BF16)
+            o, lse = be.causal_sdpa_forward(dq, dq, dq)                                                                 # tcgen05 attention, head_dim 128
+            gq, gk, gv = be.causal_sdpa_backward(dq, dq, dq, o, lse, dq)
+            assert np.linalg.norm(o.numpy() - want_o) <= 2e-2 * np.linalg.norm(want_o), device
+            assert np.isfinite(gq.numpy()).all() and np.isfinite(gk.numpy()).all() and np.isfinite(gv.numpy()).all()
+            be.sync()
+        finally:
+            be.close()
