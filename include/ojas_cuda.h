@@ -89,7 +89,7 @@ uint64_t ojc_kernel_launches(ojc_backend* be);                                  
 /* ---- instrumentation (no counterpart in the reference): when enabled, every tensor-core GEMM launch is bracketed by CUDA
  *      events on the backend's stream; the read call waits for the stream, returns the summed device time, the summed
  *      2*m*n*k and the launch count since the last read, and resets them. */
-ojc_status ojc_sdpa_forward_variant(int32_t one_tile);   /* 0: the library's choice of attention forward kernel; 1: always the one-query-tile kernel (for timing the two) */
+ojc_status ojc_sdpa_forward_variant(int32_t variant);    /* attention kernels on the tensor cores. 0: the library's choice; 1: one CTA per tile (for timing the persistent kernels against it); 2: the persistent kernels on at most three CTAs (tests: several tiles per CTA on small shapes) */
 ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable);
 ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches);
 ojc_status ojc_stream_wait_event(ojc_backend* be, void* cuda_stream, void* cuda_event);  /* cuda_stream waits for an event recorded by this backend (NULL stream: the backend's own) */

@@ -1247,6 +1247,435 @@ sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   }
 }
 
+// ================================================================================================ backward, persistent CTAs
+// The two backward kernels with their roles kept alive over many tiles, as the persistent forward kernel: a CTA takes every
+// gridDim.x-th tile of the long-walks-first order and runs them as one stream of 64-wide steps. The step ring never drains between
+// tiles, the tile the CTA keeps (K and V, or Q and dO) is reloaded as soon as the last S-type product that reads it has finished
+// (under that step's exp phase, its accumulating products and the tile's final stores), the next tile's first S-type products go out
+// under the current tile's last step, and the accumulators are handed back as soon as the compute threads hold them in registers,
+// so their conversion and stores run under the next tile's walk. TMEM and the barriers are set up once per CTA.
+enum { QP_QDFULL = 0, QP_QDEMPTY, QP_INFULL0, QP_INEMPTY0 = QP_INFULL0 + DQ_STAGES, QP_SFULL = QP_INEMPTY0 + DQ_STAGES, QP_SFREE, QP_PREADY, QP_PFREE, QP_DONE, QP_ACCFREE,
+       QP_COUNT };
+
+struct DqWalk {
+  int q0, b, h, hk, iters;
+  __device__ __forceinline__ bool set(const BwdArgs& args, int tiles, int total, int item) {
+    const int g = blockIdx.x + item * gridDim.x;
+    if (g >= total) return false;
+    const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
+    q0 = (tiles - 1 - ord.rank) * BM;
+    b = ord.plane / args.heads; h = ord.plane % args.heads; hk = h / (args.heads / args.kv_heads);
+    iters = (min(args.time, q0 + BM) + SUB - 1) / SUB;
+    return true;
+  }
+};
+
+// COLS accumulator columns of this thread's TMEM lane into registers
+template <int COLS>
+__device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&r)[COLS]) {
+#pragma unroll
+  for (int c = 0; c < COLS / 32; ++c) tmem_ld32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+  tmem_wait_ld();
+}
+template <int COLS>
+__device__ __forceinline__ void store_acc_bf16(bf16* dst, const uint32_t (&r)[COLS], float mul) {
+  if (!dst) return;
+#pragma unroll
+  for (int i = 0; i < COLS; i += 8)
+    *reinterpret_cast<uint4*>(dst + i) =
+        make_uint4(pack2_bf16(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul), pack2_bf16(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul),
+                   pack2_bf16(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul), pack2_bf16(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul));
+}
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, Dq<D>::CTAS)
+sdpa_bwd_dq_p_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  using C = Dq<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STEP_BYTES = C::STEP_BYTES;
+  constexpr uint32_t STEP16 = STEP_BYTES >> 4;
+  static_assert(QP_COUNT * 8 + 8 <= 128, "barrier table");
+  auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + C::OFF_BAR + 8 * QP_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = (args.time + BM - 1) / BM, total = tiles * args.planes;
+
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_g);
+    for (int i = 0; i < QP_COUNT; ++i) mbar_init(bar(i), (i == QP_PREADY || i == QP_SFREE || i == QP_ACCFREE) ? 256 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: S [0,64), dP [64,128), dQ [128,128+D)
+
+  if (warp == 8) {
+    if (lane == 0) {
+      DqWalk w;
+      int gs = 0;
+      bool ok = true;
+      for (int item = 0; ok && w.set(args, tiles, total, item); ++item) {
+        // the Q / dO tile is free once the previous tile's last S / dP have read it
+        if (item > 0 && !mbar_wait(bar(QP_QDEMPTY), (item - 1) & 1, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(QP_QDFULL), 2 * TILE_BYTES);
+        load_tile<NSUB, 128>(base + C::OFF_Q, &tm_q, bar(QP_QDFULL), args.h_first, w.h, w.q0, w.b);
+        load_tile<NSUB, 128>(base + C::OFF_G, &tm_g, bar(QP_QDFULL), args.h_first, w.h, w.q0, w.b);
+        for (int it = 0; it < w.iters; ++it, ++gs) {
+          const int s = gs % DQ_STAGES;
+          if (gs >= DQ_STAGES && !mbar_wait(bar(QP_INEMPTY0 + s), ((gs / DQ_STAGES) & 1) ^ 1, args.fault, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(bar(QP_INFULL0 + s), 2 * STEP_BYTES);
+          load_tile<NSUB, 64>(base + C::OFF_K + s * STEP_BYTES, &tm_k, bar(QP_INFULL0 + s), args.h_first, w.hk, it * SUB, w.b);
+          load_tile<NSUB, 64>(base + C::OFF_V + s * STEP_BYTES, &tm_v, bar(QP_INFULL0 + s), args.h_first, w.hk, it * SUB, w.b);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(BM, SUB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
+      const uint32_t q_lo = desc_lo(base + C::OFF_Q, 0), g_lo = desc_lo(base + C::OFF_G, 0), k_lo = desc_lo(base + C::OFF_K, 0), v_lo = desc_lo(base + C::OFF_V, 0);
+      const uint32_t km_lo = desc_lo(base + C::OFF_K, ST64), ds_lo = desc_lo(base + C::OFF_DS, 0);
+      // S = Q K^T and dP = dO V^T of global step n; `last`: the tile's last such pair, after which Q / dO may be replaced
+      auto issue_s = [&](uint32_t n, bool last) {
+        const uint32_t st = (n % DQ_STAGES) * STEP16;
+#pragma unroll
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base, q_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, k_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
+#pragma unroll
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base + 64, g_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, v_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
+        umma_commit(bar(QP_SFULL));
+        if (last) umma_commit(bar(QP_QDEMPTY));
+      };
+      DqWalk cur, nxt;
+      bool have = cur.set(args, tiles, total, 0);
+      bool ok = have && mbar_wait(bar(QP_QDFULL), 0, args.fault, abort_flag) && mbar_wait(bar(QP_INFULL0), 0, args.fault, abort_flag);
+      if (ok) { fence_after(); issue_s(0, cur.iters == 1); }
+      uint32_t gs = 0;
+      for (int item = 0; have && ok; ++item) {
+        const bool more = nxt.set(args, tiles, total, item + 1);
+        for (int it = 0; it < cur.iters && ok; ++it, ++gs) {
+          // the next step's S / dP (this tile's, or the first of the next tile): ahead of this step's dQ with two CTAs per SM, after it with one
+          auto next_s = [&]() -> bool {
+            const bool within = it + 1 < cur.iters;
+            if (!within && !more) return true;
+            if (C::CTAS == 2 && !mbar_wait(bar(QP_SFREE), gs & 1, args.fault, abort_flag)) return false;
+            const uint32_t n = gs + 1;
+            if (!within && !mbar_wait(bar(QP_QDFULL), (item + 1) & 1, args.fault, abort_flag)) return false;
+            if (!mbar_wait(bar(QP_INFULL0 + n % DQ_STAGES), (n / DQ_STAGES) & 1, args.fault, abort_flag)) return false;
+            fence_after();
+            issue_s(n, within ? it + 2 == cur.iters : nxt.iters == 1);
+            return true;
+          };
+          if (C::CTAS == 2 && !next_s()) { ok = false; break; }
+          if (!mbar_wait(bar(QP_PREADY), gs & 1, args.fault, abort_flag)) { ok = false; break; }
+          // a tile's first dQ product overwrites the accumulator: the previous tile's rows must hold theirs in registers
+          if (it == 0 && item > 0 && !mbar_wait(bar(QP_ACCFREE), (item - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+          const uint32_t st = (gs % DQ_STAGES) * STEP16;
+#pragma unroll
+          for (uint32_t kk = 0; kk < SUB / 16; ++kk)
+            umma_lh(tmem_base + 128, ds_lo + kk * KSTEP, km_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar(QP_INEMPTY0 + gs % DQ_STAGES));
+          umma_commit(bar(QP_PFREE));
+          if (it + 1 == cur.iters) umma_commit(bar(QP_DONE));
+          if (C::CTAS == 1 && !next_s()) { ok = false; break; }
+        }
+        cur = nxt;
+        have = more;
+      }
+    }
+  } else {
+    const int tid = threadIdx.x & 127, half = warp >> 2;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const float sl2 = args.scale * LOG2E;
+    uint8_t* ds_row = base_ptr + C::OFF_DS + tid * 128;
+    DqWalk w;
+    uint32_t gs = 0;
+    bool ok = true;
+    for (int item = 0; ok && w.set(args, tiles, total, item); ++item) {
+      const int row = w.q0 + tid;
+      const int64_t idx = ((int64_t)w.b * args.heads + w.h) * args.time + row;
+      const float lse_row = row < args.time ? args.lse[idx] * LOG2E : INFINITY, dr_row = row < args.time ? args.dr[idx] : 0.0f;
+      for (int it = 0; it < w.iters; ++it, ++gs) {
+        const int key0 = it * SUB + half * 32;
+        if (!mbar_wait(bar(QP_SFULL), gs & 1, args.fault, abort_flag)) { ok = false; break; }
+        fence_after();
+        uint32_t rs[32], rp[32];
+        tmem_ld32(lane_base + half * 32, rs);
+        tmem_ld32(lane_base + 64 + half * 32, rp);
+        tmem_wait_ld();
+        if (C::CTAS == 2) { fence_before(); mbar_arrive(bar(QP_SFREE)); }
+        auto stats = [&](int, float (&l2)[8], float (&dd)[8]) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { l2[e] = lse_row; dd[e] = dr_row; }
+        };
+        auto vis = [&](int c) { return key0 + c <= row && key0 + c < args.time; };
+        const bool masked = it * SUB + SUB > w.q0 || it * SUB + SUB > args.time;
+        if (C::CTAS == 2) {
+          uint4 dsp[4];
+          auto keep = [&](int g, const uint4&, const uint4& ds) { dsp[g] = ds; };
+          if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, keep); else bwd_step<false>(rs, rp, sl2, stats, vis, keep);
+          if (gs > 0 && !mbar_wait(bar(QP_PFREE), (gs - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) store_chunk(ds_row, dsp[g], half, g, tid);
+        } else {
+          auto put = [&](int g, const uint4&, const uint4& ds) { store_chunk(ds_row, ds, half, g, tid); };
+          if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, put); else bwd_step<false>(rs, rp, sl2, stats, vis, put);
+        }
+        fence_async_smem();
+        mbar_arrive(bar(QP_PREADY));
+      }
+      if (!ok) break;
+      if (!mbar_wait(bar(QP_DONE), item & 1, args.fault, abort_flag)) { ok = false; break; }
+      fence_after();
+      uint32_t acc[D / 2];
+      load_acc<D / 2>(lane_base + 128 + half * (D / 2), acc);
+      fence_before();
+      mbar_arrive(bar(QP_ACCFREE));              // the accumulator may take the next tile while these rows are converted and stored
+      store_acc_bf16<D / 2>(row < args.time ? args.g0.row(w.b, w.h, row) + half * (D / 2) : nullptr, acc, args.scale);
+    }
+  }
+  if (*abort_flag) __nanosleep(200000);
+  fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+enum { KP_KVFULL = 0, KP_KVEMPTY, KP_INFULL0, KP_INEMPTY0 = KP_INFULL0 + IN_STAGES, KP_SFULL = KP_INEMPTY0 + IN_STAGES, KP_SFREE, KP_PREADY, KP_PFREE, KP_DONE, KP_ACCFREE,
+       KP_COUNT };
+
+struct DkvWalk {
+  int k0, b, hk, q_subs, iters;
+  __device__ __forceinline__ bool set(const BwdArgs& args, int tiles, int total, int item) {
+    const int g = blockIdx.x + item * gridDim.x;
+    if (g >= total) return false;
+    const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
+    k0 = ord.rank * BN;                          // early key tiles see the most queries
+    b = ord.plane / args.kv_heads; hk = ord.plane % args.kv_heads;
+    q_subs = (args.time - k0 + SUB - 1) / SUB;
+    iters = (args.heads / args.kv_heads) * q_subs;
+    return true;
+  }
+};
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, Dkv<D>::CTAS)
+sdpa_bwd_dkv_p_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }
+  uint8_t* base_ptr = smem_raw;
+  using C = Dkv<D>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STEP_BYTES = C::STEP_BYTES;
+  constexpr uint32_t STEP16 = STEP_BYTES >> 4, TCOLS = C::TMEM_COLS;
+  static_assert(KP_COUNT * 8 + 8 <= 128, "barrier table");
+  auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + C::OFF_BAR + 8 * KP_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = (args.time + BN - 1) / BN, total = tiles * args.planes, rep = args.heads / args.kv_heads;
+
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_g);
+    for (int i = 0; i < KP_COUNT; ++i) mbar_init(bar(i), (i == KP_PREADY || i == KP_SFREE || i == KP_ACCFREE) ? 256 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: S^T [0,64), dP^T [64,128), dV [128,128+D), dK [128+D,128+2D)
+
+  if (warp == 8) {
+    if (lane == 0) {
+      DkvWalk w;
+      int gs = 0;
+      bool ok = true;
+      for (int item = 0; ok && w.set(args, tiles, total, item); ++item) {
+        if (item > 0 && !mbar_wait(bar(KP_KVEMPTY), (item - 1) & 1, args.fault, abort_flag)) break;
+        mbar_expect_tx(bar(KP_KVFULL), 2 * TILE_BYTES);
+        load_tile<NSUB, 128>(base + C::OFF_K, &tm_k, bar(KP_KVFULL), args.h_first, w.hk, w.k0, w.b);
+        load_tile<NSUB, 128>(base + C::OFF_V, &tm_v, bar(KP_KVFULL), args.h_first, w.hk, w.k0, w.b);
+        for (int it = 0; it < w.iters; ++it, ++gs) {
+          const int s = gs % C::STAGES, h = w.hk * rep + it / w.q_subs, q0 = w.k0 + (it % w.q_subs) * SUB;
+          if (gs >= C::STAGES && !mbar_wait(bar(KP_INEMPTY0 + s), ((gs / C::STAGES) & 1) ^ 1, args.fault, abort_flag)) { ok = false; break; }
+          const uint32_t stat_bytes = C::STATS_IN_SMEM ? (uint32_t)min(SUB, args.time - q0) * 4u : 0u;
+          mbar_expect_tx(bar(KP_INFULL0 + s), 2 * STEP_BYTES + 2 * stat_bytes);
+          load_tile<NSUB, 64>(base + C::OFF_Q + s * STEP_BYTES, &tm_q, bar(KP_INFULL0 + s), args.h_first, h, q0, w.b);
+          load_tile<NSUB, 64>(base + C::OFF_G + s * STEP_BYTES, &tm_g, bar(KP_INFULL0 + s), args.h_first, h, q0, w.b);
+          if (C::STATS_IN_SMEM) {
+            const int64_t idx = ((int64_t)w.b * args.heads + h) * args.time + q0;
+            bulk_load(base + C::OFF_STAT + s * 512, args.lse + idx, stat_bytes, bar(KP_INFULL0 + s));
+            bulk_load(base + C::OFF_STAT + s * 512 + 256, args.dr + idx, stat_bytes, bar(KP_INFULL0 + s));
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(BN, SUB, 0, 0), idesc_o = make_idesc(BN, D, 0, 1);
+      const uint32_t k_lo = desc_lo(base + C::OFF_K, 0), v_lo = desc_lo(base + C::OFF_V, 0), q_lo = desc_lo(base + C::OFF_Q, 0), g_lo = desc_lo(base + C::OFF_G, 0);
+      const uint32_t qm_lo = desc_lo(base + C::OFF_Q, ST64), gm_lo = desc_lo(base + C::OFF_G, ST64);
+      const uint32_t p_lo = desc_lo(base + C::OFF_P, 0), ds_lo = desc_lo(base + C::OFF_DS, 0);
+      auto issue_s = [&](uint32_t n, bool last) {
+        const uint32_t st = (n % C::STAGES) * STEP16;
+#pragma unroll
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base, k_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, q_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
+#pragma unroll
+        for (uint32_t kk = 0; kk < D / 16; ++kk)
+          umma_lh(tmem_base + 64, v_lo + (kk >> 2) * ST128_16 + (kk & 3) * KSTEP, g_lo + st + (kk >> 2) * ST64_16 + (kk & 3) * KSTEP, HI, idesc_s, kk > 0);
+        umma_commit(bar(KP_SFULL));
+        if (last) umma_commit(bar(KP_KVEMPTY));
+      };
+      DkvWalk cur, nxt;
+      bool have = cur.set(args, tiles, total, 0);
+      bool ok = have && mbar_wait(bar(KP_KVFULL), 0, args.fault, abort_flag) && mbar_wait(bar(KP_INFULL0), 0, args.fault, abort_flag);
+      if (ok) { fence_after(); issue_s(0, cur.iters == 1); }
+      uint32_t gs = 0;
+      for (int item = 0; have && ok; ++item) {
+        const bool more = nxt.set(args, tiles, total, item + 1);
+        for (int it = 0; it < cur.iters && ok; ++it, ++gs) {
+          auto next_s = [&]() -> bool {
+            const bool within = it + 1 < cur.iters;
+            if (!within && !more) return true;
+            if (C::CTAS == 2 && !mbar_wait(bar(KP_SFREE), gs & 1, args.fault, abort_flag)) return false;
+            const uint32_t n = gs + 1;
+            if (!within && !mbar_wait(bar(KP_KVFULL), (item + 1) & 1, args.fault, abort_flag)) return false;
+            if (!mbar_wait(bar(KP_INFULL0 + n % C::STAGES), (n / C::STAGES) & 1, args.fault, abort_flag)) return false;
+            fence_after();
+            issue_s(n, within ? it + 2 == cur.iters : nxt.iters == 1);
+            return true;
+          };
+          if (C::CTAS == 2 && !next_s()) { ok = false; break; }
+          if (!mbar_wait(bar(KP_PREADY), gs & 1, args.fault, abort_flag)) { ok = false; break; }
+          if (it == 0 && item > 0 && !mbar_wait(bar(KP_ACCFREE), (item - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+          fence_after();
+          const uint32_t st = (gs % C::STAGES) * STEP16;
+#pragma unroll
+          for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dV += P^T dO
+            umma_lh(tmem_base + 128, p_lo + kk * KSTEP, gm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (uint32_t kk = 0; kk < SUB / 16; ++kk)  // dK += dS^T Q
+            umma_lh(tmem_base + 128 + D, ds_lo + kk * KSTEP, qm_lo + st + kk * MNSTEP, HI, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar(KP_INEMPTY0 + gs % C::STAGES));
+          umma_commit(bar(KP_PFREE));
+          if (it + 1 == cur.iters) umma_commit(bar(KP_DONE));
+          if (C::CTAS == 1 && !next_s()) { ok = false; break; }
+        }
+        cur = nxt;
+        have = more;
+      }
+    }
+  } else {
+    const int tid = threadIdx.x & 127, half = warp >> 2;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const float sl2 = args.scale * LOG2E;
+    uint8_t* p_row = base_ptr + C::OFF_P + tid * 128;
+    uint8_t* ds_row = base_ptr + C::OFF_DS + tid * 128;
+    const float* stat = reinterpret_cast<const float*>(base_ptr + C::OFF_STAT);
+    DkvWalk w, wn;
+    // statistics kept in registers (two CTAs per SM): lane c of a warp holds those of column c of its half, fetched one step ahead
+    auto stat_of = [&](const DkvWalk& t, bool valid, int it, float& l2, float& dr) {
+      const int h = t.hk * rep + it / t.q_subs, q = t.k0 + (it % t.q_subs) * SUB + half * 32 + lane;
+      const bool in = !C::STATS_IN_SMEM && valid && q < args.time;
+      const int64_t idx = ((int64_t)t.b * args.heads + h) * args.time + q;
+      l2 = in ? args.lse[idx] * LOG2E : INFINITY;
+      dr = in ? args.dr[idx] : 0.0f;
+    };
+    uint32_t gs = 0;
+    bool ok = true, have = w.set(args, tiles, total, 0);
+    float my_l2 = INFINITY, my_dr = 0.0f, next_l2, next_dr;
+    if (have) stat_of(w, true, 0, my_l2, my_dr);
+    for (int item = 0; ok && have; ++item) {
+      const bool more = wn.set(args, tiles, total, item + 1);
+      const int key = w.k0 + tid;
+      int q0 = w.k0;
+      for (int it = 0; it < w.iters; ++it, ++gs) {
+        if (it + 1 < w.iters) stat_of(w, true, it + 1, next_l2, next_dr); else stat_of(wn, more, 0, next_l2, next_dr);
+        if (!mbar_wait(bar(KP_SFULL), gs & 1, args.fault, abort_flag)) { ok = false; break; }
+        fence_after();
+        uint32_t rs[32], rp[32];
+        tmem_ld32(lane_base + half * 32, rs);
+        tmem_ld32(lane_base + 64 + half * 32, rp);
+        tmem_wait_ld();
+        if (C::CTAS == 2) { fence_before(); mbar_arrive(bar(KP_SFREE)); }
+        const int qb = q0 + half * 32;
+        const float* st = stat + (gs % C::STAGES) * 128 + half * 32;
+        auto stats = [&](int g, float (&l2)[8], float (&dd)[8]) {
+          if (C::STATS_IN_SMEM) {
+            const float4 a = *reinterpret_cast<const float4*>(st + g * 8), b4 = *reinterpret_cast<const float4*>(st + g * 8 + 4);
+            const float4 c = *reinterpret_cast<const float4*>(st + SUB + g * 8), d = *reinterpret_cast<const float4*>(st + SUB + g * 8 + 4);
+            l2[0] = a.x * LOG2E; l2[1] = a.y * LOG2E; l2[2] = a.z * LOG2E; l2[3] = a.w * LOG2E;
+            l2[4] = b4.x * LOG2E; l2[5] = b4.y * LOG2E; l2[6] = b4.z * LOG2E; l2[7] = b4.w * LOG2E;
+            dd[0] = c.x; dd[1] = c.y; dd[2] = c.z; dd[3] = c.w; dd[4] = d.x; dd[5] = d.y; dd[6] = d.z; dd[7] = d.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { l2[e] = __shfl_sync(0xffffffffu, my_l2, g * 8 + e); dd[e] = __shfl_sync(0xffffffffu, my_dr, g * 8 + e); }
+          }
+        };
+        auto vis = [&](int c) { return key < args.time && qb + c < args.time && key <= qb + c; };
+        const bool masked = q0 < w.k0 + BN || q0 + SUB > args.time || w.k0 + BN > args.time;
+        if (C::CTAS == 2) {
+          uint4 pp[4], dsp[4];
+          auto keep = [&](int g, const uint4& p, const uint4& ds) { pp[g] = p; dsp[g] = ds; };
+          if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, keep); else bwd_step<false>(rs, rp, sl2, stats, vis, keep);
+          if (gs > 0 && !mbar_wait(bar(KP_PFREE), (gs - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) { store_chunk(p_row, pp[g], half, g, tid); store_chunk(ds_row, dsp[g], half, g, tid); }
+        } else {
+          auto put = [&](int g, const uint4& p, const uint4& ds) { store_chunk(p_row, p, half, g, tid); store_chunk(ds_row, ds, half, g, tid); };
+          if (masked) bwd_step<true>(rs, rp, sl2, stats, vis, put); else bwd_step<false>(rs, rp, sl2, stats, vis, put);
+        }
+        fence_async_smem();
+        mbar_arrive(bar(KP_PREADY));
+        my_l2 = next_l2; my_dr = next_dr;
+        q0 += SUB;
+        if (q0 >= args.time) q0 = w.k0;
+      }
+      if (!ok) break;
+      if (!mbar_wait(bar(KP_DONE), item & 1, args.fault, abort_flag)) { ok = false; break; }
+      fence_after();
+      uint32_t acc[D];
+      load_acc<D>(lane_base + 128 + (half == 0 ? 0 : D), acc);
+      fence_before();
+      mbar_arrive(bar(KP_ACCFREE));
+      if (half == 0) store_acc_bf16<D>(key < args.time ? args.g1.row(w.b, w.hk, key) : nullptr, acc, 1.0f);              // dV
+      else store_acc_bf16<D>(key < args.time ? args.g0.row(w.b, w.hk, key) : nullptr, acc, args.scale);                 // dK
+      w = wn;
+      have = more;
+    }
+  }
+  if (*abort_flag) __nanosleep(200000);
+  fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TCOLS) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -1266,7 +1695,7 @@ ojc_status make_map(ojc_backend* be, const char* op, CUtensorMap* map, const ojc
   return OJC_OK;
 }
 
-int g_sdpa_forward_variant = 0;   // ojc_sdpa_forward_variant: 1 forces the one-tile, one-launch-per-tile kernel (timing the others against it)
+int g_sdpa_forward_variant = 0;   // ojc_sdpa_forward_variant: 0 the library's choice, 1 one CTA per tile, 2 persistent kernels on three CTAs
 
 bool strides_ok(const ojc_tensor* t) {
   return (reinterpret_cast<uintptr_t>(t->data) & 15) == 0 && t->stride[3] == 1 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 && t->stride[2] % 8 == 0 &&
@@ -1298,7 +1727,7 @@ static ojc_status launch_fwdp(ojc_backend* be, const char* op, const CUtensorMap
   static PerDeviceFlag attr_of;
   bool& attr = attr_of[be->device];
   if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(sdpa_fwdp_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdP<D>::SMEM_BYTES), op); attr = true; }
-  const int grid = std::min(total_tiles, be->sm_count * FwdP<D>::CTAS);
+  const int grid = std::min(total_tiles, g_sdpa_forward_variant == 2 ? 3 : be->sm_count * FwdP<D>::CTAS);
   sdpa_fwdp_tcgen05_kernel<D><<<grid, NTHREADS, FwdP<D>::SMEM_BYTES, be->stream>>>(mq, mk, mv, args);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
@@ -1334,7 +1763,8 @@ ojc_status sdpa_forward_tcgen05(ojc_backend* be, const ojc_tensor* q, const ojc_
     return d.dim == 64 ? launch_fwd2<64>(be, op, mq, mk, mv, args, grid2) : launch_fwd2<128>(be, op, mq, mk, mv, args, grid2);
   }
   dim3 grid((unsigned)(((d.time + BM - 1) / BM) * args.planes));
-  if (d.dim == 64 && g_sdpa_forward_variant != 1 && grid.x > (unsigned)(be->sm_count * FwdP<64>::CTAS)) return launch_fwdp<64>(be, op, mq, mk, mv, args, (int)grid.x);
+  if (d.dim == 64 && g_sdpa_forward_variant != 1 && (g_sdpa_forward_variant == 2 || grid.x > (unsigned)(be->sm_count * FwdP<64>::CTAS)))
+    return launch_fwdp<64>(be, op, mq, mk, mv, args, (int)grid.x);
   return d.dim == 64 ? launch_fwd<64>(be, op, mq, mk, mv, args, grid) : launch_fwd<128>(be, op, mq, mk, mv, args, grid);
 }
 
@@ -1346,6 +1776,8 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
   if (!attr) {
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dkv<D>::SMEM_BYTES), op);
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_p_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dkv<D>::SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_p_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);
     attr = true;
   }
   if (dr_work) {   // the caller has no Dr of its own
@@ -1359,13 +1791,19 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
   a.planes = d.batch * d.kv_heads;
   a.group = planes_per_group(d.time, d.dim, a.planes);
   dim3 grid_k((unsigned)(((d.time + BN - 1) / BN) * a.planes));
-  sdpa_bwd_dkv_tcgen05_kernel<D><<<grid_k, BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);   // q, dO in 64-row steps
+  // persistent CTAs at head_dim 64 once there are more tiles than CTA slots (B 32 x H 12 x T 1024: 411 us against 423 us for both kernels;
+  // at head_dim 128, one CTA per SM, they measured slower: [8,16,4096,128] 3264 us against 3127 us)
+  const bool persist_k = g_sdpa_forward_variant == 2 || (D == 64 && g_sdpa_forward_variant != 1 && (int)grid_k.x > be->sm_count * Dkv<D>::CTAS);
+  if (persist_k) sdpa_bwd_dkv_p_kernel<D><<<g_sdpa_forward_variant == 2 ? std::min<unsigned>(grid_k.x, 3u) : (unsigned)(be->sm_count * Dkv<D>::CTAS), BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);
+  else sdpa_bwd_dkv_tcgen05_kernel<D><<<grid_k, BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);   // q, dO in 64-row steps
   OJC_LAUNCHED(be, op);
   a.g0 = SdpaView<bf16>{(bf16*)gq->data, gq->stride[0], gq->stride[1], gq->stride[2]};
   a.planes = d.batch * d.heads;
   a.group = planes_per_group(d.time, d.dim, a.planes);
   dim3 grid_q((unsigned)(((d.time + BM - 1) / BM) * a.planes));
-  sdpa_bwd_dq_tcgen05_kernel<D><<<grid_q, BWD_THREADS, Dq<D>::SMEM_BYTES, be->stream>>>(m[0], m[5], m[6], m[3], a);      // k, v in 64-row steps
+  const bool persist_q = g_sdpa_forward_variant == 2 || (D == 64 && g_sdpa_forward_variant != 1 && (int)grid_q.x > be->sm_count * Dq<D>::CTAS);
+  if (persist_q) sdpa_bwd_dq_p_kernel<D><<<g_sdpa_forward_variant == 2 ? std::min<unsigned>(grid_q.x, 3u) : (unsigned)(be->sm_count * Dq<D>::CTAS), BWD_THREADS, Dq<D>::SMEM_BYTES, be->stream>>>(m[0], m[5], m[6], m[3], a);
+  else sdpa_bwd_dq_tcgen05_kernel<D><<<grid_q, BWD_THREADS, Dq<D>::SMEM_BYTES, be->stream>>>(m[0], m[5], m[6], m[3], a);      // k, v in 64-row steps
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }
@@ -1394,7 +1832,8 @@ bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_t
   return strides_ok(gq) && strides_ok(gk) && strides_ok(gv) && (gout->stride[1] < gout->stride[2]) == hf;
 }
 
-// Instrumentation (no counterpart in the reference): 0 = the library's choice (head_dim 128: two query tiles per CTA; head_dim 64:
-// persistent CTAs once there are more tiles than CTA slots), 1 = always the one-tile, one-CTA-per-tile kernel. Lets the op benchmark time
-// the forward kernels against each other on the same inputs.
-extern "C" ojc_status ojc_sdpa_forward_variant(int32_t one_tile) { g_sdpa_forward_variant = one_tile != 0 ? 1 : 0; return OJC_OK; }
+// Instrumentation (no counterpart in the reference): 0 = the library's choice (forward: two query tiles per CTA at head_dim 128, persistent
+// CTAs at head_dim 64; backward: persistent CTAs; the persistent kernels once there are more tiles than CTA slots), 1 = always one CTA per
+// tile (to time the others against it), 2 = the persistent kernels on a grid of at most three CTAs, whatever the size (so that small
+// test shapes walk several tiles per CTA).
+extern "C" ojc_status ojc_sdpa_forward_variant(int32_t variant) { g_sdpa_forward_variant = variant >= 0 && variant <= 2 ? variant : 0; return OJC_OK; }

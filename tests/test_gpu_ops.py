@@ -155,6 +155,34 @@ def test_causal_sdpa_bf16_tensor_core_tier(be, shape, hkv, window):
     assert max(rel(rq.numpy(), ogq), rel(rk.numpy(), ogk), rel(rv.numpy(), ogv)) <= 2e-2
 
 
+@pytest.mark.parametrize("shape,hkv", [((2, 4, 384, 64), 2), ((1, 3, 300, 64), 3), ((3, 2, 640, 64), 1), ((2, 2, 516, 128), 2), ((1, 4, 1024, 128), 4)])
+def test_persistent_attention_kernels_walk_several_tiles_per_cta(be, shape, hkv):
+    """The persistent forward (head_dim 64) and backward kernels normally start once a launch has more tiles than the GPU has CTA slots;
+    here they are forced onto three CTAs, so each walks several tiles (ragged ends, grouped-query heads, tile boundaries), and compared
+    with the oracle at the tensor-core tier's 2e-2; the backward kernels must also reproduce the bits of the one-CTA-per-tile kernels."""
+    import ctypes as C
+    from ojas_b200 import DType
+    from ojas_b200._lib import lib
+    b, h, t, d = shape
+    q, gy = orc.round_bf16(rnd(310, shape, 1.0)), orc.round_bf16(rnd(313, shape, 1.0))
+    k, v = orc.round_bf16(rnd(311, (b, hkv, t, d), 1.0)), orc.round_bf16(rnd(312, (b, hkv, t, d), 1.0))
+    oy, olse = orc.causal_sdpa_forward(q, k, v)
+    want = orc.causal_sdpa_backward(q, k, v, oy, olse, gy)
+    dq, dk, dv, dgy = (be.upload(a, DType.BF16) for a in (q, k, v, gy))
+    try:
+        lib.ojc_sdpa_forward_variant(C.c_int32(2))
+        y, lse = be.causal_sdpa_forward(dq, dk, dv)
+        got = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]
+        lib.ojc_sdpa_forward_variant(C.c_int32(1))
+        one = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]       # same output and lse in: the same arithmetic in the same order
+    finally:
+        lib.ojc_sdpa_forward_variant(C.c_int32(0))
+    assert rel(y.numpy(), oy) <= 2e-2 and rel(lse.numpy(), olse) <= 1e-4
+    assert max(rel(g, w) for g, w in zip(got, want)) <= 2e-2
+    for a, c in zip(got, one):
+        assert np.array_equal(a, c)
+
+
 def test_sdpa_reads_permuted_views_without_a_copy(be):
     """[B,T,H,dh] storage viewed as [B,H,T,dh] gives the same result as permute + contiguous attention."""
     b, t, h, d = 2, 33, 3, 16
