@@ -94,6 +94,26 @@ ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable);
 ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches);
 ojc_status ojc_stream_wait_event(ojc_backend* be, void* cuda_stream, void* cuda_event);  /* cuda_stream waits for an event recorded by this backend (NULL stream: the backend's own) */
 
+/* ---- owner-thread session: how a host whose calls come from many threads holds this single-owner-thread backend. ojas-capi does it for
+ *      Metal with a thread that owns the device and a channel of requests (ojas-capi/src/owner.rs); its load path still refuses the CUDA
+ *      device (ojas-capi/src/load.rs:41-56), partly because the CUDA runtime handle is `!Send`. ojc_session_open starts a thread that opens
+ *      the backend and is the only thread that ever calls into it; the wait for the open is limited (open_timeout_ms), and a session
+ *      abandoned at that limit closes whatever it opens later. ojc_session_call runs fn(backend, arg) on the owner thread and returns
+ *      its status (the error text is copied to the caller's thread); calls from several threads are served in arrival order.
+ *      ojc_session_train_open / _run / _close are the training requests (OP_TRAIN_OPEN, OP_TRAIN_STEP of ojas-capi/src/train.rs) as such calls. */
+typedef struct ojc_session ojc_session;
+typedef int32_t (*ojc_session_fn)(ojc_backend* be, void* arg);   /* returns an ojc_status value */
+typedef struct ojc_model_spec ojc_model_spec;
+typedef struct ojc_train_config ojc_train_config;
+typedef struct ojc_step_report ojc_step_report;
+typedef struct ojc_trainer ojc_trainer;
+ojc_status ojc_session_open(int32_t device_ordinal, uint64_t budget_bytes, uint64_t open_timeout_ms, ojc_session** out);
+ojc_status ojc_session_call(ojc_session* session, ojc_session_fn fn, void* arg);
+ojc_status ojc_session_close(ojc_session* session);   /* answers every queued call, closes the backend on its own thread, joins it */
+ojc_status ojc_session_train_open(ojc_session* session, const ojc_model_spec* spec, const ojc_train_config* cfg, int64_t batch, int64_t seq, ojc_trainer** out);
+ojc_status ojc_session_train_run(ojc_session* session, ojc_trainer* trainer, const uint32_t* const* ids_host, const uint32_t* const* targets_host, int64_t k, ojc_step_report* report);
+ojc_status ojc_session_train_close(ojc_session* session, ojc_trainer* trainer);
+
 /* Self-test of the bounded device-side wait (no counterpart in the reference; its device-lost test traps the GPU, which this library
  * never does): one small kernel waits, with the helper every tensor-pipeline role uses, on a barrier that nothing arrives on, for at
  * most limit_cycles SM cycles (<= 2e8, about 0.1 s). Every thread must give up, the kernel ends in order, and the call returns

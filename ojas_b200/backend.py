@@ -136,9 +136,17 @@ class CudaBackend:
         _check(lib.ojc_open(C.c_int32(device), C.c_uint64(budget_bytes), C.byref(h)))
         self._handle = h
 
+    @classmethod
+    def _adopt(cls, handle) -> "CudaBackend":
+        """A view of a backend some other owner opens and closes (a Session's owner thread)."""
+        be = cls.__new__(cls)
+        be._handle, be._borrowed = C.c_void_p(handle), True
+        return be
+
     def close(self):
         if self._handle:
-            lib.ojc_close(self._handle)
+            if not getattr(self, "_borrowed", False):
+                lib.ojc_close(self._handle)
             self._handle = None
 
     def __del__(self):
@@ -738,3 +746,45 @@ class Trainer:
             _check(lib.ojc_trainer_bucket_ready_event(self._h, C.c_int64(i), C.byref(ev)))
             out.append((ptr.value, n.value, ev.value))
         return out
+
+
+_SESSION_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p)
+
+
+class Session:
+    """An owner-thread session (ojc_session_*): the library starts a thread that opens the backend and is the only one ever to touch
+    it, which is how ojas-capi holds a backend whose handle is single-owner-thread (ojas-capi/src/owner.rs). `run(fn)` executes
+    `fn(backend)` on that thread and returns its value, from whichever thread calls it; calls from several threads queue up."""
+
+    def __init__(self, device: int = 0, budget_bytes: int = 160 << 30, open_timeout_ms: int = 120_000):
+        self._h = None
+        h = C.c_void_p()
+        _check(lib.ojc_session_open(C.c_int32(device), C.c_uint64(budget_bytes), C.c_uint64(open_timeout_ms), C.byref(h)))
+        self._h = h
+
+    def run(self, fn):
+        box = {}
+
+        def thunk(be_ptr, _arg):
+            try:
+                box["value"] = fn(CudaBackend._adopt(be_ptr))
+                return 0
+            except OjasError as e:
+                box["error"] = e
+                return e.status
+            except BaseException as e:      # a Python error on the owner thread is re-raised on the caller's
+                box["error"] = e
+                return 10
+        st = lib.ojc_session_call(self._h, _SESSION_FN(thunk), None)
+        if "error" in box:
+            raise box["error"]
+        _check(st)
+        return box.get("value")
+
+    def close(self):
+        if self._h:
+            lib.ojc_session_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()

@@ -61,3 +61,15 @@ def test_schedule_multipliers_of_the_library_match_nanolab(golden_dir):
         with pytest.raises(OjasError) as e:
             bad.lr_multiplier(step)
         assert e.value.kind == "OutOfRange"
+
+
+def test_a_session_without_a_device_reports_the_open_error_and_leaves_no_thread_behind():
+    import threading
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    from ojas_b200 import OjasError, Session
+    before = threading.active_count()
+    with pytest.raises(OjasError) as e:
+        Session(0, 1 << 30, open_timeout_ms=30_000)
+    assert e.value.kind == "NoDevice" and threading.active_count() == before

@@ -299,3 +299,62 @@ def test_refusals_come_before_any_work(be, golden_dir):
     with pytest.raises(OjasError) as e:
         Trainer(be, spec, TrainConfig(schedule="cosine", total_steps=0), 2, 32)
     assert e.value.kind == "OutOfRange"
+
+
+def test_an_owner_thread_session_serves_calls_from_many_threads(golden_dir):
+    """The session ojas-capi needs for a single-owner-thread backend (ojas-capi/src/owner.rs): one library thread opens the backend and is
+    the only one to touch it; trainer calls arrive from other threads, also concurrently, and are served in order. The losses equal a
+    plain single-threaded run bit for bit."""
+    import threading
+    from ojas_b200 import CudaBackend, Session, Trainer
+    spec, _, init = tiny(golden_dir)
+    _, _, cfg = trace(golden_dir, "f32")
+    tcfg = train_config(cfg)
+    bin_, sampler = feed(golden_dir, cfg)
+    steps = [[sampler.next_batch(bin_) for _ in range(cfg["grad_accum"])] for _ in range(6)]
+
+    be = CudaBackend(0, 2 << 30)
+    tr = Trainer(be, spec, tcfg, cfg["batch_size"], cfg["block_size"])
+    tr.set_params([init[p.name] for p in tr.params])
+    want = [tr.run(b).loss for b in steps]
+    tr.close()
+    be.close()
+
+    session = Session(0, 2 << 30)
+    owner = session.run(lambda be: threading.get_ident())
+    assert owner != threading.get_ident()
+
+    def open_trainer_on_owner(be):
+        t = Trainer(be, spec, tcfg, cfg["batch_size"], cfg["block_size"])
+        t.set_params([init[p.name] for p in t.params])
+        return t
+    t = session.run(open_trainer_on_owner)
+    got, seen = [None] * 6, set()
+
+    def worker(i):
+        def call(be):
+            seen.add(threading.get_ident())
+            return t.run(steps[i]).loss
+        got[i] = session.run(call)
+    for i in range(3):                                   # three threads, one after the other
+        th = threading.Thread(target=worker, args=(i,))
+        th.start(); th.join()
+    assert got[:3] == want[:3] and seen == {owner}
+    # concurrent callers: every call still runs on the owner thread, one at a time (the order of arrival decides which step is which)
+    order = []
+
+    def racer(_):
+        def call(be):
+            i = 3 + len(order)
+            order.append(threading.get_ident())
+            return t.run(steps[i]).loss
+        return session.run(call)
+    results = []
+    threads = [threading.Thread(target=lambda k=k: results.append(racer(k))) for k in range(3)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert sorted(results) == sorted(want[3:]) and set(order) == {owner}
+    session.run(lambda be: t.close())
+    session.close()
