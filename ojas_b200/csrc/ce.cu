@@ -156,7 +156,9 @@ ce_rows_fast_kernel(const float* __restrict__ logits, int64_t ld, const uint32_t
 // The bf16 step's form: BF16 logits (the head GEMM's output, rounded once from its f32 accumulator, as a matmul output is under
 // torch's autocast) turned into the BF16 gradient IN PLACE: a thread reads the same 8-value groups in both passes and overwrites only
 // those, so no second tile exists. Statistics and the loss term are f32. 6 bytes per logit cross HBM for the head (GEMM write 2,
-// read 2, write 2) instead of 10 with an f32 tile and a separate gradient tile. Same row rules as above.
+// read 2, write 2) instead of 10 with an f32 tile and a separate gradient tile. Three passes over a row (the later ones hit L2):
+// maximum; one ex2 per logit, summed in f32 and written back as bf16 exponentials; exponentials scaled into the gradient. The
+// gradient therefore carries two bf16 roundings (the exponential's and its own). Same row rules as above.
 __device__ __forceinline__ void unpack_bf16x8(const uint4& t, float (&v)[8]) {
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -180,33 +182,43 @@ ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_
     return;
   }
   const float picked = __bfloat162float(z[target]);   // read before any thread overwrites the row
-  float tm = -INFINITY, ts = 0.0f;
+  // pass 1: the row maximum (no exponentials)
+  float tm = -INFINITY;
 #pragma unroll 2
   for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
     float v[8];
     unpack_bf16x8(*reinterpret_cast<const uint4*>(z + 8 * i), v);
-    float m8 = v[0];
 #pragma unroll
-    for (int e = 1; e < 8; ++e) m8 = fmaxf(m8, v[e]);
-    m8 *= L2E;
-    if (m8 > tm) { ts *= ex2_fast(tm - m8); tm = m8; }
+    for (int e = 0; e < 8; ++e) tm = fmaxf(tm, v[e]);
+  }
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) tm = fmaxf(tm, __bfloat162float(z[c]));
+  const float mx = block_max(tm, red);
+  const float mx2 = mx * L2E;
+  // pass 2: one ex2 per logit. The sum is taken over the f32 exponentials; when a gradient is wanted each group is written back
+  // as bf16 exponentials over the logits it came from (a thread reads and writes the same groups in every pass)
+  float ts = 0.0f;
+#pragma unroll 2
+  for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
+    float v[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(z + 8 * i), v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ts += ex2_fast(fmaf(v[e], L2E, -tm));
+    for (int e = 0; e < 8; ++e) { v[e] = ex2_fast(fmaf(v[e], L2E, -mx2)); ts += v[e]; }
+    if (want_grad) *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
   }
   for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) {
-    const float a = __bfloat162float(z[c]) * L2E;
-    if (a > tm) { ts *= ex2_fast(tm - a); tm = a; }
-    ts += ex2_fast(a - tm);
+    const float e = ex2_fast(fmaf(__bfloat162float(z[c]), L2E, -mx2));
+    ts += e;
+    if (want_grad) z[c] = __float2bfloat16_rn(e);
   }
-  const float mx2 = block_max(tm, red);
-  const float sum = block_sum(tm == -INFINITY ? 0.0f : ts * ex2_fast(tm - mx2), red);
-  const float mx = mx2 * (1.0f / L2E);
+  const float sum = block_sum(ts, red);
   if (!(isfinite(mx2) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
+  // the target-excluded form for a collapsed row (the target holds the maximum and the sum rounds to 1): the others' exponentials
   float other = 0.0f;
   bool collapsed = false;
-  if (picked * L2E == mx2 && sum == 1.0f) {
+  if (picked == mx && sum == 1.0f) {
     float o = 0.0f;
-    for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += ex2_fast(__bfloat162float(z[c]) * L2E - mx2);
+    if (want_grad) { for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += __bfloat162float(z[c]); }        // the row now holds exponentials
+    else { for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += ex2_fast(fmaf(__bfloat162float(z[c]), L2E, -mx2)); }
     other = block_sum(o, red);
     collapsed = other > 0.0f;
   }
@@ -215,17 +227,14 @@ ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_
   const float denom = (float)valid[0];
   const float inv = collapsed ? 1.0f / (1.0f + other) : 1.0f / sum;
   const float k = inv / denom * seed;
-  __syncthreads();                          // every read of the row by the statistics is done
+  // pass 3: exponentials -> gradient, one multiply each
 #pragma unroll 2
   for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
     float v[8];
     unpack_bf16x8(*reinterpret_cast<const uint4*>(z + 8 * i), v);
-    uint32_t w[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(ex2_fast(fmaf(v[2 * e], L2E, -mx2)) * k, ex2_fast(fmaf(v[2 * e + 1], L2E, -mx2)) * k);
-    *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(pack_bf16x2(v[0] * k, v[1] * k), pack_bf16x2(v[2] * k, v[3] * k), pack_bf16x2(v[4] * k, v[5] * k), pack_bf16x2(v[6] * k, v[7] * k));
   }
-  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) z[c] = __float2bfloat16_rn(ex2_fast(fmaf(__bfloat162float(z[c]), L2E, -mx2)) * k);
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) z[c] = __float2bfloat16_rn(__bfloat162float(z[c]) * k);
   __syncthreads();
   if (threadIdx.x == 0) {
     const float gt = collapsed ? -(other * inv) / denom : (ex2_fast(fmaf(picked, L2E, -mx2)) * inv) / denom - 1.0f / denom;
