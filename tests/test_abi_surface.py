@@ -73,3 +73,18 @@ def test_a_session_without_a_device_reports_the_open_error_and_leaves_no_thread_
     with pytest.raises(OjasError) as e:
         Session(0, 1 << 30, open_timeout_ms=30_000)
     assert e.value.kind == "NoDevice" and threading.active_count() == before
+
+
+def test_the_communicator_reaches_nccl_without_a_device():
+    """ojc_comm_unique_id loads NCCL with dlopen on first use and needs no GPU: two ids differ, and ojc_comm_init without a device is refused
+    by the backend check, not by a crash."""
+    import ctypes as C
+    from ojas_b200._lib import lib
+    a, b = (C.c_uint8 * 128)(), (C.c_uint8 * 128)()
+    st = lib.ojc_comm_unique_id(a)
+    if st == 11:        # Unsupported: no libnccl.so.2 on this machine
+        pytest.skip(lib.ojc_last_error().decode())
+    assert st == 0 and lib.ojc_comm_unique_id(b) == 0
+    assert any(bytes(a)) and bytes(a) != bytes(b)
+    out = C.c_void_p()
+    assert lib.ojc_comm_init(None, C.c_int32(0), C.c_int32(1), a, C.byref(out)) != 0 and not out.value
