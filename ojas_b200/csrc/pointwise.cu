@@ -146,6 +146,35 @@ __global__ void embedding_scatter_sorted_kernel(const uint32_t* __restrict__ sor
   }
 }
 
+// The same sums for F32 gradients of 16-byte rows, one warp per vocabulary row: lane 0 finds the row's run and the warp shares it,
+// the columns move as float4, and a row no token selected is left alone when the result accumulates into `out` (adding zero to
+// every element would only read and rewrite it). Same order of additions per element as the kernel above: the bits are the same.
+__global__ void embedding_scatter_sorted_rows_kernel(const uint32_t* __restrict__ sorted_ids, const uint32_t* __restrict__ sorted_tok, const float* __restrict__ grad,
+                                                     float* __restrict__ out, int64_t tokens, int64_t vocab, int dim4, int accumulate) {
+  const int lane = threadIdx.x & 31;
+  const int64_t v = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (v >= vocab) return;
+  int64_t lo = 0, n = 0;
+  if (lane == 0) {
+    int64_t hi = tokens;
+    while (lo < hi) { const int64_t mid = (lo + hi) >> 1; if (sorted_ids[mid] < (uint32_t)v) lo = mid + 1; else hi = mid; }
+    while (lo + n < tokens && sorted_ids[lo + n] == (uint32_t)v) ++n;
+  }
+  lo = __shfl_sync(0xffffffffu, lo, 0);
+  n = __shfl_sync(0xffffffffu, n, 0);
+  if (n == 0 && accumulate) return;
+  float4* dst = reinterpret_cast<float4*>(out) + v * dim4;
+  for (int c = lane; c < dim4; c += 32) {
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int64_t p = lo; p < lo + n; ++p) {
+      const float4 g = reinterpret_cast<const float4*>(grad)[(int64_t)sorted_tok[p] * dim4 + c];
+      acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+    }
+    if (accumulate) { const float4 o = dst[c]; acc.x = o.x + acc.x; acc.y = o.y + acc.y; acc.z = o.z + acc.z; acc.w = o.w + acc.w; }
+    dst[c] = acc;
+  }
+}
+
 ojc_status embedding_backward_impl(ojc_backend* be, const uint32_t* ids, const void* grad, int32_t grad_dtype, float* out,
                                    int64_t tokens, int64_t vocab, int64_t dim, bool accumulate) {
   const char* op = "embedding_backward";
@@ -165,6 +194,12 @@ ojc_status embedding_backward_impl(ojc_backend* be, const uint32_t* ids, const v
   OJC_CUDA(be, cub::DeviceRadixSort::SortPairs(cub_ws, cub_bytes, ids, sorted_ids, iota, sorted_tok, (int)tokens, 0, bits, be->stream), op);
   be->launches += 2;
   int threads = dim >= 256 ? 256 : (dim >= 128 ? 128 : 64);
+  if (grad_dtype == OJC_F32 && dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    embedding_scatter_sorted_rows_kernel<<<(unsigned)((vocab * 32 + 255) / 256), 256, 0, be->stream>>>(sorted_ids, sorted_tok, (const float*)grad, out, tokens, vocab,
+                                                                                                      (int)(dim / 4), accumulate ? 1 : 0);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  }
   if (grad_dtype == OJC_F32)
     embedding_scatter_sorted_kernel<float><<<(unsigned)vocab, threads, 0, be->stream>>>(sorted_ids, sorted_tok, (const float*)grad, out, tokens, dim, accumulate);
   else

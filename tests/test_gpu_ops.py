@@ -212,6 +212,11 @@ def test_embedding_gather_is_bit_exact_and_scatter_matches(be):
     g = be.embedding_backward(dt, di, be.upload(grad)).numpy()
     og = orc.embedding_backward(vocab, ids, grad)
     assert np.array_equal(g.view(np.uint32), og.view(np.uint32))  # ascending token order per row: same bits as the CPU
+    for v2, d2 in ((5000, 96), (5000, 50)):     # mostly empty rows; 16-byte rows (one warp per row) and rows that are not (one block per row)
+        ids2 = np.array([rng.below(v2) for _ in range(300)], np.uint32)
+        grad2 = rnd(4, (300, d2))
+        got = be.embedding_backward(be.empty((v2, d2)), be.upload(ids2), be.upload(grad2)).numpy()
+        assert np.array_equal(got.view(np.uint32), orc.embedding_backward(v2, ids2, grad2).view(np.uint32))
     bad = ids.copy(); bad[17] = vocab
     be.embedding_forward(dt, be.upload(bad))
     with pytest.raises(OjasError) as e:
