@@ -4,13 +4,14 @@
 // 128-bit accesses throughout; per-column weight-gradient sums are two-stage with a fixed order (no float atomics).
 #include "common.cuh"
 #include "ops.cuh"
+#include "swiglu_math.cuh"
 
 namespace {
 
 // hardware round-to-nearest-even conversions and approximate sigmoid: these kernels only run in the bf16 tier
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) { uint32_t r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
-__device__ __forceinline__ float rbf(float v) { return __uint_as_float(pack2(0.0f, v) & 0xffff0000u); }
-__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+using swiglu::pack2;
+using swiglu::sigmoid_fast;
+__device__ __forceinline__ float rbf(float v) { return swiglu::round_bf16(v); }
 
 __device__ __forceinline__ void load8(const bf16* p, float v[8]) {
   const uint4 t = *reinterpret_cast<const uint4*>(p);
@@ -231,7 +232,7 @@ __global__ void swiglu_rows_forward_kernel(const bf16* __restrict__ au, int64_t 
     float a[8], u[8], r[8];
     load8(au + row * ld + c, a); load8(au + row * ld + (int64_t)f8 * 8 + c, u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) r[k] = rbf(a[k] * sigmoid_fast(a[k])) * u[k];
+    for (int k = 0; k < 8; ++k) r[k] = swiglu::forward_elem(a[k], u[k]);
     store8(m + row * (int64_t)f8 * 8 + c, r);
   }
 }
@@ -242,11 +243,7 @@ __global__ void swiglu_rows_backward_kernel(const bf16* __restrict__ au, const b
     float a[8], u[8], g[8], ra[8], ru[8];
     load8(au + row * ld + c, a); load8(au + row * ld + (int64_t)f8 * 8 + c, u); load8(gm + row * (int64_t)f8 * 8 + c, g);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float sg = sigmoid_fast(a[k]);
-      ru[k] = g[k] * rbf(a[k] * sg);
-      ra[k] = rbf(g[k] * u[k]) * sg * (1.0f + a[k] * (1.0f - sg));
-    }
+    for (int k = 0; k < 8; ++k) swiglu::backward_elem(a[k], u[k], g[k], ra[k], ru[k]);
     store8(gau + row * ld + c, ra); store8(gau + row * ld + (int64_t)f8 * 8 + c, ru);
   }
 }

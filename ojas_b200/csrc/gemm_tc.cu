@@ -26,6 +26,7 @@
 
 #include "common.cuh"
 #include "gemm.cuh"
+#include "swiglu_math.cuh"
 #include "tc_common.cuh"
 
 namespace {
@@ -55,6 +56,8 @@ struct TcArgs {
   int batch;                // independent matrices: a unit is (matrix, tile, split); batch > 1 needs tma_store and splits == 1
   int tma_store;            // finished blocks leave through TMA tile stores (no residual operand; split partials need m % 32 == 0)
   const bf16* ns_src; int64_t ns_ld, ns_bs; float ns_src_mul, ns_acc_mul;   // Newton-Schulz combine epilogue (NsCombine); ns_src null: none
+  const bf16* sw_au; int64_t sw_ld;   // SwiGLU-backward epilogue (SwigluGrad): a at column 0, u at column n of rows sw_ld wide; null: none
+  int sw_f;                 // SwiGLU-forward epilogue (SwigluForward): the hidden width F; C is (a | u), n = 2 F
   int tiles_n_fast;         // tile order: 1 = neighbouring CTAs share an A row block (few column tiles), 0 = they share a B column block
 };
 
@@ -73,6 +76,9 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 
 // Drains one warp's share of a finished accumulator tile: TMEM lanes [32 quarter, +32) x columns [col_begin, col_end)
 // starting at `tsrc`, destined for rows row_base.. and columns col_tile0.. of matrix bz of C (or of the split's partial).
+// EPI selects the epilogue compiled in (kernels of their own, so the plain products keep their registers):
+// 0 plain, 1 SwiGLU backward (SwigluGrad), 2 SwiGLU forward (SwigluForward; two-SM kernel only, drained by drain_swiglu_forward).
+template <int EPI>
 __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int col_tile0, int split, int bz, int lane,
                                            int col_begin, int col_end, uint8_t* stage_bytes, uint32_t stage_addr) {
   float* stage = reinterpret_cast<float*>(stage_bytes);
@@ -84,6 +90,55 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
     const int y = (args.splits > 1 ? split * args.m : 0) + row_base;
 #pragma unroll 1
     for (int c0 = col_begin; c0 < col_end; c0 += step) {
+      if constexpr (EPI == 1) {
+        // The accumulator is g, the gradient of m = bf16(silu(a)) * u, rounded to bf16 as a stored g would be. Two boxes leave
+        // instead of one: g_a for columns x.. and g_u for columns n + x.. of the output rows; the second waits in registers
+        // until the first has been read out of the staging rows. This lane's 64 gate and 64 up activations are in flight
+        // while the accumulator arrives, and the 64 columns are taken in two halves to stay inside the register file.
+        const int x = col_tile0 + c0;
+        const bool live = row_base + lane < args.m && x < args.n;   // a clipped box still computes, from row 0's values
+        const uint4* arow = reinterpret_cast<const uint4*>(args.sw_au + (live ? (int64_t)(row_base + lane) * args.sw_ld + x : 0));
+        const uint4* urow = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(arow) + args.n);
+        uint4 qa[8], qu[8], second[8];
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) { qa[ci] = __ldg(arow + ci); qu[ci] = __ldg(urow + ci); }
+        if (lane == 0) bulk_wait_read();       // the previous box has left the staging rows
+        __syncwarp();
+        uint8_t* rowp = stage_bytes + lane * 128;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tsrc + c0 + half * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int cj = 0; cj < 4; ++cj) {
+            const int ci = half * 4 + cj;
+            const uint32_t* v = &r[cj * 8];
+            const uint32_t wa[4] = {qa[ci].x, qa[ci].y, qa[ci].z, qa[ci].w}, wu[4] = {qu[ci].x, qu[ci].y, qu[ci].z, qu[ci].w};
+            float ga[8], gu[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float av = (e & 1) ? __uint_as_float(wa[e >> 1] & 0xffff0000u) : __uint_as_float(wa[e >> 1] << 16);
+              const float uv = (e & 1) ? __uint_as_float(wu[e >> 1] & 0xffff0000u) : __uint_as_float(wu[e >> 1] << 16);
+              swiglu::backward_elem(av, uv, swiglu::round_bf16(__uint_as_float(v[e])), ga[e], gu[e]);
+            }
+            *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+                make_uint4(pack2_bf16(ga[0], ga[1]), pack2_bf16(ga[2], ga[3]), pack2_bf16(ga[4], ga[5]), pack2_bf16(ga[6], ga[7]));
+            second[ci] = make_uint4(pack2_bf16(gu[0], gu[1]), pack2_bf16(gu[2], gu[3]), pack2_bf16(gu[4], gu[5]), pack2_bf16(gu[6], gu[7]));
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        const bool issue = lane == 0 && x < args.n && row_base < args.m;
+        if (issue) { tma_store_3d(&tmap_c, stage_addr, x, y, bz); bulk_commit(); bulk_wait_read(); }
+        __syncwarp();
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = second[ci];
+        fence_async_smem();
+        __syncwarp();
+        if (issue) { tma_store_3d(&tmap_c, stage_addr, args.n + x, y, bz); bulk_commit(); }
+        continue;
+      }
       uint32_t r[32], r2[32];
       tmem_ld32(tsrc + c0, r);
       if (bf) tmem_ld32(tsrc + c0 + 32, r2);
@@ -190,6 +245,57 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
   }
 }
 
+// SwiGLU forward on a finished two-SM accumulator whose 256 columns are gate columns [j0, j0 + 128) followed by up columns
+// [F + j0, F + j0 + 128) of the (a | u) row: this warp takes 64 gate columns and the 64 up columns that go with them, rounds both
+// to bf16 (what the stored a and u hold), and sends out three boxes in turn through its staging rows: a, u and
+// m = bf16(silu(a)) * u. The same bits as the product followed by the row kernel.
+__device__ __forceinline__ void drain_swiglu_forward(const TcArgs& args, const CUtensorMap& tmap_c, const CUtensorMap& tmap_m, uint32_t tsrc, int row_base, int j0,
+                                                     int bz, int lane, int half, uint8_t* stage_bytes, uint32_t stage_addr) {
+  const int j = j0 + half * 64;
+  uint4 second[8], third[8];
+  uint8_t* rowp = stage_bytes + lane * 128;
+  if (lane == 0) bulk_wait_read();           // the previous tile's last box has left the staging rows
+  __syncwarp();
+#pragma unroll
+  for (int part = 0; part < 2; ++part) {
+    uint32_t ra[32], ru[32];
+    tmem_ld32(tsrc + half * 64 + part * 32, ra);
+    tmem_ld32(tsrc + 128 + half * 64 + part * 32, ru);
+    tmem_wait_ld();
+#pragma unroll
+    for (int cj = 0; cj < 4; ++cj) {
+      const int ci = part * 4 + cj;
+      float a[8], u[8], m[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        a[e] = swiglu::round_bf16(__uint_as_float(ra[cj * 8 + e]));
+        u[e] = swiglu::round_bf16(__uint_as_float(ru[cj * 8 + e]));
+        m[e] = swiglu::forward_elem(a[e], u[e]);
+      }
+      *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = make_uint4(pack2_bf16(a[0], a[1]), pack2_bf16(a[2], a[3]), pack2_bf16(a[4], a[5]), pack2_bf16(a[6], a[7]));
+      second[ci] = make_uint4(pack2_bf16(u[0], u[1]), pack2_bf16(u[2], u[3]), pack2_bf16(u[4], u[5]), pack2_bf16(u[6], u[7]));
+      third[ci] = make_uint4(pack2_bf16(m[0], m[1]), pack2_bf16(m[2], m[3]), pack2_bf16(m[4], m[5]), pack2_bf16(m[6], m[7]));
+    }
+  }
+  const bool issue = lane == 0 && j < args.sw_f && row_base < args.m;
+  fence_async_smem();
+  __syncwarp();
+  if (issue) { tma_store_3d(&tmap_c, stage_addr, j, row_base, bz); bulk_commit(); bulk_wait_read(); }
+  __syncwarp();
+#pragma unroll
+  for (int ci = 0; ci < 8; ++ci) *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = second[ci];
+  fence_async_smem();
+  __syncwarp();
+  if (issue) { tma_store_3d(&tmap_c, stage_addr, args.sw_f + j, row_base, bz); bulk_commit(); bulk_wait_read(); }
+  __syncwarp();
+#pragma unroll
+  for (int ci = 0; ci < 8; ++ci) *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = third[ci];
+  fence_async_smem();
+  __syncwarp();
+  if (issue) { tma_store_3d(&tmap_m, stage_addr, j, row_base, bz); bulk_commit(); }
+}
+
+template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                const TcArgs args) {
@@ -297,7 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       fence_after();
       const int row_base = tm * BM + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      drain_tile(args, tmap_c, tsrc, row_base, tn * BN, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
+      drain_tile<EPI>(args, tmap_c, tsrc, row_base, tn * BN, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -327,9 +433,10 @@ constexpr int A2_TILE_BYTES = 128 * BK * 2, B2_TILE_BYTES = 128 * BK * 2, STAGE2
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + EPI_STAGE_BYTES + 256;
 static_assert(SMEM2_BYTES <= 232448, "shared memory per CTA");
 
+template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
-                const TcArgs args) {
+                const __grid_constant__ CUtensorMap tmap_m, const TcArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;               // the same offset in both CTAs (same kernel, same layout)
@@ -375,7 +482,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const int split = ub % args.splits, tile = ub / args.splits;
         const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
         const int kb0 = split * args.kblocks_per_split, kb1 = min(kblocks_total, kb0 + args.kblocks_per_split);
-        const int row0 = tm * BM2 + (int)rank * 128, col0 = tn * BN2 + (int)rank * 128;
+        // SwiGLU forward: the even CTA brings 128 gate columns and the odd one the 128 up columns that go with them
+        const int row0 = tm * BM2 + (int)rank * 128, col0 = EPI == 2 ? (int)rank * args.sw_f + tn * 128 : tn * BN2 + (int)rank * 128;
         bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES2;
@@ -435,7 +543,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       fence_after();
       const int row_base = tm * BM2 + (int)rank * 128 + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
-      drain_tile(args, tmap_c, tsrc, row_base, tn * BN2, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
+      if constexpr (EPI == 2) drain_swiglu_forward(args, tmap_c, tmap_m, tsrc, row_base, tn * 128, bz, lane, (warp - 2) >> 2, stage_bytes, stage_addr);
+      else drain_tile<EPI>(args, tmap_c, tsrc, row_base, tn * BN2, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
@@ -509,6 +618,34 @@ bool operand_ok(const GemmOperand& o, bool is_a, int* mn_major, int64_t* ld) {
 
 }  // namespace
 
+namespace {
+// How many CTA pairs of the two-SM kernel the device runs at once (0: the cluster launch is not available); found once per device.
+ojc_status two_sm_pairs(ojc_backend* be, const char* op, int* pairs) {
+  static PerDeviceInt max_pairs_of(-1);
+  int& max_pairs = max_pairs_of[be->device];
+  if (max_pairs < 0) {
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((unsigned)(be->sm_count & ~1)); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.attrs = attr; cfg.numAttrs = 1;
+    int n_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tc2_kernel<1>, &cfg) != cudaSuccess) { cudaGetLastError(); n_clusters = 0; }
+    max_pairs = n_clusters;
+  }
+  *pairs = max_pairs;
+  return OJC_OK;
+}
+}  // namespace
+
+bool gemm_tc_swiglu_forward_eligible(ojc_backend* be, int64_t m, int64_t n, int64_t ldm, const void* mptr) {
+  int pairs = 0;
+  if (two_sm_pairs(be, "linear_forward", &pairs) != OJC_OK || pairs <= 0) return false;
+  return m >= BM2 && n >= BN2 && n % 256 == 0 && ldm % 8 == 0 && ldm >= n / 2 && (reinterpret_cast<uintptr_t>(mptr) & 15) == 0;
+}
+
 bool gemm_tc_eligible(const GemmOperand& a, const GemmOperand& b, const void* c, int32_t c_dtype, int64_t ldc, int64_t m, int64_t n, int64_t k) {
   int amn, bmn; int64_t lda, ldb;
   if (!operand_ok(a, true, &amn, &lda) || !operand_ok(b, false, &bmn, &ldb)) return false;
@@ -530,7 +667,16 @@ ojc_status gemm_tc(ojc_backend* be, const char* op, const GemmOperand& a, const 
 // `batch` independent products of the same shape; matrix i of A / B / C starts a_bs / b_bs / c_bs elements after matrix i - 1.
 ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a, const GemmOperand& b, void* c, int32_t c_dtype, int64_t ldc, int64_t m,
                            int64_t n, int64_t k, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs, float alpha, bool accumulate, const float* residual,
-                           const NsCombine* combine, bool allow_split) {
+                           const NsCombine* combine, bool allow_split, const SwigluGrad* swiglu_grad, const SwigluForward* swiglu_fwd) {
+  if (swiglu_fwd && !gemm_tc_swiglu_forward_eligible(be, m, n, swiglu_fwd->ldm, swiglu_fwd->m))
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the SwiGLU forward epilogue needs two-SM tiles (256 rows or more), a hidden width that is a multiple of 128 and an aligned bf16 m");
+  if (swiglu_fwd && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine || swiglu_grad || batch != 1))
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the SwiGLU forward epilogue needs a single bf16 product, alpha 1, no accumulation");
+  if (swiglu_fwd) allow_split = false;
+  if (swiglu_grad && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine || batch != 1 || n % 64 != 0 || swiglu_grad->ld % 8 != 0 ||
+                      swiglu_grad->ld < 2 * n || ldc < 2 * n || ((uintptr_t)swiglu_grad->au & 15) != 0))
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the SwiGLU epilogue needs bf16 (a | u) rows and output rows at least 2 n wide, n a multiple of 64, alpha 1, no accumulation");
+  if (swiglu_grad) allow_split = false;
   if (!gemm_tc_eligible(a, b, c, c_dtype, ldc, m, n, k)) return ojc_fail(OJC_ERR_UNSUPPORTED, op, "operands break the tensor-core kernel's alignment rules");
   if (combine && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine->src_ld % 8 != 0 || combine->src_bs % 8 != 0 || ((uintptr_t)combine->src & 15) != 0 || n < 64))
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the combine epilogue needs a bf16 output, alpha 1, no accumulation and an aligned source");
@@ -541,18 +687,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   int amn, bmn; int64_t lda, ldb;
   operand_ok(a, true, &amn, &lda); operand_ok(b, false, &bmn, &ldb);
   // Two-SM tiles (256 x 256 per CTA pair) whenever the output is at least one such tile; the one-SM kernel keeps the rest.
-  static PerDeviceInt max_pairs_of(-1);
-  int& max_pairs = max_pairs_of[be->device];
-  if (max_pairs < 0) {
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.gridDim = dim3((unsigned)(be->sm_count & ~1)); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.attrs = attr; cfg.numAttrs = 1;
-    int n_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tc2_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n_clusters = 0; }
-    max_pairs = n_clusters;
-  }
+  int max_pairs = 0;
+  OJC_TRY(two_sm_pairs(be, op, &max_pairs));
   const bool two_sm = max_pairs > 0 && m >= BM2 && n >= BN2;
   const int tile_m = two_sm ? BM2 : BM, tile_n = two_sm ? BN2 : BN, workers = two_sm ? max_pairs : be->sm_count;
   CUtensorMap ta, tb;
@@ -564,7 +700,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   static PerDeviceFlag attr_set_of;
   bool& attr_set = attr_set_of[be->device];
   if (!attr_set) {
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
     attr_set = true;
   }
   const int tiles = (int)(((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n) * batch);   // units before any split
@@ -593,6 +730,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev; args.batch = (int)batch;
   args.ns_src = combine ? (const bf16*)combine->src : nullptr; args.ns_ld = combine ? combine->src_ld : 0; args.ns_bs = combine ? combine->src_bs : 0;
   args.ns_src_mul = combine ? combine->src_mul : 0.0f; args.ns_acc_mul = combine ? combine->acc_mul : 0.0f;
+  args.sw_f = swiglu_fwd ? (int)(n / 2) : 0;
+  args.sw_au = swiglu_grad ? (const bf16*)swiglu_grad->au : nullptr; args.sw_ld = swiglu_grad ? swiglu_grad->ld : 0;
   if (splits > 1) {
     void* ws = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)splits * m * n * 4, &ws));
@@ -604,11 +743,13 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   CUtensorMap tc = ta;   // unused unless tma_store
   if (args.tma_store) {
     if (splits > 1) OJC_TRY(make_tmap(be, op, &tc, args.partial, (uint64_t)n, (uint64_t)splits * (uint64_t)m, (uint64_t)n, 32, 32, true));
-    else if (args.c_bf16) OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 64, 32, false, batch, c_bs));
+    else if (args.c_bf16) OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)(swiglu_grad ? 2 * n : n), (uint64_t)m, (uint64_t)ldc, 64, 32, false, batch, c_bs));
     else OJC_TRY(make_tmap(be, op, &tc, c, (uint64_t)n, (uint64_t)m, (uint64_t)ldc, 32, 32, true, batch, c_bs));
   } else if (batch > 1) {
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "a batched product needs the tile-store epilogue");
   }
+  CUtensorMap tm = tc;   // the SwiGLU forward epilogue's third output
+  if (swiglu_fwd) OJC_TRY(make_tmap(be, op, &tm, swiglu_fwd->m, (uint64_t)(n / 2), (uint64_t)m, (uint64_t)swiglu_fwd->ldm, 64, 32));
   int grid = tiles * splits < workers ? tiles * splits : workers;
   if (two_sm) grid *= 2;
   ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k * (double)batch};
@@ -617,8 +758,11 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }
     OJC_CUDA(be, cudaEventRecord(sample.start, be->stream), op);
   }
-  if (two_sm) gemm_tc2_kernel<<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, args);
-  else gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
+  if (swiglu_fwd) gemm_tc2_kernel<2><<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, tm, args);
+  else if (two_sm && swiglu_grad) gemm_tc2_kernel<1><<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, tm, args);
+  else if (two_sm) gemm_tc2_kernel<0><<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, tm, args);
+  else if (swiglu_grad) gemm_tc_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
+  else gemm_tc_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
   OJC_LAUNCHED(be, op);
   if (be->profile_gemm) {
     OJC_CUDA(be, cudaEventRecord(sample.stop, be->stream), op);

@@ -22,6 +22,25 @@ ojc_status linear_backward_input_impl(ojc_backend* be, const void* w, int32_t w_
   GemmOperand a{gy, g_dt, nout, 1}, b{w, w_dt, kin, 1};
   return gemm_auto(be, "linear_backward", a, b, gx, gx_dt, kin, rows, kin, nout, 1.0f, accumulate, nullptr);
 }
+bool linear_forward_swiglu_eligible(ojc_backend* be, const void* x, const void* w, const void* au, const void* m, int64_t ld, int64_t rows, int64_t kin, int64_t hidden) {
+  GemmOperand a{x, OJC_BF16, kin, 1}, b{w, OJC_BF16, 1, kin};
+  return ld == 2 * hidden && gemm_tc_eligible(a, b, au, OJC_BF16, ld, rows, 2 * hidden, kin) && gemm_tc_swiglu_forward_eligible(be, rows, 2 * hidden, hidden, m);
+}
+ojc_status linear_forward_swiglu_impl(ojc_backend* be, const void* x, const void* w, void* au, void* m, int64_t ld, int64_t rows, int64_t kin, int64_t hidden) {
+  GemmOperand a{x, OJC_BF16, kin, 1}, b{w, OJC_BF16, 1, kin};
+  const SwigluForward sw{m, hidden};
+  return gemm_tc_batched(be, "linear_forward", a, b, au, OJC_BF16, ld, rows, 2 * hidden, kin, 1, 0, 0, 0, 1.0f, false, nullptr, nullptr, false, nullptr, &sw);
+}
+ojc_status linear_backward_input_swiglu_impl(ojc_backend* be, const void* w, const void* gy, const void* au, void* gau, int64_t ld, int64_t rows, int64_t kin,
+                                             int64_t nout) {
+  GemmOperand a{gy, OJC_BF16, nout, 1}, b{w, OJC_BF16, kin, 1};
+  const SwigluGrad sw{au, ld};
+  return gemm_tc_batched(be, "linear_backward", a, b, gau, OJC_BF16, ld, rows, kin, nout, 1, 0, 0, 0, 1.0f, false, nullptr, nullptr, false, &sw);
+}
+bool linear_backward_input_swiglu_eligible(const void* w, const void* gy, const void* au, const void* gau, int64_t ld, int64_t rows, int64_t kin, int64_t nout) {
+  GemmOperand a{gy, OJC_BF16, nout, 1}, b{w, OJC_BF16, kin, 1};
+  return kin % 64 == 0 && ld % 8 == 0 && ld >= 2 * kin && (reinterpret_cast<uintptr_t>(au) & 15) == 0 && gemm_tc_eligible(a, b, gau, OJC_BF16, ld, rows, kin, nout);
+}
 ojc_status linear_backward_weight_impl(ojc_backend* be, const void* x, int32_t x_dt, const void* gy, int32_t g_dt, float* gw, int64_t rows, int64_t kin,
                                        int64_t nout, bool accumulate) {
   GemmOperand a{gy, g_dt, 1, nout}, b{x, x_dt, kin, 1};

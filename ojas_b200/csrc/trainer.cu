@@ -19,6 +19,9 @@
 #include "optim.cuh"
 #include "sdpa.cuh"
 
+int g_mlp_epilogue_variant = 0;   // ojc_mlp_epilogue_variant: 0 SwiGLU inside the epilogues of the gate/up product and of the down projection's input-gradient product, 1 kernels of its own
+extern "C" ojc_status ojc_mlp_epilogue_variant(int32_t variant) { g_mlp_epilogue_variant = variant == 1 ? 1 : 0; return OJC_OK; }
+
 namespace {
 
 enum { P_NORM1 = 0, P_Q, P_K, P_V, P_O, P_QN, P_KN, P_GW, P_GB, P_LAMBDA, P_NORM2, P_FG, P_FU, P_FD, P_PER_BLOCK };
@@ -250,8 +253,12 @@ ojc_status block_forward(ojc_trainer* tr, int64_t l) {
     OJC_TRY(rms_forward_impl(be, &x1, &n2, eps, &h2, add_in_place ? x_next : nullptr));
   }
   if (fl) {
-    OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, tr->ld_au, nullptr));
-    OJC_TRY(swiglu_rows_forward(be, (const bf16*)a.a, tr->ld_au, (bf16*)a.m, N, F));
+    if (g_mlp_epilogue_variant == 0 && linear_forward_swiglu_eligible(be, a.h2, tr->WM(tr->P(l, P_FG)), a.a, a.m, tr->ld_au, N, d, F)) {
+      OJC_TRY(linear_forward_swiglu_impl(be, a.h2, tr->WM(tr->P(l, P_FG)), a.a, a.m, tr->ld_au, N, d, F));   // a, u and m = silu(a) u from one product
+    } else {
+      OJC_TRY(linear_forward_impl(be, a.h2, A, tr->WM(tr->P(l, P_FG)), A, a.a, A, N, d, tr->ld_au, nullptr));
+      OJC_TRY(swiglu_rows_forward(be, (const bf16*)a.a, tr->ld_au, (bf16*)a.m, N, F));
+    }
     OJC_TRY(linear_forward_impl(be, a.m, A, tr->WM(tr->P(l, P_FD)), A, x_next, OJC_F32, N, F, d, nullptr, true));  // x2 = x1 + down(m)
     return OJC_OK;
   }
@@ -378,11 +385,16 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
       OJC_TRY(block_forward(tr, l));
     }
     // x2 = x1 + down(m)
-    OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
-    OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false); }));
     const bool fl = tr->fused_lin;
+    // With gate and up side by side the SwiGLU gradient leaves the product's epilogue directly and g_m is never stored.
+    const bool in_epilogue = fl && g_mlp_epilogue_variant == 0 &&
+                             linear_backward_input_swiglu_eligible(tr->WM(tr->P(l, P_FD)), gxo, a.a, tr->g_a, tr->ld_au, N, F, d);
+    if (in_epilogue) OJC_TRY(linear_backward_input_swiglu_impl(be, tr->WM(tr->P(l, P_FD)), gxo, a.a, tr->g_a, tr->ld_au, N, F, d));
+    else OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
+    OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false); }));
     const int64_t sq = fl ? tr->ld_qkv : qw, skv = fl ? tr->ld_qkv : kvw;
-    if (fl) OJC_TRY(swiglu_rows_backward(be, (const bf16*)a.a, (const bf16*)tr->g_m, (bf16*)tr->g_a, tr->ld_au, N, F));
+    if (in_epilogue) {}
+    else if (fl) OJC_TRY(swiglu_rows_backward(be, (const bf16*)a.a, (const bf16*)tr->g_m, (bf16*)tr->g_a, tr->ld_au, N, F));
     else if ((N * F) % 4 == 0) OJC_TRY(swiglu_backward_impl(be, a.a, a.u, tr->g_m, tr->g_a, tr->g_u, A, N * F));
     else {
       ojc_tensor ta = T1(a.a, A, N * F), tu = T1(a.u, A, N * F), gm = T1(tr->g_m, A, N * F), ga = T1(tr->g_a, A, N * F), gu = T1(tr->g_u, A, N * F);

@@ -358,3 +358,46 @@ def test_an_owner_thread_session_serves_calls_from_many_threads(golden_dir):
     assert sorted(results) == sorted(want[3:]) and set(order) == {owner}
     session.run(lambda be: t.close())
     session.close()
+
+
+@pytest.mark.parametrize("shape", [dict(b=2, t=48, d=64, heads=2, hidden=192, vocab=320, saved=1),     # one-SM tiles, ragged rows (96) and columns (192): backward only
+                                   dict(b=3, t=128, d=128, heads=2, hidden=384, vocab=512, saved=2),   # two-SM tiles, clipped second row and column tiles
+                                   dict(b=4, t=256, d=256, heads=4, hidden=768, vocab=512, saved=2)])  # several tiles per CTA pair along both axes
+def test_swiglu_in_the_product_epilogues_gives_the_same_bits_as_its_own_kernels(be, shape):
+    """Under bf16 autocast the gate/up product stores m = silu(a) u beside a and u (two-SM tiles), and the down projection's
+    input-gradient product stores SwiGLU's backward of its result instead of the result. Against the form with kernels of their own
+    after the products (ojc_mlp_epilogue_variant 1): every gradient equal bit for bit, and the loss too."""
+    import ctypes as C
+    from ojas_b200 import ModelSpec, TrainConfig, Trainer
+    from ojas_b200._lib import lib
+    kw = dict(vocab=shape["vocab"], n_embd=shape["d"], n_layer=2, n_head=shape["heads"], n_kv_head=shape["heads"], head_dim=shape["d"] // shape["heads"],
+              hidden=shape["hidden"], max_seq=shape["t"])
+    ospec = orc.Spec(**kw)
+    params = orc.init_params(ospec, 5, normal_everywhere=True)
+    rng = orc.SplitMix64(9)
+    draws = np.array([rng.below(kw["vocab"]) for _ in range(shape["b"] * (shape["t"] + 1))], np.uint32).reshape(shape["b"], shape["t"] + 1)
+    x, y = draws[:, :-1].copy(), draws[:, 1:].copy()
+    out, trains = [], []
+    try:
+        for variant in (0, 1):
+            assert lib.ojc_mlp_epilogue_variant(C.c_int32(variant)) == 0
+            tr = Trainer(be, ModelSpec(**kw), TrainConfig(autocast_bf16=True, optimizer="adamw", adam_lr=1e-3, grad_clip=0.0), shape["b"], shape["t"])
+            tr.set_params(params)
+            trains = [i for i, p in enumerate(tr.params) if p.trains]
+            launches = be.kernel_launches()
+            loss = tr.gradients(x, y)
+            out.append((loss, [tr.get_grad(i) for i, p in enumerate(tr.params) if p.trains], be.kernel_launches() - launches))
+            tr.close()
+    finally:
+        lib.ojc_mlp_epilogue_variant(C.c_int32(0))
+    (l0, g0, n0), (l1, g1, n1) = out
+    assert n1 == n0 + shape["saved"] * kw["n_layer"]      # one launch per block less for each folded pass
+    assert l0 == l1
+    for a, b_ in zip(g0, g1):
+        assert np.array_equal(a.view(np.uint32), b_.view(np.uint32))
+    # and the gradients are the model's: the oracle's, at the bf16 gates
+    _, ograds, _ = orc.forward_loss(ospec, params, x, y)
+    for g, i in zip(g0, trains):
+        if np.asarray(ograds[i]).ndim >= 2:
+            denom = np.linalg.norm(ograds[i])
+            assert np.linalg.norm(g - np.asarray(ograds[i]).reshape(g.shape)) <= 5e-2 * denom, i
