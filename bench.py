@@ -362,7 +362,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                             "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops_sustained"],
                             "peak_source": f"bf16_tflops_sustained, of {pk_kind}", "launches": int(gemm_launches), "share_of_step_time": gemm_ms / roof_ms,
                             "pass": f"second pass of the same {args.steps} steps on one stream ({roof_ms / args.steps:.2f} ms per step)",
-                            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH if args.config == "124m" else None, "traffic_launch": GEMM_TRAFFIC_LAUNCH}
+                            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH if args.config == "124m" else None,
+                            "traffic_launch": GEMM_TRAFFIC_LAUNCH if args.config == "124m" else None}
     if rank == 0 and world == 1 and not args.no_sdpa:
         line["sdpa_standalone"] = sdpa_standalone(be, main, pk["bf16_tflops"])
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.config == "124m":

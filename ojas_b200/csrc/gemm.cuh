@@ -33,7 +33,9 @@ struct NsCombine { const void* src; int64_t src_ld, src_bs; float src_mul, acc_m
 // gradient of m = bf16(silu(a)) * u, and what is stored is SwiGLU's backward of it, g_a in columns [0, n) and g_u in columns [n, 2n) of C's
 // rows, with g rounded to bf16 first (the rounding a stored g would have had; ojas-core/src/autocast.rs emits bf16 from every linear).
 // `au` holds a in columns [0, n) and u in columns [n, 2n) of bf16 rows `ld` wide. Single product, n % 64 == 0, alpha 1, no accumulation.
+// Two-SM tiles only: gemm_tc_swiglu_backward_eligible says whether a shape qualifies (256 rows and 256 columns or more).
 struct SwigluGrad { const void* au; int64_t ld; };
+bool gemm_tc_swiglu_backward_eligible(ojc_backend* be, int64_t m, int64_t n);
 // And its forward counterpart on the gate/up product, whose B operand is the [gate; up] weight (n = 2 F output columns, C = (a | u)):
 // besides a and u the kernel stores m = bf16(silu(a)) * u into `m` (bf16 rows `ldm` wide), computed from the rounded a and u.
 // Two-SM tiles only: gemm_tc_swiglu_forward_eligible says whether a shape qualifies (m >= 256 rows, F a multiple of 128).

@@ -56,7 +56,6 @@ struct TcArgs {
   int batch;                // independent matrices: a unit is (matrix, tile, split); batch > 1 needs tma_store and splits == 1
   int tma_store;            // finished blocks leave through TMA tile stores (no residual operand; split partials need m % 32 == 0)
   const bf16* ns_src; int64_t ns_ld, ns_bs; float ns_src_mul, ns_acc_mul;   // Newton-Schulz combine epilogue (NsCombine); ns_src null: none
-  const bf16* sw_au; int64_t sw_ld;   // SwiGLU-backward epilogue (SwigluGrad): a at column 0, u at column n of rows sw_ld wide; null: none
   int sw_f;                 // SwiGLU-forward epilogue (SwigluForward): the hidden width F; C is (a | u), n = 2 F
   int tiles_n_fast;         // tile order: 1 = neighbouring CTAs share an A row block (few column tiles), 0 = they share a B column block
 };
@@ -76,9 +75,6 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 
 // Drains one warp's share of a finished accumulator tile: TMEM lanes [32 quarter, +32) x columns [col_begin, col_end)
 // starting at `tsrc`, destined for rows row_base.. and columns col_tile0.. of matrix bz of C (or of the split's partial).
-// EPI selects the epilogue compiled in (kernels of their own, so the plain products keep their registers):
-// 0 plain, 1 SwiGLU backward (SwigluGrad), 2 SwiGLU forward (SwigluForward; two-SM kernel only, drained by drain_swiglu_forward).
-template <int EPI>
 __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int col_tile0, int split, int bz, int lane,
                                            int col_begin, int col_end, uint8_t* stage_bytes, uint32_t stage_addr) {
   float* stage = reinterpret_cast<float*>(stage_bytes);
@@ -90,55 +86,6 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
     const int y = (args.splits > 1 ? split * args.m : 0) + row_base;
 #pragma unroll 1
     for (int c0 = col_begin; c0 < col_end; c0 += step) {
-      if constexpr (EPI == 1) {
-        // The accumulator is g, the gradient of m = bf16(silu(a)) * u, rounded to bf16 as a stored g would be. Two boxes leave
-        // instead of one: g_a for columns x.. and g_u for columns n + x.. of the output rows; the second waits in registers
-        // until the first has been read out of the staging rows. This lane's 64 gate and 64 up activations are in flight
-        // while the accumulator arrives, and the 64 columns are taken in two halves to stay inside the register file.
-        const int x = col_tile0 + c0;
-        const bool live = row_base + lane < args.m && x < args.n;   // a clipped box still computes, from row 0's values
-        const uint4* arow = reinterpret_cast<const uint4*>(args.sw_au + (live ? (int64_t)(row_base + lane) * args.sw_ld + x : 0));
-        const uint4* urow = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(arow) + args.n);
-        uint4 qa[8], qu[8], second[8];
-#pragma unroll
-        for (int ci = 0; ci < 8; ++ci) { qa[ci] = __ldg(arow + ci); qu[ci] = __ldg(urow + ci); }
-        if (lane == 0) bulk_wait_read();       // the previous box has left the staging rows
-        __syncwarp();
-        uint8_t* rowp = stage_bytes + lane * 128;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(tsrc + c0 + half * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int cj = 0; cj < 4; ++cj) {
-            const int ci = half * 4 + cj;
-            const uint32_t* v = &r[cj * 8];
-            const uint32_t wa[4] = {qa[ci].x, qa[ci].y, qa[ci].z, qa[ci].w}, wu[4] = {qu[ci].x, qu[ci].y, qu[ci].z, qu[ci].w};
-            float ga[8], gu[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float av = (e & 1) ? __uint_as_float(wa[e >> 1] & 0xffff0000u) : __uint_as_float(wa[e >> 1] << 16);
-              const float uv = (e & 1) ? __uint_as_float(wu[e >> 1] & 0xffff0000u) : __uint_as_float(wu[e >> 1] << 16);
-              swiglu::backward_elem(av, uv, swiglu::round_bf16(__uint_as_float(v[e])), ga[e], gu[e]);
-            }
-            *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
-                make_uint4(pack2_bf16(ga[0], ga[1]), pack2_bf16(ga[2], ga[3]), pack2_bf16(ga[4], ga[5]), pack2_bf16(ga[6], ga[7]));
-            second[ci] = make_uint4(pack2_bf16(gu[0], gu[1]), pack2_bf16(gu[2], gu[3]), pack2_bf16(gu[4], gu[5]), pack2_bf16(gu[6], gu[7]));
-          }
-        }
-        fence_async_smem();
-        __syncwarp();
-        const bool issue = lane == 0 && x < args.n && row_base < args.m;
-        if (issue) { tma_store_3d(&tmap_c, stage_addr, x, y, bz); bulk_commit(); bulk_wait_read(); }
-        __syncwarp();
-#pragma unroll
-        for (int ci = 0; ci < 8; ++ci) *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = second[ci];
-        fence_async_smem();
-        __syncwarp();
-        if (issue) { tma_store_3d(&tmap_c, stage_addr, args.n + x, y, bz); bulk_commit(); }
-        continue;
-      }
       uint32_t r[32], r2[32];
       tmem_ld32(tsrc + c0, r);
       if (bf) tmem_ld32(tsrc + c0 + 32, r2);
@@ -245,6 +192,51 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
   }
 }
 
+// SwiGLU backward on 64 columns of this warp's share of a finished accumulator: the accumulator is g, the gradient of
+// m = bf16(silu(a)) * u, rounded to bf16 as a stored g would be; a and u for the same 32 rows x 64 columns were brought into the warp's
+// input boxes by TMA (128-byte swizzle, like the store boxes) and are in registers (qa, qu) by the time this runs. Two boxes leave
+// instead of one: g_a for columns x.. and g_u for columns n + x.. of the output rows; the second waits in registers until the first
+// has been read out of the staging rows. The 64 columns are taken in two halves to stay inside the register file.
+__device__ __forceinline__ void drain_swiglu_backward(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int x, int c0, int bz, int lane,
+                                                      const uint4 (&qa)[8], const uint4 (&qu)[8], uint8_t* stage_bytes, uint32_t stage_addr) {
+  uint4 second[8];
+  if (lane == 0) bulk_wait_read();           // the previous box has left the staging rows
+  __syncwarp();
+  uint8_t* rowp = stage_bytes + lane * 128;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t r[32];
+    tmem_ld32(tsrc + c0 + half * 32, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int cj = 0; cj < 4; ++cj) {
+      const int ci = half * 4 + cj;
+      const uint32_t* v = &r[cj * 8];
+      const uint32_t wa[4] = {qa[ci].x, qa[ci].y, qa[ci].z, qa[ci].w}, wu[4] = {qu[ci].x, qu[ci].y, qu[ci].z, qu[ci].w};
+      float ga[8], gu[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float av = (e & 1) ? __uint_as_float(wa[e >> 1] & 0xffff0000u) : __uint_as_float(wa[e >> 1] << 16);
+        const float uv = (e & 1) ? __uint_as_float(wu[e >> 1] & 0xffff0000u) : __uint_as_float(wu[e >> 1] << 16);
+        swiglu::backward_elem(av, uv, swiglu::round_bf16(__uint_as_float(v[e])), ga[e], gu[e]);
+      }
+      *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
+          make_uint4(pack2_bf16(ga[0], ga[1]), pack2_bf16(ga[2], ga[3]), pack2_bf16(ga[4], ga[5]), pack2_bf16(ga[6], ga[7]));
+      second[ci] = make_uint4(pack2_bf16(gu[0], gu[1]), pack2_bf16(gu[2], gu[3]), pack2_bf16(gu[4], gu[5]), pack2_bf16(gu[6], gu[7]));
+    }
+  }
+  fence_async_smem();
+  __syncwarp();
+  const bool issue = lane == 0 && x < args.n && row_base < args.m;
+  if (issue) { tma_store_3d(&tmap_c, stage_addr, x, row_base, bz); bulk_commit(); bulk_wait_read(); }
+  __syncwarp();
+#pragma unroll
+  for (int ci = 0; ci < 8; ++ci) *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = second[ci];
+  fence_async_smem();
+  __syncwarp();
+  if (issue) { tma_store_3d(&tmap_c, stage_addr, args.n + x, row_base, bz); bulk_commit(); }
+}
+
 // SwiGLU forward on a finished two-SM accumulator whose 256 columns are gate columns [j0, j0 + 128) followed by up columns
 // [F + j0, F + j0 + 128) of the (a | u) row: this warp takes 64 gate columns and the 64 up columns that go with them, rounds both
 // to bf16 (what the stored a and u hold), and sends out three boxes in turn through its staging rows: a, u and
@@ -295,7 +287,6 @@ __device__ __forceinline__ void drain_swiglu_forward(const TcArgs& args, const C
   if (issue) { tma_store_3d(&tmap_m, stage_addr, j, row_base, bz); bulk_commit(); }
 }
 
-template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                const TcArgs args) {
@@ -403,7 +394,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       fence_after();
       const int row_base = tm * BM + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      drain_tile<EPI>(args, tmap_c, tsrc, row_base, tn * BN, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
+      drain_tile(args, tmap_c, tsrc, row_base, tn * BN, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -428,10 +419,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 //   full[s]   (even CTA's copy) one arrive + the bytes of both CTAs' loads
 //   empty[s]  (each CTA's copy) the MMA thread's commit reaches both copies
 //   tfull[a]  (each CTA's copy) likewise; tempty[a] (even CTA's copy) collects the 16 epilogue warps of both CTAs
-constexpr int STAGES2 = 6, BM2 = 256, BN2 = 256;
+// EPI selects the epilogue compiled in (kernels of their own, so the plain products keep their registers and their ring):
+// 0 plain; 1 SwiGLU backward (SwigluGrad): each epilogue warp has an 8 KB input box pair for a and u, filled by TMA one step
+// ahead of its use, and the operand ring is four stages deep to make room; 2 SwiGLU forward (SwigluForward).
+constexpr int BM2 = 256, BN2 = 256;
 constexpr int A2_TILE_BYTES = 128 * BK * 2, B2_TILE_BYTES = 128 * BK * 2, STAGE2_BYTES = A2_TILE_BYTES + B2_TILE_BYTES;
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + EPI_STAGE_BYTES + 256;
-static_assert(SMEM2_BYTES <= 232448, "shared memory per CTA");
+constexpr int IN_WARP_BYTES = 2 * EPI_WARP_BYTES;
+__host__ __device__ constexpr int stages2(int epi) { return epi == 1 ? 4 : 6; }
+__host__ __device__ constexpr int smem2_bytes(int epi) { return stages2(epi) * STAGE2_BYTES + 1024 + EPI_STAGE_BYTES + (epi == 1 ? EPI_WARPS * IN_WARP_BYTES : 0) + 256; }
+static_assert(smem2_bytes(0) <= 232448 && smem2_bytes(1) <= 232448 && smem2_bytes(2) <= 232448, "shared memory per CTA");
+static_assert(8 * (2 * stages2(0) + 5 + EPI_WARPS) <= 256, "barrier area");
 
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -440,12 +437,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;               // the same offset in both CTAs (same kernel, same layout)
+  constexpr int STAGES2 = stages2(EPI);
   const uint32_t epi_base = tiles_base + STAGES2 * STAGE2_BYTES;
-  const uint32_t bar_base = epi_base + EPI_STAGE_BYTES;
+  const uint32_t in_base = epi_base + EPI_STAGE_BYTES;               // EPI 1: the epilogue warps' input boxes (1024-aligned too)
+  const uint32_t bar_base = in_base + (EPI == 1 ? EPI_WARPS * IN_WARP_BYTES : 0);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + 2 + a); };
+  auto in_bar = [&](int w) { return bar_base + 8u * (2 * STAGES2 + 5 + w); };   // EPI 1: one per epilogue warp
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bar_base - raw) + 8 * (2 * STAGES2 + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* epi_ptr = smem_raw + (epi_base - raw);
@@ -460,6 +460,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * EPI_WARPS); }
+    if (EPI == 1) for (int w = 0; w < EPI_WARPS; ++w) mbar_init(in_bar(w), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -533,18 +534,61 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const int col_begin = ((warp - 2) >> 2) * (BN2 / 2), col_end = col_begin + BN2 / 2;
     uint8_t* stage_bytes = epi_ptr + (warp - 2) * EPI_WARP_BYTES;
     const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
+    auto unit_tile = [&](int u, int* tm, int* tn, int* split, int* bz) {
+      *bz = u / units_per_matrix;
+      const int ub = u - *bz * units_per_matrix, tile = ub / args.splits;
+      *split = ub % args.splits;
+      *tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m; *tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
+    };
+    // EPI 1: a and u for rows [32 quarter, +32) x 64 columns of a unit arrive in this warp's input boxes one step before they are
+    // needed: the first step's while the unit's products still run, the second step's while the first is worked on (the boxes are
+    // free again as soon as their contents are in registers). Out-of-range rows and columns read as zero and are clipped on the way out.
+    const uint32_t in_addr = in_base + (warp - 2) * IN_WARP_BYTES, my_in_bar = in_bar(warp - 2);
+    const uint8_t* in_ptr = smem_raw + (in_addr - raw);
+    uint32_t in_count = 0;
+    auto fetch_inputs = [&](int u, int c0) {
+      int tm, tn, split, bz;
+      unit_tile(u, &tm, &tn, &split, &bz);
+      const int x = tn * BN2 + c0, y = tm * BM2 + (int)rank * 128 + quarter * 32;
+      mbar_expect_tx(my_in_bar, IN_WARP_BYTES);
+      tma_load_3d(in_addr, &tmap_m, my_in_bar, x, y, bz);
+      tma_load_3d(in_addr + EPI_WARP_BYTES, &tmap_m, my_in_bar, args.n + x, y, bz);
+    };
+    if (EPI == 1 && lane == 0 && pair < units) fetch_inputs(pair, col_begin);
     uint32_t local = 0;
     for (int u = pair; u < units; u += npairs, ++local) {
-      const int bz = u / units_per_matrix, ub = u - bz * units_per_matrix;
-      const int split = ub % args.splits, tile = ub / args.splits;
-      const int tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m, tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
+      int tm, tn, split, bz;
+      unit_tile(u, &tm, &tn, &split, &bz);
       const int acc = local & 1;
       if (!mbar_wait(tfull_bar(acc), (local >> 1) & 1, args.fault, abort_flag)) break;
       fence_after();
       const int row_base = tm * BM2 + (int)rank * 128 + quarter * 32;
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
       if constexpr (EPI == 2) drain_swiglu_forward(args, tmap_c, tmap_m, tsrc, row_base, tn * 128, bz, lane, (warp - 2) >> 2, stage_bytes, stage_addr);
-      else drain_tile<EPI>(args, tmap_c, tsrc, row_base, tn * BN2, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
+      else if constexpr (EPI == 1) {
+        bool ok = true;
+#pragma unroll 1
+        for (int c0 = col_begin; c0 < col_end; c0 += 64) {
+          if (!mbar_wait(my_in_bar, in_count & 1, args.fault, abort_flag)) { ok = false; break; }
+          ++in_count;
+          uint4 qa[8], qu[8];
+          const uint8_t* rin = in_ptr + lane * 128;
+#pragma unroll
+          for (int ci = 0; ci < 8; ++ci) {
+            qa[ci] = *reinterpret_cast<const uint4*>(rin + ((ci ^ (lane & 7)) << 4));
+            qu[ci] = *reinterpret_cast<const uint4*>(rin + EPI_WARP_BYTES + ((ci ^ (lane & 7)) << 4));
+          }
+          fence_async_smem();                    // the reads above come before the next fill of the boxes
+          __syncwarp();
+          if (lane == 0) {
+            if (c0 + 64 < col_end) fetch_inputs(u, c0 + 64);
+            else if (u + npairs < units) fetch_inputs(u + npairs, col_begin);
+          }
+          drain_swiglu_backward(args, tmap_c, tsrc, row_base, tn * BN2 + c0, c0, bz, lane, qa, qu, stage_bytes, stage_addr);
+        }
+        if (!ok) break;
+      }
+      else drain_tile(args, tmap_c, tsrc, row_base, tn * BN2, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
@@ -624,13 +668,13 @@ ojc_status two_sm_pairs(ojc_backend* be, const char* op, int* pairs) {
   static PerDeviceInt max_pairs_of(-1);
   int& max_pairs = max_pairs_of[be->device];
   if (max_pairs < 0) {
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(0)), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(1)), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(2)), op);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.gridDim = dim3((unsigned)(be->sm_count & ~1)); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.gridDim = dim3((unsigned)(be->sm_count & ~1)); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = smem2_bytes(1); cfg.attrs = attr; cfg.numAttrs = 1;
     int n_clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tc2_kernel<1>, &cfg) != cudaSuccess) { cudaGetLastError(); n_clusters = 0; }
     max_pairs = n_clusters;
@@ -640,6 +684,11 @@ ojc_status two_sm_pairs(ojc_backend* be, const char* op, int* pairs) {
 }
 }  // namespace
 
+bool gemm_tc_swiglu_backward_eligible(ojc_backend* be, int64_t m, int64_t n) {
+  int pairs = 0;
+  if (two_sm_pairs(be, "linear_backward", &pairs) != OJC_OK || pairs <= 0) return false;
+  return m >= BM2 && n >= BN2 && n % 64 == 0;
+}
 bool gemm_tc_swiglu_forward_eligible(ojc_backend* be, int64_t m, int64_t n, int64_t ldm, const void* mptr) {
   int pairs = 0;
   if (two_sm_pairs(be, "linear_forward", &pairs) != OJC_OK || pairs <= 0) return false;
@@ -673,6 +722,8 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   if (swiglu_fwd && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine || swiglu_grad || batch != 1))
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the SwiGLU forward epilogue needs a single bf16 product, alpha 1, no accumulation");
   if (swiglu_fwd) allow_split = false;
+  if (swiglu_grad && !gemm_tc_swiglu_backward_eligible(be, m, n))
+    return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the SwiGLU backward epilogue needs two-SM tiles (256 rows and 256 columns or more) and a width that is a multiple of 64");
   if (swiglu_grad && (c_dtype != OJC_BF16 || alpha != 1.0f || accumulate || residual || combine || batch != 1 || n % 64 != 0 || swiglu_grad->ld % 8 != 0 ||
                       swiglu_grad->ld < 2 * n || ldc < 2 * n || ((uintptr_t)swiglu_grad->au & 15) != 0))
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "the SwiGLU epilogue needs bf16 (a | u) rows and output rows at least 2 n wide, n a multiple of 64, alpha 1, no accumulation");
@@ -700,8 +751,7 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   static PerDeviceFlag attr_set_of;
   bool& attr_set = attr_set_of[be->device];
   if (!attr_set) {
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
-    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES), op);
     attr_set = true;
   }
   const int tiles = (int)(((m + tile_m - 1) / tile_m) * ((n + tile_n - 1) / tile_n) * batch);   // units before any split
@@ -731,7 +781,6 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   args.ns_src = combine ? (const bf16*)combine->src : nullptr; args.ns_ld = combine ? combine->src_ld : 0; args.ns_bs = combine ? combine->src_bs : 0;
   args.ns_src_mul = combine ? combine->src_mul : 0.0f; args.ns_acc_mul = combine ? combine->acc_mul : 0.0f;
   args.sw_f = swiglu_fwd ? (int)(n / 2) : 0;
-  args.sw_au = swiglu_grad ? (const bf16*)swiglu_grad->au : nullptr; args.sw_ld = swiglu_grad ? swiglu_grad->ld : 0;
   if (splits > 1) {
     void* ws = nullptr;
     OJC_TRY(ojc_scratch(be, (uint64_t)splits * m * n * 4, &ws));
@@ -749,6 +798,7 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "a batched product needs the tile-store epilogue");
   }
   CUtensorMap tm = tc;   // the SwiGLU forward epilogue's third output
+  if (swiglu_grad) OJC_TRY(make_tmap(be, op, &tm, swiglu_grad->au, (uint64_t)(2 * n), (uint64_t)m, (uint64_t)swiglu_grad->ld, 64, 32));   // a and u, fetched box by box
   if (swiglu_fwd) OJC_TRY(make_tmap(be, op, &tm, swiglu_fwd->m, (uint64_t)(n / 2), (uint64_t)m, (uint64_t)swiglu_fwd->ldm, 64, 32));
   int grid = tiles * splits < workers ? tiles * splits : workers;
   if (two_sm) grid *= 2;
@@ -758,11 +808,10 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }
     OJC_CUDA(be, cudaEventRecord(sample.start, be->stream), op);
   }
-  if (swiglu_fwd) gemm_tc2_kernel<2><<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, tm, args);
-  else if (two_sm && swiglu_grad) gemm_tc2_kernel<1><<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, tm, args);
-  else if (two_sm) gemm_tc2_kernel<0><<<grid, NUM_THREADS, SMEM2_BYTES, be->stream>>>(ta, tb, tc, tm, args);
-  else if (swiglu_grad) gemm_tc_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
-  else gemm_tc_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
+  if (swiglu_fwd) gemm_tc2_kernel<2><<<grid, NUM_THREADS, smem2_bytes(2), be->stream>>>(ta, tb, tc, tm, args);
+  else if (swiglu_grad) gemm_tc2_kernel<1><<<grid, NUM_THREADS, smem2_bytes(1), be->stream>>>(ta, tb, tc, tm, args);
+  else if (two_sm) gemm_tc2_kernel<0><<<grid, NUM_THREADS, smem2_bytes(0), be->stream>>>(ta, tb, tc, tm, args);
+  else gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
   OJC_LAUNCHED(be, op);
   if (be->profile_gemm) {
     OJC_CUDA(be, cudaEventRecord(sample.stop, be->stream), op);

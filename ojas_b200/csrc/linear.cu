@@ -37,9 +37,10 @@ ojc_status linear_backward_input_swiglu_impl(ojc_backend* be, const void* w, con
   const SwigluGrad sw{au, ld};
   return gemm_tc_batched(be, "linear_backward", a, b, gau, OJC_BF16, ld, rows, kin, nout, 1, 0, 0, 0, 1.0f, false, nullptr, nullptr, false, &sw);
 }
-bool linear_backward_input_swiglu_eligible(const void* w, const void* gy, const void* au, const void* gau, int64_t ld, int64_t rows, int64_t kin, int64_t nout) {
+bool linear_backward_input_swiglu_eligible(ojc_backend* be, const void* w, const void* gy, const void* au, const void* gau, int64_t ld, int64_t rows, int64_t kin, int64_t nout) {
   GemmOperand a{gy, OJC_BF16, nout, 1}, b{w, OJC_BF16, kin, 1};
-  return kin % 64 == 0 && ld % 8 == 0 && ld >= 2 * kin && (reinterpret_cast<uintptr_t>(au) & 15) == 0 && gemm_tc_eligible(a, b, gau, OJC_BF16, ld, rows, kin, nout);
+  return kin % 64 == 0 && ld % 8 == 0 && ld >= 2 * kin && (reinterpret_cast<uintptr_t>(au) & 15) == 0 && gemm_tc_eligible(a, b, gau, OJC_BF16, ld, rows, kin, nout) &&
+         gemm_tc_swiglu_backward_eligible(be, rows, kin);
 }
 ojc_status linear_backward_weight_impl(ojc_backend* be, const void* x, int32_t x_dt, const void* gy, int32_t g_dt, float* gw, int64_t rows, int64_t kin,
                                        int64_t nout, bool accumulate) {

@@ -12,7 +12,8 @@ ojc_status linear_backward_weight_impl(ojc_backend* be, const void* x, int32_t x
 // The MLP down projection's input gradient with SwiGLU's backward folded into the product's epilogue (bf16 tier): with
 // g = gy[rows, out] W[out, in] rounded to bf16, gau[rows, 0:in] = g_a and gau[rows, in:2 in] = g_u from au[rows, 0:in] = a and
 // au[rows, in:2 in] = u (both buffers in rows `ld` wide). The same bits as linear_backward_input_impl followed by swiglu_rows_backward.
-bool linear_backward_input_swiglu_eligible(const void* w, const void* gy, const void* au, const void* gau, int64_t ld, int64_t rows, int64_t kin, int64_t nout);
+// Two-SM tiles only: ask linear_backward_input_swiglu_eligible first.
+bool linear_backward_input_swiglu_eligible(ojc_backend* be, const void* w, const void* gy, const void* au, const void* gau, int64_t ld, int64_t rows, int64_t kin, int64_t nout);
 ojc_status linear_backward_input_swiglu_impl(ojc_backend* be, const void* w, const void* gy, const void* au, void* gau, int64_t ld, int64_t rows, int64_t kin,
                                              int64_t nout);
 // The MLP's gate/up product with SwiGLU's forward folded into its epilogue (bf16 tier): au[rows, 0:hidden] = a = x Wg^T,

@@ -388,7 +388,7 @@ ojc_status backward(ojc_trainer* tr, const uint32_t* ids_dev, const uint32_t* ta
     const bool fl = tr->fused_lin;
     // With gate and up side by side the SwiGLU gradient leaves the product's epilogue directly and g_m is never stored.
     const bool in_epilogue = fl && g_mlp_epilogue_variant == 0 &&
-                             linear_backward_input_swiglu_eligible(tr->WM(tr->P(l, P_FD)), gxo, a.a, tr->g_a, tr->ld_au, N, F, d);
+                             linear_backward_input_swiglu_eligible(be, tr->WM(tr->P(l, P_FD)), gxo, a.a, tr->g_a, tr->ld_au, N, F, d);
     if (in_epilogue) OJC_TRY(linear_backward_input_swiglu_impl(be, tr->WM(tr->P(l, P_FD)), gxo, a.a, tr->g_a, tr->ld_au, N, F, d));
     else OJC_TRY(linear_backward_input_impl(be, tr->WM(tr->P(l, P_FD)), A, gxo, A, tr->g_m, A, N, F, d, false));
     OJC_TRY(on_side([&] { return linear_backward_weight_impl(be, a.m, A, gxo, A, tr->G(tr->P(l, P_FD)), N, F, d, false); }));
