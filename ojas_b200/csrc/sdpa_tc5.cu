@@ -1676,6 +1676,8 @@ sdpa_bwd_dkv_p_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
 }
 
+#include "sdpa_bwd_wide.cuh"
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -1778,6 +1780,8 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_p_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dkv<D>::SMEM_BYTES), op);
     OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_p_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Dq<D>::SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dkv_w_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvW<D>::SMEM_BYTES), op);
+    OJC_CUDA(be, cudaFuncSetAttribute(sdpa_bwd_dq_w_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqW<D>::SMEM_BYTES), op);
     attr = true;
   }
   if (dr_work) {   // the caller has no Dr of its own
@@ -1793,6 +1797,20 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
   dim3 grid_k((unsigned)(((d.time + BN - 1) / BN) * a.planes));
   // persistent CTAs at head_dim 64 once there are more tiles than CTA slots (B 32 x H 12 x T 1024: 411 us against 423 us for both kernels;
   // at head_dim 128, one CTA per SM, they measured slower: [8,16,4096,128] 3264 us against 3127 us)
+  // the library's choice: persistent CTAs walking in 128-wide steps, P and dS in tensor memory (one CTA per SM)
+  const bool wide = (g_sdpa_forward_variant == 0 && D == 128) || g_sdpa_forward_variant == 3;   // head_dim 64 at its short walks: the 64-wide kernels, two CTAs per SM
+  const unsigned wide_cap = g_sdpa_forward_variant == 3 ? 3u : (unsigned)be->sm_count;
+  if (wide) {
+    sdpa_bwd_dkv_w_kernel<D><<<std::min<unsigned>(grid_k.x, wide_cap), BWD_THREADS, DkvW<D>::SMEM_BYTES, be->stream>>>(m[0], m[1], m[2], m[3], a);
+    OJC_LAUNCHED(be, op);
+    a.g0 = SdpaView<bf16>{(bf16*)gq->data, gq->stride[0], gq->stride[1], gq->stride[2]};
+    a.planes = d.batch * d.heads;
+    a.group = planes_per_group(d.time, d.dim, a.planes);
+    const unsigned tiles_q = (unsigned)(((d.time + BM - 1) / BM) * a.planes);
+    sdpa_bwd_dq_w_kernel<D><<<std::min<unsigned>(tiles_q, wide_cap), BWD_THREADS, DqW<D>::SMEM_BYTES, be->stream>>>(m[0], m[1], m[2], m[3], a);
+    OJC_LAUNCHED(be, op);
+    return OJC_OK;
+  }
   const bool persist_k = g_sdpa_forward_variant == 2 || (D == 64 && g_sdpa_forward_variant != 1 && (int)grid_k.x > be->sm_count * Dkv<D>::CTAS);
   if (persist_k) sdpa_bwd_dkv_p_kernel<D><<<g_sdpa_forward_variant == 2 ? std::min<unsigned>(grid_k.x, 3u) : (unsigned)(be->sm_count * Dkv<D>::CTAS), BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);
   else sdpa_bwd_dkv_tcgen05_kernel<D><<<grid_k, BWD_THREADS, Dkv<D>::SMEM_BYTES, be->stream>>>(m[4], m[1], m[2], m[7], a);   // q, dO in 64-row steps
@@ -1836,4 +1854,5 @@ bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_t
 // CTAs at head_dim 64; backward: persistent CTAs; the persistent kernels once there are more tiles than CTA slots), 1 = always one CTA per
 // tile (to time the others against it), 2 = the persistent kernels on a grid of at most three CTAs, whatever the size (so that small
 // test shapes walk several tiles per CTA).
-extern "C" ojc_status ojc_sdpa_forward_variant(int32_t variant) { g_sdpa_forward_variant = variant >= 0 && variant <= 2 ? variant : 0; return OJC_OK; }
+extern "C" ojc_status ojc_sdpa_forward_variant(int32_t variant) { g_sdpa_forward_variant = variant >= 0 && variant <= 3 ? variant : 0; return OJC_OK; }
+

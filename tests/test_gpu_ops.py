@@ -175,12 +175,20 @@ def test_persistent_attention_kernels_walk_several_tiles_per_cta(be, shape, hkv)
         got = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]
         lib.ojc_sdpa_forward_variant(C.c_int32(1))
         one = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]       # same output and lse in: the same arithmetic in the same order
+        lib.ojc_sdpa_forward_variant(C.c_int32(3))
+        wide = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]      # the 128-wide kernels (the library's choice) on three CTAs
+        lib.ojc_sdpa_forward_variant(C.c_int32(0))
+        full = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]      # and on a grid of their own choosing
     finally:
         lib.ojc_sdpa_forward_variant(C.c_int32(0))
     assert rel(y.numpy(), oy) <= 2e-2 and rel(lse.numpy(), olse) <= 1e-4
     assert max(rel(g, w) for g, w in zip(got, want)) <= 2e-2
     for a, c in zip(got, one):
         assert np.array_equal(a, c)
+    # every product accumulates over the same operands in the same order of 16-wide steps: the wide kernels give the same bits too
+    for a, c, e in zip(wide, one, full):
+        assert max(rel(a, w) for a, w in zip(wide, want)) <= 2e-2
+        assert np.array_equal(a, c) and np.array_equal(e, c)
 
 
 def test_sdpa_reads_permuted_views_without_a_copy(be):
