@@ -14,8 +14,8 @@
 //   warps 0-7  compute: thread t of a warpgroup owns TMEM lane t (a query row for dQ, a key row for dK/dV); warpgroup `half` takes
 //              64 of the step's 128 columns. Phase 1 turns S into P (the exponentials, the bulk of the work) while the pipe is still
 //              producing dP; phase 2 forms dS = P (dP - Dr).
-// A tile's accumulators are read, handed back (ACCFREE) and stored by the compute threads between the two phases of the next tile's
-// first step, so the wait for the tile's last accumulating product hides behind that step's exponentials.
+// A tile's accumulators are read, handed back (ACCFREE) and stored by the compute threads right after they have handed over the next
+// tile's first step, so the tile's last accumulating product has finished by then and the walk does not stall at a tile boundary.
 // Every mbarrier wait is bounded; on expiry the CTA raises the fault word, drains and frees its TMEM.
 
 constexpr int WB = 128;
@@ -257,17 +257,17 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       return true;
     };
     // the row's statistics are fetched one tile ahead, so their latency sits under the previous tile's walk
-    auto stat_of = [&](const DqWalkW& t, bool valid, float& l2, float& dr) {
+    // (the loaded values are not touched until the tile switch: a thread stalls at the first use of a load, not at the load)
+    auto stat_of = [&](const DqWalkW& t, bool valid, float& lse, float& dr) {
       const int r = t.q0 + tid;
-      const bool in = valid && r < args.time;
       const int64_t idx = ((int64_t)t.b * args.heads + t.h) * args.time + r;
-      l2 = in ? args.lse[idx] * LOG2E : INFINITY;
-      dr = in ? args.dr[idx] : 0.0f;
+      lse = INFINITY; dr = 0.0f;
+      if (valid && r < args.time) { lse = args.lse[idx]; dr = args.dr[idx]; }
     };
     DqWalkW wn;
     bool have = w.set(args, tiles, total, 0);
     float lse_row = INFINITY, dr_row = 0.0f, lse_next, dr_next;
-    if (have) stat_of(w, true, lse_row, dr_row);
+    if (have) { stat_of(w, true, lse_row, dr_row); lse_row *= LOG2E; }
     for (int item = 0; ok && have; ++item) {
       const bool more = wn.set(args, tiles, total, item + 1);
       stat_of(wn, more, lse_next, dr_next);
@@ -282,7 +282,6 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int lo = 0, hi = min(row - key0 + 1, args.time - key0);
         float p[64];
         if (masked) wide_phase1<true, true>(s_addr, sl2, lse_row, nullptr, lo, hi, p); else wide_phase1<false, true>(s_addr, sl2, lse_row, nullptr, lo, hi, p);
-        if (fin && !finalize()) { ok = false; break; }
         if (!mbar_wait(bar(WQ_DPFULL), n & 1, args.fault, abort_flag)) { ok = false; break; }
         fence_after();
         // phase 2: dS over this half's first 32 S columns (all of them read above)
@@ -293,10 +292,13 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tmem_wait_st();
         fence_before();
         mbar_arrive(bar(WQ_CDONE));
+        // the previous tile's dQ, after this tile's first step has been handed over: its last product has long finished, and the MMA
+        // thread needs the accumulator back only for this step's dQ product, which it issues after the next step's dP
+        if (fin && !finalize()) { ok = false; break; }
       }
       if (!ok) break;
       fin = true; fin_item = item; fin_b = w.b; fin_h = w.h; fin_row = row;
-      w = wn; have = more; lse_row = lse_next; dr_row = dr_next;
+      w = wn; have = more; lse_row = lse_next * LOG2E; dr_row = dr_next;
     }
     if (ok && fin) finalize();
   }
@@ -453,7 +455,8 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (ok) { ok = issue_dp(cp); cp.advance(args, tiles, total); }
       while (ok && cq.valid) {
         if (!mbar_wait(bar(WK_CDONE), cq.n & 1, args.fault, abort_flag)) break;
-        // a tile's first accumulating products overwrite dV and dK: the previous tile's rows must hold theirs in registers
+        // a tile's first accumulating products overwrite dV and dK: the previous tile's rows must hold theirs in registers (they read
+        // them right after handing this step over)
         if (cq.j == 0 && cq.item > 0 && !mbar_wait(bar(WK_ACCFREE), (cq.item - 1) & 1, args.fault, abort_flag)) break;
         fence_after();
         const bool last = cq.last();
@@ -519,7 +522,6 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int e = 0; e < 32; ++e) pw[e] = pack2_bf16(p[2 * e], p[2 * e + 1]);
         tmem_st_packed(s_addr, pw);
-        if (fin && !finalize()) { ok = false; break; }
         if (!mbar_wait(bar(WK_DPFULL), n & 1, args.fault, abort_flag)) { ok = false; break; }
         fence_after();
         // phase 2: dS^T over this half's first 32 dP^T columns
@@ -529,6 +531,7 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tmem_wait_st();
         fence_before();
         mbar_arrive(bar(WK_CDONE));
+        if (fin && !finalize()) { ok = false; break; }   // the previous tile's dV and dK, once this tile's first step has been handed over
       }
       if (!ok) break;
       fin = true; fin_item = item; fin_b = w.b; fin_hk = w.hk; fin_key = key;

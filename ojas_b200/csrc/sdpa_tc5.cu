@@ -1798,7 +1798,11 @@ static ojc_status launch_bwd(ojc_backend* be, const char* op, const ojc_tensor* 
   // persistent CTAs at head_dim 64 once there are more tiles than CTA slots (B 32 x H 12 x T 1024: 411 us against 423 us for both kernels;
   // at head_dim 128, one CTA per SM, they measured slower: [8,16,4096,128] 3264 us against 3127 us)
   // the library's choice: persistent CTAs walking in 128-wide steps, P and dS in tensor memory (one CTA per SM)
-  const bool wide = (g_sdpa_forward_variant == 0 && D == 128) || g_sdpa_forward_variant == 3;   // head_dim 64 at its short walks: the 64-wide kernels, two CTAs per SM
+  // At head_dim 128 they measured 1.4 to 1.55 times faster than the 64-wide kernels from T 512 to T 8192 ([8,16,4096,128]: 2039 us
+  // against 3128 us). At head_dim 64 the 64-wide kernels, two CTAs per SM, stay about 5% ahead at every length tried (T 512 to 4096):
+  // there the accumulating products are N = 64 either way, and the second CTA hides tile switches that one CTA's pipeline shows.
+  const int v = g_sdpa_forward_variant;
+  const bool wide = v == 3 || v == 5 || (v == 0 && D == 128);
   const unsigned wide_cap = g_sdpa_forward_variant == 3 ? 3u : (unsigned)be->sm_count;
   if (wide) {
     sdpa_bwd_dkv_w_kernel<D><<<std::min<unsigned>(grid_k.x, wide_cap), BWD_THREADS, DkvW<D>::SMEM_BYTES, be->stream>>>(m[0], m[1], m[2], m[3], a);
@@ -1851,8 +1855,9 @@ bool sdpa_tcgen05_bwd_eligible(ojc_backend* be, const ojc_tensor* q, const ojc_t
 }
 
 // Instrumentation (no counterpart in the reference): 0 = the library's choice (forward: two query tiles per CTA at head_dim 128, persistent
-// CTAs at head_dim 64; backward: persistent CTAs; the persistent kernels once there are more tiles than CTA slots), 1 = always one CTA per
-// tile (to time the others against it), 2 = the persistent kernels on a grid of at most three CTAs, whatever the size (so that small
-// test shapes walk several tiles per CTA).
-extern "C" ojc_status ojc_sdpa_forward_variant(int32_t variant) { g_sdpa_forward_variant = variant >= 0 && variant <= 3 ? variant : 0; return OJC_OK; }
+// CTAs at head_dim 64; backward: the 128-wide persistent kernels at head_dim 128, the 64-wide persistent ones at head_dim 64 once there
+// are more tiles than CTA slots), 1 = always one CTA per tile (to time the others against it), 2 = the 64-wide persistent kernels on a
+// grid of at most three CTAs, whatever the size (so that small test shapes walk several tiles per CTA), 3 = the 128-wide backward kernels
+// on at most three CTAs (likewise), 4 = the 64-wide backward kernels by their own rule, 5 = the 128-wide backward kernels at any head_dim.
+extern "C" ojc_status ojc_sdpa_forward_variant(int32_t variant) { g_sdpa_forward_variant = variant >= 0 && variant <= 5 ? variant : 0; return OJC_OK; }
 

@@ -46,7 +46,7 @@ def sdpa(args) -> None:
     from .backend import _check, _p
     B, H, T, D = args.batch, args.heads, args.time, args.dim
     be = CudaBackend(0, 16 << 30)
-    _check(lib.ojc_sdpa_forward_variant(C.c_int32(int(args.one_tile))))   # 1: one CTA per tile, forward and backward
+    _check(lib.ojc_sdpa_forward_variant(C.c_int32(args.variant if args.variant else int(args.one_tile))))   # 1: one CTA per tile, forward and backward
 
     def draw(seed):  # [B,T,H,D] storage viewed as [B,H,T,D], the layout the step driver uses
         return be.upload(np.random.default_rng(seed).standard_normal((B, T, H, D), dtype=np.float32), DType.BF16).permuted((0, 2, 1, 3))
@@ -76,6 +76,7 @@ def main() -> None:
     s.add_argument("batch", type=int); s.add_argument("heads", type=int); s.add_argument("time", type=int); s.add_argument("dim", type=int)
     s.add_argument("--reps", type=int, default=10)
     s.add_argument("--one-tile", action="store_true", help="time the one-CTA-per-tile kernels (forward and backward) instead of the library's choice")
+    s.add_argument("--variant", type=int, default=0, help="kernel selection as ojc_sdpa_forward_variant takes it (4: the 64-wide backward kernels by their own rule, 5: the 128-wide ones always)")
     s.set_defaults(fn=sdpa)
     args = ap.parse_args()
     args.fn(args)

@@ -176,8 +176,8 @@ def test_persistent_attention_kernels_walk_several_tiles_per_cta(be, shape, hkv)
         lib.ojc_sdpa_forward_variant(C.c_int32(1))
         one = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]       # same output and lse in: the same arithmetic in the same order
         lib.ojc_sdpa_forward_variant(C.c_int32(3))
-        wide = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]      # the 128-wide kernels (the library's choice) on three CTAs
-        lib.ojc_sdpa_forward_variant(C.c_int32(0))
+        wide = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]      # the 128-wide kernels (the library's choice at head_dim 128) on three CTAs
+        lib.ojc_sdpa_forward_variant(C.c_int32(5))
         full = [g.numpy() for g in be.causal_sdpa_backward(dq, dk, dv, y, lse, dgy)]      # and on a grid of their own choosing
     finally:
         lib.ojc_sdpa_forward_variant(C.c_int32(0))
