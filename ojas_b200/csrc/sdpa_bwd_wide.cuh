@@ -7,7 +7,10 @@
 // and the accumulating products take that as their A operand.
 //
 // One persistent CTA per SM, ten warps:
-//   warp 8     TMA producer: the tile the CTA keeps (Q and dO, or K and V; two buffers at head_dim 64), and rings of the tiles it walks
+//   warp 8     TMA producer: the tile the CTA keeps (Q and dO, or K and V; two buffers at head_dim 64), and rings of the tiles it walks.
+//              It also works out where each tile of the CTA's list sits (plane, head, position, number of steps: half a dozen integer
+//              divisions) and publishes that four tiles ahead through a ring of descriptors in shared memory, so that neither the MMA
+//              thread nor the compute threads spend a tile switch on index arithmetic
 //   warp 9     allocates all 512 TMEM columns and issues the MMAs. The roles meet once per step: when the compute threads have
 //              finished step n (barrier CDONE) the MMA thread issues, back to back, the products that depend on it and the S-type
 //              products of the steps ahead, so the tensor pipe works through them while the threads are in step n + 1.
@@ -19,6 +22,11 @@
 // Every mbarrier wait is bounded; on expiry the CTA raises the fault word, drains and frees its TMEM.
 
 constexpr int WB = 128;
+// Ring of tile descriptors, and how far ahead of its own tile the producer publishes. The producer can start tile t once the S-type
+// products of tile t - 2 are out (t - 1 with one buffer for the kept tile); the role furthest behind, the accumulating products'
+// cursor, may then still stand on tile t - 3 when tiles are one step long, about to read descriptor t - 2. Publishing t + 4 into the
+// slot of t - 4 therefore never touches a descriptor still to be read, and never runs a slot's barrier two phases ahead of a reader.
+constexpr int DESC_SLOTS = 8, DESC_AHEAD = 4;
 
 __device__ __forceinline__ void tmem_st_packed(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
 
@@ -86,36 +94,75 @@ template <int D> struct DqW {
   // from L2) before the product two or three steps on needs it, so head_dim 64, with room to spare and short steps, rings one deeper
   static constexpr int KS = D == 64 ? 4 : 3, VS = D == 64 ? 3 : 2;
   static constexpr int OFF_Q = 0, OFF_G = NQD * TILE_BYTES, OFF_K = 2 * NQD * TILE_BYTES, OFF_V = OFF_K + KS * TILE_BYTES, OFF_BAR = OFF_V + VS * TILE_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;           // D 64: 177 KB; D 128: 225 KB
+  static constexpr int OFF_DESC = OFF_BAR + 512;                    // barriers and the TMEM slot, then the ring of tile descriptors
+  static constexpr int SMEM_BYTES = OFF_DESC + DESC_SLOTS * 32 + 1024;   // D 64: 178 KB; D 128: 226 KB
   static constexpr int COL_S = 0, COL_DP = 256, COL_DQ = 384;       // S (two buffers of 128 columns; dS over the first 32 of each half), dP, dQ
 };
-enum { WQ_QDFULL0 = 0, WQ_QDEMPTY0 = 2, WQ_KFULL0 = 4, WQ_KEMPTY0 = 8, WQ_VFULL0 = 12, WQ_VEMPTY0 = 15, WQ_SFULL0 = 18, WQ_DPFULL = 20, WQ_CDONE, WQ_DONE, WQ_ACCFREE, WQ_COUNT };
+enum { WQ_QDFULL0 = 0, WQ_QDEMPTY0 = 2, WQ_KFULL0 = 4, WQ_KEMPTY0 = 8, WQ_VFULL0 = 12, WQ_VEMPTY0 = 15, WQ_SFULL0 = 18, WQ_DPFULL = 20, WQ_CDONE, WQ_DONE, WQ_ACCFREE, WQ_DESC0, WQ_COUNT = WQ_DESC0 + DESC_SLOTS };
 
-struct DqWalkW {
-  int q0, b, h, hk, iters;
-  __device__ __forceinline__ bool set(const BwdArgs& args, int tiles, int total, int item) {
-    const int g = blockIdx.x + item * gridDim.x;
-    if (g >= total) return false;
-    const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
-    q0 = (tiles - 1 - ord.rank) * BM;
-    b = ord.plane / args.heads; h = ord.plane % args.heads; hk = h / (args.heads / args.kv_heads);
-    iters = (min(args.time, q0 + BM) + WB - 1) / WB;
-    return true;
-  }
-};
+// Where a tile sits: pos = its first query (dQ) or key (dK/dV) row; h = the query head (dQ only); blocks = 128-wide query blocks
+// per head of the walk (dK/dV only); iters = steps of the walk; valid = 0 past the end of the CTA's list.
+struct TileDesc { int pos, b, h, hk, iters, blocks, valid, pad; };
+
+__device__ __forceinline__ TileDesc dq_tile(const BwdArgs& args, int tiles, int total, int item) {
+  TileDesc d = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int g = blockIdx.x + item * gridDim.x;
+  if (g >= total) return d;
+  const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
+  d.pos = (tiles - 1 - ord.rank) * BM;
+  d.b = ord.plane / args.heads; d.h = ord.plane % args.heads; d.hk = d.h / (args.heads / args.kv_heads);
+  d.iters = (min(args.time, d.pos + BM) + WB - 1) / WB;
+  d.valid = 1;
+  return d;
+}
+__device__ __forceinline__ TileDesc dkv_tile(const BwdArgs& args, int tiles, int total, int item) {
+  TileDesc d = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int g = blockIdx.x + item * gridDim.x;
+  if (g >= total) return d;
+  const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
+  d.pos = ord.rank * BN;                         // early key tiles see the most queries
+  d.b = ord.plane / args.kv_heads; d.hk = ord.plane % args.kv_heads;
+  d.blocks = (args.time - d.pos + WB - 1) / WB;
+  d.iters = (args.heads / args.kv_heads) * d.blocks;
+  d.valid = 1;
+  return d;
+}
+// The producer thread writes descriptor `item` into slot item % 8 and arrives on the slot's barrier (release); a reader waits for
+// the slot's phase item / 8 (acquire) and copies the descriptor out.
+__device__ __forceinline__ void publish_desc(uint8_t* ring, uint32_t bar0, int item, const TileDesc& d) {
+  int4* slot = reinterpret_cast<int4*>(ring + (item % DESC_SLOTS) * 32);
+  slot[0] = make_int4(d.pos, d.b, d.h, d.hk);
+  slot[1] = make_int4(d.iters, d.blocks, d.valid, 0);
+  mbar_arrive(bar0 + 8u * (item % DESC_SLOTS));
+}
+__device__ __forceinline__ bool read_desc(const uint8_t* ring, uint32_t bar0, int item, TileDesc& d, uint32_t* fault, volatile int* abort_flag) {
+  if (!mbar_wait(bar0 + 8u * (item % DESC_SLOTS), (item / DESC_SLOTS) & 1, fault, abort_flag)) { d.valid = 0; return false; }
+  const int4* slot = reinterpret_cast<const int4*>(ring + (item % DESC_SLOTS) * 32);
+  const int4 a = slot[0], c = slot[1];
+  d.pos = a.x; d.b = a.y; d.h = a.z; d.hk = a.w; d.iters = c.x; d.blocks = c.y; d.valid = c.z; d.pad = 0;
+  return true;
+}
 // where one role stands in the CTA's stream of steps: step n of the stream is step j of tile `item`
-template <class WALK>
 struct StepCursor {
-  WALK w;
+  TileDesc d;
   int item, j;
   uint32_t n;
   bool valid;
-  __device__ __forceinline__ void start(const BwdArgs& args, int tiles, int total) { item = 0; j = 0; n = 0; valid = w.set(args, tiles, total, 0); }
-  __device__ __forceinline__ void advance(const BwdArgs& args, int tiles, int total) {
-    ++n;
-    if (++j == w.iters) { ++item; j = 0; valid = w.set(args, tiles, total, item); }
+  __device__ __forceinline__ bool start(const uint8_t* ring, uint32_t bar0, uint32_t* fault, volatile int* abort_flag) {
+    item = 0; j = 0; n = 0;
+    const bool ok = read_desc(ring, bar0, 0, d, fault, abort_flag);
+    valid = ok && d.valid;
+    return ok;
   }
-  __device__ __forceinline__ bool last() const { return j + 1 == w.iters; }
+  __device__ __forceinline__ bool advance(const uint8_t* ring, uint32_t bar0, uint32_t* fault, volatile int* abort_flag) {
+    ++n;
+    if (++j < d.iters) return true;
+    ++item; j = 0;
+    const bool ok = read_desc(ring, bar0, item, d, fault, abort_flag);
+    valid = ok && d.valid;
+    return ok;
+  }
+  __device__ __forceinline__ bool last() const { return j + 1 == d.iters; }
 };
 
 template <int D>
@@ -129,7 +176,9 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   using C = DqW<D>;
   constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, NQD = C::NQD, KS = C::KS, VS = C::VS;
   constexpr uint32_t TILE16 = TILE_BYTES >> 4;
-  static_assert(WQ_COUNT * 8 + 8 <= 256, "barrier table");
+  static_assert(WQ_COUNT * 8 + 8 <= 512, "barrier table");
+  uint8_t* ring = base_ptr + C::OFF_DESC;
+  const uint32_t desc_bar = base + C::OFF_BAR + 8u * WQ_DESC0;
   auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + C::OFF_BAR + 8 * WQ_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -153,16 +202,19 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (warp == 8) {
     if (lane == 0) {
-      DqWalkW w;
+      for (int i = 0; i < DESC_AHEAD; ++i) publish_desc(ring, desc_bar, i, dq_tile(args, tiles, total, i));
       uint32_t n = 0;
       bool ok = true;
-      for (int item = 0; ok && w.set(args, tiles, total, item); ++item) {
+      for (int item = 0; ok; ++item) {
+        const TileDesc w = dq_tile(args, tiles, total, item);
+        if (!w.valid) break;
         const int qb = item % NQD;
         // a Q / dO buffer is free once the last S and dP of the tile that used it have read it
         if (item >= NQD && !mbar_wait(bar(WQ_QDEMPTY0 + qb), ((item / NQD) - 1) & 1, args.fault, abort_flag)) break;
+        publish_desc(ring, desc_bar, item + DESC_AHEAD, dq_tile(args, tiles, total, item + DESC_AHEAD));
         mbar_expect_tx(bar(WQ_QDFULL0 + qb), 2 * TILE_BYTES);
-        load_tile<NSUB, 128>(base + C::OFF_Q + qb * TILE_BYTES, &tm_q, bar(WQ_QDFULL0 + qb), args.h_first, w.h, w.q0, w.b);
-        load_tile<NSUB, 128>(base + C::OFF_G + qb * TILE_BYTES, &tm_g, bar(WQ_QDFULL0 + qb), args.h_first, w.h, w.q0, w.b);
+        load_tile<NSUB, 128>(base + C::OFF_Q + qb * TILE_BYTES, &tm_q, bar(WQ_QDFULL0 + qb), args.h_first, w.h, w.pos, w.b);
+        load_tile<NSUB, 128>(base + C::OFF_G + qb * TILE_BYTES, &tm_g, bar(WQ_QDFULL0 + qb), args.h_first, w.h, w.pos, w.b);
         for (int j = 0; j < w.iters; ++j, ++n) {
           const int ks = n % KS, vs = n % VS;
           if (n >= KS && !mbar_wait(bar(WQ_KEMPTY0 + ks), ((n / KS) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
@@ -179,7 +231,7 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t idesc_s = make_idesc(BM, WB, 0, 0), idesc_o = make_idesc(BM, D, 0, 1);
       const uint32_t q_lo = desc_lo(base + C::OFF_Q, 0), g_lo = desc_lo(base + C::OFF_G, 0), k_lo = desc_lo(base + C::OFF_K, 0), v_lo = desc_lo(base + C::OFF_V, 0);
       const uint32_t km_lo = desc_lo(base + C::OFF_K, ST128);
-      using Cur = StepCursor<DqWalkW>;
+      using Cur = StepCursor;
       // S = Q K^T of the cursor's step, into S buffer n % 2
       auto issue_s = [&](const Cur& c) -> bool {
         const uint32_t qd = (uint32_t)(c.item % NQD) * TILE16, ks = (c.n % KS) * TILE16;
@@ -218,26 +270,26 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (c.last()) umma_commit(bar(WQ_DONE));
         return true;
       };
+      auto next = [&](Cur& c) { return c.advance(ring, desc_bar, args.fault, abort_flag); };
       Cur cs, cp, cq;
-      cs.start(args, tiles, total); cp = cs; cq = cs;
-      bool ok = cs.valid;
-      if (ok) { ok = issue_s(cs); cs.advance(args, tiles, total); }
-      if (ok && cs.valid) { ok = issue_s(cs); cs.advance(args, tiles, total); }
-      if (ok) { ok = issue_dp(cp); cp.advance(args, tiles, total); }
+      bool ok = cs.start(ring, desc_bar, args.fault, abort_flag) && cs.valid;
+      cp = cs; cq = cs;
+      if (ok) ok = issue_s(cs) && next(cs);
+      if (ok && cs.valid) ok = issue_s(cs) && next(cs);
+      if (ok) ok = issue_dp(cp) && next(cp);
       while (ok && cq.valid) {
         if (!mbar_wait(bar(WQ_CDONE), cq.n & 1, args.fault, abort_flag)) break;
         fence_after();
-        if (cp.valid) { if (!issue_dp(cp)) break; cp.advance(args, tiles, total); }
-        if (!issue_dq(cq)) break;
-        cq.advance(args, tiles, total);
-        if (cs.valid) { if (!issue_s(cs)) break; cs.advance(args, tiles, total); }
+        if (cp.valid && !(issue_dp(cp) && next(cp))) break;
+        if (!(issue_dq(cq) && next(cq))) break;
+        if (cs.valid && !(issue_s(cs) && next(cs))) break;
       }
     }
   } else {
     const int tid = threadIdx.x & 127, half = warp >> 2;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
-    DqWalkW w;
+    TileDesc w, wn;
     uint32_t n = 0;
     bool ok = true, fin = false;
     int fin_item = 0, fin_b = 0, fin_h = 0, fin_row = 0;
@@ -256,28 +308,27 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       fin = false;
       return true;
     };
-    // the row's statistics are fetched one tile ahead, so their latency sits under the previous tile's walk
-    // (the loaded values are not touched until the tile switch: a thread stalls at the first use of a load, not at the load)
-    auto stat_of = [&](const DqWalkW& t, bool valid, float& lse, float& dr) {
-      const int r = t.q0 + tid;
+    // The row's statistics are fetched one tile ahead, so their latency sits under the previous tile's walk (the loaded values are
+    // not touched until the tile switch: a thread stalls at the first use of a load, not at the load).
+    auto stat_of = [&](const TileDesc& t, float& lse, float& dr) {
+      const int r = t.pos + tid;
       const int64_t idx = ((int64_t)t.b * args.heads + t.h) * args.time + r;
       lse = INFINITY; dr = 0.0f;
-      if (valid && r < args.time) { lse = args.lse[idx]; dr = args.dr[idx]; }
+      if (t.valid && r < args.time) { lse = args.lse[idx]; dr = args.dr[idx]; }
     };
-    DqWalkW wn;
-    bool have = w.set(args, tiles, total, 0);
+    ok = read_desc(ring, desc_bar, 0, w, args.fault, abort_flag);
     float lse_row = INFINITY, dr_row = 0.0f, lse_next, dr_next;
-    if (have) { stat_of(w, true, lse_row, dr_row); lse_row *= LOG2E; }
-    for (int item = 0; ok && have; ++item) {
-      const bool more = wn.set(args, tiles, total, item + 1);
-      stat_of(wn, more, lse_next, dr_next);
-      const int row = w.q0 + tid;
+    if (ok && w.valid) { stat_of(w, lse_row, dr_row); lse_row *= LOG2E; }
+    for (int item = 0; ok && w.valid; ++item) {
+      if (!read_desc(ring, desc_bar, item + 1, wn, args.fault, abort_flag)) { ok = false; break; }
+      stat_of(wn, lse_next, dr_next);
+      const int row = w.pos + tid;
       for (int j = 0; j < w.iters; ++j, ++n) {
         const int key0 = j * WB + half * 64;
         const uint32_t s_addr = lane_base + C::COL_S + (n & 1) * WB + half * 64;
         if (!mbar_wait(bar(WQ_SFULL0 + (n & 1)), (n >> 1) & 1, args.fault, abort_flag)) { ok = false; break; }
         fence_after();
-        const bool masked = j * WB + WB > w.q0 || j * WB + WB > args.time;
+        const bool masked = j * WB + WB > w.pos || j * WB + WB > args.time;
         // visible columns of this half: key <= row and key < time, as a range of column indices
         const int lo = 0, hi = min(row - key0 + 1, args.time - key0);
         float p[64];
@@ -298,7 +349,7 @@ sdpa_bwd_dq_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       if (!ok) break;
       fin = true; fin_item = item; fin_b = w.b; fin_h = w.h; fin_row = row;
-      w = wn; have = more; lse_row = lse_next * LOG2E; dr_row = dr_next;
+      w = wn; lse_row = lse_next * LOG2E; dr_row = dr_next;
     }
     if (ok && fin) finalize();
   }
@@ -321,26 +372,12 @@ template <int D> struct DkvW {
   static constexpr int QS = D == 64 ? 4 : 3, GS = D == 64 ? 3 : 2;
   static constexpr int OFF_K = 0, OFF_V = NKV * TILE_BYTES, OFF_Q = 2 * NKV * TILE_BYTES, OFF_G = OFF_Q + QS * TILE_BYTES, OFF_STAT = OFF_G + GS * TILE_BYTES,
                        OFF_BAR = OFF_STAT + GS * 1024;              // per dO stage: lse of its 128 queries, then their Dr
-  static constexpr int SMEM_BYTES = OFF_BAR + 256;                  // D 64: 179 KB; D 128: 226.25 KB (the launch asks for 1024-byte alignment)
+  static constexpr int OFF_DESC = OFF_BAR + 512;                    // barriers and the TMEM slot, then the ring of tile descriptors
+  static constexpr int SMEM_BYTES = OFF_DESC + DESC_SLOTS * 32;     // D 64: 179.75 KB; D 128: 226.75 KB (the launch asks for 1024-byte alignment)
+  static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
   static constexpr int COL_S = 0, COL_DP = NS * WB, COL_DV = COL_DP + WB, COL_DK = COL_DV + D;   // 512 columns either way
 };
-enum { WK_KVFULL0 = 0, WK_KVEMPTY0 = 2, WK_QFULL0 = 4, WK_QEMPTY0 = 8, WK_GFULL0 = 12, WK_GEMPTY0 = 15, WK_SFULL0 = 18, WK_DPFULL = 20, WK_CDONE, WK_DONE, WK_ACCFREE, WK_COUNT };
-
-struct DkvWalkW {
-  int k0, b, hk, q_blocks, iters;
-  __device__ __forceinline__ bool set(const BwdArgs& args, int tiles, int total, int item) {
-    const int g = blockIdx.x + item * gridDim.x;
-    if (g >= total) return false;
-    const TileOrder ord = tile_order(g, args.planes, args.group, tiles);
-    k0 = ord.rank * BN;                          // early key tiles see the most queries
-    b = ord.plane / args.kv_heads; hk = ord.plane % args.kv_heads;
-    q_blocks = (args.time - k0 + WB - 1) / WB;
-    iters = (args.heads / args.kv_heads) * q_blocks;
-    return true;
-  }
-  __device__ __forceinline__ int head(const BwdArgs& args, int j) const { return hk * (args.heads / args.kv_heads) + j / q_blocks; }
-  __device__ __forceinline__ int q0(int j) const { return k0 + (j % q_blocks) * WB; }
-};
+enum { WK_KVFULL0 = 0, WK_KVEMPTY0 = 2, WK_QFULL0 = 4, WK_QEMPTY0 = 8, WK_GFULL0 = 12, WK_GEMPTY0 = 15, WK_SFULL0 = 18, WK_DPFULL = 20, WK_CDONE, WK_DONE, WK_ACCFREE, WK_DESC0, WK_COUNT = WK_DESC0 + DESC_SLOTS };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -353,7 +390,9 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   using C = DkvW<D>;
   constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, NKV = C::NKV, NS = C::NS, QS = C::QS, GS = C::GS;
   constexpr uint32_t TILE16 = TILE_BYTES >> 4;
-  static_assert(WK_COUNT * 8 + 8 <= 256, "barrier table");
+  static_assert(WK_COUNT * 8 + 8 <= 512, "barrier table");
+  uint8_t* ring = base_ptr + C::OFF_DESC;
+  const uint32_t desc_bar = base + C::OFF_BAR + 8u * WK_DESC0;
   static_assert(C::COL_DK + D <= 512, "tensor memory columns");
   auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + C::OFF_BAR + 8 * WK_COUNT);
@@ -378,17 +417,22 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   if (warp == 8) {
     if (lane == 0) {
-      DkvWalkW w;
+      for (int i = 0; i < DESC_AHEAD; ++i) publish_desc(ring, desc_bar, i, dkv_tile(args, tiles, total, i));
+      const int rep = args.heads / args.kv_heads;
       uint32_t n = 0;
       bool ok = true;
-      for (int item = 0; ok && w.set(args, tiles, total, item); ++item) {
+      for (int item = 0; ok; ++item) {
+        const TileDesc w = dkv_tile(args, tiles, total, item);
+        if (!w.valid) break;
         const int kb = item % NKV;
         if (item >= NKV && !mbar_wait(bar(WK_KVEMPTY0 + kb), ((item / NKV) - 1) & 1, args.fault, abort_flag)) break;
+        publish_desc(ring, desc_bar, item + DESC_AHEAD, dkv_tile(args, tiles, total, item + DESC_AHEAD));
         mbar_expect_tx(bar(WK_KVFULL0 + kb), 2 * TILE_BYTES);
-        load_tile<NSUB, 128>(base + C::OFF_K + kb * TILE_BYTES, &tm_k, bar(WK_KVFULL0 + kb), args.h_first, w.hk, w.k0, w.b);
-        load_tile<NSUB, 128>(base + C::OFF_V + kb * TILE_BYTES, &tm_v, bar(WK_KVFULL0 + kb), args.h_first, w.hk, w.k0, w.b);
+        load_tile<NSUB, 128>(base + C::OFF_K + kb * TILE_BYTES, &tm_k, bar(WK_KVFULL0 + kb), args.h_first, w.hk, w.pos, w.b);
+        load_tile<NSUB, 128>(base + C::OFF_V + kb * TILE_BYTES, &tm_v, bar(WK_KVFULL0 + kb), args.h_first, w.hk, w.pos, w.b);
+        int h = w.hk * rep, q0 = w.pos;                // the walk: every query head of the group, each from the diagonal block to the end
         for (int j = 0; j < w.iters; ++j, ++n) {
-          const int qs = n % QS, gs = n % GS, h = w.head(args, j), q0 = w.q0(j);
+          const int qs = n % QS, gs = n % GS;
           if (n >= QS && !mbar_wait(bar(WK_QEMPTY0 + qs), ((n / QS) - 1) & 1, args.fault, abort_flag)) { ok = false; break; }
           const uint32_t stat_bytes = (uint32_t)min(WB, args.time - q0) * 4u;
           const int64_t idx = ((int64_t)w.b * args.heads + h) * args.time + q0;
@@ -399,6 +443,8 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           bulk_load(base + C::OFF_STAT + gs * 1024, args.lse + idx, stat_bytes, bar(WK_GFULL0 + gs));
           bulk_load(base + C::OFF_STAT + gs * 1024 + 512, args.dr + idx, stat_bytes, bar(WK_GFULL0 + gs));
           load_tile<NSUB, 128>(base + C::OFF_G + gs * TILE_BYTES, &tm_g, bar(WK_GFULL0 + gs), args.h_first, h, q0, w.b);
+          q0 += WB;
+          if (q0 >= args.time) { q0 = w.pos; ++h; }
         }
       }
     }
@@ -407,7 +453,7 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const uint32_t idesc_s = make_idesc(BN, WB, 0, 0), idesc_o = make_idesc(BN, D, 0, 1);
       const uint32_t k_lo = desc_lo(base + C::OFF_K, 0), v_lo = desc_lo(base + C::OFF_V, 0), q_lo = desc_lo(base + C::OFF_Q, 0), g_lo = desc_lo(base + C::OFF_G, 0);
       const uint32_t qm_lo = desc_lo(base + C::OFF_Q, ST128), gm_lo = desc_lo(base + C::OFF_G, ST128);
-      using Cur = StepCursor<DkvWalkW>;
+      using Cur = StepCursor;
       // S^T = K Q^T of the cursor's step
       auto issue_s = [&](const Cur& c) -> bool {
         const uint32_t kv = (uint32_t)(c.item % NKV) * TILE16, qs = (c.n % QS) * TILE16;
@@ -447,12 +493,13 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           umma_ts(tmem_base + C::COL_DK, dst + (kk >> 2) * 64 + (kk & 3) * 8, qm_lo + qs + kk * MNSTEP, HI, idesc_o, (c.j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(WK_QEMPTY0 + c.n % QS));
       };
+      auto next = [&](Cur& c) { return c.advance(ring, desc_bar, args.fault, abort_flag); };
       Cur cs, cp, cq;
-      cs.start(args, tiles, total); cp = cs; cq = cs;
-      bool ok = cs.valid;
-      if (ok) { ok = issue_s(cs); cs.advance(args, tiles, total); }
-      if (NS == 2 && ok && cs.valid) { ok = issue_s(cs); cs.advance(args, tiles, total); }
-      if (ok) { ok = issue_dp(cp); cp.advance(args, tiles, total); }
+      bool ok = cs.start(ring, desc_bar, args.fault, abort_flag) && cs.valid;
+      cp = cs; cq = cs;
+      if (ok) ok = issue_s(cs) && next(cs);
+      if (NS == 2 && ok && cs.valid) ok = issue_s(cs) && next(cs);
+      if (ok) ok = issue_dp(cp) && next(cp);
       while (ok && cq.valid) {
         if (!mbar_wait(bar(WK_CDONE), cq.n & 1, args.fault, abort_flag)) break;
         // a tile's first accumulating products overwrite dV and dK: the previous tile's rows must hold theirs in registers (they read
@@ -463,19 +510,19 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (NS == 2) {
           // dS^T sits over dP^T: dK first, then the next dP^T may overwrite it; P^T sits over S^T: dV, then the S^T two steps ahead
           issue_dk(cq);
-          if (cp.valid) { if (!issue_dp(cp)) break; cp.advance(args, tiles, total); }
+          if (cp.valid && !(issue_dp(cp) && next(cp))) break;
           issue_dv(cq);
           if (last) umma_commit(bar(WK_DONE));
-          cq.advance(args, tiles, total);
-          if (cs.valid) { if (!issue_s(cs)) break; cs.advance(args, tiles, total); }
+          if (!next(cq)) break;
+          if (cs.valid && !(issue_s(cs) && next(cs))) break;
         } else {
           // one S^T buffer: dV, then the next S^T at once (the compute threads wait for it), then dK and the next dP^T under its exponentials
           issue_dv(cq);
-          if (cs.valid) { if (!issue_s(cs)) break; cs.advance(args, tiles, total); }
+          if (cs.valid && !(issue_s(cs) && next(cs))) break;
           issue_dk(cq);
           if (last) umma_commit(bar(WK_DONE));
-          cq.advance(args, tiles, total);
-          if (cp.valid) { if (!issue_dp(cp)) break; cp.advance(args, tiles, total); }
+          if (!next(cq)) break;
+          if (cp.valid && !(issue_dp(cp) && next(cp))) break;
         }
       }
     }
@@ -483,7 +530,7 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int tid = threadIdx.x & 127, half = warp >> 2;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl2 = args.scale * LOG2E;
-    DkvWalkW w;
+    TileDesc w;
     uint32_t n = 0;
     bool ok = true, fin = false;
     int fin_item = 0, fin_b = 0, fin_hk = 0, fin_key = 0;
@@ -502,17 +549,22 @@ sdpa_bwd_dkv_w_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       fin = false;
       return true;
     };
-    for (int item = 0; ok && w.set(args, tiles, total, item); ++item) {
-      const int key = w.k0 + tid;
+    for (int item = 0; ok; ++item) {
+      if (!read_desc(ring, desc_bar, item, w, args.fault, abort_flag)) { ok = false; break; }
+      if (!w.valid) break;
+      const int key = w.pos + tid;
+      int q0 = w.pos - WB;
       for (int j = 0; j < w.iters; ++j, ++n) {
-        const int q0 = w.q0(j), qb = q0 + half * 64;
+        q0 += WB;
+        if (q0 >= args.time) q0 = w.pos;              // the next query head of the group, from the diagonal block again
+        const int qb = q0 + half * 64;
         const uint32_t s_addr = lane_base + C::COL_S + (n % NS) * WB + half * 64, dp_addr = lane_base + C::COL_DP + half * 64;
         const float* stat = reinterpret_cast<const float*>(base_ptr + C::OFF_STAT + (n % GS) * 1024) + half * 64;
         // the step's statistics arrive with its dO tile; then its S^T
         if (!mbar_wait(bar(WK_GFULL0 + n % GS), (n / GS) & 1, args.fault, abort_flag)) { ok = false; break; }
         if (!mbar_wait(bar(WK_SFULL0 + n % NS), (n / NS) & 1, args.fault, abort_flag)) { ok = false; break; }
         fence_after();
-        const bool masked = q0 < w.k0 + BN || q0 + WB > args.time || w.k0 + BN > args.time;
+        const bool masked = q0 < w.pos + BN || q0 + WB > args.time || w.pos + BN > args.time;
         // visible columns of this half: key <= q, q < time (and the key itself inside the sequence), as a range of column indices
         const int lo = key < args.time ? key - qb : 64, hi = args.time - qb;
         // phase 1: P^T with the columns' (queries') statistics; packed over this half's first 32 S^T columns
