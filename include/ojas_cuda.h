@@ -93,6 +93,10 @@ ojc_status ojc_sdpa_forward_variant(int32_t variant);    /* attention kernels on
 ojc_status ojc_mlp_epilogue_variant(int32_t variant);    /* the step driver's MLP backward under bf16 autocast. 0: the library's choice (SwiGLU's forward runs in the epilogue of the gate/up product and its backward in that of the down projection's input-gradient product, where the shapes allow); 1: kernels of their own after the products (tests: both give the same bits) */
 ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable);
 ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches);
+/* the same totals in two parts: the plain products, and the launches that also ran SwiGLU in their epilogue (they move 2-3x the bytes of the
+ * plain product for the same 2*m*n*k, so their rate is not a tensor-core figure) */
+ojc_status ojc_profile_gemm_read_split(ojc_backend* be, double* plain_ms, double* plain_flops, uint64_t* plain_launches, double* epilogue_ms, double* epilogue_flops,
+                                       uint64_t* epilogue_launches);
 ojc_status ojc_stream_wait_event(ojc_backend* be, void* cuda_stream, void* cuda_event);  /* cuda_stream waits for an event recorded by this backend (NULL stream: the backend's own) */
 
 /* ---- owner-thread session: how a host whose calls come from many threads holds this single-owner-thread backend. ojas-capi does it for

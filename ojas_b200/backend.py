@@ -187,6 +187,12 @@ class CudaBackend:
         _check(lib.ojc_profile_gemm_read(self._handle, C.byref(ms), C.byref(fl), C.byref(n)))
         return ms.value, fl.value, n.value
 
+    def profile_gemm_read_split(self):
+        """The same in two parts: ((ms, flops, launches) of the plain products, the same of the launches with SwiGLU in their epilogue)."""
+        v = [C.c_double(), C.c_double(), C.c_uint64(), C.c_double(), C.c_double(), C.c_uint64()]
+        _check(lib.ojc_profile_gemm_read_split(self._handle, *(C.byref(x) for x in v)))
+        return (v[0].value, v[1].value, v[2].value), (v[3].value, v[4].value, v[5].value)
+
     def stream_wait_event(self, stream_ptr: int, event_ptr: int):
         _check(lib.ojc_stream_wait_event(self._handle, C.c_void_p(stream_ptr), C.c_void_p(event_ptr)))
 

@@ -54,7 +54,7 @@ struct ojc_backend {
   int sm_count = 148;                      // the opened device's; sizes persistent grids only (never a reduction's partial count, see REDUCE_SMS)
   void* tmap_encode = nullptr;             // cuTensorMapEncodeTiled, resolved once
   bool profile_gemm = false;               // bracket tensor-core GEMM launches with events
-  struct GemmSample { cudaEvent_t start, stop; double flops; };
+  struct GemmSample { cudaEvent_t start, stop; double flops; bool with_epilogue; };   // with_epilogue: the launch also ran SwiGLU in its epilogue
   std::vector<GemmSample> gemm_samples;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> event_pool;
   // Finishing lane for two-stage reductions (per-block partials, then a few blocks that sum them into a weight gradient).

@@ -232,7 +232,7 @@ __global__ void swiglu_rows_forward_kernel(const bf16* __restrict__ au, int64_t 
     float a[8], u[8], r[8];
     load8(au + row * ld + c, a); load8(au + row * ld + (int64_t)f8 * 8 + c, u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) r[k] = swiglu::forward_elem(a[k], u[k]);
+    for (int k = 0; k < 8; k += 2) swiglu::forward_pair(a[k], a[k + 1], u[k], u[k + 1], r[k], r[k + 1]);
     store8(m + row * (int64_t)f8 * 8 + c, r);
   }
 }
@@ -243,7 +243,7 @@ __global__ void swiglu_rows_backward_kernel(const bf16* __restrict__ au, const b
     float a[8], u[8], g[8], ra[8], ru[8];
     load8(au + row * ld + c, a); load8(au + row * ld + (int64_t)f8 * 8 + c, u); load8(gm + row * (int64_t)f8 * 8 + c, g);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) swiglu::backward_elem(a[k], u[k], g[k], ra[k], ru[k]);
+    for (int k = 0; k < 8; k += 2) swiglu::backward_pair(a[k], a[k + 1], u[k], u[k + 1], g[k], g[k + 1], ra[k], ra[k + 1], ru[k], ru[k + 1]);
     store8(gau + row * ld + c, ra); store8(gau + row * ld + (int64_t)f8 * 8 + c, ru);
   }
 }

@@ -56,6 +56,7 @@ struct TcArgs {
   int batch;                // independent matrices: a unit is (matrix, tile, split); batch > 1 needs tma_store and splits == 1
   int tma_store;            // finished blocks leave through TMA tile stores (no residual operand; split partials need m % 32 == 0)
   const bf16* ns_src; int64_t ns_ld, ns_bs; float ns_src_mul, ns_acc_mul;   // Newton-Schulz combine epilogue (NsCombine); ns_src null: none
+  const bf16* sw_au; int64_t sw_ld;   // SwiGLU-backward epilogue (SwigluGrad): a at column 0, u at column n of rows sw_ld wide; null: none
   int sw_f;                 // SwiGLU-forward epilogue (SwigluForward): the hidden width F; C is (a | u), n = 2 F
   int tiles_n_fast;         // tile order: 1 = neighbouring CTAs share an A row block (few column tiles), 0 = they share a B column block
 };
@@ -193,15 +194,11 @@ __device__ __forceinline__ void drain_tile(const TcArgs& args, const CUtensorMap
 }
 
 // SwiGLU backward on 64 columns of this warp's share of a finished accumulator: the accumulator is g, the gradient of
-// m = bf16(silu(a)) * u, rounded to bf16 as a stored g would be; a and u for the same 32 rows x 64 columns were brought into the warp's
-// input boxes by TMA (128-byte swizzle, like the store boxes) and are in registers (qa, qu) by the time this runs. Two boxes leave
-// instead of one: g_a for columns x.. and g_u for columns n + x.. of the output rows; the second waits in registers until the first
-// has been read out of the staging rows. The 64 columns are taken in two halves to stay inside the register file.
+// m = bf16(silu(a)) * u, rounded to bf16 as a stored g would be. a and u of the same 32 rows x 64 columns sit in the warp's two staging
+// boxes, lane = row (swizzled 128-byte rows, put there by the caller); each lane turns its row into g_a and g_u in place, 16 bytes at a
+// time, and the boxes leave as two TMA stores: g_a to columns x.., g_u to columns n + x.. of the output rows.
 __device__ __forceinline__ void drain_swiglu_backward(const TcArgs& args, const CUtensorMap& tmap_c, uint32_t tsrc, int row_base, int x, int c0, int bz, int lane,
-                                                      const uint4 (&qa)[8], const uint4 (&qu)[8], uint8_t* stage_bytes, uint32_t stage_addr) {
-  uint4 second[8];
-  if (lane == 0) bulk_wait_read();           // the previous box has left the staging rows
-  __syncwarp();
+                                                      uint8_t* stage_bytes, uint32_t stage_addr) {
   uint8_t* rowp = stage_bytes + lane * 128;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -210,31 +207,29 @@ __device__ __forceinline__ void drain_swiglu_backward(const TcArgs& args, const 
     tmem_wait_ld();
 #pragma unroll
     for (int cj = 0; cj < 4; ++cj) {
-      const int ci = half * 4 + cj;
+      const int off = ((half * 4 + cj) ^ (lane & 7)) << 4;
       const uint32_t* v = &r[cj * 8];
-      const uint32_t wa[4] = {qa[ci].x, qa[ci].y, qa[ci].z, qa[ci].w}, wu[4] = {qu[ci].x, qu[ci].y, qu[ci].z, qu[ci].w};
+      const uint4 qa = *reinterpret_cast<const uint4*>(rowp + off), qu = *reinterpret_cast<const uint4*>(rowp + EPI_WARP_BYTES + off);
+      const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wu[4] = {qu.x, qu.y, qu.z, qu.w};
       float ga[8], gu[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float av = (e & 1) ? __uint_as_float(wa[e >> 1] & 0xffff0000u) : __uint_as_float(wa[e >> 1] << 16);
-        const float uv = (e & 1) ? __uint_as_float(wu[e >> 1] & 0xffff0000u) : __uint_as_float(wu[e >> 1] << 16);
-        swiglu::backward_elem(av, uv, swiglu::round_bf16(__uint_as_float(v[e])), ga[e], gu[e]);
+      for (int e = 0; e < 8; e += 2) {
+        float g0 = __uint_as_float(v[e]), g1 = __uint_as_float(v[e + 1]);
+        swiglu::round2_bf16(g0, g1);
+        swiglu::backward_pair(__uint_as_float(wa[e >> 1] << 16), __uint_as_float(wa[e >> 1] & 0xffff0000u), __uint_as_float(wu[e >> 1] << 16),
+                              __uint_as_float(wu[e >> 1] & 0xffff0000u), g0, g1, ga[e], ga[e + 1], gu[e], gu[e + 1]);
       }
-      *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) =
-          make_uint4(pack2_bf16(ga[0], ga[1]), pack2_bf16(ga[2], ga[3]), pack2_bf16(ga[4], ga[5]), pack2_bf16(ga[6], ga[7]));
-      second[ci] = make_uint4(pack2_bf16(gu[0], gu[1]), pack2_bf16(gu[2], gu[3]), pack2_bf16(gu[4], gu[5]), pack2_bf16(gu[6], gu[7]));
+      *reinterpret_cast<uint4*>(rowp + off) = make_uint4(pack2_bf16(ga[0], ga[1]), pack2_bf16(ga[2], ga[3]), pack2_bf16(ga[4], ga[5]), pack2_bf16(ga[6], ga[7]));
+      *reinterpret_cast<uint4*>(rowp + EPI_WARP_BYTES + off) = make_uint4(pack2_bf16(gu[0], gu[1]), pack2_bf16(gu[2], gu[3]), pack2_bf16(gu[4], gu[5]), pack2_bf16(gu[6], gu[7]));
     }
   }
   fence_async_smem();
   __syncwarp();
-  const bool issue = lane == 0 && x < args.n && row_base < args.m;
-  if (issue) { tma_store_3d(&tmap_c, stage_addr, x, row_base, bz); bulk_commit(); bulk_wait_read(); }
-  __syncwarp();
-#pragma unroll
-  for (int ci = 0; ci < 8; ++ci) *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = second[ci];
-  fence_async_smem();
-  __syncwarp();
-  if (issue) { tma_store_3d(&tmap_c, stage_addr, args.n + x, row_base, bz); bulk_commit(); }
+  if (lane == 0 && x < args.n && row_base < args.m) {
+    tma_store_3d(&tmap_c, stage_addr, x, row_base, bz);
+    tma_store_3d(&tmap_c, stage_addr + EPI_WARP_BYTES, args.n + x, row_base, bz);
+    bulk_commit();
+  }
 }
 
 // SwiGLU forward on a finished two-SM accumulator whose 256 columns are gate columns [j0, j0 + 128) followed by up columns
@@ -259,10 +254,12 @@ __device__ __forceinline__ void drain_swiglu_forward(const TcArgs& args, const C
       const int ci = part * 4 + cj;
       float a[8], u[8], m[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        a[e] = swiglu::round_bf16(__uint_as_float(ra[cj * 8 + e]));
-        u[e] = swiglu::round_bf16(__uint_as_float(ru[cj * 8 + e]));
-        m[e] = swiglu::forward_elem(a[e], u[e]);
+      for (int e = 0; e < 8; e += 2) {
+        a[e] = __uint_as_float(ra[cj * 8 + e]); a[e + 1] = __uint_as_float(ra[cj * 8 + e + 1]);
+        u[e] = __uint_as_float(ru[cj * 8 + e]); u[e + 1] = __uint_as_float(ru[cj * 8 + e + 1]);
+        swiglu::round2_bf16(a[e], a[e + 1]);
+        swiglu::round2_bf16(u[e], u[e + 1]);
+        swiglu::forward_pair(a[e], a[e + 1], u[e], u[e + 1], m[e], m[e + 1]);
       }
       *reinterpret_cast<uint4*>(rowp + ((ci ^ (lane & 7)) << 4)) = make_uint4(pack2_bf16(a[0], a[1]), pack2_bf16(a[2], a[3]), pack2_bf16(a[4], a[5]), pack2_bf16(a[6], a[7]));
       second[ci] = make_uint4(pack2_bf16(u[0], u[1]), pack2_bf16(u[2], u[3]), pack2_bf16(u[4], u[5]), pack2_bf16(u[6], u[7]));
@@ -420,15 +417,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 //   empty[s]  (each CTA's copy) the MMA thread's commit reaches both copies
 //   tfull[a]  (each CTA's copy) likewise; tempty[a] (even CTA's copy) collects the 16 epilogue warps of both CTAs
 // EPI selects the epilogue compiled in (kernels of their own, so the plain products keep their registers and their ring):
-// 0 plain; 1 SwiGLU backward (SwigluGrad): each epilogue warp has an 8 KB input box pair for a and u, filled by TMA one step
-// ahead of its use, and the operand ring is four stages deep to make room; 2 SwiGLU forward (SwigluForward).
+// 0 plain; 1 SwiGLU backward (SwigluGrad): two staging boxes per epilogue warp and a five-stage ring; 2 SwiGLU forward (SwigluForward).
 constexpr int BM2 = 256, BN2 = 256;
 constexpr int A2_TILE_BYTES = 128 * BK * 2, B2_TILE_BYTES = 128 * BK * 2, STAGE2_BYTES = A2_TILE_BYTES + B2_TILE_BYTES;
-constexpr int IN_WARP_BYTES = 2 * EPI_WARP_BYTES;
-__host__ __device__ constexpr int stages2(int epi) { return epi == 1 ? 4 : 6; }
-__host__ __device__ constexpr int smem2_bytes(int epi) { return stages2(epi) * STAGE2_BYTES + 1024 + EPI_STAGE_BYTES + (epi == 1 ? EPI_WARPS * IN_WARP_BYTES : 0) + 256; }
+// The backward epilogue has two staging boxes per warp (a and u come in through them, g_a and g_u leave through them) and a
+// five-stage ring; the ring's depth matters more than anything else here: with three stages the main loop alone took 12.2k cycles per
+// tile of 12 k-blocks against about 7.5k with six (a TMA load from L2 takes 2-3k cycles; a stage is consumed in 512).
+__host__ __device__ constexpr int stages2(int epi) { return epi == 1 ? 5 : 6; }
+__host__ __device__ constexpr int epi_boxes(int epi) { return epi == 1 ? 2 : 1; }
+__host__ __device__ constexpr int smem2_bytes(int epi) { return stages2(epi) * STAGE2_BYTES + 1024 + epi_boxes(epi) * EPI_STAGE_BYTES + 256; }
 static_assert(smem2_bytes(0) <= 232448 && smem2_bytes(1) <= 232448 && smem2_bytes(2) <= 232448, "shared memory per CTA");
-static_assert(8 * (2 * stages2(0) + 5 + EPI_WARPS) <= 256, "barrier area");
+static_assert(8 * (2 * stages2(0) + 5) <= 256, "barrier area");
 
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -439,13 +438,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;               // the same offset in both CTAs (same kernel, same layout)
   constexpr int STAGES2 = stages2(EPI);
   const uint32_t epi_base = tiles_base + STAGES2 * STAGE2_BYTES;
-  const uint32_t in_base = epi_base + EPI_STAGE_BYTES;               // EPI 1: the epilogue warps' input boxes (1024-aligned too)
-  const uint32_t bar_base = in_base + (EPI == 1 ? EPI_WARPS * IN_WARP_BYTES : 0);
+  const uint32_t bar_base = epi_base + epi_boxes(EPI) * EPI_STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES2 + 2 + a); };
-  auto in_bar = [&](int w) { return bar_base + 8u * (2 * STAGES2 + 5 + w); };   // EPI 1: one per epilogue warp
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bar_base - raw) + 8 * (2 * STAGES2 + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* epi_ptr = smem_raw + (epi_base - raw);
@@ -460,7 +457,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * EPI_WARPS); }
-    if (EPI == 1) for (int w = 0; w < EPI_WARPS; ++w) mbar_init(in_bar(w), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -532,29 +528,32 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
     const int quarter = warp & 3;
     const int col_begin = ((warp - 2) >> 2) * (BN2 / 2), col_end = col_begin + BN2 / 2;
-    uint8_t* stage_bytes = epi_ptr + (warp - 2) * EPI_WARP_BYTES;
-    const uint32_t stage_addr = epi_base + (warp - 2) * EPI_WARP_BYTES;
+    uint8_t* stage_bytes = epi_ptr + (warp - 2) * epi_boxes(EPI) * EPI_WARP_BYTES;
+    const uint32_t stage_addr = epi_base + (warp - 2) * epi_boxes(EPI) * EPI_WARP_BYTES;
     auto unit_tile = [&](int u, int* tm, int* tn, int* split, int* bz) {
       *bz = u / units_per_matrix;
       const int ub = u - *bz * units_per_matrix, tile = ub / args.splits;
       *split = ub % args.splits;
       *tm = args.tiles_n_fast ? tile / tiles_n : tile % tiles_m; *tn = args.tiles_n_fast ? tile % tiles_n : tile / tiles_m;
     };
-    // EPI 1: a and u for rows [32 quarter, +32) x 64 columns of a unit arrive in this warp's input boxes one step before they are
-    // needed: the first step's while the unit's products still run, the second step's while the first is worked on (the boxes are
-    // free again as soon as their contents are in registers). Out-of-range rows and columns read as zero and are clipped on the way out.
-    const uint32_t in_addr = in_base + (warp - 2) * IN_WARP_BYTES, my_in_bar = in_bar(warp - 2);
-    const uint8_t* in_ptr = smem_raw + (in_addr - raw);
-    uint32_t in_count = 0;
+    // EPI 1: a and u for rows [32 quarter, +32) x 64 columns of a step are read one step ahead with plain 16-byte loads, eight lanes
+    // to a row (whole 128-byte lines; a lane per row would touch 32 lines per instruction and bind on L1 wavefronts), and wait in
+    // registers: the first step's while the unit's products still run, the next one's while this one is worked on. Out-of-range
+    // rows and columns read as zero and are clipped on the way out.
+    uint4 la[8], lu[8];
     auto fetch_inputs = [&](int u, int c0) {
       int tm, tn, split, bz;
       unit_tile(u, &tm, &tn, &split, &bz);
-      const int x = tn * BN2 + c0, y = tm * BM2 + (int)rank * 128 + quarter * 32;
-      mbar_expect_tx(my_in_bar, IN_WARP_BYTES);
-      tma_load_3d(in_addr, &tmap_m, my_in_bar, x, y, bz);
-      tma_load_3d(in_addr + EPI_WARP_BYTES, &tmap_m, my_in_bar, args.n + x, y, bz);
+      const int x = tn * BN2 + c0, y = tm * BM2 + (int)rank * 128 + quarter * 32 + (lane >> 3);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const bool in = y + 4 * k < args.m && x < args.n;
+        const uint4* p = reinterpret_cast<const uint4*>(args.sw_au + (in ? (int64_t)(y + 4 * k) * args.sw_ld + x : 0)) + (lane & 7);
+        la[k] = make_uint4(0, 0, 0, 0); lu[k] = make_uint4(0, 0, 0, 0);
+        if (in) { la[k] = __ldg(p); lu[k] = __ldg(p + args.n / 8); }
+      }
     };
-    if (EPI == 1 && lane == 0 && pair < units) fetch_inputs(pair, col_begin);
+    if (EPI == 1 && pair < units) fetch_inputs(pair, col_begin);
     uint32_t local = 0;
     for (int u = pair; u < units; u += npairs, ++local) {
       int tm, tn, split, bz;
@@ -566,27 +565,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
       if constexpr (EPI == 2) drain_swiglu_forward(args, tmap_c, tmap_m, tsrc, row_base, tn * 128, bz, lane, (warp - 2) >> 2, stage_bytes, stage_addr);
       else if constexpr (EPI == 1) {
-        bool ok = true;
 #pragma unroll 1
         for (int c0 = col_begin; c0 < col_end; c0 += 64) {
-          if (!mbar_wait(my_in_bar, in_count & 1, args.fault, abort_flag)) { ok = false; break; }
-          ++in_count;
-          uint4 qa[8], qu[8];
-          const uint8_t* rin = in_ptr + lane * 128;
-#pragma unroll
-          for (int ci = 0; ci < 8; ++ci) {
-            qa[ci] = *reinterpret_cast<const uint4*>(rin + ((ci ^ (lane & 7)) << 4));
-            qu[ci] = *reinterpret_cast<const uint4*>(rin + EPI_WARP_BYTES + ((ci ^ (lane & 7)) << 4));
-          }
-          fence_async_smem();                    // the reads above come before the next fill of the boxes
+          if (lane == 0) bulk_wait_read();       // the previous step's two boxes have left the staging rows
           __syncwarp();
-          if (lane == 0) {
-            if (c0 + 64 < col_end) fetch_inputs(u, c0 + 64);
-            else if (u + npairs < units) fetch_inputs(u + npairs, col_begin);
+          // the fetched 16-byte pieces go to their rows' places in the boxes (row 4 k + lane / 8, piece lane % 8): lane = row from here on
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int row = 4 * k + (lane >> 3), off = row * 128 + (((lane & 7) ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(stage_bytes + off) = la[k];
+            *reinterpret_cast<uint4*>(stage_bytes + EPI_WARP_BYTES + off) = lu[k];
           }
-          drain_swiglu_backward(args, tmap_c, tsrc, row_base, tn * BN2 + c0, c0, bz, lane, qa, qu, stage_bytes, stage_addr);
+          __syncwarp();
+          if (c0 + 64 < col_end) fetch_inputs(u, c0 + 64);
+          else if (u + npairs < units) fetch_inputs(u + npairs, col_begin);
+          drain_swiglu_backward(args, tmap_c, tsrc, row_base, tn * BN2 + c0, c0, bz, lane, stage_bytes, stage_addr);
         }
-        if (!ok) break;
       }
       else drain_tile(args, tmap_c, tsrc, row_base, tn * BN2, split, bz, lane, col_begin, col_end, stage_bytes, stage_addr);
       fence_before();
@@ -780,6 +774,7 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
   args.splits = splits; args.kblocks_per_split = per; args.partial = nullptr; args.fault = be->fault_dev; args.batch = (int)batch;
   args.ns_src = combine ? (const bf16*)combine->src : nullptr; args.ns_ld = combine ? combine->src_ld : 0; args.ns_bs = combine ? combine->src_bs : 0;
   args.ns_src_mul = combine ? combine->src_mul : 0.0f; args.ns_acc_mul = combine ? combine->acc_mul : 0.0f;
+  args.sw_au = swiglu_grad ? (const bf16*)swiglu_grad->au : nullptr; args.sw_ld = swiglu_grad ? swiglu_grad->ld : 0;
   args.sw_f = swiglu_fwd ? (int)(n / 2) : 0;
   if (splits > 1) {
     void* ws = nullptr;
@@ -798,11 +793,10 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
     return ojc_fail(OJC_ERR_UNSUPPORTED, op, "a batched product needs the tile-store epilogue");
   }
   CUtensorMap tm = tc;   // the SwiGLU forward epilogue's third output
-  if (swiglu_grad) OJC_TRY(make_tmap(be, op, &tm, swiglu_grad->au, (uint64_t)(2 * n), (uint64_t)m, (uint64_t)swiglu_grad->ld, 64, 32));   // a and u, fetched box by box
   if (swiglu_fwd) OJC_TRY(make_tmap(be, op, &tm, swiglu_fwd->m, (uint64_t)(n / 2), (uint64_t)m, (uint64_t)swiglu_fwd->ldm, 64, 32));
   int grid = tiles * splits < workers ? tiles * splits : workers;
   if (two_sm) grid *= 2;
-  ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k * (double)batch};
+  ojc_backend::GemmSample sample{nullptr, nullptr, 2.0 * (double)m * (double)n * (double)k * (double)batch, swiglu_grad != nullptr || swiglu_fwd != nullptr};
   if (be->profile_gemm) {
     if (!be->event_pool.empty()) { sample.start = be->event_pool.back().first; sample.stop = be->event_pool.back().second; be->event_pool.pop_back(); }
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }

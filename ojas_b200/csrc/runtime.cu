@@ -254,20 +254,37 @@ ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable) {
   return OJC_OK;
 }
 
-ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches) {
+ojc_status ojc_profile_gemm_read_split(ojc_backend* be, double* plain_ms, double* plain_flops, uint64_t* plain_launches, double* epilogue_ms, double* epilogue_flops,
+                                       uint64_t* epilogue_launches) {
   OJC_ALIVE(be, "profile_gemm_read");
   OJC_CUDA(be, cudaStreamSynchronize(be->stream), "profile_gemm_read");
-  double ms = 0.0, flops = 0.0;
+  double ms[2] = {0.0, 0.0}, flops[2] = {0.0, 0.0};
+  uint64_t count[2] = {0, 0};
   for (auto& s : be->gemm_samples) {
     float t = 0.0f;
-    if (cudaEventElapsedTime(&t, s.start, s.stop) == cudaSuccess) ms += t; else cudaGetLastError();
-    flops += s.flops;
+    const int k = s.with_epilogue ? 1 : 0;
+    if (cudaEventElapsedTime(&t, s.start, s.stop) == cudaSuccess) ms[k] += t; else cudaGetLastError();
+    flops[k] += s.flops;
+    ++count[k];
     be->event_pool.emplace_back(s.start, s.stop);
   }
-  if (total_ms) *total_ms = ms;
-  if (total_flops) *total_flops = flops;
-  if (launches) *launches = be->gemm_samples.size();
+  if (plain_ms) *plain_ms = ms[0];
+  if (plain_flops) *plain_flops = flops[0];
+  if (plain_launches) *plain_launches = count[0];
+  if (epilogue_ms) *epilogue_ms = ms[1];
+  if (epilogue_flops) *epilogue_flops = flops[1];
+  if (epilogue_launches) *epilogue_launches = count[1];
   be->gemm_samples.clear();
+  return OJC_OK;
+}
+
+ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches) {
+  double ms[2], flops[2];
+  uint64_t count[2];
+  OJC_TRY(ojc_profile_gemm_read_split(be, &ms[0], &flops[0], &count[0], &ms[1], &flops[1], &count[1]));
+  if (total_ms) *total_ms = ms[0] + ms[1];
+  if (total_flops) *total_flops = flops[0] + flops[1];
+  if (launches) *launches = count[0] + count[1];
   return OJC_OK;
 }
 
