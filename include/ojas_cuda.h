@@ -91,6 +91,7 @@ uint64_t ojc_kernel_launches(ojc_backend* be);                                  
  *      2*m*n*k and the launch count since the last read, and resets them. */
 ojc_status ojc_sdpa_forward_variant(int32_t variant);    /* attention kernels on the tensor cores. 0: the library's choice; 1: one CTA per tile (for timing the persistent kernels against it); 2: the 64-wide persistent kernels on at most three CTAs (tests: several tiles per CTA on small shapes); 3: the 128-wide backward kernels on at most three CTAs (likewise); 4: the 64-wide backward kernels by their own rule; 5: the 128-wide backward kernels at any head_dim */
 ojc_status ojc_mlp_epilogue_variant(int32_t variant);    /* the step driver's MLP backward under bf16 autocast. 0: the library's choice (SwiGLU's forward runs in the epilogue of the gate/up product and its backward in that of the down projection's input-gradient product, where the shapes allow); 1: kernels of their own after the products (tests: both give the same bits) */
+ojc_status ojc_ce_rows_variant(int32_t variant);         /* the fused cross-entropy's row kernel under bf16 autocast. 0: the library's choice (rows that fit twice in an SM's shared memory are worked on there: persistent CTAs streaming rows through two buffers for tiles of at least two rows per SM, else a CTA per row); 1: always the form that re-reads the row from L2; 2: always a CTA per row (tests: all three give the same bits) */
 ojc_status ojc_profile_gemm(ojc_backend* be, int32_t enable);
 ojc_status ojc_profile_gemm_read(ojc_backend* be, double* total_ms, double* total_flops, uint64_t* launches);
 /* the same totals in two parts: the plain products, and the launches that also ran SwiGLU in their epilogue (they move 2-3x the bytes of the

@@ -13,6 +13,7 @@
 #include "dispatch.cuh"
 #include "gemm.cuh"
 #include "linear.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -164,6 +165,9 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& t, float (&v)[8]) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
 }
+constexpr size_t CE_ROW_SMEM_MAX = 112 * 1024;   // two such rows and the reduction scratch fit in an SM
+int g_ce_rows_variant = 0;                       // ojc_ce_rows_variant: 0 the library's choice, 1 always the form that keeps the row in L2, 2 a CTA per row with the row in shared memory
+
 __global__ void __launch_bounds__(512, 2)
 ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
                             const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
@@ -239,6 +243,222 @@ ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_
   if (threadIdx.x == 0) {
     const float gt = collapsed ? -(other * inv) / denom : (ex2_fast(fmaf(picked, L2E, -mx2)) * inv) / denom - 1.0f / denom;
     z[target] = __float2bfloat16_rn(gt * seed);
+  }
+}
+
+// The same kernel with the row held in shared memory: a row of the 124M head (50304 bf16 = 98.25 KB) fits twice in an SM, so the row
+// crosses the SM's memory port once in each direction (the form above reads it three times and writes it twice through L2, which is
+// what bounded it: 1.16 GB in and 1.65 GB out per 8192-row tile against 0.82 GB each way here). The maximum is taken while the row
+// is copied in, the exponentials replace the logits in shared memory, and the gradient goes straight out. The same arithmetic on the
+// same elements in the same per-thread order as the form above, so the same bits.
+__global__ void __launch_bounds__(512, 2)
+ce_rows_smem_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
+                         const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
+  extern __shared__ __align__(16) uint8_t row_raw[];
+  __shared__ float red[32];
+  bf16* srow = reinterpret_cast<bf16*>(row_raw);
+  constexpr float L2E = 1.4426950408889634f;
+  const int64_t row = blockIdx.x;
+  bf16* z = logits + row * ld;
+  const uint32_t target = targets[row];
+  const int64_t v8 = vocab >> 3;            // whole 16-byte groups; the tail (vocab % 8) is handled by scalar code
+  if ((has_ignore && target == ignore) || target >= vocab) {
+    if (threadIdx.x == 0) terms[row] = 0.0f;
+    if (want_grad) {
+      for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(0u, 0u, 0u, 0u);
+      for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) z[c] = __float2bfloat16_rn(0.0f);
+    }
+    return;
+  }
+  const float picked = __bfloat162float(z[target]);
+  // pass 1: copy the row in, taking the maximum on the way
+  float tm = -INFINITY;
+#pragma unroll 4
+  for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
+    const uint4 t = *reinterpret_cast<const uint4*>(z + 8 * i);
+    *reinterpret_cast<uint4*>(srow + 8 * i) = t;
+    float v[8];
+    unpack_bf16x8(t, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) tm = fmaxf(tm, v[e]);
+  }
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) { srow[c] = z[c]; tm = fmaxf(tm, __bfloat162float(srow[c])); }
+  const float mx = block_max(tm, red);      // (its barriers also make the copied row visible to every thread)
+  const float mx2 = mx * L2E;
+  // pass 2: one ex2 per logit, summed in f32; the bf16 exponentials replace the logits in shared memory
+  float ts = 0.0f;
+#pragma unroll 2
+  for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
+    float v[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(srow + 8 * i), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { v[e] = ex2_fast(fmaf(v[e], L2E, -mx2)); ts += v[e]; }
+    *reinterpret_cast<uint4*>(srow + 8 * i) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+  }
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) {
+    const float e = ex2_fast(fmaf(__bfloat162float(srow[c]), L2E, -mx2));
+    ts += e;
+    srow[c] = __float2bfloat16_rn(e);
+  }
+  const float sum = block_sum(ts, red);
+  if (!(isfinite(mx2) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
+  float other = 0.0f;
+  bool collapsed = false;
+  if (picked == mx && sum == 1.0f) {        // the target-excluded form for a collapsed row: the others' exponentials (the row holds them now)
+    float o = 0.0f;
+    for (int64_t c = threadIdx.x; c < vocab; c += blockDim.x) if (c != target) o += __bfloat162float(srow[c]);
+    other = block_sum(o, red);
+    collapsed = other > 0.0f;
+  }
+  if (threadIdx.x == 0) terms[row] = collapsed ? log1pf(other) : (mx + logf(sum) - picked);
+  if (!want_grad) return;
+  const float denom = (float)valid[0];
+  const float inv = collapsed ? 1.0f / (1.0f + other) : 1.0f / sum;
+  const float k = inv / denom * seed;
+  // pass 3: exponentials -> gradient, one multiply each, out to the logits' place
+#pragma unroll 4
+  for (int64_t i = threadIdx.x; i < v8; i += blockDim.x) {
+    float v[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(srow + 8 * i), v);
+    *reinterpret_cast<uint4*>(z + 8 * i) = make_uint4(pack_bf16x2(v[0] * k, v[1] * k), pack_bf16x2(v[2] * k, v[3] * k), pack_bf16x2(v[4] * k, v[5] * k), pack_bf16x2(v[6] * k, v[7] * k));
+  }
+  for (int64_t c = 8 * v8 + threadIdx.x; c < vocab; c += blockDim.x) z[c] = __float2bfloat16_rn(__bfloat162float(srow[c]) * k);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const float gt = collapsed ? -(other * inv) / denom : (ex2_fast(fmaf(picked, L2E, -mx2)) * inv) / denom - 1.0f / denom;
+    z[target] = __float2bfloat16_rn(gt * seed);
+  }
+}
+
+// The streaming form, for whole tiles of such rows: one persistent CTA per SM with two row buffers. A seventeenth warp moves the rows:
+// cp.async.bulk brings row k + 2 into a buffer as soon as the bulk store of row k has read it, so the loads and stores of neighbouring
+// rows are in flight while the sixteen compute warps work on the row between them; the compute warps never touch global memory for
+// the row itself (the gradient is formed in place in shared memory, target column included, and leaves as one bulk store). The same
+// arithmetic on the same elements in the same per-thread order as the two forms above, so the same bits. Needs vocab % 8 == 0.
+__device__ __forceinline__ void ce_bar_compute() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+__device__ __forceinline__ float ce_block_sum16(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  ce_bar_compute();
+  if (lane == 0) red[warp] = v;
+  ce_bar_compute();
+  return warp_sum(lane < 16 ? red[lane] : 0.0f);
+}
+__device__ __forceinline__ float ce_block_max16(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  ce_bar_compute();
+  if (lane == 0) red[warp] = v;
+  ce_bar_compute();
+  return warp_max(lane < 16 ? red[lane] : -INFINITY);
+}
+constexpr int CE_STREAM_THREADS = 544;
+__global__ void __launch_bounds__(CE_STREAM_THREADS, 1)
+ce_rows_stream_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t rows, int64_t vocab, int has_ignore, uint32_t ignore,
+                           const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
+  extern __shared__ __align__(128) uint8_t row_raw[];
+  __shared__ float red[32];
+  __shared__ __align__(8) uint64_t bars[4];          // full[2] (bytes of a row have landed), done[2] (the compute warps are through with it)
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  constexpr float L2E = 1.4426950408889634f;
+  const uint32_t row_bytes = (uint32_t)vocab * 2u, stride = (row_bytes + 127u) & ~127u;
+  const uint32_t buf0 = tc::smem_u32(row_raw), bar0 = tc::smem_u32(bars);
+  if (threadIdx.x == 0) {
+    tc::mbar_init(bar0, 1); tc::mbar_init(bar0 + 8, 1); tc::mbar_init(bar0 + 16, 512); tc::mbar_init(bar0 + 24, 512);
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int64_t v8 = vocab >> 3;
+  if (threadIdx.x >= 512) {
+    // ------------------------------------------------------------ the rows' mover
+    if (threadIdx.x == 512) {
+      auto load = [&](int64_t row, uint32_t b) {
+        tc::mbar_expect_tx(bar0 + 8 * b, row_bytes);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(buf0 + b * stride), "l"(logits + row * ld), "r"(row_bytes),
+                     "r"(bar0 + 8 * b) : "memory");
+      };
+      const int64_t first = blockIdx.x, step = gridDim.x;
+      if (first < rows) load(first, 0);
+      if (first + step < rows) load(first + step, 1);
+      uint32_t k = 0;
+      for (int64_t row = first; row < rows; row += step, ++k) {
+        const uint32_t b = k & 1;
+        if (!tc::mbar_wait(bar0 + 16 + 8 * b, (k >> 1) & 1, fault, abort_flag)) break;
+        if (want_grad) {
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(logits + row * ld), "r"(buf0 + b * stride), "r"(row_bytes) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");       // the buffer may be refilled
+        }
+        if (row + 2 * step < rows) load(row + 2 * step, b);
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+    return;
+  }
+  // ------------------------------------------------------------ the compute warps
+  const float denom = (float)valid[0];
+  uint32_t k = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++k) {
+    const uint32_t b = k & 1;
+    bf16* srow = reinterpret_cast<bf16*>(row_raw + b * stride);
+    const uint32_t target = targets[row];
+    if (!tc::mbar_wait(bar0 + 8 * b, (k >> 1) & 1, fault, abort_flag)) break;
+    if ((has_ignore && target == ignore) || target >= vocab) {
+      if (threadIdx.x == 0) terms[row] = 0.0f;
+      if (want_grad) for (int64_t i = threadIdx.x; i < v8; i += 512) *reinterpret_cast<uint4*>(srow + 8 * i) = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      const float picked = __bfloat162float(srow[target]);
+      float tm = -INFINITY;
+#pragma unroll 2
+      for (int64_t i = threadIdx.x; i < v8; i += 512) {
+        float v[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(srow + 8 * i), v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) tm = fmaxf(tm, v[e]);
+      }
+      const float mx = ce_block_max16(tm, red);
+      const float mx2 = mx * L2E;
+      float ts = 0.0f;
+#pragma unroll 2
+      for (int64_t i = threadIdx.x; i < v8; i += 512) {
+        float v[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(srow + 8 * i), v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { v[e] = ex2_fast(fmaf(v[e], L2E, -mx2)); ts += v[e]; }
+        *reinterpret_cast<uint4*>(srow + 8 * i) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+      }
+      const float sum = ce_block_sum16(ts, red);
+      if (!(isfinite(mx2) && isfinite(sum) && sum > 0.0f)) { if (threadIdx.x == 0) { raise_fault(fault, OP_CE); terms[row] = 0.0f; } }
+      float other = 0.0f;
+      bool collapsed = false;
+      if (picked == mx && sum == 1.0f) {
+        float o = 0.0f;
+        for (int64_t c = threadIdx.x; c < vocab; c += 512) if (c != target) o += __bfloat162float(srow[c]);
+        other = ce_block_sum16(o, red);
+        collapsed = other > 0.0f;
+      }
+      if (threadIdx.x == 0) terms[row] = collapsed ? log1pf(other) : (mx + logf(sum) - picked);
+      if (want_grad) {
+        const float inv = collapsed ? 1.0f / (1.0f + other) : 1.0f / sum;
+        const float kk = inv / denom * seed;
+#pragma unroll 2
+        for (int64_t i = threadIdx.x; i < v8; i += 512) {
+          float v[8];
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(srow + 8 * i), v);
+          *reinterpret_cast<uint4*>(srow + 8 * i) =
+              make_uint4(pack_bf16x2(v[0] * kk, v[1] * kk), pack_bf16x2(v[2] * kk, v[3] * kk), pack_bf16x2(v[4] * kk, v[5] * kk), pack_bf16x2(v[6] * kk, v[7] * kk));
+        }
+        ce_bar_compute();
+        if (threadIdx.x == 0) {
+          const float gt = collapsed ? -(other * inv) / denom : (ex2_fast(fmaf(picked, L2E, -mx2)) * inv) / denom - 1.0f / denom;
+          srow[target] = __float2bfloat16_rn(gt * seed);
+        }
+      }
+    }
+    tc::fence_async_smem();                   // the row's new contents, before the bulk store reads them
+    tc::mbar_arrive(bar0 + 16 + 8 * b);
   }
 }
 
@@ -320,8 +540,25 @@ ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const vo
       OJC_TRY(gemm_auto(be, op, a, b, logits, bf ? OJC_BF16 : OJC_F32, ldl, r, vocab, dim, 1.0f, false, nullptr));
       void* g = gbuf;
       if (bf) {
-        ce_rows_inplace_bf16_kernel<<<(unsigned)r, 512, 0, be->stream>>>((bf16*)logits, ldl, targets + r0, vocab, has_ignore, ignore, valid, terms + r0, want ? 1 : 0, seed,
-                                                                        be->fault_dev);
+        // a row that fits twice in an SM's shared memory is worked on there; wider ones stay in L2
+        const size_t row_bytes = (size_t)((vocab * 2 + 15) / 16 * 16);
+        if (row_bytes <= CE_ROW_SMEM_MAX && g_ce_rows_variant == 0 && vocab % 8 == 0 && r >= 2 * be->sm_count) {
+          static PerDeviceFlag attr2_of;
+          bool& attr2 = attr2_of[be->device];
+          const size_t stride = (row_bytes + 127) / 128 * 128;
+          if (!attr2) { OJC_CUDA(be, cudaFuncSetAttribute(ce_rows_stream_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * CE_ROW_SMEM_MAX)), op); attr2 = true; }
+          ce_rows_stream_bf16_kernel<<<(unsigned)be->sm_count, CE_STREAM_THREADS, 2 * stride, be->stream>>>((bf16*)logits, ldl, targets + r0, r, vocab, has_ignore, ignore, valid,
+                                                                                                     terms + r0, want ? 1 : 0, seed, be->fault_dev);
+        } else if (row_bytes <= CE_ROW_SMEM_MAX && g_ce_rows_variant != 1) {
+          static PerDeviceFlag attr_of;
+          bool& attr = attr_of[be->device];
+          if (!attr) { OJC_CUDA(be, cudaFuncSetAttribute(ce_rows_smem_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CE_ROW_SMEM_MAX), op); attr = true; }
+          ce_rows_smem_bf16_kernel<<<(unsigned)r, 512, row_bytes, be->stream>>>((bf16*)logits, ldl, targets + r0, vocab, has_ignore, ignore, valid, terms + r0, want ? 1 : 0,
+                                                                               seed, be->fault_dev);
+        } else {
+          ce_rows_inplace_bf16_kernel<<<(unsigned)r, 512, 0, be->stream>>>((bf16*)logits, ldl, targets + r0, vocab, has_ignore, ignore, valid, terms + r0, want ? 1 : 0, seed,
+                                                                          be->fault_dev);
+        }
         OJC_LAUNCHED(be, op);
         g = logits;
       } else {
@@ -346,6 +583,8 @@ ojc_status linear_ce_impl(ojc_backend* be, const void* x, int32_t x_dt, const vo
 }
 
 extern "C" {
+
+ojc_status ojc_ce_rows_variant(int32_t variant) { g_ce_rows_variant = variant == 1 || variant == 2 ? variant : 0; return OJC_OK; }
 
 static ojc_status ce_args(const char* op, const ojc_tensor* logits, const ojc_tensor* targets, int64_t* rows, int64_t* vocab) {
   OJC_TRY(check_tensor(op, "logits", logits)); OJC_TRY(check_tensor(op, "targets", targets));

@@ -336,6 +336,40 @@ def test_fused_linear_cross_entropy_bf16_tier(be):
     assert rel(gx.numpy(), ogx) <= 1e-2 and rel(gw.numpy(), ogw) <= 1e-2  # d(logits) is rounded to bf16 before the two GEMMs
 
 
+@pytest.mark.parametrize("vocab,rows,chunk", [(2048, 96, 40), (50304, 96, 40), (1000, 96, 40), (4096, 1000, 500), (50304, 700, 0)])
+def test_fused_cross_entropy_row_kernels_give_the_same_bits(be, vocab, rows, chunk):
+    """Under bf16 autocast the fused loss turns its bf16 logits tile into the gradient row by row. Rows that fit twice in an SM's shared
+    memory (the 124M head's 50304 columns do) are worked on there: by persistent CTAs that stream rows through two buffers with bulk
+    copies when a tile has at least two rows per SM (the last two cases; three or more rows per CTA, so buffers are reused), else by a
+    CTA per row; wider rows are re-read from L2. Same arithmetic in the same order: the loss and both gradients must be equal bit for
+    bit, also with ignored and collapsed rows and a width that is not a multiple of 8."""
+    import ctypes as C
+    from ojas_b200 import DType
+    from ojas_b200._lib import lib
+    dim = 64
+    x, w = orc.round_bf16(rnd(11, (rows, dim))), orc.round_bf16(rnd(12, (vocab, dim), 0.3))
+    x[5] *= 40.0                                         # a row whose softmax collapses onto one column
+    x = orc.round_bf16(x)
+    rng = orc.SplitMix64(13)
+    targets = np.array([rng.below(vocab) for _ in range(rows)], np.uint32)
+    targets[5] = int(np.argmax(x[5] @ w.T))
+    targets[7] = 0xFFFFFFFF                              # ignored
+    dx, dw, dt = be.upload(x, DType.BF16), be.upload(w, DType.BF16), be.upload(targets)
+    out = []
+    try:
+        for variant in (0, 1, 2):
+            assert lib.ojc_ce_rows_variant(C.c_int32(variant)) == 0
+            launches = be.kernel_launches()
+            loss, gx, gw = be.linear_cross_entropy_mean(dx, dw, dt, chunk=(chunk, 0), grad_input_dtype=DType.F32, ignore_index=0xFFFFFFFF)
+            out.append((loss.numpy().copy(), gx.numpy().copy(), gw.numpy().copy(), be.kernel_launches() - launches))
+    finally:
+        lib.ojc_ce_rows_variant(C.c_int32(0))
+    assert out[0][3] == out[1][3] == out[2][3]
+    for other in out[1:]:
+        for a, b_ in zip(out[0][:3], other[:3]):
+            assert np.array_equal(a.view(np.uint32), b_.view(np.uint32)) and np.isfinite(a).all()
+
+
 def test_argmax_rows_is_bit_exact_with_ties_to_the_lowest_column(be):
     x = rnd(1, (300, 517))
     x[3, 10] = x[3, 400] = 9.0
