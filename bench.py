@@ -238,6 +238,13 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))   # barriers and the max over ranks; the step's exchange is the library's own
     be = CudaBackend(local_rank, 170 << 30)
+    if args.kernel_variants:
+        import ctypes
+        from ojas_b200._lib import lib
+        switches = {"ce_rows": lib.ojc_ce_rows_variant, "mlp_epilogue": lib.ojc_mlp_epilogue_variant, "sdpa": lib.ojc_sdpa_forward_variant}
+        for item in args.kernel_variants.split(","):
+            name, _, value = item.partition("=")
+            switches[name.strip()](ctypes.c_int32(int(value)))
     conf = CONFIGS[args.config]
     spec = ModelSpec(**conf["spec"])
     seq = conf["seq"]
@@ -342,7 +349,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         "metric": "nanolab_gpt_124m_train_tokens_per_s" if args.config == "124m" else "nanolab_gpt_1p7b_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": warm,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(world, args.optimizer, args.config) if batch == conf["batch"] else {"workload": f"PROFILER CASE, not the benchmark workload: micro-batch {batch}"},
+        "config": workload_config(world, args.optimizer, args.config) if batch == conf["batch"] and not args.kernel_variants else
+                  {"workload": f"PROFILER CASE, not the benchmark workload: micro-batch {batch}, kernel variants '{args.kernel_variants}'"},
         "mfu": value * fpt / (world * pk["bf16_tflops"] * 1e12), "mfu_vs_sustained": value * fpt / (world * pk["bf16_tflops_sustained"] * 1e12),
         "flops_per_token": fpt, "final_loss": rep.loss if rep else None,
         "e2e": {"value": tokens * args.steps / (e2e_ms / 1000.0) if e2e_ms else None, "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 4,
@@ -437,6 +445,8 @@ def main() -> None:
     ap.add_argument("--no-second-recipe", action="store_true", help="skip the short measurement of the other optimizer recipe (Muon hybrid beside an AdamW headline)")
     ap.add_argument("--no-sdpa", action="store_true", help="skip the standalone attention case [8,16,4096,128]")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (used for profiler captures)")
+    ap.add_argument("--kernel-variants", default="", help="profiler captures only: comma-separated name=value pairs passed to the library's kernel-selection "
+                    "switches (ce_rows, mlp_epilogue, sdpa), e.g. ce_rows=1 to capture the cross-entropy row kernel that re-reads its row from L2; such a line names itself")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
