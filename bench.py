@@ -37,8 +37,8 @@ CONFIGS = {
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one full-size GEMM launch of the step, the q/k/v projection
-# [32768 x 768] x [768 x 2304] -> bf16 (profiles/gemm_tc2_kernel_qkv_32768x768x2304.md): 53.9 MB read + 96.7 MB written
-# against 205.0 MB of algorithmic bytes (the tail of the output is still in L2 when the kernel ends).
+# [32768 x 768] x [768 x 2304] -> bf16, from one ncu capture of `python -m ojas_b200.opbench gemm 32768 768 2304`:
+# 53.9 MB read + 96.7 MB written against 205.0 MB of algorithmic bytes (the tail of the output is still in L2 when the kernel ends).
 GEMM_TRAFFIC_BYTES_PER_LAUNCH = 150_663_424
 GEMM_TRAFFIC_LAUNCH = "q/k/v projection 32768x768x2304 bf16: algorithmic 205.0 MB per launch"
 
