@@ -171,6 +171,7 @@ int g_ce_rows_variant = 0;                       // ojc_ce_rows_variant: 0 the l
 __global__ void __launch_bounds__(512, 2)
 ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
                             const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
+  pdl_trigger();
   __shared__ float red[32];
   constexpr float L2E = 1.4426950408889634f;
   const int64_t row = blockIdx.x;
@@ -254,6 +255,7 @@ ce_rows_inplace_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_
 __global__ void __launch_bounds__(512, 2)
 ce_rows_smem_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t vocab, int has_ignore, uint32_t ignore,
                          const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
+  pdl_trigger();
   extern __shared__ __align__(16) uint8_t row_raw[];
   __shared__ float red[32];
   bf16* srow = reinterpret_cast<bf16*>(row_raw);
@@ -356,6 +358,7 @@ constexpr int CE_STREAM_THREADS = 544;
 __global__ void __launch_bounds__(CE_STREAM_THREADS, 1)
 ce_rows_stream_bf16_kernel(bf16* __restrict__ logits, int64_t ld, const uint32_t* __restrict__ targets, int64_t rows, int64_t vocab, int has_ignore, uint32_t ignore,
                            const uint32_t* __restrict__ valid, float* __restrict__ terms, int want_grad, float seed, uint32_t* fault) {
+  pdl_trigger();
   extern __shared__ __align__(128) uint8_t row_raw[];
   __shared__ float red[32];
   __shared__ __align__(8) uint64_t bars[4];          // full[2] (bytes of a row have landed), done[2] (the compute warps are through with it)

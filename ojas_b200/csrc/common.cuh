@@ -130,6 +130,9 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 // Block-wide sum in a fixed order (warp butterflies, then warp 0 over the warp
 // partials): every thread returns the total. `red` holds >= 32 floats.
+// Lets a kernel launched after this one with programmatic stream serialization (the tensor-core GEMMs are) set itself up on SMs
+// this kernel's CTAs have already left; such a kernel touches no global memory before this one is complete. A no-op otherwise.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ float block_sum(float v, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
   v = warp_sum(v);

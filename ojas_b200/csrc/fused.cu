@@ -39,6 +39,7 @@ template <int TPR> __device__ __forceinline__ float row_sum(float v) {
 template <int TPR, int HL>
 __global__ void qk_norm_rope_forward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
                                             const float* __restrict__ sin_t, bf16* __restrict__ y, int64_t ys, int64_t tokens, int heads, int time, float eps) {
+  pdl_trigger();
   constexpr int DH = 16 * TPR, HALF = 8 * TPR;
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int part = (int)(gid % TPR), hsub = (int)((gid / TPR) % HL);   // HL heads side by side in a warp: one load covers HL * 128 contiguous bytes per token
@@ -78,6 +79,7 @@ template <int TPR, int HL>
 __global__ void __launch_bounds__(128, 4) qk_norm_rope_backward_kernel(const bf16* __restrict__ x, int64_t xs, const float* __restrict__ w, const float* __restrict__ cos_t,
                                              const float* __restrict__ sin_t, const bf16* __restrict__ gy, int64_t gys, bf16* __restrict__ gx, int64_t gxs,
                                              float* __restrict__ part_out, int64_t tokens, int heads, int time, float eps) {
+  pdl_trigger();
   constexpr int DH = 16 * TPR, HALF = 8 * TPR;
   extern __shared__ float red[];  // [threads][16]
   const int part = threadIdx.x % TPR, hsub = (threadIdx.x / TPR) % HL, tok_in_block = threadIdx.x / (TPR * HL);
@@ -159,6 +161,7 @@ __global__ void fused_column_sum_kernel(const float* __restrict__ part, float* _
 // One thread per 8 contiguous values of one (row, head).
 __global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, const float* __restrict__ bias, const bf16* __restrict__ attn, bf16* __restrict__ out,
                                           float* __restrict__ scales, int64_t rows, int heads, int dh) {
+  pdl_trigger();
   const int per = dh / 8;
   const int64_t total = rows * heads * per;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -182,6 +185,7 @@ __global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, c
 // (rows are tokens b * time + t), which saves that op a pass over attn and dAttn.
 __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, const bf16* __restrict__ attn, const bf16* __restrict__ gout, bf16* __restrict__ gattn,
                                            bf16* __restrict__ gz, int zld, float* __restrict__ part_out, int64_t rows, int heads, int dh, float* __restrict__ dr, int time) {
+  pdl_trigger();
   extern __shared__ float red[];  // [warps][heads]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int per = dh / 8;                 // 16-byte chunks per head
@@ -226,6 +230,7 @@ __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, con
 // ---- row-strided forms for column slices of a wider [rows, ld] buffer (the outputs of one GEMM over concatenated weights)
 // SwiGLU: a = au[:, 0:F], u = au[:, F:2F]; same arithmetic (and bf16 rounding of silu(a)) as swiglu_forward / backward.
 __global__ void swiglu_rows_forward_kernel(const bf16* __restrict__ au, int64_t ld, bf16* __restrict__ m, int64_t rows, int f8) {
+  pdl_trigger();
   const int64_t total = rows * f8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / f8; const int c = (int)(i % f8) * 8;
@@ -237,6 +242,7 @@ __global__ void swiglu_rows_forward_kernel(const bf16* __restrict__ au, int64_t 
   }
 }
 __global__ void swiglu_rows_backward_kernel(const bf16* __restrict__ au, const bf16* __restrict__ gm, bf16* __restrict__ gau, int64_t ld, int64_t rows, int f8) {
+  pdl_trigger();
   const int64_t total = rows * f8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / f8; const int c = (int)(i % f8) * 8;
@@ -251,6 +257,7 @@ __global__ void swiglu_rows_backward_kernel(const bf16* __restrict__ au, const b
 // Value-residual blend over strided rows: y = (1-s) v + s v0, s = sigmoid(lambda).
 __global__ void vres_rows_forward_kernel(const bf16* __restrict__ v, int64_t ldv, const bf16* __restrict__ v0, int64_t ld0, const float* __restrict__ lambda,
                                          bf16* __restrict__ y, int64_t rows, int c8) {
+  pdl_trigger();
   const float s = sigmoidf_(lambda[0]);
   const int64_t total = rows * c8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -267,6 +274,7 @@ __global__ void vres_rows_forward_kernel(const bf16* __restrict__ v, int64_t ldv
 __global__ void vres_rows_backward_kernel(const bf16* __restrict__ v, int64_t ldv, const bf16* __restrict__ v0, int64_t ld0, const float* __restrict__ lambda,
                                           const bf16* __restrict__ gy, bf16* __restrict__ gv, int64_t ldg, float* __restrict__ acc, int first,
                                           double* __restrict__ part, int64_t rows, int c8) {
+  pdl_trigger();
   __shared__ float red[32];
   const float s = sigmoidf_(lambda[0]);
   const int64_t total = rows * c8;
@@ -298,6 +306,7 @@ __global__ void vres_rows_lambda_kernel(const double* __restrict__ part, int npa
 }
 // Layer 0's raw value gradient: out (strided) = bf16(acc + g), acc = the later layers' contributions (null: a plain strided copy).
 __global__ void vres_root_backward_kernel(const float* __restrict__ acc, const bf16* __restrict__ g, bf16* __restrict__ out, int64_t ldo, int64_t rows, int c8) {
+  pdl_trigger();
   const int64_t total = rows * c8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / c8; const int c = (int)(i % c8) * 8;
@@ -319,6 +328,7 @@ __global__ void vres_root_backward_kernel(const float* __restrict__ acc, const b
 template <int J>
 __global__ void rms_backward_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ gy, float* __restrict__ gx,
                                          bf16* __restrict__ gx_b, float* __restrict__ part, int64_t rows, float eps, int gx_accumulate) {
+  pdl_trigger();
   constexpr int DIM = 128 * J;
   extern __shared__ float smem[];  // [warps][DIM]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -372,6 +382,7 @@ __global__ void rms_backward_rows_kernel(const float* __restrict__ x, const floa
 template <int J>
 __global__ void rms_forward_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, bf16* __restrict__ y, float* __restrict__ copy, int64_t rows,
                                         float eps, uint32_t* fault) {
+  pdl_trigger();
   constexpr int DIM = 128 * J;
   const int lane = threadIdx.x & 31;
   float4 wv[J];

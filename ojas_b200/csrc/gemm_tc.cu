@@ -319,6 +319,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization: everything above (barriers, tensor memory) may run while the kernel before this
+  // one in the stream is still finishing on other SMs; nothing below touches global memory before that kernel is complete. The
+  // trigger lets the kernel after this one do the same with its own prologue once this one's CTAs start leaving.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -469,6 +474,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   cluster_sync_all();                                               // both CTAs' barriers exist before anyone arrives on a peer's
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization: everything above (barriers, tensor memory) may run while the kernel before this
+  // one in the stream is still finishing on other SMs; nothing below touches global memory before that kernel is complete. The
+  // trigger lets the kernel after this one do the same with its own prologue once this one's CTAs start leaving.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (each CTA loads its own halves)
@@ -604,6 +614,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 // into whole float4 groups.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, void* c, int c_bf16, int64_t ldc, int m, int n, float alpha,
                                      int accumulate, const float* __restrict__ residual) {
+  pdl_trigger();
   const int n4 = n >> 2;
   const int64_t total4 = (int64_t)m * n4, plane4 = total4;
   const float4* part4 = reinterpret_cast<const float4*>(partial);
@@ -802,10 +813,16 @@ ojc_status gemm_tc_batched(ojc_backend* be, const char* op, const GemmOperand& a
     else { OJC_CUDA(be, cudaEventCreate(&sample.start), op); OJC_CUDA(be, cudaEventCreate(&sample.stop), op); }
     OJC_CUDA(be, cudaEventRecord(sample.start, be->stream), op);
   }
-  if (swiglu_fwd) gemm_tc2_kernel<2><<<grid, NUM_THREADS, smem2_bytes(2), be->stream>>>(ta, tb, tc, tm, args);
-  else if (swiglu_grad) gemm_tc2_kernel<1><<<grid, NUM_THREADS, smem2_bytes(1), be->stream>>>(ta, tb, tc, tm, args);
-  else if (two_sm) gemm_tc2_kernel<0><<<grid, NUM_THREADS, smem2_bytes(0), be->stream>>>(ta, tb, tc, tm, args);
-  else gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, be->stream>>>(ta, tb, tc, args);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(NUM_THREADS); cfg.stream = be->stream; cfg.attrs = pdl; cfg.numAttrs = 1;
+  cudaError_t launched;
+  if (swiglu_fwd) { cfg.dynamicSmemBytes = smem2_bytes(2); launched = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<2>, ta, tb, tc, tm, args); }
+  else if (swiglu_grad) { cfg.dynamicSmemBytes = smem2_bytes(1); launched = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<1>, ta, tb, tc, tm, args); }
+  else if (two_sm) { cfg.dynamicSmemBytes = smem2_bytes(0); launched = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<0>, ta, tb, tc, tm, args); }
+  else { cfg.dynamicSmemBytes = SMEM_BYTES; launched = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, ta, tb, tc, args); }
+  OJC_CUDA(be, launched, op);
   OJC_LAUNCHED(be, op);
   if (be->profile_gemm) {
     OJC_CUDA(be, cudaEventRecord(sample.stop, be->stream), op);

@@ -145,6 +145,7 @@ __global__ void muon_norm_kernel(const double* __restrict__ part, int64_t nparts
 // In bf16 mode the norm, norm + eps and the quotient are each rounded (ojas-cpu/src/optim.rs:893-910).
 template <class TX>
 __global__ void muon_normalize_kernel(const float* __restrict__ u_all, const float* __restrict__ norm, TX* __restrict__ x_all, int rows, int cols, int tall, int bf16_mode) {
+  pdl_trigger();
   const int64_t n = (int64_t)rows * cols;
   const float* __restrict__ u = u_all + (int64_t)blockIdx.y * n;
   TX* __restrict__ x = x_all + (int64_t)blockIdx.y * n;
@@ -164,6 +165,7 @@ __global__ void muon_normalize_kernel(const float* __restrict__ u_all, const flo
 // grid (cols / 32, rows / 32, matrices), block (32, 8).
 template <class TX>
 __global__ void muon_normalize_tall_kernel(const float* __restrict__ u_all, const float* __restrict__ norm, TX* __restrict__ x_all, int rows, int cols, int bf16_mode) {
+  pdl_trigger();
   __shared__ float tile[32][33];
   const int64_t n = (int64_t)rows * cols;
   const float* __restrict__ u = u_all + (int64_t)blockIdx.z * n;
@@ -210,6 +212,7 @@ __global__ void muon_apply_tall_kernel(const MuonBatch mb, const TX* __restrict_
 
 // Wide matrices in bf16 mode, four elements per thread (n % 4 == 0): the same arithmetic as the scalar kernels.
 __global__ void muon_normalize_bf16x4_kernel(const float* __restrict__ u_all, const float* __restrict__ norm, bf16* __restrict__ x_all, int64_t n) {
+  pdl_trigger();
   const float4* __restrict__ u = reinterpret_cast<const float4*>(u_all + (int64_t)blockIdx.y * n);
   uint2* __restrict__ x = reinterpret_cast<uint2*>(x_all + (int64_t)blockIdx.y * n);
   const float nrm = norm[blockIdx.y];
@@ -256,6 +259,7 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 __global__ void ns_combine_a_bf16x8_kernel(const uint4* __restrict__ a, uint4* __restrict__ a2, int64_t n8, float bcoef, float ccoef) {
+  pdl_trigger();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n8; i += stride) {
     float av[8], a2v[8], r[8];
@@ -266,6 +270,7 @@ __global__ void ns_combine_a_bf16x8_kernel(const uint4* __restrict__ a, uint4* _
   }
 }
 __global__ void ns_combine_x_bf16x8_kernel(const uint4* __restrict__ x, uint4* __restrict__ bx, int64_t n8, float acoef, uint32_t* fault) {
+  pdl_trigger();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   bool bad = false;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n8; i += stride) {
@@ -281,6 +286,7 @@ __global__ void ns_combine_x_bf16x8_kernel(const uint4* __restrict__ x, uint4* _
 // out = b * A + c * A2 (A2 overwritten), every scalar multiple and the sum rounded in bf16 mode (optim.rs:947-957).
 template <class T>
 __global__ void ns_combine_a_kernel(const T* __restrict__ a, T* __restrict__ a2, int64_t n, float bcoef, float ccoef, int bf16_mode) {
+  pdl_trigger();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
     float av = ldf(a, i), a2v = ldf(a2, i);
@@ -292,6 +298,7 @@ __global__ void ns_combine_a_kernel(const T* __restrict__ a, T* __restrict__ a2,
 // bx = a * x + bx (optim.rs:966-974)
 template <class T>
 __global__ void ns_combine_x_kernel(const T* __restrict__ x, T* __restrict__ bx, int64_t n, float acoef, int bf16_mode, uint32_t* fault) {
+  pdl_trigger();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < n; i += stride) {
     float xv = ldf(x, i), bv = ldf(bx, i);

@@ -108,6 +108,7 @@ static ojc_status launch_ew(ojc_backend* be, const char* op, const ojc_tensor* a
 template <class TT, class TO>
 __global__ void embedding_gather_kernel(const TT* __restrict__ table, const uint32_t* __restrict__ ids, TO* __restrict__ out,
                                         int64_t tokens, int64_t dim, int64_t vocab, uint32_t* fault) {
+  pdl_trigger();
   // one warp per token row; the row is copied as bits (widened exactly when the table is bf16)
   const int lane = threadIdx.x & 31;
   int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;

@@ -180,6 +180,7 @@ __device__ __forceinline__ void softmax_tile(const FwdArgs& args, int b, int h, 
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, Fwd<D>::CTAS)
 sdpa_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }   // the swizzled tiles need 1024-byte alignment (whole CTA leaves)
@@ -422,6 +423,7 @@ __device__ __forceinline__ void softmax_tile2(const FwdArgs& args, int b, int h,
 template <int D>
 __global__ void __launch_bounds__(FWD2_THREADS, 1)
 sdpa_fwd2_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }
@@ -570,6 +572,7 @@ struct TileWalk {
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, FwdP<D>::CTAS)
 sdpa_fwdp_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }
@@ -897,6 +900,7 @@ template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dkv<D>::CTAS)
 sdpa_bwd_dkv_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                             const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }   // the swizzled tiles need 1024-byte alignment (whole CTA leaves)
@@ -1101,6 +1105,7 @@ template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dq<D>::CTAS)
 sdpa_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -1291,6 +1296,7 @@ template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dq<D>::CTAS)
 sdpa_bwd_dq_p_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -1477,6 +1483,7 @@ template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, Dkv<D>::CTAS)
 sdpa_bwd_dkv_p_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_g, const BwdArgs args) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) { if (threadIdx.x == 0) raise_fault(args.fault, OP_SDPA); return; }
