@@ -78,16 +78,23 @@ def token_batches(count: int, batch: int, seq: int, vocab: int, seed: int):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 100 ms; the lines that arrive while the timed region runs are the ones reported."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device: int):
         self.device, self.lines, self.proc = device, [], None
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.device)],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.device)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -96,7 +103,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -109,7 +116,10 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        # The sampler is started before the warm-up steps (nvidia-smi takes longer to produce its first line than a short timed region
+        # lasts); only lines that arrived between mark_start and mark_end count.
+        inside = [line for ts, line in self.lines if self.t0 is None or (self.t0 <= ts <= (self.t1 if self.t1 is not None else ts))]
+        for line in inside:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -324,11 +334,13 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         px, py = pinned[i % n_batches]
         return tr.step_host_ptrs(px.data_ptr(), py.data_ptr())
 
-    for i in range(warm):
-        step_resident(i)
-    launches0 = be.kernel_launches()
     with ClockSampler(local_rank) as clocks:
+        for i in range(warm):
+            step_resident(i)
+        launches0 = be.kernel_launches()
+        clocks.mark_start()
         ms, rep = timed(step_resident, args.steps)
+        clocks.mark_end()
     launches = be.kernel_launches() - launches0
     exposed_ms = tr.exposed_exchange_ms() if comm is not None else None
     # Roofline pass: the same K steps again with the weight-gradient GEMMs folded back into the one stream, so every GEMM launch
