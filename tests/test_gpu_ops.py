@@ -137,7 +137,8 @@ def test_causal_sdpa_f32_tier(be, shape, hkv, window):
 
 @pytest.mark.parametrize("shape,hkv,window", [((1, 2, 300, 64), 2, None), ((2, 4, 128, 64), 2, None), ((1, 2, 129, 128), 2, None), ((1, 2, 200, 64), 1, 40),
                                               ((1, 1, 64, 64), 1, None), ((1, 2, 1, 64), 2, None), ((2, 3, 1024, 64), 3, None),
-                                              ((1, 2, 256, 128), 2, None), ((2, 4, 384, 128), 2, None), ((1, 1, 132, 128), 1, None), ((1, 2, 640, 128), 1, None)])
+                                              ((1, 2, 256, 128), 2, None), ((2, 4, 384, 128), 2, None), ((1, 1, 132, 128), 1, None), ((1, 2, 640, 128), 1, None),
+                                              ((1, 2, 64, 128), 1, None), ((2, 2, 100, 128), 2, None), ((1, 1, 4, 128), 1, None)])
 def test_causal_sdpa_bf16_tensor_core_tier(be, shape, hkv, window):
     """bf16 q/k/v on the tensor-core kernels, against the f32 oracle on the same bf16-exact inputs: 2e-2 relative."""
     from ojas_b200 import DType
