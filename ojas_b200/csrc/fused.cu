@@ -192,16 +192,21 @@ __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, con
   float* mine = red + warp * heads;
   for (int h = lane; h < heads; h += 32) mine[h] = 0.0f;
   __syncwarp();
+  const int per_shift = 31 - __clz(per);    // per is a power of two: head and piece of a chunk by shift and mask
+  const int chunks = heads * per;
   for (int64_t row = (int64_t)blockIdx.x * nwarps + warp; row < rows; row += (int64_t)gridDim.x * nwarps) {
-    const int chunks = heads * per;
+    // once per row, not per head: the token's batch and time step (64-bit divisions cost this kernel its issue slots otherwise)
+    const int64_t rb = dr ? row / time : 0, rt = row - rb * time;
+    const float* srow = scales + row * heads;
+    const int64_t base = row * heads * (int64_t)dh;
     for (int c = lane; c < ((chunks + 31) / 32) * 32; c += 32) {
       const bool ok = c < chunks;
-      const int h = ok ? c / per : 0;
+      const int h = ok ? c >> per_shift : 0;
       float dot = 0.0f, g = 0.0f;
       if (ok) {
-        g = scales[row * heads + h];
+        g = srow[h];
         float a[8], go[8];
-        const int64_t off = (row * heads) * dh + (int64_t)c * 8;
+        const int64_t off = base + c * 8;
         load8(attn + off, a); load8(gout + off, go);
 #pragma unroll
         for (int k = 0; k < 8; ++k) { dot += go[k] * a[k]; go[k] *= g; }
@@ -209,11 +214,11 @@ __global__ void gate_apply_backward_kernel(const float* __restrict__ scales, con
       }
       // the `per` lanes of one head are contiguous (per divides 32 for head_dim 64 / 128 / 256)
       for (int o = per / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (ok && (c % per) == 0) {
+      if (ok && (c & (per - 1)) == 0) {
         const float zg = dot * g * (1.0f - g);
         gz[row * zld + h] = __float2bfloat16_rn(zg);
         mine[h] += zg;
-        if (dr) dr[((row / time) * heads + h) * (int64_t)time + row % time] = dot * g;
+        if (dr) dr[(rb * heads + h) * (int64_t)time + rt] = dot * g;
       }
     }
     for (int h = heads + lane; h < zld; h += 32) gz[row * zld + h] = __float2bfloat16_rn(0.0f);
