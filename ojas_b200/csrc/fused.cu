@@ -159,23 +159,25 @@ __global__ void fused_column_sum_kernel(const float* __restrict__ part, float* _
 
 // out = attn * sigmoid(z + b) per head; z: [rows, zld] logits (zld >= heads), scales (optional) keeps the sigmoid.
 // One thread per 8 contiguous values of one (row, head).
-__global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, const float* __restrict__ bias, const bf16* __restrict__ attn, bf16* __restrict__ out,
+__global__ void gate_apply_forward_kernel(const bf16* __restrict__ z, int zld, const bf16* __restrict__ attn, const float* __restrict__ bias, bf16* __restrict__ out,
                                           float* __restrict__ scales, int64_t rows, int heads, int dh) {
   pdl_trigger();
-  const int per = dh / 8;
-  const int64_t total = rows * heads * per;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (const int64_t stride = (int64_t)gridDim.x * blockDim.x; i < total; i += stride) {
-    const int64_t rh = i / per;
-    const int64_t row = rh / heads;
-    const int h = (int)(rh % heads);
-    const float g = sigmoid_fast(__bfloat162float(z[row * zld + h]) + bias[h]);
-    if (scales && (i % per) == 0) scales[rh] = g;
-    float v[8];
-    load8(attn + i * 8, v);
+  // threadIdx.x walks the 16-byte chunks of a token's row, threadIdx.y the tokens: a thread's head is fixed, no division per element
+  const int per = dh / 8, chunks = heads * per;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const int h = c / per;
+    const bool first = c % per == 0;
+    const float bh = bias[h];
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; row < rows; row += (int64_t)gridDim.x * blockDim.y) {
+      const float g = sigmoid_fast(__bfloat162float(z[row * zld + h]) + bh);
+      if (scales && first) scales[row * heads + h] = g;
+      const int64_t off = (row * chunks + c) * 8;
+      float v[8];
+      load8(attn + off, v);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) v[k] *= g;
-    store8(out + i * 8, v);
+      for (int k = 0; k < 8; ++k) v[k] *= g;
+      store8(out + off, v);
+    }
   }
 }
 
@@ -479,8 +481,10 @@ ojc_status qk_norm_rope_backward(ojc_backend* be, const bf16* x, int64_t xs, con
 ojc_status gate_apply_forward(ojc_backend* be, const bf16* z, int zld, const float* bias, const bf16* attn, bf16* out, float* scales, int64_t rows, int heads, int dh) {
   const char* op = "per_head_sigmoid_gate_forward";
   if (dh % 8 != 0) return ojc_fail(OJC_ERR_UNSUPPORTED_HEAD_DIM, op, "head_dim must be a multiple of 8");
-  const int64_t total = rows * heads * (dh / 8);
-  gate_apply_forward_kernel<<<elementwise_grid(be, total, 256), 256, 0, be->stream>>>(z, zld, bias, attn, out, scales, rows, heads, dh);
+  const int chunks = heads * (dh / 8);
+  const int tx = chunks >= 256 ? 256 : ((chunks + 31) / 32) * 32, ty = 256 / tx > 0 ? (256 / tx < 4 ? 256 / tx : 4) : 1;
+  const int64_t passes = (rows + ty - 1) / ty;
+  gate_apply_forward_kernel<<<elementwise_grid(be, passes * tx * ty, tx * ty), dim3(tx, ty), 0, be->stream>>>(z, zld, attn, bias, out, scales, rows, heads, dh);
   OJC_LAUNCHED(be, op);
   return OJC_OK;
 }
