@@ -33,6 +33,7 @@ template <int TPR> __device__ __forceinline__ float row_sum(float v) {
 }
 
 // y = rope(rms_norm(x) * w). x, y: [tokens, heads, dh] with a token stride (so a column slice of a wider buffer works);
+// cos_t / sin_t: [time, dh] tables whose second half of columns repeats the first, as the step driver builds them (block.rs:62-85).
 // TPR = dh / 16 threads per (token, head lane), each owning columns [8 part, 8 part + 8) of both halves, i.e. whole rotation
 // pairs, and walking every HL-th head: the weight, cosine and sine values it needs are the same for every head of its token,
 // and the HL heads side by side make one warp load cover HL * 128 contiguous bytes of a token's row (DRAM page locality).
@@ -47,10 +48,11 @@ __global__ void qk_norm_rope_forward_kernel(const bf16* __restrict__ x, int64_t 
   const bool live = tok_raw < tokens;
   const int64_t token = live ? tok_raw : tokens - 1;
   const int t = (int)(token % time), c0 = part * 8;
-  float wa[8], wb[8], c1[8], c2[8], s1[8], s2[8];
+  // the rotation tables repeat their first half in their second (one frequency per pair of columns i, i + HALF): one load serves both
+  float wa[8], wb[8], c1[8], s1[8];
   load8f(w + c0, wa); load8f(w + HALF + c0, wb);
-  load8f(cos_t + (int64_t)t * DH + c0, c1); load8f(cos_t + (int64_t)t * DH + HALF + c0, c2);
-  load8f(sin_t + (int64_t)t * DH + c0, s1); load8f(sin_t + (int64_t)t * DH + HALF + c0, s2);
+  load8f(cos_t + (int64_t)t * DH + c0, c1);
+  load8f(sin_t + (int64_t)t * DH + c0, s1);
   const bf16* src = x + token * xs + c0;
   bf16* dst = y + token * ys + c0;
 #pragma unroll 4
@@ -67,7 +69,7 @@ __global__ void qk_norm_rope_forward_kernel(const bf16* __restrict__ x, int64_t 
     for (int i = 0; i < 8; ++i) {
       const float an = a[i] * rstd * wa[i], bn = b[i] * rstd * wb[i];
       y1[i] = an * c1[i] - bn * s1[i];
-      y2[i] = bn * c2[i] + an * s2[i];
+      y2[i] = bn * c1[i] + an * s1[i];
     }
     if (live) { store8(dst + head * DH, y1); store8(dst + head * DH + HALF, y2); }
   }
@@ -95,9 +97,9 @@ __global__ void __launch_bounds__(128, 4) qk_norm_rope_backward_kernel(const bf1
     const bool live = tok_raw < tokens;
     const int64_t token = live ? tok_raw : tokens - 1;
     const int t = (int)(token % time);
-    float c1[8], c2[8], s1[8], s2[8];
-    load8f(cos_t + (int64_t)t * DH + c0, c1); load8f(cos_t + (int64_t)t * DH + HALF + c0, c2);
-    load8f(sin_t + (int64_t)t * DH + c0, s1); load8f(sin_t + (int64_t)t * DH + HALF + c0, s2);
+    float c1[8], s1[8];                        // both halves of the tables hold the same values
+    load8f(cos_t + (int64_t)t * DH + c0, c1);
+    load8f(sin_t + (int64_t)t * DH + c0, s1);
     const bf16* xsrc = x + token * xs + c0;
     const bf16* gsrc = gy + token * gys + c0;
     bf16* dst = gx + token * gxs + c0;
@@ -114,8 +116,8 @@ __global__ void __launch_bounds__(128, 4) qk_norm_rope_backward_kernel(const bf1
       float da[8], db[8], dot = 0.0f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        da[i] = ga[i] * c1[i] + gb[i] * s2[i];    // d/d(an): rope backward (ojas-cpu/src/norm.rs:303-306)
-        db[i] = -ga[i] * s1[i] + gb[i] * c2[i];
+        da[i] = ga[i] * c1[i] + gb[i] * s1[i];    // d/d(an): rope backward (ojas-cpu/src/norm.rs:303-306)
+        db[i] = -ga[i] * s1[i] + gb[i] * c1[i];
         a[i] *= rstd; b[i] *= rstd;               // x hat
         dot += (da[i] * wa[i]) * a[i] + (db[i] * wb[i]) * b[i];
       }
